@@ -1,0 +1,245 @@
+// Device routines for the GGUF expert formats: codebook tables in shared memory, exact integer
+// decode of IQ3_S / IQ4_NL sub-blocks into dp4a operands, and the Q8_K / Q8_0 activation
+// quantizers. The GEMV kernels and the parity probes call the same functions.
+//
+// Format definitions follow third_party/ggml-iq/ggml-iq.h:81-96 and the reference dequantizers
+// third_party/ggml-iq/ggml-iq.c:231-288 of the reference project.
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "iq_codebooks.h"
+
+namespace fb {
+
+// ------------------------------------------------------------------------------ tables
+// IQ3_S codebook in shared memory, replicated once per lane: entry i of lane l lives at word
+// i*32 + l, so a warp's 32 independent look-ups always hit 32 different banks.
+constexpr int kGridRepWords = 512 * 32;
+constexpr int kGridRepBytes = kGridRepWords * 4;  // 65536
+// Sign masks: nibble n -> four bytes, 0xFF where bit j of n is set. 16 words, 16 banks.
+constexpr int kSignTabWords = 16;
+
+// One copy per translation unit (internal linkage), initialised at load time.
+static __constant__ uint16_t c_iq3s_grid_packed[512] = {FB_IQ3S_GRID_PACKED};
+
+__device__ __forceinline__ uint32_t iq3s_grid_entry(int i) {
+  const uint32_t p = c_iq3s_grid_packed[i];
+  uint32_t w = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) w |= (2u * ((p >> (3 * j)) & 7u) + 1u) << (8 * j);
+  return w;
+}
+
+// Called by every thread of the block; caller synchronizes afterwards.
+__device__ __forceinline__ void iq3s_tables_fill(uint32_t* gridrep, uint32_t* signtab) {
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) {
+    const uint32_t w = iq3s_grid_entry(i);
+    uint4 v = make_uint4(w, w, w, w);
+    uint4* dst = reinterpret_cast<uint4*>(gridrep + i * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[j] = v;
+  }
+  if (threadIdx.x < 16) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (threadIdx.x & (1 << j)) m |= 0xFFu << (8 * j);
+    signtab[threadIdx.x] = m;
+  }
+}
+
+// ------------------------------------------------------------------------------ IQ3_S
+// One 32-weight sub-block: qs_lo/qs_hi = its 8 index bytes, qh = the byte with the 8 ninth index
+// bits, signs = its 4 sign bytes. Produces 8 words of four signed int8 weights in element order.
+// grid_lane = gridrep + lane.
+__device__ __forceinline__ void iq3s_decode32(uint32_t qs_lo, uint32_t qs_hi, uint32_t qh, uint32_t signs,
+                                              const uint32_t* grid_lane, const uint32_t* signtab, int (&w)[8]) {
+#pragma unroll
+  for (int l = 0; l < 8; ++l) {
+    const uint32_t src = l < 4 ? qs_lo : qs_hi;
+    const uint32_t q = (src >> (8 * (l & 3))) & 0xFFu;
+    const uint32_t idx = q | (((qh >> l) & 1u) << 8);
+    const uint32_t g = grid_lane[idx * 32];
+    const uint32_t m = signtab[(signs >> (4 * l)) & 0xFu];
+    // Byte-wise negation where m = 0xFF: (g ^ 0xFF) + 1 never carries because every magnitude is odd.
+    w[l] = int((g ^ m) + (m & 0x01010101u));
+  }
+}
+
+// 4 bytes at a static byte offset (a multiple of 2) of a word-aligned unit in shared memory.
+template <int OFF>
+__device__ __forceinline__ uint32_t ld4(const uint32_t* u) {
+  if constexpr (OFF % 4 == 0) return u[OFF / 4];
+  else return __byte_perm(u[OFF / 4], u[OFF / 4 + 1], 0x5432);
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t ld1(const uint32_t* u) {
+  return (u[OFF / 4] >> (8 * (OFF % 4))) & 0xFFu;
+}
+template <int OFF>
+__device__ __forceinline__ float ld_fp16(const uint32_t* u) {
+  const uint32_t v = u[OFF / 4] >> (8 * (OFF % 4));
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(v & 0xFFFFu)));
+}
+
+// dp4a of 8 weight words with 32 int8 activations at `a` (16-byte aligned shared memory).
+__device__ __forceinline__ int dot32(const int (&w)[8], const int8_t* a) {
+  const int4 a0 = *reinterpret_cast<const int4*>(a);
+  const int4 a1 = *reinterpret_cast<const int4*>(a + 16);
+  int s = __dp4a(w[0], a0.x, 0);
+  s = __dp4a(w[1], a0.y, s);
+  s = __dp4a(w[2], a0.z, s);
+  s = __dp4a(w[3], a0.w, s);
+  s = __dp4a(w[4], a1.x, s);
+  s = __dp4a(w[5], a1.y, s);
+  s = __dp4a(w[6], a1.z, s);
+  s = __dp4a(w[7], a1.w, s);
+  return s;
+}
+
+// Sub-block IB of the IQ3_S block at static byte offset BASE of a word-aligned unit:
+// bsum[t] += (2*s+1) * sum_i w_i * a_t,i, exact in int32.
+template <int BASE, int IB, int TT>
+__device__ __forceinline__ void iq3s_sub_idot(const uint32_t* unit, uint32_t sc, const uint32_t* grid_lane,
+                                              const uint32_t* signtab, const int8_t* const (&act)[TT],
+                                              int (&bsum)[TT]) {
+  int w[8];
+  iq3s_decode32(ld4<BASE + 2 + 8 * IB>(unit), ld4<BASE + 6 + 8 * IB>(unit), ld1<BASE + 66 + IB>(unit),
+                ld4<BASE + 74 + 4 * IB>(unit), grid_lane, signtab, w);
+  const int mult = 2 * int((sc >> (4 * IB)) & 0xFu) + 1;
+#pragma unroll
+  for (int t = 0; t < TT; ++t) bsum[t] += dot32(w, act[t] + 32 * IB) * mult;
+}
+
+// Integer dot of one IQ3_S block with TT activation blocks; act[t] points at the 256 int8 of the
+// matching Q8_K block. |bsum| < 2^24, so float(bsum) is exact.
+template <int BASE, int TT>
+__device__ __forceinline__ void iq3s_block_idot(const uint32_t* unit, const uint32_t* grid_lane,
+                                                const uint32_t* signtab, const int8_t* const (&act)[TT],
+                                                int (&bsum)[TT]) {
+  const uint32_t sc = ld4<BASE + 106>(unit);
+#pragma unroll
+  for (int t = 0; t < TT; ++t) bsum[t] = 0;
+  iq3s_sub_idot<BASE, 0, TT>(unit, sc, grid_lane, signtab, act, bsum);
+  iq3s_sub_idot<BASE, 1, TT>(unit, sc, grid_lane, signtab, act, bsum);
+  iq3s_sub_idot<BASE, 2, TT>(unit, sc, grid_lane, signtab, act, bsum);
+  iq3s_sub_idot<BASE, 3, TT>(unit, sc, grid_lane, signtab, act, bsum);
+  iq3s_sub_idot<BASE, 4, TT>(unit, sc, grid_lane, signtab, act, bsum);
+  iq3s_sub_idot<BASE, 5, TT>(unit, sc, grid_lane, signtab, act, bsum);
+  iq3s_sub_idot<BASE, 6, TT>(unit, sc, grid_lane, signtab, act, bsum);
+  iq3s_sub_idot<BASE, 7, TT>(unit, sc, grid_lane, signtab, act, bsum);
+}
+
+// ------------------------------------------------------------------------------ IQ4_NL
+// The 16 levels held in four registers for byte-permute look-ups.
+struct Iq4nlLevels {
+  uint32_t t0, t1, t2, t3;
+};
+__host__ __device__ constexpr uint32_t iq4nl_pack4(int q) {
+  constexpr int lv[16] = {FB_IQ4NL_LEVELS};
+  return uint32_t(uint8_t(lv[4 * q])) | (uint32_t(uint8_t(lv[4 * q + 1])) << 8) |
+         (uint32_t(uint8_t(lv[4 * q + 2])) << 16) | (uint32_t(uint8_t(lv[4 * q + 3])) << 24);
+}
+__device__ __forceinline__ Iq4nlLevels iq4nl_levels() {
+  constexpr uint32_t a = iq4nl_pack4(0), b = iq4nl_pack4(1), c = iq4nl_pack4(2), d = iq4nl_pack4(3);
+  Iq4nlLevels L;
+  L.t0 = a;
+  L.t1 = b;
+  L.t2 = c;
+  L.t3 = d;
+  return L;
+}
+__host__ __device__ constexpr int iq4nl_level(int i) {
+  constexpr int lv[16] = {FB_IQ4NL_LEVELS};
+  return lv[i];
+}
+// Four nibbles n0..n3 (n0 in bits 0-3 of h16) -> four int8 levels, byte i = level[n_i].
+__device__ __forceinline__ uint32_t iq4nl_lookup4(const Iq4nlLevels& L, uint32_t h16) {
+  const uint32_t sel = h16 & 0x7777u;
+  const uint32_t lo = __byte_perm(L.t0, L.t1, sel);
+  const uint32_t hi = __byte_perm(L.t2, L.t3, sel);
+  return __byte_perm(lo, hi, 0x3210u | ((h16 >> 1) & 0x4444u));
+}
+// One 32-weight block from its 16 nibble bytes (4 words). Output word 2m+h (m = word, h = half)
+// holds weights of elements {4m+2h, 4m+2h+16, 4m+2h+1, 4m+2h+17}: activations are stored in
+// that interleaved order (see q8_0_interleave_index).
+__device__ __forceinline__ void iq4nl_decode32(const Iq4nlLevels& L, const uint32_t (&q)[4], int (&w)[8]) {
+#pragma unroll
+  for (int m = 0; m < 4; ++m) {
+    w[2 * m] = int(iq4nl_lookup4(L, q[m] & 0xFFFFu));
+    w[2 * m + 1] = int(iq4nl_lookup4(L, q[m] >> 16));
+  }
+}
+// Position of element e (0..31) of a Q8_0 block in the interleaved activation order.
+__host__ __device__ __forceinline__ int q8_0_interleave_index(int e) {
+  return 2 * (e & 15) + (e >> 4);  // nibble byte e%16, low nibble first
+}
+
+// ------------------------------------------------------------------------------ quantizers
+// Q8_K of one 256-value block by one warp; lane l holds elements 8l..8l+7 in v.
+// quantize_row_q8_K_ref, third_party/ggml-iq/ggml-iq.c:313-350: max is the FIRST element of
+// largest magnitude (signed), iscale = -127/max, q = min(127, rne(iscale*x)), d = 1/iscale; an
+// all-zero block gives d = 0, q = 0, bsums = 0 (src/cpu/q8_cpu.h:7-8).
+// Returns d; q[8] are this lane's codes; pair_sum is the sum of the 16 codes of this lane's group
+// of 16 (valid in both lanes of the pair).
+__device__ __forceinline__ float q8k_block_warp(const float (&v)[8], int (&q)[8], int& pair_sum) {
+  const int lane = threadIdx.x & 31;
+  float amax = 0.0f;
+  int idx = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float a = fabsf(v[i]);
+    if (a > amax) {
+      amax = a;
+      idx = 8 * lane + i;
+    }
+  }
+  if (amax == 0.0f) idx = 0x7fffffff;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (oa > amax || (oa == amax && oi < idx)) {
+      amax = oa;
+      idx = oi;
+    }
+  }
+  if (amax == 0.0f) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = 0;
+    pair_sum = 0;
+    return 0.0f;
+  }
+  float cand = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if ((idx & 7) == i) cand = v[i];
+  const float mx = __shfl_sync(0xffffffffu, cand, idx >> 3);
+  const float iscale = __fdiv_rn(-127.0f, mx);
+  int s = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = __float2int_rn(__fmul_rn(iscale, v[i]));
+    q[i] = r < 127 ? r : 127;
+    s += q[i];
+  }
+  pair_sum = s + __shfl_xor_sync(0xffffffffu, s, 1);
+  return __fdiv_rn(1.0f, iscale);
+}
+
+// Q8_0 of one 32-value block by one warp; lane l holds element l.
+// quantize_row_q8_0_ref, third_party/ggml-iq/ggml-iq.c:75-98: d = amax/127 stored as fp16,
+// id = 1/d computed in fp32 from the unrounded d, q = roundf(x*id).
+__device__ __forceinline__ int q8_0_block_warp(float v, unsigned short& d_half) {
+  float amax = fabsf(v);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float d = __fdiv_rn(amax, 127.0f);
+  const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+  d_half = __half_as_ushort(__float2half_rn(d));
+  return int(roundf(__fmul_rn(v, id)));
+}
+
+}  // namespace fb

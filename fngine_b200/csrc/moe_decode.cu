@@ -1,0 +1,1076 @@
+// Decode-width (T <= 16) routed-expert kernels on native GGUF expert bytes.
+//
+//   select   router top-10, sorted work list, once-per-token activation quantization
+//   gate_up  h[pair][j] = silu(gate_j . x) * (up_j . x)
+//   down     partial[pair][n] = w_pair * (down_n . q8(h[pair]))
+//   combine  y[t] = sum of token t's partials in slot order (+ shared, + residual write)
+//
+// gate_up and down are persistent, one CTA per SM. A producer warp streams whole row groups of the
+// expert blob into a two-stage shared-memory ring with 1-D bulk async copies (TMA, no multicast)
+// signalled through mbarriers; consumer warps decode the blocks from shared memory with the
+// codebooks held there and accumulate exact int8 dot products (dp4a). Numerics are those of the
+// reference's CPU expert tier (src/cpu/iq_cpu.h:12-40 of the reference project): Q8_K activations
+// for IQ3_S weights, Q8_0 for IQ4_NL, integer sums per block, one fp32 scale step per block.
+#include "iq_decode.cuh"
+
+#include <cuda_bf16.h>
+
+namespace fb {
+namespace {
+
+constexpr int H = FB_HIDDEN;
+constexpr int kTopK = FB_TOPK;
+constexpr int kExperts = FB_EXPERTS;
+constexpr int kMaxTok = FB_DECODE_MAX_TOKENS;
+constexpr int kMaxPairs = FB_DECODE_MAX_PAIRS;
+constexpr int kTT = 2;  // tokens of one work item handled per pass over a staged tile
+
+__host__ __device__ constexpr int act_row_bytes_planar(int act, int k) {
+  return act == FB_ACT_Q8_K ? k + 64 : k + k / 8;
+}
+__host__ __device__ constexpr int act_of(int fmt) { return fmt == FB_FMT_IQ3_S ? FB_ACT_Q8_K : FB_ACT_Q8_0; }
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + expf(-g)) * u; }
+
+// ------------------------------------------------------------------------------ activation rows
+// One row of k values -> planar codes + scales, by the calling block (any number of warps).
+// Q8_K: codes [k], scales float[k/256]. Q8_0: codes [k] (interleaved per block), scales float[k/32].
+template <class LoadF>
+__device__ __forceinline__ void quantize_row_planar(int act, int k, LoadF load, uint8_t* out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  if (act == FB_ACT_Q8_K) {
+    float* scales = reinterpret_cast<float*>(out + k);
+    for (int b = warp; b < k / 256; b += warps) {
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = load(256 * b + 8 * lane + i);
+      int q[8], ps;
+      const float d = q8k_block_warp(v, q, ps);
+      uint2 pk;
+      pk.x = uint32_t(uint8_t(q[0])) | (uint32_t(uint8_t(q[1])) << 8) | (uint32_t(uint8_t(q[2])) << 16) |
+             (uint32_t(uint8_t(q[3])) << 24);
+      pk.y = uint32_t(uint8_t(q[4])) | (uint32_t(uint8_t(q[5])) << 8) | (uint32_t(uint8_t(q[6])) << 16) |
+             (uint32_t(uint8_t(q[7])) << 24);
+      *reinterpret_cast<uint2*>(out + 256 * b + 8 * lane) = pk;
+      if (lane == 0) scales[b] = d;
+    }
+  } else {
+    float* scales = reinterpret_cast<float*>(out + k);
+    for (int b = warp; b < k / 32; b += warps) {
+      unsigned short dh;
+      const int q = q8_0_block_warp(load(32 * b + lane), dh);
+      out[32 * b + q8_0_interleave_index(lane)] = uint8_t(int8_t(q));
+      if (lane == 0) scales[b] = __half2float(__ushort_as_half(dh));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ router
+// logits[t][r] = sum_k W[r][k] * x[t][k]; one warp per row, lane-strided 16-byte chunks, the 32
+// lane sums added by a butterfly. Fixed order: repeated calls are bitwise identical.
+template <bool XBF16>
+__global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* __restrict__ w, int rows,
+                                                     const void* __restrict__ xv, int tokens,
+                                                     float* __restrict__ logits, int stride) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float wr[80];
+  const uint4* wp = reinterpret_cast<const uint4*>(w + size_t(row) * H);
+#pragma unroll
+  for (int c = 0; c < 10; ++c) {
+    const uint4 v = wp[c * 32 + lane];
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      wr[8 * c + 2 * i] = __uint_as_float(u[i] << 16);
+      wr[8 * c + 2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u);
+    }
+  }
+  for (int t = 0; t < tokens; ++t) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 10; ++c) {
+      float xs[8];
+      if constexpr (XBF16) {
+        const uint4 v = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xv) + size_t(t) * H)[c * 32 + lane];
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          xs[2 * i] = __uint_as_float(u[i] << 16);
+          xs[2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u);
+        }
+      } else {
+        const float4* xp = reinterpret_cast<const float4*>(static_cast<const float*>(xv) + size_t(t) * H) + (c * 32 + lane) * 2;
+        const float4 a = xp[0], b = xp[1];
+        xs[0] = a.x; xs[1] = a.y; xs[2] = a.z; xs[3] = a.w;
+        xs[4] = b.x; xs[5] = b.y; xs[6] = b.z; xs[7] = b.w;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc = fmaf(wr[8 * c + i], xs[i], acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) logits[size_t(t) * stride + row] = acc;
+  }
+}
+
+// ------------------------------------------------------------------------------ select
+// Top-k of 512 logits by one warp (lane l holds logits l + 32 i): value descending, ties to the
+// lower id, NaN never wins, -0 == +0; weights = softmax over the winners in fp32
+// (src/kernels/moe/moe_common.cuh:33-85 of the reference states the same contract).
+__device__ __forceinline__ void warp_topk(const float* logits, int* ids, float* weights) {
+  const int lane = threadIdx.x & 31;
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float x = logits[lane + 32 * i];
+    if (x != x) x = -INFINITY;
+    v[i] = x;
+  }
+  uint32_t taken = 0;
+  float vals[kTopK];
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) {
+    float bv = 0.0f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const bool free_ = !((taken >> i) & 1u);
+      if (free_ && (bi == 0x7fffffff || v[i] > bv)) {
+        bv = v[i];
+        bi = lane + 32 * i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      const bool take = bi == 0x7fffffff ? oi != 0x7fffffff
+                                         : (oi != 0x7fffffff && (ov > bv || (ov == bv && oi < bi)));
+      if (take) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+    ids[k] = bi;
+    vals[k] = bv;
+  }
+  float sum = 0.0f;
+  const float top = vals[0];
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) {
+    vals[k] = expf(vals[k] - top);
+    sum += vals[k];
+  }
+  const float inv = __fdiv_rn(1.0f, sum);
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) weights[k] = vals[k] * inv;
+}
+
+template <bool XBF16>
+__global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ logits, int logits_stride,
+                                                     const void* __restrict__ xv, const int32_t* __restrict__ slot_of,
+                                                     int T, fb_moe_decode_workspace ws,
+                                                     uint32_t* __restrict__ counts) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (blockIdx.x > 0) {
+    const int t = blockIdx.x - 1;
+    auto load = [&](int i) -> float {
+      if constexpr (XBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(xv)[size_t(t) * H + i]);
+      else return static_cast<const float*>(xv)[size_t(t) * H + i];
+    };
+    quantize_row_planar(act_of(ws.gate_up_format), H, load, ws.xq + size_t(t) * FB_XQ_STRIDE);
+    return;
+  }
+  __shared__ int s_id[kMaxTok][kTopK];
+  __shared__ float s_w[kMaxTok][kTopK];
+  __shared__ int s_slot[kMaxTok][kTopK];
+  __shared__ int s_pair[kMaxTok][kTopK];
+  __shared__ int s_cnt[kExperts];
+  __shared__ int s_begin[kExperts];
+  __shared__ int s_hot_slot[kMaxPairs];
+  __shared__ int s_hot_cnt[kMaxPairs];
+  __shared__ int s_scan[2][16];
+  __shared__ int s_bad;
+  fb_moe_decode_work* work = ws.work;
+  s_cnt[tid] = 0;
+  if (tid == 0) s_bad = 0;
+  if (tid < kMaxPairs) ws.item_done[tid] = 0;
+  if (warp < T) {
+    int ids[kTopK];
+    float w[kTopK];
+    warp_topk(logits + size_t(warp) * logits_stride, ids, w);
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k)
+      if (lane == k) {
+        s_id[warp][k] = ids[k];
+        s_w[warp][k] = w[k];
+      }
+  }
+  __syncthreads();
+  const int pt = tid / kTopK, pk = tid % kTopK;
+  const bool valid = tid < T * kTopK;
+  int my_slot = -1;
+  if (valid) {
+    const int e = s_id[pt][pk];
+    my_slot = slot_of ? slot_of[e] : e;
+    s_slot[pt][pk] = my_slot;
+    if (my_slot >= 0) atomicAdd(&s_cnt[e], 1);
+    else s_bad = 1;
+    if (counts) atomicAdd(&counts[e], 1u);
+  }
+  __syncthreads();
+  // Compact the hot experts (expert order), then rank them by physical slot.
+  const int c = s_cnt[tid];
+  int incl_c = c, incl_n = c > 0 ? 1 : 0;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, incl_c, o), b = __shfl_up_sync(0xffffffffu, incl_n, o);
+    if (lane >= o) {
+      incl_c += a;
+      incl_n += b;
+    }
+  }
+  if (lane == 31) {
+    s_scan[0][warp] = incl_c;
+    s_scan[1][warp] = incl_n;
+  }
+  __syncthreads();
+  int base_n = 0, n_pairs = 0, n_items = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (i < warp) base_n += s_scan[1][i];
+    n_pairs += s_scan[0][i];
+    n_items += s_scan[1][i];
+  }
+  const int compact = base_n + incl_n - (c > 0 ? 1 : 0);
+  const int e_slot = slot_of ? slot_of[tid] : tid;
+  if (c > 0) {
+    s_hot_slot[compact] = e_slot;
+    s_hot_cnt[compact] = c;
+  }
+  __syncthreads();
+  if (c > 0) {
+    int item = 0, pair_begin = 0;
+    for (int i = 0; i < n_items; ++i)
+      if (s_hot_slot[i] < e_slot) {
+        ++item;
+        pair_begin += s_hot_cnt[i];
+      }
+    s_begin[tid] = pair_begin;
+    work->item_slot[item] = e_slot;
+    work->item_pair_begin[item] = pair_begin;
+  }
+  if (tid == 0) {
+    work->item_pair_begin[n_items] = n_pairs;
+    work->n_items = n_items;
+    work->n_pairs = n_pairs;
+    work->tokens = T;
+  }
+  __syncthreads();
+  if (valid) {
+    int idx = -1;
+    if (my_slot >= 0) {
+      const int e = s_id[pt][pk];
+      int rank = 0;
+      for (int t2 = 0; t2 < pt; ++t2)
+        for (int k2 = 0; k2 < kTopK; ++k2) rank += s_id[t2][k2] == e ? 1 : 0;
+      idx = s_begin[e] + rank;
+      work->pair_token[idx] = pt;
+      work->pair_weight[idx] = s_w[pt][pk];
+    }
+    s_pair[pt][pk] = idx;
+    work->topk_expert[pt][pk] = s_id[pt][pk];
+    work->topk_weight[pt][pk] = s_w[pt][pk];
+  }
+  __syncthreads();
+  if (tid < T) {
+    int nh = 0, nc = 0;
+    for (int k = 0; k < kTopK; ++k) {
+      const int idx = s_pair[tid][k];
+      if (idx >= 0) {
+        int rank = 0;
+        for (int k2 = 0; k2 < kTopK; ++k2) rank += (s_pair[tid][k2] >= 0 && s_pair[tid][k2] < idx) ? 1 : 0;
+        work->token_pairs[tid][rank] = idx;
+        ++nh;
+      } else {
+        ++nc;
+      }
+    }
+    work->token_pair_count[tid] = nh;
+    work->token_cold_count[tid] = nc;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int n_cold = 0;
+    for (int t = 0; t < T; ++t)
+      for (int k = 0; k < kTopK; ++k) n_cold += s_pair[t][k] < 0 ? 1 : 0;
+    work->n_cold = n_cold;
+    if (s_bad) atomicMax(ws.status, uint32_t(FB_STATUS_BAD_WORK));
+  }
+}
+
+// ------------------------------------------------------------------------------ streaming skeleton
+struct TileInfo {
+  int item, sub, pair_begin, n_tok;
+  const uint8_t* blob;
+};
+
+__device__ __forceinline__ TileInfo tile_info(const fb_moe_decode_work* work, const fb_moe_expert_layout& L,
+                                              int tile, int tiles_per_item) {
+  TileInfo ti;
+  ti.item = tile / tiles_per_item;
+  ti.sub = tile - ti.item * tiles_per_item;
+  ti.pair_begin = work->item_pair_begin[ti.item];
+  ti.n_tok = work->item_pair_begin[ti.item + 1] - ti.pair_begin;
+  ti.blob = L.slots + int64_t(work->item_slot[ti.item]) * L.blob_stride;
+  return ti;
+}
+
+struct Ring {
+  uint64_t* full;   // [2] count 1 + tx bytes
+  uint64_t* empty;  // [2] count = consumer warps
+  int* abort;
+};
+
+// After a wait has run out every later wait is skipped, so all warps keep the same control flow
+// (their barriers still match) and the kernel drains quickly with the status word set.
+__device__ __forceinline__ bool ring_aborted(const Ring& r) { return *reinterpret_cast<volatile int*>(r.abort) != 0; }
+__device__ __forceinline__ void ring_timeout(const Ring& r, uint32_t* status) {
+  *r.abort = 1;
+  atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+}
+
+// Consumers: cooperative (rare-path) load of up to kTT activation rows of later passes.
+__device__ __forceinline__ void coop_load_act(uint8_t* dst, const uint8_t* src_rows, int row_stride, const int* toks,
+                                              int n, int bytes, int tid, int nthreads) {
+  for (int t = 0; t < n; ++t) {
+    const uint4* s = reinterpret_cast<const uint4*>(src_rows + size_t(toks[t]) * row_stride);
+    uint4* d = reinterpret_cast<uint4*>(dst + size_t(t) * bytes);
+    for (int i = tid; i < bytes / 16; i += nthreads) d[i] = __ldcg(s + i);
+  }
+}
+
+// ------------------------------------------------------------------------------ per-format tile math
+template <int FMT>
+struct GateUp;
+
+// IQ3_S: a tile is 32 intermediate rows (32 gate + 32 up rows of 1100 bytes). Ten consumer warps:
+// warp w handles block pair w%5 (220 bytes, word aligned, odd word stride between rows -> no bank
+// conflicts) of the 32 gate (w<5) or up (w>=5) rows, one row per lane; the five partial sums of a
+// row meet in shared memory.
+template <>
+struct GateUp<FB_FMT_IQ3_S> {
+  static constexpr int kJ = 32, kRowBytes = 1100, kWarps = 10;
+  static constexpr int kAct = FB_ACT_Q8_K, kActBytes = H + 64;
+  static constexpr bool kGrid = true;
+  static constexpr int kPartialFloats = 2 * kWarps * kTT * 32;
+};
+// IQ4_NL: 32 intermediate rows of 1440 bytes per matrix. Sixteen consumer warps; warp w handles
+// rows 2w, 2w+1 of gate and of up, eight lanes per row, lane q taking the 36-byte units q + 8i.
+template <>
+struct GateUp<FB_FMT_IQ4_NL> {
+  static constexpr int kJ = 32, kRowBytes = 1440, kWarps = 16;
+  static constexpr int kAct = FB_ACT_Q8_0, kActBytes = H + H / 8;
+  static constexpr bool kGrid = false;
+  static constexpr int kPartialFloats = 0;
+};
+
+template <int TT>
+__device__ __forceinline__ void iq3s_unit_dot(const uint32_t* unit, const uint32_t* grid_lane, const uint32_t* signtab,
+                                              const uint8_t* const (&actrow)[TT], int pair, int act_k,
+                                              float (&acc)[TT]) {
+  const int8_t* a0[TT];
+  const int8_t* a1[TT];
+#pragma unroll
+  for (int t = 0; t < TT; ++t) {
+    a0[t] = reinterpret_cast<const int8_t*>(actrow[t]) + 512 * pair;
+    a1[t] = a0[t] + 256;
+  }
+  int bs[TT];
+  iq3s_block_idot<0, TT>(unit, grid_lane, signtab, a0, bs);
+  const float d0 = ld_fp16<0>(unit);
+#pragma unroll
+  for (int t = 0; t < TT; ++t) {
+    const float da = reinterpret_cast<const float*>(actrow[t] + act_k)[2 * pair];
+    acc[t] = fmaf(float(bs[t]), d0 * da, acc[t]);
+  }
+  iq3s_block_idot<110, TT>(unit, grid_lane, signtab, a1, bs);
+  const float d1 = ld_fp16<110>(unit);
+#pragma unroll
+  for (int t = 0; t < TT; ++t) {
+    const float da = reinterpret_cast<const float*>(actrow[t] + act_k)[2 * pair + 1];
+    acc[t] = fmaf(float(bs[t]), d1 * da, acc[t]);
+  }
+}
+
+// One 36-byte IQ4_NL unit (two blocks) against TT interleaved Q8_0 rows; ublk = index of the
+// unit's first block within the row.
+template <int TT>
+__device__ __forceinline__ void iq4nl_unit_dot(const uint32_t* unit, const Iq4nlLevels& L,
+                                               const uint8_t* const (&actrow)[TT], int ublk, int act_k,
+                                               float (&acc)[TT]) {
+  int w[8];
+  {
+    const uint32_t q[4] = {ld4<2>(unit), ld4<6>(unit), ld4<10>(unit), ld4<14>(unit)};
+    iq4nl_decode32(L, q, w);
+    const float d = ld_fp16<0>(unit);
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+      const int s = dot32(w, reinterpret_cast<const int8_t*>(actrow[t]) + 32 * ublk);
+      acc[t] = fmaf(float(s), d * reinterpret_cast<const float*>(actrow[t] + act_k)[ublk], acc[t]);
+    }
+  }
+  {
+    const uint32_t q[4] = {unit[5], unit[6], unit[7], unit[8]};
+    iq4nl_decode32(L, q, w);
+    const float d = ld_fp16<18>(unit);
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+      const int s = dot32(w, reinterpret_cast<const int8_t*>(actrow[t]) + 32 * (ublk + 1));
+      acc[t] = fmaf(float(s), d * reinterpret_cast<const float*>(actrow[t] + act_k)[ublk + 1], acc[t]);
+    }
+  }
+}
+
+// h of one finished work item -> planar activation rows for the down projection (one warp).
+__device__ __forceinline__ void quantize_item_h(const fb_moe_decode_workspace& ws, int pair_begin, int n_tok,
+                                                int down_act) {
+  const int lane = threadIdx.x & 31;
+  const int I = ws.inter;
+  for (int p = pair_begin; p < pair_begin + n_tok; ++p) {
+    const float* h = ws.h + size_t(p) * I;
+    uint8_t* out = ws.hq + size_t(p) * FB_HQ_STRIDE;
+    if (down_act == FB_ACT_Q8_K) {
+      float* scales = reinterpret_cast<float*>(out + I);
+      for (int b = 0; b < I / 256; ++b) {
+        float v[8];
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(h + 256 * b + 8 * lane));
+        const float4 c = __ldcg(reinterpret_cast<const float4*>(h + 256 * b + 8 * lane) + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
+        int q[8], ps;
+        const float d = q8k_block_warp(v, q, ps);
+        uint2 pk;
+        pk.x = uint32_t(uint8_t(q[0])) | (uint32_t(uint8_t(q[1])) << 8) | (uint32_t(uint8_t(q[2])) << 16) |
+               (uint32_t(uint8_t(q[3])) << 24);
+        pk.y = uint32_t(uint8_t(q[4])) | (uint32_t(uint8_t(q[5])) << 8) | (uint32_t(uint8_t(q[6])) << 16) |
+               (uint32_t(uint8_t(q[7])) << 24);
+        *reinterpret_cast<uint2*>(out + 256 * b + 8 * lane) = pk;
+        if (lane == 0) scales[b] = d;
+      }
+    } else {
+      float* scales = reinterpret_cast<float*>(out + I);
+      for (int b = 0; b < I / 32; ++b) {
+        unsigned short dh;
+        const int q = q8_0_block_warp(__ldcg(h + 32 * b + lane), dh);
+        out[32 * b + q8_0_interleave_index(lane)] = uint8_t(int8_t(q));
+        if (lane == 0) scales[b] = __half2float(__ushort_as_half(dh));
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ gate/up kernel
+template <int FMT>
+__global__ void __launch_bounds__((GateUp<FMT>::kWarps + 1) * 32, 1)
+gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
+  using C = GateUp<FMT>;
+  constexpr int kW = C::kWarps, kPart = C::kJ * C::kRowBytes, kStageW = 2 * kPart;
+  constexpr int kStage = kStageW + kTT * C::kActBytes;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* p = smem;
+  uint32_t* gridrep = reinterpret_cast<uint32_t*>(p);
+  if (C::kGrid) p += kGridRepBytes;
+  uint32_t* signtab = reinterpret_cast<uint32_t*>(p);
+  p += 64;
+  uint8_t* stage0 = p;
+  p += 2 * kStage;
+  float* partials = reinterpret_cast<float*>(p);
+  p += C::kPartialFloats * 4 + 16;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p);
+  __shared__ int s_abort;
+  Ring ring{bars, bars + 2, &s_abort};
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (C::kGrid) iq3s_tables_fill(gridrep, signtab);
+  if (tid == 0) {
+    mbar_init(&ring.full[0], 1);
+    mbar_init(&ring.full[1], 1);
+    mbar_init(&ring.empty[0], kW);
+    mbar_init(&ring.empty[1], kW);
+    s_abort = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+  pdl_wait_prior();
+
+  const fb_moe_decode_work* work = ws.work;
+  const int n_items = min(max(work->n_items, 0), kMaxPairs);
+  const int I = L.inter;
+  const int tpi = I / C::kJ;
+  const int n_tiles = n_items * tpi;
+  const int t_begin = int(int64_t(n_tiles) * blockIdx.x / gridDim.x);
+  const int t_end = int(int64_t(n_tiles) * (blockIdx.x + 1) / gridDim.x);
+  const int down_act = act_of(L.down_format);
+
+  if (warp == kW) {
+    // ---------------- producer: one lane issues the bulk copies of each tile into the ring.
+    if (lane == 0) {
+      for (int tile = t_begin, i = 0; tile < t_end; ++tile, ++i) {
+        const int s = i & 1;
+        if (ring_aborted(ring)) break;
+        if (i >= 2 && !mbar_wait(&ring.empty[s], ((i >> 1) - 1) & 1)) {
+          ring_timeout(ring, ws.status);
+          break;
+        }
+        const TileInfo ti = tile_info(work, L, tile, tpi);
+        const int nact = min(ti.n_tok, kTT);
+        uint8_t* st = stage0 + s * kStage;
+        mbar_expect_tx(&ring.full[s], uint32_t(kStageW + nact * C::kActBytes));
+        const size_t off = size_t(ti.sub) * kPart;
+        bulk_g2s(st, ti.blob + L.gate_offset + off, kPart, &ring.full[s]);
+        bulk_g2s(st + kPart, ti.blob + L.up_offset + off, kPart, &ring.full[s]);
+        for (int t = 0; t < nact; ++t)
+          bulk_g2s(st + kStageW + t * C::kActBytes,
+                   ws.xq + size_t(work->pair_token[ti.pair_begin + t]) * FB_XQ_STRIDE, C::kActBytes, &ring.full[s]);
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers
+  const uint32_t* grid_lane = gridrep + lane;
+  const Iq4nlLevels lv = iq4nl_levels();
+  int pbuf = 0;
+  for (int tile = t_begin, i = 0; tile < t_end; ++tile, ++i) {
+    const int s = i & 1;
+    if (!ring_aborted(ring) && !mbar_wait(&ring.full[s], (i >> 1) & 1)) ring_timeout(ring, ws.status);
+    const TileInfo ti = tile_info(work, L, tile, tpi);
+    uint8_t* st = stage0 + s * kStage;
+    const uint8_t* actbase = st + kStageW;
+    const int j0 = ti.sub * C::kJ;
+    for (int tok0 = 0; tok0 < ti.n_tok; tok0 += kTT) {
+      const int ntp = min(kTT, ti.n_tok - tok0);
+      if (tok0 > 0) {  // rare: more tokens on this expert than one pass holds
+        named_bar_sync(1, kW * 32);
+        int toks[kTT];
+        for (int t = 0; t < ntp; ++t) toks[t] = work->pair_token[ti.pair_begin + tok0 + t];
+        coop_load_act(st + kStageW, ws.xq, FB_XQ_STRIDE, toks, ntp, C::kActBytes, tid, kW * 32);
+        named_bar_sync(1, kW * 32);
+      }
+      if constexpr (FMT == FB_FMT_IQ3_S) {
+        const int mat = warp / 5, pair = warp - 5 * mat;
+        const uint32_t* unit = reinterpret_cast<const uint32_t*>(st + mat * kPart + lane * C::kRowBytes + pair * 220);
+        float* part = partials + pbuf * (kW * kTT * 32);
+        if (ntp == 1) {
+          const uint8_t* ar[1] = {actbase};
+          float acc[1] = {0.0f};
+          iq3s_unit_dot<1>(unit, grid_lane, signtab, ar, pair, H, acc);
+          part[(warp * kTT + 0) * 32 + lane] = acc[0];
+        } else {
+          const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
+          float acc[2] = {0.0f, 0.0f};
+          iq3s_unit_dot<2>(unit, grid_lane, signtab, ar, pair, H, acc);
+          part[(warp * kTT + 0) * 32 + lane] = acc[0];
+          part[(warp * kTT + 1) * 32 + lane] = acc[1];
+        }
+        named_bar_sync(1, kW * 32);
+        if (warp == 0) {
+          for (int t = 0; t < ntp; ++t) {
+            float g = 0.0f, u = 0.0f;
+#pragma unroll
+            for (int q = 0; q < 5; ++q) {
+              g += part[(q * kTT + t) * 32 + lane];
+              u += part[((5 + q) * kTT + t) * 32 + lane];
+            }
+            ws.h[size_t(ti.pair_begin + tok0 + t) * I + j0 + lane] = silu_mul(g, u);
+          }
+        }
+        pbuf ^= 1;
+      } else {
+        // lanes 0-7 gate row 2w, 8-15 gate 2w+1, 16-23 up 2w, 24-31 up 2w+1
+        const int q = lane & 7, r = (lane >> 3) & 1, mat = lane >> 4;
+        const uint8_t* row = st + mat * kPart + (2 * warp + r) * C::kRowBytes;
+        float acc[kTT] = {0.0f, 0.0f};
+        if (ntp == 1) {
+          const uint8_t* ar[1] = {actbase};
+          float a1[1] = {0.0f};
+#pragma unroll
+          for (int it = 0; it < 5; ++it) {
+            const int u = q + 8 * it;
+            iq4nl_unit_dot<1>(reinterpret_cast<const uint32_t*>(row + 36 * u), lv, ar, 2 * u, H, a1);
+          }
+          acc[0] = a1[0];
+        } else {
+          const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
+#pragma unroll
+          for (int it = 0; it < 5; ++it) {
+            const int u = q + 8 * it;
+            iq4nl_unit_dot<2>(reinterpret_cast<const uint32_t*>(row + 36 * u), lv, ar, 2 * u, H, acc);
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < kTT; ++t) {
+          float v = acc[t];
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          v += __shfl_xor_sync(0xffffffffu, v, 4);
+          const float up = __shfl_down_sync(0xffffffffu, v, 16);
+          if (t < ntp && q == 0 && mat == 0)
+            ws.h[size_t(ti.pair_begin + tok0 + t) * I + j0 + 2 * warp + r] = silu_mul(v, up);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ring.empty[s]);
+    // The CTA that finishes an item's last tile re-quantizes that item's h for the down kernel.
+    if constexpr (FMT == FB_FMT_IQ3_S) {
+      if (warp == 0) {
+        __threadfence();
+        __syncwarp();
+        int ticket = 0;
+        if (lane == 0) ticket = atomicAdd(&ws.item_done[ti.item], 1);
+        ticket = __shfl_sync(0xffffffffu, ticket, 0);
+        if (ticket == tpi - 1) {
+          __threadfence();
+          quantize_item_h(ws, ti.pair_begin, ti.n_tok, down_act);
+        }
+      }
+    } else {
+      // every warp stored part of h: count warps instead of tiles
+      __threadfence();
+      __syncwarp();
+      int ticket = 0;
+      if (lane == 0) ticket = atomicAdd(&ws.item_done[ti.item], 1);
+      ticket = __shfl_sync(0xffffffffu, ticket, 0);
+      if (ticket == tpi * kW - 1) {
+        __threadfence();
+        quantize_item_h(ws, ti.pair_begin, ti.n_tok, down_act);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ down kernel
+template <int FMT, int INTER>
+struct Down;
+// IQ3_S, inter 512: a row is one 220-byte block pair; tile = 320 rows, one row per lane.
+template <>
+struct Down<FB_FMT_IQ3_S, 512> {
+  static constexpr int kRows = 320, kRowBytes = 220, kWarps = 10, kAct = FB_ACT_Q8_K, kActBytes = 512 + 64;
+  static constexpr bool kGrid = true;
+};
+// IQ4_NL, inter 512: a row is eight 36-byte units, eight lanes per row, four rows per warp step.
+template <>
+struct Down<FB_FMT_IQ4_NL, 512> {
+  static constexpr int kRows = 320, kRowBytes = 288, kWarps = 16, kAct = FB_ACT_Q8_0, kActBytes = 512 + 64;
+  static constexpr bool kGrid = false;
+  static constexpr int kLanesPerRow = 8, kUnitsPerLane = 1, kUnitA = 1, kUnitB = 0;
+};
+// IQ4_NL, inter 640: a row is ten units, two lanes per row with five consecutive units each.
+template <>
+struct Down<FB_FMT_IQ4_NL, 640> {
+  static constexpr int kRows = 256, kRowBytes = 360, kWarps = 16, kAct = FB_ACT_Q8_0, kActBytes = 640 + 80;
+  static constexpr bool kGrid = false;
+  static constexpr int kLanesPerRow = 2, kUnitsPerLane = 5, kUnitA = 5, kUnitB = 1;
+};
+
+template <int FMT, int INTER>
+__global__ void __launch_bounds__((Down<FMT, INTER>::kWarps + 1) * 32, 1)
+down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
+  using C = Down<FMT, INTER>;
+  constexpr int kW = C::kWarps, kStageW = C::kRows * C::kRowBytes;
+  constexpr int kStage = kStageW + kTT * C::kActBytes;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* p = smem;
+  uint32_t* gridrep = reinterpret_cast<uint32_t*>(p);
+  if (C::kGrid) p += kGridRepBytes;
+  uint32_t* signtab = reinterpret_cast<uint32_t*>(p);
+  p += 64;
+  uint8_t* stage0 = p;
+  p += 2 * kStage;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p);
+  __shared__ int s_abort;
+  Ring ring{bars, bars + 2, &s_abort};
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (C::kGrid) iq3s_tables_fill(gridrep, signtab);
+  if (tid == 0) {
+    mbar_init(&ring.full[0], 1);
+    mbar_init(&ring.full[1], 1);
+    mbar_init(&ring.empty[0], kW);
+    mbar_init(&ring.empty[1], kW);
+    s_abort = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+  pdl_wait_prior();
+
+  const fb_moe_decode_work* work = ws.work;
+  const int n_items = min(max(work->n_items, 0), kMaxPairs);
+  constexpr int tpi = H / C::kRows;
+  const int n_tiles = n_items * tpi;
+  const int t_begin = int(int64_t(n_tiles) * blockIdx.x / gridDim.x);
+  const int t_end = int(int64_t(n_tiles) * (blockIdx.x + 1) / gridDim.x);
+
+  if (warp == kW) {
+    if (lane == 0) {
+      for (int tile = t_begin, i = 0; tile < t_end; ++tile, ++i) {
+        const int s = i & 1;
+        if (ring_aborted(ring)) break;
+        if (i >= 2 && !mbar_wait(&ring.empty[s], ((i >> 1) - 1) & 1)) {
+          ring_timeout(ring, ws.status);
+          break;
+        }
+        const TileInfo ti = tile_info(work, L, tile, tpi);
+        const int nact = min(ti.n_tok, kTT);
+        uint8_t* st = stage0 + s * kStage;
+        mbar_expect_tx(&ring.full[s], uint32_t(kStageW + nact * C::kActBytes));
+        bulk_g2s(st, ti.blob + L.down_offset + size_t(ti.sub) * kStageW, kStageW, &ring.full[s]);
+        for (int t = 0; t < nact; ++t)
+          bulk_g2s(st + kStageW + t * C::kActBytes, ws.hq + size_t(ti.pair_begin + t) * FB_HQ_STRIDE, C::kActBytes,
+                   &ring.full[s]);
+      }
+    }
+    return;
+  }
+
+  const uint32_t* grid_lane = gridrep + lane;
+  const Iq4nlLevels lv = iq4nl_levels();
+  for (int tile = t_begin, i = 0; tile < t_end; ++tile, ++i) {
+    const int s = i & 1;
+    if (!ring_aborted(ring) && !mbar_wait(&ring.full[s], (i >> 1) & 1)) ring_timeout(ring, ws.status);
+    const TileInfo ti = tile_info(work, L, tile, tpi);
+    uint8_t* st = stage0 + s * kStage;
+    const uint8_t* actbase = st + kStageW;
+    const int r0 = ti.sub * C::kRows;
+    for (int tok0 = 0; tok0 < ti.n_tok; tok0 += kTT) {
+      const int ntp = min(kTT, ti.n_tok - tok0);
+      if (tok0 > 0) {
+        named_bar_sync(1, kW * 32);
+        int toks[kTT];
+        for (int t = 0; t < ntp; ++t) toks[t] = ti.pair_begin + tok0 + t;
+        coop_load_act(st + kStageW, ws.hq, FB_HQ_STRIDE, toks, ntp, C::kActBytes, tid, kW * 32);
+        named_bar_sync(1, kW * 32);
+      }
+      float wgt[kTT];
+#pragma unroll
+      for (int t = 0; t < kTT; ++t) wgt[t] = t < ntp ? work->pair_weight[ti.pair_begin + tok0 + t] : 0.0f;
+      if constexpr (FMT == FB_FMT_IQ3_S) {
+        const int row = 32 * warp + lane;
+        const uint32_t* unit = reinterpret_cast<const uint32_t*>(st + row * C::kRowBytes);
+        if (ntp == 1) {
+          const uint8_t* ar[1] = {actbase};
+          float acc[1] = {0.0f};
+          iq3s_unit_dot<1>(unit, grid_lane, signtab, ar, 0, INTER, acc);
+          ws.partial[size_t(ti.pair_begin + tok0) * H + r0 + row] = wgt[0] * acc[0];
+        } else {
+          const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
+          float acc[2] = {0.0f, 0.0f};
+          iq3s_unit_dot<2>(unit, grid_lane, signtab, ar, 0, INTER, acc);
+          ws.partial[size_t(ti.pair_begin + tok0) * H + r0 + row] = wgt[0] * acc[0];
+          ws.partial[size_t(ti.pair_begin + tok0 + 1) * H + r0 + row] = wgt[1] * acc[1];
+        }
+      } else {
+        constexpr int LPR = C::kLanesPerRow, RPS = 32 / LPR;
+        const int q = lane % LPR, r = lane / LPR;
+        for (int step = warp; step < C::kRows / RPS; step += kW) {
+          const int row = step * RPS + r;
+          const uint8_t* rowp = st + row * C::kRowBytes;
+          float acc[kTT] = {0.0f, 0.0f};
+          if (ntp == 1) {
+            const uint8_t* ar[1] = {actbase};
+            float a1[1] = {0.0f};
+#pragma unroll
+            for (int it = 0; it < C::kUnitsPerLane; ++it) {
+              const int u = q * C::kUnitA + it * C::kUnitB;
+              iq4nl_unit_dot<1>(reinterpret_cast<const uint32_t*>(rowp + 36 * u), lv, ar, 2 * u, INTER, a1);
+            }
+            acc[0] = a1[0];
+          } else {
+            const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
+#pragma unroll
+            for (int it = 0; it < C::kUnitsPerLane; ++it) {
+              const int u = q * C::kUnitA + it * C::kUnitB;
+              iq4nl_unit_dot<2>(reinterpret_cast<const uint32_t*>(rowp + 36 * u), lv, ar, 2 * u, INTER, acc);
+            }
+          }
+#pragma unroll
+          for (int t = 0; t < kTT; ++t) {
+            float v = acc[t];
+#pragma unroll
+            for (int o = 1; o < LPR; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (t < ntp && q == 0) ws.partial[size_t(ti.pair_begin + tok0 + t) * H + r0 + row] = wgt[t] * v;
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ring.empty[s]);
+  }
+}
+
+// ------------------------------------------------------------------------------ combine
+// y[t][n] = partials of token t in slot order (+ y_shared); optional rank-1 ablation of the routed
+// part; X[t][s][n] += inj[t][s] * y (4 residual streams) when X is given; y_out optional.
+// One block per (token, 256-column slice): the projection r . y_routed needs the whole row, so
+// with ablation a block first reduces the row (only then).
+__global__ void __launch_bounds__(256) combine_kernel(fb_moe_decode_workspace ws, const float* __restrict__ y_shared,
+                                                      const float* __restrict__ inj, float* __restrict__ X,
+                                                      float* __restrict__ y_out, const float* __restrict__ ablate,
+                                                      float ablate_scale) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  const int t = blockIdx.y;
+  const fb_moe_decode_work* work = ws.work;
+  const int np = min(max(work->token_pair_count[t], 0), kTopK);
+  __shared__ float s_red[8];
+  __shared__ float s_proj;
+  float proj = 0.0f;
+  if (ablate) {
+    float loc = 0.0f;
+    for (int n = threadIdx.x; n < H; n += 256) {
+      float y = 0.0f;
+      for (int k = 0; k < np; ++k) y += ws.partial[size_t(work->token_pairs[t][k]) * H + n];
+      loc = fmaf(ablate[n], y, loc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) loc += __shfl_xor_sync(0xffffffffu, loc, o);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = loc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.0f;
+      for (int i = 0; i < 8; ++i) s += s_red[i];
+      s_proj = s;
+    }
+    __syncthreads();
+    proj = s_proj;
+  }
+  const int n = blockIdx.x * 256 + threadIdx.x;
+  float y = 0.0f;
+  for (int k = 0; k < np; ++k) y += ws.partial[size_t(work->token_pairs[t][k]) * H + n];
+  if (ablate) y -= ablate_scale * ablate[n] * proj;
+  if (y_shared) y += y_shared[size_t(t) * H + n];
+  if (y_out) y_out[size_t(t) * H + n] = y;
+  if (X) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s) X[(size_t(t) * 4 + s) * H + n] += inj[t * 4 + s] * y;
+  }
+}
+
+// ------------------------------------------------------------------------------ host side
+template <class K>
+cudaError_t opt_in_smem(K kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+}
+
+template <int FMT>
+constexpr size_t gate_up_smem() {
+  using C = GateUp<FMT>;
+  return (C::kGrid ? kGridRepBytes : 0) + 64 + 2 * size_t(2 * C::kJ * C::kRowBytes + kTT * C::kActBytes) +
+         C::kPartialFloats * 4 + 16 + 64;
+}
+template <int FMT, int INTER>
+constexpr size_t down_smem() {
+  using C = Down<FMT, INTER>;
+  return (C::kGrid ? kGridRepBytes : 0) + 64 + 2 * size_t(C::kRows * C::kRowBytes + kTT * C::kActBytes) + 64;
+}
+
+bool layout_ok(const fb_moe_expert_layout* L) {
+  if (!L || !L->slots) return false;
+  if ((reinterpret_cast<uintptr_t>(L->slots) | uintptr_t(L->blob_stride) | uintptr_t(L->gate_offset) |
+       uintptr_t(L->up_offset) | uintptr_t(L->down_offset)) & 15)
+    return false;
+  if (L->inter != 512 && L->inter != 640) return false;
+  if (L->gate_up_format != FB_FMT_IQ3_S && L->gate_up_format != FB_FMT_IQ4_NL) return false;
+  if (L->down_format == FB_FMT_IQ3_S) return L->inter % 256 == 0;
+  return L->down_format == FB_FMT_IQ4_NL;
+}
+
+bool ws_ok(const fb_moe_decode_workspace* ws) {
+  return ws && ws->work && ws->xq && ws->h && ws->hq && ws->partial && ws->item_done && ws->status;
+}
+
+}  // namespace
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" {
+
+size_t fb_moe_decode_workspace_bytes(int32_t inter) {
+  (void)inter;
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  return up(sizeof(fb_moe_decode_work)) + up(size_t(kMaxTok) * FB_XQ_STRIDE) + up(size_t(kMaxPairs) * 640 * 4) +
+         up(size_t(kMaxPairs) * FB_HQ_STRIDE) + up(size_t(kMaxPairs) * H * 4) + up(kMaxPairs * 4) + 256;
+}
+
+int32_t fb_moe_decode_workspace_make(void* base, const fb_moe_expert_layout* layout, fb_moe_decode_workspace* out) {
+  if (!base || !out || (reinterpret_cast<uintptr_t>(base) & 255)) return invalid("decode workspace: base must be 256-byte aligned");
+  if (!layout_ok(layout)) return invalid("decode workspace: unsupported expert layout");
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  uint8_t* p = static_cast<uint8_t*>(base);
+  out->work = reinterpret_cast<fb_moe_decode_work*>(p);
+  p += up(sizeof(fb_moe_decode_work));
+  out->xq = p;
+  p += up(size_t(kMaxTok) * FB_XQ_STRIDE);
+  out->h = reinterpret_cast<float*>(p);
+  p += up(size_t(kMaxPairs) * 640 * 4);
+  out->hq = p;
+  p += up(size_t(kMaxPairs) * FB_HQ_STRIDE);
+  out->partial = reinterpret_cast<float*>(p);
+  p += up(size_t(kMaxPairs) * H * 4);
+  out->item_done = reinterpret_cast<int32_t*>(p);
+  p += up(kMaxPairs * 4);
+  out->status = reinterpret_cast<uint32_t*>(p);
+  out->gate_up_format = layout->gate_up_format;
+  out->down_format = layout->down_format;
+  out->inter = layout->inter;
+  out->reserved = 0;
+  return 0;
+}
+
+int32_t fb_router_logits(const void* w_bf16, int32_t rows, const void* x, int32_t x_dtype, int32_t tokens,
+                         float* logits, int32_t logits_stride, void* stream) {
+  if (!w_bf16 || !x || !logits || rows <= 0 || tokens <= 0 || logits_stride < rows)
+    return invalid("router_logits: bad arguments");
+  const dim3 grid((rows + 7) / 8), block(256);
+  cudaError_t e = x_dtype == FB_DT_BF16
+                      ? launch_pdl(router_kernel<true>, grid, block, 0, as_stream(stream),
+                                   static_cast<const __nv_bfloat16*>(w_bf16), rows, x, tokens, logits, logits_stride)
+                      : launch_pdl(router_kernel<false>, grid, block, 0, as_stream(stream),
+                                   static_cast<const __nv_bfloat16*>(w_bf16), rows, x, tokens, logits, logits_stride);
+  if (e != cudaSuccess) return check_launch("router_logits");
+  return 0;
+}
+
+int32_t fb_moe_select_publish(const float* router_logits, int32_t logits_stride, const void* x, int32_t x_dtype,
+                              const int32_t* slot_of, int32_t layer, const uint32_t* seq, void* exchange,
+                              int32_t tokens, const fb_moe_decode_workspace* ws, void* stream,
+                              uint32_t* routing_counts) {
+  (void)layer;
+  (void)seq;
+  if (exchange) return invalid("select_publish: no CPU expert tier exists behind these kernels; exchange must be NULL");
+  if (!router_logits || !x || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok || logits_stride < kExperts)
+    return invalid("select_publish: bad arguments (tokens must be 1..16)");
+  cudaError_t e = x_dtype == FB_DT_BF16
+                      ? launch_pdl(select_kernel<true>, dim3(1 + tokens), dim3(512), 0, as_stream(stream),
+                                   router_logits, logits_stride, x, slot_of, tokens, *ws, routing_counts)
+                      : launch_pdl(select_kernel<false>, dim3(1 + tokens), dim3(512), 0, as_stream(stream),
+                                   router_logits, logits_stride, x, slot_of, tokens, *ws, routing_counts);
+  if (e != cudaSuccess) return check_launch("select_publish");
+  return 0;
+}
+
+int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
+                           void* stream) {
+  if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_gate_up: bad arguments");
+  if (layout->inter != ws->inter || layout->gate_up_format != ws->gate_up_format ||
+      layout->down_format != ws->down_format)
+    return invalid("hot_gate_up: workspace was made for a different layout");
+  static bool once = [] {
+    opt_in_smem(gate_up_kernel<FB_FMT_IQ3_S>, gate_up_smem<FB_FMT_IQ3_S>());
+    opt_in_smem(gate_up_kernel<FB_FMT_IQ4_NL>, gate_up_smem<FB_FMT_IQ4_NL>());
+    return true;
+  }();
+  (void)once;
+  const dim3 grid(sm_count());
+  cudaError_t e;
+  if (layout->gate_up_format == FB_FMT_IQ3_S)
+    e = launch_pdl(gate_up_kernel<FB_FMT_IQ3_S>, grid, dim3((GateUp<FB_FMT_IQ3_S>::kWarps + 1) * 32),
+                   gate_up_smem<FB_FMT_IQ3_S>(), as_stream(stream), *layout, *ws);
+  else
+    e = launch_pdl(gate_up_kernel<FB_FMT_IQ4_NL>, grid, dim3((GateUp<FB_FMT_IQ4_NL>::kWarps + 1) * 32),
+                   gate_up_smem<FB_FMT_IQ4_NL>(), as_stream(stream), *layout, *ws);
+  if (e != cudaSuccess) return check_launch("hot_gate_up");
+  return 0;
+}
+
+int32_t fb_moe_hot_down(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
+                        void* stream) {
+  if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_down: bad arguments");
+  if (layout->inter != ws->inter || layout->down_format != ws->down_format)
+    return invalid("hot_down: workspace was made for a different layout");
+  static bool once = [] {
+    opt_in_smem(down_kernel<FB_FMT_IQ3_S, 512>, down_smem<FB_FMT_IQ3_S, 512>());
+    opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 512>, down_smem<FB_FMT_IQ4_NL, 512>());
+    opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 640>, down_smem<FB_FMT_IQ4_NL, 640>());
+    return true;
+  }();
+  (void)once;
+  const dim3 grid(sm_count());
+  cudaError_t e;
+  if (layout->down_format == FB_FMT_IQ3_S)
+    e = launch_pdl(down_kernel<FB_FMT_IQ3_S, 512>, grid, dim3((Down<FB_FMT_IQ3_S, 512>::kWarps + 1) * 32),
+                   down_smem<FB_FMT_IQ3_S, 512>(), as_stream(stream), *layout, *ws);
+  else if (layout->inter == 512)
+    e = launch_pdl(down_kernel<FB_FMT_IQ4_NL, 512>, grid, dim3((Down<FB_FMT_IQ4_NL, 512>::kWarps + 1) * 32),
+                   down_smem<FB_FMT_IQ4_NL, 512>(), as_stream(stream), *layout, *ws);
+  else
+    e = launch_pdl(down_kernel<FB_FMT_IQ4_NL, 640>, grid, dim3((Down<FB_FMT_IQ4_NL, 640>::kWarps + 1) * 32),
+                   down_smem<FB_FMT_IQ4_NL, 640>(), as_stream(stream), *layout, *ws);
+  if (e != cudaSuccess) return check_launch("hot_down");
+  return 0;
+}
+
+int32_t fb_moe_combine(const fb_moe_decode_workspace* ws, const float* y_shared, void* exchange, int32_t layer,
+                       const uint32_t* seq, const float* inj, float* X, float* y_out, int32_t tokens,
+                       long long timeout_cycles, const float* ablate_direction, float ablate_scale, void* stream) {
+  (void)layer;
+  (void)seq;
+  (void)timeout_cycles;
+  if (exchange) return invalid("combine: no CPU expert tier exists behind these kernels; exchange must be NULL");
+  if (!ws_ok(ws) || tokens < 1 || tokens > kMaxTok || (X && !inj) || (!X && !y_out))
+    return invalid("combine: bad arguments");
+  cudaError_t e = launch_pdl(combine_kernel, dim3(H / 256, tokens), dim3(256), 0, as_stream(stream), *ws, y_shared, inj,
+                             X, y_out, ablate_direction, ablate_scale);
+  if (e != cudaSuccess) return check_launch("combine");
+  return 0;
+}
+
+int32_t fb_moe_layer_decode(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x,
+                            int32_t x_dtype, int32_t tokens, const fb_moe_decode_workspace* ws, float* logits_scratch,
+                            float* y_out, void* stream) {
+  if (!logits_scratch) return invalid("layer_decode: logits scratch [tokens][513] is required");
+  int32_t st = fb_router_logits(router_w_bf16, kExperts, x, x_dtype, tokens, logits_scratch, FB_ROUTER_ROWS, stream);
+  if (st) return st;
+  st = fb_moe_select_publish(logits_scratch, FB_ROUTER_ROWS, x, x_dtype, nullptr, 0, nullptr, nullptr, tokens, ws,
+                             stream, nullptr);
+  if (st) return st;
+  st = fb_moe_hot_gate_up(layout, tokens, ws, stream);
+  if (st) return st;
+  st = fb_moe_hot_down(layout, tokens, ws, stream);
+  if (st) return st;
+  return fb_moe_combine(ws, nullptr, nullptr, 0, nullptr, nullptr, nullptr, y_out, tokens, 0, nullptr, 0.0f, stream);
+}
+
+int32_t fb_moe_layer_decode_host(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x_host,
+                                 int32_t x_dtype, int32_t tokens, const fb_moe_decode_workspace* ws,
+                                 float* logits_scratch, void* x_dev, float* y_dev, float* y_host, void* stream) {
+  if (!x_host || !x_dev || !y_dev || !y_host || tokens < 1 || tokens > kMaxTok)
+    return invalid("layer_decode_host: bad arguments");
+  const size_t xb = size_t(tokens) * H * (x_dtype == FB_DT_BF16 ? 2 : 4);
+  cudaError_t e = cudaMemcpyAsync(x_dev, x_host, xb, cudaMemcpyHostToDevice, as_stream(stream));
+  if (e != cudaSuccess) return check_launch("layer_decode_host: copy in");
+  int32_t st = fb_moe_layer_decode(router_w_bf16, layout, x_dev, x_dtype, tokens, ws, logits_scratch, y_dev, stream);
+  if (st) return st;
+  e = cudaMemcpyAsync(y_host, y_dev, size_t(tokens) * H * 4, cudaMemcpyDeviceToHost, as_stream(stream));
+  if (e != cudaSuccess) return check_launch("layer_decode_host: copy out");
+  e = cudaStreamSynchronize(as_stream(stream));
+  if (e != cudaSuccess) {
+    set_error("layer_decode_host: %s", cudaGetErrorString(e));
+    return int32_t(e);
+  }
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,196 @@
+/* fngine_b200 -- C ABI of the B200 (sm_100a) quantized-expert kernels.
+ *
+ * Every entry point replaces one function of the reference engine's kernel interface for the
+ * routed-expert MoE path and the FP8-row dense projection; the comment above each declaration
+ * names the reference declaration it stands in for (paths relative to the reference project).
+ * The reference exposes these as C++ free functions (namespace fngine::kernels); the header
+ * include/fngine_b200/kernels.hpp re-creates those C++ names on top of this ABI.
+ *
+ * Conventions (same as the reference, src/kernels/moe/moe.h:19-24, src/kernels/linear/linear.h:46-47):
+ *  - all tensor arguments are raw device pointers owned by the caller; kernels never allocate and
+ *    never synchronize; everything is ordered on the `stream` argument (a cudaStream_t passed as
+ *    void*); `tokens` is a host value.
+ *  - return value: 0 on success, otherwise a cudaError_t value (cudaErrorInvalidValue = 1 for bad
+ *    arguments). fb_last_error_string() describes the last failure on the calling thread.
+ *  - there is no CPU fallback: without a CUDA device every compute entry point fails.
+ *
+ * Differences from the reference interface, all additive:
+ *  - `inter` (expert intermediate size) is a run-time field (512 or 640), the reference fixes 640
+ *    at compile time (src/core/model_dims.h:60);
+ *  - IQ3_S is accepted as a down-projection format (needs inter % 256 == 0);
+ *  - activations follow the reference's CPU tier: Q8_K blocks for IQ3_S weights, Q8_0 blocks for
+ *    IQ4_NL weights (src/cpu/iq_cpu.h:12-21), not the GPU tier's per-32 fp32-scale variant;
+ *  - there is no CPU expert tier behind these kernels: `exchange`/`control` must be NULL and every
+ *    routed expert must be resident (slot_of[e] >= 0), which the reference API already permits
+ *    (src/kernels/moe/moe.h:119-121, :198-200).
+ */
+#ifndef FNGINE_B200_H
+#define FNGINE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ggml type ids of the expert formats (src/kernels/moe/moe.h:48-55). */
+enum { FB_FMT_IQ4_NL = 20, FB_FMT_IQ3_S = 21 };
+/* element types of activation inputs */
+enum { FB_DT_F32 = 0, FB_DT_BF16 = 1 };
+/* activation block formats (src/cpu/iq_cpu.h:44) */
+enum { FB_ACT_Q8_K = 0, FB_ACT_Q8_0 = 1 };
+
+enum {
+  FB_HIDDEN = 2560,           /* src/core/model_dims.h:9 */
+  FB_EXPERTS = 512,           /* :58 */
+  FB_TOPK = 10,               /* :59 */
+  FB_ROUTER_ROWS = 513,       /* :62 router | shared-expert gate */
+  FB_DECODE_MAX_TOKENS = 16,  /* src/kernels/moe/moe.h:81 */
+  FB_DECODE_MAX_PAIRS = 160   /* :82 */
+};
+
+/* Device-side status word values written by kernels whose bounded waits ran out. */
+enum { FB_STATUS_OK = 0, FB_STATUS_PIPELINE_TIMEOUT = 1, FB_STATUS_BAD_WORK = 2 };
+
+const char* fb_last_error_string(void);
+/* Library/ABI version and the SM architecture the kernels were compiled for (100). */
+int32_t fb_abi_version(void);
+int32_t fb_compiled_sm(void);
+
+/* ---------------------------------------------------------------- formats and layout */
+/* moe_row_bytes, src/kernels/moe/moe.h:58 (src/kernels/moe/moe_format.cpp:5-15). 0 if unsupported. */
+int64_t fb_moe_row_bytes(int32_t format, int32_t k);
+/* Activation block format a weight format pairs with (format_info().act, src/cpu/iq_cpu.cpp:467-478). */
+int32_t fb_moe_act_format(int32_t format);
+/* Bytes of one activation row of k values in ggml layout (act_row_bytes, src/cpu/iq_cpu.h:66). */
+int64_t fb_act_row_bytes(int32_t act_format, int32_t k);
+
+/* MoeExpertLayout, src/kernels/moe/moe.h:62-71, plus the run-time `inter`. */
+typedef struct fb_moe_expert_layout {
+  const uint8_t* slots; /* device base of the layer's slot array */
+  int64_t blob_stride;  /* bytes between consecutive slots (multiple of 16) */
+  int64_t gate_offset;  /* byte offsets of gate / up / down inside a blob (multiples of 16) */
+  int64_t up_offset;
+  int64_t down_offset;
+  int32_t gate_up_format;
+  int32_t down_format;
+  int32_t inter; /* 512 or 640 */
+  int32_t reserved;
+} fb_moe_expert_layout;
+
+/* make_moe_expert_layout, src/kernels/moe/moe.h:75-76: gate | up | down packed back to back. */
+int32_t fb_moe_expert_layout_make(const uint8_t* slots, int64_t blob_stride, int32_t gate_up_format,
+                                  int32_t down_format, int32_t inter, fb_moe_expert_layout* out);
+/* Bytes of one packed blob for these formats (gate + up + down). */
+int64_t fb_moe_blob_bytes(int32_t gate_up_format, int32_t down_format, int32_t inter);
+
+/* ---------------------------------------------------------------- decode (T <= 16) */
+/* MoeDecodeWork, src/kernels/moe/moe.h:91-105 (same fields, same meaning; every pair is hot). */
+typedef struct fb_moe_decode_work {
+  int32_t n_items;
+  int32_t n_pairs;
+  int32_t n_cold;
+  int32_t tokens;
+  int32_t item_slot[FB_DECODE_MAX_PAIRS];
+  int32_t item_pair_begin[FB_DECODE_MAX_PAIRS + 1];
+  int32_t pair_token[FB_DECODE_MAX_PAIRS];
+  float pair_weight[FB_DECODE_MAX_PAIRS];
+  int32_t token_pair_count[FB_DECODE_MAX_TOKENS];
+  int32_t token_pairs[FB_DECODE_MAX_TOKENS][FB_TOPK];
+  int32_t token_cold_count[FB_DECODE_MAX_TOKENS];
+  int32_t topk_expert[FB_DECODE_MAX_TOKENS][FB_TOPK];
+  float topk_weight[FB_DECODE_MAX_TOKENS][FB_TOPK];
+} fb_moe_decode_work;
+
+/* MoeDecodeWorkspace, src/kernels/moe/moe.h:108-115. Activations are kept in a planar form of
+ * the ggml blocks the CPU tier uses (Q8_K for IQ3_S weights, Q8_0 for IQ4_NL): per row the int8
+ * codes first, then the block scales as fp32 (Q8_0 scales are the fp16-rounded values widened;
+ * Q8_0 codes are stored per block in the order 2*(e%16) + e/16 that the IQ4_NL nibble decode
+ * produces). `hq` is h re-quantized for the down projection, `item_done` counts finished gate/up
+ * tiles per work item, `status` is one device word set when a bounded wait runs out. */
+typedef struct fb_moe_decode_workspace {
+  fb_moe_decode_work* work;
+  uint8_t* xq;        /* [16][FB_XQ_STRIDE] */
+  float* h;           /* [160 pairs][inter] fp32 silu(g)*u */
+  uint8_t* hq;        /* [160 pairs][FB_HQ_STRIDE] */
+  float* partial;     /* [160 pairs][2560], routing weight applied */
+  int32_t* item_done; /* [160] */
+  uint32_t* status;   /* FB_STATUS_* */
+  int32_t gate_up_format;
+  int32_t down_format;
+  int32_t inter;
+  int32_t reserved;
+} fb_moe_decode_workspace;
+enum { FB_XQ_STRIDE = 2880, FB_HQ_STRIDE = 720 };
+
+/* moe_decode_workspace_bytes / make_moe_decode_workspace, src/kernels/moe/moe.h:116-117.
+ * `base` is 256-byte aligned device memory of at least the returned size, zero-filled once. */
+size_t fb_moe_decode_workspace_bytes(int32_t inter);
+int32_t fb_moe_decode_workspace_make(void* base, const fb_moe_expert_layout* layout,
+                                     fb_moe_decode_workspace* out);
+
+/* Router projection feeding the selection: logits[t][r] = sum_k W[r][k] * x[t][k], W bf16
+ * [rows][2560], fp32 accumulation, fp32 out with row stride `logits_stride` (linear_bf16 with the
+ * (513, 2560) StoreF32 registry entry, src/kernels/linear/linear.h:20,170-172). */
+int32_t fb_router_logits(const void* w_bf16, int32_t rows, const void* x, int32_t x_dtype, int32_t tokens,
+                         float* logits, int32_t logits_stride, void* stream);
+
+/* moe_select_publish, src/kernels/moe/moe.h:127-131. Router top-10 (ties to the lower id),
+ * renormalised softmax weights, sorted work list, and the once-per-token activation quantization
+ * of x (dtype FB_DT_F32 or FB_DT_BF16, [tokens][2560]). `slot_of` may be NULL (slot == expert).
+ * `exchange` must be NULL. `routing_counts` optional device u32[512]. */
+int32_t fb_moe_select_publish(const float* router_logits, int32_t logits_stride, const void* x, int32_t x_dtype,
+                              const int32_t* slot_of, int32_t layer, const uint32_t* seq, void* exchange,
+                              int32_t tokens, const fb_moe_decode_workspace* ws, void* stream,
+                              uint32_t* routing_counts);
+/* moe_hot_gate_up, src/kernels/moe/moe.h:136-137: h[pair][j] = silu(gate_j . x) * (up_j . x). */
+int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
+                           void* stream);
+/* moe_hot_down, src/kernels/moe/moe.h:141-142: partial[pair][n] = w_pair * (down_n . q8(h[pair])). */
+int32_t fb_moe_hot_down(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
+                        void* stream);
+/* moe_combine, src/kernels/moe/moe.h:154-158: y[t] = sum of token t's partials in slot order
+ * + y_shared[t] (optional); X[t][s][d] += inj[t][s] * y[t][d] when X is given; y_out optional.
+ * `exchange` must be NULL (no CPU tier), so timeout_cycles is unused; the rank-1 ablation of the
+ * routed part is applied when ablate_direction is given. */
+int32_t fb_moe_combine(const fb_moe_decode_workspace* ws, const float* y_shared, void* exchange, int32_t layer,
+                       const uint32_t* seq, const float* inj, float* X, float* y_out, int32_t tokens,
+                       long long timeout_cycles, const float* ablate_direction, float ablate_scale, void* stream);
+
+/* One whole decode MoE layer: router projection -> select -> gate/up -> down -> combine, the call
+ * sequence of Forward::moe's decode branch (src/model/forward.cpp:333,358-375) without the shared
+ * expert. x: device [tokens][2560]; y_out: device fp32 [tokens][2560]. No reference counterpart
+ * as a single function. */
+int32_t fb_moe_layer_decode(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x,
+                            int32_t x_dtype, int32_t tokens, const fb_moe_decode_workspace* ws, float* logits_scratch,
+                            float* y_out, void* stream);
+/* Same with HOST x and y: copies x in, runs the layer, copies y back and waits for it. `x_dev`
+ * ([tokens][2560] of x_dtype) and `y_dev` (fp32) are caller-owned device staging buffers. */
+int32_t fb_moe_layer_decode_host(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x_host,
+                                 int32_t x_dtype, int32_t tokens, const fb_moe_decode_workspace* ws,
+                                 float* logits_scratch, void* x_dev, float* y_dev, float* y_host, void* stream);
+
+/* ---------------------------------------------------------------- parity probes (no reference counterpart)
+ * The same device routines the GEMV kernels use, exposed so that dequantized weights and int8
+ * activations can be compared bit for bit with the CPU reference. */
+/* out[r][0..k) = exact fp32 dequantization of row r (dequantize_row_iq3_s / _iq4_nl,
+ * third_party/ggml-iq/ggml-iq.c:231-288). */
+int32_t fb_dequant_rows(int32_t format, const uint8_t* rows, int64_t row_bytes, int32_t nrows, int32_t k,
+                        float* out, void* stream);
+/* ggml activation blocks of `rows` rows of k values (quantize_row_q8_K_ref / quantize_row_q8_0_ref,
+ * third_party/ggml-iq/ggml-iq.c:313-350, :75-98; all-zero Q8_K blocks get zero bsums as in
+ * src/cpu/q8_cpu.h:7-8). */
+int32_t fb_quantize_act(int32_t act_format, const void* x, int32_t x_dtype, int32_t rows, int32_t k, uint8_t* out,
+                        void* stream);
+
+/* Seeded synthetic expert bytes, generated on the device and reproducible on the host with
+ * integer arithmetic only (see fngine_b200/synth.py): block b of the tensor takes its free bytes
+ * from splitmix64(seed, counter) and its fp16 scale from `d_table[65536]` (device). */
+int32_t fb_synth_fill_blocks(int32_t format, uint8_t* dst, int64_t n_blocks, int64_t first_block, uint64_t seed,
+                             const uint16_t* d_table, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FNGINE_B200_H */

@@ -1,0 +1,62 @@
+"""The C-ABI library builds, loads, and exports every symbol the header declares (no compute)."""
+import ctypes
+import os
+import re
+
+from fngine_b200 import lib as fblib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = set()
+    for fn in sorted(os.listdir(os.path.join(ROOT, "include"))):
+        if fn.endswith(".h"):
+            txt = open(os.path.join(ROOT, "include", fn)).read()
+            txt = re.sub(r"/\*.*?\*/", "", txt, flags=re.S)
+            names |= set(re.findall(r"\b(fb_[a-z0-9_]+)\s*\(", txt))
+    return names
+
+
+def test_header_and_binding_agree():
+    assert declared_symbols() == set(fblib.exported_names())
+
+
+def test_library_exports_every_declared_symbol(fb_built):
+    lib = ctypes.CDLL(fb_built)
+    for name in declared_symbols():
+        assert hasattr(lib, name), name
+
+
+def test_format_tables(fb_built):
+    lib = fblib.load()
+    assert lib.fb_abi_version() == 1 and lib.fb_compiled_sm() == 100
+    # src/kernels/moe/moe_format.cpp:5-15 of the reference
+    assert lib.fb_moe_row_bytes(21, 2560) == 1100 and lib.fb_moe_row_bytes(21, 512) == 220
+    assert lib.fb_moe_row_bytes(20, 2560) == 1440 and lib.fb_moe_row_bytes(20, 640) == 360
+    assert lib.fb_moe_row_bytes(21, 640) == 0 and lib.fb_moe_row_bytes(99, 2560) == 0
+    assert lib.fb_moe_blob_bytes(21, 21, 512) == 1689600
+    assert lib.fb_moe_blob_bytes(20, 20, 512) == 2211840
+    assert lib.fb_moe_blob_bytes(21, 20, 640) == 2329600
+    assert lib.fb_act_row_bytes(0, 2560) == 2920 and lib.fb_act_row_bytes(1, 2560) == 2720
+    assert lib.fb_moe_act_format(21) == 0 and lib.fb_moe_act_format(20) == 1
+
+
+def test_layout_and_argument_errors(fb_built):
+    lib = fblib.load()
+    lay = fblib.ExpertLayout()
+    assert lib.fb_moe_expert_layout_make(0x1000, 1689600, 21, 21, 512, ctypes.byref(lay)) == 0
+    assert (lay.gate_offset, lay.up_offset, lay.down_offset) == (0, 563200, 1126400)
+    # IQ3_S down needs inter % 256 == 0; stride must hold a blob and be 16-aligned
+    assert lib.fb_moe_expert_layout_make(0x1000, 4000000, 21, 21, 640, ctypes.byref(lay)) == 1
+    assert lib.fb_moe_expert_layout_make(0x1000, 1000, 21, 21, 512, ctypes.byref(lay)) == 1
+    assert b"blob_stride" in lib.fb_last_error_string()
+    assert lib.fb_moe_decode_workspace_bytes(512) % 256 == 0
+    # a CPU exchange is refused (no CPU tier) before anything is launched
+    ws = fblib.DecodeWorkspace()
+    for f in ("work", "xq", "h", "hq", "partial", "item_done", "status"):
+        setattr(ws, f, 0x1000)
+    st = lib.fb_moe_select_publish(0x1000, 513, 0x1000, 0, None, 0, None, 0x1000, 4, ctypes.byref(ws), None, None)
+    assert st == 1 and b"exchange" in lib.fb_last_error_string()
+    st = lib.fb_moe_select_publish(0x1000, 513, 0x1000, 0, None, 0, None, None, 17, ctypes.byref(ws), None, None)
+    assert st == 1

@@ -1,0 +1,196 @@
+"""Pins the CPU oracle (oracle/fb_oracle.c) to the reference.
+
+Two anchors: (1) committed vectors in tests/golden/reference_vectors.npz, produced by the
+reference's own code (tests/golden/make_golden.py); (2) where oracle/_ref is present and the host
+CPU can run it, a direct comparison with the reference's functions on more inputs.
+Bit-exact for weights, int8 activations, SwiGLU and expert outputs of the decode numerics; the
+prefill (bf16) family is compared within 1e-5 relative (fp32 summation order differs).
+"""
+import os
+
+import numpy as np
+import pytest
+
+from fngine_b200 import synth
+from oracle import oracle as O
+import patterns
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.npz"))
+IQ3_S, IQ4_NL = 21, 20
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+@pytest.mark.parametrize("fmt,seed,name", [(IQ3_S, 11, "iq3s"), (IQ4_NL, 12, "iq4nl")])
+def test_dequant_matches_golden(fmt, seed, name):
+    nb = 2 * 2560 // synth.BLOCK_ELEMS[fmt]
+    rows = synth.fill_blocks(fmt, nb, 0, seed)
+    assert np.array_equal(bits(O.dequant_rows(fmt, rows, 2, 2560)), bits(GOLD["dequant_" + name]))
+    assert np.array_equal(O.dequant_rows_bf16(fmt, rows, 2, 2560), GOLD["dequant_bf16_" + name])
+
+
+def test_quantizers_match_golden():
+    x = patterns.all_inputs()
+    assert np.array_equal(O.quantize_act(O.ACT_Q8_K, x), GOLD["q8k"])
+    assert np.array_equal(O.quantize_act(O.ACT_Q8_0, x), GOLD["q80"])
+
+
+def test_silu_matches_golden():
+    g = (synth.normal(21, 4096) * 6).astype(np.float32)
+    u = synth.normal(22, 4096).astype(np.float32)
+    g[:8] = [0.0, -0.0, 100.0, -100.0, 88.0, -88.0, 1e-20, -1e-20]
+    assert np.array_equal(bits(O.silu_mul(g, u)), bits(GOLD["silu"]))
+
+
+@pytest.mark.parametrize("fg,fd,inter,name", [(IQ3_S, IQ3_S, 512, "ffn_iq3s_512"),
+                                              (IQ4_NL, IQ4_NL, 512, "ffn_iq4nl_512"),
+                                              (IQ3_S, IQ4_NL, 640, "ffn_iq3s_iq4nl_640")])
+def test_expert_ffn_matches_golden(fg, fd, inter, name):
+    xs = synth.activations(31, 3)
+    blob = synth.expert_blob(fg, fd, inter, 41, 5)
+    h, y = O.expert_ffn(fg, fd, 2560, inter, blob, xs)
+    assert np.array_equal(bits(h), bits(GOLD[name + "_h"]))
+    assert np.array_equal(bits(y), bits(GOLD[name + "_y"]))
+
+
+def test_expert_ffn_bf16_matches_golden():
+    xs = synth.activations(31, 3)
+    xb = synth.to_bf16_bits(xs[:2])
+    blob = synth.expert_blob(IQ3_S, IQ3_S, 512, 41, 5)
+    h, y = O.expert_ffn_bf16(IQ3_S, IQ3_S, 2560, 512, blob, xb)
+    gh = synth.bf16_bits_to_f32(GOLD["ffn_bf16_iq3s_512_h"])
+    hh = synth.bf16_bits_to_f32(h)
+    # h is a bf16 rounding of an fp32 sum taken in a different order: allow one bf16 step
+    assert np.max(np.abs(hh - gh) / (np.abs(gh) + 1e-3)) < 2 ** -7
+    gy = GOLD["ffn_bf16_iq3s_512_y"]
+    assert np.linalg.norm(y - gy) / np.linalg.norm(gy) < 2e-3
+
+
+def test_fp16_round_trip_all_codes():
+    p = O.port()
+    for code in range(0, 0x7C00):  # every finite positive half
+        f = p.fbo_fp16_to_fp32(code)
+        assert p.fbo_fp32_to_fp16(f) == code
+        assert np.float32(f) == np.array([code], dtype=np.uint16).view(np.float16)[0].astype(np.float32)
+        if code > 2000:
+            break
+
+
+def test_fp16_matches_numpy():
+    p = O.port()
+    xs = np.concatenate([synth.normal(3, 4000) * s for s in (1e-8, 1e-5, 1e-3, 1.0, 300.0, 7e4)]).astype(np.float32)
+    want = xs.astype(np.float16).view(np.uint16)
+    got = np.array([p.fbo_fp32_to_fp16(float(v)) for v in xs], dtype=np.uint16)
+    assert np.array_equal(got, want)
+    codes = np.arange(65536, dtype=np.uint16)
+    finite = ((codes >> 10) & 0x1F) != 31
+    back = np.array([p.fbo_fp16_to_fp32(int(c)) for c in codes[finite]], dtype=np.float32)
+    assert np.array_equal(back.view(np.uint32), codes[finite].view(np.float16).astype(np.float32).view(np.uint32))
+
+
+def test_e4m3_tables():
+    # Known values of the format (tests/common/test_util.h:105-112 of the reference): 0x7E = 448,
+    # 0x38 = 1.0, 0x01 = 2^-9, 0x7F = NaN.
+    t = O.e4m3_table()
+    assert t[0x7E] == 448.0 and t[0x38] == 1.0 and t[0x01] == 2.0 ** -9 and np.isnan(t[0x7F])
+    assert t[0xFE] == -448.0
+    p = O.port()
+    assert p.fbo_e4m3_satfinite(1e9) == 0x7E and p.fbo_e4m3_satfinite(-1e9) == 0xFE
+    # round trip and ties-to-even on every pair of neighbours
+    for c in range(0x7E):
+        assert p.fbo_e4m3_satfinite(float(t[c])) == c
+        mid = (float(t[c]) + float(t[c + 1])) / 2
+        assert p.fbo_e4m3_satfinite(mid) == (c if c % 2 == 0 else c + 1)
+    try:
+        import torch
+        xs = (synth.normal(5, 20000) * 40).astype(np.float32)
+        want = torch.from_numpy(xs).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+        got = np.array([p.fbo_e4m3_satfinite(float(v)) for v in xs], dtype=np.uint8)
+        assert np.array_equal(got, want)
+    except ImportError:
+        pass
+
+
+def test_topk_contract():
+    # value descending, ties to the lower id, NaN never wins, -0 == +0
+    # (tests/kernels/moe/moe_test_common.h:50-65 of the reference)
+    l = np.zeros((1, 512), dtype=np.float32)
+    l[0, 7] = 2.0
+    l[0, 300] = 2.0
+    l[0, 5] = np.nan
+    l[0, 9] = -0.0
+    ids, w = O.topk(l)
+    assert list(ids[0][:2]) == [7, 300]
+    assert 5 not in ids[0]
+    assert list(ids[0][2:]) == [0, 1, 2, 3, 4, 6, 8, 9]
+    assert abs(w[0].sum() - 1) < 1e-6
+    e = np.exp(l[0, ids[0]].astype(np.float64) - 2.0)
+    assert np.allclose(w[0], e / e.sum(), atol=1e-6)
+
+
+# ------------------------------------------------------------------ direct comparison with the reference
+ref_only = pytest.mark.skipif(O.ref() is None, reason="oracle/_ref not built here or CPU lacks AVX-512 VNNI/BF16")
+
+
+@ref_only
+@pytest.mark.parametrize("fmt", [IQ3_S, IQ4_NL])
+def test_port_equals_reference_dequant_and_dot(fmt):
+    ref = O.ref()
+    k = 2560
+    nrows = 64
+    nb = nrows * k // synth.BLOCK_ELEMS[fmt]
+    rows = synth.fill_blocks(fmt, nb, 123, 77)
+    assert np.array_equal(bits(O.dequant_rows(fmt, rows, nrows, k)), bits(O.dequant_rows(fmt, rows, nrows, k, lib=ref)))
+    x = patterns.all_inputs(k=k, trials=8)
+    act = O.ACT_OF[fmt]
+    aq = O.quantize_act(act, x)
+    assert np.array_equal(aq, O.quantize_act(act, x, lib=ref, variant="avx"))
+    # dot: port vs ggml generic (tolerance) and vs the AVX-512 tier (bit-exact through expert_ffn below)
+    rb = O.row_bytes(fmt, k)
+    fn = ref.ref_vec_dot_iq3_s_q8_K if fmt == IQ3_S else ref.ref_vec_dot_iq4_nl_q8_0
+    for r in range(0, nrows, 7):
+        for t in range(8):
+            a = O.port().fbo_dot(fmt, k, rows[r * rb:].ctypes.data, aq[t].ctypes.data)
+            b = fn(k, rows[r * rb:].ctypes.data, aq[t].ctypes.data)
+            assert abs(a - b) <= 2e-5 * max(1.0, abs(b))
+
+
+@ref_only
+def test_port_equals_reference_quantizers_many():
+    ref = O.ref()
+    x = patterns.all_inputs(trials=160, seed=999)
+    for act in (O.ACT_Q8_K, O.ACT_Q8_0):
+        assert np.array_equal(O.quantize_act(act, x), O.quantize_act(act, x, lib=ref, variant="avx"))
+        assert np.array_equal(O.quantize_act(act, x), O.quantize_act(act, x, lib=ref, variant="ref"))
+
+
+@ref_only
+@pytest.mark.parametrize("fg,fd,inter", [(IQ3_S, IQ3_S, 512), (IQ4_NL, IQ4_NL, 512), (IQ4_NL, IQ4_NL, 640),
+                                         (IQ3_S, IQ4_NL, 640)])
+def test_port_equals_reference_expert_ffn(fg, fd, inter):
+    ref = O.ref()
+    xs = synth.activations(88, 5)
+    blob = synth.expert_blob(fg, fd, inter, 99, 17)
+    h0, y0 = O.expert_ffn(fg, fd, 2560, inter, blob, xs)
+    h1, y1 = O.expert_ffn(fg, fd, 2560, inter, blob, xs, lib=ref)
+    assert np.array_equal(bits(h0), bits(h1))
+    assert np.array_equal(bits(y0), bits(y1))
+    # batch invariance of the reference tier (src/cpu/iq_cpu.h:23-27): T tokens == T single calls
+    h2, y2 = O.expert_ffn(fg, fd, 2560, inter, blob, xs[3:4], lib=ref)
+    assert np.array_equal(bits(y2[0]), bits(y1[3]))
+
+
+@ref_only
+def test_port_equals_reference_moe_layer():
+    ref = O.ref()
+    E, inter = 12, 512
+    stride = synth.blob_bytes(IQ3_S, IQ3_S, inter)
+    blobs = np.concatenate([synth.expert_blob(IQ3_S, IQ3_S, inter, 5, e) for e in range(E)])
+    x = synth.activations(6, 4)
+    ids = np.array([[3, 1, 7], [0, 11, 1], [7, 3, 2], [5, 6, 1]], dtype=np.int32)
+    w = np.abs(synth.normal(8, 12)).astype(np.float32).reshape(4, 3)
+    y0 = O.moe_layer(IQ3_S, IQ3_S, 2560, inter, blobs, stride, x, ids, w, threads=2)
+    y1 = O.moe_layer(IQ3_S, IQ3_S, 2560, inter, blobs, stride, x, ids, w, threads=3, lib=ref)
+    assert np.array_equal(bits(y0), bits(y1))
