@@ -1,0 +1,351 @@
+"""GPU parity tests of the decode path, through the C ABI, against the CPU oracle.
+
+Bars: dequantized weights and int8 activations bit-exact; router ids exact on the GPU's own logits,
+weights within 1e-6; expert and layer outputs within 1e-3 relative L2 per token row
+(the metric of tests/cpu/test_expert_pool.cpp:166-188 of the reference), measured at ~1e-6.
+"""
+import numpy as np
+import pytest
+
+from fngine_b200 import synth
+from oracle import oracle as O
+import patterns
+
+pytestmark = pytest.mark.gpu
+
+IQ3_S, IQ4_NL = 21, 20
+H = 2560
+TOL = 1e-3  # relative L2 per row, the bar stated for fp32 expert outputs
+
+
+def _torch():
+    import torch
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch
+
+
+def rel_l2(got, want):
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    return float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+
+
+def fast_lib():
+    """The reference build where it runs (AVX-512 hosts), else the scalar port: same results."""
+    return O.ref()
+
+
+def planar_from_blocks(act, blocks, k):
+    """ggml activation blocks -> (codes int8 [k] in the workspace order, scales float32)."""
+    if act == O.ACT_Q8_K:
+        b = blocks.reshape(k // 256, 292)
+        return b[:, 4:260].reshape(-1).view(np.int8), b[:, :4].copy().view(np.float32).reshape(-1)
+    b = blocks.reshape(k // 32, 34)
+    d = b[:, :2].copy().view(np.float16).astype(np.float32).reshape(-1)
+    q = b[:, 2:].view(np.int8)
+    order = np.array([2 * (e % 16) + e // 16 for e in range(32)])
+    inter = np.empty_like(q)
+    inter[:, order] = q
+    return inter.reshape(-1), d
+
+
+# ---------------------------------------------------------------------------------- probes
+@pytest.mark.parametrize("fmt", [IQ3_S, IQ4_NL])
+def test_synth_device_equals_host(fmt):
+    torch = _torch()
+    from fngine_b200 import moe
+    layer = moe.synth_layer(fmt, fmt, 512, 3, 77)
+    torch.cuda.synchronize()
+    dev = layer.slots.cpu().numpy()
+    for e in range(3):
+        host = synth.expert_blob(fmt, fmt, 512, 77, e)
+        assert np.array_equal(dev[e * len(host):(e + 1) * len(host)], host)
+
+
+@pytest.mark.parametrize("fmt,k", [(IQ3_S, 2560), (IQ3_S, 512), (IQ4_NL, 2560), (IQ4_NL, 640)])
+def test_dequant_bit_exact(fmt, k):
+    torch = _torch()
+    from fngine_b200 import moe
+    nrows = 96
+    rows = synth.fill_blocks(fmt, nrows * k // synth.BLOCK_ELEMS[fmt], 5, 31)
+    got = moe.dequant_rows(fmt, torch.from_numpy(rows).cuda(), nrows, k).cpu().numpy()
+    want = O.dequant_rows(fmt, rows, nrows, k)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("act", [O.ACT_Q8_K, O.ACT_Q8_0])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_quantize_act_bit_exact(act, bf16):
+    torch = _torch()
+    from fngine_b200 import moe
+    x = patterns.all_inputs(trials=64, seed=4321)
+    if bf16:
+        bits = synth.to_bf16_bits(x)
+        x = synth.bf16_bits_to_f32(bits)
+        xd = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+    else:
+        xd = torch.from_numpy(x).cuda()
+    got = moe.quantize_act(act, xd).cpu().numpy()
+    want = O.quantize_act(act, x)
+    assert np.array_equal(got, want)
+
+
+# ---------------------------------------------------------------------------------- router + select
+def run_layer(torch, moe, layer, ws, wr, x, tokens, slot_of=None, logits=None):
+    if logits is None:
+        moe.router_logits(wr, x, ws.logits)
+        logits = ws.logits
+    moe.moe_select_publish(logits, x, slot_of, 0, None, None, tokens, ws)
+    moe.moe_hot_gate_up(layer, tokens, ws)
+    moe.moe_hot_down(layer, tokens, ws)
+    y = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    moe.moe_combine(ws, None, None, 0, None, None, None, y, tokens)
+    torch.cuda.synchronize()
+    return y
+
+
+def check_work_list(work, ids, w, tokens, slot_of=None):
+    """Invariants of the sorted work list (moe.h:87-105 of the reference)."""
+    slots = ids if slot_of is None else slot_of[ids]
+    distinct = sorted(set(slots.reshape(-1).tolist()))
+    assert work.n_items == len(distinct) and work.n_pairs == tokens * 10 and work.n_cold == 0
+    assert list(work.item_slot[:work.n_items]) == distinct
+    assert work.item_pair_begin[0] == 0 and work.item_pair_begin[work.n_items] == work.n_pairs
+    for it, s in enumerate(distinct):
+        b, e = work.item_pair_begin[it], work.item_pair_begin[it + 1]
+        toks = [t for t in range(tokens) if s in slots[t]]
+        assert list(work.pair_token[b:e]) == toks  # tokens ascending inside an item
+        for p, t in zip(range(b, e), toks):
+            k = list(slots[t]).index(s)
+            assert abs(work.pair_weight[p] - w[t, k]) <= 1e-6
+    for t in range(tokens):
+        assert work.token_pair_count[t] == 10
+        pairs = list(work.token_pairs[t])
+        assert pairs == sorted(pairs)  # slot order == pair order
+        assert sorted(work.pair_token[p] for p in pairs) == [t] * 10
+
+
+@pytest.mark.parametrize("tokens,bf16", [(1, False), (4, False), (16, False), (9, True)])
+def test_router_and_select(tokens, bf16):
+    torch = _torch()
+    from fngine_b200 import moe
+    wr_bits = synth.router_weights(101, rows=513)
+    wr = torch.from_numpy(wr_bits.view(np.int16)).cuda().view(torch.bfloat16)
+    x = synth.activations(202, tokens)
+    if bf16:
+        xb = synth.to_bf16_bits(x)
+        x = synth.bf16_bits_to_f32(xb)
+        xd = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    else:
+        xd = torch.from_numpy(x).cuda()
+    layer = moe.synth_layer(IQ3_S, IQ3_S, 512, 8, 1)  # only the formats matter here
+    ws = moe.DecodeWorkspace(layer)
+    moe.router_logits(wr, xd, ws.logits)
+    logits = ws.logits.cpu().numpy()[:tokens * 513].reshape(tokens, 513)
+    want = x.astype(np.float64) @ synth.bf16_bits_to_f32(wr_bits).astype(np.float64).T
+    assert np.max(np.abs(logits - want)) <= 1e-4 * np.sqrt(np.mean(want ** 2))
+    moe.moe_select_publish(ws.logits, xd, None, 0, None, None, tokens, ws)
+    torch.cuda.synchronize()
+    ids, w = O.topk(logits[:, :512])
+    work = ws.work()
+    got_ids = np.array([list(work.topk_expert[t]) for t in range(tokens)])
+    got_w = np.array([list(work.topk_weight[t]) for t in range(tokens)])
+    assert np.array_equal(got_ids, ids)
+    assert np.max(np.abs(got_w - w)) <= 1e-6
+    check_work_list(work, ids, w, tokens)
+    # int8 activations: bit-identical to the host quantizer
+    xq = ws.xq(tokens)
+    for t in range(tokens):
+        codes, scales = planar_from_blocks(O.ACT_Q8_K, O.quantize_act(O.ACT_Q8_K, x[t]), H)
+        assert np.array_equal(xq[t, :H].view(np.int8), codes)
+        assert np.array_equal(xq[t, H:H + 40].copy().view(np.float32), scales)
+    assert ws.status() == 0
+
+
+def test_select_ties_nan_and_slot_map():
+    torch = _torch()
+    from fngine_b200 import moe
+    tokens = 3
+    logits = (synth.normal(5, tokens * 513) * 0.5).astype(np.float32).reshape(tokens, 513)
+    logits[0, [7, 300, 40]] = 3.0       # ties -> lower id first
+    logits[1, 11] = np.nan              # NaN never wins
+    logits[2, :] = 0.0                  # all equal: ids 0..9
+    logits[2, 3] = -0.0
+    ids, w = O.topk(logits[:, :512])
+    assert list(ids[0][:3]) == [7, 40, 300] and 11 not in ids[1] and list(ids[2]) == list(range(10))
+    perm = np.random.default_rng(3).permutation(512).astype(np.int32)
+    layer = moe.synth_layer(IQ3_S, IQ3_S, 512, 8, 1)
+    ws = moe.DecodeWorkspace(layer)
+    x = torch.from_numpy(synth.activations(1, tokens)).cuda()
+    for slot_of in (None, perm):
+        sd = None if slot_of is None else torch.from_numpy(slot_of).cuda()
+        moe.moe_select_publish(torch.from_numpy(logits).cuda(), x, sd, 0, None, None, tokens, ws)
+        torch.cuda.synchronize()
+        work = ws.work()
+        got_ids = np.array([list(work.topk_expert[t]) for t in range(tokens)])
+        assert np.array_equal(got_ids, ids)
+        check_work_list(work, ids, w, tokens, slot_of)
+
+
+# ---------------------------------------------------------------------------------- experts
+def forced_logits(tokens, experts_per_token):
+    """Router logits that make token t pick exactly experts_per_token[t] (descending preference)."""
+    l = np.full((tokens, 513), -30.0, dtype=np.float32)
+    for t, es in enumerate(experts_per_token):
+        for r, e in enumerate(es):
+            l[t, e] = 4.0 - 0.37 * r
+    return l
+
+
+@pytest.mark.parametrize("fg,fd,inter", [(IQ3_S, IQ3_S, 512), (IQ4_NL, IQ4_NL, 512), (IQ3_S, IQ4_NL, 640),
+                                         (IQ4_NL, IQ4_NL, 640)])
+def test_single_expert_rows(fg, fd, inter):
+    """One token through ten experts: every h row and every weighted partial row against the CPU
+    expert path on identical bytes (the single-expert case of the benchmark definition, ten times)."""
+    torch = _torch()
+    from fngine_b200 import moe
+    n_exp = 16
+    layer = moe.synth_layer(fg, fd, inter, n_exp, 4242)
+    ws = moe.DecodeWorkspace(layer)
+    x = synth.activations(9, 1)
+    xd = torch.from_numpy(x).cuda()
+    chosen = [[12, 3, 5, 0, 9, 15, 1, 7, 8, 2]]
+    logits = torch.from_numpy(forced_logits(1, chosen)).cuda()
+    y = run_layer(torch, moe, layer, ws, None, xd, 1, logits=logits).cpu().numpy()
+    work = ws.work()
+    ids, w = O.topk(forced_logits(1, chosen)[:, :512])
+    hs, parts = ws.h(10), ws.partial(10)
+    y_ref = np.zeros(H, dtype=np.float64)
+    worst_h = worst_y = 0.0
+    for it in range(work.n_items):
+        e = work.item_slot[it]
+        p = work.item_pair_begin[it]
+        blob = synth.expert_blob(fg, fd, inter, 4242, e)
+        h_ref, ye = O.expert_ffn(fg, fd, H, inter, blob, x, lib=fast_lib())
+        wt = float(w[0][list(ids[0]).index(e)])
+        worst_h = max(worst_h, rel_l2(hs[p], h_ref[0]))
+        worst_y = max(worst_y, rel_l2(parts[p], wt * ye[0]))
+        y_ref += wt * ye[0].astype(np.float64)
+    assert worst_h <= TOL and worst_y <= TOL, (worst_h, worst_y)
+    assert rel_l2(y[0], y_ref) <= TOL
+    assert ws.status() == 0
+    print("single expert rows: max rel h %.2e, partial %.2e, y %.2e" % (worst_h, worst_y, rel_l2(y[0], y_ref)))
+
+
+def oracle_layer(fg, fd, inter, seed, x, ids, w):
+    """CPU layer over only the experts that were selected (blobs regenerated on the host)."""
+    used = sorted(set(ids.reshape(-1).tolist()))
+    remap = {e: i for i, e in enumerate(used)}
+    blobs = np.concatenate([synth.expert_blob(fg, fd, inter, seed, e) for e in used])
+    ids2 = np.vectorize(remap.get)(ids).astype(np.int32)
+    stride = synth.blob_bytes(fg, fd, inter)
+    return O.moe_layer(fg, fd, H, inter, blobs, stride, x, ids2, w, threads=8, lib=fast_lib())
+
+
+@pytest.mark.parametrize("fg,fd,inter,tokens", [(IQ3_S, IQ3_S, 512, 1), (IQ3_S, IQ3_S, 512, 4),
+                                                (IQ3_S, IQ3_S, 512, 16), (IQ4_NL, IQ4_NL, 512, 1),
+                                                (IQ4_NL, IQ4_NL, 512, 8), (IQ3_S, IQ4_NL, 640, 5)])
+def test_moe_layer_decode(fg, fd, inter, tokens):
+    """The MoE layer of the benchmark definition: 512 experts, bf16 router ~ N(0, 0.02), top-10."""
+    torch = _torch()
+    from fngine_b200 import moe
+    seed = 1000 + inter + fg
+    layer = moe.synth_layer(fg, fd, inter, 512, seed)
+    ws = moe.DecodeWorkspace(layer)
+    wr_bits = synth.router_weights(303, rows=512)
+    wr = torch.from_numpy(wr_bits.view(np.int16)).cuda().view(torch.bfloat16)
+    x = synth.activations(404 + tokens, tokens)
+    xd = torch.from_numpy(x).cuda()
+    y = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    moe.moe_layer_decode(wr, layer, xd, ws, y)
+    torch.cuda.synchronize()
+    y1 = y.cpu().numpy()
+    logits = ws.logits.cpu().numpy()[:tokens * 513].reshape(tokens, 513)[:, :512]
+    ids, w = O.topk(logits)
+    work = ws.work()
+    assert np.array_equal(np.array([list(work.topk_expert[t]) for t in range(tokens)]), ids)
+    want = oracle_layer(fg, fd, inter, seed, x, ids, w)
+    errs = [rel_l2(y1[t], want[t]) for t in range(tokens)]
+    assert max(errs) <= TOL, errs
+    assert ws.status() == 0
+    # repeated calls are bitwise identical (fixed reduction order)
+    moe.moe_layer_decode(wr, layer, xd, ws, y)
+    torch.cuda.synchronize()
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), y1.view(np.uint32))
+    print("layer fmt %d/%d inter %d T=%d: distinct experts %d, max rel L2 %.2e" %
+          (fg, fd, inter, tokens, work.n_items, max(errs)))
+
+
+@pytest.mark.parametrize("fg,fd", [(IQ3_S, IQ3_S), (IQ4_NL, IQ4_NL)])
+def test_crowded_experts_and_h_requantization(fg, fd):
+    """All 16 tokens on the same ten experts (more tokens per expert than one pass holds), and the
+    re-quantized h of every pair bit-identical to the host quantizer applied to the GPU's own h."""
+    torch = _torch()
+    from fngine_b200 import moe
+    tokens, inter = 16, 512
+    layer = moe.synth_layer(fg, fd, inter, 32, 77)
+    ws = moe.DecodeWorkspace(layer)
+    chosen = [[(3 * i + r) % 32 for i in range(10)] for r in (0,) * 11 + (1, 1, 1, 2, 2)]
+    lg = forced_logits(tokens, chosen)
+    x = synth.activations(55, tokens)
+    y = run_layer(torch, moe, layer, ws, None, torch.from_numpy(x).cuda(), tokens,
+                  logits=torch.from_numpy(lg).cuda()).cpu().numpy()
+    ids, w = O.topk(lg[:, :512])
+    want = oracle_layer(fg, fd, inter, 77, x, ids, w)
+    errs = [rel_l2(y[t], want[t]) for t in range(tokens)]
+    assert max(errs) <= TOL, errs
+    work = ws.work()
+    assert max(work.item_pair_begin[i + 1] - work.item_pair_begin[i] for i in range(work.n_items)) >= 11
+    act = O.ACT_OF[fd]
+    hs, hq = ws.h(work.n_pairs), ws.hq(work.n_pairs)
+    nscale = inter // (256 if act == O.ACT_Q8_K else 32)
+    for p in range(work.n_pairs):
+        codes, scales = planar_from_blocks(act, O.quantize_act(act, hs[p]), inter)
+        assert np.array_equal(hq[p, :inter].view(np.int8), codes)
+        assert np.array_equal(hq[p, inter:inter + 4 * nscale].copy().view(np.float32), scales)
+    assert ws.status() == 0
+
+
+def test_combine_shared_residual_and_ablation():
+    """y_shared, the 4-stream residual write X += inj * y and the rank-1 ablation of the routed part
+    (moe.h:144-158 of the reference)."""
+    torch = _torch()
+    from fngine_b200 import moe
+    tokens = 3
+    layer = moe.synth_layer(IQ3_S, IQ3_S, 512, 16, 5)
+    ws = moe.DecodeWorkspace(layer)
+    lg = forced_logits(tokens, [[(t + i) % 16 for i in range(10)] for t in range(tokens)])
+    x = torch.from_numpy(synth.activations(3, tokens)).cuda()
+    y0 = run_layer(torch, moe, layer, ws, None, x, tokens, logits=torch.from_numpy(lg).cuda())
+    ysh = torch.from_numpy(synth.activations(4, tokens) * 1e5).cuda()
+    inj = torch.from_numpy(synth.normal(6, tokens * 4).astype(np.float32).reshape(tokens, 4)).cuda()
+    X0 = torch.from_numpy(synth.normal(7, tokens * 4 * H).astype(np.float32).reshape(tokens, 4, H)).cuda()
+    X = X0.clone()
+    r = torch.from_numpy(synth.normal(8, H).astype(np.float32)).cuda()
+    r = r / r.norm()
+    yo = torch.empty_like(y0)
+    moe.moe_combine(ws, ysh, None, 0, None, inj, X, yo, tokens, 0, r, 0.75)
+    torch.cuda.synchronize()
+    routed = y0.double() - 0.75 * r.double()[None, :] * (y0.double() @ r.double())[:, None]
+    want = routed + ysh.double()
+    assert rel_l2(yo.cpu().numpy(), want.cpu().numpy()) <= 1e-5
+    wantX = X0.double() + inj.double()[:, :, None] * want[:, None, :]
+    assert rel_l2(X.cpu().numpy(), wantX.cpu().numpy()) <= 1e-5
+
+
+def test_host_entry_point_matches_device_path():
+    torch = _torch()
+    from fngine_b200 import moe
+    tokens = 4
+    layer = moe.synth_layer(IQ3_S, IQ3_S, 512, 512, 9)
+    ws = moe.DecodeWorkspace(layer)
+    wr = torch.from_numpy(synth.router_weights(303, rows=512).view(np.int16)).cuda().view(torch.bfloat16)
+    xh = torch.from_numpy(synth.activations(12, tokens)).pin_memory()
+    yh = torch.empty(tokens, H, dtype=torch.float32).pin_memory()
+    xd = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    yd = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    moe.moe_layer_decode_host(wr, layer, xh, ws, xd, yd, yh)
+    y2 = torch.empty_like(yd)
+    moe.moe_layer_decode(wr, layer, xh.cuda(), ws, y2)
+    torch.cuda.synchronize()
+    assert np.array_equal(yh.numpy().view(np.uint32), y2.cpu().numpy().view(np.uint32))
