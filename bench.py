@@ -1,0 +1,360 @@
+"""Benchmark of the quantized-expert decode path (one JSON line on stdout).
+
+Workload (N = 1): one decode step of a stack of MoE layers, each with 512 IQ3_S experts
+(hidden 2560, intermediate 512, gate/up/down all IQ3_S), a bf16 router ~ N(0, 0.02), softmax top-10
+routing, batch 16 tokens of fp32 x ~ N(0, 1) per layer. The layers only rotate the weight set: every
+layer owns its own 865 MB of expert bytes, so with >= 8 layers each launch streams weights the
+126 MB L2 cannot hold. metric = weight bytes the step has to read (distinct routed experts x
+1,689,600 B + router) / device time, in GB/s.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+--impl reference times the reference's own CPU expert path (oracle/_ref when it was built and the
+host CPU can run it, else this repository's scalar restatement) on the host cores, same metric.
+N > 1 (launched under torchrun, one rank per GPU) shards the 512 experts over the ranks; see
+fngine_b200/ep.py.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FMT = 21  # IQ3_S
+INTER = 512
+HIDDEN = 2560
+TOPK = 10
+EXPERTS = 512
+BLOB = 1689600
+ROUTER_BYTES = EXPERTS * HIDDEN * 2
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def host_routing(wr_bits, x):
+    """Router projection and top-10 on the host (numpy fp32 + the oracle's top-k)."""
+    from fngine_b200 import synth
+    from oracle import oracle as O
+    logits = x.astype(np.float32) @ synth.bf16_bits_to_f32(wr_bits).T
+    return O.topk(np.ascontiguousarray(logits[:, :EXPERTS]))
+
+
+def cpu_layer_runner(seed, x, ids, w, threads):
+    """Returns (callable running one CPU MoE layer step, bytes it streams, kind)."""
+    from fngine_b200 import synth
+    from oracle import oracle as O
+    lib = O.ref()
+    kind = "reference" if lib is not None else "port"
+    used = sorted(set(ids.reshape(-1).tolist()))
+    tables = {FMT: synth.d_table(FMT)}
+    blobs = np.concatenate([synth.expert_blob(FMT, FMT, INTER, seed, e, tables=tables) for e in used])
+    ids2 = np.vectorize({e: i for i, e in enumerate(used)}.get)(ids).astype(np.int32)
+
+    def run():
+        return O.moe_layer(FMT, FMT, HIDDEN, INTER, blobs, BLOB, x, ids2, w, threads=threads, lib=lib)
+
+    return run, len(used) * BLOB + ROUTER_BYTES, kind
+
+
+def run_reference(args, rank):
+    """The reference arm: the reference's CPU expert path on the host cores, rank 0 only."""
+    if rank != 0:
+        return
+    from fngine_b200 import synth
+    threads = os.cpu_count() or 1
+    layers = min(args.layers, 4)
+    runners = []
+    for l in range(layers):
+        wr = synth.router_weights(9000 + l)
+        x = synth.activations(7000 + l, args.batch)
+        ids, w = host_routing(wr, x)
+        runners.append(cpu_layer_runner(5000 + l, x, ids, w, threads))
+    kind = runners[0][2]
+    for i in range(args.warmup):
+        runners[i % layers][0]()
+    t0 = time.perf_counter()
+    nbytes = 0
+    for i in range(args.steps):
+        run, b, _ = runners[i % layers]
+        run()
+        nbytes += b
+    dt = time.perf_counter() - t0
+    gbs = nbytes / dt / 1e9
+    sample = "%d steps, each one MoE layer of batch %d (distinct routed experts only), %d layers rotated" % (
+        args.steps, args.batch, layers)
+    line = {"impl": "reference", "metric": "iq3s_expert_gemv_hbm_gbs", "value": gbs, "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": workload_config(args, 1),
+            "tokens_per_s": args.batch * args.steps / dt,
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def workload_config(args, layers_per_step):
+    return {"workload": "MoE layer at decode: 512 IQ3_S experts (hidden 2560, inter 512, gate/up/down IQ3_S), "
+                        "bf16 router N(0,0.02), softmax top-10, batch %d fp32 x~N(0,1)" % args.batch,
+            "batch": args.batch, "layers_per_step": layers_per_step, "experts": EXPERTS, "top_k": TOPK,
+            "l2_policy": "inputs larger than L2: every layer has its own 865 MB expert set, "
+                         "%d layers rotate (%.1f GB resident)" % (args.layers, args.layers * EXPERTS * BLOB / 1e9),
+            "activation_format": "Q8_K (reference CPU tier numerics)"}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    from fngine_b200 import lib as fblib
+    from fngine_b200 import moe, synth
+    fblib.load()  # fails loudly when the CUDA library is missing: there is no CPU path
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        from fngine_b200 import ep
+        return ep.bench_main(args, rank, world, local_rank)
+
+    B, Lr = args.batch, args.layers
+    layers, routers, xs_host, xs = [], [], [], []
+    for l in range(Lr):
+        layers.append(moe.synth_layer(FMT, FMT, INTER, EXPERTS, 5000 + l))
+        wr = synth.router_weights(9000 + l)
+        routers.append(torch.from_numpy(wr.view(np.int16)).cuda().view(torch.bfloat16))
+        xh = torch.from_numpy(synth.activations(7000 + l, B)).pin_memory()
+        xs_host.append(xh)
+        xs.append(xh.cuda())
+    ws = moe.DecodeWorkspace(layers[0])
+    y = torch.empty(B, HIDDEN, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+
+    def step():
+        for l in range(Lr):
+            moe.moe_layer_decode(routers[l], layers[l], xs[l], ws, y)
+
+    # distinct experts per layer (the routing is a function of the seeded inputs only)
+    distinct, ids_layer0 = [], None
+    for l in range(Lr):
+        moe.moe_layer_decode(routers[l], layers[l], xs[l], ws, y)
+        torch.cuda.synchronize()
+        wk = ws.work()
+        distinct.append(wk.n_items)
+        if l == 0:
+            ids_layer0 = (np.array([list(wk.topk_expert[t]) for t in range(B)], dtype=np.int32),
+                          np.array([list(wk.topk_weight[t]) for t in range(B)], dtype=np.float32))
+    step_bytes = sum(d * BLOB + ROUTER_BYTES for d in distinct)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+
+    # per-kernel device times over the same steps (gate/up is the dominant kernel)
+    evs = []
+    for _ in range(args.steps):
+        for l in range(Lr):
+            moe.router_logits(routers[l], xs[l], ws.logits)
+            moe.moe_select_publish(ws.logits, xs[l], None, 0, None, None, B, ws)
+            a, b, c, d = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+            a.record()
+            moe.moe_hot_gate_up(layers[l], B, ws)
+            b.record()
+            moe.moe_hot_down(layers[l], B, ws)
+            c.record()
+            moe.moe_combine(ws, None, None, 0, None, None, None, y, B)
+            d.record()
+            evs.append((l, a, b, c, d))
+    torch.cuda.synchronize()
+    gu_ms = [a.elapsed_time(b) for (_, a, b, _, _) in evs]
+    dn_ms = [b.elapsed_time(c) for (_, _, b, c, _) in evs]
+    gu_bytes = [distinct[l] * (BLOB * 2 // 3) for (l, *_r) in evs]
+    dn_bytes = [distinct[l] * (BLOB // 3) for (l, *_r) in evs]
+
+    # end to end through the host entry point: pinned host x in, host y out, every layer
+    yh = torch.empty(B, HIDDEN, dtype=torch.float32).pin_memory()
+    xd = torch.empty(B, HIDDEN, dtype=torch.float32, device="cuda")
+    for l in range(Lr):
+        moe.moe_layer_decode_host(routers[l], layers[l], xs_host[l], ws, xd, y, yh)
+    torch.cuda.synchronize()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        for l in range(Lr):
+            moe.moe_layer_decode_host(routers[l], layers[l], xs_host[l], ws, xd, y, yh)
+    f1.record()
+    torch.cuda.synchronize()
+    e2e_ms = f0.elapsed_time(f1)
+    clocks = sampler.stop()
+    status = ws.status()
+
+    # other batch sizes of the same layer definition, CUDA-graph replayed (launch-bound otherwise)
+    other = {}
+    for b2 in (1, 4):
+        xs2 = [x[:b2].contiguous() for x in xs]
+        d2 = []
+        for l in range(Lr):
+            moe.moe_layer_decode(routers[l], layers[l], xs2[l], ws, y)
+            torch.cuda.synchronize()
+            d2.append(ws.work().n_items)
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g, stream=s):
+                for l in range(Lr):
+                    moe.moe_layer_decode(routers[l], layers[l], xs2[l], ws, y)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            g.replay()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(args.steps):
+            g.replay()
+        g1.record()
+        torch.cuda.synchronize()
+        t = g0.elapsed_time(g1) / args.steps
+        by = sum(d * BLOB + ROUTER_BYTES for d in d2)
+        other[str(b2)] = {"gbs": by / t / 1e6, "us_per_layer": t / Lr * 1e3, "distinct_experts_mean": sum(d2) / Lr,
+                          "timing": "CUDA graph of %d layers" % Lr}
+
+    # CPU baseline beside it: the same layer-0 step on the host cores, bounded to ~10 s
+    threads = os.cpu_count() or 1
+    run_cpu, cpu_bytes, kind = cpu_layer_runner(5000, xs_host[0].numpy(), ids_layer0[0], ids_layer0[1], threads)
+    y_cpu = run_cpu()
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        run_cpu()
+        reps += 1
+        if time.perf_counter() - t0 > (10.0 if kind == "reference" else 1.0) or reps >= 2000:
+            break
+    cpu_dt = (time.perf_counter() - t0) / reps
+    # the GPU result of that layer against the CPU result (parity of the measured workload)
+    moe.moe_layer_decode(routers[0], layers[0], xs[0], ws, y)
+    torch.cuda.synchronize()
+    yg = y.cpu().numpy()
+    parity = float(max(np.linalg.norm(yg[t] - y_cpu[t]) / np.linalg.norm(y_cpu[t]) for t in range(B)))
+
+    peak, peak_src = peaks()
+    gu_ach = sum(gu_bytes) / (sum(gu_ms) * 1e-3) / 1e9
+    value = step_bytes * args.steps / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "iq3s_expert_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": workload_config(args, Lr),
+        "tokens_per_s": B * Lr * args.steps / (ms * 1e-3),
+        "us_per_layer": ms / args.steps / Lr * 1e3,
+        "distinct_experts_per_layer": distinct,
+        "frac_of_hbm_peak": value / peak,
+        "roofline": {"bound": "hbm", "kernel": "gate_up_kernel<IQ3_S>", "achieved": gu_ach, "peak": peak,
+                     "unit": "GB/s", "frac": gu_ach / peak, "peak_source": peak_src, "traffic": None,
+                     "us_per_launch": sum(gu_ms) / len(gu_ms) * 1e3,
+                     "algorithmic_bytes_per_launch": sum(gu_bytes) / len(gu_bytes),
+                     "down_kernel": {"achieved": sum(dn_bytes) / (sum(dn_ms) * 1e-3) / 1e9,
+                                     "us_per_launch": sum(dn_ms) / len(dn_ms) * 1e3}},
+        "cpu_baseline": {"value": cpu_bytes / cpu_dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+                         "sample": "layer 0 of the same workload (batch %d, %d distinct experts), %d repetitions, "
+                                   "%.2f ms each" % (B, distinct[0], reps, cpu_dt * 1e3)},
+        "e2e": {"value": step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": B * HIDDEN * 4 * Lr, "d2h_bytes_per_step": B * HIDDEN * 4 * Lr,
+                "ms_per_step": e2e_ms / args.steps,
+                "api": "fb_moe_layer_decode_host per layer: pinned host x in, host y out, stream wait inside"},
+        "gpu_launches": args.steps * Lr * 4,
+        "other_batches": other,
+        "parity_vs_cpu_max_rel_l2": parity,
+        "device_status": status,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--layers", type=int, default=8)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -51,40 +51,66 @@ __device__ __forceinline__ void iq3s_tables_fill(uint32_t* gridrep, uint32_t* si
 }
 
 // ------------------------------------------------------------------------------ IQ3_S
-// One 32-weight sub-block: qs_lo/qs_hi = its 8 index bytes, qh = the byte with the 8 ninth index
-// bits, signs = its 4 sign bytes. Produces 8 words of four signed int8 weights in element order.
-// grid_lane = gridrep + lane.
-__device__ __forceinline__ void iq3s_decode32(uint32_t qs_lo, uint32_t qs_hi, uint32_t qh, uint32_t signs,
-                                              const uint32_t* grid_lane, const uint32_t* signtab, int (&w)[8]) {
+// One 32-weight sub-block. Inputs: qs_lo/qs_hi = its 8 index bytes, qh = a word whose bits
+// [sh, sh+8) are the 8 ninth index bits, sg = its 4 sign bytes (nibble l = signs of look-up l).
+// Outputs per look-up l: g[l] = four magnitudes (bytes, element order), m[l] = 0xFF in the bytes
+// whose weight is negative. grid_lane = gridrep + lane.
+//
+// Instruction budget matters here (the integer pipe, not HBM, bounds this kernel): the ninth
+// index bits are spread to bytes with one multiply per nibble, then each 9-bit index is one
+// byte-permute (low byte from qs, high byte from the spread bits) and each sign-table offset is
+// one byte-permute of the pre-scaled nibbles.
+// prmt.b32 in its default mode: selector nibble n picks byte (n & 7) of {a, b}; with bit 3 set the
+// selected byte's sign bit is replicated over the output byte instead (0x00 for bytes < 0x80).
+// (__byte_perm documents only three selector bits per byte, so the PTX form is spelled out.)
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+
+__device__ __forceinline__ void iq3s_decode_sub(uint32_t qs_lo, uint32_t qs_hi, uint32_t qh, int sh, uint32_t sg,
+                                                const uint32_t* grid_lane, const uint32_t* signtab,
+                                                uint32_t (&g)[8], uint32_t (&m)[8]) {
+  // bit j of a nibble -> byte j (0 or 1): n * (1 + 2^7 + 2^14 + 2^21) has bit j at position 8j
+  const uint32_t h_lo = (((qh >> sh) & 0xFu) * 0x00204081u) & 0x01010101u;
+  const uint32_t h_hi = (((qh >> (sh + 4)) & 0xFu) * 0x00204081u) & 0x01010101u;
+  // nibbles pre-scaled by 4 (byte offsets into the 16-word sign table)
+  const uint32_t s_even = (sg << 2) & 0x3C3C3C3Cu;  // look-ups 0,2,4,6
+  const uint32_t s_odd = (sg >> 2) & 0x3C3C3C3Cu;   // look-ups 1,3,5,7
+  const char* signb = reinterpret_cast<const char*>(signtab);
 #pragma unroll
   for (int l = 0; l < 8; ++l) {
-    const uint32_t src = l < 4 ? qs_lo : qs_hi;
-    const uint32_t q = (src >> (8 * (l & 3))) & 0xFFu;
-    const uint32_t idx = q | (((qh >> l) & 1u) << 8);
-    const uint32_t g = grid_lane[idx * 32];
-    const uint32_t m = signtab[(signs >> (4 * l)) & 0xFu];
-    // Byte-wise negation where m = 0xFF: (g ^ 0xFF) + 1 never carries because every magnitude is odd.
-    w[l] = int((g ^ m) + (m & 0x01010101u));
+    const int b = l & 3;
+    // byte0 = qs byte b, byte1 = spread bit b, bytes 2-3 = 0 (sign-replicate of a 0/1 byte)
+    const uint32_t sel = uint32_t(b) | (uint32_t(4 + b) << 4) | (uint32_t(0xC + b) << 8) | (uint32_t(0xC + b) << 12);
+    const uint32_t idx = prmt(l < 4 ? qs_lo : qs_hi, l < 4 ? h_lo : h_hi, sel);
+    g[l] = grid_lane[idx * 32];
+    const uint32_t off = __byte_perm((l & 1) ? s_odd : s_even, 0u, 0x4440u | uint32_t(l >> 1));
+    m[l] = *reinterpret_cast<const uint32_t*>(signb + off);
   }
 }
 
-// 4 bytes at a static byte offset (a multiple of 2) of a word-aligned unit in shared memory.
-template <int OFF>
-__device__ __forceinline__ uint32_t ld4(const uint32_t* u) {
-  if constexpr (OFF % 4 == 0) return u[OFF / 4];
-  else return __byte_perm(u[OFF / 4], u[OFF / 4 + 1], 0x5432);
-}
-template <int OFF>
-__device__ __forceinline__ uint32_t ld1(const uint32_t* u) {
-  return (u[OFF / 4] >> (8 * (OFF % 4))) & 0xFFu;
-}
-template <int OFF>
-__device__ __forceinline__ float ld_fp16(const uint32_t* u) {
-  const uint32_t v = u[OFF / 4] >> (8 * (OFF % 4));
-  return __half2float(__ushort_as_half(static_cast<unsigned short>(v & 0xFFFFu)));
+// Signed int8x4 weights from (g, m): byte-wise negation where m = 0xFF; (g ^ 0xFF) + 1 never carries
+// because every magnitude is odd.
+__device__ __forceinline__ int iq3s_signed(uint32_t g, uint32_t m) { return int((g ^ m) + (m & 0x01010101u)); }
+
+// sum_i s_i g_i a_i over 32 weights for one token: with x = g ^ m (negated bytes become -g-1),
+// sum s g a = dp4a(x, a) - dp4a(m, a) since m's 0xFF bytes are -1.
+__device__ __forceinline__ int iq3s_dot32(const uint32_t (&g)[8], const uint32_t (&m)[8], const int8_t* a) {
+  const int4 a0 = *reinterpret_cast<const int4*>(a);
+  const int4 a1 = *reinterpret_cast<const int4*>(a + 16);
+  const int av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+  int p = 0, n = 0;
+#pragma unroll
+  for (int l = 0; l < 8; ++l) {
+    p = __dp4a(int(g[l] ^ m[l]), av[l], p);
+    n = __dp4a(int(m[l]), av[l], n);
+  }
+  return p - n;
 }
 
-// dp4a of 8 weight words with 32 int8 activations at `a` (16-byte aligned shared memory).
+// dp4a of 8 signed weight words with 32 int8 activations at `a` (16-byte aligned shared memory).
 __device__ __forceinline__ int dot32(const int (&w)[8], const int8_t* a) {
   const int4 a0 = *reinterpret_cast<const int4*>(a);
   const int4 a1 = *reinterpret_cast<const int4*>(a + 16);
@@ -99,37 +125,54 @@ __device__ __forceinline__ int dot32(const int (&w)[8], const int8_t* a) {
   return s;
 }
 
-// Sub-block IB of the IQ3_S block at static byte offset BASE of a word-aligned unit:
-// bsum[t] += (2*s+1) * sum_i w_i * a_t,i, exact in int32.
-template <int BASE, int IB, int TT>
-__device__ __forceinline__ void iq3s_sub_idot(const uint32_t* unit, uint32_t sc, const uint32_t* grid_lane,
-                                              const uint32_t* signtab, const int8_t* const (&act)[TT],
-                                              int (&bsum)[TT]) {
-  int w[8];
-  iq3s_decode32(ld4<BASE + 2 + 8 * IB>(unit), ld4<BASE + 6 + 8 * IB>(unit), ld1<BASE + 66 + IB>(unit),
-                ld4<BASE + 74 + 4 * IB>(unit), grid_lane, signtab, w);
-  const int mult = 2 * int((sc >> (4 * IB)) & 0xFu) + 1;
-#pragma unroll
-  for (int t = 0; t < TT; ++t) bsum[t] += dot32(w, act[t] + 32 * IB) * mult;
+// 4 bytes at a static byte offset (a multiple of 2) of a word-aligned unit in shared memory.
+template <int OFF>
+__device__ __forceinline__ uint32_t ld4(const uint32_t* u) {
+  if constexpr (OFF % 4 == 0) return u[OFF / 4];
+  else return __byte_perm(u[OFF / 4], u[OFF / 4 + 1], 0x5432);
+}
+template <int OFF>
+__device__ __forceinline__ float ld_fp16(const uint32_t* u) {
+  const uint32_t v = u[OFF / 4] >> (8 * (OFF % 4));
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(v & 0xFFFFu)));
 }
 
-// Integer dot of one IQ3_S block with TT activation blocks; act[t] points at the 256 int8 of the
-// matching Q8_K block. |bsum| < 2^24, so float(bsum) is exact.
-template <int BASE, int TT>
-__device__ __forceinline__ void iq3s_block_idot(const uint32_t* unit, const uint32_t* grid_lane,
+// An IQ3_S block is a 2-byte scale followed by 27 words: 16 of index bytes, 2 of ninth bits, 8 of
+// signs, 1 of sub-block scales. In a 220-byte unit (two blocks, word aligned) the first block's
+// 27 words sit 2 bytes off word alignment, the second block's are aligned: S<MIS>(w, k) reads
+// word k of the stream either way (w = the word holding the fp16 scale).
+template <bool MIS>
+__device__ __forceinline__ uint32_t iq3s_stream(const uint32_t* w, int k) {
+  if constexpr (MIS) return __byte_perm(w[k], w[k + 1], 0x5432);
+  else return w[k + 1];
+}
+
+// Integer dot of one IQ3_S block with TT activation blocks: bsum[t] = sum over its 8 sub-blocks of
+// (2*s+1) * sum_i w_i * a_t,i, exact in int32 (|bsum| < 2^24, so float(bsum) is exact).
+// act[t] points at the 256 int8 of the matching Q8_K block. Two runtime halves of four unrolled
+// sub-blocks keep the loop body inside the instruction cache.
+template <bool MIS, int TT>
+__device__ __forceinline__ void iq3s_block_idot(const uint32_t* w, const uint32_t* grid_lane,
                                                 const uint32_t* signtab, const int8_t* const (&act)[TT],
                                                 int (&bsum)[TT]) {
-  const uint32_t sc = ld4<BASE + 106>(unit);
+  const uint32_t sc = iq3s_stream<MIS>(w, 26);
 #pragma unroll
   for (int t = 0; t < TT; ++t) bsum[t] = 0;
-  iq3s_sub_idot<BASE, 0, TT>(unit, sc, grid_lane, signtab, act, bsum);
-  iq3s_sub_idot<BASE, 1, TT>(unit, sc, grid_lane, signtab, act, bsum);
-  iq3s_sub_idot<BASE, 2, TT>(unit, sc, grid_lane, signtab, act, bsum);
-  iq3s_sub_idot<BASE, 3, TT>(unit, sc, grid_lane, signtab, act, bsum);
-  iq3s_sub_idot<BASE, 4, TT>(unit, sc, grid_lane, signtab, act, bsum);
-  iq3s_sub_idot<BASE, 5, TT>(unit, sc, grid_lane, signtab, act, bsum);
-  iq3s_sub_idot<BASE, 6, TT>(unit, sc, grid_lane, signtab, act, bsum);
-  iq3s_sub_idot<BASE, 7, TT>(unit, sc, grid_lane, signtab, act, bsum);
+#pragma unroll 1
+  for (int half = 0; half < 2; ++half) {
+    const uint32_t qh = iq3s_stream<MIS>(w, 16 + half);
+    const uint32_t sch = sc >> (16 * half);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int ib = 4 * half + i;
+      uint32_t g[8], m[8];
+      iq3s_decode_sub(iq3s_stream<MIS>(w, 2 * ib), iq3s_stream<MIS>(w, 2 * ib + 1), qh, 8 * i,
+                      iq3s_stream<MIS>(w, 18 + ib), grid_lane, signtab, g, m);
+      const int mult = 2 * int((sch >> (4 * i)) & 0xFu) + 1;
+#pragma unroll
+      for (int t = 0; t < TT; ++t) bsum[t] += iq3s_dot32(g, m, act[t] + 32 * ib) * mult;
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------ IQ4_NL

@@ -24,6 +24,11 @@ constexpr int kExperts = FB_EXPERTS;
 constexpr int kMaxTok = FB_DECODE_MAX_TOKENS;
 constexpr int kMaxPairs = FB_DECODE_MAX_PAIRS;
 constexpr int kTT = 2;  // tokens of one work item handled per pass over a staged tile
+// ws.sched: [0] gate/up tile counter, [1] down tile counter, [2] finished route blocks,
+// [8..168) item order
+constexpr int kSchedOrderBase = 8;
+constexpr int kSchedRoute = 2;
+constexpr int kSchedInts = 192;
 
 __host__ __device__ constexpr int act_row_bytes_planar(int act, int k) {
   return act == FB_ACT_Q8_K ? k + 64 : k + k / 8;
@@ -66,54 +71,67 @@ __device__ __forceinline__ void quantize_row_planar(int act, int k, LoadF load, 
 }
 
 // ------------------------------------------------------------------------------ router
-// logits[t][r] = sum_k W[r][k] * x[t][k]; one warp per row, lane-strided 16-byte chunks, the 32
-// lane sums added by a butterfly. Fixed order: repeated calls are bitwise identical.
+// logits[t][r] = sum_k W[r][k] * x[t][k]; one warp per row (four rows per block), the row's
+// weights held in registers, tokens taken four at a time so that their loads overlap; the 32 lane
+// sums are added by a butterfly. Fixed order: repeated calls are bitwise identical.
 template <bool XBF16>
-__global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* __restrict__ w, int rows,
+__global__ void __launch_bounds__(128) router_kernel(const __nv_bfloat16* __restrict__ w, int rows,
                                                      const void* __restrict__ xv, int tokens,
                                                      float* __restrict__ logits, int stride) {
   pdl_launch_dependents();
-  pdl_wait_prior();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_wait_prior();
   if (row >= rows) return;
   float wr[80];
-  const uint4* wp = reinterpret_cast<const uint4*>(w + size_t(row) * H);
-#pragma unroll
-  for (int c = 0; c < 10; ++c) {
-    const uint4 v = wp[c * 32 + lane];
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      wr[8 * c + 2 * i] = __uint_as_float(u[i] << 16);
-      wr[8 * c + 2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u);
-    }
-  }
-  for (int t = 0; t < tokens; ++t) {
-    float acc = 0.0f;
+  {
+    const uint4* wp = reinterpret_cast<const uint4*>(w + size_t(row) * H);
 #pragma unroll
     for (int c = 0; c < 10; ++c) {
-      float xs[8];
-      if constexpr (XBF16) {
-        const uint4 v = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xv) + size_t(t) * H)[c * 32 + lane];
-        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+      const uint4 v = wp[c * 32 + lane];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          xs[2 * i] = __uint_as_float(u[i] << 16);
-          xs[2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u);
-        }
-      } else {
-        const float4* xp = reinterpret_cast<const float4*>(static_cast<const float*>(xv) + size_t(t) * H) + (c * 32 + lane) * 2;
-        const float4 a = xp[0], b = xp[1];
-        xs[0] = a.x; xs[1] = a.y; xs[2] = a.z; xs[3] = a.w;
-        xs[4] = b.x; xs[5] = b.y; xs[6] = b.z; xs[7] = b.w;
+      for (int i = 0; i < 4; ++i) {
+        wr[8 * c + 2 * i] = __uint_as_float(u[i] << 16);
+        wr[8 * c + 2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u);
       }
+    }
+  }
+  for (int t0 = 0; t0 < tokens; t0 += 4) {
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc = fmaf(wr[8 * c + i], xs[i], acc);
+    for (int c = 0; c < 10; ++c) {
+#pragma unroll
+      for (int tt = 0; tt < 4; ++tt) {
+        const int t = min(t0 + tt, tokens - 1);  // clamped rows are computed and dropped
+        float xs[8];
+        if constexpr (XBF16) {
+          const uint4 v =
+              reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xv) + size_t(t) * H)[c * 32 + lane];
+          const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            xs[2 * i] = __uint_as_float(u[i] << 16);
+            xs[2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u);
+          }
+        } else {
+          const float4* xp =
+              reinterpret_cast<const float4*>(static_cast<const float*>(xv) + size_t(t) * H) + (c * 32 + lane) * 2;
+          const float4 a = xp[0], b = xp[1];
+          xs[0] = a.x; xs[1] = a.y; xs[2] = a.z; xs[3] = a.w;
+          xs[4] = b.x; xs[5] = b.y; xs[6] = b.z; xs[7] = b.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[tt] = fmaf(wr[8 * c + i], xs[i], acc[tt]);
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) logits[size_t(t) * stride + row] = acc;
+    for (int tt = 0; tt < 4; ++tt) {
+      float v = acc[tt];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0 && t0 + tt < tokens) logits[size_t(t0 + tt) * stride + row] = v;
+    }
   }
 }
 
@@ -121,43 +139,52 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* __rest
 // Top-k of 512 logits by one warp (lane l holds logits l + 32 i): value descending, ties to the
 // lower id, NaN never wins, -0 == +0; weights = softmax over the winners in fp32
 // (src/kernels/moe/moe_common.cuh:33-85 of the reference states the same contract).
-__device__ __forceinline__ void warp_topk(const float* logits, int* ids, float* weights) {
+// Order-preserving map of a float to uint32 (larger float -> larger key); NaN maps below every
+// number and -0 equals +0.
+__device__ __forceinline__ uint32_t logit_key(float x) {
+  if (x != x) x = -INFINITY;
+  if (x == 0.0f) x = 0.0f;
+  const uint32_t u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+template <class LoadF>
+__device__ __forceinline__ void warp_topk(LoadF load_logit, int* ids, float* weights) {
   const int lane = threadIdx.x & 31;
-  float v[16];
+  uint32_t key[16];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    float x = logits[lane + 32 * i];
-    if (x != x) x = -INFINITY;
-    v[i] = x;
-  }
-  uint32_t taken = 0;
+  for (int i = 0; i < 16; ++i) key[i] = logit_key(load_logit(lane + 32 * i));
   float vals[kTopK];
 #pragma unroll
   for (int k = 0; k < kTopK; ++k) {
-    float bv = 0.0f;
-    int bi = 0x7fffffff;
+    // lane-local best as a 4-level tree: a higher slot wins only when strictly greater, so equal
+    // keys resolve to the lower id; the warp step is two redux operations (max key, then min id).
+    uint32_t tk[16];
+    int ti[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const bool free_ = !((taken >> i) & 1u);
-      if (free_ && (bi == 0x7fffffff || v[i] > bv)) {
-        bv = v[i];
-        bi = lane + 32 * i;
-      }
+      tk[i] = key[i];
+      ti[i] = i;
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      const bool take = bi == 0x7fffffff ? oi != 0x7fffffff
-                                         : (oi != 0x7fffffff && (ov > bv || (ov == bv && oi < bi)));
-      if (take) {
-        bv = ov;
-        bi = oi;
+    for (int w = 1; w < 16; w <<= 1) {
+#pragma unroll
+      for (int i = 0; i < 16; i += 2 * w) {
+        const bool up = tk[i + w] > tk[i];
+        tk[i] = up ? tk[i + w] : tk[i];
+        ti[i] = up ? ti[i + w] : ti[i];
       }
     }
-    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-    ids[k] = bi;
-    vals[k] = bv;
+    const uint32_t best = __reduce_max_sync(0xffffffffu, tk[0]);
+    const uint32_t cand = tk[0] == best ? uint32_t(lane + 32 * ti[0]) : 0xffffffffu;
+    const int win = int(__reduce_min_sync(0xffffffffu, cand));
+    ids[k] = win;
+    const uint32_t u = (best & 0x80000000u) ? (best & 0x7fffffffu) : ~best;
+    vals[k] = __uint_as_float(u);
+    // retire the winner: key 0 is below every real key (the smallest real key is ~0xFF800000 = 0x007FFFFF)
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (win == lane + 32 * i) key[i] = 0u;
   }
   float sum = 0.0f;
   const float top = vals[0];
@@ -171,41 +198,31 @@ __device__ __forceinline__ void warp_topk(const float* logits, int* ids, float* 
   for (int k = 0; k < kTopK; ++k) weights[k] = vals[k] * inv;
 }
 
-template <bool XBF16>
-__global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ logits, int logits_stride,
-                                                     const void* __restrict__ xv, const int32_t* __restrict__ slot_of,
-                                                     int T, fb_moe_decode_workspace ws,
-                                                     uint32_t* __restrict__ counts) {
-  pdl_launch_dependents();
-  pdl_wait_prior();
+// load_logit(t, e) returns router logit e of token t.
+template <class LoadF>
+__device__ __forceinline__ void select_block(LoadF load_logit, const int32_t* slot_of, int T,
+                                             const fb_moe_decode_workspace& ws, uint32_t* counts) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (blockIdx.x > 0) {
-    const int t = blockIdx.x - 1;
-    auto load = [&](int i) -> float {
-      if constexpr (XBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(xv)[size_t(t) * H + i]);
-      else return static_cast<const float*>(xv)[size_t(t) * H + i];
-    };
-    quantize_row_planar(act_of(ws.gate_up_format), H, load, ws.xq + size_t(t) * FB_XQ_STRIDE);
-    return;
-  }
   __shared__ int s_id[kMaxTok][kTopK];
   __shared__ float s_w[kMaxTok][kTopK];
-  __shared__ int s_slot[kMaxTok][kTopK];
   __shared__ int s_pair[kMaxTok][kTopK];
-  __shared__ int s_cnt[kExperts];
+  __shared__ uint32_t s_mask[kExperts];
   __shared__ int s_begin[kExperts];
   __shared__ int s_hot_slot[kMaxPairs];
   __shared__ int s_hot_cnt[kMaxPairs];
+  __shared__ int s_item_cnt[kMaxPairs];
   __shared__ int s_scan[2][16];
-  __shared__ int s_bad;
+  __shared__ int s_hist[5][kMaxTok + 1];
   fb_moe_decode_work* work = ws.work;
-  s_cnt[tid] = 0;
-  if (tid == 0) s_bad = 0;
+  s_mask[tid] = 0;
+  if (tid < 5 * (kMaxTok + 1)) (&s_hist[0][0])[tid] = 0;
   if (tid < kMaxPairs) ws.item_done[tid] = 0;
+  if (tid < kSchedOrderBase) ws.sched[tid] = 0;
+  const int e_slot = slot_of ? slot_of[tid] : tid;
   if (warp < T) {
     int ids[kTopK];
     float w[kTopK];
-    warp_topk(logits + size_t(warp) * logits_stride, ids, w);
+    warp_topk([&](int e) { return load_logit(warp, e); }, ids, w);
 #pragma unroll
     for (int k = 0; k < kTopK; ++k)
       if (lane == k) {
@@ -216,18 +233,17 @@ __global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ l
   __syncthreads();
   const int pt = tid / kTopK, pk = tid % kTopK;
   const bool valid = tid < T * kTopK;
-  int my_slot = -1;
+  int my_e = 0, my_slot = -1;
   if (valid) {
-    const int e = s_id[pt][pk];
-    my_slot = slot_of ? slot_of[e] : e;
-    s_slot[pt][pk] = my_slot;
-    if (my_slot >= 0) atomicAdd(&s_cnt[e], 1);
-    else s_bad = 1;
-    if (counts) atomicAdd(&counts[e], 1u);
+    my_e = s_id[pt][pk];
+    my_slot = slot_of ? slot_of[my_e] : my_e;
+    if (my_slot >= 0) atomicOr(&s_mask[my_e], 1u << pt);
+    if (counts) atomicAdd(&counts[my_e], 1u);
   }
-  __syncthreads();
-  // Compact the hot experts (expert order), then rank them by physical slot.
-  const int c = s_cnt[tid];
+  const int n_cold = __syncthreads_count(valid && my_slot < 0);
+  // Exclusive scans of (pairs, hot flag) over the 512 experts.
+  const uint32_t mask = s_mask[tid];
+  const int c = __popc(mask);
   int incl_c = c, incl_n = c > 0 ? 1 : 0;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -242,28 +258,40 @@ __global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ l
     s_scan[1][warp] = incl_n;
   }
   __syncthreads();
-  int base_n = 0, n_pairs = 0, n_items = 0;
+  int base_c = 0, base_n = 0, n_pairs = 0, n_items = 0;
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    if (i < warp) base_n += s_scan[1][i];
-    n_pairs += s_scan[0][i];
-    n_items += s_scan[1][i];
+    const int sc = s_scan[0][i], sn = s_scan[1][i];
+    if (i < warp) {
+      base_c += sc;
+      base_n += sn;
+    }
+    n_pairs += sc;
+    n_items += sn;
   }
-  const int compact = base_n + incl_n - (c > 0 ? 1 : 0);
-  const int e_slot = slot_of ? slot_of[tid] : tid;
-  if (c > 0) {
-    s_hot_slot[compact] = e_slot;
-    s_hot_cnt[compact] = c;
-  }
-  __syncthreads();
-  if (c > 0) {
-    int item = 0, pair_begin = 0;
-    for (int i = 0; i < n_items; ++i)
-      if (s_hot_slot[i] < e_slot) {
-        ++item;
-        pair_begin += s_hot_cnt[i];
+  int item = base_n + incl_n - (c > 0 ? 1 : 0);  // expert order == slot order when slot_of is null
+  int pair_begin = base_c + incl_c - c;
+  if (slot_of) {  // rank the hot experts by physical slot instead
+    if (c > 0) {
+      s_hot_slot[item] = e_slot;
+      s_hot_cnt[item] = c;
+    }
+    __syncthreads();
+    if (c > 0) {
+      int it = 0, pb = 0;
+#pragma unroll 8
+      for (int i = 0; i < n_items; ++i) {
+        const bool before = s_hot_slot[i] < e_slot;
+        it += before ? 1 : 0;
+        pb += before ? s_hot_cnt[i] : 0;
       }
+      item = it;
+      pair_begin = pb;
+    }
+  }
+  if (c > 0) {
     s_begin[tid] = pair_begin;
+    s_item_cnt[item] = c;
     work->item_slot[item] = e_slot;
     work->item_pair_begin[item] = pair_begin;
   }
@@ -271,89 +299,289 @@ __global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ l
     work->item_pair_begin[n_items] = n_pairs;
     work->n_items = n_items;
     work->n_pairs = n_pairs;
+    work->n_cold = n_cold;
     work->tokens = T;
+    if (n_cold) atomicMax(ws.status, uint32_t(FB_STATUS_BAD_WORK));
   }
   __syncthreads();
+  // Visiting order of the streaming kernels: most tokens first, ties by item index. Counting
+  // sort: rank = items with more tokens + items with as many tokens and a lower index.
+  {
+    const bool live = tid < n_items;
+    const int mine = live ? s_item_cnt[tid] : 0;
+    const unsigned peers = __match_any_sync(0xffffffffu, mine);
+    const int before_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (live && before_in_warp == 0) s_hist[warp][mine] = __popc(peers);  // one lane per (warp, count)
+    __syncthreads();
+    if (live) {
+      int rank = before_in_warp;
+      for (int wv = 0; wv < (n_items + 31) / 32; ++wv)
+        for (int cnt = mine; cnt <= kMaxTok; ++cnt)
+          if (cnt > mine || wv < warp) rank += s_hist[wv][cnt];
+      ws.sched[kSchedOrderBase + rank] = tid;
+    }
+  }
   if (valid) {
     int idx = -1;
     if (my_slot >= 0) {
-      const int e = s_id[pt][pk];
-      int rank = 0;
-      for (int t2 = 0; t2 < pt; ++t2)
-        for (int k2 = 0; k2 < kTopK; ++k2) rank += s_id[t2][k2] == e ? 1 : 0;
-      idx = s_begin[e] + rank;
+      idx = s_begin[my_e] + __popc(s_mask[my_e] & ((1u << pt) - 1u));  // tokens ascending inside an item
       work->pair_token[idx] = pt;
       work->pair_weight[idx] = s_w[pt][pk];
     }
     s_pair[pt][pk] = idx;
-    work->topk_expert[pt][pk] = s_id[pt][pk];
+    work->topk_expert[pt][pk] = my_e;
     work->topk_weight[pt][pk] = s_w[pt][pk];
   }
   __syncthreads();
   if (tid < T) {
-    int nh = 0, nc = 0;
+    int idx[kTopK];
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) idx[k] = s_pair[tid][k];
+    int nh = 0;
+#pragma unroll
     for (int k = 0; k < kTopK; ++k) {
-      const int idx = s_pair[tid][k];
-      if (idx >= 0) {
+      if (idx[k] >= 0) {
         int rank = 0;
-        for (int k2 = 0; k2 < kTopK; ++k2) rank += (s_pair[tid][k2] >= 0 && s_pair[tid][k2] < idx) ? 1 : 0;
-        work->token_pairs[tid][rank] = idx;
+#pragma unroll
+        for (int k2 = 0; k2 < kTopK; ++k2) rank += (idx[k2] >= 0 && idx[k2] < idx[k]) ? 1 : 0;
+        work->token_pairs[tid][rank] = idx[k];  // slot order == pair order
         ++nh;
-      } else {
-        ++nc;
       }
     }
     work->token_pair_count[tid] = nh;
-    work->token_cold_count[tid] = nc;
+    work->token_cold_count[tid] = kTopK - nh;
+  }
+}
+
+// Stand-alone selection (the reference's moe_select_publish): block 0 routes, blocks 1..T quantize
+// one token's activations each.
+template <bool XBF16>
+__global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ logits, int logits_stride,
+                                                     const void* __restrict__ xv, const int32_t* __restrict__ slot_of,
+                                                     int T, fb_moe_decode_workspace ws,
+                                                     uint32_t* __restrict__ counts) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  if (blockIdx.x > 0) {
+    const int t = blockIdx.x - 1;
+    auto load = [&](int i) -> float {
+      if constexpr (XBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(xv)[size_t(t) * H + i]);
+      else return static_cast<const float*>(xv)[size_t(t) * H + i];
+    };
+    quantize_row_planar(act_of(ws.gate_up_format), H, load, ws.xq + size_t(t) * FB_XQ_STRIDE);
+    return;
+  }
+  select_block([&](int t, int e) { return logits[size_t(t) * logits_stride + e]; }, slot_of, T, ws, counts);
+}
+
+// Router projection, activation quantization and selection in one launch (the head of the fused
+// layer call). Block (g, q) projects router rows 16g..16g+15 over the K slice [512q, 512q+512): the
+// x slice of all tokens sits in shared memory, one warp per row; partial sums go to `part`
+// [5][16][512]. Every block also quantizes a share of the activation blocks. The block that
+// finishes last - found with a device counter, nobody waits - adds the five slices in order,
+// stores the logits and runs the selection.
+constexpr int kRouteSplits = 5, kRouteSlice = H / kRouteSplits;  // 512
+
+template <bool XBF16>
+__global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restrict__ w, const void* __restrict__ xv,
+                                                    int T, float* __restrict__ logits, int stride,
+                                                    float* __restrict__ part, fb_moe_decode_workspace ws) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  __shared__ __align__(16) float s_x[kMaxTok][kRouteSlice];
+  __shared__ int s_last;
+  const int g = blockIdx.x / kRouteSplits, q = blockIdx.x - g * kRouteSplits;
+  for (int i = tid; i < T * (kRouteSlice / 4); i += 512) {
+    const int t = i / (kRouteSlice / 4), c = i - t * (kRouteSlice / 4);
+    float4 v;
+    if constexpr (XBF16) {
+      const uint2 u = reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(xv) + size_t(t) * H +
+                                                     q * kRouteSlice)[c];
+      v = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u), __uint_as_float(u.y << 16),
+                      __uint_as_float(u.y & 0xFFFF0000u));
+    } else {
+      v = reinterpret_cast<const float4*>(static_cast<const float*>(xv) + size_t(t) * H + q * kRouteSlice)[c];
+    }
+    reinterpret_cast<float4*>(&s_x[t][0])[c] = v;
+  }
+  const int row = g * 16 + warp;
+  float wr[16];
+  {
+    const uint2* wp = reinterpret_cast<const uint2*>(w + size_t(row) * H + q * kRouteSlice);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // lane holds elements 128c + 4 lane .. +3 of the slice
+      const uint2 u = wp[c * 32 + lane];
+      wr[4 * c + 0] = __uint_as_float(u.x << 16);
+      wr[4 * c + 1] = __uint_as_float(u.x & 0xFFFF0000u);
+      wr[4 * c + 2] = __uint_as_float(u.y << 16);
+      wr[4 * c + 3] = __uint_as_float(u.y & 0xFFFF0000u);
+    }
   }
   __syncthreads();
-  if (tid == 0) {
-    int n_cold = 0;
-    for (int t = 0; t < T; ++t)
-      for (int k = 0; k < kTopK; ++k) n_cold += s_pair[t][k] < 0 ? 1 : 0;
-    work->n_cold = n_cold;
-    if (s_bad) atomicMax(ws.status, uint32_t(FB_STATUS_BAD_WORK));
+  for (int t = 0; t < T; ++t) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float4 xv4 = reinterpret_cast<const float4*>(&s_x[t][0])[c * 32 + lane];
+      acc = fmaf(wr[4 * c + 0], xv4.x, acc);
+      acc = fmaf(wr[4 * c + 1], xv4.y, acc);
+      acc = fmaf(wr[4 * c + 2], xv4.z, acc);
+      acc = fmaf(wr[4 * c + 3], xv4.w, acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) part[(size_t(q) * kMaxTok + t) * kExperts + row] = acc;
   }
+  // activation quantization, one warp per ggml block, strided over every warp of the grid
+  {
+    const int act = act_of(ws.gate_up_format);
+    const int per_tok = act == FB_ACT_Q8_K ? H / 256 : H / 32;
+    const int n_warps = gridDim.x * 16;
+    for (int task = blockIdx.x * 16 + warp; task < T * per_tok; task += n_warps) {
+      const int t = task / per_tok, b = task - t * per_tok;
+      auto load = [&](int i) -> float {
+        if constexpr (XBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(xv)[size_t(t) * H + i]);
+        else return static_cast<const float*>(xv)[size_t(t) * H + i];
+      };
+      uint8_t* out = ws.xq + size_t(t) * FB_XQ_STRIDE;
+      float* scales = reinterpret_cast<float*>(out + H);
+      if (act == FB_ACT_Q8_K) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = load(256 * b + 8 * lane + i);
+        int qv[8], ps;
+        const float d = q8k_block_warp(v, qv, ps);
+        uint2 pk;
+        pk.x = uint32_t(uint8_t(qv[0])) | (uint32_t(uint8_t(qv[1])) << 8) | (uint32_t(uint8_t(qv[2])) << 16) |
+               (uint32_t(uint8_t(qv[3])) << 24);
+        pk.y = uint32_t(uint8_t(qv[4])) | (uint32_t(uint8_t(qv[5])) << 8) | (uint32_t(uint8_t(qv[6])) << 16) |
+               (uint32_t(uint8_t(qv[7])) << 24);
+        *reinterpret_cast<uint2*>(out + 256 * b + 8 * lane) = pk;
+        if (lane == 0) scales[b] = d;
+      } else {
+        unsigned short dh;
+        const int qv = q8_0_block_warp(load(32 * b + lane), dh);
+        out[32 * b + q8_0_interleave_index(lane)] = uint8_t(int8_t(qv));
+        if (lane == 0) scales[b] = __half2float(__ushort_as_half(dh));
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int ticket = atomicAdd(ws.sched + kSchedRoute, 1);
+    s_last = ticket == int(gridDim.x) - 1;
+    if (s_last) ws.sched[kSchedRoute] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // slices added in order 0..4 (fixed: repeated calls are bitwise identical); thread e <-> expert e
+  for (int t = 0; t < T; ++t) {
+    float v = 0.0f;
+#pragma unroll
+    for (int qq = 0; qq < kRouteSplits; ++qq) v += __ldcg(part + (size_t(qq) * kMaxTok + t) * kExperts + tid);
+    logits[size_t(t) * stride + tid] = v;
+  }
+  __syncthreads();
+  select_block([&](int t, int e) { return logits[size_t(t) * stride + e]; }, nullptr, T, ws, nullptr);
 }
 
 // ------------------------------------------------------------------------------ streaming skeleton
-struct TileInfo {
-  int item, sub, pair_begin, n_tok;
-  const uint8_t* blob;
-};
+// Tiles are handed out dynamically: the producer lane of each CTA takes the next tile index from a
+// device counter (reset by the select kernel), so a CTA that drew an expert with many tokens simply
+// takes fewer tiles. Work items are visited heaviest first (ws.sched[8..]). An expert with more
+// than kTT tokens is staged once per group of kTT tokens (its weights come back from L2). Every
+// output element is still written by exactly one thread after a fixed-order reduction: results do
+// not depend on which CTA or warp ran which piece.
+constexpr int kSchedGateUp = 0, kSchedDown = 1, kSchedOrder = kSchedOrderBase;
 
-__device__ __forceinline__ TileInfo tile_info(const fb_moe_decode_work* work, const fb_moe_expert_layout& L,
-                                              int tile, int tiles_per_item) {
-  TileInfo ti;
-  ti.item = tile / tiles_per_item;
-  ti.sub = tile - ti.item * tiles_per_item;
-  ti.pair_begin = work->item_pair_begin[ti.item];
-  ti.n_tok = work->item_pair_begin[ti.item + 1] - ti.pair_begin;
-  ti.blob = L.slots + int64_t(work->item_slot[ti.item]) * L.blob_stride;
-  return ti;
-}
+// What the producer tells the consumers about the entry staged in a ring slot (shared memory).
+struct StageMeta {
+  int tile;        // -1: no more work
+  int pair0;       // first pair (row of h / partial) of this pass
+  int ntp;         // tokens in this pass (1..kTT)
+  int row0;        // first intermediate row (gate/up) or output row (down) of the tile
+  int item;        // work item
+  int item_pair0;  // first pair of the item
+  int item_tok;    // tokens of the item
+  int pad;
+  float wgt[kTT];  // routing weights of the pass's pairs (down)
+};
 
 struct Ring {
   uint64_t* full;   // [2] count 1 + tx bytes
-  uint64_t* empty;  // [2] count = consumer warps
-  int* abort;
+  uint64_t* empty;  // [2]
+  volatile StageMeta* meta;  // [2]
+  volatile int* abort;
 };
 
-// After a wait has run out every later wait is skipped, so all warps keep the same control flow
-// (their barriers still match) and the kernel drains quickly with the status word set.
-__device__ __forceinline__ bool ring_aborted(const Ring& r) { return *reinterpret_cast<volatile int*>(r.abort) != 0; }
+// After a wait has run out every later wait is skipped and all loops end at their next check, so
+// the kernel drains quickly with the status word set; nothing ever waits without a limit.
+__device__ __forceinline__ bool ring_aborted(const Ring& r) { return *r.abort != 0; }
 __device__ __forceinline__ void ring_timeout(const Ring& r, uint32_t* status) {
   *r.abort = 1;
   atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
 }
 
-// Consumers: cooperative (rare-path) load of up to kTT activation rows of later passes.
-__device__ __forceinline__ void coop_load_act(uint8_t* dst, const uint8_t* src_rows, int row_stride, const int* toks,
-                                              int n, int bytes, int tid, int nthreads) {
-  for (int t = 0; t < n; ++t) {
-    const uint4* s = reinterpret_cast<const uint4*>(src_rows + size_t(toks[t]) * row_stride);
-    uint4* d = reinterpret_cast<uint4*>(dst + size_t(t) * bytes);
-    for (int i = tid; i < bytes / 16; i += nthreads) d[i] = __ldcg(s + i);
+__device__ __forceinline__ void ring_init(const Ring& r, int empty_count) {
+  mbar_init(&r.full[0], 1);
+  mbar_init(&r.full[1], 1);
+  mbar_init(&r.empty[0], empty_count);
+  mbar_init(&r.empty[1], empty_count);
+  r.meta[0].tile = -1;
+  r.meta[1].tile = -1;
+  *r.abort = 0;
+  mbar_fence_init();
+}
+
+// Producer loop of one CTA (one thread): draws tiles from `counter`, stages every pass of each
+// tile through issue(meta, slot), and finally posts the end marker in both slots.
+template <class IssueF>
+__device__ __forceinline__ void producer_loop(const Ring& r, const fb_moe_decode_workspace& ws, int* counter,
+                                              int n_tiles, int tiles_per_item, int rows_per_tile, IssueF issue) {
+  const fb_moe_decode_work* work = ws.work;
+  int i = 0;
+  auto slot_free = [&](int s) -> bool {
+    if (ring_aborted(r)) return false;
+    if (i >= 2 && !mbar_wait(&r.empty[s], ((i >> 1) - 1) & 1)) {
+      ring_timeout(r, ws.status);
+      return false;
+    }
+    return true;
+  };
+  int next = atomicAdd(counter, 1);  // drawn one step ahead of its use
+  while (true) {
+    const int tile = next;
+    if (tile >= n_tiles) break;
+    next = atomicAdd(counter, 1);
+    const int pos = tile / tiles_per_item;
+    const int item = ws.sched[kSchedOrder + pos];
+    const int sub = tile - pos * tiles_per_item;
+    const int pb = work->item_pair_begin[item];
+    const int ntok = work->item_pair_begin[item + 1] - pb;
+    const int slot_id = work->item_slot[item];
+    for (int tok0 = 0; tok0 < ntok; tok0 += kTT, ++i) {
+      const int s = i & 1;
+      if (!slot_free(s)) return;
+      volatile StageMeta* m = &r.meta[s];
+      m->tile = tile;
+      m->pair0 = pb + tok0;
+      m->ntp = min(kTT, ntok - tok0);
+      m->row0 = sub * rows_per_tile;
+      m->item = item;
+      m->item_pair0 = pb;
+      m->item_tok = ntok;
+      for (int t = 0; t < kTT; ++t) m->wgt[t] = tok0 + t < ntok ? work->pair_weight[pb + tok0 + t] : 0.0f;
+      issue(s, slot_id, sub, pb + tok0, min(kTT, ntok - tok0));
+    }
+  }
+  for (int e = 0; e < 2; ++e, ++i) {  // end marker in both slots: every waiting warp sees it
+    const int s = i & 1;
+    if (!slot_free(s)) return;
+    r.meta[s].tile = -1;
+    mbar_arrive(&r.full[s]);
   }
 }
 
@@ -361,22 +589,23 @@ __device__ __forceinline__ void coop_load_act(uint8_t* dst, const uint8_t* src_r
 template <int FMT>
 struct GateUp;
 
-// IQ3_S: a tile is 32 intermediate rows (32 gate + 32 up rows of 1100 bytes). Ten consumer warps:
-// warp w handles block pair w%5 (220 bytes, word aligned, odd word stride between rows -> no bank
-// conflicts) of the 32 gate (w<5) or up (w>=5) rows, one row per lane; the five partial sums of a
-// row meet in shared memory.
+// IQ3_S: a tile is 32 intermediate rows (32 gate + 32 up rows of 1100 bytes), cut into ten tasks:
+// task k is block pair k%5 (220 bytes, word aligned, odd word stride between rows -> no bank
+// conflicts) of the 32 gate (k<5) or up (k>=5) rows, one row per lane. Sixteen consumer warps (four
+// per scheduler) draw tasks from a shared-memory ticket; the five partial sums of a row meet in
+// shared memory, where the warp that finishes the tile's last task adds them in a fixed order.
 template <>
 struct GateUp<FB_FMT_IQ3_S> {
-  static constexpr int kJ = 32, kRowBytes = 1100, kWarps = 10;
+  static constexpr int kJ = 32, kRowBytes = 1100, kWarps = 16, kTasks = 10;
   static constexpr int kAct = FB_ACT_Q8_K, kActBytes = H + 64;
   static constexpr bool kGrid = true;
-  static constexpr int kPartialFloats = 2 * kWarps * kTT * 32;
+  static constexpr int kPartialFloats = 2 * kTasks * kTT * 32;
 };
 // IQ4_NL: 32 intermediate rows of 1440 bytes per matrix. Sixteen consumer warps; warp w handles
 // rows 2w, 2w+1 of gate and of up, eight lanes per row, lane q taking the 36-byte units q + 8i.
 template <>
 struct GateUp<FB_FMT_IQ4_NL> {
-  static constexpr int kJ = 32, kRowBytes = 1440, kWarps = 16;
+  static constexpr int kJ = 32, kRowBytes = 1440, kWarps = 16, kTasks = 0;
   static constexpr int kAct = FB_ACT_Q8_0, kActBytes = H + H / 8;
   static constexpr bool kGrid = false;
   static constexpr int kPartialFloats = 0;
@@ -394,14 +623,14 @@ __device__ __forceinline__ void iq3s_unit_dot(const uint32_t* unit, const uint32
     a1[t] = a0[t] + 256;
   }
   int bs[TT];
-  iq3s_block_idot<0, TT>(unit, grid_lane, signtab, a0, bs);
+  iq3s_block_idot<true, TT>(unit, grid_lane, signtab, a0, bs);
   const float d0 = ld_fp16<0>(unit);
 #pragma unroll
   for (int t = 0; t < TT; ++t) {
     const float da = reinterpret_cast<const float*>(actrow[t] + act_k)[2 * pair];
     acc[t] = fmaf(float(bs[t]), d0 * da, acc[t]);
   }
-  iq3s_block_idot<110, TT>(unit, grid_lane, signtab, a1, bs);
+  iq3s_block_idot<false, TT>(unit + 27, grid_lane, signtab, a1, bs);
   const float d1 = ld_fp16<110>(unit);
 #pragma unroll
   for (int t = 0; t < TT; ++t) {
@@ -477,6 +706,40 @@ __device__ __forceinline__ void quantize_item_h(const fb_moe_decode_workspace& w
   }
 }
 
+// Counts one finished contribution to an item's h; the last one re-quantizes that item's h for the
+// down kernel. `expected` = contributions per item.
+__device__ __forceinline__ void item_contribution_done(const fb_moe_decode_workspace& ws, int item, int pair_begin,
+                                                       int n_tok, int expected, int down_act, int lane) {
+  __threadfence();
+  __syncwarp();
+  int ticket = 0;
+  if (lane == 0) ticket = atomicAdd(&ws.item_done[item], 1);
+  ticket = __shfl_sync(0xffffffffu, ticket, 0);
+  if (ticket == expected - 1) {
+    __threadfence();
+    quantize_item_h(ws, pair_begin, n_tok, down_act);
+  }
+}
+
+// Consumer side of the task scheme: draws the next (entry, task) ticket; returns false at the end.
+// seq = entry number of this CTA, s = its ring slot.
+template <int TASKS>
+__device__ __forceinline__ bool draw_task(const Ring& r, int* ticket_ctr, uint32_t* status, int lane, int& s,
+                                          int& task) {
+  int ticket = 0;
+  if (lane == 0) ticket = atomicAdd(ticket_ctr, 1);
+  ticket = __shfl_sync(0xffffffffu, ticket, 0);
+  const int seq = ticket / TASKS;
+  task = ticket - seq * TASKS;
+  s = seq & 1;
+  if (ring_aborted(r)) return false;
+  if (!mbar_wait(&r.full[s], (seq >> 1) & 1)) {
+    ring_timeout(r, status);
+    return false;
+  }
+  return r.meta[s].tile >= 0;
+}
+
 // ------------------------------------------------------------------------------ gate/up kernel
 template <int FMT>
 __global__ void __launch_bounds__((GateUp<FMT>::kWarps + 1) * 32, 1)
@@ -495,18 +758,17 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   float* partials = reinterpret_cast<float*>(p);
   p += C::kPartialFloats * 4 + 16;
   uint64_t* bars = reinterpret_cast<uint64_t*>(p);
-  __shared__ int s_abort;
-  Ring ring{bars, bars + 2, &s_abort};
+  __shared__ StageMeta s_meta[2];
+  __shared__ int s_misc[4];  // [0] abort, [1] task ticket, [2..3] finished tasks per slot
+  Ring ring{bars, bars + 2, s_meta, s_misc};
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (C::kGrid) iq3s_tables_fill(gridrep, signtab);
   if (tid == 0) {
-    mbar_init(&ring.full[0], 1);
-    mbar_init(&ring.full[1], 1);
-    mbar_init(&ring.empty[0], kW);
-    mbar_init(&ring.empty[1], kW);
-    s_abort = 0;
-    mbar_fence_init();
+    ring_init(ring, FMT == FB_FMT_IQ3_S ? 1 : kW);
+    s_misc[1] = 0;
+    s_misc[2] = 0;
+    s_misc[3] = 0;
   }
   __syncthreads();
   pdl_launch_dependents();
@@ -517,144 +779,127 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   const int I = L.inter;
   const int tpi = I / C::kJ;
   const int n_tiles = n_items * tpi;
-  const int t_begin = int(int64_t(n_tiles) * blockIdx.x / gridDim.x);
-  const int t_end = int(int64_t(n_tiles) * (blockIdx.x + 1) / gridDim.x);
   const int down_act = act_of(L.down_format);
 
   if (warp == kW) {
-    // ---------------- producer: one lane issues the bulk copies of each tile into the ring.
+    // ---------------- producer: one lane draws tiles and issues their bulk copies into the ring.
     if (lane == 0) {
-      for (int tile = t_begin, i = 0; tile < t_end; ++tile, ++i) {
-        const int s = i & 1;
-        if (ring_aborted(ring)) break;
-        if (i >= 2 && !mbar_wait(&ring.empty[s], ((i >> 1) - 1) & 1)) {
-          ring_timeout(ring, ws.status);
-          break;
-        }
-        const TileInfo ti = tile_info(work, L, tile, tpi);
-        const int nact = min(ti.n_tok, kTT);
-        uint8_t* st = stage0 + s * kStage;
-        mbar_expect_tx(&ring.full[s], uint32_t(kStageW + nact * C::kActBytes));
-        const size_t off = size_t(ti.sub) * kPart;
-        bulk_g2s(st, ti.blob + L.gate_offset + off, kPart, &ring.full[s]);
-        bulk_g2s(st + kPart, ti.blob + L.up_offset + off, kPart, &ring.full[s]);
-        for (int t = 0; t < nact; ++t)
-          bulk_g2s(st + kStageW + t * C::kActBytes,
-                   ws.xq + size_t(work->pair_token[ti.pair_begin + t]) * FB_XQ_STRIDE, C::kActBytes, &ring.full[s]);
-      }
+      producer_loop(ring, ws, ws.sched + kSchedGateUp, n_tiles, tpi, C::kJ,
+                    [&](int s, int slot_id, int sub, int pair0, int ntp) {
+                      const uint8_t* blob = L.slots + int64_t(slot_id) * L.blob_stride;
+                      uint8_t* st = stage0 + s * kStage;
+                      mbar_expect_tx(&ring.full[s], uint32_t(kStageW + ntp * C::kActBytes));
+                      const size_t off = size_t(sub) * kPart;
+                      bulk_g2s(st, blob + L.gate_offset + off, kPart, &ring.full[s]);
+                      bulk_g2s(st + kPart, blob + L.up_offset + off, kPart, &ring.full[s]);
+                      for (int t = 0; t < ntp; ++t)
+                        bulk_g2s(st + kStageW + t * C::kActBytes,
+                                 ws.xq + size_t(work->pair_token[pair0 + t]) * FB_XQ_STRIDE, C::kActBytes,
+                                 &ring.full[s]);
+                    });
     }
     return;
   }
 
   // ---------------- consumers
-  const uint32_t* grid_lane = gridrep + lane;
-  const Iq4nlLevels lv = iq4nl_levels();
-  int pbuf = 0;
-  for (int tile = t_begin, i = 0; tile < t_end; ++tile, ++i) {
-    const int s = i & 1;
-    if (!ring_aborted(ring) && !mbar_wait(&ring.full[s], (i >> 1) & 1)) ring_timeout(ring, ws.status);
-    const TileInfo ti = tile_info(work, L, tile, tpi);
-    uint8_t* st = stage0 + s * kStage;
-    const uint8_t* actbase = st + kStageW;
-    const int j0 = ti.sub * C::kJ;
-    for (int tok0 = 0; tok0 < ti.n_tok; tok0 += kTT) {
-      const int ntp = min(kTT, ti.n_tok - tok0);
-      if (tok0 > 0) {  // rare: more tokens on this expert than one pass holds
-        named_bar_sync(1, kW * 32);
-        int toks[kTT];
-        for (int t = 0; t < ntp; ++t) toks[t] = work->pair_token[ti.pair_begin + tok0 + t];
-        coop_load_act(st + kStageW, ws.xq, FB_XQ_STRIDE, toks, ntp, C::kActBytes, tid, kW * 32);
-        named_bar_sync(1, kW * 32);
-      }
-      if constexpr (FMT == FB_FMT_IQ3_S) {
-        const int mat = warp / 5, pair = warp - 5 * mat;
-        const uint32_t* unit = reinterpret_cast<const uint32_t*>(st + mat * kPart + lane * C::kRowBytes + pair * 220);
-        float* part = partials + pbuf * (kW * kTT * 32);
-        if (ntp == 1) {
-          const uint8_t* ar[1] = {actbase};
-          float acc[1] = {0.0f};
-          iq3s_unit_dot<1>(unit, grid_lane, signtab, ar, pair, H, acc);
-          part[(warp * kTT + 0) * 32 + lane] = acc[0];
-        } else {
-          const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
-          float acc[2] = {0.0f, 0.0f};
-          iq3s_unit_dot<2>(unit, grid_lane, signtab, ar, pair, H, acc);
-          part[(warp * kTT + 0) * 32 + lane] = acc[0];
-          part[(warp * kTT + 1) * 32 + lane] = acc[1];
-        }
-        named_bar_sync(1, kW * 32);
-        if (warp == 0) {
-          for (int t = 0; t < ntp; ++t) {
-            float g = 0.0f, u = 0.0f;
-#pragma unroll
-            for (int q = 0; q < 5; ++q) {
-              g += part[(q * kTT + t) * 32 + lane];
-              u += part[((5 + q) * kTT + t) * 32 + lane];
-            }
-            ws.h[size_t(ti.pair_begin + tok0 + t) * I + j0 + lane] = silu_mul(g, u);
-          }
-        }
-        pbuf ^= 1;
+  if constexpr (FMT == FB_FMT_IQ3_S) {
+    const uint32_t* grid_lane = gridrep + lane;
+    while (true) {
+      int s, task;
+      if (!draw_task<C::kTasks>(ring, &s_misc[1], ws.status, lane, s, task)) break;
+      const int ntp = ring.meta[s].ntp;
+      uint8_t* st = stage0 + s * kStage;
+      const uint8_t* actbase = st + kStageW;
+      const int mat = task / 5, pair = task - 5 * mat;
+      const uint32_t* unit = reinterpret_cast<const uint32_t*>(st + mat * kPart + lane * C::kRowBytes + pair * 220);
+      float* part = partials + s * (C::kTasks * kTT * 32);
+      if (ntp == 1) {
+        const uint8_t* ar[1] = {actbase};
+        float acc[1] = {0.0f};
+        iq3s_unit_dot<1>(unit, grid_lane, signtab, ar, pair, H, acc);
+        part[(task * kTT + 0) * 32 + lane] = acc[0];
       } else {
-        // lanes 0-7 gate row 2w, 8-15 gate 2w+1, 16-23 up 2w, 24-31 up 2w+1
-        const int q = lane & 7, r = (lane >> 3) & 1, mat = lane >> 4;
-        const uint8_t* row = st + mat * kPart + (2 * warp + r) * C::kRowBytes;
-        float acc[kTT] = {0.0f, 0.0f};
-        if (ntp == 1) {
-          const uint8_t* ar[1] = {actbase};
-          float a1[1] = {0.0f};
+        const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
+        float acc[2] = {0.0f, 0.0f};
+        iq3s_unit_dot<2>(unit, grid_lane, signtab, ar, pair, H, acc);
+        part[(task * kTT + 0) * 32 + lane] = acc[0];
+        part[(task * kTT + 1) * 32 + lane] = acc[1];
+      }
+      // The warp that finishes the entry's last task adds the ten partial rows (fixed order),
+      // applies SwiGLU and hands the slot back to the producer.
+      __threadfence_block();
+      __syncwarp();
+      int done = 0;
+      if (lane == 0) done = atomicAdd(&s_misc[2 + s], 1);
+      done = __shfl_sync(0xffffffffu, done, 0);
+      if (done == C::kTasks - 1) {
+        __threadfence_block();
+        const int pair0 = ring.meta[s].pair0, j0 = ring.meta[s].row0;
+        const int item = ring.meta[s].item, ipb = ring.meta[s].item_pair0, itok = ring.meta[s].item_tok;
+        for (int t = 0; t < ntp; ++t) {
+          float g = 0.0f, u = 0.0f;
 #pragma unroll
-          for (int it = 0; it < 5; ++it) {
-            const int u = q + 8 * it;
-            iq4nl_unit_dot<1>(reinterpret_cast<const uint32_t*>(row + 36 * u), lv, ar, 2 * u, H, a1);
+          for (int q = 0; q < 5; ++q) {
+            g += part[(q * kTT + t) * 32 + lane];
+            u += part[((5 + q) * kTT + t) * 32 + lane];
           }
-          acc[0] = a1[0];
-        } else {
-          const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
-#pragma unroll
-          for (int it = 0; it < 5; ++it) {
-            const int u = q + 8 * it;
-            iq4nl_unit_dot<2>(reinterpret_cast<const uint32_t*>(row + 36 * u), lv, ar, 2 * u, H, acc);
-          }
+          ws.h[size_t(pair0 + t) * I + j0 + lane] = silu_mul(g, u);
         }
-#pragma unroll
-        for (int t = 0; t < kTT; ++t) {
-          float v = acc[t];
-          v += __shfl_xor_sync(0xffffffffu, v, 1);
-          v += __shfl_xor_sync(0xffffffffu, v, 2);
-          v += __shfl_xor_sync(0xffffffffu, v, 4);
-          const float up = __shfl_down_sync(0xffffffffu, v, 16);
-          if (t < ntp && q == 0 && mat == 0)
-            ws.h[size_t(ti.pair_begin + tok0 + t) * I + j0 + 2 * warp + r] = silu_mul(v, up);
+        __syncwarp();
+        if (lane == 0) {
+          s_misc[2 + s] = 0;
+          mbar_arrive(&ring.empty[s]);
         }
+        item_contribution_done(ws, item, ipb, itok, tpi * ((itok + kTT - 1) / kTT), down_act, lane);
       }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&ring.empty[s]);
-    // The CTA that finishes an item's last tile re-quantizes that item's h for the down kernel.
-    if constexpr (FMT == FB_FMT_IQ3_S) {
-      if (warp == 0) {
-        __threadfence();
-        __syncwarp();
-        int ticket = 0;
-        if (lane == 0) ticket = atomicAdd(&ws.item_done[ti.item], 1);
-        ticket = __shfl_sync(0xffffffffu, ticket, 0);
-        if (ticket == tpi - 1) {
-          __threadfence();
-          quantize_item_h(ws, ti.pair_begin, ti.n_tok, down_act);
+  } else {
+    const Iq4nlLevels lv = iq4nl_levels();
+    for (int i = 0;; ++i) {
+      const int s = i & 1;
+      if (ring_aborted(ring)) break;
+      if (!mbar_wait(&ring.full[s], (i >> 1) & 1)) {
+        ring_timeout(ring, ws.status);
+        break;
+      }
+      if (ring.meta[s].tile < 0) break;
+      const int ntp = ring.meta[s].ntp, pair0 = ring.meta[s].pair0, j0 = ring.meta[s].row0;
+      const int item = ring.meta[s].item, ipb = ring.meta[s].item_pair0, itok = ring.meta[s].item_tok;
+      uint8_t* st = stage0 + s * kStage;
+      const uint8_t* actbase = st + kStageW;
+      // lanes 0-7 gate row 2w, 8-15 gate 2w+1, 16-23 up 2w, 24-31 up 2w+1
+      const int q = lane & 7, r = (lane >> 3) & 1, mat = lane >> 4;
+      const uint8_t* row = st + mat * kPart + (2 * warp + r) * C::kRowBytes;
+      float acc[kTT] = {0.0f, 0.0f};
+      if (ntp == 1) {
+        const uint8_t* ar[1] = {actbase};
+        float a1[1] = {0.0f};
+#pragma unroll
+        for (int it = 0; it < 5; ++it) {
+          const int u = q + 8 * it;
+          iq4nl_unit_dot<1>(reinterpret_cast<const uint32_t*>(row + 36 * u), lv, ar, 2 * u, H, a1);
+        }
+        acc[0] = a1[0];
+      } else {
+        const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
+#pragma unroll
+        for (int it = 0; it < 5; ++it) {
+          const int u = q + 8 * it;
+          iq4nl_unit_dot<2>(reinterpret_cast<const uint32_t*>(row + 36 * u), lv, ar, 2 * u, H, acc);
         }
       }
-    } else {
-      // every warp stored part of h: count warps instead of tiles
-      __threadfence();
-      __syncwarp();
-      int ticket = 0;
-      if (lane == 0) ticket = atomicAdd(&ws.item_done[ti.item], 1);
-      ticket = __shfl_sync(0xffffffffu, ticket, 0);
-      if (ticket == tpi * kW - 1) {
-        __threadfence();
-        quantize_item_h(ws, ti.pair_begin, ti.n_tok, down_act);
+#pragma unroll
+      for (int t = 0; t < kTT; ++t) {
+        float v = acc[t];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        const float up = __shfl_down_sync(0xffffffffu, v, 16);
+        if (t < ntp && q == 0 && mat == 0) ws.h[size_t(pair0 + t) * I + j0 + 2 * warp + r] = silu_mul(v, up);
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ring.empty[s]);
+      item_contribution_done(ws, item, ipb, itok, tpi * kW * ((itok + kTT - 1) / kTT), down_act, lane);
     }
   }
 }
@@ -662,23 +907,27 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
 // ------------------------------------------------------------------------------ down kernel
 template <int FMT, int INTER>
 struct Down;
-// IQ3_S, inter 512: a row is one 220-byte block pair; tile = 320 rows, one row per lane.
+// IQ3_S, inter 512: a row is one 220-byte block pair; tile = 320 rows = ten tasks of 32 rows, one
+// row per lane, drawn by sixteen consumer warps.
 template <>
 struct Down<FB_FMT_IQ3_S, 512> {
-  static constexpr int kRows = 320, kRowBytes = 220, kWarps = 10, kAct = FB_ACT_Q8_K, kActBytes = 512 + 64;
+  static constexpr int kRows = 320, kRowBytes = 220, kWarps = 16, kTasks = 10, kAct = FB_ACT_Q8_K,
+                       kActBytes = 512 + 64;
   static constexpr bool kGrid = true;
 };
 // IQ4_NL, inter 512: a row is eight 36-byte units, eight lanes per row, four rows per warp step.
 template <>
 struct Down<FB_FMT_IQ4_NL, 512> {
-  static constexpr int kRows = 320, kRowBytes = 288, kWarps = 16, kAct = FB_ACT_Q8_0, kActBytes = 512 + 64;
+  static constexpr int kRows = 320, kRowBytes = 288, kWarps = 16, kTasks = 0, kAct = FB_ACT_Q8_0,
+                       kActBytes = 512 + 64;
   static constexpr bool kGrid = false;
   static constexpr int kLanesPerRow = 8, kUnitsPerLane = 1, kUnitA = 1, kUnitB = 0;
 };
 // IQ4_NL, inter 640: a row is ten units, two lanes per row with five consecutive units each.
 template <>
 struct Down<FB_FMT_IQ4_NL, 640> {
-  static constexpr int kRows = 256, kRowBytes = 360, kWarps = 16, kAct = FB_ACT_Q8_0, kActBytes = 640 + 80;
+  static constexpr int kRows = 256, kRowBytes = 360, kWarps = 16, kTasks = 0, kAct = FB_ACT_Q8_0,
+                       kActBytes = 640 + 80;
   static constexpr bool kGrid = false;
   static constexpr int kLanesPerRow = 2, kUnitsPerLane = 5, kUnitA = 5, kUnitB = 1;
 };
@@ -698,18 +947,17 @@ down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   uint8_t* stage0 = p;
   p += 2 * kStage;
   uint64_t* bars = reinterpret_cast<uint64_t*>(p);
-  __shared__ int s_abort;
-  Ring ring{bars, bars + 2, &s_abort};
+  __shared__ StageMeta s_meta[2];
+  __shared__ int s_misc[4];
+  Ring ring{bars, bars + 2, s_meta, s_misc};
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (C::kGrid) iq3s_tables_fill(gridrep, signtab);
   if (tid == 0) {
-    mbar_init(&ring.full[0], 1);
-    mbar_init(&ring.full[1], 1);
-    mbar_init(&ring.empty[0], kW);
-    mbar_init(&ring.empty[1], kW);
-    s_abort = 0;
-    mbar_fence_init();
+    ring_init(ring, FMT == FB_FMT_IQ3_S ? 1 : kW);
+    s_misc[1] = 0;
+    s_misc[2] = 0;
+    s_misc[3] = 0;
   }
   __syncthreads();
   pdl_launch_dependents();
@@ -719,103 +967,103 @@ down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   const int n_items = min(max(work->n_items, 0), kMaxPairs);
   constexpr int tpi = H / C::kRows;
   const int n_tiles = n_items * tpi;
-  const int t_begin = int(int64_t(n_tiles) * blockIdx.x / gridDim.x);
-  const int t_end = int(int64_t(n_tiles) * (blockIdx.x + 1) / gridDim.x);
 
   if (warp == kW) {
     if (lane == 0) {
-      for (int tile = t_begin, i = 0; tile < t_end; ++tile, ++i) {
-        const int s = i & 1;
-        if (ring_aborted(ring)) break;
-        if (i >= 2 && !mbar_wait(&ring.empty[s], ((i >> 1) - 1) & 1)) {
-          ring_timeout(ring, ws.status);
-          break;
-        }
-        const TileInfo ti = tile_info(work, L, tile, tpi);
-        const int nact = min(ti.n_tok, kTT);
-        uint8_t* st = stage0 + s * kStage;
-        mbar_expect_tx(&ring.full[s], uint32_t(kStageW + nact * C::kActBytes));
-        bulk_g2s(st, ti.blob + L.down_offset + size_t(ti.sub) * kStageW, kStageW, &ring.full[s]);
-        for (int t = 0; t < nact; ++t)
-          bulk_g2s(st + kStageW + t * C::kActBytes, ws.hq + size_t(ti.pair_begin + t) * FB_HQ_STRIDE, C::kActBytes,
-                   &ring.full[s]);
-      }
+      producer_loop(ring, ws, ws.sched + kSchedDown, n_tiles, tpi, C::kRows,
+                    [&](int s, int slot_id, int sub, int pair0, int ntp) {
+                      const uint8_t* blob = L.slots + int64_t(slot_id) * L.blob_stride;
+                      uint8_t* st = stage0 + s * kStage;
+                      mbar_expect_tx(&ring.full[s], uint32_t(kStageW + ntp * C::kActBytes));
+                      bulk_g2s(st, blob + L.down_offset + size_t(sub) * kStageW, kStageW, &ring.full[s]);
+                      for (int t = 0; t < ntp; ++t)
+                        bulk_g2s(st + kStageW + t * C::kActBytes, ws.hq + size_t(pair0 + t) * FB_HQ_STRIDE,
+                                 C::kActBytes, &ring.full[s]);
+                    });
     }
     return;
   }
 
-  const uint32_t* grid_lane = gridrep + lane;
-  const Iq4nlLevels lv = iq4nl_levels();
-  for (int tile = t_begin, i = 0; tile < t_end; ++tile, ++i) {
-    const int s = i & 1;
-    if (!ring_aborted(ring) && !mbar_wait(&ring.full[s], (i >> 1) & 1)) ring_timeout(ring, ws.status);
-    const TileInfo ti = tile_info(work, L, tile, tpi);
-    uint8_t* st = stage0 + s * kStage;
-    const uint8_t* actbase = st + kStageW;
-    const int r0 = ti.sub * C::kRows;
-    for (int tok0 = 0; tok0 < ti.n_tok; tok0 += kTT) {
-      const int ntp = min(kTT, ti.n_tok - tok0);
-      if (tok0 > 0) {
-        named_bar_sync(1, kW * 32);
-        int toks[kTT];
-        for (int t = 0; t < ntp; ++t) toks[t] = ti.pair_begin + tok0 + t;
-        coop_load_act(st + kStageW, ws.hq, FB_HQ_STRIDE, toks, ntp, C::kActBytes, tid, kW * 32);
-        named_bar_sync(1, kW * 32);
-      }
-      float wgt[kTT];
-#pragma unroll
-      for (int t = 0; t < kTT; ++t) wgt[t] = t < ntp ? work->pair_weight[ti.pair_begin + tok0 + t] : 0.0f;
-      if constexpr (FMT == FB_FMT_IQ3_S) {
-        const int row = 32 * warp + lane;
-        const uint32_t* unit = reinterpret_cast<const uint32_t*>(st + row * C::kRowBytes);
-        if (ntp == 1) {
-          const uint8_t* ar[1] = {actbase};
-          float acc[1] = {0.0f};
-          iq3s_unit_dot<1>(unit, grid_lane, signtab, ar, 0, INTER, acc);
-          ws.partial[size_t(ti.pair_begin + tok0) * H + r0 + row] = wgt[0] * acc[0];
-        } else {
-          const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
-          float acc[2] = {0.0f, 0.0f};
-          iq3s_unit_dot<2>(unit, grid_lane, signtab, ar, 0, INTER, acc);
-          ws.partial[size_t(ti.pair_begin + tok0) * H + r0 + row] = wgt[0] * acc[0];
-          ws.partial[size_t(ti.pair_begin + tok0 + 1) * H + r0 + row] = wgt[1] * acc[1];
-        }
+  if constexpr (FMT == FB_FMT_IQ3_S) {
+    const uint32_t* grid_lane = gridrep + lane;
+    while (true) {
+      int s, task;
+      if (!draw_task<C::kTasks>(ring, &s_misc[1], ws.status, lane, s, task)) break;
+      const int ntp = ring.meta[s].ntp, pair0 = ring.meta[s].pair0, r0 = ring.meta[s].row0;
+      const float w0 = ring.meta[s].wgt[0], w1 = ring.meta[s].wgt[1];
+      uint8_t* st = stage0 + s * kStage;
+      const uint8_t* actbase = st + kStageW;
+      const int row = 32 * task + lane;
+      const uint32_t* unit = reinterpret_cast<const uint32_t*>(st + row * C::kRowBytes);
+      if (ntp == 1) {
+        const uint8_t* ar[1] = {actbase};
+        float acc[1] = {0.0f};
+        iq3s_unit_dot<1>(unit, grid_lane, signtab, ar, 0, INTER, acc);
+        ws.partial[size_t(pair0) * H + r0 + row] = w0 * acc[0];
       } else {
-        constexpr int LPR = C::kLanesPerRow, RPS = 32 / LPR;
-        const int q = lane % LPR, r = lane / LPR;
-        for (int step = warp; step < C::kRows / RPS; step += kW) {
-          const int row = step * RPS + r;
-          const uint8_t* rowp = st + row * C::kRowBytes;
-          float acc[kTT] = {0.0f, 0.0f};
-          if (ntp == 1) {
-            const uint8_t* ar[1] = {actbase};
-            float a1[1] = {0.0f};
-#pragma unroll
-            for (int it = 0; it < C::kUnitsPerLane; ++it) {
-              const int u = q * C::kUnitA + it * C::kUnitB;
-              iq4nl_unit_dot<1>(reinterpret_cast<const uint32_t*>(rowp + 36 * u), lv, ar, 2 * u, INTER, a1);
-            }
-            acc[0] = a1[0];
-          } else {
-            const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
-#pragma unroll
-            for (int it = 0; it < C::kUnitsPerLane; ++it) {
-              const int u = q * C::kUnitA + it * C::kUnitB;
-              iq4nl_unit_dot<2>(reinterpret_cast<const uint32_t*>(rowp + 36 * u), lv, ar, 2 * u, INTER, acc);
-            }
-          }
-#pragma unroll
-          for (int t = 0; t < kTT; ++t) {
-            float v = acc[t];
-#pragma unroll
-            for (int o = 1; o < LPR; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (t < ntp && q == 0) ws.partial[size_t(ti.pair_begin + tok0 + t) * H + r0 + row] = wgt[t] * v;
-          }
+        const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
+        float acc[2] = {0.0f, 0.0f};
+        iq3s_unit_dot<2>(unit, grid_lane, signtab, ar, 0, INTER, acc);
+        ws.partial[size_t(pair0) * H + r0 + row] = w0 * acc[0];
+        ws.partial[size_t(pair0 + 1) * H + r0 + row] = w1 * acc[1];
+      }
+      __syncwarp();
+      if (lane == 0) {
+        const int done = atomicAdd(&s_misc[2 + s], 1);
+        if (done == C::kTasks - 1) {  // the tile's last task hands the slot back to the producer
+          s_misc[2 + s] = 0;
+          mbar_arrive(&ring.empty[s]);
         }
       }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&ring.empty[s]);
+  } else {
+    const Iq4nlLevels lv = iq4nl_levels();
+    for (int i = 0;; ++i) {
+      const int s = i & 1;
+      if (ring_aborted(ring)) break;
+      if (!mbar_wait(&ring.full[s], (i >> 1) & 1)) {
+        ring_timeout(ring, ws.status);
+        break;
+      }
+      if (ring.meta[s].tile < 0) break;
+      const int ntp = ring.meta[s].ntp, pair0 = ring.meta[s].pair0, r0 = ring.meta[s].row0;
+      const float wgt[kTT] = {ring.meta[s].wgt[0], ring.meta[s].wgt[1]};
+      uint8_t* st = stage0 + s * kStage;
+      const uint8_t* actbase = st + kStageW;
+      constexpr int LPR = C::kLanesPerRow, RPS = 32 / LPR;
+      const int q = lane % LPR, r = lane / LPR;
+      for (int step = warp; step < C::kRows / RPS; step += kW) {
+        const int row = step * RPS + r;
+        const uint8_t* rowp = st + row * C::kRowBytes;
+        float acc[kTT] = {0.0f, 0.0f};
+        if (ntp == 1) {
+          const uint8_t* ar[1] = {actbase};
+          float a1[1] = {0.0f};
+#pragma unroll
+          for (int it = 0; it < C::kUnitsPerLane; ++it) {
+            const int u = q * C::kUnitA + it * C::kUnitB;
+            iq4nl_unit_dot<1>(reinterpret_cast<const uint32_t*>(rowp + 36 * u), lv, ar, 2 * u, INTER, a1);
+          }
+          acc[0] = a1[0];
+        } else {
+          const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
+#pragma unroll
+          for (int it = 0; it < C::kUnitsPerLane; ++it) {
+            const int u = q * C::kUnitA + it * C::kUnitB;
+            iq4nl_unit_dot<2>(reinterpret_cast<const uint32_t*>(rowp + 36 * u), lv, ar, 2 * u, INTER, acc);
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < kTT; ++t) {
+          float v = acc[t];
+#pragma unroll
+          for (int o = 1; o < LPR; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+          if (t < ntp && q == 0) ws.partial[size_t(pair0 + t) * H + r0 + row] = wgt[t] * v;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ring.empty[s]);
+    }
   }
 }
 
@@ -897,7 +1145,7 @@ bool layout_ok(const fb_moe_expert_layout* L) {
 }
 
 bool ws_ok(const fb_moe_decode_workspace* ws) {
-  return ws && ws->work && ws->xq && ws->h && ws->hq && ws->partial && ws->item_done && ws->status;
+  return ws && ws->work && ws->xq && ws->h && ws->hq && ws->partial && ws->item_done && ws->sched && ws->status;
 }
 
 }  // namespace
@@ -911,7 +1159,8 @@ size_t fb_moe_decode_workspace_bytes(int32_t inter) {
   (void)inter;
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
   return up(sizeof(fb_moe_decode_work)) + up(size_t(kMaxTok) * FB_XQ_STRIDE) + up(size_t(kMaxPairs) * 640 * 4) +
-         up(size_t(kMaxPairs) * FB_HQ_STRIDE) + up(size_t(kMaxPairs) * H * 4) + up(kMaxPairs * 4) + 256;
+         up(size_t(kMaxPairs) * FB_HQ_STRIDE) + up(size_t(kMaxPairs) * H * 4) + up(kMaxPairs * 4) +
+         up(kSchedInts * 4) + 256;
 }
 
 int32_t fb_moe_decode_workspace_make(void* base, const fb_moe_expert_layout* layout, fb_moe_decode_workspace* out) {
@@ -931,6 +1180,8 @@ int32_t fb_moe_decode_workspace_make(void* base, const fb_moe_expert_layout* lay
   p += up(size_t(kMaxPairs) * H * 4);
   out->item_done = reinterpret_cast<int32_t*>(p);
   p += up(kMaxPairs * 4);
+  out->sched = reinterpret_cast<int32_t*>(p);
+  p += up(kSchedInts * 4);
   out->status = reinterpret_cast<uint32_t*>(p);
   out->gate_up_format = layout->gate_up_format;
   out->down_format = layout->down_format;
@@ -943,7 +1194,7 @@ int32_t fb_router_logits(const void* w_bf16, int32_t rows, const void* x, int32_
                          float* logits, int32_t logits_stride, void* stream) {
   if (!w_bf16 || !x || !logits || rows <= 0 || tokens <= 0 || logits_stride < rows)
     return invalid("router_logits: bad arguments");
-  const dim3 grid((rows + 7) / 8), block(256);
+  const dim3 grid((rows + 3) / 4), block(128);
   cudaError_t e = x_dtype == FB_DT_BF16
                       ? launch_pdl(router_kernel<true>, grid, block, 0, as_stream(stream),
                                    static_cast<const __nv_bfloat16*>(w_bf16), rows, x, tokens, logits, logits_stride)
@@ -995,11 +1246,7 @@ int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, c
   return 0;
 }
 
-int32_t fb_moe_hot_down(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
-                        void* stream) {
-  if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_down: bad arguments");
-  if (layout->inter != ws->inter || layout->down_format != ws->down_format)
-    return invalid("hot_down: workspace was made for a different layout");
+static int32_t launch_down(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, void* stream) {
   static bool once = [] {
     opt_in_smem(down_kernel<FB_FMT_IQ3_S, 512>, down_smem<FB_FMT_IQ3_S, 512>());
     opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 512>, down_smem<FB_FMT_IQ4_NL, 512>());
@@ -1022,6 +1269,14 @@ int32_t fb_moe_hot_down(const fb_moe_expert_layout* layout, int32_t tokens, cons
   return 0;
 }
 
+int32_t fb_moe_hot_down(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
+                        void* stream) {
+  if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_down: bad arguments");
+  if (layout->inter != ws->inter || layout->down_format != ws->down_format)
+    return invalid("hot_down: workspace was made for a different layout");
+  return launch_down(layout, ws, stream);
+}
+
 int32_t fb_moe_combine(const fb_moe_decode_workspace* ws, const float* y_shared, void* exchange, int32_t layer,
                        const uint32_t* seq, const float* inj, float* X, float* y_out, int32_t tokens,
                        long long timeout_cycles, const float* ablate_direction, float ablate_scale, void* stream) {
@@ -1040,15 +1295,28 @@ int32_t fb_moe_combine(const fb_moe_decode_workspace* ws, const float* y_shared,
 int32_t fb_moe_layer_decode(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x,
                             int32_t x_dtype, int32_t tokens, const fb_moe_decode_workspace* ws, float* logits_scratch,
                             float* y_out, void* stream) {
-  if (!logits_scratch) return invalid("layer_decode: logits scratch [tokens][513] is required");
-  int32_t st = fb_router_logits(router_w_bf16, kExperts, x, x_dtype, tokens, logits_scratch, FB_ROUTER_ROWS, stream);
+  // Four launches: route (router projection + activation quantization + selection), gate/up, down,
+  // combine. Same arithmetic, in the same order, as the five separate entry points.
+  if (!router_w_bf16 || !x || !y_out || !logits_scratch || !layout_ok(layout) || !ws_ok(ws) || tokens < 1 ||
+      tokens > kMaxTok)
+    return invalid("layer_decode: bad arguments (tokens must be 1..16, logits scratch [tokens][513] required)");
+  if (layout->inter != ws->inter || layout->gate_up_format != ws->gate_up_format ||
+      layout->down_format != ws->down_format)
+    return invalid("layer_decode: workspace was made for a different layout");
+  // the [5][16][512] slice sums borrow the head of ws->partial, which nothing reads before the down kernel
+  const dim3 grid(kExperts / 16 * kRouteSplits), block(512);
+  cudaError_t e =
+      x_dtype == FB_DT_BF16
+          ? launch_pdl(route_kernel<true>, grid, block, 0, as_stream(stream),
+                       static_cast<const __nv_bfloat16*>(router_w_bf16), x, tokens, logits_scratch, int(FB_ROUTER_ROWS),
+                       ws->partial, *ws)
+          : launch_pdl(route_kernel<false>, grid, block, 0, as_stream(stream),
+                       static_cast<const __nv_bfloat16*>(router_w_bf16), x, tokens, logits_scratch, int(FB_ROUTER_ROWS),
+                       ws->partial, *ws);
+  if (e != cudaSuccess) return check_launch("layer_decode: route");
+  int32_t st = fb_moe_hot_gate_up(layout, tokens, ws, stream);
   if (st) return st;
-  st = fb_moe_select_publish(logits_scratch, FB_ROUTER_ROWS, x, x_dtype, nullptr, 0, nullptr, nullptr, tokens, ws,
-                             stream, nullptr);
-  if (st) return st;
-  st = fb_moe_hot_gate_up(layout, tokens, ws, stream);
-  if (st) return st;
-  st = fb_moe_hot_down(layout, tokens, ws, stream);
+  st = launch_down(layout, ws, stream);
   if (st) return st;
   return fb_moe_combine(ws, nullptr, nullptr, 0, nullptr, nullptr, nullptr, y_out, tokens, 0, nullptr, 0.0f, stream);
 }

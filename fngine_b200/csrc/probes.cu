@@ -28,8 +28,11 @@ __global__ void __launch_bounds__(256) dequant_iq3s_kernel(const uint8_t* __rest
       auto rd16 = [&](int off) { return uint32_t(blk[off]) | (uint32_t(blk[off + 1]) << 8); };
       auto rd32 = [&](int off) { return rd16(off) | (rd16(off + 2) << 16); };
       const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(rd16(0))));
+      uint32_t g[8], m[8];
+      iq3s_decode_sub(rd32(2 + 8 * ib), rd32(6 + 8 * ib), blk[66 + ib], 0, rd32(74 + 4 * ib), grid_lane, signtab, g, m);
       int w[8];
-      iq3s_decode32(rd32(2 + 8 * ib), rd32(6 + 8 * ib), blk[66 + ib], rd32(74 + 4 * ib), grid_lane, signtab, w);
+#pragma unroll
+      for (int l = 0; l < 8; ++l) w[l] = iq3s_signed(g[l], m[l]);
       const int s = (blk[106 + ib / 2] >> (4 * (ib & 1))) & 0xF;
       const float db = __fmul_rn(d, float(1 + 2 * s));
       float* o = out + int64_t(r) * k + 32 * sb;

@@ -40,7 +40,7 @@ class DecodeWork(C.Structure):
 
 class DecodeWorkspace(C.Structure):
     _fields_ = [("work", C.c_void_p), ("xq", C.c_void_p), ("h", C.c_void_p), ("hq", C.c_void_p),
-                ("partial", C.c_void_p), ("item_done", C.c_void_p), ("status", C.c_void_p),
+                ("partial", C.c_void_p), ("item_done", C.c_void_p), ("sched", C.c_void_p), ("status", C.c_void_p),
                 ("gate_up_format", C.c_int32), ("down_format", C.c_int32), ("inter", C.c_int32),
                 ("reserved", C.c_int32)]
 

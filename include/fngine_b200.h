@@ -108,7 +108,9 @@ typedef struct fb_moe_decode_work {
  * codes first, then the block scales as fp32 (Q8_0 scales are the fp16-rounded values widened;
  * Q8_0 codes are stored per block in the order 2*(e%16) + e/16 that the IQ4_NL nibble decode
  * produces). `hq` is h re-quantized for the down projection, `item_done` counts finished gate/up
- * tiles per work item, `status` is one device word set when a bounded wait runs out. */
+ * tiles per work item, `sched` holds the dynamic tile counters ([0] gate/up, [1] down) and from
+ * [8] on the work items ordered by token count (heaviest first), `status` is one device word set
+ * when a bounded wait runs out. */
 typedef struct fb_moe_decode_workspace {
   fb_moe_decode_work* work;
   uint8_t* xq;        /* [16][FB_XQ_STRIDE] */
@@ -116,6 +118,7 @@ typedef struct fb_moe_decode_workspace {
   uint8_t* hq;        /* [160 pairs][FB_HQ_STRIDE] */
   float* partial;     /* [160 pairs][2560], routing weight applied */
   int32_t* item_done; /* [160] */
+  int32_t* sched;     /* [8 + 160] */
   uint32_t* status;   /* FB_STATUS_* */
   int32_t gate_up_format;
   int32_t down_format;

@@ -54,7 +54,7 @@ def test_layout_and_argument_errors(fb_built):
     assert lib.fb_moe_decode_workspace_bytes(512) % 256 == 0
     # a CPU exchange is refused (no CPU tier) before anything is launched
     ws = fblib.DecodeWorkspace()
-    for f in ("work", "xq", "h", "hq", "partial", "item_done", "status"):
+    for f in ("work", "xq", "h", "hq", "partial", "item_done", "sched", "status"):
         setattr(ws, f, 0x1000)
     st = lib.fb_moe_select_publish(0x1000, 513, 0x1000, 0, None, 0, None, 0x1000, 4, ctypes.byref(ws), None, None)
     assert st == 1 and b"exchange" in lib.fb_last_error_string()

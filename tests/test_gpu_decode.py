@@ -272,6 +272,9 @@ def test_moe_layer_decode(fg, fd, inter, tokens):
     moe.moe_layer_decode(wr, layer, xd, ws, y)
     torch.cuda.synchronize()
     assert np.array_equal(y.cpu().numpy().view(np.uint32), y1.view(np.uint32))
+    # the fused layer call equals the reference's five-call sequence on the same logits
+    y5 = run_layer(torch, moe, layer, ws, None, xd, tokens, logits=ws.logits.clone())
+    assert np.array_equal(y5.cpu().numpy().view(np.uint32), y1.view(np.uint32))
     print("layer fmt %d/%d inter %d T=%d: distinct experts %d, max rel L2 %.2e" %
           (fg, fd, inter, tokens, work.n_items, max(errs)))
 
