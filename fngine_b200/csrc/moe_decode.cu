@@ -1341,4 +1341,71 @@ int32_t fb_moe_layer_decode_host(const void* router_w_bf16, const fb_moe_expert_
   return 0;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// fb_moe_layer_decode_static: the whole decode layer without any caller-provided scratch.
+//
+// Some hosts of this library may not allocate device memory at the point where they run a layer:
+// an engine whose memory plan is frozen after start-up (every byte of HBM already handed to
+// weights and KV cache), a plug-in that is only given tensor pointers, or code running where a
+// cudaMalloc would serialize the device. For them the layer's scratch - work list, quantized
+// activations, h, partial sums, router logits - lives in one array inside the library image.
+// Every GPU that loads the library carries these kStaticScratchBytes until the process exits.
+//
+// The array's name is only a host-side handle; its device address comes from
+// cudaGetSymbolAddress, taken once per device on that device's first call (so make that first
+// call outside any stream capture). All calls on a device share the array and it keeps the last
+// call's contents: the entry point clears the one word that must start at zero, and two calls
+// that overlap on the same GPU (different streams) race on it - serialize them.
+namespace {
+constexpr size_t kStaticWorkspaceBytes = 2304 * 1024;  // >= fb_moe_decode_workspace_bytes(640), checked at set-up
+constexpr size_t kStaticLogitsBytes = size_t(FB_DECODE_MAX_TOKENS) * FB_ROUTER_ROWS * 4;
+constexpr size_t kStaticScratchBytes = kStaticWorkspaceBytes + ((kStaticLogitsBytes + 255) & ~size_t(255));
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+struct StaticScratch {
+  bool ready = false;
+  unsigned char* base = nullptr;
+};
+StaticScratch g_static[64];
+}  // namespace
+
+int32_t fb_moe_layer_decode_static(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x,
+                                   int32_t x_dtype, int32_t tokens, float* y_out, void* stream) {
+  if (tokens < 1 || tokens > kMaxTok)
+    return invalid("layer_decode_static: tokens must be 1..%d (the static scratch is sized for that)", kMaxTok);
+  if (!layout_ok(layout)) return invalid("layer_decode_static: unsupported expert layout");
+  if (fb_moe_decode_workspace_bytes(layout->inter) > kStaticWorkspaceBytes)
+    return invalid("layer_decode_static: layout needs more scratch than the %zu static bytes", kStaticWorkspaceBytes);
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("layer_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    return e != cudaSuccess ? int32_t(e) : int32_t(cudaErrorInvalidDevice);
+  }
+  StaticScratch& sc = g_static[dev];
+  if (!sc.ready) {  // first call on this device: resolve the array's device address
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) {
+      set_error("layer_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      return e != cudaSuccess ? int32_t(e) : int32_t(cudaErrorInvalidSymbol);
+    }
+    sc.base = static_cast<unsigned char*>(p);
+    sc.ready = true;
+  }
+  fb_moe_decode_workspace ws;
+  int32_t st = fb_moe_decode_workspace_make(sc.base, layout, &ws);
+  if (st) return st;
+  float* logits = reinterpret_cast<float*>(sc.base + kStaticWorkspaceBytes);
+  // the sticky status word and the route counter are the only state a call inherits
+  e = cudaMemsetAsync(ws.status, 0, sizeof(uint32_t), as_stream(stream));
+  if (e == cudaSuccess) e = cudaMemsetAsync(ws.sched, 0, kSchedOrderBase * sizeof(int32_t), as_stream(stream));
+  if (e != cudaSuccess) {
+    set_error("layer_decode_static: clearing scratch state: %s", cudaGetErrorString(e));
+    return int32_t(e);
+  }
+  return fb_moe_layer_decode(router_w_bf16, layout, x, x_dtype, tokens, &ws, logits, y_out, stream);
+}
+
 }  // extern "C"

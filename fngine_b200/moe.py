@@ -156,6 +156,12 @@ def moe_layer_decode_host(w_router, layer, x_host, ws, x_dev, y_dev, y_host):
             "moe_layer_decode_host")
 
 
+def moe_layer_decode_static(w_router, layer, x, y_out):
+    """The decode layer with the library's built-in scratch (for callers that cannot allocate)."""
+    L.check(L.load().fb_moe_layer_decode_static(_ptr(w_router), C.byref(layer.layout), _ptr(x), _dtype_code(x),
+                                                x.shape[0], _ptr(y_out), _stream()), "moe_layer_decode_static")
+
+
 def dequant_rows(fmt, rows, nrows, k):
     """Exact fp32 weights of `nrows` back-to-back rows (device uint8 tensor)."""
     lib = L.load()

@@ -174,6 +174,18 @@ int32_t fb_moe_layer_decode_host(const void* router_w_bf16, const fb_moe_expert_
                                  int32_t x_dtype, int32_t tokens, const fb_moe_decode_workspace* ws,
                                  float* logits_scratch, void* x_dev, float* y_dev, float* y_host, void* stream);
 
+/* The decode layer for callers that may not allocate: no workspace, no logits scratch. This entry
+ * point has no counterpart in the reference (whose kernels always take a caller workspace). It is
+ * for hosts that cannot call cudaMalloc where they run a layer - a frozen memory plan, a plug-in
+ * handed only tensor pointers - so the scratch sits in a static device array inside the library
+ * (about 2.3 MB held by every GPU that loads it, until the process exits). Limit: tokens <= 16 and
+ * the layouts fb_moe_layer_decode accepts; larger requests are refused with an error. The first
+ * call on a device looks up the array's device address, so issue it before any stream capture.
+ * All calls on a GPU share the array: calls that overlap on that GPU race, keep them in one
+ * stream (or otherwise ordered). x and y_out are the caller's device buffers as above. */
+int32_t fb_moe_layer_decode_static(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x,
+                                   int32_t x_dtype, int32_t tokens, float* y_out, void* stream);
+
 /* ---------------------------------------------------------------- parity probes (no reference counterpart)
  * The same device routines the GEMV kernels use, exposed so that dequantized weights and int8
  * activations can be compared bit for bit with the CPU reference. */
