@@ -201,7 +201,8 @@ __device__ __forceinline__ void warp_topk(LoadF load_logit, int* ids, float* wei
 // load_logit(t, e) returns router logit e of token t.
 template <class LoadF>
 __device__ __forceinline__ void select_block(LoadF load_logit, const int32_t* slot_of, int T,
-                                             const fb_moe_decode_workspace& ws, uint32_t* counts) {
+                                             const fb_moe_decode_workspace& ws, uint32_t* counts,
+                                             bool remote_ok = false) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   __shared__ int s_id[kMaxTok][kTopK];
   __shared__ float s_w[kMaxTok][kTopK];
@@ -301,7 +302,7 @@ __device__ __forceinline__ void select_block(LoadF load_logit, const int32_t* sl
     work->n_pairs = n_pairs;
     work->n_cold = n_cold;
     work->tokens = T;
-    if (n_cold) atomicMax(ws.status, uint32_t(FB_STATUS_BAD_WORK));
+    if (n_cold && !remote_ok) atomicMax(ws.status, uint32_t(FB_STATUS_BAD_WORK));
   }
   __syncthreads();
   // Visiting order of the streaming kernels: most tokens first, ties by item index. Counting
@@ -385,7 +386,8 @@ constexpr int kRouteSplits = 5, kRouteSlice = H / kRouteSplits;  // 512
 template <bool XBF16>
 __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restrict__ w, const void* __restrict__ xv,
                                                     int T, float* __restrict__ logits, int stride,
-                                                    float* __restrict__ part, fb_moe_decode_workspace ws) {
+                                                    float* __restrict__ part, fb_moe_decode_workspace ws,
+                                                    const int32_t* __restrict__ slot_of, bool remote_ok) {
   pdl_launch_dependents();
   pdl_wait_prior();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -485,7 +487,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
     logits[size_t(t) * stride + tid] = v;
   }
   __syncthreads();
-  select_block([&](int t, int e) { return logits[size_t(t) * stride + e]; }, nullptr, T, ws, nullptr);
+  select_block([&](int t, int e) { return logits[size_t(t) * stride + e]; }, slot_of, T, ws, nullptr, remote_ok);
 }
 
 // ------------------------------------------------------------------------------ streaming skeleton
@@ -1115,6 +1117,17 @@ __global__ void __launch_bounds__(256) combine_kernel(fb_moe_decode_workspace ws
   }
 }
 
+// ------------------------------------------------------------------------------ expert-parallel combine
+// y[r][n] = parts[0][r][n] + parts[1][r][n] + ... in rank order (deterministic).
+__global__ void __launch_bounds__(256) sum_ranks_kernel(const float* __restrict__ parts, int n_ranks, int64_t elems,
+                                                        float* __restrict__ y) {
+  const int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= elems) return;
+  float v = 0.0f;
+  for (int r = 0; r < n_ranks; ++r) v += parts[int64_t(r) * elems + i];
+  y[i] = v;
+}
+
 // ------------------------------------------------------------------------------ host side
 template <class K>
 cudaError_t opt_in_smem(K kernel, size_t bytes) {
@@ -1292,9 +1305,10 @@ int32_t fb_moe_combine(const fb_moe_decode_workspace* ws, const float* y_shared,
   return 0;
 }
 
-int32_t fb_moe_layer_decode(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x,
-                            int32_t x_dtype, int32_t tokens, const fb_moe_decode_workspace* ws, float* logits_scratch,
-                            float* y_out, void* stream) {
+static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_layout* layout,
+                                 const int32_t* slot_of, bool remote_ok, const void* x, int32_t x_dtype,
+                                 int32_t tokens, const fb_moe_decode_workspace* ws, float* logits_scratch, float* y_out,
+                                 void* stream) {
   // Four launches: route (router projection + activation quantization + selection), gate/up, down,
   // combine. Same arithmetic, in the same order, as the five separate entry points.
   if (!router_w_bf16 || !x || !y_out || !logits_scratch || !layout_ok(layout) || !ws_ok(ws) || tokens < 1 ||
@@ -1309,16 +1323,39 @@ int32_t fb_moe_layer_decode(const void* router_w_bf16, const fb_moe_expert_layou
       x_dtype == FB_DT_BF16
           ? launch_pdl(route_kernel<true>, grid, block, 0, as_stream(stream),
                        static_cast<const __nv_bfloat16*>(router_w_bf16), x, tokens, logits_scratch, int(FB_ROUTER_ROWS),
-                       ws->partial, *ws)
+                       ws->partial, *ws, slot_of, remote_ok)
           : launch_pdl(route_kernel<false>, grid, block, 0, as_stream(stream),
                        static_cast<const __nv_bfloat16*>(router_w_bf16), x, tokens, logits_scratch, int(FB_ROUTER_ROWS),
-                       ws->partial, *ws);
+                       ws->partial, *ws, slot_of, remote_ok);
   if (e != cudaSuccess) return check_launch("layer_decode: route");
   int32_t st = fb_moe_hot_gate_up(layout, tokens, ws, stream);
   if (st) return st;
   st = launch_down(layout, ws, stream);
   if (st) return st;
   return fb_moe_combine(ws, nullptr, nullptr, 0, nullptr, nullptr, nullptr, y_out, tokens, 0, nullptr, 0.0f, stream);
+}
+
+int32_t fb_moe_layer_decode(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x,
+                            int32_t x_dtype, int32_t tokens, const fb_moe_decode_workspace* ws, float* logits_scratch,
+                            float* y_out, void* stream) {
+  return layer_decode_impl(router_w_bf16, layout, nullptr, false, x, x_dtype, tokens, ws, logits_scratch, y_out,
+                           stream);
+}
+
+int32_t fb_moe_layer_decode_ep(const void* router_w_bf16, const fb_moe_expert_layout* layout,
+                               const int32_t* slot_of, const void* x, int32_t x_dtype, int32_t tokens,
+                               const fb_moe_decode_workspace* ws, float* logits_scratch, float* y_partial,
+                               void* stream) {
+  if (!slot_of) return invalid("layer_decode_ep: slot_of (expert -> local slot, -1 = another rank) is required");
+  return layer_decode_impl(router_w_bf16, layout, slot_of, true, x, x_dtype, tokens, ws, logits_scratch, y_partial,
+                           stream);
+}
+
+int32_t fb_ep_sum_ranks(const float* parts, int32_t n_ranks, int32_t rows, float* y, void* stream) {
+  if (!parts || !y || n_ranks < 1 || rows < 1) return invalid("ep_sum_ranks: bad arguments");
+  const int64_t elems = int64_t(rows) * H;
+  sum_ranks_kernel<<<unsigned((elems + 255) / 256), 256, 0, as_stream(stream)>>>(parts, n_ranks, elems, y);
+  return check_launch("ep_sum_ranks");
 }
 
 int32_t fb_moe_layer_decode_host(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x_host,

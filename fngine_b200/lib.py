@@ -68,6 +68,9 @@ _SIGNATURES = {
     "fb_moe_layer_decode": (_I32, [_P, C.POINTER(ExpertLayout), _P, _I32, _I32, C.POINTER(DecodeWorkspace), _P, _P, _P]),
     "fb_moe_layer_decode_host": (_I32, [_P, C.POINTER(ExpertLayout), _P, _I32, _I32, C.POINTER(DecodeWorkspace), _P,
                                         _P, _P, _P, _P]),
+    "fb_moe_layer_decode_ep": (_I32, [_P, C.POINTER(ExpertLayout), _P, _P, _I32, _I32, C.POINTER(DecodeWorkspace), _P, _P,
+                               _P]),
+    "fb_ep_sum_ranks": (_I32, [_P, _I32, _I32, _P, _P]),
     "fb_moe_layer_decode_static": (_I32, [_P, C.POINTER(ExpertLayout), _P, _I32, _I32, _P, _P]),
     "fb_dequant_rows": (_I32, [_I32, _P, _I64, _I32, _I32, _P, _P]),
     "fb_quantize_act": (_I32, [_I32, _P, _I32, _I32, _I32, _P, _P]),

@@ -174,6 +174,21 @@ int32_t fb_moe_layer_decode_host(const void* router_w_bf16, const fb_moe_expert_
                                  int32_t x_dtype, int32_t tokens, const fb_moe_decode_workspace* ws,
                                  float* logits_scratch, void* x_dev, float* y_dev, float* y_host, void* stream);
 
+/* ---------------------------------------------------------------- expert parallel (no reference counterpart)
+ * The reference is single-GPU. Here the 512 experts of a layer are sharded over the ranks of one
+ * node; a rank's slot array holds only its own experts and `slot_of[e]` is the local slot of expert
+ * e or -1 when another rank owns it (the role the reference gives to "cold" experts,
+ * src/kernels/moe/moe.h:119-121). */
+/* One decode layer over this rank's experts: x holds ALL tokens of the step (after dispatch),
+ * y_partial[t] = sum over token t's LOCAL experts, in slot order; pairs of other ranks are skipped
+ * and counted in the work list's n_cold. */
+int32_t fb_moe_layer_decode_ep(const void* router_w_bf16, const fb_moe_expert_layout* layout,
+                               const int32_t* slot_of, const void* x, int32_t x_dtype, int32_t tokens,
+                               const fb_moe_decode_workspace* ws, float* logits_scratch, float* y_partial,
+                               void* stream);
+/* Combine on the owning rank: y[r] = parts[0][r] + parts[1][r] + ... (rank order), rows x 2560 fp32. */
+int32_t fb_ep_sum_ranks(const float* parts, int32_t n_ranks, int32_t rows, float* y, void* stream);
+
 /* The decode layer for callers that may not allocate: no workspace, no logits scratch. This entry
  * point has no counterpart in the reference (whose kernels always take a caller workspace). It is
  * for hosts that cannot call cudaMalloc where they run a layer - a frozen memory plan, a plug-in

@@ -352,3 +352,40 @@ def test_host_entry_point_matches_device_path():
     moe.moe_layer_decode(wr, layer, xh.cuda(), ws, y2)
     torch.cuda.synchronize()
     assert np.array_equal(yh.numpy().view(np.uint32), y2.cpu().numpy().view(np.uint32))
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_expert_parallel_shards_on_one_gpu(world):
+    """The expert-parallel entry points, with the ranks played one after another on a single GPU:
+    each rank's shard (its own slot array and slot map) gives partial rows, the rank-order sum equals
+    the single-GPU layer (same routing) within summation-order noise and the CPU oracle within 1e-3."""
+    torch = _torch()
+    from fngine_b200 import ep, moe
+    tokens, seed = 16, 5000
+    wr = torch.from_numpy(synth.router_weights(303, rows=512).view(np.int16)).cuda().view(torch.bfloat16)
+    x = synth.activations(77, tokens)
+    xd = torch.from_numpy(x).cuda()
+    full = moe.synth_layer(IQ3_S, IQ3_S, 512, 512, seed)
+    ws = moe.DecodeWorkspace(full)
+    y_full = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    moe.moe_layer_decode(wr, full, xd, ws, y_full)
+    torch.cuda.synchronize()
+    parts = torch.empty(world, tokens, H, dtype=torch.float32, device="cuda")
+    n_local = 0
+    for r in range(world):
+        shard = ep.EpDecodeLayer(r, world, seed)
+        ep.layer_decode_ep(wr, shard, xd, ws, parts[r])
+        torch.cuda.synchronize()
+        wk = ws.work()
+        n_local += wk.n_pairs
+        assert wk.n_cold == tokens * 10 - wk.n_pairs and ws.status() == 0
+    assert n_local == tokens * 10  # every pair is computed by exactly one rank
+    y = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    ep.sum_ranks(parts, y)
+    torch.cuda.synchronize()
+    got, ref = y.cpu().numpy(), y_full.cpu().numpy()
+    assert max(rel_l2(got[t], ref[t]) for t in range(tokens)) <= 1e-6
+    logits = ws.logits.cpu().numpy()[:tokens * 513].reshape(tokens, 513)[:, :512]
+    ids, w = O.topk(logits)
+    want = oracle_layer(IQ3_S, IQ3_S, 512, seed, x, ids, w)
+    assert max(rel_l2(got[t], want[t]) for t in range(tokens)) <= TOL
