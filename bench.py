@@ -164,6 +164,55 @@ def workload_config(args, layers_per_step):
             "activation_format": "Q8_K (reference CPU tier numerics)"}
 
 
+def fp8_gemm_section(torch, iters=10):
+    """The FP8-row dense GEMM of the benchmark definition (bf16 [4096x2560] x E4M3 [9216x2560] -> bf16),
+    each call timed alone with CUDA events after an L2 flush; the library FP8 GEMM of the same shape
+    (torch._scaled_mm, when present) gives the practical tensor-core ceiling on this box."""
+    from fngine_b200 import linear, synth
+    T, N, K = 4096, 9216, 2560
+    codes, scales = synth.fp8_row_weight(4, N, K)
+    wc, ws = torch.from_numpy(codes).cuda(), torch.from_numpy(scales).cuda()
+    weight = linear.Fp8RowWeight(wc, ws)
+    x = torch.from_numpy(synth.to_bf16_bits(synth.activations(44, T, hidden=K)).view(np.int16)).cuda().view(torch.bfloat16)
+    out = torch.empty(T, N, dtype=torch.bfloat16, device="cuda")
+    work = linear.linear_fp8_workspace(weight, T)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    xq, xs = linear.fp8_quantize_tokens(x)
+
+    def timed(fn):
+        ts = []
+        for _ in range(3):
+            fn()
+        for _ in range(iters):
+            flush.fill_(1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts), min(ts)
+
+    flops = 2.0 * T * N * K
+    med, best = timed(lambda: linear.linear_fp8(x, weight, out, work))
+    res = {"shape": "bf16[4096x2560] x e4m3[9216x2560] -> bf16[4096x9216], fp32 row scales",
+           "tflops": flops / (med * 1e-3) / 1e12, "tflops_best": flops / (best * 1e-3) / 1e12, "ms": med,
+           "includes": "per-token E4M3 activation quantization + tcgen05 GEMM + scale/bf16 epilogue",
+           "nominal_dense_fp8_tflops": 4500.0, "frac_of_nominal": flops / (med * 1e-3) / 1e12 / 4500.0,
+           "l2_policy": "256 MB flush write before every timed call"}
+    try:
+        a8 = xq.view(torch.float8_e4m3fn)
+        b8 = wc.view(torch.float8_e4m3fn).t()
+        one = torch.ones((), dtype=torch.float32, device="cuda")
+        lm, lb = timed(lambda: torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
+        res["library_fp8_gemm_tflops"] = flops / (lm * 1e-3) / 1e12
+        res["frac_of_library"] = lm / med
+    except Exception as e:  # the comparison is optional
+        res["library_fp8_gemm_tflops"] = None
+        res["library_note"] = type(e).__name__
+    return res
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     from fngine_b200 import lib as fblib
@@ -305,6 +354,9 @@ def run_ours(args, rank, world, local_rank):
     yg = y.cpu().numpy()
     parity = float(max(np.linalg.norm(yg[t] - y_cpu[t]) / np.linalg.norm(y_cpu[t]) for t in range(B)))
 
+    del layers
+    torch.cuda.empty_cache()
+    fp8 = fp8_gemm_section(torch)
     peak, peak_src = peaks()
     gu_ach = sum(gu_bytes) / (sum(gu_ms) * 1e-3) / 1e9
     value = step_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -331,6 +383,7 @@ def run_ours(args, rank, world, local_rank):
                 "api": "fb_moe_layer_decode_host per layer: pinned host x in, host y out, stream wait inside"},
         "gpu_launches": args.steps * Lr * 4,
         "other_batches": other,
+        "fp8_row_gemm": fp8,
         "parity_vs_cpu_max_rel_l2": parity,
         "device_status": status,
         "clocks": clocks,

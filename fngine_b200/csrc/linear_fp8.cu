@@ -1,0 +1,368 @@
+// FP8-row dense projection for sm_100a: out[t][n] = bf16( (sum_k a8[t][k] * w8[n][k]) * sa[t] * sw[n] )
+//
+//   a8, sa : per-token E4M3 quantization of the bf16 activations (scale = max|x| / 448), the
+//            reference's "A8" path (src/kernels/linear/fp8/fp8_a8_quantize.cuh:14-26 and
+//            fp8_a8.cu:22-69 of the reference project);
+//   w8, sw : E4M3 weight codes [n][k] with one scale per row (src/kernels/linear/linear.h:57-62).
+//
+// The GEMM is a persistent tcgen05 kernel: 128 x 256 output tiles, K steps of 128 bytes. One
+// thread issues TMA tile loads (128-byte swizzle, no multicast) into a 4-stage shared-memory ring,
+// one thread issues tcgen05.mma (kind::f8f6f4, E4M3 x E4M3 -> fp32) into one of two 256-column TMEM
+// accumulators, four warps drain the other accumulator (tcgen05.ld), apply the two scales and store
+// bf16. All hand-offs are mbarriers; every wait is bounded and reports through a status word.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+namespace fb {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 128, kStages = 4;
+constexpr int kStageA = BM * BK, kStageB = BN * BK;           // bytes (1 byte per element)
+constexpr int kRingBytes = kStages * (kStageA + kStageB);      // 196608
+constexpr int kGemmSmem = kRingBytes + 256 + 1024;             // + barriers + alignment slack
+constexpr int kThreads = 192;                                  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr uint32_t kTmemCols = 512;                            // two 256-column fp32 accumulators
+
+// ------------------------------------------------------------------------------ PTX
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D[tmem] (+)= A[smem desc] * B[smem desc], E4M3 operands, fp32 accumulate.
+__device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// 32 lanes x 32 columns of fp32: thread i of the warp receives lane (base lane + i), 32 columns.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled,
+// 8-row groups 1024 bytes apart (the layout the TMA box below writes): start address, leading
+// offset 1 (unused for this layout), stride offset 1024 B, descriptor version 1, SWIZZLE_128B.
+__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
+  return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// Instruction descriptor: D fp32, A and B E4M3, both K-major, N = 256, M = 128.
+constexpr uint32_t kIdescF8 = (1u << 4) | (0u << 7) | (0u << 10) | (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+
+struct GemmBars {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ bool gemm_wait(GemmBars* b, uint64_t* bar, uint32_t parity, uint32_t* status) {
+  if (*reinterpret_cast<volatile int*>(&b->abort)) return false;
+  if (mbar_wait(bar, parity)) return true;
+  *reinterpret_cast<volatile int*>(&b->abort) = 1;
+  atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+  return false;
+}
+
+// ------------------------------------------------------------------------------ activation quantization
+// One block per token: scale = max|x| / 448, codes = satfinite_rne_e4m3(x * (1 / scale)).
+__global__ void __launch_bounds__(256) fp8_quantize_tokens_kernel(const __nv_bfloat16* __restrict__ x, int K,
+                                                                  uint8_t* __restrict__ codes,
+                                                                  float* __restrict__ scales) {
+  const int t = blockIdx.x;
+  const __nv_bfloat16* row = x + size_t(t) * K;
+  __shared__ float s_red[8];
+  float m = 0.0f;
+  for (int i = threadIdx.x * 8; i < K; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + i);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      m = fmaxf(m, fabsf(__uint_as_float(u[j] << 16)));
+      m = fmaxf(m, fabsf(__uint_as_float(u[j] & 0xFFFF0000u)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = s_red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m = fmaxf(m, s_red[i]);
+  const float scale = m > 0.0f ? __fdiv_rn(m, 448.0f) : 0.0f;
+  const float inv = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+  if (threadIdx.x == 0) scales[t] = scale;
+  for (int i = threadIdx.x * 8; i < K; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + i);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = make_float2(__fmul_rn(__uint_as_float(u[j] << 16), inv),
+                                   __fmul_rn(__uint_as_float(u[j] & 0xFFFF0000u), inv));
+      const uint32_t pair = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+      o[j >> 1] |= pair << (16 * (j & 1));
+    }
+    *reinterpret_cast<uint2*>(codes + size_t(t) * K + i) = make_uint2(o[0], o[1]);
+  }
+}
+
+// ------------------------------------------------------------------------------ GEMM
+template <bool SCALE_BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const float* __restrict__ act_scale, const void* __restrict__ w_scale,
+                __nv_bfloat16* __restrict__ out, int M, int N, int K, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring_a = smem;
+  uint8_t* ring_b = smem + kStages * kStageA;
+  GemmBars* bars = reinterpret_cast<GemmBars*>(smem + kRingBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, k_blocks = K / BK;
+  const int n_work = m_tiles * n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&bars->full[i], 1);
+      mbar_init(&bars->empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->tmem_full[i], 1);
+      mbar_init(&bars->tmem_empty[i], 4);
+    }
+    bars->abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&bars->tmem_base, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < n_work; tile += gridDim.x) {
+        const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          if (!gemm_wait(bars, &bars->empty[s], ((it / kStages) & 1) ^ 1, status)) { ok = false; break; }
+          mbar_expect_tx(&bars->full[s], kStageA + kStageB);
+          tma_load_2d(ring_a + s * kStageA, &map_a, kb * BK, m_blk * BM, &bars->full[s]);
+          tma_load_2d(ring_b + s * kStageB, &map_b, kb * BK, n_blk * BN, &bars->full[s]);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tl = 0;
+      for (int tile = blockIdx.x; tile < n_work; tile += gridDim.x, ++tl) {
+        const int ab = tl & 1;
+        if (!gemm_wait(bars, &bars->tmem_empty[ab], ((tl >> 1) & 1) ^ 1, status)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + uint32_t(ab * BN);
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          if (!gemm_wait(bars, &bars->full[s], (it / kStages) & 1, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = umma_desc_k128(smem_u32(ring_a + s * kStageA));
+          const uint64_t db = umma_desc_k128(smem_u32(ring_b + s * kStageB));
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 32; ++k4)  // 32 bytes of K per instruction: +2 in 16-byte units
+            umma_f8(d_tmem, da + uint64_t(2 * k4), db + uint64_t(2 * k4), kIdescF8, (kb | k4) ? 1u : 0u);
+          umma_commit(&bars->empty[s]);  // stage reusable once these MMAs have read it
+        }
+        if (!ok) break;
+        umma_commit(&bars->tmem_full[ab]);  // accumulator complete
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 2..5: TMEM lane quarter = warp % 4
+    const int q = warp & 3;
+    uint32_t tl = 0;
+    for (int tile = blockIdx.x; tile < n_work; tile += gridDim.x, ++tl) {
+      const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
+      const int ab = tl & 1;
+      if (!gemm_wait(bars, &bars->tmem_full[ab], (tl >> 1) & 1, status)) break;
+      tc_fence_after();
+      const int row = m_blk * BM + q * 32 + lane;
+      const float sa = row < M ? act_scale[row] : 0.0f;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(ab * BN + c * 32), r);
+        const int col0 = n_blk * BN + c * 32;
+        if (row < M && col0 < N) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float s0, s1;
+            if constexpr (SCALE_BF16) {
+              const uint32_t u = reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(w_scale) + col0)[j];
+              s0 = __uint_as_float(u << 16);
+              s1 = __uint_as_float(u & 0xFFFF0000u);
+            } else {
+              const float2 f = reinterpret_cast<const float2*>(static_cast<const float*>(w_scale) + col0)[j];
+              s0 = f.x;
+              s1 = f.y;
+            }
+            const float v0 = __uint_as_float(r[2 * j]) * sa * s0;
+            const float v1 = __uint_as_float(r[2 * j + 1]) * sa * s1;
+            const __nv_bfloat162 b = __floats2bfloat162_rn(v0, v1);
+            packed[j] = *reinterpret_cast<const uint32_t*>(&b);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(out + size_t(row) * N + col0);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tmem_empty[ab]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------ host
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// uint8 [rows][k] row-major, boxes of 128 bytes x box_rows, 128-byte swizzle, zero fill outside.
+bool make_map_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(k)};
+  const cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+}  // namespace
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" {
+
+size_t fb_linear_fp8_workspace_bytes(int32_t n, int32_t k, int32_t max_tokens) {
+  (void)n;
+  if (k <= 0 || max_tokens <= 0) return 0;
+  return align256(size_t(max_tokens) * size_t(k)) + align256(size_t(max_tokens) * 4) + 256;
+}
+
+int32_t fb_fp8_quantize_tokens(const void* x_bf16, int32_t tokens, int32_t k, uint8_t* codes, float* scales,
+                               void* stream) {
+  if (!x_bf16 || !codes || !scales || tokens <= 0 || k <= 0 || k % 8)
+    return invalid("fp8_quantize_tokens: bad arguments (k must be a multiple of 8)");
+  fp8_quantize_tokens_kernel<<<tokens, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x_bf16), k, codes,
+                                                                    scales);
+  return check_launch("fp8_quantize_tokens");
+}
+
+int32_t fb_linear_fp8(const void* x_bf16, int32_t tokens, const uint8_t* w_codes, const void* w_scales,
+                      int32_t w_scales_dtype, int32_t n, int32_t k, void* out_bf16, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  if (!x_bf16 || !w_codes || !w_scales || !out_bf16 || tokens <= 0)
+    return invalid("linear_fp8: null argument or no tokens");
+  if (n <= 0 || k <= 0 || n % 64 || k % BK)
+    return invalid("linear_fp8: unsupported shape (n must be a multiple of 64, k of 128)");
+  if ((reinterpret_cast<uintptr_t>(w_codes) | reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(out_bf16)) & 15)
+    return invalid("linear_fp8: x, weight codes and out must be 16-byte aligned");
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      workspace_bytes < fb_linear_fp8_workspace_bytes(n, k, tokens))
+    return invalid("linear_fp8: workspace missing, misaligned (256 B) or smaller than fb_linear_fp8_workspace_bytes");
+  uint8_t* a_codes = static_cast<uint8_t*>(workspace);
+  float* a_scales = reinterpret_cast<float*>(a_codes + align256(size_t(tokens) * size_t(k)));
+  uint32_t* status = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a_scales) + align256(size_t(tokens) * 4));
+  int32_t st = fb_fp8_quantize_tokens(x_bf16, tokens, k, a_codes, a_scales, stream);
+  if (st) return st;
+  CUtensorMap map_a, map_b;
+  if (!make_map_u8(&map_a, a_codes, tokens, k, BM) || !make_map_u8(&map_b, w_codes, n, k, BN)) {
+    set_error("linear_fp8: cuTensorMapEncodeTiled failed");
+    return int32_t(cudaErrorInvalidValue);
+  }
+  static bool once = [] {
+    cudaFuncSetAttribute(fp8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
+    cudaFuncSetAttribute(fp8_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
+    return true;
+  }();
+  (void)once;
+  cudaError_t e = cudaMemsetAsync(status, 0, 4, as_stream(stream));
+  if (e != cudaSuccess) return check_launch("linear_fp8: status clear");
+  const int m_tiles = (tokens + BM - 1) / BM, n_tiles = (n + BN - 1) / BN;
+  const int grid = m_tiles * n_tiles < sm_count() ? m_tiles * n_tiles : sm_count();
+  if (w_scales_dtype == FB_DT_BF16)
+    fp8_gemm_kernel<true><<<grid, kThreads, kGemmSmem, as_stream(stream)>>>(
+        map_a, map_b, a_scales, w_scales, static_cast<__nv_bfloat16*>(out_bf16), tokens, n, k, status);
+  else
+    fp8_gemm_kernel<false><<<grid, kThreads, kGemmSmem, as_stream(stream)>>>(
+        map_a, map_b, a_scales, w_scales, static_cast<__nv_bfloat16*>(out_bf16), tokens, n, k, status);
+  return check_launch("linear_fp8");
+}
+
+}  // extern "C"

@@ -72,6 +72,9 @@ _SIGNATURES = {
                                _P]),
     "fb_ep_sum_ranks": (_I32, [_P, _I32, _I32, _P, _P]),
     "fb_moe_layer_decode_static": (_I32, [_P, C.POINTER(ExpertLayout), _P, _I32, _I32, _P, _P]),
+    "fb_linear_fp8_workspace_bytes": (C.c_size_t, [_I32, _I32, _I32]),
+    "fb_linear_fp8": (_I32, [_P, _I32, _P, _P, _I32, _I32, _I32, _P, _P, C.c_size_t, _P]),
+    "fb_fp8_quantize_tokens": (_I32, [_P, _I32, _I32, _P, _P, _P]),
     "fb_dequant_rows": (_I32, [_I32, _P, _I64, _I32, _I32, _P, _P]),
     "fb_quantize_act": (_I32, [_I32, _P, _I32, _I32, _I32, _P, _P]),
     "fb_synth_fill_blocks": (_I32, [_I32, _P, _I64, _I64, C.c_uint64, _P, _P]),

@@ -93,3 +93,14 @@ def bf16_bits_to_f32(b):
 def router_weights(seed, rows=512, hidden=2560, std=0.02):
     """bf16 router [rows][hidden] ~ N(0, std) as uint16 bit patterns."""
     return to_bf16_bits((normal(seed, rows * hidden) * std).astype(np.float32)).reshape(rows, hidden)
+
+
+def fp8_row_weight(seed, n, k):
+    """FP8-row weight of the dense-GEMM benchmark definition: values ~ N(0,1) clipped to +-448 and
+    rounded to E4M3FN (nearest even), one fp32 scale per row ~ U(0.001, 0.01).
+    Returns (codes uint8 [n][k], scales float32 [n])."""
+    import torch
+    v = np.clip(normal(seed, n * k), -448.0, 448.0).astype(np.float32).reshape(n, k)
+    codes = torch.from_numpy(v).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    scales = (0.001 + 0.009 * uniform(seed ^ 0x5CA1E, 0, n)).astype(np.float32)
+    return codes, scales

@@ -201,6 +201,27 @@ int32_t fb_ep_sum_ranks(const float* parts, int32_t n_ranks, int32_t rows, float
 int32_t fb_moe_layer_decode_static(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x,
                                    int32_t x_dtype, int32_t tokens, float* y_out, void* stream);
 
+/* ---------------------------------------------------------------- FP8-row dense projection
+ * Fp8RowWeight + linear_fp8 with the StoreBf16 epilogue, src/kernels/linear/linear.h:57-62, :137-139:
+ * out[t][n] = bf16((x[t] . W[n]) * scale[n]), W = E4M3FN codes [n][k] (16-byte aligned) with one
+ * scale per row. This implementation is the reference's "A8" path (linear.h:32-37): each token is
+ * quantized to E4M3 with a per-token fp32 scale max|x|/448 into the workspace, then an
+ * E4M3 x E4M3 tensor-core GEMM (tcgen05, fp32 accumulation in tensor memory) runs and the epilogue
+ * multiplies by act_scale[t] * row_scale[n]. Row scales may be fp32 (FB_DT_F32) or bf16 (FB_DT_BF16,
+ * the reference's pack format). Shapes: any n % 64 == 0, k % 128 == 0 (the reference's closed
+ * registry, linear_fp8.cpp:19-24, is not enforced). Bad arguments return cudaErrorInvalidValue where
+ * the reference throws std::invalid_argument (linear_fp8.cpp:83-95). */
+/* linear_fp8_workspace_bytes, src/kernels/linear/linear.h:132. */
+size_t fb_linear_fp8_workspace_bytes(int32_t n, int32_t k, int32_t max_tokens);
+int32_t fb_linear_fp8(const void* x_bf16, int32_t tokens, const uint8_t* w_codes, const void* w_scales,
+                      int32_t w_scales_dtype, int32_t n, int32_t k, void* out_bf16, void* workspace,
+                      size_t workspace_bytes, void* stream);
+/* The activation quantizer alone (fp8_a8_quantize_kernel, src/kernels/linear/fp8/fp8_a8.cu:22-69):
+ * codes [tokens][k], scales [tokens]; bit-identical to the host statement in
+ * tests/kernels/linear/linear_ref.h:99-107 of the reference. */
+int32_t fb_fp8_quantize_tokens(const void* x_bf16, int32_t tokens, int32_t k, uint8_t* codes, float* scales,
+                               void* stream);
+
 /* ---------------------------------------------------------------- parity probes (no reference counterpart)
  * The same device routines the GEMV kernels use, exposed so that dequantized weights and int8
  * activations can be compared bit for bit with the CPU reference. */
