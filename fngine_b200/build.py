@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfngine_b200.so")
-SOURCES = ["api.cu", "probes.cu", "moe_decode.cu", "linear_fp8.cu"]
+SOURCES = ["api.cu", "probes.cu", "moe_decode.cu", "linear_fp8.cu", "moe_prefill.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

@@ -136,68 +136,6 @@ __global__ void __launch_bounds__(128) router_kernel(const __nv_bfloat16* __rest
 }
 
 // ------------------------------------------------------------------------------ select
-// Top-k of 512 logits by one warp (lane l holds logits l + 32 i): value descending, ties to the
-// lower id, NaN never wins, -0 == +0; weights = softmax over the winners in fp32
-// (src/kernels/moe/moe_common.cuh:33-85 of the reference states the same contract).
-// Order-preserving map of a float to uint32 (larger float -> larger key); NaN maps below every
-// number and -0 equals +0.
-__device__ __forceinline__ uint32_t logit_key(float x) {
-  if (x != x) x = -INFINITY;
-  if (x == 0.0f) x = 0.0f;
-  const uint32_t u = __float_as_uint(x);
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-
-template <class LoadF>
-__device__ __forceinline__ void warp_topk(LoadF load_logit, int* ids, float* weights) {
-  const int lane = threadIdx.x & 31;
-  uint32_t key[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) key[i] = logit_key(load_logit(lane + 32 * i));
-  float vals[kTopK];
-#pragma unroll
-  for (int k = 0; k < kTopK; ++k) {
-    // lane-local best as a 4-level tree: a higher slot wins only when strictly greater, so equal
-    // keys resolve to the lower id; the warp step is two redux operations (max key, then min id).
-    uint32_t tk[16];
-    int ti[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      tk[i] = key[i];
-      ti[i] = i;
-    }
-#pragma unroll
-    for (int w = 1; w < 16; w <<= 1) {
-#pragma unroll
-      for (int i = 0; i < 16; i += 2 * w) {
-        const bool up = tk[i + w] > tk[i];
-        tk[i] = up ? tk[i + w] : tk[i];
-        ti[i] = up ? ti[i + w] : ti[i];
-      }
-    }
-    const uint32_t best = __reduce_max_sync(0xffffffffu, tk[0]);
-    const uint32_t cand = tk[0] == best ? uint32_t(lane + 32 * ti[0]) : 0xffffffffu;
-    const int win = int(__reduce_min_sync(0xffffffffu, cand));
-    ids[k] = win;
-    const uint32_t u = (best & 0x80000000u) ? (best & 0x7fffffffu) : ~best;
-    vals[k] = __uint_as_float(u);
-    // retire the winner: key 0 is below every real key (the smallest real key is ~0xFF800000 = 0x007FFFFF)
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-      if (win == lane + 32 * i) key[i] = 0u;
-  }
-  float sum = 0.0f;
-  const float top = vals[0];
-#pragma unroll
-  for (int k = 0; k < kTopK; ++k) {
-    vals[k] = expf(vals[k] - top);
-    sum += vals[k];
-  }
-  const float inv = __fdiv_rn(1.0f, sum);
-#pragma unroll
-  for (int k = 0; k < kTopK; ++k) weights[k] = vals[k] * inv;
-}
-
 // load_logit(t, e) returns router logit e of token t.
 template <class LoadF>
 __device__ __forceinline__ void select_block(LoadF load_logit, const int32_t* slot_of, int T,
@@ -223,7 +161,7 @@ __device__ __forceinline__ void select_block(LoadF load_logit, const int32_t* sl
   if (warp < T) {
     int ids[kTopK];
     float w[kTopK];
-    warp_topk([&](int e) { return load_logit(warp, e); }, ids, w);
+    warp_topk10([&](int e) { return load_logit(warp, e); }, ids, w);
 #pragma unroll
     for (int k = 0; k < kTopK; ++k)
       if (lane == k) {

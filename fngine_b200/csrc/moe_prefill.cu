@@ -1,0 +1,858 @@
+// Prefill-width routed experts: route -> grouped gate/up -> grouped down -> combine.
+//
+// Numerics are the reference's prefill family (src/kernels/moe/moe.h:32-35 and the CPU pool's
+// prefill mode, src/cpu/iq_cpu.h:93-99): weights dequantized exactly and rounded to bf16, bf16
+// activations, fp32 accumulation, h stored as bf16.
+//
+// Both grouped GEMMs run on tcgen05 (kind::f16, bf16 x bf16 -> fp32 in tensor memory) with the
+// WEIGHT rows on the 128 TMEM lanes and the expert's TOKENS on the N axis (a multiple of 16, up to
+// 256), so ragged per-expert token counts waste at most 15 columns:
+//   D[128 weight rows][tokens] += W_bf16[128][64] * X[tokens][64]^T        per 64-wide K step.
+// The A operand never exists in global memory: 256 dequant threads (one per weight row of the gate
+// and of the up tile) decode their row's quarter IQ3_S block (or two IQ4_NL blocks) per K step
+// straight into the 128-byte-swizzled shared-memory tile the MMA reads. The B operand is gathered
+// token rows (cp.async, gate/up) or the expert-sorted h rows (TMA, down). One thread issues the
+// MMAs; four warps drain tensor memory. All hand-offs are mbarriers with bounded waits.
+#include "iq_decode.cuh"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+namespace fb {
+namespace {
+
+constexpr int H = FB_HIDDEN;
+constexpr int kExperts = FB_EXPERTS;
+constexpr int kTopK = FB_TOPK;
+constexpr int kBK = 64;          // K elements per pipeline stage = one 128-byte swizzled row
+constexpr int kTileM = 128;      // weight rows per unit (TMEM lanes)
+constexpr int kTileN = 256;      // tokens per unit (TMEM columns per accumulator)
+constexpr int kStagesGU = 3, kStagesDN = 4;
+constexpr int kTileA = kTileM * 128;  // 16 KB
+constexpr int kTileB = kTileN * 128;  // 32 KB
+
+// ------------------------------------------------------------------------------ PTX (tcgen05 / TMA / cp.async)
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// K-major bf16 tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
+  return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// D fp32, A and B bf16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t idesc_bf16(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
+}
+// Byte offset of 16-byte chunk c of row r inside a 128-byte-swizzled tile.
+__device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
+
+struct Abort {
+  volatile int* flag;
+  uint32_t* status;
+  __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity) const {
+    if (*flag) return false;
+    if (mbar_wait(bar, parity)) return true;
+    *flag = 1;
+    atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+    return false;
+  }
+};
+
+// ------------------------------------------------------------------------------ weights -> bf16 tile rows
+// One thread writes the 64 bf16 (128 bytes) of its weight row for K step `kb` into the swizzled
+// tile: value = bf16_rne(fp32 dequantized weight), the reference's rounding
+// (cpu::decode_rows_bf16, src/cpu/iq_cpu.cpp:712-753). `row_bytes` points at the row's first block.
+__device__ __forceinline__ uint32_t ldg16(const uint8_t* p) { return __ldg(reinterpret_cast<const unsigned short*>(p)); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// IQ3_S: K step kb covers sub-blocks 2q, 2q+1 (q = kb % 4) of block kb / 4.
+__device__ __forceinline__ void dequant_row_step_iq3s(const uint8_t* row_bytes, int kb, const uint32_t* grid,
+                                                      const uint32_t* signtab, uint8_t* tile, int row) {
+  const uint8_t* blk = row_bytes + (kb >> 2) * 110;
+  const int q = kb & 3;
+  const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(ldg16(blk))));
+  uint32_t qs[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) qs[i] = ldg16(blk + 2 + 16 * q + 4 * i) | (ldg16(blk + 4 + 16 * q + 4 * i) << 16);
+  const uint32_t qh = ldg16(blk + 66 + 2 * q);
+  uint32_t sg[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) sg[i] = ldg16(blk + 74 + 8 * q + 4 * i) | (ldg16(blk + 76 + 8 * q + 4 * i) << 16);
+  const uint32_t sc = blk[106 + q];
+#pragma unroll
+  for (int sb = 0; sb < 2; ++sb) {
+    const float db = __fmul_rn(d, float(1 + 2 * int((sc >> (4 * sb)) & 0xFu)));
+#pragma unroll
+    for (int l = 0; l < 8; l += 2) {  // two look-ups = 8 weights = one 16-byte chunk
+      uint32_t packed[4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int ll = l + h;
+        const uint32_t src = qs[2 * sb + (ll >> 2)];
+        const uint32_t idx = ((src >> (8 * (ll & 3))) & 0xFFu) | (((qh >> (8 * sb + ll)) & 1u) << 8);
+        const uint32_t g = grid[idx];
+        const uint32_t m = signtab[(sg[sb] >> (4 * ll)) & 0xFu];
+        const uint32_t w = (g ^ m) + (m & 0x01010101u);  // signed int8 x4
+        const float f0 = __fmul_rn(db, float(int8_t(w)));
+        const float f1 = __fmul_rn(db, float(int8_t(w >> 8)));
+        const float f2 = __fmul_rn(db, float(int8_t(w >> 16)));
+        const float f3 = __fmul_rn(db, float(int8_t(w >> 24)));
+        packed[2 * h] = pack_bf16(f0, f1);
+        packed[2 * h + 1] = pack_bf16(f2, f3);
+      }
+      const int c = 4 * sb + (l >> 1);
+      *reinterpret_cast<uint4*>(tile + swz(row, c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+  }
+}
+
+// IQ4_NL: K step kb covers blocks 2kb, 2kb+1 (32 weights each; low nibbles are elements 0..15).
+__device__ __forceinline__ void dequant_row_step_iq4nl(const uint8_t* row_bytes, int kb, uint8_t* tile, int row) {
+  const Iq4nlLevels lv = iq4nl_levels();
+#pragma unroll
+  for (int b = 0; b < 2; ++b) {
+    const uint8_t* blk = row_bytes + (2 * kb + b) * 18;
+    const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(ldg16(blk))));
+    uint32_t qw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qw[i] = ldg16(blk + 2 + 4 * i) | (ldg16(blk + 4 + 4 * i) << 16);
+    int w[8];  // word e/2 holds levels of elements {e, e+16, e+1, e+17} (e even)
+    iq4nl_decode32(lv, qw, w);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {  // elements 16*half .. 16*half+15
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {      // 8 elements per 16-byte chunk
+        uint32_t packed[4];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const uint32_t ww = uint32_t(w[(8 * c2 + e) >> 1]);
+          const float f0 = __fmul_rn(d, float(int8_t(ww >> (8 * half))));
+          const float f1 = __fmul_rn(d, float(int8_t(ww >> (16 + 8 * half))));
+          packed[e >> 1] = pack_bf16(f0, f1);
+        }
+        const int c = 4 * b + 2 * half + c2;
+        *reinterpret_cast<uint4*>(tile + swz(row, c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ route
+// Top-10 per token (one warp each), per-expert pair counts.
+__global__ void __launch_bounds__(256) pf_topk_kernel(const float* __restrict__ logits, int stride, int T,
+                                                      int32_t* __restrict__ topk_e, float* __restrict__ topk_w,
+                                                      int32_t* __restrict__ count) {
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  int ids[kTopK];
+  float w[kTopK];
+  warp_topk10([&](int e) { return logits[size_t(t) * stride + e]; }, ids, w);
+  if (lane < kTopK) {
+    int id = 0;
+    float wt = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k)
+      if (lane == k) {
+        id = ids[k];
+        wt = w[k];
+      }
+    topk_e[t * kTopK + lane] = id;
+    topk_w[t * kTopK + lane] = wt;
+    atomicAdd(&count[id], 1);
+  }
+}
+
+// Exclusive scan of the counts and the unit lists of both grouped GEMMs (one block of 512).
+// unit = {expert, first row of the 128-row weight tile, first pair, tokens in this unit}.
+__global__ void __launch_bounds__(512) pf_scan_kernel(const int32_t* __restrict__ count, int32_t* __restrict__ offset,
+                                                      int32_t* __restrict__ cursor, int4* __restrict__ units_gu,
+                                                      int4* __restrict__ units_dn, int32_t* __restrict__ meta,
+                                                      int inter, int max_units_gu, int max_units_dn) {
+  __shared__ int s_scan[16];
+  __shared__ int s_tiles[16];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c = count[tid];
+  const int tiles = (c + kTileN - 1) / kTileN;
+  int ic = c, it = tiles;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, ic, o), b = __shfl_up_sync(0xffffffffu, it, o);
+    if (lane >= o) {
+      ic += a;
+      it += b;
+    }
+  }
+  if (lane == 31) {
+    s_scan[warp] = ic;
+    s_tiles[warp] = it;
+  }
+  __syncthreads();
+  int bc = 0, bt = 0, tot_c = 0, tot_t = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (i < warp) {
+      bc += s_scan[i];
+      bt += s_tiles[i];
+    }
+    tot_c += s_scan[i];
+    tot_t += s_tiles[i];
+  }
+  const int off = bc + ic - c, tile0 = bt + it - tiles;
+  offset[tid] = off;
+  cursor[tid] = 0;
+  if (tid == 0) {
+    offset[kExperts] = tot_c;
+    meta[0] = min(tot_t * (inter / kTileM), max_units_gu);
+    meta[1] = min(tot_t * (H / kTileM), max_units_dn);
+    meta[2] = tot_c;
+  }
+  const int mg = inter / kTileM, md = H / kTileM;
+  for (int t = 0; t < tiles; ++t) {
+    const int p0 = off + t * kTileN, nt = min(kTileN, c - t * kTileN);
+    for (int m = 0; m < mg; ++m) {
+      const int u = (tile0 + t) * mg + m;
+      if (u < max_units_gu) units_gu[u] = make_int4(tid, m * kTileM, p0, nt);
+    }
+    for (int m = 0; m < md; ++m) {
+      const int u = (tile0 + t) * md + m;
+      if (u < max_units_dn) units_dn[u] = make_int4(tid, m * kTileM, p0, nt);
+    }
+  }
+}
+
+// Pairs grouped by expert. The order inside an expert depends on the atomics, the results do not:
+// every pair's h and y rows depend only on (token, expert) and the combine adds a token's ten rows
+// in ascending-expert order.
+__global__ void __launch_bounds__(256) pf_scatter_kernel(const int32_t* __restrict__ topk_e,
+                                                         const float* __restrict__ topk_w,
+                                                         const int32_t* __restrict__ offset, int32_t* __restrict__ cursor,
+                                                         int32_t* __restrict__ pair_token, float* __restrict__ pair_weight,
+                                                         int32_t* __restrict__ token_pair, int T) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i >= T * kTopK) return;
+  const int e = topk_e[i];
+  const int pos = offset[e] + atomicAdd(&cursor[e], 1);
+  pair_token[pos] = i / kTopK;
+  pair_weight[pos] = topk_w[i];
+  token_pair[i] = pos;
+}
+
+// ------------------------------------------------------------------------------ grouped gate/up
+struct GuBars {
+  uint64_t full[kStagesGU];
+  uint64_t empty[kStagesGU];
+  uint64_t tmem_full;
+  uint64_t tmem_empty;
+  uint32_t tmem_base;
+  int abort;
+};
+constexpr int kGuStage = 2 * kTileA + kTileB;                       // 64 KB
+constexpr int kGuSmem = kStagesGU * kGuStage + 2048 + 64 + sizeof(GuBars) + 1024;
+constexpr int kGuThreads = 15 * 32;  // warp 0 MMA, 1-2 gather, 3-10 dequant, 11-14 epilogue
+
+template <int FMT>
+__global__ void __launch_bounds__(kGuThreads, 1)
+grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ expert_blob,
+                       const __nv_bfloat16* __restrict__ x, const int4* __restrict__ units,
+                       const int32_t* __restrict__ meta, const int32_t* __restrict__ pair_token,
+                       __nv_bfloat16* __restrict__ h, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  uint32_t* grid = reinterpret_cast<uint32_t*>(smem + kStagesGU * kGuStage);
+  uint32_t* signtab = grid + 512;
+  GuBars* bars = reinterpret_cast<GuBars*>(reinterpret_cast<uint8_t*>(signtab) + 64);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int I = L.inter;
+  const int n_units = meta[0];
+  const int row_bytes = FMT == FB_FMT_IQ3_S ? 1100 : 1440;
+  const Abort ab{&bars->abort, status};
+
+  for (int i = tid; i < 512; i += kGuThreads) grid[i] = iq3s_grid_entry(i);
+  if (tid < 16) {
+    uint32_t m = 0;
+    for (int j = 0; j < 4; ++j)
+      if (tid & (1 << j)) m |= 0xFFu << (8 * j);
+    signtab[tid] = m;
+  }
+  if (tid == 0) {
+    for (int i = 0; i < kStagesGU; ++i) {
+      mbar_init(&bars->full[i], 10);  // 2 gather warps + 8 dequant warps
+      mbar_init(&bars->empty[i], 1);
+    }
+    mbar_init(&bars->tmem_full, 1);
+    mbar_init(&bars->tmem_empty, 4);
+    bars->abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(&bars->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  constexpr int kSteps = H / kBK;  // 40
+
+  if (warp == 0) {
+    // ---------------- MMA issuer: gate accumulator in columns [0,256), up in [256,512)
+    if (lane == 0) {
+      uint32_t it = 0, ul = 0;
+      for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++ul) {
+        const int4 un = units[u];
+        const int n = (un.w + 15) & ~15;
+        const uint32_t idesc = idesc_bf16(n);
+        if (!ab.wait(&bars->tmem_empty, (ul & 1) ^ 1)) break;
+        tc_fence_after();
+        bool ok = true;
+        for (int kb = 0; kb < kSteps; ++kb, ++it) {
+          const int s = it % kStagesGU;
+          if (!ab.wait(&bars->full[s], (it / kStagesGU) & 1)) { ok = false; break; }
+          tc_fence_after();
+          uint8_t* st = ring + s * kGuStage;
+          const uint64_t dg = umma_desc_k128(smem_u32(st)), du = umma_desc_k128(smem_u32(st + kTileA));
+          const uint64_t db = umma_desc_k128(smem_u32(st + 2 * kTileA));
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {  // 16 bf16 = 32 bytes of K per instruction
+            umma_bf16(tmem_base, dg + uint64_t(2 * k4), db + uint64_t(2 * k4), idesc, (kb | k4) ? 1u : 0u);
+            umma_bf16(tmem_base + 256u, du + uint64_t(2 * k4), db + uint64_t(2 * k4), idesc, (kb | k4) ? 1u : 0u);
+          }
+          umma_commit(&bars->empty[s]);
+        }
+        if (!ok) break;
+        umma_commit(&bars->tmem_full);
+      }
+    }
+  } else if (warp <= 2) {
+    // ---------------- token-row gather: 256 rows x 128 bytes per K step, 16-byte cp.async each.
+    // Thread tg copies chunk (tg & 7) of rows 8i + (tg >> 3), i < 32; it keeps those 32 token ids
+    // in registers for the whole unit.
+    const int tg = tid - 32;  // 0..63
+    const int c = tg & 7, nbase = tg >> 3;
+    uint32_t it = 0;
+    int pending = -1;  // stage whose copies are committed but not yet published
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+      const int4 un = units[u];
+      int tok[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int n = 8 * i + nbase;
+        tok[i] = n < un.w ? pair_token[un.z + n] : -1;
+      }
+      bool ok = true;
+      for (int kb = 0; kb < kSteps; ++kb, ++it) {
+        const int s = it % kStagesGU;
+        if (!ab.wait(&bars->empty[s], ((it / kStagesGU) & 1) ^ 1)) { ok = false; break; }
+        uint8_t* tb = ring + s * kGuStage + 2 * kTileA;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int n = 8 * i + nbase;
+          if (tok[i] >= 0) cp_async16(tb + swz(n, c), x + size_t(tok[i]) * H + kb * kBK + c * 8);
+        }
+        cp_async_commit();
+        if (pending >= 0) {  // the previous stage's copies have landed once only one group is in flight
+          cp_async_wait<1>();
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->full[pending]);
+        }
+        pending = s;
+      }
+      if (!ok) break;
+    }
+    if (pending >= 0) {
+      cp_async_wait<0>();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->full[pending]);
+    }
+  } else if (warp <= 10) {
+    // ---------------- dequant: thread = (matrix, weight row)
+    const int td = tid - 96, mat = td >> 7, row = td & 127;
+    uint32_t it = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+      const int4 un = units[u];
+      const uint8_t* blob = expert_blob ? expert_blob[un.x] : L.slots + int64_t(un.x) * L.blob_stride;
+      const uint8_t* rowp = blob + (mat ? L.up_offset : L.gate_offset) + size_t(un.y + row) * row_bytes;
+      bool ok = true;
+      for (int kb = 0; kb < kSteps; ++kb, ++it) {
+        const int s = it % kStagesGU;
+        if (!ab.wait(&bars->empty[s], ((it / kStagesGU) & 1) ^ 1)) { ok = false; break; }
+        uint8_t* ta = ring + s * kGuStage + mat * kTileA;
+        if constexpr (FMT == FB_FMT_IQ3_S) dequant_row_step_iq3s(rowp, kb, grid, signtab, ta, row);
+        else dequant_row_step_iq4nl(rowp, kb, ta, row);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->full[s]);
+      }
+      if (!ok) break;
+    }
+  } else {
+    // ---------------- epilogue: lane quarter = warp % 4; thread = intermediate row j
+    const int q = warp & 3;
+    uint32_t ul = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++ul) {
+      const int4 un = units[u];
+      if (!ab.wait(&bars->tmem_full, ul & 1)) break;
+      tc_fence_after();
+      const int j = un.y + q * 32 + lane;
+      for (int c0 = 0; c0 < un.w; c0 += 32) {
+        uint32_t g[32], up[32];
+        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c0), g);
+        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(256 + c0), up);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (c0 + i < un.w) {
+            const float gv = __uint_as_float(g[i]), uv = __uint_as_float(up[i]);
+            const float hv = (gv / (1.0f + expf(-gv))) * uv;
+            h[size_t(un.z + c0 + i) * I + j] = __float2bfloat16_rn(hv);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tmem_empty);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------ grouped down
+struct DnBars {
+  uint64_t full[kStagesDN];
+  uint64_t empty[kStagesDN];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort;
+};
+constexpr int kDnStage = kTileA + kTileB;  // 48 KB
+constexpr int kDnSmem = kStagesDN * kDnStage + 2048 + 64 + sizeof(DnBars) + 1024;
+constexpr int kDnThreads = 10 * 32;  // warp 0 MMA, warp 1 TMA, 2-5 dequant, 6-9 epilogue
+
+// yp[pair][n] = w_pair * (down_n . h[pair])
+template <int FMT>
+__global__ void __launch_bounds__(kDnThreads, 1)
+grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ expert_blob,
+                    const __grid_constant__ CUtensorMap map_h, const int4* __restrict__ units,
+                    const int32_t* __restrict__ meta, const float* __restrict__ pair_weight, float* __restrict__ yp,
+                    uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  uint32_t* grid = reinterpret_cast<uint32_t*>(smem + kStagesDN * kDnStage);
+  uint32_t* signtab = grid + 512;
+  DnBars* bars = reinterpret_cast<DnBars*>(reinterpret_cast<uint8_t*>(signtab) + 64);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int I = L.inter;
+  const int n_units = meta[1];
+  const int row_bytes = FMT == FB_FMT_IQ3_S ? I / 256 * 110 : I / 32 * 18;
+  const int k_steps = I / kBK;
+  const Abort ab{&bars->abort, status};
+
+  for (int i = tid; i < 512; i += kDnThreads) grid[i] = iq3s_grid_entry(i);
+  if (tid < 16) {
+    uint32_t m = 0;
+    for (int j = 0; j < 4; ++j)
+      if (tid & (1 << j)) m |= 0xFFu << (8 * j);
+    signtab[tid] = m;
+  }
+  if (tid == 0) {
+    for (int i = 0; i < kStagesDN; ++i) {
+      mbar_init(&bars->full[i], 5);  // TMA thread (with its byte count) + 4 dequant warps
+      mbar_init(&bars->empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->tmem_full[i], 1);
+      mbar_init(&bars->tmem_empty[i], 4);
+    }
+    bars->abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(&bars->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0, ul = 0;
+      for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++ul) {
+        const int4 un = units[u];
+        const uint32_t idesc = idesc_bf16((un.w + 15) & ~15);
+        const int acc = ul & 1;
+        if (!ab.wait(&bars->tmem_empty[acc], ((ul >> 1) & 1) ^ 1)) break;
+        tc_fence_after();
+        bool ok = true;
+        for (int kb = 0; kb < k_steps; ++kb, ++it) {
+          const int s = it % kStagesDN;
+          if (!ab.wait(&bars->full[s], (it / kStagesDN) & 1)) { ok = false; break; }
+          tc_fence_after();
+          uint8_t* st = ring + s * kDnStage;
+          const uint64_t da = umma_desc_k128(smem_u32(st)), db = umma_desc_k128(smem_u32(st + kTileA));
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            umma_bf16(tmem_base + uint32_t(acc * 256), da + uint64_t(2 * k4), db + uint64_t(2 * k4), idesc,
+                      (kb | k4) ? 1u : 0u);
+          umma_commit(&bars->empty[s]);
+        }
+        if (!ok) break;
+        umma_commit(&bars->tmem_full[acc]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- h rows of the unit's pairs: expert-sorted, so one TMA box per K step
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+        const int4 un = units[u];
+        bool ok = true;
+        for (int kb = 0; kb < k_steps; ++kb, ++it) {
+          const int s = it % kStagesDN;
+          if (!ab.wait(&bars->empty[s], ((it / kStagesDN) & 1) ^ 1)) { ok = false; break; }
+          mbar_expect_tx(&bars->full[s], kTileB);
+          tma_load_2d(ring + s * kDnStage + kTileA, &map_h, kb * kBK, un.z, &bars->full[s]);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp <= 5) {
+    const int row = tid - 64;
+    uint32_t it = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+      const int4 un = units[u];
+      const uint8_t* blob = expert_blob ? expert_blob[un.x] : L.slots + int64_t(un.x) * L.blob_stride;
+      const uint8_t* rowp = blob + L.down_offset + size_t(un.y + row) * row_bytes;
+      bool ok = true;
+      for (int kb = 0; kb < k_steps; ++kb, ++it) {
+        const int s = it % kStagesDN;
+        if (!ab.wait(&bars->empty[s], ((it / kStagesDN) & 1) ^ 1)) { ok = false; break; }
+        uint8_t* ta = ring + s * kDnStage;
+        if constexpr (FMT == FB_FMT_IQ3_S) dequant_row_step_iq3s(rowp, kb, grid, signtab, ta, row);
+        else dequant_row_step_iq4nl(rowp, kb, ta, row);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->full[s]);
+      }
+      if (!ok) break;
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t ul = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++ul) {
+      const int4 un = units[u];
+      const int acc = ul & 1;
+      if (!ab.wait(&bars->tmem_full[acc], (ul >> 1) & 1)) break;
+      tc_fence_after();
+      const int n = un.y + q * 32 + lane;
+      for (int c0 = 0; c0 < un.w; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * 256 + c0), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c0 + i < un.w) yp[size_t(un.z + c0 + i) * H + n] = pair_weight[un.z + c0 + i] * __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------ combine
+// y[t][n] = sum over token t's ten pairs, in ascending expert id, of yp[pair][n] (+ shared);
+// X[t][s][n] += inj[t][s] * y when X is given.
+__global__ void __launch_bounds__(256) pf_combine_kernel(const int32_t* __restrict__ topk_e,
+                                                         const int32_t* __restrict__ token_pair,
+                                                         const float* __restrict__ yp, const float* __restrict__ y_shared,
+                                                         const float* __restrict__ inj, float* __restrict__ X,
+                                                         float* __restrict__ y_out) {
+  const int t = blockIdx.y;
+  __shared__ int s_order[kTopK];
+  if (threadIdx.x < kTopK) {
+    const int e = topk_e[t * kTopK + threadIdx.x];
+    int rank = 0;
+    for (int k = 0; k < kTopK; ++k) rank += topk_e[t * kTopK + k] < e ? 1 : 0;
+    s_order[rank] = token_pair[t * kTopK + threadIdx.x];
+  }
+  __syncthreads();
+  const int n = blockIdx.x * 256 + threadIdx.x;
+  float y = 0.0f;
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) y += yp[size_t(s_order[k]) * H + n];
+  if (y_shared) y += y_shared[size_t(t) * H + n];
+  if (y_out) y_out[size_t(t) * H + n] = y;
+  if (X) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s) X[(size_t(t) * 4 + s) * H + n] += inj[t * 4 + s] * y;
+  }
+}
+
+// ------------------------------------------------------------------------------ host
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+size_t up256(size_t v) { return (v + 255) & ~size_t(255); }
+int max_units(int capacity, int tiles_per_group) {
+  return (capacity * kTopK / kTileN + kExperts) * tiles_per_group;
+}
+
+struct PfLayout {
+  size_t meta, count, offset, cursor, topk_e, topk_w, pair_token, pair_weight, token_pair, units_gu, units_dn, h, yp,
+      status, total;
+};
+PfLayout pf_layout(int capacity, int inter) {
+  PfLayout l;
+  size_t o = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = o;
+    o = up256(o + bytes);
+    return at;
+  };
+  const size_t pairs = size_t(capacity) * kTopK;
+  l.meta = take(64);
+  l.count = take(kExperts * 4);
+  l.offset = take((kExperts + 1) * 4);
+  l.cursor = take(kExperts * 4);
+  l.topk_e = take(pairs * 4);
+  l.topk_w = take(pairs * 4);
+  l.pair_token = take(pairs * 4);
+  l.pair_weight = take(pairs * 4);
+  l.token_pair = take(pairs * 4);
+  l.units_gu = take(size_t(max_units(capacity, inter / kTileM)) * 16);
+  l.units_dn = take(size_t(max_units(capacity, H / kTileM)) * 16);
+  l.h = take((pairs + kTileN) * size_t(inter) * 2);  // + one tile so a TMA box never leaves the buffer
+  l.yp = take(pairs * size_t(H) * 4);
+  l.status = take(64);
+  l.total = o;
+  return l;
+}
+
+bool pf_layout_ok(const fb_moe_expert_layout* L, const void* table) {
+  if (!L || (!L->slots && !table)) return false;
+  if ((uintptr_t(L->blob_stride) | uintptr_t(L->gate_offset) | uintptr_t(L->up_offset) | uintptr_t(L->down_offset)) & 1)
+    return false;
+  if (L->inter != 512 && L->inter != 640) return false;
+  if (L->gate_up_format != FB_FMT_IQ3_S && L->gate_up_format != FB_FMT_IQ4_NL) return false;
+  if (L->down_format == FB_FMT_IQ3_S) return L->inter % 256 == 0;
+  return L->down_format == FB_FMT_IQ4_NL;
+}
+
+bool pf_ws_ok(const fb_moe_prefill_workspace* ws, int tokens) {
+  return ws && ws->meta && ws->h && ws->yp && ws->units_gate_up && ws->units_down && tokens >= 1 &&
+         tokens <= ws->capacity;
+}
+
+}  // namespace
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" {
+
+size_t fb_moe_prefill_workspace_bytes(int32_t capacity, int32_t inter) {
+  if (capacity < 1 || (inter != 512 && inter != 640)) return 0;
+  return pf_layout(capacity, inter).total;
+}
+
+int32_t fb_moe_prefill_workspace_make(void* base, int32_t capacity, int32_t inter, fb_moe_prefill_workspace* out) {
+  if (!base || !out || (reinterpret_cast<uintptr_t>(base) & 255) || capacity < 1 || (inter != 512 && inter != 640))
+    return invalid("prefill_workspace_make: bad arguments (base 256-byte aligned, inter 512 or 640)");
+  const PfLayout l = pf_layout(capacity, inter);
+  uint8_t* b = static_cast<uint8_t*>(base);
+  out->capacity = capacity;
+  out->inter = inter;
+  out->max_units_gate_up = max_units(capacity, inter / kTileM);
+  out->max_units_down = max_units(capacity, H / kTileM);
+  out->meta = reinterpret_cast<int32_t*>(b + l.meta);
+  out->expert_count = reinterpret_cast<int32_t*>(b + l.count);
+  out->expert_offset = reinterpret_cast<int32_t*>(b + l.offset);
+  out->expert_cursor = reinterpret_cast<int32_t*>(b + l.cursor);
+  out->topk_expert = reinterpret_cast<int32_t*>(b + l.topk_e);
+  out->topk_weight = reinterpret_cast<float*>(b + l.topk_w);
+  out->pair_token = reinterpret_cast<int32_t*>(b + l.pair_token);
+  out->pair_weight = reinterpret_cast<float*>(b + l.pair_weight);
+  out->token_pair = reinterpret_cast<int32_t*>(b + l.token_pair);
+  out->units_gate_up = b + l.units_gu;
+  out->units_down = b + l.units_dn;
+  out->h = b + l.h;
+  out->yp = reinterpret_cast<float*>(b + l.yp);
+  out->status = reinterpret_cast<uint32_t*>(b + l.status);
+  return 0;
+}
+
+int32_t fb_moe_route(const float* router_logits, int32_t logits_stride, const void* x, const uint8_t* const* expert_blob,
+                     int32_t layer, const uint32_t* seq, void* control, int32_t tokens,
+                     const fb_moe_prefill_workspace* ws, void* stream) {
+  (void)x;
+  (void)expert_blob;
+  (void)layer;
+  (void)seq;
+  if (control) return invalid("route: no CPU expert tier exists behind these kernels; control must be NULL");
+  if (!router_logits || logits_stride < kExperts || !pf_ws_ok(ws, tokens)) return invalid("route: bad arguments");
+  cudaStream_t s = as_stream(stream);
+  cudaError_t e = cudaMemsetAsync(ws->expert_count, 0, kExperts * 4, s);
+  if (e != cudaSuccess) return check_launch("route: memset");
+  pf_topk_kernel<<<(tokens + 7) / 8, 256, 0, s>>>(router_logits, logits_stride, tokens, ws->topk_expert, ws->topk_weight,
+                                                  ws->expert_count);
+  pf_scan_kernel<<<1, 512, 0, s>>>(ws->expert_count, ws->expert_offset, ws->expert_cursor,
+                                   static_cast<int4*>(ws->units_gate_up), static_cast<int4*>(ws->units_down), ws->meta,
+                                   ws->inter, ws->max_units_gate_up, ws->max_units_down);
+  pf_scatter_kernel<<<(tokens * kTopK + 255) / 256, 256, 0, s>>>(ws->topk_expert, ws->topk_weight, ws->expert_offset,
+                                                                 ws->expert_cursor, ws->pair_token, ws->pair_weight,
+                                                                 ws->token_pair, tokens);
+  return check_launch("route");
+}
+
+int32_t fb_moe_grouped_gate_up(const fb_moe_expert_layout* layout, const uint8_t* const* expert_blob, const void* x_bf16,
+                               int32_t tokens, const fb_moe_prefill_workspace* ws, void* stream) {
+  if (!pf_layout_ok(layout, expert_blob) || !x_bf16 || !pf_ws_ok(ws, tokens) || layout->inter != ws->inter ||
+      (reinterpret_cast<uintptr_t>(x_bf16) & 15))
+    return invalid("grouped_gate_up: bad arguments");
+  static bool once = [] {
+    cudaFuncSetAttribute(grouped_gate_up_kernel<FB_FMT_IQ3_S>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGuSmem);
+    cudaFuncSetAttribute(grouped_gate_up_kernel<FB_FMT_IQ4_NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGuSmem);
+    return true;
+  }();
+  (void)once;
+  const int grid = sm_count();
+  const auto* xb = static_cast<const __nv_bfloat16*>(x_bf16);
+  auto* hb = static_cast<__nv_bfloat16*>(ws->h);
+  const auto* un = static_cast<const int4*>(ws->units_gate_up);
+  if (layout->gate_up_format == FB_FMT_IQ3_S)
+    grouped_gate_up_kernel<FB_FMT_IQ3_S><<<grid, kGuThreads, kGuSmem, as_stream(stream)>>>(
+        *layout, expert_blob, xb, un, ws->meta, ws->pair_token, hb, ws->status);
+  else
+    grouped_gate_up_kernel<FB_FMT_IQ4_NL><<<grid, kGuThreads, kGuSmem, as_stream(stream)>>>(
+        *layout, expert_blob, xb, un, ws->meta, ws->pair_token, hb, ws->status);
+  return check_launch("grouped_gate_up");
+}
+
+int32_t fb_moe_grouped_down(const fb_moe_expert_layout* layout, const uint8_t* const* expert_blob, int32_t tokens,
+                            const fb_moe_prefill_workspace* ws, void* stream) {
+  if (!pf_layout_ok(layout, expert_blob) || !pf_ws_ok(ws, tokens) || layout->inter != ws->inter)
+    return invalid("grouped_down: bad arguments");
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) {
+    set_error("grouped_down: cuTensorMapEncodeTiled is not available");
+    return int32_t(cudaErrorNotSupported);
+  }
+  // h as a 2-D bf16 tensor [pairs + one tile][inter]; boxes of 64 x 256, 128-byte swizzle
+  CUtensorMap map_h;
+  const cuuint64_t dims[2] = {cuuint64_t(ws->inter), cuuint64_t(size_t(ws->capacity) * kTopK + kTileN)};
+  const cuuint64_t strides[1] = {cuuint64_t(ws->inter) * 2};
+  const cuuint32_t box[2] = {cuuint32_t(kBK), cuuint32_t(kTileN)};
+  const cuuint32_t elem[2] = {1, 1};
+  if (fn(&map_h, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ws->h, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+    set_error("grouped_down: cuTensorMapEncodeTiled failed");
+    return int32_t(cudaErrorInvalidValue);
+  }
+  static bool once = [] {
+    cudaFuncSetAttribute(grouped_down_kernel<FB_FMT_IQ3_S>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDnSmem);
+    cudaFuncSetAttribute(grouped_down_kernel<FB_FMT_IQ4_NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDnSmem);
+    return true;
+  }();
+  (void)once;
+  const int grid = sm_count();
+  const auto* un = static_cast<const int4*>(ws->units_down);
+  if (layout->down_format == FB_FMT_IQ3_S)
+    grouped_down_kernel<FB_FMT_IQ3_S><<<grid, kDnThreads, kDnSmem, as_stream(stream)>>>(
+        *layout, expert_blob, map_h, un, ws->meta, ws->pair_weight, ws->yp, ws->status);
+  else
+    grouped_down_kernel<FB_FMT_IQ4_NL><<<grid, kDnThreads, kDnSmem, as_stream(stream)>>>(
+        *layout, expert_blob, map_h, un, ws->meta, ws->pair_weight, ws->yp, ws->status);
+  return check_launch("grouped_down");
+}
+
+int32_t fb_moe_prefill_combine(const fb_moe_prefill_workspace* ws, const float* y_shared, void* control, int32_t layer,
+                               const uint32_t* seq, const float* inj, float* X, float* y_out, int32_t tokens,
+                               long long timeout_cycles, const float* ablate_direction, float ablate_scale,
+                               void* stream) {
+  (void)layer;
+  (void)seq;
+  (void)timeout_cycles;
+  (void)ablate_scale;
+  if (control) return invalid("prefill_combine: no CPU expert tier exists behind these kernels; control must be NULL");
+  if (ablate_direction) return invalid("prefill_combine: the rank-1 ablation is not built for the prefill path");
+  if (!pf_ws_ok(ws, tokens) || (X && !inj) || (!X && !y_out)) return invalid("prefill_combine: bad arguments");
+  pf_combine_kernel<<<dim3(H / 256, tokens), 256, 0, as_stream(stream)>>>(ws->topk_expert, ws->token_pair, ws->yp,
+                                                                        y_shared, inj, X, y_out);
+  return check_launch("prefill_combine");
+}
+
+}  // extern "C"

@@ -45,6 +45,15 @@ class DecodeWorkspace(C.Structure):
                 ("reserved", C.c_int32)]
 
 
+class PrefillWorkspace(C.Structure):
+    _fields_ = [("capacity", C.c_int32), ("inter", C.c_int32), ("max_units_gate_up", C.c_int32),
+                ("max_units_down", C.c_int32), ("meta", C.c_void_p), ("expert_count", C.c_void_p),
+                ("expert_offset", C.c_void_p), ("expert_cursor", C.c_void_p), ("topk_expert", C.c_void_p),
+                ("topk_weight", C.c_void_p), ("pair_token", C.c_void_p), ("pair_weight", C.c_void_p),
+                ("token_pair", C.c_void_p), ("units_gate_up", C.c_void_p), ("units_down", C.c_void_p),
+                ("h", C.c_void_p), ("yp", C.c_void_p), ("status", C.c_void_p)]
+
+
 _P = C.c_void_p
 _I32, _I64 = C.c_int32, C.c_int64
 _SIGNATURES = {
@@ -68,6 +77,13 @@ _SIGNATURES = {
     "fb_moe_layer_decode": (_I32, [_P, C.POINTER(ExpertLayout), _P, _I32, _I32, C.POINTER(DecodeWorkspace), _P, _P, _P]),
     "fb_moe_layer_decode_host": (_I32, [_P, C.POINTER(ExpertLayout), _P, _I32, _I32, C.POINTER(DecodeWorkspace), _P,
                                         _P, _P, _P, _P]),
+    "fb_moe_prefill_workspace_bytes": (C.c_size_t, [_I32, _I32]),
+    "fb_moe_prefill_workspace_make": (_I32, [_P, _I32, _I32, C.POINTER(PrefillWorkspace)]),
+    "fb_moe_route": (_I32, [_P, _I32, _P, _P, _I32, _P, _P, _I32, C.POINTER(PrefillWorkspace), _P]),
+    "fb_moe_grouped_gate_up": (_I32, [C.POINTER(ExpertLayout), _P, _P, _I32, C.POINTER(PrefillWorkspace), _P]),
+    "fb_moe_grouped_down": (_I32, [C.POINTER(ExpertLayout), _P, _I32, C.POINTER(PrefillWorkspace), _P]),
+    "fb_moe_prefill_combine": (_I32, [C.POINTER(PrefillWorkspace), _P, _P, _I32, _P, _P, _P, _P, _I32, C.c_longlong, _P,
+                                      C.c_float, _P]),
     "fb_moe_layer_decode_ep": (_I32, [_P, C.POINTER(ExpertLayout), _P, _P, _I32, _I32, C.POINTER(DecodeWorkspace), _P, _P,
                                _P]),
     "fb_ep_sum_ranks": (_I32, [_P, _I32, _I32, _P, _P]),

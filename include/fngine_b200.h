@@ -174,6 +174,59 @@ int32_t fb_moe_layer_decode_host(const void* router_w_bf16, const fb_moe_expert_
                                  int32_t x_dtype, int32_t tokens, const fb_moe_decode_workspace* ws,
                                  float* logits_scratch, void* x_dev, float* y_dev, float* y_host, void* stream);
 
+/* ---------------------------------------------------------------- prefill (eager, T up to the workspace capacity)
+ * MoePrefillWorkspace, src/kernels/moe/moe.h:167-184. Differences: the work list holds the units
+ * of both grouped GEMMs ({expert, first weight row of a 128-row tile, first pair, tokens}, up to 256
+ * tokens per unit) instead of 64-token tiles; the per-pair results go to `yp` (fp32, routing weight
+ * applied) and the combine adds a token's ten rows in ascending-expert order, which replaces the
+ * reference's 64-bit fixed-point atomics (moe.h:186-192) as the mechanism that makes the prefill sum
+ * independent of scheduling; `token_pair` maps (token, rank) to its pair. */
+typedef struct fb_moe_prefill_workspace {
+  int32_t capacity;
+  int32_t inter;
+  int32_t max_units_gate_up;
+  int32_t max_units_down;
+  int32_t* meta;          /* [0] gate/up units [1] down units [2] pairs */
+  int32_t* expert_count;  /* [512] */
+  int32_t* expert_offset; /* [513] */
+  int32_t* expert_cursor; /* [512] */
+  int32_t* topk_expert;   /* [capacity][10] */
+  float* topk_weight;     /* [capacity][10] */
+  int32_t* pair_token;    /* [capacity*10] pairs grouped by expert */
+  float* pair_weight;     /* [capacity*10] */
+  int32_t* token_pair;    /* [capacity][10] */
+  void* units_gate_up;    /* int4 [max_units_gate_up] */
+  void* units_down;       /* int4 [max_units_down] */
+  void* h;                /* bf16 [capacity*10 + 256][inter] */
+  float* yp;              /* [capacity*10][2560] */
+  uint32_t* status;       /* FB_STATUS_* */
+} fb_moe_prefill_workspace;
+
+/* moe_prefill_workspace_bytes / make_moe_prefill_workspace, src/kernels/moe/moe.h:193-194. */
+size_t fb_moe_prefill_workspace_bytes(int32_t capacity, int32_t inter);
+int32_t fb_moe_prefill_workspace_make(void* base, int32_t capacity, int32_t inter, fb_moe_prefill_workspace* out);
+/* moe_route, src/kernels/moe/moe.h:201-204: top-10 for `tokens` tokens, per-expert pair lists, unit
+ * lists. `control` must be NULL (no CPU tier); x and expert_blob are accepted for signature parity
+ * and not read (every expert is resident). */
+int32_t fb_moe_route(const float* router_logits, int32_t logits_stride, const void* x, const uint8_t* const* expert_blob,
+                     int32_t layer, const uint32_t* seq, void* control, int32_t tokens,
+                     const fb_moe_prefill_workspace* ws, void* stream);
+/* moe_grouped_gate_up, src/kernels/moe/moe.h:209-211: h[pair] = bf16(silu(gate . x) * (up . x)), x bf16
+ * [tokens][2560]. `expert_blob` is the device table of blob addresses ([512]) or NULL to address
+ * expert e at layout->slots + e * blob_stride. */
+int32_t fb_moe_grouped_gate_up(const fb_moe_expert_layout* layout, const uint8_t* const* expert_blob, const void* x_bf16,
+                               int32_t tokens, const fb_moe_prefill_workspace* ws, void* stream);
+/* moe_grouped_down, src/kernels/moe/moe.h:213-214: yp[pair] = w_pair * (down . h[pair]). */
+int32_t fb_moe_grouped_down(const fb_moe_expert_layout* layout, const uint8_t* const* expert_blob, int32_t tokens,
+                            const fb_moe_prefill_workspace* ws, void* stream);
+/* moe_prefill_combine, src/kernels/moe/moe.h:221-226: y[t] = sum of token t's pair rows (ascending
+ * expert id) + y_shared[t]; X[t][s] += inj[t][s] * y[t]; y_out optional. `control` must be NULL; the
+ * rank-1 ablation is not built for this path (ablate_direction must be NULL). */
+int32_t fb_moe_prefill_combine(const fb_moe_prefill_workspace* ws, const float* y_shared, void* control, int32_t layer,
+                               const uint32_t* seq, const float* inj, float* X, float* y_out, int32_t tokens,
+                               long long timeout_cycles, const float* ablate_direction, float ablate_scale,
+                               void* stream);
+
 /* ---------------------------------------------------------------- expert parallel (no reference counterpart)
  * The reference is single-GPU. Here the 512 experts of a layer are sharded over the ranks of one
  * node; a rank's slot array holds only its own experts and `slot_of[e]` is the local slot of expert

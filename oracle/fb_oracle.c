@@ -503,6 +503,20 @@ void fbo_expert_ffn_bf16(int fmt_gu, int fmt_down, int hidden, int inter, const 
   free(hb);
 }
 
+// The down projection alone in the prefill numerics, from given bf16 h rows (raw bits): lets a test
+// separate "h is within one bf16 step" from "the down GEMM is right for the h it was given", as the
+// reference's own prefill test does (tests/kernels/moe/test_moe_experts.cpp:426-488).
+void fbo_down_bf16(int fmt_down, int hidden, int inter, const uint8_t* down, const uint16_t* h, int T,
+                   float* y_out) {
+  const int64_t rb = fbo_row_bytes(fmt_down, inter);
+  uint16_t* wd = (uint16_t*)malloc(sizeof(uint16_t) * (size_t)hidden * inter);
+  fbo_dequant_rows_bf16(fmt_down, down, rb, hidden, inter, wd);
+  for (int t = 0; t < T; ++t)
+    for (int n = 0; n < hidden; ++n)
+      y_out[(int64_t)t * hidden + n] = dot_bf16(wd + (size_t)n * inter, h + (int64_t)t * inter, inter);
+  free(wd);
+}
+
 // ---------------------------------------------------------------------------------- FP8 rows
 // E4M3FN code -> float: tests/common/test_util.h:105-112 (0x7F / 0xFF are NaN).
 float fbo_e4m3_to_float(uint8_t code) {

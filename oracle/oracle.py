@@ -65,6 +65,7 @@ def port():
         lib.fbo_expert_ffn.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         lib.fbo_expert_ffn_bf16.argtypes = lib.fbo_expert_ffn.argtypes
+        lib.fbo_down_bf16.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         lib.fbo_topk.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         lib.fbo_moe_layer.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_void_p,
                                       C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
@@ -217,6 +218,15 @@ def expert_ffn_bf16(fmt_gu, fmt_down, hidden, inter, blob, x_bf16, lib=None):
     fn = port().fbo_expert_ffn_bf16 if (lib is None or lib is port()) else lib.ref_expert_ffn_bf16
     fn(fmt_gu, fmt_down, hidden, inter, base, base + gb, base + 2 * gb, _ptr(x), T, _ptr(h), _ptr(y))
     return h, y
+
+
+def down_bf16(fmt_down, hidden, inter, down_bytes, h_bits):
+    """Prefill-numerics down projection of given bf16 h rows (uint16 [T][inter]) -> float32 [T][hidden]."""
+    down_bytes = np.ascontiguousarray(down_bytes, dtype=np.uint8)
+    h = np.ascontiguousarray(h_bits, dtype=np.uint16).reshape(-1, inter)
+    y = np.empty((h.shape[0], hidden), dtype=np.float32)
+    port().fbo_down_bf16(fmt_down, hidden, inter, _ptr(down_bytes), _ptr(h), h.shape[0], _ptr(y))
+    return y
 
 
 def topk(logits, k=10):

@@ -1,0 +1,140 @@
+"""GPU parity of the prefill MoE path (tcgen05 grouped GEMMs with in-kernel dequantization) against
+the CPU oracle in the reference's prefill numerics: bf16 weights (exactly dequantized, then rounded),
+bf16 activations, fp32 accumulation, h rounded to bf16 (src/cpu/iq_cpu.h:93-99,
+src/cpu/expert_pool.cpp:341-347,364-367,390-393 of the reference). Bars: router ids exact, weights
+1e-6; h equal to the oracle's bf16 h up to one bf16 step; y within 1e-3 relative L2 per token row."""
+import numpy as np
+import pytest
+
+from fngine_b200 import synth
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+IQ3_S, IQ4_NL, H = 21, 20, 2560
+
+
+def _torch():
+    import torch
+    assert torch.cuda.is_available()
+    return torch
+
+
+def rel_l2(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def oracle_prefill(fg, fd, inter, seed, x_bits, ids, w):
+    """y [T][H] and a dict expert -> (tokens, h bits) from the CPU oracle, pairs grouped by expert."""
+    T = ids.shape[0]
+    y_e = {}
+    h_e = {}
+    for e in sorted(set(ids.reshape(-1).tolist())):
+        toks = [t for t in range(T) if e in ids[t]]
+        blob = synth.expert_blob(fg, fd, inter, seed, e)
+        hb, ye = O.expert_ffn_bf16(fg, fd, H, inter, blob, x_bits[toks], lib=O.ref())
+        h_e[e] = (toks, hb)
+        for i, t in enumerate(toks):
+            y_e[(t, e)] = ye[i]
+    y = np.zeros((T, H), dtype=np.float32)
+    for t in range(T):
+        for e in sorted(ids[t].tolist()):  # ascending expert id
+            k = list(ids[t]).index(e)
+            y[t] = y[t] + np.float32(w[t, k]) * y_e[(t, e)]
+    return y, h_e
+
+
+def run_prefill(torch, layer, ws, logits, xd, T):
+    from fngine_b200 import prefill
+    y = torch.full((T, H), float("nan"), dtype=torch.float32, device="cuda")
+    prefill.moe_layer_prefill(logits, layer, xd, ws, y)
+    torch.cuda.synchronize()
+    return y
+
+
+def check_layer(fg, fd, inter, T, logits, seed=2024):
+    torch = _torch()
+    from fngine_b200 import moe, prefill
+    layer = moe.synth_layer(fg, fd, inter, 512, seed)
+    ws = prefill.PrefillWorkspace(max(T, 64), inter)
+    x = synth.activations(600 + T, T)
+    xb = synth.to_bf16_bits(x)
+    xd = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    ld = torch.from_numpy(logits).cuda()
+    y = run_prefill(torch, layer, ws, ld, xd, T).cpu().numpy()
+    assert ws.status() == 0
+    ids, w = O.topk(logits[:, :512])
+    got_ids = ws.ints(ws.ws.topk_expert, T * 10).reshape(T, 10)
+    got_w = ws.floats(ws.ws.topk_weight, T * 10).reshape(T, 10)
+    assert np.array_equal(got_ids, ids) and np.max(np.abs(got_w - w)) <= 1e-6
+    # pair lists: grouped by expert, every (token, rank) appears once
+    meta = ws.meta()
+    assert meta[2] == T * 10
+    off = ws.ints(ws.ws.expert_offset, 513)
+    ptok = ws.ints(ws.ws.pair_token, T * 10)
+    tpair = ws.ints(ws.ws.token_pair, T * 10).reshape(T, 10)
+    for t in range(T):
+        for k in range(10):
+            p = tpair[t, k]
+            assert off[ids[t, k]] <= p < off[ids[t, k] + 1] and ptok[p] == t
+    want, h_e = oracle_prefill(fg, fd, inter, seed, xb, ids, w)
+    # h rows: equal to the oracle's bf16 h up to one bf16 step (fp32 summation order and expf differ)
+    hg = synth.bf16_bits_to_f32(ws.h(T * 10))
+    worst = 0.0
+    for e, (toks, hb) in h_e.items():
+        href = synth.bf16_bits_to_f32(hb)
+        for i, t in enumerate(toks):
+            p = tpair[t, list(ids[t]).index(e)]
+            worst = max(worst, float(np.max(np.abs(hg[p] - href[i]) / (np.abs(href[i]) + 1e-2 * np.abs(href[i]).max()))))
+    assert worst <= 2 ** -7, worst
+    # down projection + combine: against the oracle's down GEMM fed with the GPU's own bf16 h, so
+    # that a legal one-step difference in h is not amplified into the y comparison
+    hbits = ws.h(T * 10)
+    gate_bytes = inter * O.row_bytes(fg, H)
+    y_dn = np.zeros((T, H), dtype=np.float32)
+    ye_cache = {}
+    for e in h_e:
+        toks = h_e[e][0]
+        rows = np.stack([hbits[tpair[t, list(ids[t]).index(e)]] for t in toks])
+        ye = O.down_bf16(fd, H, inter, synth.expert_blob(fg, fd, inter, seed, e)[2 * gate_bytes:], rows)
+        for i, t in enumerate(toks):
+            ye_cache[(t, e)] = ye[i]
+    for t in range(T):
+        for e in sorted(ids[t].tolist()):
+            y_dn[t] = y_dn[t] + np.float32(w[t, list(ids[t]).index(e)]) * ye_cache[(t, e)]
+    errs_dn = [rel_l2(y[t], y_dn[t]) for t in range(T)]
+    assert max(errs_dn) <= 1e-3, max(errs_dn)
+    # end to end against the all-CPU result: 1e-3 in the typical row; a row where a dominant h
+    # element sits on a bf16 rounding boundary may reach a few 1e-3 (the reference accepts the same
+    # one-step h differences in its prefill test)
+    errs = [rel_l2(y[t], want[t]) for t in range(T)]
+    assert float(np.median(errs)) <= 1e-3 and max(errs) <= 1e-2, (float(np.median(errs)), max(errs))
+    # deterministic: a second run is bitwise identical although pair order inside an expert may differ
+    y2 = run_prefill(torch, layer, ws, ld, xd, T).cpu().numpy()
+    assert np.array_equal(y2.view(np.uint32), y.view(np.uint32))
+    return max(errs_dn), max(errs)
+
+
+@pytest.mark.parametrize("T", [1, 3, 9, 64])
+def test_prefill_layer_small_batches(T):
+    logits = (synth.normal(31 + T, T * 512) * 1.5).astype(np.float32).reshape(T, 512)
+    err = check_layer(IQ3_S, IQ3_S, 512, T, logits)
+    print("prefill IQ3_S T=%d: max rel L2 down %.2e, end to end %.2e" % ((T,) + err))
+
+
+@pytest.mark.parametrize("fg,fd,inter", [(IQ4_NL, IQ4_NL, 512), (IQ3_S, IQ4_NL, 640)])
+def test_prefill_layer_other_formats(fg, fd, inter):
+    T = 40
+    logits = (synth.normal(77, T * 512) * 1.5).astype(np.float32).reshape(T, 512)
+    err = check_layer(fg, fd, inter, T, logits)
+    print("prefill fmt %d/%d inter %d: max rel L2 down %.2e, end to end %.2e" % ((fg, fd, inter) + err))
+
+
+def test_prefill_crowded_expert_spans_several_units():
+    """600 tokens, all of them routed to expert 7 (three 256-token units) plus nine others each."""
+    T = 600
+    logits = (synth.normal(5, T * 512) * 1.0).astype(np.float32).reshape(T, 512)
+    logits[:, 7] += 20.0
+    logits[::3, 300] += 10.0
+    err = check_layer(IQ3_S, IQ3_S, 512, T, logits)
+    print("prefill crowded expert: max rel L2 down %.2e, end to end %.2e" % err)
