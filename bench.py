@@ -213,6 +213,72 @@ def fp8_gemm_section(torch, iters=10):
     return res
 
 
+def prefill_section(torch, n_layers=48, tokens=8192, steps=2):
+    """The 48-layer routed-expert stack at prefill on one GPU: 8192 bf16 tokens, 512 IQ3_S experts per
+    layer (inter 512), top-10, router logits = bf16 projection (std 0.02) + a Zipf(1.1) popularity bias
+    over a seeded permutation of the experts (bias = -1.1 * 0.41 * ln(rank): with unit-variance logit noise
+    the factor 0.41 makes the fitted log-log slope of pairs against rank -1.1). Layer l+1's input is layer l's output scaled to unit RMS
+    per token. The router projection and that rescale are torch calls (they sit outside the path);
+    route / grouped gate-up / grouped down / combine are this library's kernels."""
+    from fngine_b200 import moe, prefill, synth
+    layers = [moe.synth_layer(FMT, FMT, INTER, EXPERTS, 5000 + l) for l in range(n_layers)]
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    routers = [(torch.randn(EXPERTS, HIDDEN, generator=g, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(n_layers)]
+    perm = torch.randperm(EXPERTS, generator=g, device="cuda")
+    bias = torch.empty(EXPERTS, device="cuda")
+    bias[perm] = -1.1 * 0.41 * torch.log(torch.arange(1, EXPERTS + 1, device="cuda", dtype=torch.float32))
+    x0 = torch.randn(tokens, HIDDEN, generator=g, device="cuda").to(torch.bfloat16)
+    ws = prefill.PrefillWorkspace(tokens, INTER)
+    y = torch.empty(tokens, HIDDEN, dtype=torch.float32, device="cuda")
+
+    def step():
+        x = x0
+        for l in range(n_layers):
+            logits = (x @ routers[l].t()).float() + bias
+            prefill.moe_layer_prefill(logits, layers[l], x, ws, y)
+            x = (y * torch.rsqrt(y.pow(2).mean(dim=1, keepdim=True) + 1e-12)).to(torch.bfloat16)
+        return x
+
+    step()
+    torch.cuda.synchronize()
+    counts = ws.ints(ws.ws.expert_count, EXPERTS)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        out = step()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    # the two grouped GEMMs of one layer, timed alone
+    logits = (x0 @ routers[0].t()).float() + bias
+    prefill.moe_route(logits, x0, None, 0, None, None, tokens, ws)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    ev[0].record()
+    prefill.moe_grouped_gate_up(layers[0], None, x0, tokens, ws)
+    ev[1].record()
+    prefill.moe_grouped_down(layers[0], None, tokens, ws)
+    ev[2].record()
+    torch.cuda.synchronize()
+    flops_layer = float(tokens) * TOPK * 7864320.0
+    peaks_json = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    bf16_peak = float(json.load(open(peaks_json))["bf16_tflops_sustained"]) if os.path.exists(peaks_json) else 1400.0
+    tfl = flops_layer * n_layers / (ms * 1e-3) / 1e12
+    res = {"workload": "%d layers x %d tokens, 512 IQ3_S experts/layer, top-10, Zipf(1.1) router bias" % (n_layers, tokens),
+           "tokens_per_s": tokens / (ms * 1e-3), "ms_per_stack": ms, "tflops": tfl,
+           "numerics": "bf16 weights (exact dequant, rounded) x bf16 activations, fp32 accumulate (reference prefill family)",
+           "roofline": {"bound": "tensor", "achieved": tfl, "peak": bf16_peak, "unit": "TFLOP/s", "frac": tfl / bf16_peak,
+                        "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)"},
+           "gate_up_ms_layer0": ev[0].elapsed_time(ev[1]), "down_ms_layer0": ev[1].elapsed_time(ev[2]),
+           "gate_up_tflops_layer0": flops_layer * 2 / 3 / (ev[0].elapsed_time(ev[1]) * 1e-3) / 1e12,
+           "down_tflops_layer0": flops_layer / 3 / (ev[1].elapsed_time(ev[2]) * 1e-3) / 1e12,
+           "busiest_expert_pairs_last_layer": int(counts.max()), "median_expert_pairs_last_layer": int(np.median(counts)),
+           "device_status": ws.status(), "finite_output": bool(torch.isfinite(out.float()).all().item()),
+           "timed_region_includes": "torch router projection + unit-RMS rescale between layers"}
+    del layers
+    torch.cuda.empty_cache()
+    return res
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     from fngine_b200 import lib as fblib
@@ -357,6 +423,7 @@ def run_ours(args, rank, world, local_rank):
     del layers
     torch.cuda.empty_cache()
     fp8 = fp8_gemm_section(torch)
+    pre = prefill_section(torch)
     peak, peak_src = peaks()
     gu_ach = sum(gu_bytes) / (sum(gu_ms) * 1e-3) / 1e9
     value = step_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -384,6 +451,7 @@ def run_ours(args, rank, world, local_rank):
         "gpu_launches": args.steps * Lr * 4,
         "other_batches": other,
         "fp8_row_gemm": fp8,
+        "prefill_stack": pre,
         "parity_vs_cpu_max_rel_l2": parity,
         "device_status": status,
         "clocks": clocks,

@@ -8,11 +8,12 @@
 // WEIGHT rows on the 128 TMEM lanes and the expert's TOKENS on the N axis (a multiple of 16, up to
 // 256), so ragged per-expert token counts waste at most 15 columns:
 //   D[128 weight rows][tokens] += W_bf16[128][64] * X[tokens][64]^T        per 64-wide K step.
-// The A operand never exists in global memory: 256 dequant threads (one per weight row of the gate
-// and of the up tile) decode their row's quarter IQ3_S block (or two IQ4_NL blocks) per K step
-// straight into the 128-byte-swizzled shared-memory tile the MMA reads. The B operand is gathered
-// token rows (cp.async, gate/up) or the expert-sorted h rows (TMA, down). One thread issues the
-// MMAs; four warps drain tensor memory. All hand-offs are mbarriers with bounded waits.
+// The A operand never exists in global memory: dequant warps (16 for gate/up, 8 for down; a warp =
+// 16 weight rows, a lane = half of a row's K step = one IQ3_S sub-block or one IQ4_NL block) decode
+// straight into the 128-byte-swizzled shared-memory tile the MMA reads. The raw block bytes reach
+// them through a coalesced, register-prefetched staging copy in shared memory. The B operand is
+// gathered token rows (cp.async, gate/up) or the expert-sorted h rows (TMA, down). One thread
+// issues the MMAs; four warps drain tensor memory. All hand-offs are mbarriers with bounded waits.
 #include "iq_decode.cuh"
 
 #include <cuda.h>
@@ -66,6 +67,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
@@ -105,86 +115,156 @@ struct Abort {
 };
 
 // ------------------------------------------------------------------------------ weights -> bf16 tile rows
-// One thread writes the 64 bf16 (128 bytes) of its weight row for K step `kb` into the swizzled
-// tile: value = bf16_rne(fp32 dequantized weight), the reference's rounding
-// (cpu::decode_rows_bf16, src/cpu/iq_cpu.cpp:712-753). `row_bytes` points at the row's first block.
-__device__ __forceinline__ uint32_t ldg16(const uint8_t* p) { return __ldg(reinterpret_cast<const unsigned short*>(p)); }
+// A dequant thread owns half of a weight row per K step: 32 weights (one IQ3_S sub-block or one
+// IQ4_NL block) = four 16-byte chunks of the swizzled tile. Values are bf16_rne(fp32 dequantized
+// weight), the reference's rounding (cpu::decode_rows_bf16, src/cpu/iq_cpu.cpp:712-753).
+//
+// Integer -> float without the conversion pipe: PRMT drops the byte b into the mantissa of 2^23
+// (0x4B0000bb = 8388608 + b, exact), and one FMA with the exact constant -db * 2^23 gives
+// rn(db * b), bit-identical to fmul_rn(db, float(b)).
+__device__ __forceinline__ uint32_t lds16(const uint8_t* p) { return *reinterpret_cast<const unsigned short*>(p); }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
+template <int K>
+__device__ __forceinline__ float byte_as_magic(uint32_t w) {  // 2^23 + byte K of w
+  return __uint_as_float(prmt(w, 0x4B000000u, 0x7440u | uint32_t(K)));
+}
 
-// IQ3_S: K step kb covers sub-blocks 2q, 2q+1 (q = kb % 4) of block kb / 4.
-__device__ __forceinline__ void dequant_row_step_iq3s(const uint8_t* row_bytes, int kb, const uint32_t* grid,
-                                                      const uint32_t* signtab, uint8_t* tile, int row) {
-  const uint8_t* blk = row_bytes + (kb >> 2) * 110;
-  const int q = kb & 3;
-  const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(ldg16(blk))));
-  uint32_t qs[4];
+// IQ3_S: `blk` = the row's 110-byte block staged in shared memory (2-byte aligned), `sb` = the
+// sub-block (0..7); writes chunks chunk0 .. chunk0+3 of tile row `row`. Signs are applied to the
+// packed bf16 pairs (rounding is sign-symmetric): signtab[nibble] = {s0<<15 | s1<<31, s2<<15 | s3<<31}.
+__device__ __forceinline__ void dequant_sub_iq3s(const uint8_t* blk, int sb, const uint32_t* grid, const uint2* signtab,
+                                                 uint8_t* tile, int row, int chunk0) {
+  const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(lds16(blk))));
+  const uint32_t sc = (uint32_t(blk[106 + (sb >> 1)]) >> (4 * (sb & 1))) & 0xFu;
+  const float db = __fmul_rn(d, float(int(1 + 2 * sc)));
+  const float c = -db * 8388608.0f;
+  const uint8_t* qp = blk + 2 + 8 * sb;
+  const uint32_t qs[2] = {lds16(qp) | (lds16(qp + 2) << 16), lds16(qp + 4) | (lds16(qp + 6) << 16)};
+  const uint32_t qh = blk[66 + sb];
+  const uint32_t sg = lds16(blk + 74 + 4 * sb) | (lds16(blk + 76 + 4 * sb) << 16);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) qs[i] = ldg16(blk + 2 + 16 * q + 4 * i) | (ldg16(blk + 4 + 16 * q + 4 * i) << 16);
-  const uint32_t qh = ldg16(blk + 66 + 2 * q);
-  uint32_t sg[2];
+  for (int l = 0; l < 8; l += 2) {  // two look-ups = 8 weights = one 16-byte chunk
+    uint32_t packed[4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) sg[i] = ldg16(blk + 74 + 8 * q + 4 * i) | (ldg16(blk + 76 + 8 * q + 4 * i) << 16);
-  const uint32_t sc = blk[106 + q];
+    for (int h = 0; h < 2; ++h) {
+      const int ll = l + h;
+      const uint32_t idx = ((qs[ll >> 2] >> (8 * (ll & 3))) & 0xFFu) | (((qh >> ll) & 1u) << 8);
+      const uint32_t g = grid[idx];
+      const uint2 sm = signtab[(sg >> (4 * ll)) & 0xFu];
+      packed[2 * h] = pack_bf16(__fmaf_rn(db, byte_as_magic<0>(g), c), __fmaf_rn(db, byte_as_magic<1>(g), c)) ^ sm.x;
+      packed[2 * h + 1] = pack_bf16(__fmaf_rn(db, byte_as_magic<2>(g), c), __fmaf_rn(db, byte_as_magic<3>(g), c)) ^ sm.y;
+    }
+    *reinterpret_cast<uint4*>(tile + swz(row, chunk0 + (l >> 1))) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+}
+
+// IQ4_NL: `blk` = one staged 18-byte block (32 weights; low nibbles are elements 0..15). Levels
+// are signed bytes: biased by 128 they go through the same mantissa trick, un-biased by an exact
+// subtraction before the multiply.
+__device__ __forceinline__ void dequant_sub_iq4nl(const uint8_t* blk, uint8_t* tile, int row, int chunk0) {
+  const Iq4nlLevels lv = iq4nl_levels();
+  const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(lds16(blk))));
+  uint32_t qw[4];
 #pragma unroll
-  for (int sb = 0; sb < 2; ++sb) {
-    const float db = __fmul_rn(d, float(1 + 2 * int((sc >> (4 * sb)) & 0xFu)));
+  for (int i = 0; i < 4; ++i) qw[i] = lds16(blk + 2 + 4 * i) | (lds16(blk + 4 + 4 * i) << 16);
+  int w[8];  // word e/2 holds levels of elements {e, e+16, e+1, e+17} (e even)
+  iq4nl_decode32(lv, qw, w);
 #pragma unroll
-    for (int l = 0; l < 8; l += 2) {  // two look-ups = 8 weights = one 16-byte chunk
+  for (int hi = 0; hi < 2; ++hi) {    // elements 16*hi .. 16*hi+15
+#pragma unroll
+    for (int c2 = 0; c2 < 2; ++c2) {  // 8 elements per 16-byte chunk
       uint32_t packed[4];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int ll = l + h;
-        const uint32_t src = qs[2 * sb + (ll >> 2)];
-        const uint32_t idx = ((src >> (8 * (ll & 3))) & 0xFFu) | (((qh >> (8 * sb + ll)) & 1u) << 8);
-        const uint32_t g = grid[idx];
-        const uint32_t m = signtab[(sg[sb] >> (4 * ll)) & 0xFu];
-        const uint32_t w = (g ^ m) + (m & 0x01010101u);  // signed int8 x4
-        const float f0 = __fmul_rn(db, float(int8_t(w)));
-        const float f1 = __fmul_rn(db, float(int8_t(w >> 8)));
-        const float f2 = __fmul_rn(db, float(int8_t(w >> 16)));
-        const float f3 = __fmul_rn(db, float(int8_t(w >> 24)));
-        packed[2 * h] = pack_bf16(f0, f1);
-        packed[2 * h + 1] = pack_bf16(f2, f3);
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t ww = uint32_t(w[4 * c2 + e]) ^ 0x80808080u;
+        const float m0 = hi ? byte_as_magic<1>(ww) : byte_as_magic<0>(ww);
+        const float m1 = hi ? byte_as_magic<3>(ww) : byte_as_magic<2>(ww);
+        packed[e] = pack_bf16(__fmul_rn(d, m0 - 8388736.0f), __fmul_rn(d, m1 - 8388736.0f));
       }
-      const int c = 4 * sb + (l >> 1);
-      *reinterpret_cast<uint4*>(tile + swz(row, c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      *reinterpret_cast<uint4*>(tile + swz(row, chunk0 + 2 * hi + c2)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
   }
 }
 
-// IQ4_NL: K step kb covers blocks 2kb, 2kb+1 (32 weights each; low nibbles are elements 0..15).
-__device__ __forceinline__ void dequant_row_step_iq4nl(const uint8_t* row_bytes, int kb, uint8_t* tile, int row) {
-  const Iq4nlLevels lv = iq4nl_levels();
+// How the raw expert bytes reach the dequant threads. Per "column" (kColSteps consecutive K steps)
+// a thread needs one contiguous piece of its row. Reading pieces straight from global memory costs
+// one cache line per lane, so each warp copies the pieces of its 16 rows with coalesced word loads
+// (lane = word of the piece, one piece per instruction) into a padded shared-memory array (odd
+// word stride: conflict-free row access), one column ahead in registers. A piece starts 0 or 2
+// bytes into its first word; row sizes and matrix offsets are multiples of 4, so a piece never
+// needs a word that starts beyond the end of its matrix.
+template <int FMT>
+struct RawCfg;
+template <>
+struct RawCfg<FB_FMT_IQ3_S> {
+  static constexpr int kColSteps = 4, kPiece = 110, kWords = 28, kStride = 116;
+};
+template <>
+struct RawCfg<FB_FMT_IQ4_NL> {
+  static constexpr int kColSteps = 2, kPiece = 72, kWords = 18, kStride = 76;
+};
+constexpr int kRawStrideMax = 116;
+
+template <int FMT>
+__device__ __forceinline__ void raw_prefetch(const uint8_t* warp_rows, int row_bytes, int col, int lane,
+                                             uint32_t (&pre)[16]) {
+  using R = RawCfg<FMT>;
+  const uint8_t* src = warp_rows + col * R::kPiece;
+  const uint8_t* w = src - (reinterpret_cast<uintptr_t>(src) & 3) + 4 * lane;
+  if (lane < R::kWords) {
 #pragma unroll
-  for (int b = 0; b < 2; ++b) {
-    const uint8_t* blk = row_bytes + (2 * kb + b) * 18;
-    const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(ldg16(blk))));
-    uint32_t qw[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) qw[i] = ldg16(blk + 2 + 4 * i) | (ldg16(blk + 4 + 4 * i) << 16);
-    int w[8];  // word e/2 holds levels of elements {e, e+16, e+1, e+17} (e even)
-    iq4nl_decode32(lv, qw, w);
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {  // elements 16*half .. 16*half+15
-#pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2) {      // 8 elements per 16-byte chunk
-        uint32_t packed[4];
-#pragma unroll
-        for (int e = 0; e < 8; e += 2) {
-          const uint32_t ww = uint32_t(w[(8 * c2 + e) >> 1]);
-          const float f0 = __fmul_rn(d, float(int8_t(ww >> (8 * half))));
-          const float f1 = __fmul_rn(d, float(int8_t(ww >> (16 + 8 * half))));
-          packed[e >> 1] = pack_bf16(f0, f1);
-        }
-        const int c = 4 * b + 2 * half + c2;
-        *reinterpret_cast<uint4*>(tile + swz(row, c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      }
-    }
+    for (int pp = 0; pp < 16; ++pp) pre[pp] = __ldg(reinterpret_cast<const uint32_t*>(w + size_t(pp) * row_bytes));
   }
+}
+
+// One unit's weight rows -> bf16 tiles, K step by K step, by NW warps of 16 rows x 2 halves.
+// `warp_rows` = the first of this warp's 16 rows, `slot0` = their index in the staging array,
+// `tile_off` = byte offset of the A tile inside a ring stage, `row` = this thread's tile row and
+// `half` its half of the K step. After a failed wait the remaining waits fall through at once (the
+// abort flag is set), so the loop just drains.
+template <int FMT, int STAGES>
+__device__ __forceinline__ void dequant_unit(const uint8_t* warp_rows, int row_bytes, int k_steps, uint8_t* raw,
+                                             int slot0, uint8_t* ring, int stage_bytes, int tile_off, int row,
+                                             int half, uint64_t* full, uint64_t* empty, uint32_t& it, const Abort& ab,
+                                             const uint32_t* grid, const uint2* signtab) {
+  using R = RawCfg<FMT>;
+  const int lane = threadIdx.x & 31;
+  const int n_cols = k_steps / R::kColSteps;
+  uint32_t pre[16];
+  raw_prefetch<FMT>(warp_rows, row_bytes, 0, lane, pre);
+  const int shift0 = int(reinterpret_cast<uintptr_t>(warp_rows) & 3);
+  for (int col = 0; col < n_cols; ++col) {
+    if (lane < R::kWords) {
+#pragma unroll
+      for (int pp = 0; pp < 16; ++pp)
+        *reinterpret_cast<uint32_t*>(raw + (slot0 + pp) * R::kStride + 4 * lane) = pre[pp];
+    }
+    __syncwarp();  // a warp stages and consumes only its own 16 rows
+    if (col + 1 < n_cols) raw_prefetch<FMT>(warp_rows, row_bytes, col + 1, lane, pre);
+    const uint8_t* piece = raw + (slot0 + (lane >> 1)) * R::kStride + ((shift0 + col * R::kPiece) & 3);
+#pragma unroll 1
+    for (int q = 0; q < R::kColSteps; ++q, ++it) {
+      const int s = it % STAGES;
+      ab.wait(&empty[s], ((it / STAGES) & 1) ^ 1);
+      uint8_t* ta = ring + s * stage_bytes + tile_off;
+      if constexpr (FMT == FB_FMT_IQ3_S) dequant_sub_iq3s(piece, 2 * q + half, grid, signtab, ta, row, 4 * half);
+      else dequant_sub_iq4nl(piece + 18 * (2 * q + half), ta, row, 4 * half);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full[s]);
+    }
+    __syncwarp();  // the warp is done with this column's pieces
+  }
+}
+
+// signtab[nibble] for dequant_sub_iq3s.
+__device__ __forceinline__ uint2 iq3s_sign_pair_masks(int nib) {
+  return make_uint2(((nib & 1) ? 0x8000u : 0u) | ((nib & 2) ? 0x80000000u : 0u),
+                    ((nib & 4) ? 0x8000u : 0u) | ((nib & 8) ? 0x80000000u : 0u));
 }
 
 // ------------------------------------------------------------------------------ route
@@ -297,8 +377,9 @@ struct GuBars {
   int abort;
 };
 constexpr int kGuStage = 2 * kTileA + kTileB;                       // 64 KB
-constexpr int kGuSmem = kStagesGU * kGuStage + 2048 + 64 + sizeof(GuBars) + 1024;
-constexpr int kGuThreads = 15 * 32;  // warp 0 MMA, 1-2 gather, 3-10 dequant, 11-14 epilogue
+constexpr int kGuRaw = 256 * 116;  // staged raw pieces of the 256 weight rows
+constexpr int kGuSmem = kStagesGU * kGuStage + kGuRaw + 2048 + 128 + sizeof(GuBars) + 1024;
+constexpr int kGuThreads = 23 * 32;  // warp 0 MMA, 1-2 gather, 3-18 dequant, 19-22 epilogue
 
 template <int FMT>
 __global__ void __launch_bounds__(kGuThreads, 1)
@@ -309,9 +390,10 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = smem;
-  uint32_t* grid = reinterpret_cast<uint32_t*>(smem + kStagesGU * kGuStage);
-  uint32_t* signtab = grid + 512;
-  GuBars* bars = reinterpret_cast<GuBars*>(reinterpret_cast<uint8_t*>(signtab) + 64);
+  uint8_t* raw = smem + kStagesGU * kGuStage;
+  uint32_t* grid = reinterpret_cast<uint32_t*>(raw + kGuRaw);
+  uint2* signtab = reinterpret_cast<uint2*>(grid + 512);
+  GuBars* bars = reinterpret_cast<GuBars*>(reinterpret_cast<uint8_t*>(signtab) + 128);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int I = L.inter;
   const int n_units = meta[0];
@@ -319,15 +401,10 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
   const Abort ab{&bars->abort, status};
 
   for (int i = tid; i < 512; i += kGuThreads) grid[i] = iq3s_grid_entry(i);
-  if (tid < 16) {
-    uint32_t m = 0;
-    for (int j = 0; j < 4; ++j)
-      if (tid & (1 << j)) m |= 0xFFu << (8 * j);
-    signtab[tid] = m;
-  }
+  if (tid < 16) signtab[tid] = iq3s_sign_pair_masks(tid);
   if (tid == 0) {
     for (int i = 0; i < kStagesGU; ++i) {
-      mbar_init(&bars->full[i], 10);  // 2 gather warps + 8 dequant warps
+      mbar_init(&bars->full[i], 18);  // 2 gather warps + 16 dequant warps
       mbar_init(&bars->empty[i], 1);
     }
     mbar_init(&bars->tmem_full, 1);
@@ -414,26 +491,16 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->full[pending]);
     }
-  } else if (warp <= 10) {
-    // ---------------- dequant: thread = (matrix, weight row)
-    const int td = tid - 96, mat = td >> 7, row = td & 127;
+  } else if (warp <= 18) {
+    // ---------------- dequant: warp = (matrix, 16 rows), lane = (row, half of the K step)
+    const int wd = warp - 3, mat = wd >> 3, row0 = (wd & 7) * 16;
     uint32_t it = 0;
     for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
       const int4 un = units[u];
       const uint8_t* blob = expert_blob ? expert_blob[un.x] : L.slots + int64_t(un.x) * L.blob_stride;
-      const uint8_t* rowp = blob + (mat ? L.up_offset : L.gate_offset) + size_t(un.y + row) * row_bytes;
-      bool ok = true;
-      for (int kb = 0; kb < kSteps; ++kb, ++it) {
-        const int s = it % kStagesGU;
-        if (!ab.wait(&bars->empty[s], ((it / kStagesGU) & 1) ^ 1)) { ok = false; break; }
-        uint8_t* ta = ring + s * kGuStage + mat * kTileA;
-        if constexpr (FMT == FB_FMT_IQ3_S) dequant_row_step_iq3s(rowp, kb, grid, signtab, ta, row);
-        else dequant_row_step_iq4nl(rowp, kb, ta, row);
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->full[s]);
-      }
-      if (!ok) break;
+      const uint8_t* warp_rows = blob + (mat ? L.up_offset : L.gate_offset) + size_t(un.y + row0) * row_bytes;
+      dequant_unit<FMT, kStagesGU>(warp_rows, row_bytes, kSteps, raw, wd * 16, ring, kGuStage, mat * kTileA,
+                                   row0 + (lane >> 1), lane & 1, bars->full, bars->empty, it, ab, grid, signtab);
     }
   } else {
     // ---------------- epilogue: lane quarter = warp % 4; thread = intermediate row j
@@ -444,16 +511,17 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
       if (!ab.wait(&bars->tmem_full, ul & 1)) break;
       tc_fence_after();
       const int j = un.y + q * 32 + lane;
-      for (int c0 = 0; c0 < un.w; c0 += 32) {
-        uint32_t g[32], up[32];
-        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c0), g);
-        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(256 + c0), up);
+      for (int c0 = 0; c0 < un.w; c0 += 16) {
+        uint32_t g[16], up[16];
+        tmem_ld16(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c0), g);
+        tmem_ld16(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(256 + c0), up);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 16; ++i) {
           if (c0 + i < un.w) {
+            // silu(g) * u; fast exp and divide: their error (a few fp32 ulp) is far below the bf16 step of h
             const float gv = __uint_as_float(g[i]), uv = __uint_as_float(up[i]);
-            const float hv = (gv / (1.0f + expf(-gv))) * uv;
+            const float hv = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
             h[size_t(un.z + c0 + i) * I + j] = __float2bfloat16_rn(hv);
           }
         }
@@ -481,8 +549,9 @@ struct DnBars {
   int abort;
 };
 constexpr int kDnStage = kTileA + kTileB;  // 48 KB
-constexpr int kDnSmem = kStagesDN * kDnStage + 2048 + 64 + sizeof(DnBars) + 1024;
-constexpr int kDnThreads = 10 * 32;  // warp 0 MMA, warp 1 TMA, 2-5 dequant, 6-9 epilogue
+constexpr int kDnRaw = 128 * 116;
+constexpr int kDnSmem = kStagesDN * kDnStage + kDnRaw + 2048 + 128 + sizeof(DnBars) + 1024;
+constexpr int kDnThreads = 14 * 32;  // warp 0 MMA, warp 1 TMA, 2-9 dequant, 10-13 epilogue
 
 // yp[pair][n] = w_pair * (down_n . h[pair])
 template <int FMT>
@@ -494,9 +563,10 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = smem;
-  uint32_t* grid = reinterpret_cast<uint32_t*>(smem + kStagesDN * kDnStage);
-  uint32_t* signtab = grid + 512;
-  DnBars* bars = reinterpret_cast<DnBars*>(reinterpret_cast<uint8_t*>(signtab) + 64);
+  uint8_t* raw = smem + kStagesDN * kDnStage;
+  uint32_t* grid = reinterpret_cast<uint32_t*>(raw + kDnRaw);
+  uint2* signtab = reinterpret_cast<uint2*>(grid + 512);
+  DnBars* bars = reinterpret_cast<DnBars*>(reinterpret_cast<uint8_t*>(signtab) + 128);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int I = L.inter;
   const int n_units = meta[1];
@@ -505,15 +575,10 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
   const Abort ab{&bars->abort, status};
 
   for (int i = tid; i < 512; i += kDnThreads) grid[i] = iq3s_grid_entry(i);
-  if (tid < 16) {
-    uint32_t m = 0;
-    for (int j = 0; j < 4; ++j)
-      if (tid & (1 << j)) m |= 0xFFu << (8 * j);
-    signtab[tid] = m;
-  }
+  if (tid < 16) signtab[tid] = iq3s_sign_pair_masks(tid);
   if (tid == 0) {
     for (int i = 0; i < kStagesDN; ++i) {
-      mbar_init(&bars->full[i], 5);  // TMA thread (with its byte count) + 4 dequant warps
+      mbar_init(&bars->full[i], 9);  // TMA thread (with its byte count) + 8 dequant warps
       mbar_init(&bars->empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -571,25 +636,16 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
         if (!ok) break;
       }
     }
-  } else if (warp <= 5) {
-    const int row = tid - 64;
+  } else if (warp <= 9) {
+    // ---------------- dequant: warp = 16 rows, lane = (row, half of the K step)
+    const int wd = warp - 2, row0 = wd * 16;
     uint32_t it = 0;
     for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
       const int4 un = units[u];
       const uint8_t* blob = expert_blob ? expert_blob[un.x] : L.slots + int64_t(un.x) * L.blob_stride;
-      const uint8_t* rowp = blob + L.down_offset + size_t(un.y + row) * row_bytes;
-      bool ok = true;
-      for (int kb = 0; kb < k_steps; ++kb, ++it) {
-        const int s = it % kStagesDN;
-        if (!ab.wait(&bars->empty[s], ((it / kStagesDN) & 1) ^ 1)) { ok = false; break; }
-        uint8_t* ta = ring + s * kDnStage;
-        if constexpr (FMT == FB_FMT_IQ3_S) dequant_row_step_iq3s(rowp, kb, grid, signtab, ta, row);
-        else dequant_row_step_iq4nl(rowp, kb, ta, row);
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->full[s]);
-      }
-      if (!ok) break;
+      const uint8_t* warp_rows = blob + L.down_offset + size_t(un.y + row0) * row_bytes;
+      dequant_unit<FMT, kStagesDN>(warp_rows, row_bytes, k_steps, raw, row0, ring, kDnStage, 0, row0 + (lane >> 1),
+                                   lane & 1, bars->full, bars->empty, it, ab, grid, signtab);
     }
   } else {
     const int q = warp & 3;
