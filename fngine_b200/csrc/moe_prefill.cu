@@ -19,6 +19,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <type_traits>
+
 namespace fb {
 namespace {
 
@@ -133,39 +135,78 @@ __device__ __forceinline__ float byte_as_magic(uint32_t w) {  // 2^23 + byte K o
   return __uint_as_float(prmt(w, 0x4B000000u, 0x7440u | uint32_t(K)));
 }
 
-// IQ3_S: `blk` = the row's 110-byte block staged in shared memory (2-byte aligned), `sb` = the
-// sub-block (0..7); writes chunks chunk0 .. chunk0+3 of tile row `row`. Signs are applied to the
-// packed bf16 pairs (rounding is sign-symmetric): signtab[nibble] = {s0<<15 | s1<<31, s2<<15 | s3<<31}.
-__device__ __forceinline__ void dequant_sub_iq3s(const uint8_t* blk, int sb, const uint32_t* grid, const uint2* signtab,
-                                                 uint8_t* tile, int row, int chunk0) {
-  const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(lds16(blk))));
-  const uint32_t sc = (uint32_t(blk[106 + (sb >> 1)]) >> (4 * (sb & 1))) & 0xFu;
-  const float db = __fmul_rn(d, float(int(1 + 2 * sc)));
-  const float c = -db * 8388608.0f;
-  const uint8_t* qp = blk + 2 + 8 * sb;
-  const uint32_t qs[2] = {lds16(qp) | (lds16(qp + 2) << 16), lds16(qp + 4) | (lds16(qp + 6) << 16)};
-  const uint32_t qh = blk[66 + sb];
-  const uint32_t sg = lds16(blk + 74 + 4 * sb) | (lds16(blk + 76 + 4 * sb) << 16);
+// IQ3_S, one sub-block (32 weights) per call. A weight is db * g * sign with g one of the 8 odd
+// magnitudes 1..15, so the 8 possible bf16 values of the sub-block are computed once
+// (db * (2k+1) is exact in fp32, then rounded like the reference rounds) and kept as two byte
+// planes in four registers; the codebook table holds, per 9-bit index, the four 3-bit magnitude
+// numbers as PRMT selector nibbles, so one PRMT per plane picks four weights, one XOR flips their
+// signs (bit 7 of the high bytes; rounding is sign-symmetric) and two PRMTs interleave the planes
+// into bf16 pairs. The integer ALU does ~2.7 operations per weight, none on the conversion pipe.
+//
+// `slot` = the row's staged block, 8-byte aligned + 4, block byte 0 at slot + 2: that puts qs
+// (8 bytes per sub-block), qh and the sign words on their natural alignment.
+struct Iq3sColumn {  // per-thread constants of a column (4 K steps of one block)
+  float d;
+  uint32_t qh_lo, qh_hi;  // qh bytes, shifted so that step q's byte is byte 2*(q&1) of word q>>1
+  uint32_t sc;            // scale nibbles, shifted so that step q's nibble is bits 8q..8q+3
+};
+__device__ __forceinline__ Iq3sColumn iq3s_column(const uint8_t* slot, int half) {
+  Iq3sColumn c;
+  c.d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(slot + 2)));
+  const uint2 qh = *reinterpret_cast<const uint2*>(slot + 68);
+  c.qh_lo = qh.x >> (8 * half);
+  c.qh_hi = qh.y >> (8 * half);
+  c.sc = *reinterpret_cast<const uint32_t*>(slot + 108) >> (4 * half);
+  return c;
+}
+// seltab[idx] (16-bit entries) = k0 | k1 << 4 | k2 << 8 | k3 << 12 with grid magnitude j = 2 k_j + 1.
+template <int Q>
+__device__ __forceinline__ void dequant_sub_iq3s(const uint8_t* slot, int half, const Iq3sColumn& col,
+                                                 const uint16_t* seltab, uint8_t* tile_row, const int (&coff)[4]) {
+  const uint2 qs = *reinterpret_cast<const uint2*>(slot + 4 + 16 * Q + 8 * half);
+  const uint32_t sg = *reinterpret_cast<const uint32_t*>(slot + 76 + 8 * Q + 4 * half);
+  const uint32_t B = (((Q >> 1) ? col.qh_hi : col.qh_lo) >> (16 * (Q & 1))) & 0xFFu;  // this sub-block's qh
+  const float db = __fmul_rn(col.d, float(int(1u + 2u * ((col.sc >> (8 * Q)) & 0xFu))));
+  const float db2 = db + db;
+  float pv[8];
+  pv[0] = db;
 #pragma unroll
-  for (int l = 0; l < 8; l += 2) {  // two look-ups = 8 weights = one 16-byte chunk
-    uint32_t packed[4];
+  for (int k = 1; k < 8; ++k) pv[k] = pv[k - 1] + db2;  // exact: (2k+1) * db has at most 20 significant bits
+  const uint32_t t01 = pack_bf16(pv[0], pv[1]), t23 = pack_bf16(pv[2], pv[3]);
+  const uint32_t t45 = pack_bf16(pv[4], pv[5]), t67 = pack_bf16(pv[6], pv[7]);
+  const uint32_t lo_a = prmt(t01, t23, 0x6420u), hi_a = prmt(t01, t23, 0x7531u);
+  const uint32_t lo_b = prmt(t45, t67, 0x6420u), hi_b = prmt(t45, t67, 0x7531u);
+  // Table byte offsets (2 * index) of two look-ups per word: qs byte << 1 in bits 1..8 (17..24), the
+  // ninth index bit, taken from qh by a multiply that lands it on bit 9 (25).
+  constexpr uint32_t kM = 0x01FE01FEu, kM2 = 0x02000200u;
+  uint32_t a[4];
+  a[0] = ((qs.x << 1) & kM) | ((B * 0x00800200u) & kM2);  // look-ups 0, 2
+  a[1] = ((qs.x >> 7) & kM) | ((B * 0x00400100u) & kM2);  // look-ups 1, 3
+  a[2] = ((qs.y << 1) & kM) | ((B * 0x00080020u) & kM2);  // look-ups 4, 6
+  a[3] = ((qs.y >> 7) & kM) | ((B * 0x00040010u) & kM2);  // look-ups 5, 7
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {  // two look-ups = 8 weights = one 16-byte chunk
+    uint32_t out[4];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const int ll = l + h;
-      const uint32_t idx = ((qs[ll >> 2] >> (8 * (ll & 3))) & 0xFFu) | (((qh >> ll) & 1u) << 8);
-      const uint32_t g = grid[idx];
-      const uint2 sm = signtab[(sg >> (4 * ll)) & 0xFu];
-      packed[2 * h] = pack_bf16(__fmaf_rn(db, byte_as_magic<0>(g), c), __fmaf_rn(db, byte_as_magic<1>(g), c)) ^ sm.x;
-      packed[2 * h + 1] = pack_bf16(__fmaf_rn(db, byte_as_magic<2>(g), c), __fmaf_rn(db, byte_as_magic<3>(g), c)) ^ sm.y;
+      const int l = 2 * c + h;
+      const uint32_t aw = a[2 * (l >> 2) + (l & 1)];
+      const uint32_t off = (l & 2) ? (aw >> 16) : (aw & 0xFFFFu);
+      const uint32_t sel = *reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(seltab) + off);
+      const uint32_t sx = ((sg >> (4 * l)) & 0xFu) * 0x10204080u;  // sign bit j -> bit 7 of byte j
+      const uint32_t lo4 = prmt(lo_a, lo_b, sel);
+      const uint32_t hi4 = prmt(hi_a, hi_b, sel) ^ (sx & 0x80808080u);
+      out[2 * h] = prmt(lo4, hi4, 0x5140u);
+      out[2 * h + 1] = prmt(lo4, hi4, 0x7362u);
     }
-    *reinterpret_cast<uint4*>(tile + swz(row, chunk0 + (l >> 1))) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    *reinterpret_cast<uint4*>(tile_row + coff[c]) = make_uint4(out[0], out[1], out[2], out[3]);
   }
 }
 
 // IQ4_NL: `blk` = one staged 18-byte block (32 weights; low nibbles are elements 0..15). Levels
 // are signed bytes: biased by 128 they go through the same mantissa trick, un-biased by an exact
 // subtraction before the multiply.
-__device__ __forceinline__ void dequant_sub_iq4nl(const uint8_t* blk, uint8_t* tile, int row, int chunk0) {
+__device__ __forceinline__ void dequant_sub_iq4nl(const uint8_t* blk, uint8_t* tile_row, const int (&coff)[4]) {
   const Iq4nlLevels lv = iq4nl_levels();
   const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(lds16(blk))));
   uint32_t qw[4];
@@ -185,7 +226,7 @@ __device__ __forceinline__ void dequant_sub_iq4nl(const uint8_t* blk, uint8_t* t
         const float m1 = hi ? byte_as_magic<3>(ww) : byte_as_magic<2>(ww);
         packed[e] = pack_bf16(__fmul_rn(d, m0 - 8388736.0f), __fmul_rn(d, m1 - 8388736.0f));
       }
-      *reinterpret_cast<uint4*>(tile + swz(row, chunk0 + 2 * hi + c2)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      *reinterpret_cast<uint4*>(tile_row + coff[2 * hi + c2]) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
   }
 }
@@ -193,21 +234,24 @@ __device__ __forceinline__ void dequant_sub_iq4nl(const uint8_t* blk, uint8_t* t
 // How the raw expert bytes reach the dequant threads. Per "column" (kColSteps consecutive K steps)
 // a thread needs one contiguous piece of its row. Reading pieces straight from global memory costs
 // one cache line per lane, so each warp copies the pieces of its 16 rows with coalesced word loads
-// (lane = word of the piece, one piece per instruction) into a padded shared-memory array (odd
-// word stride: conflict-free row access), one column ahead in registers. A piece starts 0 or 2
-// bytes into its first word; row sizes and matrix offsets are multiples of 4, so a piece never
-// needs a word that starts beyond the end of its matrix.
+// (lane = word of the piece, one piece per instruction) into a padded shared-memory array, one
+// column ahead in registers. Row sizes and matrix offsets are multiples of 4, so a piece starts 0
+// or 2 bytes into its first word (the same for all rows of a column) and never needs a word that
+// starts beyond the end of its matrix. IQ3_S pieces are stored with byte 0 at slot + 2: columns
+// whose pieces start on a word boundary are shifted by two bytes on the way (one shuffle and one
+// funnel shift per word).
 template <int FMT>
 struct RawCfg;
 template <>
 struct RawCfg<FB_FMT_IQ3_S> {
-  static constexpr int kColSteps = 4, kPiece = 110, kWords = 28, kStride = 116;
+  static constexpr int kColSteps = 4, kPiece = 110, kWords = 28, kStride = 120;
 };
 template <>
 struct RawCfg<FB_FMT_IQ4_NL> {
   static constexpr int kColSteps = 2, kPiece = 72, kWords = 18, kStride = 76;
 };
-constexpr int kRawStrideMax = 116;
+constexpr int kRawBase = 4;       // slots start 8-byte aligned + 4
+constexpr int kRawStrideMax = 120;
 
 template <int FMT>
 __device__ __forceinline__ void raw_prefetch(const uint8_t* warp_rows, int row_bytes, int col, int lane,
@@ -215,56 +259,79 @@ __device__ __forceinline__ void raw_prefetch(const uint8_t* warp_rows, int row_b
   using R = RawCfg<FMT>;
   const uint8_t* src = warp_rows + col * R::kPiece;
   const uint8_t* w = src - (reinterpret_cast<uintptr_t>(src) & 3) + 4 * lane;
-  if (lane < R::kWords) {
 #pragma unroll
-    for (int pp = 0; pp < 16; ++pp) pre[pp] = __ldg(reinterpret_cast<const uint32_t*>(w + size_t(pp) * row_bytes));
-  }
+  for (int pp = 0; pp < 16; ++pp)
+    pre[pp] = lane < R::kWords ? __ldg(reinterpret_cast<const uint32_t*>(w + size_t(pp) * row_bytes)) : 0u;
 }
 
-// One unit's weight rows -> bf16 tiles, K step by K step, by NW warps of 16 rows x 2 halves.
+// One unit's weight rows -> bf16 tiles, K step by K step, by warps of 16 rows x 2 halves.
 // `warp_rows` = the first of this warp's 16 rows, `slot0` = their index in the staging array,
 // `tile_off` = byte offset of the A tile inside a ring stage, `row` = this thread's tile row and
-// `half` its half of the K step. After a failed wait the remaining waits fall through at once (the
-// abort flag is set), so the loop just drains.
+// `half` its half of the K step. `s`/`ph` = ring stage and phase, carried across units. After a
+// failed wait the remaining waits fall through at once (the abort flag is set), so the loop just
+// drains.
 template <int FMT, int STAGES>
 __device__ __forceinline__ void dequant_unit(const uint8_t* warp_rows, int row_bytes, int k_steps, uint8_t* raw,
                                              int slot0, uint8_t* ring, int stage_bytes, int tile_off, int row,
-                                             int half, uint64_t* full, uint64_t* empty, uint32_t& it, const Abort& ab,
-                                             const uint32_t* grid, const uint2* signtab) {
+                                             int half, uint64_t* full, uint64_t* empty, int& s, uint32_t& ph,
+                                             const Abort& ab, const uint16_t* seltab) {
   using R = RawCfg<FMT>;
   const int lane = threadIdx.x & 31;
   const int n_cols = k_steps / R::kColSteps;
+  int coff[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) coff[c] = ((4 * half + c) ^ (row & 7)) << 4;
+  uint8_t* const tile_row0 = ring + tile_off + row * 128;
+  uint8_t* const wslots = raw + kRawBase + slot0 * R::kStride;
+  const uint8_t* const slot = wslots + (lane >> 1) * R::kStride;
+  const int shift0 = int(reinterpret_cast<uintptr_t>(warp_rows) & 3);
   uint32_t pre[16];
   raw_prefetch<FMT>(warp_rows, row_bytes, 0, lane, pre);
-  const int shift0 = int(reinterpret_cast<uintptr_t>(warp_rows) & 3);
   for (int col = 0; col < n_cols; ++col) {
+    const int shift = (shift0 + col * R::kPiece) & 3;
+    if (FMT == FB_FMT_IQ3_S && shift == 0) {
+#pragma unroll
+      for (int pp = 0; pp < 16; ++pp) pre[pp] = __funnelshift_r(__shfl_up_sync(0xFFFFFFFFu, pre[pp], 1), pre[pp], 16);
+    }
     if (lane < R::kWords) {
 #pragma unroll
-      for (int pp = 0; pp < 16; ++pp)
-        *reinterpret_cast<uint32_t*>(raw + (slot0 + pp) * R::kStride + 4 * lane) = pre[pp];
+      for (int pp = 0; pp < 16; ++pp) *reinterpret_cast<uint32_t*>(wslots + pp * R::kStride + 4 * lane) = pre[pp];
     }
     __syncwarp();  // a warp stages and consumes only its own 16 rows
     if (col + 1 < n_cols) raw_prefetch<FMT>(warp_rows, row_bytes, col + 1, lane, pre);
-    const uint8_t* piece = raw + (slot0 + (lane >> 1)) * R::kStride + ((shift0 + col * R::kPiece) & 3);
-#pragma unroll 1
-    for (int q = 0; q < R::kColSteps; ++q, ++it) {
-      const int s = it % STAGES;
-      ab.wait(&empty[s], ((it / STAGES) & 1) ^ 1);
-      uint8_t* ta = ring + s * stage_bytes + tile_off;
-      if constexpr (FMT == FB_FMT_IQ3_S) dequant_sub_iq3s(piece, 2 * q + half, grid, signtab, ta, row, 4 * half);
-      else dequant_sub_iq4nl(piece + 18 * (2 * q + half), ta, row, 4 * half);
+    Iq3sColumn cc{};
+    if constexpr (FMT == FB_FMT_IQ3_S) cc = iq3s_column(slot, half);
+    auto step = [&](auto qc) {
+      constexpr int Q = decltype(qc)::value;
+      ab.wait(&empty[s], ph ^ 1);
+      uint8_t* tile_row = tile_row0 + s * stage_bytes;
+      if constexpr (FMT == FB_FMT_IQ3_S) {
+        dequant_sub_iq3s<Q>(slot, half, cc, seltab, tile_row, coff);
+      } else {
+        dequant_sub_iq4nl(slot + 18 * (2 * Q + half), tile_row, coff);
+      }
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&full[s]);
+      if (++s == STAGES) { s = 0; ph ^= 1; }
+    };
+    step(std::integral_constant<int, 0>{});
+    step(std::integral_constant<int, 1>{});
+    if constexpr (R::kColSteps == 4) {
+      step(std::integral_constant<int, 2>{});
+      step(std::integral_constant<int, 3>{});
     }
     __syncwarp();  // the warp is done with this column's pieces
   }
 }
 
-// signtab[nibble] for dequant_sub_iq3s.
-__device__ __forceinline__ uint2 iq3s_sign_pair_masks(int nib) {
-  return make_uint2(((nib & 1) ? 0x8000u : 0u) | ((nib & 2) ? 0x80000000u : 0u),
-                    ((nib & 4) ? 0x8000u : 0u) | ((nib & 8) ? 0x80000000u : 0u));
+// Fills the 512-entry selector table of dequant_sub_iq3s from the packed codebook (3 bits per
+// magnitude number).
+__device__ __forceinline__ void iq3s_selector_table_fill(uint16_t* seltab, int tid, int n_threads) {
+  for (int i = tid; i < 512; i += n_threads) {
+    const uint32_t p = c_iq3s_grid_packed[i];
+    seltab[i] = uint16_t((p & 7u) | (((p >> 3) & 7u) << 4) | (((p >> 6) & 7u) << 8) | (((p >> 9) & 7u) << 12));
+  }
 }
 
 // ------------------------------------------------------------------------------ route
@@ -371,14 +438,14 @@ __global__ void __launch_bounds__(256) pf_scatter_kernel(const int32_t* __restri
 struct GuBars {
   uint64_t full[kStagesGU];
   uint64_t empty[kStagesGU];
-  uint64_t tmem_full;
-  uint64_t tmem_empty;
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort;
 };
 constexpr int kGuStage = 2 * kTileA + kTileB;                       // 64 KB
-constexpr int kGuRaw = 256 * 116;  // staged raw pieces of the 256 weight rows
-constexpr int kGuSmem = kStagesGU * kGuStage + kGuRaw + 2048 + 128 + sizeof(GuBars) + 1024;
+constexpr int kGuRaw = 256 * kRawStrideMax + 16;  // staged raw pieces of the 256 weight rows
+constexpr int kGuSmem = kStagesGU * kGuStage + kGuRaw + 1024 + sizeof(GuBars) + 1024;
 constexpr int kGuThreads = 23 * 32;  // warp 0 MMA, 1-2 gather, 3-18 dequant, 19-22 epilogue
 
 template <int FMT>
@@ -391,24 +458,24 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = smem;
   uint8_t* raw = smem + kStagesGU * kGuStage;
-  uint32_t* grid = reinterpret_cast<uint32_t*>(raw + kGuRaw);
-  uint2* signtab = reinterpret_cast<uint2*>(grid + 512);
-  GuBars* bars = reinterpret_cast<GuBars*>(reinterpret_cast<uint8_t*>(signtab) + 128);
+  uint16_t* seltab = reinterpret_cast<uint16_t*>(raw + kGuRaw);
+  GuBars* bars = reinterpret_cast<GuBars*>(seltab + 512);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int I = L.inter;
   const int n_units = meta[0];
   const int row_bytes = FMT == FB_FMT_IQ3_S ? 1100 : 1440;
   const Abort ab{&bars->abort, status};
 
-  for (int i = tid; i < 512; i += kGuThreads) grid[i] = iq3s_grid_entry(i);
-  if (tid < 16) signtab[tid] = iq3s_sign_pair_masks(tid);
+  iq3s_selector_table_fill(seltab, tid, kGuThreads);
   if (tid == 0) {
     for (int i = 0; i < kStagesGU; ++i) {
       mbar_init(&bars->full[i], 18);  // 2 gather warps + 16 dequant warps
       mbar_init(&bars->empty[i], 1);
     }
-    mbar_init(&bars->tmem_full, 1);
-    mbar_init(&bars->tmem_empty, 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->tmem_full[i], 1);
+      mbar_init(&bars->tmem_empty[i], 4);
+    }
     bars->abort = 0;
     mbar_fence_init();
   }
@@ -420,16 +487,23 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
   constexpr int kSteps = H / kBK;  // 40
 
   if (warp == 0) {
-    // ---------------- MMA issuer: gate accumulator in columns [0,256), up in [256,512)
+    // ---------------- MMA issuer. Tensor memory holds two accumulator buffers of 256 columns. A
+    // unit of at most 128 tokens takes one buffer (gate in its first 128 columns, up in the
+    // second), so its epilogue overlaps the next unit's K loop; a wider unit takes both (gate in
+    // columns [0,256), up in [256,512)). The epilogue warps walk the same sequence.
     if (lane == 0) {
-      uint32_t it = 0, ul = 0;
-      for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++ul) {
+      uint32_t it = 0, use0 = 0, use1 = 0, nb = 0;
+      for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
         const int4 un = units[u];
         const int n = (un.w + 15) & ~15;
+        const bool wide = n > 128;
         const uint32_t idesc = idesc_bf16(n);
-        if (!ab.wait(&bars->tmem_empty, (ul & 1) ^ 1)) break;
-        tc_fence_after();
         bool ok = true;
+        if (wide || nb == 0) ok = ab.wait(&bars->tmem_empty[0], (use0 & 1) ^ 1);
+        if (ok && (wide || nb == 1)) ok = ab.wait(&bars->tmem_empty[1], (use1 & 1) ^ 1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t gcol = tmem_base + (wide ? 0u : nb * 256u), ucol = gcol + (wide ? 256u : 128u);
         for (int kb = 0; kb < kSteps; ++kb, ++it) {
           const int s = it % kStagesGU;
           if (!ab.wait(&bars->full[s], (it / kStagesGU) & 1)) { ok = false; break; }
@@ -439,13 +513,15 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
           const uint64_t db = umma_desc_k128(smem_u32(st + 2 * kTileA));
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {  // 16 bf16 = 32 bytes of K per instruction
-            umma_bf16(tmem_base, dg + uint64_t(2 * k4), db + uint64_t(2 * k4), idesc, (kb | k4) ? 1u : 0u);
-            umma_bf16(tmem_base + 256u, du + uint64_t(2 * k4), db + uint64_t(2 * k4), idesc, (kb | k4) ? 1u : 0u);
+            umma_bf16(gcol, dg + uint64_t(2 * k4), db + uint64_t(2 * k4), idesc, (kb | k4) ? 1u : 0u);
+            umma_bf16(ucol, du + uint64_t(2 * k4), db + uint64_t(2 * k4), idesc, (kb | k4) ? 1u : 0u);
           }
           umma_commit(&bars->empty[s]);
         }
         if (!ok) break;
-        umma_commit(&bars->tmem_full);
+        if (wide || nb == 0) { umma_commit(&bars->tmem_full[0]); ++use0; }
+        if (wide || nb == 1) { umma_commit(&bars->tmem_full[1]); ++use1; }
+        if (!wide) nb ^= 1u;
       }
     }
   } else if (warp <= 2) {
@@ -494,27 +570,34 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
   } else if (warp <= 18) {
     // ---------------- dequant: warp = (matrix, 16 rows), lane = (row, half of the K step)
     const int wd = warp - 3, mat = wd >> 3, row0 = (wd & 7) * 16;
-    uint32_t it = 0;
+    int s = 0;
+    uint32_t ph = 0;
     for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
       const int4 un = units[u];
       const uint8_t* blob = expert_blob ? expert_blob[un.x] : L.slots + int64_t(un.x) * L.blob_stride;
       const uint8_t* warp_rows = blob + (mat ? L.up_offset : L.gate_offset) + size_t(un.y + row0) * row_bytes;
       dequant_unit<FMT, kStagesGU>(warp_rows, row_bytes, kSteps, raw, wd * 16, ring, kGuStage, mat * kTileA,
-                                   row0 + (lane >> 1), lane & 1, bars->full, bars->empty, it, ab, grid, signtab);
+                                   row0 + (lane >> 1), lane & 1, bars->full, bars->empty, s, ph, ab, seltab);
     }
   } else {
     // ---------------- epilogue: lane quarter = warp % 4; thread = intermediate row j
     const int q = warp & 3;
-    uint32_t ul = 0;
-    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++ul) {
+    uint32_t use0 = 0, use1 = 0, nb = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
       const int4 un = units[u];
-      if (!ab.wait(&bars->tmem_full, ul & 1)) break;
+      const bool wide = ((un.w + 15) & ~15) > 128;
+      bool ok = true;
+      if (wide || nb == 0) ok = ab.wait(&bars->tmem_full[0], use0 & 1);
+      if (ok && (wide || nb == 1)) ok = ab.wait(&bars->tmem_full[1], use1 & 1);
+      if (!ok) break;
       tc_fence_after();
+      const uint32_t gcol = tmem_base + (uint32_t(q * 32) << 16) + (wide ? 0u : nb * 256u);
+      const uint32_t ucol = gcol + (wide ? 256u : 128u);
       const int j = un.y + q * 32 + lane;
       for (int c0 = 0; c0 < un.w; c0 += 16) {
         uint32_t g[16], up[16];
-        tmem_ld16(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c0), g);
-        tmem_ld16(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(256 + c0), up);
+        tmem_ld16(gcol + uint32_t(c0), g);
+        tmem_ld16(ucol + uint32_t(c0), up);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -528,7 +611,9 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->tmem_empty);
+      if (wide || nb == 0) { if (lane == 0) mbar_arrive(&bars->tmem_empty[0]); ++use0; }
+      if (wide || nb == 1) { if (lane == 0) mbar_arrive(&bars->tmem_empty[1]); ++use1; }
+      if (!wide) nb ^= 1u;
     }
   }
   tc_fence_before();
@@ -549,8 +634,8 @@ struct DnBars {
   int abort;
 };
 constexpr int kDnStage = kTileA + kTileB;  // 48 KB
-constexpr int kDnRaw = 128 * 116;
-constexpr int kDnSmem = kStagesDN * kDnStage + kDnRaw + 2048 + 128 + sizeof(DnBars) + 1024;
+constexpr int kDnRaw = 128 * kRawStrideMax + 16;
+constexpr int kDnSmem = kStagesDN * kDnStage + kDnRaw + 1024 + sizeof(DnBars) + 1024;
 constexpr int kDnThreads = 14 * 32;  // warp 0 MMA, warp 1 TMA, 2-9 dequant, 10-13 epilogue
 
 // yp[pair][n] = w_pair * (down_n . h[pair])
@@ -564,9 +649,8 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = smem;
   uint8_t* raw = smem + kStagesDN * kDnStage;
-  uint32_t* grid = reinterpret_cast<uint32_t*>(raw + kDnRaw);
-  uint2* signtab = reinterpret_cast<uint2*>(grid + 512);
-  DnBars* bars = reinterpret_cast<DnBars*>(reinterpret_cast<uint8_t*>(signtab) + 128);
+  uint16_t* seltab = reinterpret_cast<uint16_t*>(raw + kDnRaw);
+  DnBars* bars = reinterpret_cast<DnBars*>(seltab + 512);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int I = L.inter;
   const int n_units = meta[1];
@@ -574,8 +658,7 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
   const int k_steps = I / kBK;
   const Abort ab{&bars->abort, status};
 
-  for (int i = tid; i < 512; i += kDnThreads) grid[i] = iq3s_grid_entry(i);
-  if (tid < 16) signtab[tid] = iq3s_sign_pair_masks(tid);
+  iq3s_selector_table_fill(seltab, tid, kDnThreads);
   if (tid == 0) {
     for (int i = 0; i < kStagesDN; ++i) {
       mbar_init(&bars->full[i], 9);  // TMA thread (with its byte count) + 8 dequant warps
@@ -639,13 +722,14 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
   } else if (warp <= 9) {
     // ---------------- dequant: warp = 16 rows, lane = (row, half of the K step)
     const int wd = warp - 2, row0 = wd * 16;
-    uint32_t it = 0;
+    int s = 0;
+    uint32_t ph = 0;
     for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
       const int4 un = units[u];
       const uint8_t* blob = expert_blob ? expert_blob[un.x] : L.slots + int64_t(un.x) * L.blob_stride;
       const uint8_t* warp_rows = blob + L.down_offset + size_t(un.y + row0) * row_bytes;
       dequant_unit<FMT, kStagesDN>(warp_rows, row_bytes, k_steps, raw, row0, ring, kDnStage, 0, row0 + (lane >> 1),
-                                   lane & 1, bars->full, bars->empty, it, ab, grid, signtab);
+                                   lane & 1, bars->full, bars->empty, s, ph, ab, seltab);
     }
   } else {
     const int q = warp & 3;
