@@ -20,6 +20,7 @@
 #include <cuda_bf16.h>
 
 #include <type_traits>
+#include <utility>
 
 namespace fb {
 namespace {
@@ -108,8 +109,10 @@ struct Abort {
   volatile int* flag;
   uint32_t* status;
   __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity) const {
-    if (*flag) return false;
-    if (mbar_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if (*flag) return false;  // another role gave up: fall through every later wait
+    }
     *flag = 1;
     atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
     return false;
@@ -130,6 +133,40 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
+// Shared-memory accesses by 32-bit window address with a compile-time offset: one instruction
+// each, no 64-bit pointer arithmetic.
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF) : "memory");
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+  uint32_t v;
+  asm volatile("{\n\t.reg .b16 t;\n\tld.shared.u16 t, [%1+%2];\n\tcvt.u32.u16 %0, t;\n\t}" : "=r"(v) : "r"(a), "n"(OFF) : "memory");
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint2 lds_v2(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(a), "n"(OFF) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts_v4(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ void sts_u32(uint32_t a, uint32_t v) {
+  asm volatile("st.shared.u32 [%0+%1], %2;" ::"r"(a), "n"(OFF), "r"(v) : "memory");
+}
+
+template <int STRIDE, int PP = 0>
+__device__ __forceinline__ void sts_rows(uint32_t a, const uint32_t (&v)[16]) {  // v[pp] -> a + pp * STRIDE
+  sts_u32<PP * STRIDE>(a, v[PP]);
+  if constexpr (PP + 1 < 16) sts_rows<STRIDE, PP + 1>(a, v);
+}
+
 template <int K>
 __device__ __forceinline__ float byte_as_magic(uint32_t w) {  // 2^23 + byte K of w
   return __uint_as_float(prmt(w, 0x4B000000u, 0x7440u | uint32_t(K)));
@@ -150,21 +187,22 @@ struct Iq3sColumn {  // per-thread constants of a column (4 K steps of one block
   uint32_t qh_lo, qh_hi;  // qh bytes, shifted so that step q's byte is byte 2*(q&1) of word q>>1
   uint32_t sc;            // scale nibbles, shifted so that step q's nibble is bits 8q..8q+3
 };
-__device__ __forceinline__ Iq3sColumn iq3s_column(const uint8_t* slot, int half) {
+__device__ __forceinline__ Iq3sColumn iq3s_column(uint32_t slot, int half) {
   Iq3sColumn c;
-  c.d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(slot + 2)));
-  const uint2 qh = *reinterpret_cast<const uint2*>(slot + 68);
+  c.d = __half2float(__ushort_as_half(static_cast<unsigned short>(lds_u16<2>(slot))));
+  const uint2 qh = lds_v2<68>(slot);
   c.qh_lo = qh.x >> (8 * half);
   c.qh_hi = qh.y >> (8 * half);
-  c.sc = *reinterpret_cast<const uint32_t*>(slot + 108) >> (4 * half);
+  c.sc = lds_u32<108>(slot) >> (4 * half);
   return c;
 }
 // seltab[idx] (16-bit entries) = k0 | k1 << 4 | k2 << 8 | k3 << 12 with grid magnitude j = 2 k_j + 1.
+// `slot_h` = slot + 8 * half (window address); `tile_row` = window address of the tile row.
 template <int Q>
-__device__ __forceinline__ void dequant_sub_iq3s(const uint8_t* slot, int half, const Iq3sColumn& col,
-                                                 const uint16_t* seltab, uint8_t* tile_row, const int (&coff)[4]) {
-  const uint2 qs = *reinterpret_cast<const uint2*>(slot + 4 + 16 * Q + 8 * half);
-  const uint32_t sg = *reinterpret_cast<const uint32_t*>(slot + 76 + 8 * Q + 4 * half);
+__device__ __forceinline__ void dequant_sub_iq3s(uint32_t slot_h, uint32_t slot_hh, const Iq3sColumn& col,
+                                                 const uint16_t* seltab, uint32_t (&out)[16]) {
+  const uint2 qs = lds_v2<4 + 16 * Q>(slot_h);      // slot + 4 + 16 Q + 8 half
+  const uint32_t sg = lds_u32<76 + 8 * Q>(slot_hh);  // slot + 76 + 8 Q + 4 half
   const uint32_t B = (((Q >> 1) ? col.qh_hi : col.qh_lo) >> (16 * (Q & 1))) & 0xFFu;  // this sub-block's qh
   const float db = __fmul_rn(col.d, float(int(1u + 2u * ((col.sc >> (8 * Q)) & 0xFu))));
   const float db2 = db + db;
@@ -185,8 +223,7 @@ __device__ __forceinline__ void dequant_sub_iq3s(const uint8_t* slot, int half, 
   a[2] = ((qs.y << 1) & kM) | ((B * 0x00080020u) & kM2);  // look-ups 4, 6
   a[3] = ((qs.y >> 7) & kM) | ((B * 0x00040010u) & kM2);  // look-ups 5, 7
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {  // two look-ups = 8 weights = one 16-byte chunk
-    uint32_t out[4];
+  for (int c = 0; c < 4; ++c) {  // two look-ups = 8 weights = one 16-byte chunk (out[4c .. 4c+3])
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int l = 2 * c + h;
@@ -196,37 +233,37 @@ __device__ __forceinline__ void dequant_sub_iq3s(const uint8_t* slot, int half, 
       const uint32_t sx = ((sg >> (4 * l)) & 0xFu) * 0x10204080u;  // sign bit j -> bit 7 of byte j
       const uint32_t lo4 = prmt(lo_a, lo_b, sel);
       const uint32_t hi4 = prmt(hi_a, hi_b, sel) ^ (sx & 0x80808080u);
-      out[2 * h] = prmt(lo4, hi4, 0x5140u);
-      out[2 * h + 1] = prmt(lo4, hi4, 0x7362u);
+      out[4 * c + 2 * h] = prmt(lo4, hi4, 0x5140u);
+      out[4 * c + 2 * h + 1] = prmt(lo4, hi4, 0x7362u);
     }
-    *reinterpret_cast<uint4*>(tile_row + coff[c]) = make_uint4(out[0], out[1], out[2], out[3]);
   }
 }
 
 // IQ4_NL: `blk` = one staged 18-byte block (32 weights; low nibbles are elements 0..15). Levels
 // are signed bytes: biased by 128 they go through the same mantissa trick, un-biased by an exact
 // subtraction before the multiply.
-__device__ __forceinline__ void dequant_sub_iq4nl(const uint8_t* blk, uint8_t* tile_row, const int (&coff)[4]) {
+template <int OFF>
+__device__ __forceinline__ void dequant_sub_iq4nl(uint32_t blk, uint32_t (&out)[16]) {
   const Iq4nlLevels lv = iq4nl_levels();
-  const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(lds16(blk))));
+  const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(lds_u16<OFF>(blk))));
   uint32_t qw[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) qw[i] = lds16(blk + 2 + 4 * i) | (lds16(blk + 4 + 4 * i) << 16);
+  qw[0] = lds_u16<OFF + 2>(blk) | (lds_u16<OFF + 4>(blk) << 16);
+  qw[1] = lds_u16<OFF + 6>(blk) | (lds_u16<OFF + 8>(blk) << 16);
+  qw[2] = lds_u16<OFF + 10>(blk) | (lds_u16<OFF + 12>(blk) << 16);
+  qw[3] = lds_u16<OFF + 14>(blk) | (lds_u16<OFF + 16>(blk) << 16);
   int w[8];  // word e/2 holds levels of elements {e, e+16, e+1, e+17} (e even)
   iq4nl_decode32(lv, qw, w);
 #pragma unroll
   for (int hi = 0; hi < 2; ++hi) {    // elements 16*hi .. 16*hi+15
 #pragma unroll
-    for (int c2 = 0; c2 < 2; ++c2) {  // 8 elements per 16-byte chunk
-      uint32_t packed[4];
+    for (int c2 = 0; c2 < 2; ++c2) {  // 8 elements per 16-byte chunk (out[4c .. 4c+3], c = 2 hi + c2)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const uint32_t ww = uint32_t(w[4 * c2 + e]) ^ 0x80808080u;
         const float m0 = hi ? byte_as_magic<1>(ww) : byte_as_magic<0>(ww);
         const float m1 = hi ? byte_as_magic<3>(ww) : byte_as_magic<2>(ww);
-        packed[e] = pack_bf16(__fmul_rn(d, m0 - 8388736.0f), __fmul_rn(d, m1 - 8388736.0f));
+        out[4 * (2 * hi + c2) + e] = pack_bf16(__fmul_rn(d, m0 - 8388736.0f), __fmul_rn(d, m1 - 8388736.0f));
       }
-      *reinterpret_cast<uint4*>(tile_row + coff[2 * hi + c2]) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
   }
 }
@@ -281,9 +318,10 @@ __device__ __forceinline__ void dequant_unit(const uint8_t* warp_rows, int row_b
   int coff[4];
 #pragma unroll
   for (int c = 0; c < 4; ++c) coff[c] = ((4 * half + c) ^ (row & 7)) << 4;
-  uint8_t* const tile_row0 = ring + tile_off + row * 128;
-  uint8_t* const wslots = raw + kRawBase + slot0 * R::kStride;
-  const uint8_t* const slot = wslots + (lane >> 1) * R::kStride;
+  const uint32_t tile_row0 = smem_u32(ring) + tile_off + row * 128;
+  const uint32_t wslots = smem_u32(raw) + kRawBase + slot0 * R::kStride + 4 * lane;  // this lane's word of row 0
+  const uint32_t slot = smem_u32(raw) + kRawBase + (slot0 + (lane >> 1)) * R::kStride;
+  const uint32_t slot_h = slot + (FMT == FB_FMT_IQ3_S ? 8 : 18) * half, slot_hh = slot + 4 * half;
   const int shift0 = int(reinterpret_cast<uintptr_t>(warp_rows) & 3);
   uint32_t pre[16];
   raw_prefetch<FMT>(warp_rows, row_bytes, 0, lane, pre);
@@ -294,8 +332,7 @@ __device__ __forceinline__ void dequant_unit(const uint8_t* warp_rows, int row_b
       for (int pp = 0; pp < 16; ++pp) pre[pp] = __funnelshift_r(__shfl_up_sync(0xFFFFFFFFu, pre[pp], 1), pre[pp], 16);
     }
     if (lane < R::kWords) {
-#pragma unroll
-      for (int pp = 0; pp < 16; ++pp) *reinterpret_cast<uint32_t*>(wslots + pp * R::kStride + 4 * lane) = pre[pp];
+      sts_rows<R::kStride>(wslots, pre);
     }
     __syncwarp();  // a warp stages and consumes only its own 16 rows
     if (col + 1 < n_cols) raw_prefetch<FMT>(warp_rows, row_bytes, col + 1, lane, pre);
@@ -303,13 +340,13 @@ __device__ __forceinline__ void dequant_unit(const uint8_t* warp_rows, int row_b
     if constexpr (FMT == FB_FMT_IQ3_S) cc = iq3s_column(slot, half);
     auto step = [&](auto qc) {
       constexpr int Q = decltype(qc)::value;
+      uint32_t out[16];  // decoded before the stage is known to be free: the wait is off the decode's path
+      if constexpr (FMT == FB_FMT_IQ3_S) dequant_sub_iq3s<Q>(slot_h, slot_hh, cc, seltab, out);
+      else dequant_sub_iq4nl<36 * Q>(slot_h, out);
       ab.wait(&empty[s], ph ^ 1);
-      uint8_t* tile_row = tile_row0 + s * stage_bytes;
-      if constexpr (FMT == FB_FMT_IQ3_S) {
-        dequant_sub_iq3s<Q>(slot, half, cc, seltab, tile_row, coff);
-      } else {
-        dequant_sub_iq4nl(slot + 18 * (2 * Q + half), tile_row, coff);
-      }
+      const uint32_t tile_row = tile_row0 + s * stage_bytes;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) sts_v4(tile_row + coff[c], out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&full[s]);
@@ -445,7 +482,7 @@ struct GuBars {
 };
 constexpr int kGuStage = 2 * kTileA + kTileB;                       // 64 KB
 constexpr int kGuRaw = 256 * kRawStrideMax + 16;  // staged raw pieces of the 256 weight rows
-constexpr int kGuSmem = kStagesGU * kGuStage + kGuRaw + 1024 + sizeof(GuBars) + 1024;
+constexpr int kGuSmem = kStagesGU * kGuStage + kGuRaw + sizeof(GuBars) + 1024;
 constexpr int kGuThreads = 23 * 32;  // warp 0 MMA, 1-2 gather, 3-18 dequant, 19-22 epilogue
 
 template <int FMT>
@@ -458,8 +495,8 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = smem;
   uint8_t* raw = smem + kStagesGU * kGuStage;
-  uint16_t* seltab = reinterpret_cast<uint16_t*>(raw + kGuRaw);
-  GuBars* bars = reinterpret_cast<GuBars*>(seltab + 512);
+  __shared__ uint16_t seltab[512];  // static: its address folds into the look-up instruction
+  GuBars* bars = reinterpret_cast<GuBars*>(raw + kGuRaw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int I = L.inter;
   const int n_units = meta[0];
@@ -635,7 +672,7 @@ struct DnBars {
 };
 constexpr int kDnStage = kTileA + kTileB;  // 48 KB
 constexpr int kDnRaw = 128 * kRawStrideMax + 16;
-constexpr int kDnSmem = kStagesDN * kDnStage + kDnRaw + 1024 + sizeof(DnBars) + 1024;
+constexpr int kDnSmem = kStagesDN * kDnStage + kDnRaw + sizeof(DnBars) + 1024;
 constexpr int kDnThreads = 14 * 32;  // warp 0 MMA, warp 1 TMA, 2-9 dequant, 10-13 epilogue
 
 // yp[pair][n] = w_pair * (down_n . h[pair])
@@ -649,8 +686,8 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = smem;
   uint8_t* raw = smem + kStagesDN * kDnStage;
-  uint16_t* seltab = reinterpret_cast<uint16_t*>(raw + kDnRaw);
-  DnBars* bars = reinterpret_cast<DnBars*>(seltab + 512);
+  __shared__ uint16_t seltab[512];  // static: its address folds into the look-up instruction
+  DnBars* bars = reinterpret_cast<DnBars*>(raw + kDnRaw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int I = L.inter;
   const int n_units = meta[1];
