@@ -373,8 +373,14 @@ def run_ours(args, rank, world, local_rank):
     status = ws.status()
 
     # other batch sizes of the same layer definition, CUDA-graph replayed (launch-bound otherwise)
+    sections = set("batches,cpu,fp8,prefill".split(",")) if args.sections == "all" else \
+        set(x for x in args.sections.split(",") if x and x != "none")
+
+    def want(name):
+        return name in sections
+
     other = {}
-    for b2 in (1, 4):
+    for b2 in ((1, 4) if want("batches") else ()):
         xs2 = [x[:b2].contiguous() for x in xs]
         d2 = []
         for l in range(Lr):
@@ -408,10 +414,11 @@ def run_ours(args, rank, world, local_rank):
     y_cpu = run_cpu()
     t0 = time.perf_counter()
     reps = 0
+    cpu_budget_s = (10.0 if kind == "reference" else 1.0) if want("cpu") else 0.0
     while True:
         run_cpu()
         reps += 1
-        if time.perf_counter() - t0 > (10.0 if kind == "reference" else 1.0) or reps >= 2000:
+        if time.perf_counter() - t0 > cpu_budget_s or reps >= 2000:
             break
     cpu_dt = (time.perf_counter() - t0) / reps
     # the GPU result of that layer against the CPU result (parity of the measured workload)
@@ -422,8 +429,8 @@ def run_ours(args, rank, world, local_rank):
 
     del layers
     torch.cuda.empty_cache()
-    fp8 = fp8_gemm_section(torch)
-    pre = prefill_section(torch)
+    fp8 = fp8_gemm_section(torch) if want("fp8") else None
+    pre = prefill_section(torch) if want("prefill") else None
     peak, peak_src = peaks()
     gu_ach = sum(gu_bytes) / (sum(gu_ms) * 1e-3) / 1e9
     value = step_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -467,6 +474,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--sections", default="all",
+                    help="extra sections beside the headline decode measurement: all | none | comma list of "
+                         "batches,cpu,fp8,prefill (a profiler run wants none)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -28,7 +28,8 @@ constexpr int kTT = 2;  // tokens of one work item handled per pass over a stage
 // [8..168) item order
 constexpr int kSchedOrderBase = 8;
 constexpr int kSchedRoute = 2;
-constexpr int kSchedInts = 192;
+constexpr int kSchedGroup = 192;  // 32 row-group tickets of route_kernel
+constexpr int kSchedInts = 256;
 
 __host__ __device__ constexpr int act_row_bytes_planar(int act, int k) {
   return act == FB_ACT_Q8_K ? k + 64 : k + k / 8;
@@ -315,11 +316,13 @@ __global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ l
 
 // Router projection, activation quantization and selection in one launch (the head of the fused
 // layer call). Block (g, q) projects router rows 16g..16g+15 over the K slice [512q, 512q+512): the
-// x slice of all tokens sits in shared memory, one warp per row; partial sums go to `part`
-// [5][16][512]. Every block also quantizes a share of the activation blocks. The block that
-// finishes last - found with a device counter, nobody waits - adds the five slices in order,
-// stores the logits and runs the selection.
+// x slice of all tokens sits in shared memory, one warp per row, all tokens in flight at once;
+// partial sums go to `part` [5][16][512]. Every block also quantizes a share of the activation
+// blocks. Hand-offs use device tickets, nobody waits: the block that finishes last in its row
+// group adds the group's five slices in order 0..4 (fixed: repeated calls are bitwise identical)
+// and stores the logits; the row group that finishes last runs the selection.
 constexpr int kRouteSplits = 5, kRouteSlice = H / kRouteSplits;  // 512
+constexpr int kRouteGroups = kExperts / 16;                      // 32
 
 template <bool XBF16>
 __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restrict__ w, const void* __restrict__ xv,
@@ -329,7 +332,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
   pdl_launch_dependents();
   pdl_wait_prior();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  __shared__ __align__(16) float s_x[kMaxTok][kRouteSlice];
+  __shared__ __align__(16) float s_x[kMaxTok][kRouteSlice];  // x slice; later the logits [token][expert]
   __shared__ int s_last;
   const int g = blockIdx.x / kRouteSplits, q = blockIdx.x - g * kRouteSplits;
   for (int i = tid; i < T * (kRouteSlice / 4); i += 512) {
@@ -359,19 +362,37 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
     }
   }
   __syncthreads();
-  for (int t = 0; t < T; ++t) {
-    float acc = 0.0f;
+  {
+    float acc[kMaxTok];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const float4 xv4 = reinterpret_cast<const float4*>(&s_x[t][0])[c * 32 + lane];
-      acc = fmaf(wr[4 * c + 0], xv4.x, acc);
-      acc = fmaf(wr[4 * c + 1], xv4.y, acc);
-      acc = fmaf(wr[4 * c + 2], xv4.z, acc);
-      acc = fmaf(wr[4 * c + 3], xv4.w, acc);
+    for (int t = 0; t < kMaxTok; ++t) {
+      acc[t] = 0.0f;
+      if (t < T) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float4 xv4 = reinterpret_cast<const float4*>(&s_x[t][0])[c * 32 + lane];
+          acc[t] = fmaf(wr[4 * c + 0], xv4.x, acc[t]);
+          acc[t] = fmaf(wr[4 * c + 1], xv4.y, acc[t]);
+          acc[t] = fmaf(wr[4 * c + 2], xv4.z, acc[t]);
+          acc[t] = fmaf(wr[4 * c + 3], xv4.w, acc[t]);
+        }
+      }
     }
+    // Sum over the 32 lanes by the butterfly xor 16, 8, 4, 2, 1 (the order a per-token shuffle
+    // reduction uses), halving the tokens a lane carries at each step: 16 shuffles instead of 80.
+    // Lane l ends with token l >> 1.
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) part[(size_t(q) * kMaxTok + t) * kExperts + row] = acc;
+    for (int n = 8, o = 16; n >= 1; n >>= 1, o >>= 1) {
+      const bool hi = (lane & o) != 0;
+#pragma unroll
+      for (int i = 0; i < n; ++i) {
+        const float send = hi ? acc[i] : acc[i + n], keep = hi ? acc[i + n] : acc[i];
+        acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+      }
+    }
+    acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
+    const int t = lane >> 1;
+    if (!(lane & 1) && t < T) part[(size_t(q) * kMaxTok + t) * kExperts + row] = acc[0];
   }
   // activation quantization, one warp per ggml block, strided over every warp of the grid
   {
@@ -410,22 +431,41 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
   __threadfence();
   __syncthreads();
   if (tid == 0) {
+    const int ticket = atomicAdd(ws.sched + kSchedGroup + g, 1);
+    s_last = ticket == kRouteSplits - 1;
+    if (s_last) ws.sched[kSchedGroup + g] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (tid < kMaxTok * 16) {  // thread (token, row of the group)
+    const int t = tid >> 4, e = g * 16 + (tid & 15);
+    if (t < T) {
+      float v = 0.0f;
+#pragma unroll
+      for (int qq = 0; qq < kRouteSplits; ++qq) v += __ldcg(part + (size_t(qq) * kMaxTok + t) * kExperts + e);
+      logits[size_t(t) * stride + e] = v;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
     const int ticket = atomicAdd(ws.sched + kSchedRoute, 1);
-    s_last = ticket == int(gridDim.x) - 1;
+    s_last = ticket == kRouteGroups - 1;
     if (s_last) ws.sched[kSchedRoute] = 0;
   }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // slices added in order 0..4 (fixed: repeated calls are bitwise identical); thread e <-> expert e
-  for (int t = 0; t < T; ++t) {
-    float v = 0.0f;
+  {  // thread e <-> expert e: all logits into shared memory, loads issued together
+    float v[kMaxTok];
 #pragma unroll
-    for (int qq = 0; qq < kRouteSplits; ++qq) v += __ldcg(part + (size_t(qq) * kMaxTok + t) * kExperts + tid);
-    logits[size_t(t) * stride + tid] = v;
+    for (int t = 0; t < kMaxTok; ++t) v[t] = t < T ? __ldcg(logits + size_t(t) * stride + tid) : 0.0f;
+#pragma unroll
+    for (int t = 0; t < kMaxTok; ++t) s_x[t][tid] = v[t];
   }
   __syncthreads();
-  select_block([&](int t, int e) { return logits[size_t(t) * stride + e]; }, slot_of, T, ws, nullptr, remote_ok);
+  select_block([&](int t, int e) { return s_x[t][e]; }, slot_of, T, ws, nullptr, remote_ok);
 }
 
 // ------------------------------------------------------------------------------ streaming skeleton
