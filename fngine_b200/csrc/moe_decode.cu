@@ -315,14 +315,16 @@ __global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ l
 }
 
 // Router projection, activation quantization and selection in one launch (the head of the fused
-// layer call). Block (g, q) projects router rows 16g..16g+15 over the K slice [512q, 512q+512): the
-// x slice of all tokens sits in shared memory, one warp per row, all tokens in flight at once;
-// partial sums go to `part` [5][16][512]. Every block also quantizes a share of the activation
-// blocks. Hand-offs use device tickets, nobody waits: the block that finishes last in its row
-// group adds the group's five slices in order 0..4 (fixed: repeated calls are bitwise identical)
-// and stores the logits; the row group that finishes last runs the selection.
-constexpr int kRouteSplits = 5, kRouteSlice = H / kRouteSplits;  // 512
-constexpr int kRouteGroups = kExperts / 16;                      // 32
+// layer call). Block (g, q) projects router rows 32g..32g+31 over the K slice [320q, 320q+320): the
+// x slice of all tokens sits in shared memory, one warp per row pair (every x value read from
+// shared memory feeds two rows), all tokens in flight at once; partial sums go to `part`
+// [8][16][512]. 128 blocks: one per SM, no second wave. Every block also quantizes a share of the
+// activation blocks. Hand-offs use device tickets, nobody waits: the block that finishes last in its
+// row group adds the group's eight slices in order 0..7 (fixed: repeated calls are bitwise
+// identical) and stores the logits; the row group that finishes last runs the selection.
+constexpr int kRouteSplits = 8, kRouteSlice = H / kRouteSplits;  // 320
+constexpr int kRouteGroups = kExperts / 32;                      // 16
+static_assert(kRouteSlice == 320, "lane layout below: two 128-element chunks and a 64-element tail");
 
 template <bool XBF16>
 __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restrict__ w, const void* __restrict__ xv,
@@ -332,8 +334,10 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
   pdl_launch_dependents();
   pdl_wait_prior();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  __shared__ __align__(16) float s_x[kMaxTok][kRouteSlice];  // x slice; later the logits [token][expert]
+  // x slice [token][320]; later the logits [token][expert]
+  __shared__ __align__(16) float s_buf[kMaxTok * kExperts];
   __shared__ int s_last;
+  float(*s_x)[kRouteSlice] = reinterpret_cast<float(*)[kRouteSlice]>(s_buf);
   const int g = blockIdx.x / kRouteSplits, q = blockIdx.x - g * kRouteSplits;
   for (int i = tid; i < T * (kRouteSlice / 4); i += 512) {
     const int t = i / (kRouteSlice / 4), c = i - t * (kRouteSlice / 4);
@@ -348,41 +352,55 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
     }
     reinterpret_cast<float4*>(&s_x[t][0])[c] = v;
   }
-  const int row = g * 16 + warp;
-  float wr[16];
-  {
-    const uint2* wp = reinterpret_cast<const uint2*>(w + size_t(row) * H + q * kRouteSlice);
+  const int row0 = g * 32 + 2 * warp;
+  float wr[2][10];  // lane holds elements 128c + 4 lane .. +3 (c = 0, 1) and 256 + 2 lane, +1 of the slice
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {  // lane holds elements 128c + 4 lane .. +3 of the slice
-      const uint2 u = wp[c * 32 + lane];
-      wr[4 * c + 0] = __uint_as_float(u.x << 16);
-      wr[4 * c + 1] = __uint_as_float(u.x & 0xFFFF0000u);
-      wr[4 * c + 2] = __uint_as_float(u.y << 16);
-      wr[4 * c + 3] = __uint_as_float(u.y & 0xFFFF0000u);
+  for (int r = 0; r < 2; ++r) {
+    const __nv_bfloat16* wrow = w + size_t(row0 + r) * H + q * kRouteSlice;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const uint2 u = reinterpret_cast<const uint2*>(wrow)[c * 32 + lane];
+      wr[r][4 * c + 0] = __uint_as_float(u.x << 16);
+      wr[r][4 * c + 1] = __uint_as_float(u.x & 0xFFFF0000u);
+      wr[r][4 * c + 2] = __uint_as_float(u.y << 16);
+      wr[r][4 * c + 3] = __uint_as_float(u.y & 0xFFFF0000u);
     }
+    const uint32_t u = reinterpret_cast<const uint32_t*>(wrow + 256)[lane];
+    wr[r][8] = __uint_as_float(u << 16);
+    wr[r][9] = __uint_as_float(u & 0xFFFF0000u);
   }
   __syncthreads();
   {
-    float acc[kMaxTok];
+    float acc[2 * kMaxTok];  // [row of the pair][token]
 #pragma unroll
     for (int t = 0; t < kMaxTok; ++t) {
-      acc[t] = 0.0f;
+      float a0 = 0.0f, a1 = 0.0f;
       if (t < T) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float4 xv4 = reinterpret_cast<const float4*>(&s_x[t][0])[c * 32 + lane];
-          acc[t] = fmaf(wr[4 * c + 0], xv4.x, acc[t]);
-          acc[t] = fmaf(wr[4 * c + 1], xv4.y, acc[t]);
-          acc[t] = fmaf(wr[4 * c + 2], xv4.z, acc[t]);
-          acc[t] = fmaf(wr[4 * c + 3], xv4.w, acc[t]);
+        for (int c = 0; c < 2; ++c) {
+          const float4 x4 = reinterpret_cast<const float4*>(&s_x[t][0])[c * 32 + lane];
+          a0 = fmaf(wr[0][4 * c + 0], x4.x, a0);
+          a1 = fmaf(wr[1][4 * c + 0], x4.x, a1);
+          a0 = fmaf(wr[0][4 * c + 1], x4.y, a0);
+          a1 = fmaf(wr[1][4 * c + 1], x4.y, a1);
+          a0 = fmaf(wr[0][4 * c + 2], x4.z, a0);
+          a1 = fmaf(wr[1][4 * c + 2], x4.z, a1);
+          a0 = fmaf(wr[0][4 * c + 3], x4.w, a0);
+          a1 = fmaf(wr[1][4 * c + 3], x4.w, a1);
         }
+        const float2 x2 = reinterpret_cast<const float2*>(&s_x[t][256])[lane];
+        a0 = fmaf(wr[0][8], x2.x, a0);
+        a1 = fmaf(wr[1][8], x2.x, a1);
+        a0 = fmaf(wr[0][9], x2.y, a0);
+        a1 = fmaf(wr[1][9], x2.y, a1);
       }
+      acc[t] = a0;
+      acc[kMaxTok + t] = a1;
     }
-    // Sum over the 32 lanes by the butterfly xor 16, 8, 4, 2, 1 (the order a per-token shuffle
-    // reduction uses), halving the tokens a lane carries at each step: 16 shuffles instead of 80.
-    // Lane l ends with token l >> 1.
+    // Sum over the 32 lanes by the butterfly xor 16, 8, 4, 2, 1, halving the values a lane carries
+    // at each step: 31 shuffles for the 32 (row, token) sums. Lane l ends with row l >> 4, token l & 15.
 #pragma unroll
-    for (int n = 8, o = 16; n >= 1; n >>= 1, o >>= 1) {
+    for (int n = 16, o = 16; n >= 1; n >>= 1, o >>= 1) {
       const bool hi = (lane & o) != 0;
 #pragma unroll
       for (int i = 0; i < n; ++i) {
@@ -390,9 +408,8 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
         acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
       }
     }
-    acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
-    const int t = lane >> 1;
-    if (!(lane & 1) && t < T) part[(size_t(q) * kMaxTok + t) * kExperts + row] = acc[0];
+    const int t = lane & 15;
+    if (t < T) part[(size_t(q) * kMaxTok + t) * kExperts + row0 + (lane >> 4)] = acc[0];
   }
   // activation quantization, one warp per ggml block, strided over every warp of the grid
   {
@@ -438,8 +455,8 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  if (tid < kMaxTok * 16) {  // thread (token, row of the group)
-    const int t = tid >> 4, e = g * 16 + (tid & 15);
+  {  // thread (token, row of the group)
+    const int t = tid >> 5, e = g * 32 + lane;
     if (t < T) {
       float v = 0.0f;
 #pragma unroll
@@ -462,10 +479,10 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
 #pragma unroll
     for (int t = 0; t < kMaxTok; ++t) v[t] = t < T ? __ldcg(logits + size_t(t) * stride + tid) : 0.0f;
 #pragma unroll
-    for (int t = 0; t < kMaxTok; ++t) s_x[t][tid] = v[t];
+    for (int t = 0; t < kMaxTok; ++t) s_buf[t * kExperts + tid] = v[t];
   }
   __syncthreads();
-  select_block([&](int t, int e) { return s_x[t][e]; }, slot_of, T, ws, nullptr, remote_ok);
+  select_block([&](int t, int e) { return s_buf[t * kExperts + e]; }, slot_of, T, ws, nullptr, remote_ok);
 }
 
 // ------------------------------------------------------------------------------ streaming skeleton
@@ -1295,8 +1312,8 @@ static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_
   if (layout->inter != ws->inter || layout->gate_up_format != ws->gate_up_format ||
       layout->down_format != ws->down_format)
     return invalid("layer_decode: workspace was made for a different layout");
-  // the [5][16][512] slice sums borrow the head of ws->partial, which nothing reads before the down kernel
-  const dim3 grid(kExperts / 16 * kRouteSplits), block(512);
+  // the [8][16][512] slice sums borrow the head of ws->partial, which nothing reads before the down kernel
+  const dim3 grid(kRouteGroups * kRouteSplits), block(512);
   cudaError_t e =
       x_dtype == FB_DT_BF16
           ? launch_pdl(route_kernel<true>, grid, block, 0, as_stream(stream),
