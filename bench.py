@@ -430,7 +430,7 @@ def run_ours(args, rank, world, local_rank):
     del layers
     torch.cuda.empty_cache()
     fp8 = fp8_gemm_section(torch) if want("fp8") else None
-    pre = prefill_section(torch) if want("prefill") else None
+    pre = prefill_section(torch, n_layers=args.prefill_layers) if want("prefill") else None
     peak, peak_src = peaks()
     gu_ach = sum(gu_bytes) / (sum(gu_ms) * 1e-3) / 1e9
     value = step_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -474,6 +474,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--prefill-layers", type=int, default=48,
+                    help="layers of the prefill stack section (a profiler run wants 1)")
     ap.add_argument("--sections", default="all",
                     help="extra sections beside the headline decode measurement: all | none | comma list of "
                          "batches,cpu,fp8,prefill (a profiler run wants none)")

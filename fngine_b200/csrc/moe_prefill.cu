@@ -111,7 +111,7 @@ struct Abort {
   __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity) const {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
-      if (*flag) return false;  // another role gave up: fall through every later wait
+      if ((i & 31u) == 31u && *flag) return false;  // another role gave up: fall through every later wait
     }
     *flag = 1;
     atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
