@@ -164,6 +164,12 @@ def workload_config(args, layers_per_step):
             "activation_format": "Q8_K (reference CPU tier numerics)"}
 
 
+# DRAM bytes moved / algorithmic bytes of one gate_up_kernel launch, from an ncu capture of layer 0 of the
+# benchmark workload (profiles/gate_up_down_iq3s_decode_b16.md): traffic grows with the expert count like the
+# algorithmic bytes do, so the ratio carries over to the other layers.
+GATE_UP_DRAM_TRAFFIC_RATIO = 160.57 / 156.85
+
+
 def fp8_gemm_section(torch, iters=10):
     """The FP8-row dense GEMM of the benchmark definition (bf16 [4096x2560] x E4M3 [9216x2560] -> bf16),
     each call timed alone with CUDA events after an L2 flush; the library FP8 GEMM of the same shape
@@ -443,7 +449,11 @@ def run_ours(args, rank, world, local_rank):
         "distinct_experts_per_layer": distinct,
         "frac_of_hbm_peak": value / peak,
         "roofline": {"bound": "hbm", "kernel": "gate_up_kernel<IQ3_S>", "achieved": gu_ach, "peak": peak,
-                     "unit": "GB/s", "frac": gu_ach / peak, "peak_source": peak_src, "traffic": None,
+                     "unit": "GB/s", "frac": gu_ach / peak, "peak_source": peak_src,
+                     "traffic": GATE_UP_DRAM_TRAFFIC_RATIO * sum(gu_bytes) / len(gu_bytes),
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one gate_up_kernel launch on "
+                                       "layer 0 of this workload (160.57 MB for 156.85 MB algorithmic), scaled by the "
+                                       "expert count of each layer",
                      "us_per_launch": sum(gu_ms) / len(gu_ms) * 1e3,
                      "algorithmic_bytes_per_launch": sum(gu_bytes) / len(gu_bytes),
                      "down_kernel": {"achieved": sum(dn_bytes) / (sum(dn_ms) * 1e-3) / 1e9,
