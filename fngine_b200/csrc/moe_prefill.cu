@@ -392,8 +392,22 @@ __global__ void __launch_bounds__(256) pf_topk_kernel(const float* __restrict__ 
       }
     topk_e[t * kTopK + lane] = id;
     topk_w[t * kTopK + lane] = wt;
-    atomicAdd(&count[id], 1);
+    if (count) atomicAdd(&count[id], 1);
   }
+}
+
+// Expert-parallel routing: the (expert, weight) lists arrive with the dispatched rows; entries of
+// experts other ranks own ([lo, hi) is this rank's range) become -1 and take no part.
+__global__ void __launch_bounds__(256) pf_import_kernel(const int32_t* __restrict__ in_e, const float* __restrict__ in_w,
+                                                        int lo, int hi, int n, int32_t* __restrict__ topk_e,
+                                                        float* __restrict__ topk_w, int32_t* __restrict__ count) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const int e = in_e[i];
+  const bool local = e >= lo && e < hi;
+  topk_e[i] = local ? e : -1;
+  topk_w[i] = in_w[i];
+  if (local) atomicAdd(&count[e], 1);
 }
 
 // Exclusive scan of the counts and the unit lists of both grouped GEMMs (one block of 512).
@@ -465,10 +479,29 @@ __global__ void __launch_bounds__(256) pf_scatter_kernel(const int32_t* __restri
   const int i = blockIdx.x * 256 + threadIdx.x;
   if (i >= T * kTopK) return;
   const int e = topk_e[i];
+  if (e < 0) {  // an expert of another rank
+    token_pair[i] = -1;
+    return;
+  }
   const int pos = offset[e] + atomicAdd(&cursor[e], 1);
   pair_token[pos] = i / kTopK;
   pair_weight[pos] = topk_w[i];
   token_pair[i] = pos;
+}
+
+// Owner-side sum of an expert-parallel step: y[t] = sum over source ranks d, in rank order, of the
+// partial row that rank d returned for token t (row_of[t][d] = its row in `recv`, -1 if rank d held
+// none of the token's experts).
+__global__ void __launch_bounds__(256) ep_scatter_sum_kernel(const float* __restrict__ recv,
+                                                             const int32_t* __restrict__ row_of, int n_ranks,
+                                                             float* __restrict__ y) {
+  const int t = blockIdx.y, n = blockIdx.x * 256 + threadIdx.x;
+  float acc = 0.0f;
+  for (int d = 0; d < n_ranks; ++d) {
+    const int r = row_of[t * n_ranks + d];
+    if (r >= 0) acc += recv[size_t(r) * H + n];
+  }
+  y[size_t(t) * H + n] = acc;
 }
 
 // ------------------------------------------------------------------------------ grouped gate/up
@@ -809,16 +842,22 @@ __global__ void __launch_bounds__(256) pf_combine_kernel(const int32_t* __restri
   const int t = blockIdx.y;
   __shared__ int s_order[kTopK];
   if (threadIdx.x < kTopK) {
-    const int e = topk_e[t * kTopK + threadIdx.x];
+    // ascending expert id; entries without a local pair (expert-parallel shards) sort last
+    auto key = [&](int k) {
+      const int e = topk_e[t * kTopK + k];
+      return e < 0 ? kExperts + k : e;
+    };
+    const int mine = key(threadIdx.x);
     int rank = 0;
-    for (int k = 0; k < kTopK; ++k) rank += topk_e[t * kTopK + k] < e ? 1 : 0;
+    for (int k = 0; k < kTopK; ++k) rank += key(k) < mine ? 1 : 0;
     s_order[rank] = token_pair[t * kTopK + threadIdx.x];
   }
   __syncthreads();
   const int n = blockIdx.x * 256 + threadIdx.x;
   float y = 0.0f;
 #pragma unroll
-  for (int k = 0; k < kTopK; ++k) y += yp[size_t(s_order[k]) * H + n];
+  for (int k = 0; k < kTopK; ++k)
+    if (s_order[k] >= 0) y += yp[size_t(s_order[k]) * H + n];
   if (y_shared) y += y_shared[size_t(t) * H + n];
   if (y_out) y_out[size_t(t) * H + n] = y;
   if (X) {
@@ -953,6 +992,42 @@ int32_t fb_moe_route(const float* router_logits, int32_t logits_stride, const vo
                                                                  ws->expert_cursor, ws->pair_token, ws->pair_weight,
                                                                  ws->token_pair, tokens);
   return check_launch("route");
+}
+
+int32_t fb_moe_topk(const float* router_logits, int32_t logits_stride, int32_t tokens, int32_t* topk_expert,
+                    float* topk_weight, void* stream) {
+  if (!router_logits || logits_stride < kExperts || tokens < 1 || !topk_expert || !topk_weight)
+    return invalid("topk: bad arguments");
+  pf_topk_kernel<<<(tokens + 7) / 8, 256, 0, as_stream(stream)>>>(router_logits, logits_stride, tokens, topk_expert,
+                                                                 topk_weight, nullptr);
+  return check_launch("topk");
+}
+
+int32_t fb_moe_route_ep(const int32_t* topk_expert, const float* topk_weight, int32_t expert_lo, int32_t expert_hi,
+                        int32_t rows, const fb_moe_prefill_workspace* ws, void* stream) {
+  if (!topk_expert || !topk_weight || expert_lo < 0 || expert_hi > kExperts || expert_lo >= expert_hi ||
+      !pf_ws_ok(ws, rows))
+    return invalid("route_ep: bad arguments");
+  cudaStream_t s = as_stream(stream);
+  cudaError_t e = cudaMemsetAsync(ws->expert_count, 0, kExperts * 4, s);
+  if (e != cudaSuccess) return check_launch("route_ep: memset");
+  const int n = rows * kTopK;
+  pf_import_kernel<<<(n + 255) / 256, 256, 0, s>>>(topk_expert, topk_weight, expert_lo, expert_hi, n, ws->topk_expert,
+                                                   ws->topk_weight, ws->expert_count);
+  pf_scan_kernel<<<1, 512, 0, s>>>(ws->expert_count, ws->expert_offset, ws->expert_cursor,
+                                   static_cast<int4*>(ws->units_gate_up), static_cast<int4*>(ws->units_down), ws->meta,
+                                   ws->inter, ws->max_units_gate_up, ws->max_units_down);
+  pf_scatter_kernel<<<(n + 255) / 256, 256, 0, s>>>(ws->topk_expert, ws->topk_weight, ws->expert_offset,
+                                                    ws->expert_cursor, ws->pair_token, ws->pair_weight, ws->token_pair,
+                                                    rows);
+  return check_launch("route_ep");
+}
+
+int32_t fb_ep_scatter_sum(const float* recv, const int32_t* row_of, int32_t n_ranks, int32_t tokens, float* y,
+                          void* stream) {
+  if (!recv || !row_of || n_ranks < 1 || tokens < 1 || !y) return invalid("ep_scatter_sum: bad arguments");
+  ep_scatter_sum_kernel<<<dim3(H / 256, tokens), 256, 0, as_stream(stream)>>>(recv, row_of, n_ranks, y);
+  return check_launch("ep_scatter_sum");
 }
 
 int32_t fb_moe_grouped_gate_up(const fb_moe_expert_layout* layout, const uint8_t* const* expert_blob, const void* x_bf16,

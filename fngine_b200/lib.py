@@ -87,6 +87,9 @@ _SIGNATURES = {
     "fb_moe_layer_decode_ep": (_I32, [_P, C.POINTER(ExpertLayout), _P, _P, _I32, _I32, C.POINTER(DecodeWorkspace), _P, _P,
                                _P]),
     "fb_ep_sum_ranks": (_I32, [_P, _I32, _I32, _P, _P]),
+    "fb_moe_topk": (_I32, [_P, _I32, _I32, _P, _P, _P]),
+    "fb_moe_route_ep": (_I32, [_P, _P, _I32, _I32, _I32, C.POINTER(PrefillWorkspace), _P]),
+    "fb_ep_scatter_sum": (_I32, [_P, _P, _I32, _I32, _P, _P]),
     "fb_moe_layer_decode_static": (_I32, [_P, C.POINTER(ExpertLayout), _P, _I32, _I32, _P, _P]),
     "fb_linear_fp8_workspace_bytes": (C.c_size_t, [_I32, _I32, _I32]),
     "fb_linear_fp8": (_I32, [_P, _I32, _P, _P, _I32, _I32, _I32, _P, _P, C.c_size_t, _P]),

@@ -232,6 +232,22 @@ int32_t fb_moe_prefill_combine(const fb_moe_prefill_workspace* ws, const float* 
  * node; a rank's slot array holds only its own experts and `slot_of[e]` is the local slot of expert
  * e or -1 when another rank owns it (the role the reference gives to "cold" experts,
  * src/kernels/moe/moe.h:119-121). */
+/* Prefill, expert parallel. The owner of a token sends its bf16 row once to every rank that holds
+ * at least one of the token's ten experts, together with the token's (expert, weight) lists;
+ * fb_moe_topk makes those lists on the owner (the same top-10 rule as fb_moe_route), fb_moe_route_ep
+ * builds the receiving rank's pair and unit lists from them, keeping only experts in
+ * [expert_lo, expert_hi) (the others take no part: their pairs are skipped by the grouped kernels
+ * and by fb_moe_prefill_combine, whose output is then the partial sum over this rank's experts, in
+ * ascending expert order). `expert_blob` of the grouped kernels must be the [512] table of blob
+ * addresses indexed by GLOBAL expert id. fb_ep_scatter_sum adds, on the owner, the partial rows the
+ * ranks returned: y[t] = sum over d in rank order of recv[row_of[t][d]] (row_of < 0: rank d holds none
+ * of the token's experts). */
+int32_t fb_moe_topk(const float* router_logits, int32_t logits_stride, int32_t tokens, int32_t* topk_expert,
+                    float* topk_weight, void* stream);
+int32_t fb_moe_route_ep(const int32_t* topk_expert, const float* topk_weight, int32_t expert_lo, int32_t expert_hi,
+                        int32_t rows, const fb_moe_prefill_workspace* ws, void* stream);
+int32_t fb_ep_scatter_sum(const float* recv, const int32_t* row_of, int32_t n_ranks, int32_t tokens, float* y,
+                          void* stream);
 /* One decode layer over this rank's experts: x holds ALL tokens of the step (after dispatch),
  * y_partial[t] = sum over token t's LOCAL experts, in slot order; pairs of other ranks are skipped
  * and counted in the work list's n_cold. */

@@ -96,3 +96,83 @@ def _absent_rank_main(rank, world, port, out_dir):
 def test_missing_rank_ends_the_collective_with_an_error(tmp_path):
     mp.spawn(_absent_rank_main, args=(2, 29612, str(tmp_path)), nprocs=2, join=True)
     assert open(os.path.join(str(tmp_path), "outcome.txt")).read().startswith("error:")
+
+
+# ---------------------------------------------------------------------------------- prefill (all-to-all-v)
+from fngine_b200 import ep_prefill  # noqa: E402
+
+TP = 6  # tokens of the prefill exchange test (3 per rank)
+
+
+def test_prefill_dispatch_plan():
+    rng = np.random.default_rng(5)
+    for world in (1, 2, 4, 8):
+        ids = np.stack([rng.choice(512, size=10, replace=False) for _ in range(17)]).astype(np.int32)
+        send_tok, counts, row_of = ep_prefill.plan_dispatch(torch.from_numpy(ids), world)
+        per = 512 // world
+        want = [(d, t) for d in range(world) for t in range(17) if (ids[t] // per == d).any()]
+        got, pos = [], 0
+        for d in range(world):
+            for _ in range(counts[d]):
+                got.append((d, int(send_tok[pos])))
+                pos += 1
+        assert got == want  # once per (rank, token), ordered by rank then token
+        for i, (d, t) in enumerate(want):
+            assert int(row_of[t, d]) == i
+        assert int((row_of >= 0).sum()) == len(want)
+
+
+def _prefill_routing():
+    x = synth.to_bf16_bits(synth.activations(21, TP))
+    logits = (synth.normal(22, TP * 512) * 2).astype(np.float32).reshape(TP, 512)
+    ids, w = O.topk(logits)
+    return x, ids, w
+
+
+def _expert_row(e, x_bits):
+    _, y = O.expert_ffn_bf16(IQ3_S, IQ3_S, H, INTER, synth.expert_blob(IQ3_S, IQ3_S, INTER, SEED, e), x_bits)
+    return y[0]
+
+
+def _prefill_rank_main(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    x, ids, w = _prefill_routing()
+    lo, hi = ep.token_range(rank, world, TP)
+
+    def local_rows(x_rows, e_rows, w_rows, elo, ehi):  # what route_ep + grouped kernels + combine compute
+        out = np.zeros((x_rows.shape[0], H), dtype=np.float32)
+        for r in range(x_rows.shape[0]):
+            pairs = sorted((int(e), float(wt)) for e, wt in zip(e_rows[r].tolist(), w_rows[r].tolist()) if elo <= e < ehi)
+            assert pairs, "a row was sent to a rank that holds none of its experts"
+            for e, wt in pairs:  # ascending expert id
+                out[r] += np.float32(wt) * _expert_row(e, x_rows[r].numpy().view(np.uint16))
+        return torch.from_numpy(out)
+
+    def scatter_sum(y_back, row_of):
+        y = np.zeros((row_of.shape[0], H), dtype=np.float32)
+        for t in range(row_of.shape[0]):
+            for d in range(row_of.shape[1]):  # rank order
+                if row_of[t, d] >= 0:
+                    y[t] += y_back[int(row_of[t, d])].numpy()
+        return torch.from_numpy(y)
+
+    y, stats = ep_prefill.ep_layer_generic(torch.from_numpy(x[lo:hi].view(np.int16).copy()),
+                                           torch.from_numpy(ids[lo:hi].copy()), torch.from_numpy(w[lo:hi].copy()),
+                                           rank, world, local_rows, scatter_sum)
+    assert stats["rows_sent"] <= (hi - lo) * world
+    np.save(os.path.join(out_dir, "yp%d.npy" % rank), y.numpy())
+    dist.destroy_process_group()
+
+
+def test_two_rank_prefill_exchange_equals_single_rank(tmp_path):
+    mp.spawn(_prefill_rank_main, args=(2, 29613, str(tmp_path)), nprocs=2, join=True)
+    x, ids, w = _prefill_routing()
+    want = np.zeros((TP, H), dtype=np.float32)
+    for t in range(TP):
+        for e, wt in sorted(zip(ids[t].tolist(), w[t].tolist())):
+            want[t] += np.float32(wt) * _expert_row(int(e), x[t])
+    got = np.concatenate([np.load(os.path.join(str(tmp_path), "yp%d.npy" % r)) for r in range(2)])
+    err = max(np.linalg.norm(got[t] - want[t]) / np.linalg.norm(want[t]) for t in range(TP))
+    assert err <= 1e-5, err

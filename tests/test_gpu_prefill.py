@@ -138,3 +138,47 @@ def test_prefill_crowded_expert_spans_several_units():
     logits[::3, 300] += 10.0
     err = check_layer(IQ3_S, IQ3_S, 512, T, logits)
     print("prefill crowded expert: max rel L2 down %.2e, end to end %.2e" % err)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_expert_parallel_shards_match_single_gpu(world):
+    """The expert-parallel prefill pieces (fb_moe_topk, the dispatch plan, fb_moe_route_ep + grouped
+    kernels over one shard's experts, fb_ep_scatter_sum) run rank by rank on one GPU: the owners'
+    results equal the single-GPU layer up to the re-association of the per-token sum."""
+    torch = _torch()
+    from types import SimpleNamespace
+
+    from fngine_b200 import ep_prefill, moe, prefill
+    T, inter, seed = 96, 512, 77
+    layer = moe.synth_layer(IQ3_S, IQ3_S, inter, 512, seed)
+    ws = prefill.PrefillWorkspace(T, inter)
+    xd = torch.from_numpy(synth.to_bf16_bits(synth.activations(901, T)).view(np.int16)).cuda().view(torch.bfloat16)
+    logits = torch.from_numpy((synth.normal(902, T * 513) * 1.5).astype(np.float32).reshape(T, 513)).cuda()
+    want = run_prefill(torch, layer, ws, logits, xd, T).cpu().numpy()
+    per = 512 // world
+    stride = layer.layout.blob_stride
+    shards = []
+    for d in range(world):
+        table = np.zeros(512, dtype=np.int64)
+        table[d * per:(d + 1) * per] = layer.slots.data_ptr() + stride * np.arange(d * per, (d + 1) * per, dtype=np.int64)
+        shards.append(SimpleNamespace(layer=layer, blob_table=torch.from_numpy(table).cuda(), rank=d, world=world))
+    got = np.zeros((T, H), dtype=np.float32)
+    tl = T // world
+    for owner in range(world):
+        lo, hi = owner * tl, (owner + 1) * tl
+        e, w = ep_prefill.topk(logits[lo:hi].contiguous())
+        send_tok, counts, row_of = ep_prefill.plan_dispatch(e, world)
+        lists = ep_prefill.pack_lists(e, w).index_select(0, send_tok)
+        xs = xd[lo:hi].index_select(0, send_tok)
+        back, pos = [], 0
+        for d in range(world):  # what rank d computes for the rows this owner sends it
+            n = counts[d]
+            er, wr = ep_prefill.unpack_lists(lists[pos:pos + n])
+            back.append(ep_prefill.local_rows(shards[d], ws, xs[pos:pos + n].contiguous(), er, wr, d * per, (d + 1) * per))
+            pos += n
+        y = ep_prefill.scatter_sum(torch.cat(back), row_of)
+        torch.cuda.synchronize()
+        got[lo:hi] = y.cpu().numpy()
+    assert ws.status() == 0
+    err = max(rel_l2(got[t], want[t]) for t in range(T))
+    assert err <= 1e-5, err
