@@ -231,6 +231,13 @@ def bench_main(args, rank, world, local_rank):
         got = y0.cpu().numpy()
         parity = float(max(np.linalg.norm(got[i] - want[i]) / np.linalg.norm(want[i]) for i in range(hi - lo)))
     dist.barrier()
+    # the 48-layer prefill stack, expert-parallel (the decode layers are released first)
+    pre = None
+    if args.sections == "all" or "prefill" in args.sections.split(","):
+        from . import ep_prefill
+        del layers
+        torch.cuda.empty_cache()
+        pre = ep_prefill.bench_section(rank, world, n_layers=args.prefill_layers)
     if rank == 0:
         peak, peak_src = peaks()
         value = step_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -249,7 +256,7 @@ def bench_main(args, rank, world, local_rank):
                         "h2d_bytes_per_step": (hi - lo) * HIDDEN * 4 * Lr * world,
                         "d2h_bytes_per_step": (hi - lo) * HIDDEN * 4 * Lr * world, "ms_per_step": e2e_ms / args.steps},
                 "gpu_launches": args.steps * Lr * 5 * world, "parity_vs_cpu_max_rel_l2": parity,
-                "device_status": status, "clocks": clocks,
+                "device_status": status, "clocks": clocks, "prefill_stack": pre,
                 "cpu_baseline": None}
         print(json.dumps(line))
     dist.destroy_process_group()

@@ -134,7 +134,7 @@ def _expert_row(e, x_bits):
     return y[0]
 
 
-def _prefill_rank_main(rank, world, port, out_dir):
+def _prefill_rank_main(rank, world, port, out_dir, mode):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -145,7 +145,7 @@ def _prefill_rank_main(rank, world, port, out_dir):
         out = np.zeros((x_rows.shape[0], H), dtype=np.float32)
         for r in range(x_rows.shape[0]):
             pairs = sorted((int(e), float(wt)) for e, wt in zip(e_rows[r].tolist(), w_rows[r].tolist()) if elo <= e < ehi)
-            assert pairs, "a row was sent to a rank that holds none of its experts"
+            assert pairs or mode == "dense", "a row was sent to a rank that holds none of its experts"
             for e, wt in pairs:  # ascending expert id
                 out[r] += np.float32(wt) * _expert_row(e, x_rows[r].numpy().view(np.uint16))
         return torch.from_numpy(out)
@@ -158,16 +158,21 @@ def _prefill_rank_main(rank, world, port, out_dir):
                     y[t] += y_back[int(row_of[t, d])].numpy()
         return torch.from_numpy(y)
 
-    y, stats = ep_prefill.ep_layer_generic(torch.from_numpy(x[lo:hi].view(np.int16).copy()),
-                                           torch.from_numpy(ids[lo:hi].copy()), torch.from_numpy(w[lo:hi].copy()),
-                                           rank, world, local_rows, scatter_sum)
-    assert stats["rows_sent"] <= (hi - lo) * world
+    args = (torch.from_numpy(x[lo:hi].view(np.int16).copy()), torch.from_numpy(ids[lo:hi].copy()),
+            torch.from_numpy(w[lo:hi].copy()), rank, world, local_rows)
+    if mode == "dense":
+        y, stats = ep_prefill.ep_layer_dense(*args, ep.combine_sum)
+        assert stats["rows_received"] == TP
+    else:
+        y, stats = ep_prefill.ep_layer_generic(*args, scatter_sum)
+        assert stats["rows_sent"] <= (hi - lo) * world
     np.save(os.path.join(out_dir, "yp%d.npy" % rank), y.numpy())
     dist.destroy_process_group()
 
 
-def test_two_rank_prefill_exchange_equals_single_rank(tmp_path):
-    mp.spawn(_prefill_rank_main, args=(2, 29613, str(tmp_path)), nprocs=2, join=True)
+@pytest.mark.parametrize("mode,port", [("sparse", 29613), ("dense", 29614)])
+def test_two_rank_prefill_exchange_equals_single_rank(tmp_path, mode, port):
+    mp.spawn(_prefill_rank_main, args=(2, port, str(tmp_path), mode), nprocs=2, join=True)
     x, ids, w = _prefill_routing()
     want = np.zeros((TP, H), dtype=np.float32)
     for t in range(TP):
