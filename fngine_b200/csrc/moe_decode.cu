@@ -13,6 +13,8 @@
 // for IQ3_S weights, Q8_0 for IQ4_NL, integer sums per block, one fp32 scale step per block.
 #include "iq_decode.cuh"
 
+#include <cstring>
+
 #include <cuda_bf16.h>
 
 namespace fb {
@@ -27,7 +29,26 @@ constexpr int kTT = 2;  // tokens of one work item handled per pass over a stage
 // ws.sched: [0] gate/up tile counter, [1] down tile counter, [2] finished route blocks,
 // [8..168) item order
 constexpr int kSchedOrderBase = 8;
+constexpr uint32_t kPeerSpinLimit = 1u << 20;  // polls of a peer-written flag before giving up (about a second)
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Step counters only grow: true once *p has reached `want`, false when the limit ran out.
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want) {
+  for (uint32_t i = 0; i < kPeerSpinLimit; ++i) {
+    if (int32_t(ld_acquire_sys(p) - want) >= 0) return true;
+    __nanosleep(200);
+  }
+  return false;
+}
 constexpr int kSchedRoute = 2;
+constexpr int kSchedEpSend = 3;  // ticket of ep_combine_send_kernel
 constexpr int kSchedGroup = 192;  // 32 row-group tickets of route_kernel
 constexpr int kSchedInts = 256;
 
@@ -330,10 +351,17 @@ template <bool XBF16>
 __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restrict__ w, const void* __restrict__ xv,
                                                     int T, float* __restrict__ logits, int stride,
                                                     float* __restrict__ part, fb_moe_decode_workspace ws,
-                                                    const int32_t* __restrict__ slot_of, bool remote_ok) {
+                                                    const int32_t* __restrict__ slot_of, bool remote_ok,
+                                                    const uint32_t* __restrict__ wait_flags, int n_wait,
+                                                    uint32_t wait_value) {
   pdl_launch_dependents();
   pdl_wait_prior();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (wait_flags) {  // expert-parallel step: x rows are written by the peers, one flag per source rank
+    if (tid < n_wait && !wait_flag(wait_flags + tid, wait_value))
+      atomicMax(ws.status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+    __syncthreads();
+  }
   // x slice [token][320]; later the logits [token][expert]
   __shared__ __align__(16) float s_buf[kMaxTok * kExperts];
   __shared__ int s_last;
@@ -1123,6 +1151,76 @@ __global__ void __launch_bounds__(256) sum_ranks_kernel(const float* __restrict_
   y[i] = v;
 }
 
+// ------------------------------------------------------------------------------ peer-memory exchange
+// Expert-parallel decode without a collective library call in the step: ranks write straight into
+// each other's buffers over NVLink (plain peer stores) and publish a step counter per source rank
+// with a system-scope release store; readers poll their OWN memory with acquire loads, a bounded
+// number of times. Buffers are double-buffered by step parity: a rank can be at most one step ahead
+// of a peer (it needs that peer's partial rows to finish a step), so parity p of step k+2 is never
+// written while anyone still reads step k.
+//   x_all   [2][16][2560] fp32    all tokens of the step, rows written by their owners
+//   y_parts [2][8][16][2560] fp32 [parity][source rank][local token]: partial rows for this rank's tokens
+//   flags   [2][2][8] u32         [parity][0 = x rows, 1 = partial rows][source rank] = step number
+constexpr int kEpMaxRanks = FB_EP_MAX_RANKS;
+
+// One block per destination rank: copy this rank's rows, fence, publish.
+__global__ void __launch_bounds__(256) ep_publish_x_kernel(fb_ep_peers peers, const float* __restrict__ x_local,
+                                                           int tpr, int parity, uint32_t step) {
+  const int d = blockIdx.x;
+  float4* dst = reinterpret_cast<float4*>(peers.x_all[d] + (size_t(parity) * kMaxTok + size_t(peers.rank) * tpr) * H);
+  const float4* src = reinterpret_cast<const float4*>(x_local);
+  for (int i = threadIdx.x; i < tpr * (H / 4); i += 256) dst[i] = src[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) st_release_sys(peers.flags[d] + (parity * 2 + 0) * kEpMaxRanks + peers.rank, step);
+}
+
+// The combine of an expert-parallel step: token t's partial row (its local pairs, slot order) goes
+// straight into its owner's y_parts; the block that finishes last publishes this rank's flag on
+// every peer.
+__global__ void __launch_bounds__(256) ep_combine_send_kernel(fb_moe_decode_workspace ws, fb_ep_peers peers, int tpr,
+                                                              int parity, uint32_t step) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  const int t = blockIdx.y;
+  const fb_moe_decode_work* work = ws.work;
+  const int np = min(max(work->token_pair_count[t], 0), kTopK);
+  const int n = blockIdx.x * 256 + threadIdx.x;
+  float y = 0.0f;
+  for (int k = 0; k < np; ++k) y += ws.partial[size_t(work->token_pairs[t][k]) * H + n];
+  const int d = t / tpr, i = t - d * tpr;
+  peers.y_parts[d][((size_t(parity) * kEpMaxRanks + peers.rank) * kMaxTok + i) * H + n] = y;
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(ws.sched + kSchedEpSend, 1);
+    s_last = ticket == int(gridDim.x * gridDim.y) - 1;
+    if (s_last) ws.sched[kSchedEpSend] = 0;
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x < peers.n_ranks) {
+    __threadfence_system();
+    st_release_sys(peers.flags[threadIdx.x] + (parity * 2 + 1) * kEpMaxRanks + peers.rank, step);
+  }
+}
+
+// Owner side: wait (bounded) for every rank's partial rows of this step, add them in rank order.
+__global__ void __launch_bounds__(256) ep_wait_sum_kernel(const float* __restrict__ y_parts,
+                                                          const uint32_t* __restrict__ flags, int n_ranks, int parity,
+                                                          uint32_t step, float* __restrict__ y, uint32_t* status) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  if (threadIdx.x < n_ranks && !wait_flag(flags + (parity * 2 + 1) * kEpMaxRanks + threadIdx.x, step))
+    atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+  __syncthreads();
+  const int i = blockIdx.y, n = blockIdx.x * 256 + threadIdx.x;
+  float acc = 0.0f;
+  for (int s = 0; s < n_ranks; ++s)
+    acc += __ldcg(y_parts + ((size_t(parity) * kEpMaxRanks + s) * kMaxTok + i) * H + n);
+  y[size_t(i) * H + n] = acc;
+}
+
 // ------------------------------------------------------------------------------ host side
 template <class K>
 cudaError_t opt_in_smem(K kernel, size_t bytes) {
@@ -1303,11 +1401,12 @@ int32_t fb_moe_combine(const fb_moe_decode_workspace* ws, const float* y_shared,
 static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_layout* layout,
                                  const int32_t* slot_of, bool remote_ok, const void* x, int32_t x_dtype,
                                  int32_t tokens, const fb_moe_decode_workspace* ws, float* logits_scratch, float* y_out,
-                                 void* stream) {
+                                 void* stream, const uint32_t* wait_flags = nullptr, int n_wait = 0,
+                                 uint32_t wait_value = 0, bool with_combine = true) {
   // Four launches: route (router projection + activation quantization + selection), gate/up, down,
   // combine. Same arithmetic, in the same order, as the five separate entry points.
-  if (!router_w_bf16 || !x || !y_out || !logits_scratch || !layout_ok(layout) || !ws_ok(ws) || tokens < 1 ||
-      tokens > kMaxTok)
+  if (!router_w_bf16 || !x || (!y_out && with_combine) || !logits_scratch || !layout_ok(layout) || !ws_ok(ws) ||
+      tokens < 1 || tokens > kMaxTok)
     return invalid("layer_decode: bad arguments (tokens must be 1..16, logits scratch [tokens][513] required)");
   if (layout->inter != ws->inter || layout->gate_up_format != ws->gate_up_format ||
       layout->down_format != ws->down_format)
@@ -1318,15 +1417,15 @@ static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_
       x_dtype == FB_DT_BF16
           ? launch_pdl(route_kernel<true>, grid, block, 0, as_stream(stream),
                        static_cast<const __nv_bfloat16*>(router_w_bf16), x, tokens, logits_scratch, int(FB_ROUTER_ROWS),
-                       ws->partial, *ws, slot_of, remote_ok)
+                       ws->partial, *ws, slot_of, remote_ok, wait_flags, n_wait, wait_value)
           : launch_pdl(route_kernel<false>, grid, block, 0, as_stream(stream),
                        static_cast<const __nv_bfloat16*>(router_w_bf16), x, tokens, logits_scratch, int(FB_ROUTER_ROWS),
-                       ws->partial, *ws, slot_of, remote_ok);
+                       ws->partial, *ws, slot_of, remote_ok, wait_flags, n_wait, wait_value);
   if (e != cudaSuccess) return check_launch("layer_decode: route");
   int32_t st = fb_moe_hot_gate_up(layout, tokens, ws, stream);
   if (st) return st;
   st = launch_down(layout, ws, stream);
-  if (st) return st;
+  if (st || !with_combine) return st;
   return fb_moe_combine(ws, nullptr, nullptr, 0, nullptr, nullptr, nullptr, y_out, tokens, 0, nullptr, 0.0f, stream);
 }
 
@@ -1344,6 +1443,94 @@ int32_t fb_moe_layer_decode_ep(const void* router_w_bf16, const fb_moe_expert_la
   if (!slot_of) return invalid("layer_decode_ep: slot_of (expert -> local slot, -1 = another rank) is required");
   return layer_decode_impl(router_w_bf16, layout, slot_of, true, x, x_dtype, tokens, ws, logits_scratch, y_partial,
                            stream);
+}
+
+int32_t fb_moe_layer_decode_ep_p2p(const void* router_w_bf16, const fb_moe_expert_layout* layout,
+                                   const int32_t* slot_of, const float* x_local, int32_t tokens,
+                                   const fb_ep_peers* peers, uint32_t step, const fb_moe_decode_workspace* ws,
+                                   float* logits_scratch, float* y_local, void* stream) {
+  if (!slot_of || !x_local || !y_local || !peers || peers->n_ranks < 1 || peers->n_ranks > kEpMaxRanks ||
+      peers->rank < 0 || peers->rank >= peers->n_ranks || tokens < peers->n_ranks || tokens > kMaxTok ||
+      tokens % peers->n_ranks || step == 0)
+    return invalid("layer_decode_ep_p2p: bad arguments (tokens a multiple of the rank count, at most 16; step >= 1)");
+  for (int d = 0; d < peers->n_ranks; ++d)
+    if (!peers->x_all[d] || !peers->y_parts[d] || !peers->flags[d])
+      return invalid("layer_decode_ep_p2p: a peer buffer address is missing");
+  const int R = peers->n_ranks, tpr = tokens / R, parity = int(step & 1u);
+  cudaStream_t s = as_stream(stream);
+  ep_publish_x_kernel<<<R, 256, 0, s>>>(*peers, x_local, tpr, parity, step);
+  if (cudaGetLastError() != cudaSuccess) return check_launch("layer_decode_ep_p2p: publish");
+  const float* x_all = peers->x_all[peers->rank] + size_t(parity) * kMaxTok * H;
+  const uint32_t* my_flags = peers->flags[peers->rank];
+  int32_t st = layer_decode_impl(router_w_bf16, layout, slot_of, true, x_all, FB_DT_F32, tokens, ws, logits_scratch,
+                                 nullptr, stream, my_flags + (parity * 2 + 0) * kEpMaxRanks, R, step, false);
+  if (st) return st;
+  cudaError_t e = launch_pdl(ep_combine_send_kernel, dim3(H / 256, tokens), dim3(256), 0, s, *ws, *peers, tpr, parity,
+                             step);
+  if (e != cudaSuccess) return check_launch("layer_decode_ep_p2p: combine");
+  e = launch_pdl(ep_wait_sum_kernel, dim3(H / 256, tpr), dim3(256), 0, s,
+                 static_cast<const float*>(peers->y_parts[peers->rank]), my_flags, R, parity, step, y_local, ws->status);
+  if (e != cudaSuccess) return check_launch("layer_decode_ep_p2p: sum");
+  return check_launch("layer_decode_ep_p2p");
+}
+
+// Exchange buffers of fb_moe_layer_decode_ep_p2p. They are allocated here (cudaMalloc, so a CUDA IPC
+// handle names exactly the buffer) and opened by the peers in the context of THEIR OWN device with
+// lazy peer access, the way collective libraries map each other's memory.
+constexpr size_t kEpBytes[3] = {size_t(2) * kMaxTok * H * 4, size_t(2) * kEpMaxRanks * kMaxTok * H * 4,
+                                size_t(2) * 2 * kEpMaxRanks * 4};
+
+int32_t fb_ep_exchange_create(void** x_all, void** y_parts, void** flags, uint8_t* handles) {
+  if (!x_all || !y_parts || !flags || !handles) return invalid("ep_exchange_create: NULL argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == FB_EP_HANDLE_BYTES, "handle size");
+  void** out[3] = {x_all, y_parts, flags};
+  for (int k = 0; k < 3; ++k) {
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, kEpBytes[k]);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, kEpBytes[k]);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      set_error("ep_exchange_create: %s", cudaGetErrorString(e));
+      return int32_t(e);
+    }
+    memcpy(handles + k * FB_EP_HANDLE_BYTES, &h, FB_EP_HANDLE_BYTES);
+    *out[k] = p;
+  }
+  return int32_t(cudaDeviceSynchronize());
+}
+
+int32_t fb_ep_exchange_open(const uint8_t* handles, void** x_all, void** y_parts, void** flags) {
+  if (!x_all || !y_parts || !flags || !handles) return invalid("ep_exchange_open: NULL argument");
+  void** out[3] = {x_all, y_parts, flags};
+  for (int k = 0; k < 3; ++k) {
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handles + k * FB_EP_HANDLE_BYTES, FB_EP_HANDLE_BYTES);
+    void* p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      set_error("ep_exchange_open: %s", cudaGetErrorString(e));
+      return int32_t(e);
+    }
+    *out[k] = p;
+  }
+  return 0;
+}
+
+int32_t fb_ep_exchange_close(void* x_all, void* y_parts, void* flags, int32_t own) {
+  void* p[3] = {x_all, y_parts, flags};
+  int32_t st = 0;
+  for (int k = 0; k < 3; ++k) {
+    if (!p[k]) continue;
+    const cudaError_t e = own ? cudaFree(p[k]) : cudaIpcCloseMemHandle(p[k]);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      st = int32_t(e);
+    }
+  }
+  return st;
 }
 
 int32_t fb_ep_sum_ranks(const float* parts, int32_t n_ranks, int32_t rows, float* y, void* stream) {

@@ -125,6 +125,60 @@ def sum_ranks(parts, y):
     L.check(L.load().fb_ep_sum_ranks(_ptr(parts), parts.shape[0], parts.shape[1], _ptr(y), _stream()), "ep_sum_ranks")
 
 
+class PeerExchange:
+    """The three exchange buffers of fb_moe_layer_decode_ep_p2p on this rank, mapped into every peer
+    process with CUDA IPC (the 192 handle bytes travel through the process group once, at set-up)."""
+
+    def __init__(self, rank, world, group=None):
+        import ctypes as C
+        import torch.distributed as dist
+        from . import lib as L
+        lib = L.load()
+        self.rank, self.world, self.step = rank, world, 0
+        own = [C.c_void_p() for _ in range(3)]
+        handles = (C.c_uint8 * 192)()
+        L.check(lib.fb_ep_exchange_create(C.byref(own[0]), C.byref(own[1]), C.byref(own[2]), handles), "ep_exchange_create")
+        gathered = [None] * world
+        dist.all_gather_object(gathered, bytes(handles), group=group)
+        self.peers = L.EpPeers()
+        self.peers.rank, self.peers.n_ranks = rank, world
+        self._opened = []
+        for d in range(world):
+            if d == rank:
+                ptrs = own
+            else:
+                ptrs = [C.c_void_p() for _ in range(3)]
+                hb = (C.c_uint8 * 192).from_buffer_copy(gathered[d])
+                L.check(lib.fb_ep_exchange_open(hb, C.byref(ptrs[0]), C.byref(ptrs[1]), C.byref(ptrs[2])), "ep_exchange_open")
+                self._opened.append(ptrs)
+            self.peers.x_all[d], self.peers.y_parts[d], self.peers.flags[d] = (p.value for p in ptrs)
+        self._own = own
+        dist.barrier(group=group)
+
+    def close(self):
+        from . import lib as L
+        lib = L.load()
+        for ptrs in self._opened:
+            lib.fb_ep_exchange_close(ptrs[0], ptrs[1], ptrs[2], 0)
+        self._opened = []
+        if self._own:
+            lib.fb_ep_exchange_close(self._own[0], self._own[1], self._own[2], 1)
+            self._own = None
+
+
+def layer_decode_ep_p2p(router, ep_layer, x_local, ws, xchg, y_local):
+    """One expert-parallel decode layer with the exchange inside the kernels (peer stores + flags)."""
+    import ctypes as C
+    from . import lib as L
+    from .moe import _ptr, _stream
+    xchg.step += 1
+    tokens = x_local.shape[0] * xchg.world
+    L.check(L.load().fb_moe_layer_decode_ep_p2p(_ptr(router), C.byref(ep_layer.layer.layout), _ptr(ep_layer.slot_of),
+                                                _ptr(x_local), tokens, C.byref(xchg.peers), xchg.step, C.byref(ws.ws),
+                                                _ptr(ws.logits), _ptr(y_local), _stream()), "moe_layer_decode_ep_p2p")
+    return y_local
+
+
 def ep_layer_step(router, ep_layer, x_local, ws, bufs):
     """dispatch -> local experts -> combine for one layer; returns y of this rank's tokens."""
     world = ep_layer.world

@@ -389,3 +389,37 @@ def test_expert_parallel_shards_on_one_gpu(world):
     ids, w = O.topk(logits)
     want = oracle_layer(IQ3_S, IQ3_S, 512, seed, x, ids, w)
     assert max(rel_l2(got[t], want[t]) for t in range(tokens)) <= TOL
+
+
+def test_peer_exchange_layer_with_one_rank_equals_the_plain_layer():
+    """fb_moe_layer_decode_ep_p2p with a world of one rank: the rank is its own peer, so the publish /
+    wait / partial-row / rank-order-sum machinery runs on one GPU (nobody else is waited for) and must
+    reproduce fb_moe_layer_decode bit for bit, step after step, on both buffer parities."""
+    torch = _torch()
+    import ctypes as C
+
+    from fngine_b200 import ep, lib as fblib, moe
+    tokens, seed = 16, 5000
+    wr = torch.from_numpy(synth.router_weights(303, rows=512).view(np.int16)).cuda().view(torch.bfloat16)
+    full = moe.synth_layer(IQ3_S, IQ3_S, 512, 512, seed)
+    ws = moe.DecodeWorkspace(full)
+    slot_of = torch.arange(512, dtype=torch.int32, device="cuda")
+    bufs = [torch.zeros(n, dtype=torch.uint8, device="cuda")
+            for n in (2 * 16 * H * 4, 2 * fblib.EP_MAX_RANKS * 16 * H * 4, 2 * 2 * fblib.EP_MAX_RANKS * 4)]
+    xchg = ep.PeerExchange.__new__(ep.PeerExchange)
+    xchg.rank, xchg.world, xchg.step, xchg.local = 0, 1, 0, bufs
+    xchg.peers = fblib.EpPeers()
+    xchg.peers.rank, xchg.peers.n_ranks = 0, 1
+    xchg.peers.x_all[0], xchg.peers.y_parts[0], xchg.peers.flags[0] = (b.data_ptr() for b in bufs)
+    shard = C.Structure.__new__(C.Structure) if False else type("S", (), {})()
+    shard.layer, shard.slot_of = full, slot_of
+    y_ref = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    y = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    for step in range(3):
+        xd = torch.from_numpy(synth.activations(80 + step, tokens)).cuda()
+        moe.moe_layer_decode(wr, full, xd, ws, y_ref)
+        torch.cuda.synchronize()
+        ep.layer_decode_ep_p2p(wr, shard, xd, ws, xchg, y)
+        torch.cuda.synchronize()
+        assert ws.status() == 0
+        assert torch.equal(y, y_ref)
