@@ -190,7 +190,9 @@ def ep_layer_step(router, ep_layer, x_local, ws, bufs):
 
 
 def bench_main(args, rank, world, local_rank):
-    """bench.py for N > 1: strong scaling of the same 16-token decode step over expert-parallel ranks."""
+    """bench.py for N > 1: strong scaling of the same 16-token decode step over expert-parallel ranks.
+    The timed step exchanges through peer memory inside the kernels (fb_moe_layer_decode_ep_p2p); the
+    same step with NCCL all-to-alls is timed beside it and the two results are compared bit for bit."""
     import torch
     import torch.distributed as dist
     from . import moe, synth
@@ -210,11 +212,28 @@ def bench_main(args, rank, world, local_rank):
     ws = moe.DecodeWorkspace(layers[0].layer)
     bufs = {"y_partial": torch.empty(B, HIDDEN, dtype=torch.float32, device="cuda"),
             "y_local": torch.empty(hi - lo, HIDDEN, dtype=torch.float32, device="cuda")}
+    xchg = PeerExchange(rank, world)
+    y_p2p = torch.empty(hi - lo, HIDDEN, dtype=torch.float32, device="cuda")
     torch.cuda.synchronize()
+
+    def step_nccl():
+        for l in range(Lr):
+            ep_layer_step(routers[l], layers[l], xs[l], ws, bufs)
 
     def step():
         for l in range(Lr):
-            ep_layer_step(routers[l], layers[l], xs[l], ws, bufs)
+            layer_decode_ep_p2p(routers[l], layers[l], xs[l], ws, xchg, y_p2p)
+
+    # the two exchanges give the same bits (same partial rows, same rank-order sum)
+    same = True
+    for l in range(Lr):
+        y_a = ep_layer_step(routers[l], layers[l], xs[l], ws, bufs).clone()
+        layer_decode_ep_p2p(routers[l], layers[l], xs[l], ws, xchg, y_p2p)
+        torch.cuda.synchronize()
+        same = same and bool(torch.equal(y_a, y_p2p))
+    flag = torch.tensor([1.0 if same else 0.0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    same = bool(flag.item() == 1.0)
 
     # local distinct experts per layer (for the byte count) and a parity check of layer 0 on rank 0
     distinct = []
@@ -223,7 +242,9 @@ def bench_main(args, rank, world, local_rank):
         torch.cuda.synchronize()
         distinct.append(ws.work().n_items)
         if l == 0:
-            y0 = bufs["y_local"].clone()
+            layer_decode_ep_p2p(routers[l], layers[l], xs[l], ws, xchg, y_p2p)
+            torch.cuda.synchronize()
+            y0 = y_p2p.clone()
     local_bytes = torch.tensor([float(sum(d * BLOB + ROUTER_BYTES for d in distinct))], device="cuda")
     dist.all_reduce(local_bytes)
     step_bytes = float(local_bytes.item())
@@ -246,6 +267,22 @@ def bench_main(args, rank, world, local_rank):
     t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
+    # the NCCL all-to-all step beside it
+    for _ in range(3):
+        step_nccl()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    n0, n1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0.record()
+    for _ in range(args.steps):
+        step_nccl()
+    n1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    tn = torch.tensor([n0.elapsed_time(n1)], device="cuda")
+    dist.all_reduce(tn, op=dist.ReduceOp.MAX)
+    nccl_ms = float(tn.item())
 
     # end to end: pinned host rows of the own tokens in, own y rows out, every layer
     yh = torch.empty(hi - lo, HIDDEN, dtype=torch.float32).pin_memory()
@@ -257,7 +294,7 @@ def bench_main(args, rank, world, local_rank):
     for _ in range(args.steps):
         for l in range(Lr):
             xd.copy_(xs_host[l], non_blocking=True)
-            y = ep_layer_step(routers[l], layers[l], xd, ws, bufs)
+            y = layer_decode_ep_p2p(routers[l], layers[l], xd, ws, xchg, y_p2p)
             yh.copy_(y, non_blocking=True)
             torch.cuda.current_stream().synchronize()
     f1.record()
@@ -297,20 +334,25 @@ def bench_main(args, rank, world, local_rank):
         value = step_bytes * args.steps / (ms * 1e-3) / 1e9
         ach = value / world  # per GPU, whole layer step (kernels are timed one by one only at N = 1)
         cfg = workload_config(args, Lr)
-        cfg["parallelism"] = "ep%d: %d experts per GPU, tokens data-parallel (%d per GPU), NCCL all-to-all dispatch + combine" % (
-            world, EXPERTS // world, B // world)
+        cfg["parallelism"] = ("ep%d: %d experts per GPU, tokens data-parallel (%d per GPU), dispatch + combine by peer "
+                              "stores over NVLink inside the kernels (no collective call in the step)" % (
+                                  world, EXPERTS // world, B // world))
         line = {"metric": "iq3s_expert_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
                 "config": cfg, "tokens_per_s": B * Lr * args.steps / (ms * 1e-3), "us_per_layer": ms / args.steps / Lr * 1e3,
                 "distinct_local_experts_rank0": distinct,
-                "roofline": {"bound": "hbm", "kernel": "whole expert-parallel layer step, per GPU (incl. both all-to-alls)", "achieved": ach, "peak": peak,
+                "nccl_all_to_all_step": {"us_per_layer": nccl_ms / args.steps / Lr * 1e3,
+                                         "value": step_bytes * args.steps / (nccl_ms * 1e-3) / 1e9,
+                                         "bitwise_equal_to_peer_exchange": same},
+                "roofline": {"bound": "hbm", "kernel": "whole expert-parallel layer step, per GPU (incl. the exchange)", "achieved": ach, "peak": peak,
                              "unit": "GB/s", "frac": ach / peak, "peak_source": peak_src, "traffic": None},
                 "e2e": {"value": step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                         "h2d_bytes_per_step": (hi - lo) * HIDDEN * 4 * Lr * world,
                         "d2h_bytes_per_step": (hi - lo) * HIDDEN * 4 * Lr * world, "ms_per_step": e2e_ms / args.steps},
-                "gpu_launches": args.steps * Lr * 5 * world, "parity_vs_cpu_max_rel_l2": parity,
+                "gpu_launches": args.steps * Lr * 6 * world, "parity_vs_cpu_max_rel_l2": parity,
                 "device_status": status, "clocks": clocks, "prefill_stack": pre,
                 "cpu_baseline": None}
         print(json.dumps(line))
+    xchg.close()
     dist.destroy_process_group()
