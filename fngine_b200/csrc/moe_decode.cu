@@ -29,6 +29,7 @@ constexpr int kTT = 2;  // tokens of one work item handled per pass over a stage
 // ws.sched: [0] gate/up tile counter, [1] down tile counter, [2] finished route blocks,
 // [8..168) item order
 constexpr int kSchedOrderBase = 8;
+constexpr int kEpMaxRanks = FB_EP_MAX_RANKS;
 constexpr uint32_t kPeerSpinLimit = 1u << 20;  // polls of a peer-written flag before giving up (about a second)
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -48,7 +49,8 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want) {
   return false;
 }
 constexpr int kSchedRoute = 2;
-constexpr int kSchedEpSend = 3;  // ticket of ep_combine_send_kernel
+constexpr int kSchedEpSend = 3;  // ticket of ep_combine_exchange_kernel
+constexpr int kSchedEpPub = 224;  // 8 per-destination tickets of the x publication in route_kernel
 constexpr int kSchedGroup = 192;  // 32 row-group tickets of route_kernel
 constexpr int kSchedInts = 256;
 
@@ -335,6 +337,15 @@ __global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ l
   select_block([&](int t, int e) { return logits[size_t(t) * logits_stride + e]; }, slot_of, T, ws, counts);
 }
 
+// What route_kernel needs for an expert-parallel step with peer-memory exchange (n_ranks == 0: none).
+struct EpRouteArgs {
+  fb_ep_peers peers;
+  const float* x_local;  // this rank's rows, fp32 [tpr][2560]
+  int tpr;               // tokens per rank
+  int parity;
+  uint32_t step;
+};
+
 // Router projection, activation quantization and selection in one launch (the head of the fused
 // layer call). Block (g, q) projects router rows 32g..32g+31 over the K slice [320q, 320q+320): the
 // x slice of all tokens sits in shared memory, one warp per row pair (every x value read from
@@ -352,13 +363,35 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
                                                     int T, float* __restrict__ logits, int stride,
                                                     float* __restrict__ part, fb_moe_decode_workspace ws,
                                                     const int32_t* __restrict__ slot_of, bool remote_ok,
-                                                    const uint32_t* __restrict__ wait_flags, int n_wait,
-                                                    uint32_t wait_value) {
+                                                    EpRouteArgs ep) {
   pdl_launch_dependents();
   pdl_wait_prior();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (wait_flags) {  // expert-parallel step: x rows are written by the peers, one flag per source rank
-    if (tid < n_wait && !wait_flag(wait_flags + tid, wait_value))
+  if (ep.peers.n_ranks > 0) {
+    // Expert-parallel step: first this rank's own rows go to every rank (block b serves rank
+    // b % R with slice b / R of the rows; the block that completes a rank's slices publishes the
+    // flag there), then every block waits until all source ranks' rows have arrived here.
+    const int R = ep.peers.n_ranks, d = int(blockIdx.x) % R, slice = int(blockIdx.x) / R, n_slices = int(gridDim.x) / R;
+    const int total = ep.tpr * (H / 4), lo = int(int64_t(total) * slice / n_slices),
+              hi = int(int64_t(total) * (slice + 1) / n_slices);
+    float4* dst = reinterpret_cast<float4*>(ep.peers.x_all[d] +
+                                            (size_t(ep.parity) * kMaxTok + size_t(ep.peers.rank) * ep.tpr) * H);
+    const float4* src = reinterpret_cast<const float4*>(ep.x_local);
+    for (int i = lo + tid; i < hi; i += 512) dst[i] = src[i];
+    __shared__ int s_pub;
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+      const int ticket = atomicAdd(ws.sched + kSchedEpPub + d, 1);
+      s_pub = ticket == n_slices - 1;
+      if (s_pub) {
+        ws.sched[kSchedEpPub + d] = 0;
+        __threadfence_system();
+        st_release_sys(ep.peers.flags[d] + (ep.parity * 2 + 0) * kEpMaxRanks + ep.peers.rank, ep.step);
+      }
+    }
+    if (tid < R &&
+        !wait_flag(ep.peers.flags[ep.peers.rank] + (ep.parity * 2 + 0) * kEpMaxRanks + tid, ep.step))
       atomicMax(ws.status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
     __syncthreads();
   }
@@ -1161,25 +1194,13 @@ __global__ void __launch_bounds__(256) sum_ranks_kernel(const float* __restrict_
 //   x_all   [2][16][2560] fp32    all tokens of the step, rows written by their owners
 //   y_parts [2][8][16][2560] fp32 [parity][source rank][local token]: partial rows for this rank's tokens
 //   flags   [2][2][8] u32         [parity][0 = x rows, 1 = partial rows][source rank] = step number
-constexpr int kEpMaxRanks = FB_EP_MAX_RANKS;
 
-// One block per destination rank: copy this rank's rows, fence, publish.
-__global__ void __launch_bounds__(256) ep_publish_x_kernel(fb_ep_peers peers, const float* __restrict__ x_local,
-                                                           int tpr, int parity, uint32_t step) {
-  const int d = blockIdx.x;
-  float4* dst = reinterpret_cast<float4*>(peers.x_all[d] + (size_t(parity) * kMaxTok + size_t(peers.rank) * tpr) * H);
-  const float4* src = reinterpret_cast<const float4*>(x_local);
-  for (int i = threadIdx.x; i < tpr * (H / 4); i += 256) dst[i] = src[i];
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) st_release_sys(peers.flags[d] + (parity * 2 + 0) * kEpMaxRanks + peers.rank, step);
-}
-
-// The combine of an expert-parallel step: token t's partial row (its local pairs, slot order) goes
-// straight into its owner's y_parts; the block that finishes last publishes this rank's flag on
-// every peer.
-__global__ void __launch_bounds__(256) ep_combine_send_kernel(fb_moe_decode_workspace ws, fb_ep_peers peers, int tpr,
-                                                              int parity, uint32_t step) {
+// The combine of an expert-parallel step. Block (t, column slice): token t's partial row over the local
+// pairs (slot order) goes straight into its owner's y_parts; the block that finishes last publishes
+// this rank's flag on every rank. Blocks of tokens this rank owns then wait (bounded) for every
+// rank's flag and add the partial rows in rank order.
+__global__ void __launch_bounds__(256) ep_combine_exchange_kernel(fb_moe_decode_workspace ws, fb_ep_peers peers, int tpr,
+                                                                  int parity, uint32_t step, float* __restrict__ y_local) {
   pdl_launch_dependents();
   pdl_wait_prior();
   const int t = blockIdx.y;
@@ -1203,22 +1224,16 @@ __global__ void __launch_bounds__(256) ep_combine_send_kernel(fb_moe_decode_work
     __threadfence_system();
     st_release_sys(peers.flags[threadIdx.x] + (parity * 2 + 1) * kEpMaxRanks + peers.rank, step);
   }
-}
-
-// Owner side: wait (bounded) for every rank's partial rows of this step, add them in rank order.
-__global__ void __launch_bounds__(256) ep_wait_sum_kernel(const float* __restrict__ y_parts,
-                                                          const uint32_t* __restrict__ flags, int n_ranks, int parity,
-                                                          uint32_t step, float* __restrict__ y, uint32_t* status) {
-  pdl_launch_dependents();
-  pdl_wait_prior();
-  if (threadIdx.x < n_ranks && !wait_flag(flags + (parity * 2 + 1) * kEpMaxRanks + threadIdx.x, step))
-    atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+  if (d != peers.rank) return;
+  if (threadIdx.x < peers.n_ranks &&
+      !wait_flag(peers.flags[peers.rank] + (parity * 2 + 1) * kEpMaxRanks + threadIdx.x, step))
+    atomicMax(ws.status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
   __syncthreads();
-  const int i = blockIdx.y, n = blockIdx.x * 256 + threadIdx.x;
+  const float* mine = peers.y_parts[peers.rank];
   float acc = 0.0f;
-  for (int s = 0; s < n_ranks; ++s)
-    acc += __ldcg(y_parts + ((size_t(parity) * kEpMaxRanks + s) * kMaxTok + i) * H + n);
-  y[size_t(i) * H + n] = acc;
+  for (int s = 0; s < peers.n_ranks; ++s)
+    acc += __ldcg(mine + ((size_t(parity) * kEpMaxRanks + s) * kMaxTok + i) * H + n);
+  y_local[size_t(i) * H + n] = acc;
 }
 
 // ------------------------------------------------------------------------------ host side
@@ -1401,8 +1416,10 @@ int32_t fb_moe_combine(const fb_moe_decode_workspace* ws, const float* y_shared,
 static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_layout* layout,
                                  const int32_t* slot_of, bool remote_ok, const void* x, int32_t x_dtype,
                                  int32_t tokens, const fb_moe_decode_workspace* ws, float* logits_scratch, float* y_out,
-                                 void* stream, const uint32_t* wait_flags = nullptr, int n_wait = 0,
-                                 uint32_t wait_value = 0, bool with_combine = true) {
+                                 void* stream, const EpRouteArgs* ep = nullptr) {
+  const bool with_combine = ep == nullptr;
+  EpRouteArgs era{};
+  if (ep) era = *ep;
   // Four launches: route (router projection + activation quantization + selection), gate/up, down,
   // combine. Same arithmetic, in the same order, as the five separate entry points.
   if (!router_w_bf16 || !x || (!y_out && with_combine) || !logits_scratch || !layout_ok(layout) || !ws_ok(ws) ||
@@ -1417,10 +1434,10 @@ static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_
       x_dtype == FB_DT_BF16
           ? launch_pdl(route_kernel<true>, grid, block, 0, as_stream(stream),
                        static_cast<const __nv_bfloat16*>(router_w_bf16), x, tokens, logits_scratch, int(FB_ROUTER_ROWS),
-                       ws->partial, *ws, slot_of, remote_ok, wait_flags, n_wait, wait_value)
+                       ws->partial, *ws, slot_of, remote_ok, era)
           : launch_pdl(route_kernel<false>, grid, block, 0, as_stream(stream),
                        static_cast<const __nv_bfloat16*>(router_w_bf16), x, tokens, logits_scratch, int(FB_ROUTER_ROWS),
-                       ws->partial, *ws, slot_of, remote_ok, wait_flags, n_wait, wait_value);
+                       ws->partial, *ws, slot_of, remote_ok, era);
   if (e != cudaSuccess) return check_launch("layer_decode: route");
   int32_t st = fb_moe_hot_gate_up(layout, tokens, ws, stream);
   if (st) return st;
@@ -1458,19 +1475,21 @@ int32_t fb_moe_layer_decode_ep_p2p(const void* router_w_bf16, const fb_moe_exper
       return invalid("layer_decode_ep_p2p: a peer buffer address is missing");
   const int R = peers->n_ranks, tpr = tokens / R, parity = int(step & 1u);
   cudaStream_t s = as_stream(stream);
-  ep_publish_x_kernel<<<R, 256, 0, s>>>(*peers, x_local, tpr, parity, step);
-  if (cudaGetLastError() != cudaSuccess) return check_launch("layer_decode_ep_p2p: publish");
+  // Four launches, chained like the single-GPU layer: route (publishes this rank's rows, waits for
+  // everyone's), gate/up, down, combine (sends partial rows, waits, sums).
+  EpRouteArgs era{};
+  era.peers = *peers;
+  era.x_local = x_local;
+  era.tpr = tpr;
+  era.parity = parity;
+  era.step = step;
   const float* x_all = peers->x_all[peers->rank] + size_t(parity) * kMaxTok * H;
-  const uint32_t* my_flags = peers->flags[peers->rank];
   int32_t st = layer_decode_impl(router_w_bf16, layout, slot_of, true, x_all, FB_DT_F32, tokens, ws, logits_scratch,
-                                 nullptr, stream, my_flags + (parity * 2 + 0) * kEpMaxRanks, R, step, false);
+                                 nullptr, stream, &era);
   if (st) return st;
-  cudaError_t e = launch_pdl(ep_combine_send_kernel, dim3(H / 256, tokens), dim3(256), 0, s, *ws, *peers, tpr, parity,
-                             step);
+  const cudaError_t e = launch_pdl(ep_combine_exchange_kernel, dim3(H / 256, tokens), dim3(256), 0, s, *ws, *peers, tpr,
+                                   parity, step, y_local);
   if (e != cudaSuccess) return check_launch("layer_decode_ep_p2p: combine");
-  e = launch_pdl(ep_wait_sum_kernel, dim3(H / 256, tpr), dim3(256), 0, s,
-                 static_cast<const float*>(peers->y_parts[peers->rank]), my_flags, R, parity, step, y_local, ws->status);
-  if (e != cudaSuccess) return check_launch("layer_decode_ep_p2p: sum");
   return check_launch("layer_decode_ep_p2p");
 }
 
