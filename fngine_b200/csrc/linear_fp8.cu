@@ -20,6 +20,8 @@
 #include "common.cuh"
 
 #include <cuda.h>
+
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -277,6 +279,217 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
 }
 
+// ------------------------------------------------------------------------------ GEMM on CTA pairs
+// The same GEMM with the two-SM MMA (cta_group::2): a cluster of two CTAs computes a 256 x 256 output
+// tile, CTA r of the pair holding A rows [128 r, 128 r + 128) and B rows (output columns)
+// [128 r, 128 r + 128) of every K step, so each SM stages 32 KB per K step instead of 48 KB and the
+// tensor cores of the pair share the B halves. Each CTA keeps its 128 x 256 half of the accumulator
+// in its own tensor memory. Barrier protocol (one pipeline, CTA 0 is the leader):
+//   full[s]   lives in the leader: its producer arms it with the bytes of BOTH CTAs, both CTAs' TMA
+//             loads complete on it (barrier address with the peer bit cleared);
+//   empty[s]  in each CTA, freed for both by one multicast commit of the leader's MMA thread;
+//   tmem_full[a] in each CTA, same multicast commit; tmem_empty[a] in the leader, eight arrivals
+//             (four epilogue warps per CTA, CTA 1's through the cluster window).
+// No TMA load is multicast: each CTA loads only its own operand halves.
+constexpr int BM2 = 256, kStages2 = 6;
+constexpr int kStageA2 = 128 * BK, kStageB2 = 128 * BK;              // per CTA and stage
+constexpr int kRingBytes2 = kStages2 * (kStageA2 + kStageB2);         // 196608
+constexpr int kGemmSmem2 = kRingBytes2 + 256 + 1024;
+constexpr uint32_t kIdescF8Pair = (1u << 4) | (uint32_t(BN >> 3) << 17) | (uint32_t(BM2 >> 4) << 24);
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the bit that separates the two CTAs of a pair
+
+struct GemmBars2 {
+  uint64_t full[kStages2];
+  uint64_t empty[kStages2];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint64_t* leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(leader_bar) & kPeerBitMask)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in BOTH CTAs once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(static_cast<unsigned short>(3))
+      : "memory");
+}
+// Arrive on the leader CTA's copy of `bar`.
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, 0;\n\t"
+      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}"
+      ::"r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ bool gemm_wait2(GemmBars2* b, uint64_t* bar, uint32_t parity, uint32_t* status) {
+  if (*reinterpret_cast<volatile int*>(&b->abort)) return false;
+  if (mbar_wait(bar, parity)) return true;
+  *reinterpret_cast<volatile int*>(&b->abort) = 1;
+  atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+  return false;
+}
+
+template <bool SCALE_BF16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const float* __restrict__ act_scale, const void* __restrict__ w_scale,
+                     __nv_bfloat16* __restrict__ out, int M, int N, int K, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring_a = smem;
+  uint8_t* ring_b = smem + kStages2 * kStageA2;
+  GemmBars2* bars = reinterpret_cast<GemmBars2*>(smem + kRingBytes2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = int(cluster_ctarank());
+  const int m_tiles = (M + BM2 - 1) / BM2, n_tiles = (N + BN - 1) / BN, k_blocks = K / BK;
+  const int n_work = m_tiles * n_tiles, pair = int(blockIdx.x) >> 1, n_pairs = int(gridDim.x) >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages2; ++i) {
+      mbar_init(&bars->full[i], 1);
+      mbar_init(&bars->empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->tmem_full[i], 1);
+      mbar_init(&bars->tmem_empty[i], 8);
+    }
+    bars->abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc_pair(&bars->tmem_base, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is sent to them
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs): own A rows and own B rows, completion on the leader's barrier
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = pair; tile < n_work; tile += n_pairs) {
+        const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages2;
+          if (!gemm_wait2(bars, &bars->empty[s], ((it / kStages2) & 1) ^ 1, status)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(&bars->full[s], 2 * (kStageA2 + kStageB2));
+          tma_load_2d_pair(ring_a + s * kStageA2, &map_a, kb * BK, m_blk * BM2 + rank * 128, &bars->full[s]);
+          tma_load_2d_pair(ring_b + s * kStageB2, &map_b, kb * BK, n_blk * BN + rank * 128, &bars->full[s]);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      uint32_t it = 0, tl = 0;
+      for (int tile = pair; tile < n_work; tile += n_pairs, ++tl) {
+        const int ab = tl & 1;
+        if (!gemm_wait2(bars, &bars->tmem_empty[ab], ((tl >> 1) & 1) ^ 1, status)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + uint32_t(ab * BN);
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages2;
+          if (!gemm_wait2(bars, &bars->full[s], (it / kStages2) & 1, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = umma_desc_k128(smem_u32(ring_a + s * kStageA2));
+          const uint64_t db = umma_desc_k128(smem_u32(ring_b + s * kStageB2));
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 32; ++k4)
+            umma_f8_pair(d_tmem, da + uint64_t(2 * k4), db + uint64_t(2 * k4), kIdescF8Pair, (kb | k4) ? 1u : 0u);
+          umma_commit_pair(&bars->empty[s]);
+        }
+        if (!ok) break;
+        umma_commit_pair(&bars->tmem_full[ab]);
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 2..5 of each CTA: its 128 rows of the pair's tile
+    const int q = warp & 3;
+    uint32_t tl = 0;
+    for (int tile = pair; tile < n_work; tile += n_pairs, ++tl) {
+      const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
+      const int ab = tl & 1;
+      if (!gemm_wait2(bars, &bars->tmem_full[ab], (tl >> 1) & 1, status)) break;
+      tc_fence_after();
+      const int row = m_blk * BM2 + rank * 128 + q * 32 + lane;
+      const float sa = row < M ? act_scale[row] : 0.0f;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(ab * BN + c * 32), r);
+        const int col0 = n_blk * BN + c * 32;
+        if (row < M && col0 < N) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float s0, s1;
+            if constexpr (SCALE_BF16) {
+              const uint32_t u = reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(w_scale) + col0)[j];
+              s0 = __uint_as_float(u << 16);
+              s1 = __uint_as_float(u & 0xFFFF0000u);
+            } else {
+              const float2 f = reinterpret_cast<const float2*>(static_cast<const float*>(w_scale) + col0)[j];
+              s0 = f.x;
+              s1 = f.y;
+            }
+            const float v0 = __uint_as_float(r[2 * j]) * sa * s0;
+            const float v1 = __uint_as_float(r[2 * j + 1]) * sa * s1;
+            const __nv_bfloat162 b = __floats2bfloat162_rn(v0, v1);
+            packed[j] = *reinterpret_cast<const uint32_t*>(&b);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(out + size_t(row) * N + col0);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&bars->tmem_empty[ab]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves (or frees tensor memory) while the peer may still signal or read
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
 // ------------------------------------------------------------------------------ host
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -308,6 +521,24 @@ bool make_map_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t k, in
 }
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+// CTA pairs of the two-SM kernel that can be resident at once (asked of the occupancy calculator once).
+int pair_count() {
+  static int n = [] {
+    cudaFuncSetAttribute(fp8_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(sm_count()) & ~1u);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kGemmSmem2;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, fp8_gemm_pair_kernel<false>, &cfg) != cudaSuccess || clusters < 1) {
+      cudaGetLastError();
+      clusters = sm_count() / 2;
+    }
+    return clusters;
+  }();
+  return n;
+}
 
 }  // namespace
 }  // namespace fb
@@ -348,19 +579,36 @@ int32_t fb_linear_fp8(const void* x_bf16, int32_t tokens, const uint8_t* w_codes
   uint32_t* status = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a_scales) + align256(size_t(tokens) * 4));
   int32_t st = fb_fp8_quantize_tokens(x_bf16, tokens, k, a_codes, a_scales, stream);
   if (st) return st;
-  CUtensorMap map_a, map_b;
-  if (!make_map_u8(&map_a, a_codes, tokens, k, BM) || !make_map_u8(&map_b, w_codes, n, k, BN)) {
-    set_error("linear_fp8: cuTensorMapEncodeTiled failed");
-    return int32_t(cudaErrorInvalidValue);
-  }
   static bool once = [] {
     cudaFuncSetAttribute(fp8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
     cudaFuncSetAttribute(fp8_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
+    cudaFuncSetAttribute(fp8_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem2);
+    cudaFuncSetAttribute(fp8_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem2);
     return true;
   }();
   (void)once;
   cudaError_t e = cudaMemsetAsync(status, 0, 4, as_stream(stream));
   if (e != cudaSuccess) return check_launch("linear_fp8: status clear");
+  // Two-SM tiles (256 x 256 per CTA pair) once there are enough rows to fill them; the single-CTA
+  // kernel (128 x 256) below that and when FB_FP8_SINGLE_CTA is set (for comparisons).
+  static const bool force_single = getenv("FB_FP8_SINGLE_CTA") != nullptr;
+  const bool pair = tokens >= BM2 && !force_single;
+  CUtensorMap map_a, map_b;
+  if (!make_map_u8(&map_a, a_codes, tokens, k, 128) || !make_map_u8(&map_b, w_codes, n, k, pair ? 128 : BN)) {
+    set_error("linear_fp8: cuTensorMapEncodeTiled failed");
+    return int32_t(cudaErrorInvalidValue);
+  }
+  if (pair) {
+    const int work = ((tokens + BM2 - 1) / BM2) * ((n + BN - 1) / BN);
+    const int pairs = work < pair_count() ? work : pair_count();
+    if (w_scales_dtype == FB_DT_BF16)
+      fp8_gemm_pair_kernel<true><<<2 * pairs, kThreads, kGemmSmem2, as_stream(stream)>>>(
+          map_a, map_b, a_scales, w_scales, static_cast<__nv_bfloat16*>(out_bf16), tokens, n, k, status);
+    else
+      fp8_gemm_pair_kernel<false><<<2 * pairs, kThreads, kGemmSmem2, as_stream(stream)>>>(
+          map_a, map_b, a_scales, w_scales, static_cast<__nv_bfloat16*>(out_bf16), tokens, n, k, status);
+    return check_launch("linear_fp8");
+  }
   const int m_tiles = (tokens + BM - 1) / BM, n_tiles = (n + BN - 1) / BN;
   const int grid = m_tiles * n_tiles < sm_count() ? m_tiles * n_tiles : sm_count();
   if (w_scales_dtype == FB_DT_BF16)
