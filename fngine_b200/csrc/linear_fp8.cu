@@ -5,18 +5,20 @@
 //            fp8_a8.cu:22-69 of the reference project);
 //   w8, sw : E4M3 weight codes [n][k] with one scale per row (src/kernels/linear/linear.h:57-62).
 //
-// The GEMM is a persistent tcgen05 kernel: 128 x 256 output tiles, K steps of 128 bytes. One
-// thread issues TMA tile loads (128-byte swizzle, no multicast) into a 4-stage shared-memory ring,
-// one thread issues tcgen05.mma (kind::f8f6f4, E4M3 x E4M3 -> fp32) into one of two 256-column TMEM
-// accumulators, four warps drain the other accumulator (tcgen05.ld), apply the two scales and store
-// bf16. All hand-offs are mbarriers; every wait is bounded and reports through a status word.
-//
-// Why this tile: with one CTA per MMA (cta_group::1) a K step moves 48 KB into shared memory and
-// the four MMAs read 48 KB of operands back out, i.e. ~176 B/clk of shared-memory traffic at the
-// tensor peak against 128 B/clk available - the kernel is bound there (measured: tensor pipe 49-55 %
-// busy). A 256 x 256 tile without a second accumulator was measured slower (116.7 vs 109 us): the
-// drain of the accumulators no longer hides behind the next tile's MMAs. Pairing CTAs
-// (cta_group::2, each CTA staging half of B) is the step that lifts this bound.
+// The GEMM is a persistent tcgen05 kernel (kind::f8f6f4, E4M3 x E4M3 -> fp32 in tensor memory). One
+// thread issues TMA tile loads (128-byte swizzle, no multicast) into a shared-memory ring, one
+// thread issues the MMAs into one of two 256-column TMEM accumulators, four warps drain the other
+// accumulator (tcgen05.ld), apply the two scales and store bf16. All hand-offs are mbarriers; every
+// wait is bounded and reports through a status word. Two variants:
+//   * CTA pairs (tokens >= 256): the two-SM MMA (cta_group::2), 256 x 256 tiles per cluster of two
+//     CTAs, each CTA staging its 128 rows of A and its 128 rows of B per K step (32 KB, six stages);
+//   * single CTA: 128 x 256 tiles, 48 KB per K step, four stages.
+// What the measurements said (B200, 4096 x 9216 x 2560): operand traffic is not the limit (a run
+// that skips every load after the first ring fill takes the same time); the per-K-step work of the
+// MMA-issuing thread is. A tcgen05 fence after each full-barrier wait and a shared-memory flag load
+// in front of it cost 17 % of the kernel; with both gone the pair kernel runs at 2.4 PFLOP/s, within
+// 8 % of issuing the MMAs back to back with no barriers at all (2.65 PFLOP/s), while a library FP8
+// GEMM of the same shape on the same GPU reaches 2.7 - 2.9 PFLOP/s.
 #include "common.cuh"
 
 #include <cuda.h>
@@ -100,32 +102,47 @@ struct GemmBars {
   int abort;
 };
 
+// Bounded wait. The barrier is tried first: the abort flag (set by a role whose own wait ran out)
+// is looked at only every 32nd failed try, so the common path is one instruction.
 __device__ __forceinline__ bool gemm_wait(GemmBars* b, uint64_t* bar, uint32_t parity, uint32_t* status) {
-  if (*reinterpret_cast<volatile int*>(&b->abort)) return false;
-  if (mbar_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 31u) == 31u && *reinterpret_cast<volatile int*>(&b->abort)) return false;
+  }
   *reinterpret_cast<volatile int*>(&b->abort) = 1;
   atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
   return false;
 }
 
 // ------------------------------------------------------------------------------ activation quantization
-// One block per token: scale = max|x| / 448, codes = satfinite_rne_e4m3(x * (1 / scale)).
+// One block per token: scale = max|x| / 448, codes = satfinite_rne_e4m3(x * (1 / scale)). Each thread
+// keeps up to kQPer 16-byte pieces of the row in registers between the two phases (rows up to
+// 256 * 8 * kQPer elements are read from memory once); longer rows re-read the remainder.
+constexpr int kQPer = 2;
+
 __global__ void __launch_bounds__(256) fp8_quantize_tokens_kernel(const __nv_bfloat16* __restrict__ x, int K,
                                                                   uint8_t* __restrict__ codes,
                                                                   float* __restrict__ scales) {
   const int t = blockIdx.x;
   const __nv_bfloat16* row = x + size_t(t) * K;
   __shared__ float s_red[8];
+  uint4 held[kQPer];
   float m = 0.0f;
-  for (int i = threadIdx.x * 8; i < K; i += 256 * 8) {
-    const uint4 v = *reinterpret_cast<const uint4*>(row + i);
+  auto absmax = [&](const uint4& v) {
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       m = fmaxf(m, fabsf(__uint_as_float(u[j] << 16)));
       m = fmaxf(m, fabsf(__uint_as_float(u[j] & 0xFFFF0000u)));
     }
+  };
+#pragma unroll
+  for (int p = 0; p < kQPer; ++p) {
+    const int i = (p * 256 + threadIdx.x) * 8;
+    held[p] = i < K ? *reinterpret_cast<const uint4*>(row + i) : make_uint4(0, 0, 0, 0);
+    absmax(held[p]);
   }
+  for (int i = (kQPer * 256 + threadIdx.x) * 8; i < K; i += 256 * 8) absmax(*reinterpret_cast<const uint4*>(row + i));
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m;
@@ -136,8 +153,7 @@ __global__ void __launch_bounds__(256) fp8_quantize_tokens_kernel(const __nv_bfl
   const float scale = m > 0.0f ? __fdiv_rn(m, 448.0f) : 0.0f;
   const float inv = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
   if (threadIdx.x == 0) scales[t] = scale;
-  for (int i = threadIdx.x * 8; i < K; i += 256 * 8) {
-    const uint4 v = *reinterpret_cast<const uint4*>(row + i);
+  auto encode = [&](const uint4& v, int i) {
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
     uint32_t o[2] = {0, 0};
 #pragma unroll
@@ -148,7 +164,13 @@ __global__ void __launch_bounds__(256) fp8_quantize_tokens_kernel(const __nv_bfl
       o[j >> 1] |= pair << (16 * (j & 1));
     }
     *reinterpret_cast<uint2*>(codes + size_t(t) * K + i) = make_uint2(o[0], o[1]);
+  };
+#pragma unroll
+  for (int p = 0; p < kQPer; ++p) {
+    const int i = (p * 256 + threadIdx.x) * 8;
+    if (i < K) encode(held[p], i);
   }
+  for (int i = (kQPer * 256 + threadIdx.x) * 8; i < K; i += 256 * 8) encode(*reinterpret_cast<const uint4*>(row + i), i);
 }
 
 // ------------------------------------------------------------------------------ GEMM
@@ -213,8 +235,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         bool ok = true;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
+          // (no tcgen05 fence here: the operands were written through the async proxy and the
+          // barrier wait orders them; a fence per K step costs a fifth of the kernel)
           if (!gemm_wait(bars, &bars->full[s], (it / kStages) & 1, status)) { ok = false; break; }
-          tc_fence_after();
           const uint64_t da = umma_desc_k128(smem_u32(ring_a + s * kStageA));
           const uint64_t db = umma_desc_k128(smem_u32(ring_b + s * kStageB));
 #pragma unroll
@@ -353,8 +376,10 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
       : "memory");
 }
 __device__ __forceinline__ bool gemm_wait2(GemmBars2* b, uint64_t* bar, uint32_t parity, uint32_t* status) {
-  if (*reinterpret_cast<volatile int*>(&b->abort)) return false;
-  if (mbar_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 31u) == 31u && *reinterpret_cast<volatile int*>(&b->abort)) return false;  // a peer role gave up
+  }
   *reinterpret_cast<volatile int*>(&b->abort) = 1;
   atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
   return false;
@@ -424,7 +449,6 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages2;
           if (!gemm_wait2(bars, &bars->full[s], (it / kStages2) & 1, status)) { ok = false; break; }
-          tc_fence_after();
           const uint64_t da = umma_desc_k128(smem_u32(ring_a + s * kStageA2));
           const uint64_t db = umma_desc_k128(smem_u32(ring_b + s * kStageB2));
 #pragma unroll
