@@ -170,6 +170,51 @@ def workload_config(args, layers_per_step):
 GATE_UP_DRAM_TRAFFIC_RATIO = 160.57 / 156.85
 
 
+def iq4nl_section(torch, steps, n_layers=4):
+    """The IQ4_NL resident-expert variant (18-byte blocks, Q8_0 activations): the same decode layer at batch
+    1 and 8, four rotating layers (4.5 GB, larger than L2), CUDA-graph replays, device time."""
+    from fngine_b200 import moe, synth
+    fmt = 20
+    blob = 3 * 737280
+    layers = [moe.synth_layer(fmt, fmt, INTER, EXPERTS, 6000 + l) for l in range(n_layers)]
+    routers = [torch.from_numpy(synth.router_weights(9100 + l).view(np.int16)).cuda().view(torch.bfloat16)
+               for l in range(n_layers)]
+    ws = moe.DecodeWorkspace(layers[0])
+    res = {}
+    for b in (1, 8):
+        xs = [torch.from_numpy(synth.activations(7100 + l, b)).cuda() for l in range(n_layers)]
+        y = torch.empty(b, HIDDEN, dtype=torch.float32, device="cuda")
+        d = []
+        for l in range(n_layers):
+            moe.moe_layer_decode(routers[l], layers[l], xs[l], ws, y)
+            torch.cuda.synchronize()
+            d.append(ws.work().n_items)
+        g = torch.cuda.CUDAGraph()
+        st = torch.cuda.Stream()
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st):
+            with torch.cuda.graph(g, stream=st):
+                for l in range(n_layers):
+                    moe.moe_layer_decode(routers[l], layers[l], xs[l], ws, y)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t = e0.elapsed_time(e1) / steps
+        by = sum(k * blob + ROUTER_BYTES for k in d)
+        res[str(b)] = {"gbs": by / t / 1e6, "us_per_layer": t / n_layers * 1e3, "distinct_experts_mean": sum(d) / n_layers}
+    res["workload"] = "512 IQ4_NL experts per layer (2,211,840 B each), Q8_0 activations, %d rotating layers" % n_layers
+    res["device_status"] = ws.status()
+    del layers
+    torch.cuda.empty_cache()
+    return res
+
+
 def fp8_gemm_section(torch, iters=10):
     """The FP8-row dense GEMM of the benchmark definition (bf16 [4096x2560] x E4M3 [9216x2560] -> bf16),
     each call timed alone with CUDA events after an L2 flush; the library FP8 GEMM of the same shape
@@ -379,7 +424,7 @@ def run_ours(args, rank, world, local_rank):
     status = ws.status()
 
     # other batch sizes of the same layer definition, CUDA-graph replayed (launch-bound otherwise)
-    sections = set("batches,cpu,fp8,prefill".split(",")) if args.sections == "all" else \
+    sections = set("batches,cpu,iq4nl,fp8,prefill".split(",")) if args.sections == "all" else \
         set(x for x in args.sections.split(",") if x and x != "none")
 
     def want(name):
@@ -435,6 +480,7 @@ def run_ours(args, rank, world, local_rank):
 
     del layers
     torch.cuda.empty_cache()
+    iq4 = iq4nl_section(torch, args.steps) if want("iq4nl") else None
     fp8 = fp8_gemm_section(torch) if want("fp8") else None
     pre = prefill_section(torch, n_layers=args.prefill_layers) if want("prefill") else None
     peak, peak_src = peaks()
@@ -467,6 +513,7 @@ def run_ours(args, rank, world, local_rank):
                 "api": "fb_moe_layer_decode_host per layer: pinned host x in, host y out, stream wait inside"},
         "gpu_launches": args.steps * Lr * 4,
         "other_batches": other,
+        "iq4nl_decode": iq4,
         "fp8_row_gemm": fp8,
         "prefill_stack": pre,
         "parity_vs_cpu_max_rel_l2": parity,
@@ -488,7 +535,7 @@ def main():
                     help="layers of the prefill stack section (a profiler run wants 1)")
     ap.add_argument("--sections", default="all",
                     help="extra sections beside the headline decode measurement: all | none | comma list of "
-                         "batches,cpu,fp8,prefill (a profiler run wants none)")
+                         "batches,cpu,iq4nl,fp8,prefill (a profiler run wants none)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

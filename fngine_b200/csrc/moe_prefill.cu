@@ -577,8 +577,7 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
         for (int kb = 0; kb < kSteps; ++kb, ++it) {
           const int s = it % kStagesGU;
           if (!ab.wait(&bars->full[s], (it / kStagesGU) & 1)) { ok = false; break; }
-          tc_fence_after();
-          uint8_t* st = ring + s * kGuStage;
+          uint8_t* st = ring + s * kGuStage;  // (the barrier orders the operand writes; no tcgen05 fence per K step)
           const uint64_t dg = umma_desc_k128(smem_u32(st)), du = umma_desc_k128(smem_u32(st + kTileA));
           const uint64_t db = umma_desc_k128(smem_u32(st + 2 * kTileA));
 #pragma unroll
@@ -760,7 +759,6 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
         for (int kb = 0; kb < k_steps; ++kb, ++it) {
           const int s = it % kStagesDN;
           if (!ab.wait(&bars->full[s], (it / kStagesDN) & 1)) { ok = false; break; }
-          tc_fence_after();
           uint8_t* st = ring + s * kDnStage;
           const uint64_t da = umma_desc_k128(smem_u32(st)), db = umma_desc_k128(smem_u32(st + kTileA));
 #pragma unroll
