@@ -658,6 +658,7 @@ struct GateUp<FB_FMT_IQ3_S> {
   static constexpr int kAct = FB_ACT_Q8_K, kActBytes = H + 64;
   static constexpr bool kGrid = true;
   static constexpr int kPartialFloats = 2 * kTasks * kTT * 32;
+  static constexpr int kUpPad = 0;
 };
 // IQ4_NL: 32 intermediate rows of 1440 bytes per matrix. Sixteen consumer warps; warp w handles
 // rows 2w, 2w+1 of gate and of up, eight lanes per row, lane q taking the 36-byte units q + 8i.
@@ -667,6 +668,10 @@ struct GateUp<FB_FMT_IQ4_NL> {
   static constexpr int kAct = FB_ACT_Q8_0, kActBytes = H + H / 8;
   static constexpr bool kGrid = false;
   static constexpr int kPartialFloats = 0;
+  // The up rows sit 64 bytes after the gate rows: a row is 360 words (8 mod 32), so with both
+  // parts on the same bank phase the gate and the up lanes of a warp would collide pairwise; 16
+  // words apart the 32 lanes' words fall in 32 different banks.
+  static constexpr int kUpPad = 64;
 };
 
 template <int TT>
@@ -803,7 +808,7 @@ template <int FMT>
 __global__ void __launch_bounds__((GateUp<FMT>::kWarps + 1) * 32, 1)
 gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   using C = GateUp<FMT>;
-  constexpr int kW = C::kWarps, kPart = C::kJ * C::kRowBytes, kStageW = 2 * kPart;
+  constexpr int kW = C::kWarps, kPart = C::kJ * C::kRowBytes, kUp = kPart + C::kUpPad, kStageW = kUp + kPart;
   constexpr int kStage = kStageW + kTT * C::kActBytes;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* p = smem;
@@ -846,10 +851,10 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
                     [&](int s, int slot_id, int sub, int pair0, int ntp) {
                       const uint8_t* blob = L.slots + int64_t(slot_id) * L.blob_stride;
                       uint8_t* st = stage0 + s * kStage;
-                      mbar_expect_tx(&ring.full[s], uint32_t(kStageW + ntp * C::kActBytes));
+                      mbar_expect_tx(&ring.full[s], uint32_t(2 * kPart + ntp * C::kActBytes));
                       const size_t off = size_t(sub) * kPart;
                       bulk_g2s(st, blob + L.gate_offset + off, kPart, &ring.full[s]);
-                      bulk_g2s(st + kPart, blob + L.up_offset + off, kPart, &ring.full[s]);
+                      bulk_g2s(st + kUp, blob + L.up_offset + off, kPart, &ring.full[s]);
                       for (int t = 0; t < ntp; ++t)
                         bulk_g2s(st + kStageW + t * C::kActBytes,
                                  ws.xq + size_t(work->pair_token[pair0 + t]) * FB_XQ_STRIDE, C::kActBytes,
@@ -869,7 +874,7 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
       uint8_t* st = stage0 + s * kStage;
       const uint8_t* actbase = st + kStageW;
       const int mat = task / 5, pair = task - 5 * mat;
-      const uint32_t* unit = reinterpret_cast<const uint32_t*>(st + mat * kPart + lane * C::kRowBytes + pair * 220);
+      const uint32_t* unit = reinterpret_cast<const uint32_t*>(st + mat * kUp + lane * C::kRowBytes + pair * 220);
       float* part = partials + s * (C::kTasks * kTT * 32);
       if (ntp == 1) {
         const uint8_t* ar[1] = {actbase};
@@ -927,7 +932,7 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
       const uint8_t* actbase = st + kStageW;
       // lanes 0-7 gate row 2w, 8-15 gate 2w+1, 16-23 up 2w, 24-31 up 2w+1
       const int q = lane & 7, r = (lane >> 3) & 1, mat = lane >> 4;
-      const uint8_t* row = st + mat * kPart + (2 * warp + r) * C::kRowBytes;
+      const uint8_t* row = st + mat * kUp + (2 * warp + r) * C::kRowBytes;
       float acc[kTT] = {0.0f, 0.0f};
       if (ntp == 1) {
         const uint8_t* ar[1] = {actbase};
@@ -1245,7 +1250,7 @@ cudaError_t opt_in_smem(K kernel, size_t bytes) {
 template <int FMT>
 constexpr size_t gate_up_smem() {
   using C = GateUp<FMT>;
-  return (C::kGrid ? kGridRepBytes : 0) + 64 + 2 * size_t(2 * C::kJ * C::kRowBytes + kTT * C::kActBytes) +
+  return (C::kGrid ? kGridRepBytes : 0) + 64 + 2 * size_t(2 * C::kJ * C::kRowBytes + C::kUpPad + kTT * C::kActBytes) +
          C::kPartialFloats * 4 + 16 + 64;
 }
 template <int FMT, int INTER>
