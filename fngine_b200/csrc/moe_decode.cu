@@ -32,25 +32,29 @@ constexpr int kSchedOrderBase = 8;
 constexpr int kEpMaxRanks = FB_EP_MAX_RANKS;
 constexpr uint32_t kPeerSpinLimit = 1u << 20;  // polls of a peer-written flag before giving up (about a second)
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// Flag-in-data exchange lines (the low-latency protocol of collective libraries): 16 bytes =
+// {value 0, step, value 1, step}, written by ONE 16-byte store, so a reader that sees the step
+// number of the current step in both flag words holds both values - no fence, no separate flag.
+__device__ __forceinline__ void ll_store(uint4* line, float v0, float v1, uint32_t step) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(line), "r"(__float_as_uint(v0)), "r"(step),
+               "r"(__float_as_uint(v1)), "r"(step)
+               : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// Step counters only grow: true once *p has reached `want`, false when the limit ran out.
-__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want) {
+// Polls the line (a bounded number of times) until both halves carry `step`.
+__device__ __forceinline__ float2 ll_read(const uint4* line, uint32_t step, uint32_t* status) {
+  uint4 v;
   for (uint32_t i = 0; i < kPeerSpinLimit; ++i) {
-    if (int32_t(ld_acquire_sys(p) - want) >= 0) return true;
-    __nanosleep(200);
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(line)
+                 : "memory");
+    if (v.y == step && v.w == step) return make_float2(__uint_as_float(v.x), __uint_as_float(v.z));
+    __nanosleep(100);
   }
-  return false;
+  atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+  return make_float2(0.0f, 0.0f);
 }
 constexpr int kSchedRoute = 2;
-constexpr int kSchedEpSend = 3;  // ticket of ep_combine_exchange_kernel
-constexpr int kSchedEpPub = 224;  // 8 per-destination tickets of the x publication in route_kernel
 constexpr int kSchedGroup = 192;  // 32 row-group tickets of route_kernel
 constexpr int kSchedInts = 256;
 
@@ -367,33 +371,23 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
   pdl_launch_dependents();
   pdl_wait_prior();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (ep.peers.n_ranks > 0) {
-    // Expert-parallel step: first this rank's own rows go to every rank (block b serves rank
-    // b % R with slice b / R of the rows; the block that completes a rank's slices publishes the
-    // flag there), then every block waits until all source ranks' rows have arrived here.
+  const bool ep_mode = ep.peers.n_ranks > 0;
+  const uint4* x_lines = nullptr;  // this rank's copy of all tokens' rows, as exchange lines
+  if (ep_mode) {
+    // Expert-parallel step: this rank's own rows go to every rank as flag-in-data lines (block b
+    // serves rank b % R with slice b / R of the rows); readers below poll the lines they need.
     const int R = ep.peers.n_ranks, d = int(blockIdx.x) % R, slice = int(blockIdx.x) / R, n_slices = int(gridDim.x) / R;
     const int total = ep.tpr * (H / 4), lo = int(int64_t(total) * slice / n_slices),
               hi = int(int64_t(total) * (slice + 1) / n_slices);
-    float4* dst = reinterpret_cast<float4*>(ep.peers.x_all[d] +
-                                            (size_t(ep.parity) * kMaxTok + size_t(ep.peers.rank) * ep.tpr) * H);
+    uint4* dst = static_cast<uint4*>(ep.peers.x_all[d]) +
+                 (size_t(ep.parity) * kMaxTok + size_t(ep.peers.rank) * ep.tpr) * (H / 2);
     const float4* src = reinterpret_cast<const float4*>(ep.x_local);
-    for (int i = lo + tid; i < hi; i += 512) dst[i] = src[i];
-    __shared__ int s_pub;
-    __threadfence_system();
-    __syncthreads();
-    if (tid == 0) {
-      const int ticket = atomicAdd(ws.sched + kSchedEpPub + d, 1);
-      s_pub = ticket == n_slices - 1;
-      if (s_pub) {
-        ws.sched[kSchedEpPub + d] = 0;
-        __threadfence_system();
-        st_release_sys(ep.peers.flags[d] + (ep.parity * 2 + 0) * kEpMaxRanks + ep.peers.rank, ep.step);
-      }
+    for (int i = lo + tid; i < hi; i += 512) {
+      const float4 v = src[i];
+      ll_store(dst + 2 * i, v.x, v.y, ep.step);
+      ll_store(dst + 2 * i + 1, v.z, v.w, ep.step);
     }
-    if (tid < R &&
-        !wait_flag(ep.peers.flags[ep.peers.rank] + (ep.parity * 2 + 0) * kEpMaxRanks + tid, ep.step))
-      atomicMax(ws.status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
-    __syncthreads();
+    x_lines = static_cast<const uint4*>(ep.peers.x_all[ep.peers.rank]) + size_t(ep.parity) * kMaxTok * (H / 2);
   }
   // x slice [token][320]; later the logits [token][expert]
   __shared__ __align__(16) float s_buf[kMaxTok * kExperts];
@@ -403,7 +397,11 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
   for (int i = tid; i < T * (kRouteSlice / 4); i += 512) {
     const int t = i / (kRouteSlice / 4), c = i - t * (kRouteSlice / 4);
     float4 v;
-    if constexpr (XBF16) {
+    if (ep_mode) {
+      const uint4* ln = x_lines + (size_t(t) * H + q * kRouteSlice) / 2 + 2 * c;
+      const float2 a = ll_read(ln, ep.step, ws.status), b2 = ll_read(ln + 1, ep.step, ws.status);
+      v = make_float4(a.x, a.y, b2.x, b2.y);
+    } else if constexpr (XBF16) {
       const uint2 u = reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(xv) + size_t(t) * H +
                                                      q * kRouteSlice)[c];
       v = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u), __uint_as_float(u.y << 16),
@@ -487,8 +485,18 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
       float* scales = reinterpret_cast<float*>(out + H);
       if (act == FB_ACT_Q8_K) {
         float v[8];
+        if (ep_mode) {
+          const uint4* ln = x_lines + (size_t(t) * H + 256 * b + 8 * lane) / 2;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = load(256 * b + 8 * lane + i);
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = ll_read(ln + i, ep.step, ws.status);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = load(256 * b + 8 * lane + i);
+        }
         int qv[8], ps;
         const float d = q8k_block_warp(v, qv, ps);
         uint2 pk;
@@ -500,7 +508,14 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
         if (lane == 0) scales[b] = d;
       } else {
         unsigned short dh;
-        const int qv = q8_0_block_warp(load(32 * b + lane), dh);
+        float xv1;
+        if (ep_mode) {
+          const float2 f = ll_read(x_lines + (size_t(t) * H + 32 * b + lane) / 2, ep.step, ws.status);
+          xv1 = (lane & 1) ? f.y : f.x;
+        } else {
+          xv1 = load(32 * b + lane);
+        }
+        const int qv = q8_0_block_warp(xv1, dh);
         out[32 * b + q8_0_interleave_index(lane)] = uint8_t(int8_t(qv));
         if (lane == 0) scales[b] = __half2float(__ushort_as_half(dh));
       }
@@ -1190,20 +1205,19 @@ __global__ void __launch_bounds__(256) sum_ranks_kernel(const float* __restrict_
 }
 
 // ------------------------------------------------------------------------------ peer-memory exchange
-// Expert-parallel decode without a collective library call in the step: ranks write straight into
-// each other's buffers over NVLink (plain peer stores) and publish a step counter per source rank
-// with a system-scope release store; readers poll their OWN memory with acquire loads, a bounded
-// number of times. Buffers are double-buffered by step parity: a rank can be at most one step ahead
-// of a peer (it needs that peer's partial rows to finish a step), so parity p of step k+2 is never
-// written while anyone still reads step k.
-//   x_all   [2][16][2560] fp32    all tokens of the step, rows written by their owners
-//   y_parts [2][8][16][2560] fp32 [parity][source rank][local token]: partial rows for this rank's tokens
-//   flags   [2][2][8] u32         [parity][0 = x rows, 1 = partial rows][source rank] = step number
+// Expert-parallel decode without a collective library call in the step: ranks write flag-in-data
+// lines (ll_store) straight into each other's buffers over NVLink and readers poll the lines they
+// need in their OWN memory, a bounded number of times. No fence, no ticket, no separate flag sits
+// between the data and its arrival. Buffers are double-buffered by step parity: a rank can be at
+// most one step ahead of a peer (it needs that peer's partial rows to finish a step), so the lines
+// of step k+2 never overwrite lines of step k that someone still reads, and a stale line (step
+// k-2) never passes for a current one.
+//   x_all   [2][16][1280] lines         all tokens of the step, rows written by their owners
+//   y_parts [2][8][16][1280] lines      [parity][source rank][local token]: partial rows for this rank's tokens
 
-// The combine of an expert-parallel step. Block (t, column slice): token t's partial row over the local
-// pairs (slot order) goes straight into its owner's y_parts; the block that finishes last publishes
-// this rank's flag on every rank. Blocks of tokens this rank owns then wait (bounded) for every
-// rank's flag and add the partial rows in rank order.
+// The combine of an expert-parallel step. Thread = (token t, two adjacent columns): token t's partial
+// row over the local pairs (slot order) goes straight into its owner's y_parts; threads of tokens
+// this rank owns then read the partial rows of all ranks and add them in rank order.
 __global__ void __launch_bounds__(256) ep_combine_exchange_kernel(fb_moe_decode_workspace ws, fb_ep_peers peers, int tpr,
                                                                   int parity, uint32_t step, float* __restrict__ y_local) {
   pdl_launch_dependents();
@@ -1211,34 +1225,25 @@ __global__ void __launch_bounds__(256) ep_combine_exchange_kernel(fb_moe_decode_
   const int t = blockIdx.y;
   const fb_moe_decode_work* work = ws.work;
   const int np = min(max(work->token_pair_count[t], 0), kTopK);
-  const int n = blockIdx.x * 256 + threadIdx.x;
-  float y = 0.0f;
-  for (int k = 0; k < np; ++k) y += ws.partial[size_t(work->token_pairs[t][k]) * H + n];
+  const int c = blockIdx.x * 256 + threadIdx.x;  // line = columns 2c, 2c+1
+  float y0 = 0.0f, y1 = 0.0f;
+  for (int k = 0; k < np; ++k) {
+    const float2 v = *reinterpret_cast<const float2*>(ws.partial + size_t(work->token_pairs[t][k]) * H + 2 * c);
+    y0 += v.x;
+    y1 += v.y;
+  }
   const int d = t / tpr, i = t - d * tpr;
-  peers.y_parts[d][((size_t(parity) * kEpMaxRanks + peers.rank) * kMaxTok + i) * H + n] = y;
-  __shared__ int s_last;
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int ticket = atomicAdd(ws.sched + kSchedEpSend, 1);
-    s_last = ticket == int(gridDim.x * gridDim.y) - 1;
-    if (s_last) ws.sched[kSchedEpSend] = 0;
-  }
-  __syncthreads();
-  if (s_last && threadIdx.x < peers.n_ranks) {
-    __threadfence_system();
-    st_release_sys(peers.flags[threadIdx.x] + (parity * 2 + 1) * kEpMaxRanks + peers.rank, step);
-  }
+  ll_store(static_cast<uint4*>(peers.y_parts[d]) + ((size_t(parity) * kEpMaxRanks + peers.rank) * kMaxTok + i) * (H / 2) + c,
+           y0, y1, step);
   if (d != peers.rank) return;
-  if (threadIdx.x < peers.n_ranks &&
-      !wait_flag(peers.flags[peers.rank] + (parity * 2 + 1) * kEpMaxRanks + threadIdx.x, step))
-    atomicMax(ws.status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
-  __syncthreads();
-  const float* mine = peers.y_parts[peers.rank];
-  float acc = 0.0f;
-  for (int s = 0; s < peers.n_ranks; ++s)
-    acc += __ldcg(mine + ((size_t(parity) * kEpMaxRanks + s) * kMaxTok + i) * H + n);
-  y_local[size_t(i) * H + n] = acc;
+  const uint4* mine = static_cast<const uint4*>(peers.y_parts[peers.rank]);
+  float a0 = 0.0f, a1 = 0.0f;
+  for (int s = 0; s < peers.n_ranks; ++s) {
+    const float2 v = ll_read(mine + ((size_t(parity) * kEpMaxRanks + s) * kMaxTok + i) * (H / 2) + c, step, ws.status);
+    a0 += v.x;
+    a1 += v.y;
+  }
+  *reinterpret_cast<float2*>(y_local + size_t(i) * H + 2 * c) = make_float2(a0, a1);
 }
 
 // ------------------------------------------------------------------------------ host side
@@ -1476,7 +1481,7 @@ int32_t fb_moe_layer_decode_ep_p2p(const void* router_w_bf16, const fb_moe_exper
       tokens % peers->n_ranks || step == 0)
     return invalid("layer_decode_ep_p2p: bad arguments (tokens a multiple of the rank count, at most 16; step >= 1)");
   for (int d = 0; d < peers->n_ranks; ++d)
-    if (!peers->x_all[d] || !peers->y_parts[d] || !peers->flags[d])
+    if (!peers->x_all[d] || !peers->y_parts[d])
       return invalid("layer_decode_ep_p2p: a peer buffer address is missing");
   const int R = peers->n_ranks, tpr = tokens / R, parity = int(step & 1u);
   cudaStream_t s = as_stream(stream);
@@ -1488,11 +1493,11 @@ int32_t fb_moe_layer_decode_ep_p2p(const void* router_w_bf16, const fb_moe_exper
   era.tpr = tpr;
   era.parity = parity;
   era.step = step;
-  const float* x_all = peers->x_all[peers->rank] + size_t(parity) * kMaxTok * H;
-  int32_t st = layer_decode_impl(router_w_bf16, layout, slot_of, true, x_all, FB_DT_F32, tokens, ws, logits_scratch,
+  // (the route kernel reads every x row through the exchange lines; x_local only satisfies the argument check)
+  int32_t st = layer_decode_impl(router_w_bf16, layout, slot_of, true, x_local, FB_DT_F32, tokens, ws, logits_scratch,
                                  nullptr, stream, &era);
   if (st) return st;
-  const cudaError_t e = launch_pdl(ep_combine_exchange_kernel, dim3(H / 256, tokens), dim3(256), 0, s, *ws, *peers, tpr,
+  const cudaError_t e = launch_pdl(ep_combine_exchange_kernel, dim3(H / 512, tokens), dim3(256), 0, s, *ws, *peers, tpr,
                                    parity, step, y_local);
   if (e != cudaSuccess) return check_launch("layer_decode_ep_p2p: combine");
   return check_launch("layer_decode_ep_p2p");
@@ -1501,14 +1506,13 @@ int32_t fb_moe_layer_decode_ep_p2p(const void* router_w_bf16, const fb_moe_exper
 // Exchange buffers of fb_moe_layer_decode_ep_p2p. They are allocated here (cudaMalloc, so a CUDA IPC
 // handle names exactly the buffer) and opened by the peers in the context of THEIR OWN device with
 // lazy peer access, the way collective libraries map each other's memory.
-constexpr size_t kEpBytes[3] = {size_t(2) * kMaxTok * H * 4, size_t(2) * kEpMaxRanks * kMaxTok * H * 4,
-                                size_t(2) * 2 * kEpMaxRanks * 4};
+constexpr size_t kEpBytes[2] = {size_t(2) * kMaxTok * (H / 2) * 16, size_t(2) * kEpMaxRanks * kMaxTok * (H / 2) * 16};
 
-int32_t fb_ep_exchange_create(void** x_all, void** y_parts, void** flags, uint8_t* handles) {
-  if (!x_all || !y_parts || !flags || !handles) return invalid("ep_exchange_create: NULL argument");
+int32_t fb_ep_exchange_create(void** x_all, void** y_parts, uint8_t* handles) {
+  if (!x_all || !y_parts || !handles) return invalid("ep_exchange_create: NULL argument");
   static_assert(sizeof(cudaIpcMemHandle_t) == FB_EP_HANDLE_BYTES, "handle size");
-  void** out[3] = {x_all, y_parts, flags};
-  for (int k = 0; k < 3; ++k) {
+  void** out[2] = {x_all, y_parts};
+  for (int k = 0; k < 2; ++k) {
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, kEpBytes[k]);
     if (e == cudaSuccess) e = cudaMemset(p, 0, kEpBytes[k]);
@@ -1525,10 +1529,10 @@ int32_t fb_ep_exchange_create(void** x_all, void** y_parts, void** flags, uint8_
   return int32_t(cudaDeviceSynchronize());
 }
 
-int32_t fb_ep_exchange_open(const uint8_t* handles, void** x_all, void** y_parts, void** flags) {
-  if (!x_all || !y_parts || !flags || !handles) return invalid("ep_exchange_open: NULL argument");
-  void** out[3] = {x_all, y_parts, flags};
-  for (int k = 0; k < 3; ++k) {
+int32_t fb_ep_exchange_open(const uint8_t* handles, void** x_all, void** y_parts) {
+  if (!x_all || !y_parts || !handles) return invalid("ep_exchange_open: NULL argument");
+  void** out[2] = {x_all, y_parts};
+  for (int k = 0; k < 2; ++k) {
     cudaIpcMemHandle_t h;
     memcpy(&h, handles + k * FB_EP_HANDLE_BYTES, FB_EP_HANDLE_BYTES);
     void* p = nullptr;
@@ -1543,10 +1547,10 @@ int32_t fb_ep_exchange_open(const uint8_t* handles, void** x_all, void** y_parts
   return 0;
 }
 
-int32_t fb_ep_exchange_close(void* x_all, void* y_parts, void* flags, int32_t own) {
-  void* p[3] = {x_all, y_parts, flags};
+int32_t fb_ep_exchange_close(void* x_all, void* y_parts, int32_t own) {
+  void* p[2] = {x_all, y_parts};
   int32_t st = 0;
-  for (int k = 0; k < 3; ++k) {
+  for (int k = 0; k < 2; ++k) {
     if (!p[k]) continue;
     const cudaError_t e = own ? cudaFree(p[k]) : cudaIpcCloseMemHandle(p[k]);
     if (e != cudaSuccess) {
@@ -1556,6 +1560,8 @@ int32_t fb_ep_exchange_close(void* x_all, void* y_parts, void* flags, int32_t ow
   }
   return st;
 }
+
+size_t fb_ep_exchange_bytes(int32_t which) { return which == 0 ? kEpBytes[0] : which == 1 ? kEpBytes[1] : 0; }
 
 int32_t fb_ep_sum_ranks(const float* parts, int32_t n_ranks, int32_t rows, float* y, void* stream) {
   if (!parts || !y || n_ranks < 1 || rows < 1) return invalid("ep_sum_ranks: bad arguments");

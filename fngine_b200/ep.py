@@ -126,8 +126,8 @@ def sum_ranks(parts, y):
 
 
 class PeerExchange:
-    """The three exchange buffers of fb_moe_layer_decode_ep_p2p on this rank, mapped into every peer
-    process with CUDA IPC (the 192 handle bytes travel through the process group once, at set-up)."""
+    """The two exchange buffers of fb_moe_layer_decode_ep_p2p on this rank, mapped into every peer
+    process with CUDA IPC (the 128 handle bytes travel through the process group once, at set-up)."""
 
     def __init__(self, rank, world, group=None):
         import ctypes as C
@@ -135,9 +135,9 @@ class PeerExchange:
         from . import lib as L
         lib = L.load()
         self.rank, self.world, self.step = rank, world, 0
-        own = [C.c_void_p() for _ in range(3)]
-        handles = (C.c_uint8 * 192)()
-        L.check(lib.fb_ep_exchange_create(C.byref(own[0]), C.byref(own[1]), C.byref(own[2]), handles), "ep_exchange_create")
+        own = [C.c_void_p() for _ in range(2)]
+        handles = (C.c_uint8 * 128)()
+        L.check(lib.fb_ep_exchange_create(C.byref(own[0]), C.byref(own[1]), handles), "ep_exchange_create")
         gathered = [None] * world
         dist.all_gather_object(gathered, bytes(handles), group=group)
         self.peers = L.EpPeers()
@@ -147,11 +147,11 @@ class PeerExchange:
             if d == rank:
                 ptrs = own
             else:
-                ptrs = [C.c_void_p() for _ in range(3)]
-                hb = (C.c_uint8 * 192).from_buffer_copy(gathered[d])
-                L.check(lib.fb_ep_exchange_open(hb, C.byref(ptrs[0]), C.byref(ptrs[1]), C.byref(ptrs[2])), "ep_exchange_open")
+                ptrs = [C.c_void_p() for _ in range(2)]
+                hb = (C.c_uint8 * 128).from_buffer_copy(gathered[d])
+                L.check(lib.fb_ep_exchange_open(hb, C.byref(ptrs[0]), C.byref(ptrs[1])), "ep_exchange_open")
                 self._opened.append(ptrs)
-            self.peers.x_all[d], self.peers.y_parts[d], self.peers.flags[d] = (p.value for p in ptrs)
+            self.peers.x_all[d], self.peers.y_parts[d] = (p.value for p in ptrs)
         self._own = own
         dist.barrier(group=group)
 
@@ -159,10 +159,10 @@ class PeerExchange:
         from . import lib as L
         lib = L.load()
         for ptrs in self._opened:
-            lib.fb_ep_exchange_close(ptrs[0], ptrs[1], ptrs[2], 0)
+            lib.fb_ep_exchange_close(ptrs[0], ptrs[1], 0)
         self._opened = []
         if self._own:
-            lib.fb_ep_exchange_close(self._own[0], self._own[1], self._own[2], 1)
+            lib.fb_ep_exchange_close(self._own[0], self._own[1], 1)
             self._own = None
 
 

@@ -62,7 +62,7 @@ EP_MAX_RANKS = 8
 class EpPeers(C.Structure):
     """fb_ep_peers: peer-mapped exchange buffers of an expert-parallel decode step."""
     _fields_ = [("rank", C.c_int32), ("n_ranks", C.c_int32), ("x_all", C.c_void_p * EP_MAX_RANKS),
-                ("y_parts", C.c_void_p * EP_MAX_RANKS), ("flags", C.c_void_p * EP_MAX_RANKS)]
+                ("y_parts", C.c_void_p * EP_MAX_RANKS)]
 
 
 _SIGNATURES = {
@@ -96,9 +96,10 @@ _SIGNATURES = {
     "fb_moe_layer_decode_ep": (_I32, [_P, C.POINTER(ExpertLayout), _P, _P, _I32, _I32, C.POINTER(DecodeWorkspace), _P, _P,
                                _P]),
     "fb_ep_sum_ranks": (_I32, [_P, _I32, _I32, _P, _P]),
-    "fb_ep_exchange_create": (_I32, [_P, _P, _P, _P]),
-    "fb_ep_exchange_open": (_I32, [_P, _P, _P, _P]),
-    "fb_ep_exchange_close": (_I32, [_P, _P, _P, _I32]),
+    "fb_ep_exchange_bytes": (C.c_size_t, [_I32]),
+    "fb_ep_exchange_create": (_I32, [_P, _P, _P]),
+    "fb_ep_exchange_open": (_I32, [_P, _P, _P]),
+    "fb_ep_exchange_close": (_I32, [_P, _P, _I32]),
     "fb_moe_layer_decode_ep_p2p": (_I32, [_P, C.POINTER(ExpertLayout), _P, _P, _I32, C.POINTER(EpPeers), C.c_uint32,
                                           C.POINTER(DecodeWorkspace), _P, _P, _P]),
     "fb_moe_topk": (_I32, [_P, _I32, _I32, _P, _P, _P]),

@@ -256,34 +256,34 @@ int32_t fb_moe_layer_decode_ep(const void* router_w_bf16, const fb_moe_expert_la
                                const fb_moe_decode_workspace* ws, float* logits_scratch, float* y_partial,
                                void* stream);
 /* The same step with the exchange done by the kernels themselves over peer-mapped memory (NVLink
- * loads/stores, no collective library call): every rank owns tokens / n_ranks consecutive tokens.
- * x_all[d], y_parts[d], flags[d] are the addresses, valid in THIS process, of rank d's three exchange
- * buffers (CUDA IPC or any other peer mapping; entry `rank` is this rank's own memory):
- *   x_all   fp32 [2][16][2560], y_parts fp32 [2][8][16][2560], flags u32 [2][2][8], zero-filled once.
- * A step: the rank writes its x rows into every x_all and publishes flags[d][parity][0][rank] = step;
- * the route kernel waits for the n_ranks x flags in its own memory, the layer runs over the local
- * experts, the combine writes each token's partial row into its owner's y_parts and publishes
- * flags[d][parity][1][rank]; the owner waits for the n_ranks flags and adds the partial rows in rank
+ * stores, no collective library call): every rank owns tokens / n_ranks consecutive tokens.
+ * x_all[d] and y_parts[d] are the addresses, valid in THIS process, of rank d's two exchange buffers
+ * (entry `rank` is this rank's own memory). Data travels as 16-byte lines {value, step, value, step}
+ * written by one store each, so a reader that finds the current step number in both flag words has
+ * the values: there is no fence and no separate flag. A step: the route kernel writes the rank's x
+ * rows into every rank's x_all and reads all rows of the step from its own x_all, polling lines
+ * that have not arrived yet; the layer runs over the local experts; the combine writes every
+ * token's partial row into its owner's y_parts, and the owner adds the n_ranks partial rows in rank
  * order into y_local [tokens / n_ranks][2560]. `step` must be 1, 2, 3, ... in call order and equal
- * on all ranks; waits are bounded (about a second) and end with FB_STATUS_PIPELINE_TIMEOUT in the
- * workspace status word. x_local is fp32. */
-/* Set-up of those buffers (not part of a step). fb_ep_exchange_create allocates and zero-fills this
- * rank's three buffers on the current device and writes their CUDA IPC handles (3 x 64 bytes) to
- * `handles`; the ranks trade the handle bytes through any channel and fb_ep_exchange_open maps a
- * peer's buffers into the context of the current device (lazy peer access). fb_ep_exchange_close
- * unmaps a peer's buffers (own = 0) or frees this rank's (own = 1). */
+ * on all ranks; polls are bounded (about a second) and end with FB_STATUS_PIPELINE_TIMEOUT in the
+ * workspace status word. x_local is fp32.
+ * Set-up (not part of a step): fb_ep_exchange_create allocates and zero-fills this rank's two
+ * buffers on the current device (fb_ep_exchange_bytes(0 / 1) bytes) and writes their CUDA IPC
+ * handles (2 x 64 bytes) to `handles`; the ranks trade the handle bytes through any channel and
+ * fb_ep_exchange_open maps a peer's buffers into the context of the current device (lazy peer
+ * access). fb_ep_exchange_close unmaps a peer's buffers (own = 0) or frees this rank's (own = 1). */
 #define FB_EP_HANDLE_BYTES 64
-int32_t fb_ep_exchange_create(void** x_all, void** y_parts, void** flags, uint8_t* handles);
-int32_t fb_ep_exchange_open(const uint8_t* handles, void** x_all, void** y_parts, void** flags);
-int32_t fb_ep_exchange_close(void* x_all, void* y_parts, void* flags, int32_t own);
 #define FB_EP_MAX_RANKS 8
 typedef struct fb_ep_peers {
   int32_t rank;
   int32_t n_ranks;
-  float* x_all[FB_EP_MAX_RANKS];
-  float* y_parts[FB_EP_MAX_RANKS];
-  uint32_t* flags[FB_EP_MAX_RANKS];
+  void* x_all[FB_EP_MAX_RANKS];
+  void* y_parts[FB_EP_MAX_RANKS];
 } fb_ep_peers;
+size_t fb_ep_exchange_bytes(int32_t which);
+int32_t fb_ep_exchange_create(void** x_all, void** y_parts, uint8_t* handles);
+int32_t fb_ep_exchange_open(const uint8_t* handles, void** x_all, void** y_parts);
+int32_t fb_ep_exchange_close(void* x_all, void* y_parts, int32_t own);
 int32_t fb_moe_layer_decode_ep_p2p(const void* router_w_bf16, const fb_moe_expert_layout* layout,
                                    const int32_t* slot_of, const float* x_local, int32_t tokens,
                                    const fb_ep_peers* peers, uint32_t step, const fb_moe_decode_workspace* ws,

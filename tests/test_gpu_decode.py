@@ -404,13 +404,13 @@ def test_peer_exchange_layer_with_one_rank_equals_the_plain_layer():
     full = moe.synth_layer(IQ3_S, IQ3_S, 512, 512, seed)
     ws = moe.DecodeWorkspace(full)
     slot_of = torch.arange(512, dtype=torch.int32, device="cuda")
-    bufs = [torch.zeros(n, dtype=torch.uint8, device="cuda")
-            for n in (2 * 16 * H * 4, 2 * fblib.EP_MAX_RANKS * 16 * H * 4, 2 * 2 * fblib.EP_MAX_RANKS * 4)]
+    lib = fblib.load()
+    bufs = [torch.zeros(lib.fb_ep_exchange_bytes(k), dtype=torch.uint8, device="cuda") for k in (0, 1)]
     xchg = ep.PeerExchange.__new__(ep.PeerExchange)
     xchg.rank, xchg.world, xchg.step, xchg.local = 0, 1, 0, bufs
     xchg.peers = fblib.EpPeers()
     xchg.peers.rank, xchg.peers.n_ranks = 0, 1
-    xchg.peers.x_all[0], xchg.peers.y_parts[0], xchg.peers.flags[0] = (b.data_ptr() for b in bufs)
+    xchg.peers.x_all[0], xchg.peers.y_parts[0] = (b.data_ptr() for b in bufs)
     shard = C.Structure.__new__(C.Structure) if False else type("S", (), {})()
     shard.layer, shard.slot_of = full, slot_of
     y_ref = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
