@@ -118,33 +118,53 @@ def ep_layer_generic(x_local, topk_expert, topk_weight, rank, world, local_rows_
     return y, stats
 
 
-def ep_layer_dense(x_local, topk_expert, topk_weight, rank, world, local_rows_fn, sum_ranks_fn, group=None):
+def ep_layer_dense(x_local, topk_expert, topk_weight, rank, world, local_rows_fn, sum_ranks_fn, group=None, chunks=1):
     """Dense exchange: all-gather rows and lists, partial rows for all tokens, fixed-size all-to-all,
-    rank-order sum. local_rows_fn as in ep_layer_generic; sum_ranks_fn([R][T_local][H]) -> [T_local][H]."""
+    rank-order sum. local_rows_fn as in ep_layer_generic; sum_ranks_fn([R][rows][H]) -> [rows][H].
+    With chunks > 1 the rank's tokens are cut into that many pieces and pipelined: the all-to-all of
+    piece c runs (on the collective library's stream) while piece c+1 is gathered and computed."""
     import torch.distributed as dist
     per = experts_per_rank(world)
     tl = x_local.shape[0]
     lists = pack_lists(topk_expert, topk_weight)
-    if world == 1:
-        x_all, l_all = x_local, lists
-    else:
-        xb = x_local.contiguous().view(torch.uint8).reshape(tl, -1)
-        x_all_b = torch.empty(tl * world, xb.shape[1], dtype=torch.uint8, device=x_local.device)
-        l_all = torch.empty(tl * world, lists.shape[1], dtype=lists.dtype, device=lists.device)
-        dist.all_gather_into_tensor(x_all_b, xb, group=group)
-        dist.all_gather_into_tensor(l_all, lists.contiguous(), group=group)
-        x_all = x_all_b.view(x_local.dtype).reshape(tl * world, x_local.shape[1])
-    e_rows, w_rows = unpack_lists(l_all)
-    y_part = local_rows_fn(x_all, e_rows, w_rows, rank * per, (rank + 1) * per)  # [T][H] fp32
-    if world == 1:
-        parts = y_part.unsqueeze(0)
-    else:
-        recv = torch.empty_like(y_part)
-        dist.all_to_all_single(recv, y_part.contiguous(), group=group)
-        parts = recv.view(world, tl, y_part.shape[1])
-    stats = {"rows_received": tl * world, "dispatch_bytes": tl * (world - 1) * (x_local.shape[1] * x_local.element_size() + 8 * TOPK),
+    stats = {"rows_received": tl * world,
+             "dispatch_bytes": tl * (world - 1) * (x_local.shape[1] * x_local.element_size() + 8 * TOPK),
              "combine_bytes": tl * (world - 1) * x_local.shape[1] * 4}
-    return sum_ranks_fn(parts), stats
+    if world == 1:
+        e_rows, w_rows = unpack_lists(lists)
+        return sum_ranks_fn(local_rows_fn(x_local, e_rows, w_rows, 0, per).unsqueeze(0)), stats
+    chunks = max(1, min(chunks, tl))
+    bounds = [tl * c // chunks for c in range(chunks + 1)]
+
+    def gather(c):
+        lo, hi = bounds[c], bounds[c + 1]
+        xb = x_local[lo:hi].contiguous().view(torch.uint8).reshape(hi - lo, -1)
+        x_all_b = torch.empty((hi - lo) * world, xb.shape[1], dtype=torch.uint8, device=x_local.device)
+        l_all = torch.empty((hi - lo) * world, lists.shape[1], dtype=lists.dtype, device=lists.device)
+        w1 = dist.all_gather_into_tensor(x_all_b, xb, group=group, async_op=True)
+        w2 = dist.all_gather_into_tensor(l_all, lists[lo:hi].contiguous(), group=group, async_op=True)
+        return x_all_b, l_all, (w1, w2)
+
+    pending = gather(0)
+    returns = []
+    for c in range(chunks):
+        x_all_b, l_all, works = pending
+        for w in works:
+            w.wait()
+        if c + 1 < chunks:
+            pending = gather(c + 1)
+        n = bounds[c + 1] - bounds[c]
+        x_all = x_all_b.view(x_local.dtype).reshape(n * world, x_local.shape[1])
+        e_rows, w_rows = unpack_lists(l_all)
+        y_part = local_rows_fn(x_all, e_rows, w_rows, rank * per, (rank + 1) * per)  # [n * R][H] fp32
+        recv = torch.empty_like(y_part)
+        work = dist.all_to_all_single(recv, y_part.contiguous(), group=group, async_op=True)
+        returns.append((recv, work, n, y_part))
+    outs = []
+    for recv, work, n, _keep in returns:
+        work.wait()
+        outs.append(sum_ranks_fn(recv.view(world, n, recv.shape[1])))
+    return (outs[0] if chunks == 1 else torch.cat(outs)), stats
 
 
 # --------------------------------------------------------------------------------------------- GPU side
@@ -210,12 +230,12 @@ def sum_ranks(parts):
     return y
 
 
-def ep_prefill_layer(logits_local, x_local, shard, ws, group=None, mode="dense"):
+def ep_prefill_layer(logits_local, x_local, shard, ws, group=None, mode="dense", chunks=2):
     """One expert-parallel prefill layer on GPUs; returns (y of this rank's tokens, stats)."""
     e, w = topk(logits_local)
     compute = lambda xr, er, wr, lo, hi: local_rows(shard, ws, xr, er, wr, lo, hi)  # noqa: E731
     if mode == "dense":
-        return ep_layer_dense(x_local, e, w, shard.rank, shard.world, compute, sum_ranks, group)
+        return ep_layer_dense(x_local, e, w, shard.rank, shard.world, compute, sum_ranks, group, chunks)
     return ep_layer_generic(x_local, e, w, shard.rank, shard.world, compute, scatter_sum, group)
 
 
@@ -305,8 +325,10 @@ def bench_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_tokens=
             "rows_received_per_stack": {"sum": agg[0].item(), "max_rank": mx[0].item()},
             "all_to_all_bytes_per_stack": {"dispatch": agg[1].item(), "combine": agg[2].item(),
                                            "max_rank_dispatch": mx[1].item(), "max_rank_combine": mx[2].item()},
-            "collectives_per_layer": "dense exchange: all-gather of bf16 rows + all-gather of (expert, weight) lists + one "
-                                     "fixed-size fp32 all-to-all, rank-order sum on the owner (NCCL; no host sync)",
+            "collectives_per_layer": "dense exchange in two pipelined pieces: all-gather of bf16 rows + all-gather of "
+                                     "(expert, weight) lists + one fixed-size fp32 all-to-all per piece, rank-order "
+                                     "sum on the owner (NCCL; no host sync; a piece's all-to-all overlaps the next "
+                                     "piece's GEMMs)",
             "parity_layer0_max_rel_l2": parity, "parity_tokens": parity_tokens,
             "finite_output": bool(finite[0].item()), "device_status_ok": bool(finite[1].item()),
             "timed_region_includes": "torch router projection + unit-RMS rescale between layers, dispatch gather"}

@@ -102,7 +102,7 @@ void ref_silu_mul(const float* g, const float* u, float* h, int n) { silu_mul(g,
 // ---------------------------------------------------------------------------------------------
 // Drivers over the reference primitives. The reference's ExpertPool fixes hidden 2560 / inter 640
 // and a Q8_0 down projection at compile time (src/cpu/expert_pool.cpp:22-38, :525-526), so the
-// judged shapes (inter 512, IQ3_S down) are assembled here from the same primitives in the same
+// benchmark shapes (inter 512, IQ3_S down) are assembled here from the same primitives in the same
 // phase order (src/cpu/expert_pool.cpp:330-408): activations quantized and packed once per token,
 // gate/up rows decoded four at a time and multiplied, SwiGLU, h re-quantized for the down format,
 // down rows decoded and multiplied, per-token weighted sum over experts in ascending id.

@@ -47,7 +47,7 @@ def main():
     u = synth.normal(22, 4096).astype(np.float32)
     g[:8] = [0.0, -0.0, 100.0, -100.0, 88.0, -88.0, 1e-20, -1e-20]
     out["silu"] = O.silu_mul(g, u, lib=ref)
-    # one expert, decode numerics, the judged shapes (IQ3_S x3, inter 512) and the IQ4_NL variant
+    # one expert, decode numerics, the benchmark shapes (IQ3_S x3, inter 512) and the IQ4_NL variant
     xs = synth.activations(31, 3)
     for fg, fd, inter, name in ((IQ3_S, IQ3_S, 512, "ffn_iq3s_512"), (IQ4_NL, IQ4_NL, 512, "ffn_iq4nl_512"),
                                 (IQ3_S, IQ4_NL, 640, "ffn_iq3s_iq4nl_640")):

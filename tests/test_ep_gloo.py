@@ -145,7 +145,7 @@ def _prefill_rank_main(rank, world, port, out_dir, mode):
         out = np.zeros((x_rows.shape[0], H), dtype=np.float32)
         for r in range(x_rows.shape[0]):
             pairs = sorted((int(e), float(wt)) for e, wt in zip(e_rows[r].tolist(), w_rows[r].tolist()) if elo <= e < ehi)
-            assert pairs or mode == "dense", "a row was sent to a rank that holds none of its experts"
+            assert pairs or mode.startswith("dense"), "a row was sent to a rank that holds none of its experts"
             for e, wt in pairs:  # ascending expert id
                 out[r] += np.float32(wt) * _expert_row(e, x_rows[r].numpy().view(np.uint16))
         return torch.from_numpy(out)
@@ -160,8 +160,8 @@ def _prefill_rank_main(rank, world, port, out_dir, mode):
 
     args = (torch.from_numpy(x[lo:hi].view(np.int16).copy()), torch.from_numpy(ids[lo:hi].copy()),
             torch.from_numpy(w[lo:hi].copy()), rank, world, local_rows)
-    if mode == "dense":
-        y, stats = ep_prefill.ep_layer_dense(*args, ep.combine_sum)
+    if mode.startswith("dense"):
+        y, stats = ep_prefill.ep_layer_dense(*args, ep.combine_sum, chunks=3 if mode == "dense3" else 1)
         assert stats["rows_received"] == TP
     else:
         y, stats = ep_prefill.ep_layer_generic(*args, scatter_sum)
@@ -170,7 +170,7 @@ def _prefill_rank_main(rank, world, port, out_dir, mode):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode,port", [("sparse", 29613), ("dense", 29614)])
+@pytest.mark.parametrize("mode,port", [("sparse", 29613), ("dense", 29614), ("dense3", 29615)])
 def test_two_rank_prefill_exchange_equals_single_rank(tmp_path, mode, port):
     mp.spawn(_prefill_rank_main, args=(2, port, str(tmp_path), mode), nprocs=2, join=True)
     x, ids, w = _prefill_routing()
