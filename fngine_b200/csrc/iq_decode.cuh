@@ -298,76 +298,43 @@ __device__ __forceinline__ uint32_t logit_key(float x) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-// Lane-local best of 16 keys as a 4-level tree: a higher slot wins only when strictly greater, so
-// equal keys resolve to the lower slot (= the lower expert id inside a lane).
-__device__ __forceinline__ void lane_best16(const uint32_t (&key)[16], uint32_t& bk, int& bi) {
-  uint32_t tk[16];
-  int ti[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    tk[i] = key[i];
-    ti[i] = i;
-  }
-#pragma unroll
-  for (int w = 1; w < 16; w <<= 1) {
-#pragma unroll
-    for (int i = 0; i < 16; i += 2 * w) {
-      const bool up = tk[i + w] > tk[i];
-      tk[i] = up ? tk[i + w] : tk[i];
-      ti[i] = up ? ti[i + w] : ti[i];
-    }
-  }
-  bk = tk[0];
-  bi = ti[0];
-}
-
-// Top-10 of 512 logits by one warp, value descending, ties to the lower id, softmax over the ten.
-// Lane l holds experts l, l+32, ...; each lane keeps its best and second-best remaining key, so a
-// round is two redux operations; the 16-key trees are rebuilt (by the whole warp, the branch is
-// uniform) only when a lane that has already promoted its second best wins again - once or twice per
-// token on average instead of every round.
 template <class LoadF>
 __device__ __forceinline__ void warp_topk10(LoadF load_logit, int* ids, float* weights) {
   const int lane = threadIdx.x & 31;
   uint32_t key[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) key[i] = logit_key(load_logit(lane + 32 * i));
-  uint32_t b1k, b2k;
-  int b1i, b2i;
-  bool have2;
-  auto refill = [&]() {  // best and second best of the keys that are left (retired keys are 0)
-    lane_best16(key, b1k, b1i);
-    uint32_t k2[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) k2[i] = i == b1i ? 0u : key[i];
-    lane_best16(k2, b2k, b2i);
-    have2 = true;
-  };
-  refill();
   float vals[FB_TOPK];
 #pragma unroll
   for (int k = 0; k < FB_TOPK; ++k) {
-    const uint32_t best = __reduce_max_sync(0xffffffffu, b1k);
-    const uint32_t cand = b1k == best ? uint32_t(lane + 32 * b1i) : 0xffffffffu;
+    // lane-local best as a 4-level tree: a higher slot wins only when strictly greater, so equal
+    // keys resolve to the lower id; the warp step is two redux operations (max key, then min id).
+    uint32_t tk[16];
+    int ti[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      tk[i] = key[i];
+      ti[i] = i;
+    }
+#pragma unroll
+    for (int w = 1; w < 16; w <<= 1) {
+#pragma unroll
+      for (int i = 0; i < 16; i += 2 * w) {
+        const bool up = tk[i + w] > tk[i];
+        tk[i] = up ? tk[i + w] : tk[i];
+        ti[i] = up ? ti[i + w] : ti[i];
+      }
+    }
+    const uint32_t best = __reduce_max_sync(0xffffffffu, tk[0]);
+    const uint32_t cand = tk[0] == best ? uint32_t(lane + 32 * ti[0]) : 0xffffffffu;
     const int win = int(__reduce_min_sync(0xffffffffu, cand));
     ids[k] = win;
     const uint32_t u = (best & 0x80000000u) ? (best & 0x7fffffffu) : ~best;
     vals[k] = __uint_as_float(u);
     // retire the winner: key 0 is below every real key (the smallest real key is ~0xFF800000 = 0x007FFFFF)
-    bool starved = false;
-    if (uint32_t(win) == cand) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i)
-        if (i == b1i) key[i] = 0u;
-      if (have2) {
-        b1k = b2k;
-        b1i = b2i;
-        have2 = false;
-      } else {
-        starved = true;
-      }
-    }
-    if (k + 1 < FB_TOPK && __any_sync(0xffffffffu, starved)) refill();
+    for (int i = 0; i < 16; ++i)
+      if (win == lane + 32 * i) key[i] = 0u;
   }
   float sum = 0.0f;
   const float top = vals[0];
