@@ -264,6 +264,38 @@ def fp8_gemm_section(torch, iters=10):
     return res
 
 
+def prefill_cpu_baseline(seed, x_bits, ids, budget_s=8.0):
+    """The reference's CPU prefill path (decode_rows_bf16 + gemm_bf16 per expert, h rounded to bf16) on a
+    bounded sample: the first tokens of layer 0 with their real routing, experts spread over the host cores.
+    Returns (expert-token pairs per second, pairs done, threads, kind)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from fngine_b200 import synth
+    from oracle import oracle as O
+    lib = O.ref()
+    kind = "reference" if lib is not None else "port"
+    threads = os.cpu_count() or 1
+    by_expert = {}
+    for t in range(ids.shape[0]):
+        for e in ids[t].tolist():
+            by_expert.setdefault(int(e), []).append(t)
+    tables = {FMT: synth.d_table(FMT)}
+    jobs = [(synth.expert_blob(FMT, FMT, INTER, seed, e, tables=tables), np.ascontiguousarray(x_bits[toks]))
+            for e, toks in sorted(by_expert.items())]
+
+    def one(job):
+        O.expert_ffn_bf16(FMT, FMT, HIDDEN, INTER, job[0], job[1], lib=lib)
+        return job[1].shape[0]
+
+    t0 = time.perf_counter()
+    done = 0
+    with ThreadPoolExecutor(max_workers=threads) as pool:  # ctypes releases the GIL inside the C call
+        for lo in range(0, len(jobs), 4 * threads):
+            done += sum(pool.map(one, jobs[lo:lo + 4 * threads]))
+            if time.perf_counter() - t0 > budget_s:
+                break
+    return done / (time.perf_counter() - t0), done, threads, kind
+
+
 def prefill_section(torch, n_layers=48, tokens=8192, steps=2):
     """The 48-layer routed-expert stack at prefill on one GPU: 8192 bf16 tokens, 512 IQ3_S experts per
     layer (inter 512), top-10, router logits = bf16 projection (std 0.02) + a Zipf(1.1) popularity bias
@@ -325,6 +357,17 @@ def prefill_section(torch, n_layers=48, tokens=8192, steps=2):
            "busiest_expert_pairs_last_layer": int(counts.max()), "median_expert_pairs_last_layer": int(np.median(counts)),
            "device_status": ws.status(), "finite_output": bool(torch.isfinite(out.float()).all().item()),
            "timed_region_includes": "torch router projection + unit-RMS rescale between layers"}
+    try:  # the CPU path beside it, on a bounded sample (reported, not a target)
+        n_cpu = 256
+        ids_cpu = ws.ints(ws.ws.topk_expert, tokens * TOPK).reshape(tokens, TOPK)[:n_cpu]
+        x_bits = x0[:n_cpu].view(torch.int16).cpu().numpy().view(np.uint16)
+        pairs_s, pairs, threads, kind = prefill_cpu_baseline(5000, x_bits, ids_cpu)
+        res["cpu_baseline"] = {"value": pairs_s / TOPK, "unit": "tokens/s per layer", "cores": threads, "kind": kind,
+                               "sample": "layer 0, first %d tokens with their routing: %d (token, expert) pairs, experts "
+                                         "spread over the cores; the GPU figure for one layer is %.0f tokens/s" % (
+                                             n_cpu, pairs, tokens * n_layers / (ms * 1e-3))}
+    except Exception as exc:  # the oracle is a checker, never a dependency of the measurement
+        res["cpu_baseline"] = {"unavailable": type(exc).__name__}
     del layers
     torch.cuda.empty_cache()
     return res
