@@ -362,7 +362,7 @@ constexpr int kRouteSplits = 8, kRouteSlice = H / kRouteSplits;  // 320
 constexpr int kRouteGroups = kExperts / 32;                      // 16
 static_assert(kRouteSlice == 320, "lane layout below: two 128-element chunks and a 64-element tail");
 
-template <bool XBF16>
+template <bool XBF16, bool EP>
 __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restrict__ w, const void* __restrict__ xv,
                                                     int T, float* __restrict__ logits, int stride,
                                                     float* __restrict__ part, fb_moe_decode_workspace ws,
@@ -371,9 +371,9 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
   pdl_launch_dependents();
   pdl_wait_prior();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const bool ep_mode = ep.peers.n_ranks > 0;
+  constexpr bool ep_mode = EP;  // the single-GPU instantiation carries none of the exchange code
   const uint4* x_lines = nullptr;  // this rank's copy of all tokens' rows, as exchange lines
-  if (ep_mode) {
+  if constexpr (EP) {
     // Expert-parallel step: this rank's own rows go to every rank as flag-in-data lines (block b
     // serves rank b % R with slice b / R of the rows); readers below poll the lines they need.
     const int R = ep.peers.n_ranks, d = int(blockIdx.x) % R, slice = int(blockIdx.x) / R, n_slices = int(gridDim.x) / R;
@@ -397,7 +397,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
   for (int i = tid; i < T * (kRouteSlice / 4); i += 512) {
     const int t = i / (kRouteSlice / 4), c = i - t * (kRouteSlice / 4);
     float4 v;
-    if (ep_mode) {
+    if constexpr (ep_mode) {
       const uint4* ln = x_lines + (size_t(t) * H + q * kRouteSlice) / 2 + 2 * c;
       const float2 a = ll_read(ln, ep.step, ws.status), b2 = ll_read(ln + 1, ep.step, ws.status);
       v = make_float4(a.x, a.y, b2.x, b2.y);
@@ -485,7 +485,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
       float* scales = reinterpret_cast<float*>(out + H);
       if (act == FB_ACT_Q8_K) {
         float v[8];
-        if (ep_mode) {
+        if constexpr (ep_mode) {
           const uint4* ln = x_lines + (size_t(t) * H + 256 * b + 8 * lane) / 2;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -509,7 +509,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
       } else {
         unsigned short dh;
         float xv1;
-        if (ep_mode) {
+        if constexpr (ep_mode) {
           const float2 f = ll_read(x_lines + (size_t(t) * H + 32 * b + lane) / 2, ep.step, ws.status);
           xv1 = (lane & 1) ? f.y : f.x;
         } else {
@@ -1440,14 +1440,13 @@ static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_
     return invalid("layer_decode: workspace was made for a different layout");
   // the [8][16][512] slice sums borrow the head of ws->partial, which nothing reads before the down kernel
   const dim3 grid(kRouteGroups * kRouteSplits), block(512);
-  cudaError_t e =
-      x_dtype == FB_DT_BF16
-          ? launch_pdl(route_kernel<true>, grid, block, 0, as_stream(stream),
-                       static_cast<const __nv_bfloat16*>(router_w_bf16), x, tokens, logits_scratch, int(FB_ROUTER_ROWS),
-                       ws->partial, *ws, slot_of, remote_ok, era)
-          : launch_pdl(route_kernel<false>, grid, block, 0, as_stream(stream),
-                       static_cast<const __nv_bfloat16*>(router_w_bf16), x, tokens, logits_scratch, int(FB_ROUTER_ROWS),
-                       ws->partial, *ws, slot_of, remote_ok, era);
+  auto launch = [&](auto kernel) {
+    return launch_pdl(kernel, grid, block, 0, as_stream(stream), static_cast<const __nv_bfloat16*>(router_w_bf16), x,
+                      tokens, logits_scratch, int(FB_ROUTER_ROWS), ws->partial, *ws, slot_of, remote_ok, era);
+  };
+  cudaError_t e = ep                       ? launch(route_kernel<false, true>)
+                  : x_dtype == FB_DT_BF16 ? launch(route_kernel<true, false>)
+                                          : launch(route_kernel<false, false>);
   if (e != cudaSuccess) return check_launch("layer_decode: route");
   int32_t st = fb_moe_hot_gate_up(layout, tokens, ws, stream);
   if (st) return st;
