@@ -298,6 +298,79 @@ __device__ __forceinline__ uint32_t logit_key(float x) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// weights = softmax over the ten winners (fp32, expf(v - top), summed in rank order).
+__device__ __forceinline__ void topk_softmax(float (&vals)[FB_TOPK], float* weights) {
+  float sum = 0.0f;
+  const float top = vals[0];
+#pragma unroll
+  for (int k = 0; k < FB_TOPK; ++k) {
+    vals[k] = expf(vals[k] - top);
+    sum += vals[k];
+  }
+  const float inv = __fdiv_rn(1.0f, sum);
+#pragma unroll
+  for (int k = 0; k < FB_TOPK; ++k) weights[k] = vals[k] * inv;
+}
+__device__ __forceinline__ float key_logit(uint32_t key) {
+  return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
+// Two-level top-10. Level one: a warp holds 32 consecutive experts' logits of one token, one per
+// lane, and emits their ten best as (key, id) candidates, best first (lane k < 10 returns the k-th).
+// The global top-10 is a subset of the union of such candidate lists, and the tie rule (lower id)
+// holds inside a list because ids grow with the lane.
+__device__ __forceinline__ void warp_top10_of32(float logit, int id, uint32_t& out_key, int& out_id) {
+  const int lane = threadIdx.x & 31;
+  uint32_t key = logit_key(logit);
+  out_key = 0u;
+  out_id = 0;
+#pragma unroll
+  for (int k = 0; k < FB_TOPK; ++k) {
+    const uint32_t best = __reduce_max_sync(0xffffffffu, key);
+    const int win = int(__reduce_min_sync(0xffffffffu, key == best ? uint32_t(lane) : 0xffffffffu));
+    const int wid = __shfl_sync(0xffffffffu, id, win);
+    if (lane == k) {
+      out_key = best;
+      out_id = wid;
+    }
+    if (lane == win) key = 0u;  // retired: below every real key
+  }
+}
+// Level two: one warp merges n_cand (<= 160) candidates of a token; load(c, key, id) reads candidate c.
+template <class LoadF>
+__device__ __forceinline__ void warp_topk10_merge(LoadF load, int n_cand, int* ids, float* weights) {
+  const int lane = threadIdx.x & 31;
+  uint32_t key[5];
+  int cid[5];
+#pragma unroll
+  for (int j = 0; j < 5; ++j) {
+    key[j] = 0u;
+    cid[j] = 0x7fffffff;
+    if (lane + 32 * j < n_cand) load(lane + 32 * j, key[j], cid[j]);
+  }
+  float vals[FB_TOPK];
+#pragma unroll
+  for (int k = 0; k < FB_TOPK; ++k) {
+    // lane-local best: larger key, then lower id
+    uint32_t bk = key[0];
+    int bi = cid[0];
+#pragma unroll
+    for (int j = 1; j < 5; ++j) {
+      const bool up = key[j] > bk || (key[j] == bk && cid[j] < bi);
+      bk = up ? key[j] : bk;
+      bi = up ? cid[j] : bi;
+    }
+    const uint32_t best = __reduce_max_sync(0xffffffffu, bk);
+    const int win = int(__reduce_min_sync(0xffffffffu, bk == best ? uint32_t(bi) : 0xffffffffu));
+    ids[k] = win;
+    vals[k] = key_logit(best);
+#pragma unroll
+    for (int j = 0; j < 5; ++j)
+      if (key[j] == best && cid[j] == win) key[j] = 0u;
+  }
+  topk_softmax(vals, weights);
+}
+
 template <class LoadF>
 __device__ __forceinline__ void warp_topk10(LoadF load_logit, int* ids, float* weights) {
   const int lane = threadIdx.x & 31;
@@ -336,16 +409,7 @@ __device__ __forceinline__ void warp_topk10(LoadF load_logit, int* ids, float* w
     for (int i = 0; i < 16; ++i)
       if (win == lane + 32 * i) key[i] = 0u;
   }
-  float sum = 0.0f;
-  const float top = vals[0];
-#pragma unroll
-  for (int k = 0; k < FB_TOPK; ++k) {
-    vals[k] = expf(vals[k] - top);
-    sum += vals[k];
-  }
-  const float inv = __fdiv_rn(1.0f, sum);
-#pragma unroll
-  for (int k = 0; k < FB_TOPK; ++k) weights[k] = vals[k] * inv;
+  topk_softmax(vals, weights);
 }
 
 

@@ -164,9 +164,9 @@ __global__ void __launch_bounds__(128) router_kernel(const __nv_bfloat16* __rest
 }
 
 // ------------------------------------------------------------------------------ select
-// load_logit(t, e) returns router logit e of token t.
-template <class LoadF>
-__device__ __forceinline__ void select_block(LoadF load_logit, const int32_t* slot_of, int T,
+// topk(t, ids, weights): the calling warp's top-10 of token t (ids and softmax weights, rank order).
+template <class TopkF>
+__device__ __forceinline__ void select_block(TopkF topk, const int32_t* slot_of, int T,
                                              const fb_moe_decode_workspace& ws, uint32_t* counts,
                                              bool remote_ok = false) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -189,7 +189,7 @@ __device__ __forceinline__ void select_block(LoadF load_logit, const int32_t* sl
   if (warp < T) {
     int ids[kTopK];
     float w[kTopK];
-    warp_topk10([&](int e) { return load_logit(warp, e); }, ids, w);
+    topk(warp, ids, w);
 #pragma unroll
     for (int k = 0; k < kTopK; ++k)
       if (lane == k) {
@@ -338,7 +338,11 @@ __global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ l
     quantize_row_planar(act_of(ws.gate_up_format), H, load, ws.xq + size_t(t) * FB_XQ_STRIDE);
     return;
   }
-  select_block([&](int t, int e) { return logits[size_t(t) * logits_stride + e]; }, slot_of, T, ws, counts);
+  select_block(
+      [&](int t, int* ids, float* wts) {
+        warp_topk10([&](int e) { return logits[size_t(t) * logits_stride + e]; }, ids, wts);
+      },
+      slot_of, T, ws, counts);
 }
 
 // What route_kernel needs for an expert-parallel step with peer-memory exchange (n_ranks == 0: none).
@@ -357,7 +361,9 @@ struct EpRouteArgs {
 // [8][16][512]. 128 blocks: one per SM, no second wave. Every block also quantizes a share of the
 // activation blocks. Hand-offs use device tickets, nobody waits: the block that finishes last in its
 // row group adds the group's eight slices in order 0..7 (fixed: repeated calls are bitwise
-// identical) and stores the logits; the row group that finishes last runs the selection.
+// identical), stores the logits and, per token, the ten best of its 32 experts; the row group that
+// finishes last merges the sixteen candidate lists of each token (the global top-10 is among them)
+// and runs the selection.
 constexpr int kRouteSplits = 8, kRouteSlice = H / kRouteSplits;  // 320
 constexpr int kRouteGroups = kExperts / 32;                      // 16
 static_assert(kRouteSlice == 320, "lane layout below: two 128-element chunks and a 64-element tail");
@@ -531,13 +537,19 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  {  // thread (token, row of the group)
-    const int t = tid >> 5, e = g * 32 + lane;
+  // Candidate lists of the two-level top-10 sit behind the slice sums: [token][row group][10] x {key, id}.
+  uint2* cands = reinterpret_cast<uint2*>(part + size_t(kRouteSplits) * kMaxTok * kExperts);
+  {  // warp = token, lane = row of the group
+    const int t = warp, e = g * 32 + lane;
     if (t < T) {
       float v = 0.0f;
 #pragma unroll
       for (int qq = 0; qq < kRouteSplits; ++qq) v += __ldcg(part + (size_t(qq) * kMaxTok + t) * kExperts + e);
       logits[size_t(t) * stride + e] = v;
+      uint32_t ck;
+      int ci;
+      warp_top10_of32(v, e, ck, ci);  // the group's ten best of this token, best first
+      if (lane < kTopK) cands[(size_t(t) * kRouteGroups + g) * kTopK + lane] = make_uint2(ck, uint32_t(ci));
     }
   }
   __threadfence();
@@ -550,15 +562,17 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  {  // thread e <-> expert e: all logits into shared memory, loads issued together
-    float v[kMaxTok];
-#pragma unroll
-    for (int t = 0; t < kMaxTok; ++t) v[t] = t < T ? __ldcg(logits + size_t(t) * stride + tid) : 0.0f;
-#pragma unroll
-    for (int t = 0; t < kMaxTok; ++t) s_buf[t * kExperts + tid] = v[t];
-  }
-  __syncthreads();
-  select_block([&](int t, int e) { return s_buf[t * kExperts + e]; }, slot_of, T, ws, nullptr, remote_ok);
+  select_block(
+      [&](int t, int* ids, float* wts) {  // merge the sixteen row groups' candidate lists of token t
+        warp_topk10_merge(
+            [&](int c, uint32_t& k, int& id) {
+              const uint2 v = __ldcg(cands + size_t(t) * kRouteGroups * kTopK + c);
+              k = v.x;
+              id = int(v.y);
+            },
+            kRouteGroups * kTopK, ids, wts);
+      },
+      slot_of, T, ws, nullptr, remote_ok);
 }
 
 // ------------------------------------------------------------------------------ streaming skeleton
