@@ -49,6 +49,9 @@ __device__ __forceinline__ float2 ll_read(const uint4* line, uint32_t step, uint
                  : "l"(line)
                  : "memory");
     if (v.y == step && v.w == step) return make_float2(__uint_as_float(v.x), __uint_as_float(v.z));
+    // once any reader of this launch has given up, the others stop waiting too (checked rarely)
+    if ((i & 1023u) == 1023u && *reinterpret_cast<volatile uint32_t*>(status) >= uint32_t(FB_STATUS_PIPELINE_TIMEOUT))
+      return make_float2(0.0f, 0.0f);
     __nanosleep(100);
   }
   atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
@@ -760,6 +763,47 @@ __device__ __forceinline__ void iq4nl_unit_dot(const uint32_t* unit, const Iq4nl
   }
 }
 
+// One IQ4_NL block (18 bytes at row + 18 b, two-byte aligned) against TT interleaved Q8_0 rows, for
+// the gate/up kernel where eight lanes share a row and lane q takes blocks q, q + 8, ...: the
+// block's parity, hence its alignment, is a lane constant (`odd`), so the five aligned words that
+// cover it are read directly and the four code words come out of one PRMT each. The eight lanes
+// read eight consecutive 32-byte activation blocks; lanes 4-7 (`swap`) take the two 16-byte halves in
+// the other order, which puts the eight 128-bit loads of an instruction in eight different bank
+// groups. Integer sums do not depend on that order.
+template <int TT>
+__device__ __forceinline__ void iq4nl_block_dot(const uint8_t* row, int b, bool odd, bool swap, const Iq4nlLevels& L,
+                                                const uint8_t* const (&actrow)[TT], int act_k, float (&acc)[TT]) {
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(row + 18 * b - (odd ? 2 : 0));
+  const uint32_t u0 = u[0], u1 = u[1], u2 = u[2], u3 = u[3], u4 = u[4];
+  const uint32_t sel = odd ? 0x7654u : 0x5432u;
+  const uint32_t q[4] = {__byte_perm(u0, u1, sel), __byte_perm(u1, u2, sel), __byte_perm(u2, u3, sel),
+                         __byte_perm(u3, u4, sel)};
+  const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(odd ? (u0 >> 16) : (u0 & 0xFFFFu))));
+  int w[8];
+  iq4nl_decode32(L, q, w);
+  int wa[4], wb[4];  // weights of the half read first / second
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    wa[i] = swap ? w[4 + i] : w[i];
+    wb[i] = swap ? w[i] : w[4 + i];
+  }
+  const int off_a = 32 * b + (swap ? 16 : 0), off_b = 32 * b + (swap ? 0 : 16);
+#pragma unroll
+  for (int t = 0; t < TT; ++t) {
+    const int4 a = *reinterpret_cast<const int4*>(actrow[t] + off_a);
+    const int4 c = *reinterpret_cast<const int4*>(actrow[t] + off_b);
+    int sum = __dp4a(wa[0], a.x, 0);
+    sum = __dp4a(wa[1], a.y, sum);
+    sum = __dp4a(wa[2], a.z, sum);
+    sum = __dp4a(wa[3], a.w, sum);
+    sum = __dp4a(wb[0], c.x, sum);
+    sum = __dp4a(wb[1], c.y, sum);
+    sum = __dp4a(wb[2], c.z, sum);
+    sum = __dp4a(wb[3], c.w, sum);
+    acc[t] = fmaf(float(sum), d * reinterpret_cast<const float*>(actrow[t] + act_k)[b], acc[t]);
+  }
+}
+
 // h of one finished work item -> planar activation rows for the down projection (one warp).
 __device__ __forceinline__ void quantize_item_h(const fb_moe_decode_workspace& ws, int pair_begin, int n_tok,
                                                 int down_act) {
@@ -963,22 +1007,17 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
       const int q = lane & 7, r = (lane >> 3) & 1, mat = lane >> 4;
       const uint8_t* row = st + mat * kUp + (2 * warp + r) * C::kRowBytes;
       float acc[kTT] = {0.0f, 0.0f};
+      const bool odd = (q & 1) != 0, swap = (q & 4) != 0;
       if (ntp == 1) {
         const uint8_t* ar[1] = {actbase};
         float a1[1] = {0.0f};
-#pragma unroll
-        for (int it = 0; it < 5; ++it) {
-          const int u = q + 8 * it;
-          iq4nl_unit_dot<1>(reinterpret_cast<const uint32_t*>(row + 36 * u), lv, ar, 2 * u, H, a1);
-        }
+#pragma unroll 2
+        for (int it = 0; it < 10; ++it) iq4nl_block_dot<1>(row, q + 8 * it, odd, swap, lv, ar, H, a1);
         acc[0] = a1[0];
       } else {
         const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
-#pragma unroll
-        for (int it = 0; it < 5; ++it) {
-          const int u = q + 8 * it;
-          iq4nl_unit_dot<2>(reinterpret_cast<const uint32_t*>(row + 36 * u), lv, ar, 2 * u, H, acc);
-        }
+#pragma unroll 2
+        for (int it = 0; it < 10; ++it) iq4nl_block_dot<2>(row, q + 8 * it, odd, swap, lv, ar, H, acc);
       }
 #pragma unroll
       for (int t = 0; t < kTT; ++t) {
