@@ -692,11 +692,12 @@ struct GateUp<FB_FMT_IQ3_S> {
   static constexpr int kPartialFloats = 2 * kTasks * kTT * 32;
   static constexpr int kUpPad = 0;
 };
-// IQ4_NL: 32 intermediate rows of 1440 bytes per matrix. Sixteen consumer warps; warp w handles
-// rows 2w, 2w+1 of gate and of up, eight lanes per row, lane q taking the 36-byte units q + 8i.
+// IQ4_NL: 32 intermediate rows of 1440 bytes per matrix, cut into sixteen tasks drawn from the same
+// ticket as the IQ3_S tasks: task k is rows 2k, 2k+1 of gate and of up, eight lanes per row, lane q
+// taking the 18-byte blocks q, q + 8, ... (SwiGLU needs no cross-task reduction).
 template <>
 struct GateUp<FB_FMT_IQ4_NL> {
-  static constexpr int kJ = 32, kRowBytes = 1440, kWarps = 16, kTasks = 0;
+  static constexpr int kJ = 32, kRowBytes = 1440, kWarps = 16, kTasks = 16;
   static constexpr int kAct = FB_ACT_Q8_0, kActBytes = H + H / 8;
   static constexpr bool kGrid = false;
   static constexpr int kPartialFloats = 0;
@@ -901,7 +902,7 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (C::kGrid) iq3s_tables_fill(gridrep, signtab);
   if (tid == 0) {
-    ring_init(ring, FMT == FB_FMT_IQ3_S ? 1 : kW);
+    ring_init(ring, 1);  // one arrival frees a slot: the warp that finishes the entry's last task
     s_misc[1] = 0;
     s_misc[2] = 0;
     s_misc[3] = 0;
@@ -991,21 +992,16 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
     }
   } else {
     const Iq4nlLevels lv = iq4nl_levels();
-    for (int i = 0;; ++i) {
-      const int s = i & 1;
-      if (ring_aborted(ring)) break;
-      if (!mbar_wait(&ring.full[s], (i >> 1) & 1)) {
-        ring_timeout(ring, ws.status);
-        break;
-      }
-      if (ring.meta[s].tile < 0) break;
+    while (true) {
+      int s, task;
+      if (!draw_task<C::kTasks>(ring, &s_misc[1], ws.status, lane, s, task)) break;
       const int ntp = ring.meta[s].ntp, pair0 = ring.meta[s].pair0, j0 = ring.meta[s].row0;
       const int item = ring.meta[s].item, ipb = ring.meta[s].item_pair0, itok = ring.meta[s].item_tok;
       uint8_t* st = stage0 + s * kStage;
       const uint8_t* actbase = st + kStageW;
-      // lanes 0-7 gate row 2w, 8-15 gate 2w+1, 16-23 up 2w, 24-31 up 2w+1
+      // lanes 0-7 gate row 2k, 8-15 gate 2k+1, 16-23 up 2k, 24-31 up 2k+1
       const int q = lane & 7, r = (lane >> 3) & 1, mat = lane >> 4;
-      const uint8_t* row = st + mat * kUp + (2 * warp + r) * C::kRowBytes;
+      const uint8_t* row = st + mat * kUp + (2 * task + r) * C::kRowBytes;
       float acc[kTT] = {0.0f, 0.0f};
       const bool odd = (q & 1) != 0, swap = (q & 4) != 0;
       if (ntp == 1) {
@@ -1026,11 +1022,18 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
         v += __shfl_xor_sync(0xffffffffu, v, 2);
         v += __shfl_xor_sync(0xffffffffu, v, 4);
         const float up = __shfl_down_sync(0xffffffffu, v, 16);
-        if (t < ntp && q == 0 && mat == 0) ws.h[size_t(pair0 + t) * I + j0 + 2 * warp + r] = silu_mul(v, up);
+        if (t < ntp && q == 0 && mat == 0) ws.h[size_t(pair0 + t) * I + j0 + 2 * task + r] = silu_mul(v, up);
       }
+      // the warp that finishes the entry's last task hands the slot back to the producer
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ring.empty[s]);
-      item_contribution_done(ws, item, ipb, itok, tpi * kW * ((itok + kTT - 1) / kTT), down_act, lane);
+      int done = 0;
+      if (lane == 0) done = atomicAdd(&s_misc[2 + s], 1);
+      done = __shfl_sync(0xffffffffu, done, 0);
+      if (done == C::kTasks - 1 && lane == 0) {
+        s_misc[2 + s] = 0;
+        mbar_arrive(&ring.empty[s]);
+      }
+      item_contribution_done(ws, item, ipb, itok, tpi * C::kTasks * ((itok + kTT - 1) / kTT), down_act, lane);
     }
   }
 }
