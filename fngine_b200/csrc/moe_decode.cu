@@ -1052,7 +1052,7 @@ struct Down<FB_FMT_IQ3_S, 512> {
 // IQ4_NL, inter 512: a row is eight 36-byte units, eight lanes per row, four rows per warp step.
 template <>
 struct Down<FB_FMT_IQ4_NL, 512> {
-  static constexpr int kRows = 320, kRowBytes = 288, kWarps = 16, kTasks = 0, kAct = FB_ACT_Q8_0,
+  static constexpr int kRows = 320, kRowBytes = 288, kWarps = 16, kTasks = 16, kAct = FB_ACT_Q8_0,
                        kActBytes = 512 + 64;
   static constexpr bool kGrid = false;
   static constexpr int kLanesPerRow = 8, kUnitsPerLane = 1, kUnitA = 1, kUnitB = 0;
@@ -1060,7 +1060,7 @@ struct Down<FB_FMT_IQ4_NL, 512> {
 // IQ4_NL, inter 640: a row is ten units, two lanes per row with five consecutive units each.
 template <>
 struct Down<FB_FMT_IQ4_NL, 640> {
-  static constexpr int kRows = 256, kRowBytes = 360, kWarps = 16, kTasks = 0, kAct = FB_ACT_Q8_0,
+  static constexpr int kRows = 256, kRowBytes = 360, kWarps = 16, kTasks = 16, kAct = FB_ACT_Q8_0,
                        kActBytes = 640 + 80;
   static constexpr bool kGrid = false;
   static constexpr int kLanesPerRow = 2, kUnitsPerLane = 5, kUnitA = 5, kUnitB = 1;
@@ -1088,7 +1088,7 @@ down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (C::kGrid) iq3s_tables_fill(gridrep, signtab);
   if (tid == 0) {
-    ring_init(ring, FMT == FB_FMT_IQ3_S ? 1 : kW);
+    ring_init(ring, 1);  // one arrival frees a slot: the warp that finishes the entry's last task
     s_misc[1] = 0;
     s_misc[2] = 0;
     s_misc[3] = 0;
@@ -1152,25 +1152,34 @@ down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
     }
   } else {
     const Iq4nlLevels lv = iq4nl_levels();
-    for (int i = 0;; ++i) {
-      const int s = i & 1;
-      if (ring_aborted(ring)) break;
-      if (!mbar_wait(&ring.full[s], (i >> 1) & 1)) {
-        ring_timeout(ring, ws.status);
-        break;
-      }
-      if (ring.meta[s].tile < 0) break;
+    while (true) {  // sixteen tasks per tile, drawn from the ticket: task k takes row steps k, k + 16, ...
+      int s, task;
+      if (!draw_task<C::kTasks>(ring, &s_misc[1], ws.status, lane, s, task)) break;
       const int ntp = ring.meta[s].ntp, pair0 = ring.meta[s].pair0, r0 = ring.meta[s].row0;
       const float wgt[kTT] = {ring.meta[s].wgt[0], ring.meta[s].wgt[1]};
       uint8_t* st = stage0 + s * kStage;
       const uint8_t* actbase = st + kStageW;
       constexpr int LPR = C::kLanesPerRow, RPS = 32 / LPR;
       const int q = lane % LPR, r = lane / LPR;
-      for (int step = warp; step < C::kRows / RPS; step += kW) {
+      for (int step = task; step < C::kRows / RPS; step += C::kTasks) {
         const int row = step * RPS + r;
         const uint8_t* rowp = st + row * C::kRowBytes;
         float acc[kTT] = {0.0f, 0.0f};
-        if (ntp == 1) {
+        if constexpr (INTER == 512) {
+          // eight lanes per row, lane q takes blocks q and q + 8 (conflict-free weight and activation reads)
+          const bool odd = (q & 1) != 0, swap = (q & 4) != 0;
+          if (ntp == 1) {
+            const uint8_t* ar[1] = {actbase};
+            float a1[1] = {0.0f};
+            iq4nl_block_dot<1>(rowp, q, odd, swap, lv, ar, INTER, a1);
+            iq4nl_block_dot<1>(rowp, q + 8, odd, swap, lv, ar, INTER, a1);
+            acc[0] = a1[0];
+          } else {
+            const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
+            iq4nl_block_dot<2>(rowp, q, odd, swap, lv, ar, INTER, acc);
+            iq4nl_block_dot<2>(rowp, q + 8, odd, swap, lv, ar, INTER, acc);
+          }
+        } else if (ntp == 1) {
           const uint8_t* ar[1] = {actbase};
           float a1[1] = {0.0f};
 #pragma unroll
@@ -1196,7 +1205,13 @@ down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ring.empty[s]);
+      int done = 0;
+      if (lane == 0) done = atomicAdd(&s_misc[2 + s], 1);
+      done = __shfl_sync(0xffffffffu, done, 0);
+      if (done == C::kTasks - 1 && lane == 0) {
+        s_misc[2 + s] = 0;
+        mbar_arrive(&ring.empty[s]);
+      }
     }
   }
 }
