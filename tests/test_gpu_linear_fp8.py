@@ -47,7 +47,8 @@ def reference_gemm(torch, xq_codes, xq_scales, w_codes, w_scales):
 
 
 @pytest.mark.parametrize("T,N,K,bf16_scales", [(1, 256, 128, False), (3, 512, 256, False), (64, 320, 640, True),
-                                               (128, 1280, 2560, False), (300, 2560, 384, True)])
+                                               (128, 1280, 2560, False), (300, 2560, 384, True),
+                                               (512, 320, 256, False), (257, 192, 128, True)])
 def test_linear_fp8_small_shapes(T, N, K, bf16_scales):
     torch = _torch()
     from fngine_b200 import linear
