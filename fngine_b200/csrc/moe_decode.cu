@@ -1,6 +1,7 @@
 // Decode-width (T <= 16) routed-expert kernels on native GGUF expert bytes.
 //
-//   select   router top-10, sorted work list, once-per-token activation quantization
+//   route    router projection, once-per-token activation quantization, top-10, sorted work list
+//            (select = the same selection from given logits)
 //   gate_up  h[pair][j] = silu(gate_j . x) * (up_j . x)
 //   down     partial[pair][n] = w_pair * (down_n . q8(h[pair]))
 //   combine  y[t] = sum of token t's partials in slot order (+ shared, + residual write)
@@ -26,8 +27,8 @@ constexpr int kExperts = FB_EXPERTS;
 constexpr int kMaxTok = FB_DECODE_MAX_TOKENS;
 constexpr int kMaxPairs = FB_DECODE_MAX_PAIRS;
 constexpr int kTT = 2;  // tokens of one work item handled per pass over a staged tile
-// ws.sched: [0] gate/up tile counter, [1] down tile counter, [2] finished route blocks,
-// [8..168) item order
+// ws.sched: [0] gate/up tile counter, [1] down tile counter, [2] finished route row groups,
+// [8..168) item order, [192..208) finished slices per route row group
 constexpr int kSchedOrderBase = 8;
 constexpr int kEpMaxRanks = FB_EP_MAX_RANKS;
 constexpr uint32_t kPeerSpinLimit = 1u << 20;  // polls of a peer-written flag before giving up (about a second)

@@ -12,8 +12,14 @@ CPU tier (src/kernels/moe/moe.h:119-121 of the reference). Here "elsewhere" is a
   * combine   = all-to-all of the partial y rows back to the owning rank, which adds the R partial
                 rows of each token in rank order (deterministic).
 
+Two exchanges are implemented on GPUs. ep_layer_step runs the collectives through NCCL
+(all_to_all_single for dispatch and combine, fb_ep_sum_ranks for the owner's rank-order sum).
+layer_decode_ep_p2p (PeerExchange + fb_moe_layer_decode_ep_p2p) does the same exchange inside the
+layer's own kernels: ranks store flag-in-data lines into each other's CUDA-IPC-mapped buffers over
+NVLink and poll their own memory, so a step makes no collective call; both give the same bits.
+
 The split / ordering logic in this file is backend-agnostic and is exercised on CPU ranks (gloo) by
-tests/test_ep_gloo.py; on GPUs the collectives run over NCCL (NVLink / NVSwitch).
+tests/test_ep_gloo.py.
 """
 import json
 import os
