@@ -264,6 +264,81 @@ def fp8_gemm_section(torch, iters=10):
     return res
 
 
+def fp8_decode_section(torch, iters=10):
+    """Decode-width FP8-row projections (T <= 16, exact bf16 activations): the dense shapes of one decode step
+    that the reference registers (src/kernels/linear/linear.h:8-18), each call (activation split + streaming
+    kernel) timed alone with CUDA events after an L2 flush. Bytes = weight codes + row scales."""
+    from fngine_b200 import linear
+    peak, _ = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    res = {"l2_policy": "256 MB flush write before every call",
+           "timing": "CUDA graph of %d x (flush, call) minus a graph of %d x flush, CUDA events around the replays, "
+                     "median of 5 (a call timed eagerly is bounded by its host-side launch work, about 20 us)" % (iters, iters),
+           "shapes": {}}
+
+    def graph_time(fn):
+        for _ in range(3):
+            flush.fill_(1)
+            fn()
+        torch.cuda.synchronize()
+
+        def build(with_call):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(iters):
+                    flush.fill_(1)
+                    if with_call:
+                        fn()
+            return g
+
+        def run(g):
+            ts = []
+            g.replay()
+            for _ in range(5):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b))
+            return statistics.median(ts)
+
+        return (run(build(True)) - run(build(False))) / iters
+
+    shapes = [("gdn.qkvz", 16384, 2560, "store_bf16"), ("gdn.out", 2560, 6144, "gr_write"),
+              ("moe.shared_gate_up", 1280, 2560, "swiglu"), ("moe.shared_down", 2560, 640, "shared_scale"),
+              ("lm_head", 248320, 2560, "store_f32")]
+    for name, n, k, kind in shapes:
+        mag = torch.randint(0, 0x78, (n, k), dtype=torch.uint8, device="cuda", generator=gen)
+        sign = torch.randint(0, 2, (n, k), dtype=torch.uint8, device="cuda", generator=gen) << 7
+        weight = linear.Fp8RowWeight(mag | sign, (torch.rand(n, device="cuda", generator=gen) * 1e-3 + 1e-4).to(torch.bfloat16))
+        del mag, sign
+        work = linear.linear_fp8_decode_workspace(weight)
+        entry = {}
+        for T in (1, 16):
+            x = torch.randn(T, k, device="cuda", generator=gen).to(torch.bfloat16)
+            if kind == "store_bf16":
+                epi = linear.store_bf16(torch.empty(T, n, dtype=torch.bfloat16, device="cuda"))
+            elif kind == "store_f32":
+                epi = linear.store_f32(torch.empty(T, n, dtype=torch.float32, device="cuda"))
+            elif kind == "swiglu":
+                epi = linear.swiglu(torch.empty(T, n // 2, dtype=torch.bfloat16, device="cuda"))
+            elif kind == "shared_scale":
+                logit = torch.randn(T, 513, device="cuda", generator=gen)
+                epi = linear.shared_scale(torch.empty(T, n, dtype=torch.float32, device="cuda"), logit[:, 512:], 513)
+            else:
+                inj = torch.randn(T, 4, device="cuda", generator=gen)
+                epi = linear.gr_write(torch.zeros(T, 4, n, device="cuda"), inj)
+            med = graph_time(lambda: linear.linear_fp8_decode(x, weight, epi, work))
+            gbs = (n * k + 2 * n) / (med * 1e-3) / 1e9
+            entry["T%d" % T] = {"us": med * 1e3, "gbs": gbs, "frac_of_hbm_peak": gbs / peak}
+        res["shapes"]["%s %dx%d %s" % (name, n, k, kind)] = entry
+        del weight, work
+        torch.cuda.empty_cache()
+    return res
+
+
 def prefill_cpu_baseline(seed, x_bits, ids, budget_s=8.0):
     """The reference's CPU prefill path (decode_rows_bf16 + gemm_bf16 per expert, h rounded to bf16) on a
     bounded sample: the first tokens of layer 0 with their real routing, experts spread over the host cores.
@@ -467,7 +542,7 @@ def run_ours(args, rank, world, local_rank):
     status = ws.status()
 
     # other batch sizes of the same layer definition, CUDA-graph replayed (launch-bound otherwise)
-    sections = set("batches,cpu,iq4nl,fp8,prefill".split(",")) if args.sections == "all" else \
+    sections = set("batches,cpu,iq4nl,fp8,fp8dec,prefill".split(",")) if args.sections == "all" else \
         set(x for x in args.sections.split(",") if x and x != "none")
 
     def want(name):
@@ -525,6 +600,7 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.empty_cache()
     iq4 = iq4nl_section(torch, args.steps) if want("iq4nl") else None
     fp8 = fp8_gemm_section(torch) if want("fp8") else None
+    fp8dec = fp8_decode_section(torch) if want("fp8dec") else None
     pre = prefill_section(torch, n_layers=args.prefill_layers) if want("prefill") else None
     peak, peak_src = peaks()
     gu_ach = sum(gu_bytes) / (sum(gu_ms) * 1e-3) / 1e9
@@ -558,6 +634,7 @@ def run_ours(args, rank, world, local_rank):
         "other_batches": other,
         "iq4nl_decode": iq4,
         "fp8_row_gemm": fp8,
+        "fp8_row_decode": fp8dec,
         "prefill_stack": pre,
         "parity_vs_cpu_max_rel_l2": parity,
         "device_status": status,
@@ -578,7 +655,7 @@ def main():
                     help="layers of the prefill stack section (a profiler run wants 1)")
     ap.add_argument("--sections", default="all",
                     help="extra sections beside the headline decode measurement: all | none | comma list of "
-                         "batches,cpu,iq4nl,fp8,prefill (a profiler run wants none)")
+                         "batches,cpu,iq4nl,fp8,fp8dec,prefill (a profiler run wants none)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -514,6 +514,396 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   }
 }
 
+// ------------------------------------------------------------------------------ decode-width projection
+// T <= 16 tokens with the activations kept exactly (the reference's "A16" numerics: exact E4M3
+// weights x the represented bf16 activation, fp32 accumulation, one multiplication by the row
+// scale; src/kernels/linear/linear.h:27-31, fp8/fp8_gemv.cuh:8-12). The operation is a stream over
+// the weight codes, so nothing may stand between HBM and the tensor core: the codes go from the
+// TMA box straight into tcgen05.mma as the E4M3 A operand, with no widening pass. The bf16
+// activations become the B operand without loss by writing each one as a sum of three E5M2
+// numbers: after a per-token power-of-two scale that puts the row maximum in [2^14, 2^15), round to
+// nearest E5M2 (three significant bits), subtract, and repeat twice; the second remainder has one
+// significant bit and the third piece is exact (values below 2^-16 of the scaled range, 2^-30 of the
+// row maximum, are dropped). The three pieces of the sixteen token slots are 48 B-operand rows, so
+// one MMA of N = 48 per 32 bytes of K produces three partial columns per token, which the epilogue
+// adds (smallest first) before the token and row scales.
+//
+// Work is cut stream-K fashion: the (row tile, K block) sequence is divided evenly over the
+// resident CTAs, so every shape - 1940 row tiles of the vocabulary projection or 10 of the
+// shared expert - keeps all SMs streaming. A CTA whose range covers a whole row tile finishes it
+// from tensor memory; partial ranges leave fp32 partial sums in the workspace and the last CTA to
+// arrive at a tile (a ticket) adds them in CTA order, which is fixed for a shape: results are
+// deterministic.
+constexpr int kDecTok = 16;                              // token slots per piece
+constexpr int kDecN = 3 * kDecTok;                       // B-operand rows
+constexpr int kDecStages = 8;
+constexpr int kDecStageA = 128 * BK;                     // 16 KB of weight codes
+constexpr int kDecStageB = kDecN * BK;                   // 6 KB of activation pieces
+constexpr int kDecStage = kDecStageA + kDecStageB;       // 22 KB, a multiple of the 1024-byte swizzle atom
+constexpr int kDecXchFloats = 128 * 17;
+constexpr int kDecSmem = kDecStages * kDecStage + kDecXchFloats * 4 + 256 + 1024;
+constexpr uint32_t kDecTmemCols = 128;                   // two accumulators of 64 columns (48 used)
+constexpr int kDecPartialFloats = 128 * kDecTok;         // one partial tile
+// D fp32, A = E4M3 (format 0), B = E5M2 (format 1), both K-major, N = 48, M = 128.
+constexpr uint32_t kIdescDec = (1u << 4) | (0u << 7) | (1u << 10) | (uint32_t(kDecN >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+static_assert(kDecStage % 1024 == 0 && kDecStageA % 1024 == 0, "operand tiles start on swizzle atoms");
+
+struct DecArgs {
+  const float* tok_scale;   // [16] power-of-two scale of each token's pieces
+  const void* w_scale;      // [n] fp32 or bf16
+  int scale_bf16;
+  int kind;                 // FB_EPI_*
+  void* out;
+  const float* inj;         // GrWrite: [T][4]
+  const float* gate_logit;  // SharedScale: logit of token t at gate_logit[t * gate_stride]
+  int gate_stride;
+  int T, n, k;
+  float* partial;           // [2 * grid][16][128] fp32
+  int32_t* tickets;         // [row tiles], zero at kernel start
+  uint32_t* status;
+};
+
+struct DecBars {
+  uint64_t full[kDecStages];
+  uint64_t empty[kDecStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort;
+  int last;
+};
+static_assert(sizeof(DecBars) <= 256, "barrier block");
+
+__device__ __forceinline__ bool dec_wait(DecBars* b, uint64_t* bar, uint32_t parity, uint32_t* status) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 31u) == 31u && *reinterpret_cast<volatile int*>(&b->abort)) return false;
+  }
+  *reinterpret_cast<volatile int*>(&b->abort) = 1;
+  atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+  return false;
+}
+// All `threads` threads of named barrier `id` learn whether every one of them passed `ok`.
+__device__ __forceinline__ bool named_bar_all(int id, int threads, bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %3, 0;\n\t"
+      "barrier.cta.red.and.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(threads), "r"(uint32_t(ok))
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ float e5m2_to_float(uint32_t code) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(code << 8)));  // E5M2 = the top byte of binary16
+}
+__device__ __forceinline__ uint32_t float_to_e5m2(float v) {
+  return uint32_t(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E5M2));  // round to nearest even
+}
+
+// One block per token slot. pieces[(p * 16 + t) * K + j], p = 0..2; slots >= T are zero rows. Block 0
+// also clears the tickets and the status word of the projection that follows.
+__global__ void __launch_bounds__(256) fp8_split_tokens_kernel(const __nv_bfloat16* __restrict__ x, int T, int K,
+                                                               uint8_t* __restrict__ pieces,
+                                                               float* __restrict__ tok_scale,
+                                                               int32_t* __restrict__ tickets, int n_tickets,
+                                                               uint32_t* __restrict__ status) {
+  pdl_launch_dependents();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  if (t == 0) {
+    for (int i = tid; i < n_tickets; i += 256) tickets[i] = 0;
+    if (tid == 0) *status = 0;
+  }
+  uint8_t* piece[3] = {pieces + size_t(t) * K, pieces + size_t(kDecTok + t) * K, pieces + size_t(2 * kDecTok + t) * K};
+  if (t >= T) {
+    for (int i = tid; i < K / 8; i += 256)
+#pragma unroll
+      for (int p = 0; p < 3; ++p) reinterpret_cast<uint2*>(piece[p])[i] = make_uint2(0u, 0u);
+    if (tid == 0) tok_scale[t] = 0.0f;
+    return;
+  }
+  const uint4* row = reinterpret_cast<const uint4*>(x + size_t(t) * K);
+  float m = 0.0f;
+  for (int i = tid; i < K / 8; i += 256) {
+    const uint4 v = row[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      m = fmaxf(m, fabsf(__uint_as_float(w[j] << 16)));
+      m = fmaxf(m, fabsf(__uint_as_float(w[j] & 0xFFFF0000u)));
+    }
+  }
+  __shared__ float red[8];
+#pragma unroll
+  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  if ((tid & 31) == 0) red[tid >> 5] = m;
+  __syncthreads();
+  m = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+  // scale = 2^(exponent(max) - 14): the scaled maximum lies in [2^14, 2^15), so rounding up stays finite
+  uint32_t e = (__float_as_uint(m) >> 23) & 0xFFu;
+  e = e < 15u ? 15u : (e > 253u ? 253u : e);
+  const float scale = __uint_as_float((e - 14u) << 23), inv = __uint_as_float((268u - e) << 23);
+  for (int i = tid; i < K / 8; i += 256) {
+    const uint4 v = row[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t out[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t bits = (j & 1) ? (w[j >> 1] & 0xFFFF0000u) : (w[j >> 1] << 16);
+      float r = __uint_as_float(bits) * inv;
+#pragma unroll
+      for (int p = 0; p < 3; ++p) {
+        const uint32_t c = float_to_e5m2(r);
+        r -= e5m2_to_float(c);
+        out[p][j >> 2] |= c << (8 * (j & 3));
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < 3; ++p) reinterpret_cast<uint2*>(piece[p])[i] = make_uint2(out[p][0], out[p][1]);
+  }
+  if (tid == 0) tok_scale[t] = scale;
+}
+
+// First K-block position of CTA c when `total` positions are divided over G CTAs.
+__device__ __forceinline__ long long dec_begin(int c, int G, long long total) { return (total * c) / G; }
+// The CTA whose range holds position p.
+__device__ __forceinline__ int dec_owner(long long p, int G, long long total) {
+  int c = int((p * G) / total);
+  while (c + 1 < G && dec_begin(c + 1, G, total) <= p) ++c;
+  while (c > 0 && dec_begin(c, G, total) > p) --c;
+  return c;
+}
+
+__device__ __forceinline__ float dec_row_scale(const DecArgs& a, int row) {
+  return a.scale_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.w_scale)[row])
+                      : static_cast<const float*>(a.w_scale)[row];
+}
+
+// Finishes row tile m: v[t] is the K-complete sum of tile row `rl` for token slot t, before scales.
+// Called by all 128 epilogue threads (et = 0..127; rl is the thread's tensor-memory lane).
+__device__ __forceinline__ void dec_emit(const DecArgs& a, int m, int rl, int et, const float (&v)[kDecTok],
+                                         float* xch) {
+  if (a.kind == FB_EPI_SWIGLU) {
+    // tile rows 0..63 are gate rows m*64.., rows 64..127 the matching up rows
+    const int half_n = a.n >> 1, j = m * 64 + (rl & 63);
+    const float ws = j < half_n ? dec_row_scale(a, rl < 64 ? j : half_n + j) : 0.0f;
+#pragma unroll
+    for (int t = 0; t < kDecTok; ++t) xch[rl * 17 + t] = v[t] * a.tok_scale[t] * ws;
+    named_bar_sync(2, 128);
+    const int r = et & 63, t0 = (et >> 6) * 8, jo = m * 64 + r;
+    if (jo < half_n) {
+      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.out);
+#pragma unroll
+      for (int t = t0; t < t0 + 8; ++t)
+        if (t < a.T) {
+          const float g = xch[r * 17 + t], u = xch[(r + 64) * 17 + t];
+          out[size_t(t) * half_n + jo] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+        }
+    }
+    named_bar_sync(2, 128);
+    return;
+  }
+  const int row = m * 128 + rl;
+  if (row >= a.n) return;
+  const float ws = dec_row_scale(a, row);
+  if (a.kind == FB_EPI_GR_WRITE) {
+    // X[t][s][row] += inj[t][s] * val. All loads first: interleaved with the stores they would be
+    // issued one memory round trip at a time.
+    float* xs = static_cast<float*>(a.out) + row;
+    const size_t n = size_t(a.n);
+    float x4[kDecTok][4];
+#pragma unroll
+    for (int t = 0; t < kDecTok; ++t)
+      if (t < a.T) {
+#pragma unroll
+        for (int st = 0; st < 4; ++st) x4[t][st] = __ldcg(xs + (size_t(t) * 4 + st) * n);
+      }
+#pragma unroll
+    for (int t = 0; t < kDecTok; ++t)
+      if (t < a.T) {
+        const float val = v[t] * a.tok_scale[t] * ws;
+        const float4 g = *reinterpret_cast<const float4*>(a.inj + size_t(t) * 4);
+        xs[(size_t(t) * 4 + 0) * n] = fmaf(g.x, val, x4[t][0]);
+        xs[(size_t(t) * 4 + 1) * n] = fmaf(g.y, val, x4[t][1]);
+        xs[(size_t(t) * 4 + 2) * n] = fmaf(g.z, val, x4[t][2]);
+        xs[(size_t(t) * 4 + 3) * n] = fmaf(g.w, val, x4[t][3]);
+      }
+    return;
+  }
+#pragma unroll
+  for (int t = 0; t < kDecTok; ++t) {
+    if (t >= a.T) break;
+    const float val = v[t] * a.tok_scale[t] * ws;
+    if (a.kind == FB_EPI_STORE_BF16) {
+      static_cast<__nv_bfloat16*>(a.out)[size_t(t) * a.n + row] = __float2bfloat16_rn(val);
+    } else if (a.kind == FB_EPI_STORE_F32) {
+      static_cast<float*>(a.out)[size_t(t) * a.n + row] = val;
+    } else {  // FB_EPI_SHARED_SCALE
+      const float gl = a.gate_logit[size_t(t) * a.gate_stride];
+      static_cast<float*>(a.out)[size_t(t) * a.n + row] = val / (1.0f + expf(-gl));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+fp8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_p,
+                  const __grid_constant__ DecArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  float* xch = reinterpret_cast<float*>(smem + kDecStages * kDecStage);
+  DecBars* bars = reinterpret_cast<DecBars*>(smem + kDecStages * kDecStage + kDecXchFloats * 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool swiglu = a.kind == FB_EPI_SWIGLU;
+  const int kbt = a.k / BK;
+  const int m_tiles = swiglu ? ((a.n >> 1) + 63) / 64 : (a.n + 127) / 128;
+  const int G = int(gridDim.x);
+  const long long total = (long long)m_tiles * kbt;
+  const long long begin = dec_begin(int(blockIdx.x), G, total), end = dec_begin(int(blockIdx.x) + 1, G, total);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kDecStages; ++i) {
+      mbar_init(&bars->full[i], 1);
+      mbar_init(&bars->empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->tmem_full[i], 1);
+      mbar_init(&bars->tmem_empty[i], 4);
+    }
+    bars->abort = 0;
+    bars->last = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&bars->tmem_base, kDecTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+  if (warp == 0) {
+    // ---------------- TMA producer: 128 weight rows (two 64-row boxes) + the 48 piece rows per K block
+    if (lane == 0) {
+      pdl_wait_prior();  // the pieces are written by the kernel launched just before
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long pos = begin; pos < end && ok;) {
+        const int m = int(pos / kbt), kb0 = int(pos - (long long)m * kbt);
+        const int kb1 = int(end - pos) < kbt - kb0 ? kb0 + int(end - pos) : kbt;
+        const int r0 = swiglu ? m * 64 : m * 128, r1 = swiglu ? (a.n >> 1) + m * 64 : m * 128 + 64;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % kDecStages;
+          if (!dec_wait(bars, &bars->empty[s], ((it / kDecStages) & 1) ^ 1, a.status)) { ok = false; break; }
+          uint8_t* st = ring + s * kDecStage;
+          mbar_expect_tx(&bars->full[s], kDecStage);
+          tma_load_2d(st, &map_w, kb * BK, r0, &bars->full[s]);
+          tma_load_2d(st + 64 * BK, &map_w, kb * BK, r1, &bars->full[s]);
+          tma_load_2d(st + kDecStageA, &map_p, kb * BK, 0, &bars->full[s]);
+        }
+        pos += kb1 - kb0;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, seg = 0;
+      bool ok = true;
+      for (long long pos = begin; pos < end && ok; ++seg) {
+        const int m = int(pos / kbt), kb0 = int(pos - (long long)m * kbt);
+        const int kb1 = int(end - pos) < kbt - kb0 ? kb0 + int(end - pos) : kbt;
+        const int ab = seg & 1;
+        if (!dec_wait(bars, &bars->tmem_empty[ab], ((seg >> 1) & 1) ^ 1, a.status)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + uint32_t(ab * 64);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % kDecStages;
+          if (!dec_wait(bars, &bars->full[s], (it / kDecStages) & 1, a.status)) { ok = false; break; }
+          uint8_t* st = ring + s * kDecStage;
+          const uint64_t da = umma_desc_k128(smem_u32(st)), db = umma_desc_k128(smem_u32(st + kDecStageA));
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 32; ++k4)
+            umma_f8(d_tmem, da + uint64_t(2 * k4), db + uint64_t(2 * k4), kIdescDec, (kb > kb0 || k4) ? 1u : 0u);
+          umma_commit(&bars->empty[s]);
+        }
+        if (!ok) break;
+        umma_commit(&bars->tmem_full[ab]);
+        pos += kb1 - kb0;
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 2..5: tensor-memory lane quarter = warp % 4
+    const int q = warp & 3, rl = q * 32 + lane, et = (warp - 2) * 32 + lane;
+    pdl_wait_prior();  // token scales and cleared tickets come from the kernel launched just before
+    uint32_t seg = 0;
+    for (long long pos = begin; pos < end; ++seg) {
+      const int m = int(pos / kbt), kb0 = int(pos - (long long)m * kbt);
+      const int kb1 = int(end - pos) < kbt - kb0 ? kb0 + int(end - pos) : kbt;
+      const int ab = seg & 1;
+      const bool got = dec_wait(bars, &bars->tmem_full[ab], (seg >> 1) & 1, a.status);
+      if (!named_bar_all(1, 128, got)) break;  // the four warps leave together
+      tc_fence_after();
+      uint32_t c[kDecN];
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(ab * 64);
+      tmem_ld16_nowait(taddr, c);
+      tmem_ld16_nowait(taddr + 16, c + 16);
+      tmem_ld16_nowait(taddr + 32, c + 32);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      float v[kDecTok];
+#pragma unroll
+      for (int t = 0; t < kDecTok; ++t)
+        v[t] = (__uint_as_float(c[32 + t]) + __uint_as_float(c[16 + t])) + __uint_as_float(c[t]);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tmem_empty[ab]);
+      if (kb0 == 0 && kb1 == kbt) {
+        dec_emit(a, m, rl, et, v, xch);
+      } else {
+        // a partial range: leave the sums in this CTA's slot (first segment: slot 0, a later one: 1)
+        float* mine = a.partial + size_t(2 * blockIdx.x + (pos == begin ? 0 : 1)) * kDecPartialFloats;
+#pragma unroll
+        for (int t = 0; t < kDecTok; ++t) __stcg(mine + t * 128 + rl, v[t]);
+        __threadfence();
+        named_bar_sync(1, 128);
+        const int c_first = dec_owner((long long)m * kbt, G, total);
+        const int c_last = dec_owner((long long)(m + 1) * kbt - 1, G, total);
+        if (et == 0) bars->last = atomicAdd(&a.tickets[m], 1) == c_last - c_first ? 1 : 0;
+        named_bar_sync(1, 128);
+        if (*reinterpret_cast<volatile int*>(&bars->last)) {
+          __threadfence();
+#pragma unroll
+          for (int t = 0; t < kDecTok; ++t) v[t] = 0.0f;
+          for (int cc = c_first; cc <= c_last; ++cc) {  // fixed order: results do not depend on arrival order
+            const bool first_seg = dec_begin(cc, G, total) / kbt == m;
+            const float* theirs = a.partial + size_t(2 * cc + (first_seg ? 0 : 1)) * kDecPartialFloats;
+#pragma unroll
+            for (int t = 0; t < kDecTok; ++t) v[t] += __ldcg(theirs + t * 128 + rl);
+          }
+          dec_emit(a, m, rl, et, v, xch);
+        }
+      }
+      pos += kb1 - kb0;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kDecTmemCols);
+  }
+}
+
 // ------------------------------------------------------------------------------ host
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -642,6 +1032,81 @@ int32_t fb_linear_fp8(const void* x_bf16, int32_t tokens, const uint8_t* w_codes
     fp8_gemm_kernel<false><<<grid, kThreads, kGemmSmem, as_stream(stream)>>>(
         map_a, map_b, a_scales, w_scales, static_cast<__nv_bfloat16*>(out_bf16), tokens, n, k, status);
   return check_launch("linear_fp8");
+}
+
+size_t fb_linear_fp8_decode_workspace_bytes(int32_t n, int32_t k) {
+  if (n <= 0 || k <= 0) return 0;
+  // pieces [48][k] | token scales | status | tickets (one per 64 output rows) | partial tiles (two per CTA,
+  // sized for 256 multiprocessors so that the figure does not depend on the device)
+  return align256(size_t(kDecN) * size_t(k)) + 256 + 256 + align256(size_t((n + 63) / 64) * 4) +
+         size_t(2 * 256) * kDecPartialFloats * 4;
+}
+
+int32_t fb_linear_fp8_decode(const void* x_bf16, int32_t tokens, const uint8_t* w_codes, const void* w_scales,
+                             int32_t w_scales_dtype, int32_t n, int32_t k, const fb_linear_epilogue* epilogue,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x_bf16 || !w_codes || !w_scales || !epilogue || !epilogue->out)
+    return invalid("linear_fp8_decode: null argument");
+  if (tokens <= 0 || tokens > kDecTok) return invalid("linear_fp8_decode: tokens must be 1..16");
+  if (n <= 0 || k <= 0 || k % BK || n % 8) return invalid("linear_fp8_decode: unsupported shape (n %% 8, k %% 128)");
+  const int kind = epilogue->kind;
+  if (kind < FB_EPI_STORE_BF16 || kind > FB_EPI_SHARED_SCALE) return invalid("linear_fp8_decode: unknown epilogue");
+  if (kind == FB_EPI_GR_WRITE && (!epilogue->inj || (reinterpret_cast<uintptr_t>(epilogue->inj) & 15)))
+    return invalid("linear_fp8_decode: GrWrite needs inj fp32 [tokens][4], 16-byte aligned");
+  if (kind == FB_EPI_SHARED_SCALE && !epilogue->gate_logit)
+    return invalid("linear_fp8_decode: SharedScale needs gate_logit");
+  if (kind == FB_EPI_SWIGLU && n % 16) return invalid("linear_fp8_decode: SwiGlu needs n %% 16 == 0");
+  if ((reinterpret_cast<uintptr_t>(w_codes) | reinterpret_cast<uintptr_t>(x_bf16)) & 15)
+    return invalid("linear_fp8_decode: x and weight codes must be 16-byte aligned");
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      workspace_bytes < fb_linear_fp8_decode_workspace_bytes(n, k))
+    return invalid("linear_fp8_decode: workspace missing, misaligned (256 B) or smaller than "
+                   "fb_linear_fp8_decode_workspace_bytes");
+  if (sm_count() > 256) return invalid("linear_fp8_decode: more than 256 multiprocessors");
+  uint8_t* pieces = static_cast<uint8_t*>(workspace);
+  float* tok_scale = reinterpret_cast<float*>(pieces + align256(size_t(kDecN) * size_t(k)));
+  uint32_t* status = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(tok_scale) + 256);
+  int32_t* tickets = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(status) + 256);
+  const int n_tickets = (n + 63) / 64;
+  float* partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tickets) + align256(size_t(n_tickets) * 4));
+  static bool once = [] {
+    cudaFuncSetAttribute(fp8_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
+    return true;
+  }();
+  (void)once;
+  cudaStream_t s = as_stream(stream);
+  fp8_split_tokens_kernel<<<kDecTok, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x_bf16), tokens, k, pieces,
+                                                   tok_scale, tickets, n_tickets, status);
+  int32_t st = check_launch("linear_fp8_decode: split");
+  if (st) return st;
+  CUtensorMap map_w, map_p;
+  if (!make_map_u8(&map_w, w_codes, n, k, 64) || !make_map_u8(&map_p, pieces, kDecN, k, kDecN)) {
+    set_error("linear_fp8_decode: cuTensorMapEncodeTiled failed");
+    return int32_t(cudaErrorInvalidValue);
+  }
+  DecArgs a;
+  a.tok_scale = tok_scale;
+  a.w_scale = w_scales;
+  a.scale_bf16 = w_scales_dtype == FB_DT_BF16;
+  a.kind = kind;
+  a.out = epilogue->out;
+  a.inj = epilogue->inj;
+  a.gate_logit = epilogue->gate_logit;
+  a.gate_stride = epilogue->gate_stride;
+  a.T = tokens;
+  a.n = n;
+  a.k = k;
+  a.partial = partial;
+  a.tickets = tickets;
+  a.status = status;
+  const int m_tiles = kind == FB_EPI_SWIGLU ? ((n >> 1) + 63) / 64 : (n + 127) / 128;
+  const long long total = (long long)m_tiles * (k / BK);
+  // at least two K blocks per CTA: below that the partial-sum traffic outweighs the extra parallelism
+  const long long want = total / 2 > 0 ? total / 2 : 1;
+  const int grid = want < sm_count() ? int(want) : sm_count();
+  cudaError_t e = launch_pdl(fp8_decode_kernel, dim3(grid), dim3(kThreads), size_t(kDecSmem), s, map_w, map_p, a);
+  if (e != cudaSuccess) return check_launch("linear_fp8_decode");
+  return check_launch("linear_fp8_decode");
 }
 
 }  // extern "C"

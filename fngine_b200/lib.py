@@ -59,6 +59,15 @@ _I32, _I64 = C.c_int32, C.c_int64
 EP_MAX_RANKS = 8
 
 
+class LinearEpilogue(C.Structure):
+    """fb_linear_epilogue: the output side of a decode-width projection."""
+    _fields_ = [("kind", C.c_int32), ("gate_stride", C.c_int32), ("out", C.c_void_p), ("inj", C.c_void_p),
+                ("gate_logit", C.c_void_p)]
+
+
+EPI_STORE_BF16, EPI_STORE_F32, EPI_GR_WRITE, EPI_SWIGLU, EPI_SHARED_SCALE = range(5)
+
+
 class EpPeers(C.Structure):
     """fb_ep_peers: peer-mapped exchange buffers of an expert-parallel decode step."""
     _fields_ = [("rank", C.c_int32), ("n_ranks", C.c_int32), ("x_all", C.c_void_p * EP_MAX_RANKS),
@@ -109,6 +118,8 @@ _SIGNATURES = {
     "fb_linear_fp8_workspace_bytes": (C.c_size_t, [_I32, _I32, _I32]),
     "fb_linear_fp8": (_I32, [_P, _I32, _P, _P, _I32, _I32, _I32, _P, _P, C.c_size_t, _P]),
     "fb_fp8_quantize_tokens": (_I32, [_P, _I32, _I32, _P, _P, _P]),
+    "fb_linear_fp8_decode_workspace_bytes": (C.c_size_t, [_I32, _I32]),
+    "fb_linear_fp8_decode": (_I32, [_P, _I32, _P, _P, _I32, _I32, _I32, C.POINTER(LinearEpilogue), _P, C.c_size_t, _P]),
     "fb_dequant_rows": (_I32, [_I32, _P, _I64, _I32, _I32, _P, _P]),
     "fb_quantize_act": (_I32, [_I32, _P, _I32, _I32, _I32, _P, _P]),
     "fb_synth_fill_blocks": (_I32, [_I32, _P, _I64, _I64, C.c_uint64, _P, _P]),

@@ -32,6 +32,57 @@ def linear_fp8(x, weight, out, workspace):
                                    torch.cuda.current_stream().cuda_stream), "linear_fp8")
 
 
+def store_bf16(out):
+    """linear_store_bf16 (linear.h:88-90 of the reference): out bf16 [T][n]."""
+    assert out.dtype == torch.bfloat16 and out.is_contiguous()
+    return L.LinearEpilogue(L.EPI_STORE_BF16, 0, out.data_ptr(), None, None)
+
+
+def store_f32(out):
+    """linear_store_f32 (linear.h:91): out fp32 [T][n]."""
+    assert out.dtype == torch.float32 and out.is_contiguous()
+    return L.LinearEpilogue(L.EPI_STORE_F32, 0, out.data_ptr(), None, None)
+
+
+def gr_write(x_streams, inj):
+    """linear_gr_write (linear.h:92-94): X fp32 [T][4][n] += inj fp32 [T][4] * acc, in place."""
+    assert x_streams.dtype == torch.float32 and inj.dtype == torch.float32
+    assert x_streams.is_contiguous() and inj.is_contiguous()
+    return L.LinearEpilogue(L.EPI_GR_WRITE, 0, x_streams.data_ptr(), inj.data_ptr(), None)
+
+
+def swiglu(h):
+    """linear_swiglu (linear.h:95): h bf16 [T][n/2] = silu(acc[j]) * acc[n/2 + j]."""
+    assert h.dtype == torch.bfloat16 and h.is_contiguous()
+    return L.LinearEpilogue(L.EPI_SWIGLU, 0, h.data_ptr(), None, None)
+
+
+def shared_scale(y, gate_logit, gate_stride):
+    """linear_shared_scale (linear.h:96-99): y fp32 [T][n] = sigmoid(gate_logit[t * gate_stride]) * acc."""
+    assert y.dtype == torch.float32 and gate_logit.dtype == torch.float32 and y.is_contiguous()
+    return L.LinearEpilogue(L.EPI_SHARED_SCALE, gate_stride, y.data_ptr(), None, gate_logit.data_ptr())
+
+
+def linear_fp8_decode_workspace(weight, device="cuda"):
+    n = L.load().fb_linear_fp8_decode_workspace_bytes(weight.n, weight.k)
+    buf = torch.empty(n + 256, dtype=torch.uint8, device=device)
+    off = (-buf.data_ptr()) % 256
+    return buf[off:off + n]
+
+
+def linear_fp8_decode(x, weight, epilogue, workspace):
+    """linear_fp8 for T <= 16 on the exact-activation path (linear.h:137-139 with Fp8LinearPath::A16):
+    x bf16 [T][k]; the output is whatever `epilogue` (store_bf16, store_f32, gr_write, swiglu,
+    shared_scale) names."""
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == weight.k
+    dt = L.DT_BF16 if weight.scales.dtype == torch.bfloat16 else L.DT_F32
+    import ctypes
+    L.check(L.load().fb_linear_fp8_decode(x.data_ptr(), x.shape[0], weight.codes.data_ptr(), weight.scales.data_ptr(),
+                                          dt, weight.n, weight.k, ctypes.byref(epilogue), workspace.data_ptr(),
+                                          workspace.numel(), torch.cuda.current_stream().cuda_stream),
+            "linear_fp8_decode")
+
+
 def fp8_quantize_tokens(x):
     """Per-token E4M3 codes and fp32 scales of bf16 x [T][k]."""
     T, k = x.shape

@@ -324,6 +324,33 @@ int32_t fb_linear_fp8(const void* x_bf16, int32_t tokens, const uint8_t* w_codes
 int32_t fb_fp8_quantize_tokens(const void* x_bf16, int32_t tokens, int32_t k, uint8_t* codes, float* scales,
                                void* stream);
 
+/* linear_fp8 at decode width, the reference's "A16" path for T <= 16 (src/kernels/linear/linear.h:27-31,
+ * :137-139; fp8/fp8_gemv.cuh, fp8/fp8_a16_ksplit_mma.cuh): bf16 activations are kept exactly, E4M3
+ * weights are used exactly, fp32 accumulation, one multiplication by the row scale, then the
+ * epilogue (LinearEpilogue / LinearEpilogueParams, linear.h:64-103):
+ *   FB_EPI_STORE_BF16    out bf16 [T][n]
+ *   FB_EPI_STORE_F32     out fp32 [T][n]
+ *   FB_EPI_GR_WRITE      out = X fp32 [T][4][n], X[t][s][r] += inj[t][s] * acc[t][r]   (inj fp32 [T][4])
+ *   FB_EPI_SWIGLU        out = h bf16 [T][n/2], h[t][j] = silu(acc[t][j]) * acc[t][n/2 + j]
+ *   FB_EPI_SHARED_SCALE  out = y fp32 [T][n], y[t][r] = sigmoid(gate_logit[t * gate_stride]) * acc[t][r]
+ * (SiluQuarter and GrMix belong to the residual-stream mixer and are not provided.) tokens 1..16,
+ * k % 128 == 0, n % 8 == 0; any such shape is accepted (the closed registry of linear_fp8.cpp:19-24
+ * is not enforced). Every output element is written once, by one thread, after the complete K
+ * reduction, in an order that depends only on the shape: repeated calls are bitwise identical
+ * (linear.h:39-41). Bad arguments return cudaErrorInvalidValue where the reference throws. */
+enum { FB_EPI_STORE_BF16 = 0, FB_EPI_STORE_F32 = 1, FB_EPI_GR_WRITE = 2, FB_EPI_SWIGLU = 3, FB_EPI_SHARED_SCALE = 4 };
+typedef struct fb_linear_epilogue {
+  int32_t kind;            /* FB_EPI_* */
+  int32_t gate_stride;     /* SharedScale */
+  void* out;
+  const float* inj;        /* GrWrite */
+  const float* gate_logit; /* SharedScale */
+} fb_linear_epilogue;
+size_t fb_linear_fp8_decode_workspace_bytes(int32_t n, int32_t k);
+int32_t fb_linear_fp8_decode(const void* x_bf16, int32_t tokens, const uint8_t* w_codes, const void* w_scales,
+                             int32_t w_scales_dtype, int32_t n, int32_t k, const fb_linear_epilogue* epilogue,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---------------------------------------------------------------- parity probes (no reference counterpart)
  * The same device routines the GEMV kernels use, exposed so that dequantized weights and int8
  * activations can be compared bit for bit with the CPU reference. */
