@@ -32,35 +32,43 @@ def linear_fp8(x, weight, out, workspace):
                                    torch.cuda.current_stream().cuda_stream), "linear_fp8")
 
 
+def _epilogue(kind, gate_stride, out, inj=None, gate_logit=None):
+    """fb_linear_epilogue that also keeps its tensors alive: the struct holds raw device pointers."""
+    e = L.LinearEpilogue(kind, gate_stride, out.data_ptr(), None if inj is None else inj.data_ptr(),
+                         None if gate_logit is None else gate_logit.data_ptr())
+    e._keep = (out, inj, gate_logit)
+    return e
+
+
 def store_bf16(out):
     """linear_store_bf16 (linear.h:88-90 of the reference): out bf16 [T][n]."""
     assert out.dtype == torch.bfloat16 and out.is_contiguous()
-    return L.LinearEpilogue(L.EPI_STORE_BF16, 0, out.data_ptr(), None, None)
+    return _epilogue(L.EPI_STORE_BF16, 0, out)
 
 
 def store_f32(out):
     """linear_store_f32 (linear.h:91): out fp32 [T][n]."""
     assert out.dtype == torch.float32 and out.is_contiguous()
-    return L.LinearEpilogue(L.EPI_STORE_F32, 0, out.data_ptr(), None, None)
+    return _epilogue(L.EPI_STORE_F32, 0, out)
 
 
 def gr_write(x_streams, inj):
     """linear_gr_write (linear.h:92-94): X fp32 [T][4][n] += inj fp32 [T][4] * acc, in place."""
     assert x_streams.dtype == torch.float32 and inj.dtype == torch.float32
     assert x_streams.is_contiguous() and inj.is_contiguous()
-    return L.LinearEpilogue(L.EPI_GR_WRITE, 0, x_streams.data_ptr(), inj.data_ptr(), None)
+    return _epilogue(L.EPI_GR_WRITE, 0, x_streams, inj=inj)
 
 
 def swiglu(h):
     """linear_swiglu (linear.h:95): h bf16 [T][n/2] = silu(acc[j]) * acc[n/2 + j]."""
     assert h.dtype == torch.bfloat16 and h.is_contiguous()
-    return L.LinearEpilogue(L.EPI_SWIGLU, 0, h.data_ptr(), None, None)
+    return _epilogue(L.EPI_SWIGLU, 0, h)
 
 
 def shared_scale(y, gate_logit, gate_stride):
     """linear_shared_scale (linear.h:96-99): y fp32 [T][n] = sigmoid(gate_logit[t * gate_stride]) * acc."""
     assert y.dtype == torch.float32 and gate_logit.dtype == torch.float32 and y.is_contiguous()
-    return L.LinearEpilogue(L.EPI_SHARED_SCALE, gate_stride, y.data_ptr(), None, gate_logit.data_ptr())
+    return _epilogue(L.EPI_SHARED_SCALE, gate_stride, y, gate_logit=gate_logit)
 
 
 def linear_fp8_decode_workspace(weight, device="cuda"):

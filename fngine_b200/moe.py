@@ -148,6 +148,47 @@ def moe_layer_decode(w_router, layer, x, ws, y_out):
                                          C.byref(ws.ws), _ptr(ws.logits), _ptr(y_out), _stream()), "moe_layer_decode")
 
 
+class SharedExpert:
+    """The shared expert of one layer as the reference registers it (src/kernels/linear/linear.h:11-12):
+    gate_up = Fp8RowWeight (2 * inter_s, 2560) with the SwiGlu epilogue, down = Fp8RowWeight (2560, inter_s)
+    with the SharedScale epilogue. Owns the workspaces and the two intermediate buffers."""
+
+    def __init__(self, gate_up, down, max_tokens=16):
+        from . import linear
+        assert gate_up.n == 2 * down.k and down.n == gate_up.k
+        self.gate_up, self.down = gate_up, down
+        self.work_gu = linear.linear_fp8_decode_workspace(gate_up)
+        self.work_dn = linear.linear_fp8_decode_workspace(down)
+        self.h = torch.empty(max_tokens, down.k, dtype=torch.bfloat16, device=gate_up.codes.device)
+        self.y = torch.empty(max_tokens, down.n, dtype=torch.float32, device=gate_up.codes.device)
+
+
+def forward_moe_decode(w_router, shared, layer, x, ws, inj, X, y_out=None, aux_stream=None):
+    """The decode branch of Forward::moe (src/model/forward.cpp:333,356-376 of the reference): router
+    projection (513 rows, row 512 = the shared gate), select, the shared expert beside the routed
+    experts on `aux_stream` (its down epilogue reads the shared-gate logit), gate/up, down, and the
+    combine that adds y_shared and writes the residual streams X += inj * y. x: bf16 [T][2560]."""
+    from . import linear
+    T = x.shape[0]
+    assert x.dtype == torch.bfloat16 and w_router.shape[0] == L.ROUTER_ROWS and T <= shared.h.shape[0]
+    router_logits(w_router, x, ws.logits)
+    moe_select_publish(ws.logits, x, None, 0, None, None, T, ws)
+    cur = torch.cuda.current_stream()
+    side = aux_stream if aux_stream is not None else cur
+    if side is not cur:
+        side.wait_stream(cur)
+    with torch.cuda.stream(side):
+        h, y_sh = shared.h[:T], shared.y[:T]
+        linear.linear_fp8_decode(x, shared.gate_up, linear.swiglu(h), shared.work_gu)
+        gate = ws.logits.view(-1)[L.ROUTER_ROWS - 1:]
+        linear.linear_fp8_decode(h, shared.down, linear.shared_scale(y_sh, gate, L.ROUTER_ROWS), shared.work_dn)
+    moe_hot_gate_up(layer, T, ws)
+    moe_hot_down(layer, T, ws)
+    if side is not cur:
+        cur.wait_stream(side)
+    moe_combine(ws, shared.y, None, 0, None, inj, X, y_out, T)
+
+
 def moe_layer_decode_host(w_router, layer, x_host, ws, x_dev, y_dev, y_host):
     """Same with pinned HOST x / y: the copies in and out and the final wait are inside the call."""
     L.check(L.load().fb_moe_layer_decode_host(_ptr(w_router), C.byref(layer.layout), x_host.data_ptr(),

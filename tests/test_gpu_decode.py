@@ -336,6 +336,54 @@ def test_combine_shared_residual_and_ablation():
     assert rel_l2(X.cpu().numpy(), wantX.cpu().numpy()) <= 1e-5
 
 
+@pytest.mark.parametrize("tokens,aux", [(1, False), (5, True), (16, True)])
+def test_forward_moe_decode_with_shared_expert(tokens, aux):
+    """The whole decode branch of Forward::moe (src/model/forward.cpp:333,356-376 of the reference):
+    513-row router, routed experts, the FP8-row shared expert (SwiGlu, then SharedScale with the
+    shared-gate logit) on a side stream, combine with the residual write. Checked against the CPU
+    expert path plus an fp64 shared expert over the represented weights, 1e-3 relative per token."""
+    torch = _torch()
+    from fngine_b200 import linear, moe
+    seed, inter = 4242, 512
+    layer = moe.synth_layer(IQ3_S, IQ3_S, inter, 512, seed)
+    ws = moe.DecodeWorkspace(layer)
+    wr = torch.from_numpy(synth.router_weights(909, rows=513).view(np.int16)).cuda().view(torch.bfloat16)
+    gu_c, gu_s = synth.fp8_row_weight(31, 1280, H)
+    dn_c, dn_s = synth.fp8_row_weight(32, H, 640)
+    gu_s = gu_s * np.float32(10.0)  # gate and up values of order one, so that the shared part matters
+    shared = moe.SharedExpert(
+        linear.Fp8RowWeight(torch.from_numpy(gu_c).cuda(), torch.from_numpy(gu_s).cuda().to(torch.bfloat16)),
+        linear.Fp8RowWeight(torch.from_numpy(dn_c).cuda(), torch.from_numpy(dn_s).cuda().to(torch.bfloat16)))
+    xb = synth.to_bf16_bits(synth.activations(77 + tokens, tokens))
+    x = synth.bf16_bits_to_f32(xb)
+    xd = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    inj = torch.from_numpy(synth.normal(61, tokens * 4).astype(np.float32).reshape(tokens, 4)).cuda()
+    X0 = torch.from_numpy(synth.normal(62, tokens * 4 * H).astype(np.float32).reshape(tokens, 4, H)).cuda()
+    X = X0.clone()
+    y = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    side = torch.cuda.Stream() if aux else None
+    moe.forward_moe_decode(wr, shared, layer, xd, ws, inj, X, y, aux_stream=side)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    logits = ws.logits.cpu().numpy()[:tokens * 513].reshape(tokens, 513)
+    ids, w = O.topk(logits[:, :512])
+    routed = oracle_layer(IQ3_S, IQ3_S, inter, seed, x, ids, w).astype(np.float64)
+    tab = O.e4m3_table().astype(np.float64)
+    acc = (x.astype(np.float64) @ tab[gu_c].T) * synth.bf16_bits_to_f32(synth.to_bf16_bits(gu_s)).astype(np.float64)[None, :]
+    g, u = acc[:, :640], acc[:, 640:]
+    h = synth.bf16_bits_to_f32(synth.to_bf16_bits((g / (1.0 + np.exp(-g)) * u).astype(np.float32))).astype(np.float64)
+    ysh = (h @ tab[dn_c].T) * synth.bf16_bits_to_f32(synth.to_bf16_bits(dn_s)).astype(np.float64)[None, :]
+    ysh = ysh / (1.0 + np.exp(-logits[:, 512].astype(np.float64)))[:, None]
+    want = routed + ysh
+    got = y.cpu().numpy()
+    errs = [rel_l2(got[t], want[t]) for t in range(tokens)]
+    assert max(errs) <= TOL, errs
+    wantX = X0.cpu().numpy().astype(np.float64) + inj.cpu().numpy().astype(np.float64)[:, :, None] * want[:, None, :]
+    assert rel_l2(X.cpu().numpy(), wantX) <= 1e-5
+    print("forward moe decode T=%d: shared/routed norm %.2f, max rel L2 %.2e" %
+          (tokens, float(np.linalg.norm(ysh) / np.linalg.norm(routed)), max(errs)))
+
+
 def test_host_entry_point_matches_device_path():
     torch = _torch()
     from fngine_b200 import moe
