@@ -696,12 +696,21 @@ __device__ __forceinline__ float dec_row_scale(const DecArgs& a, int row) {
 // Called by all 128 epilogue threads (et = 0..127; rl is the thread's tensor-memory lane).
 __device__ __forceinline__ void dec_emit(const DecArgs& a, int m, int rl, int et, const float (&v)[kDecTok],
                                          float* xch) {
+  // The token scales (and gate logits below) are fetched before the first store: a load that follows
+  // a store through an unrelated pointer cannot be moved above it by the compiler, and sixteen
+  // dependent memory round trips would cost more than the whole tile.
+  float ts[kDecTok];
+#pragma unroll
+  for (int t4 = 0; t4 < kDecTok / 4; ++t4) {
+    const float4 f = __ldg(reinterpret_cast<const float4*>(a.tok_scale) + t4);
+    ts[4 * t4] = f.x, ts[4 * t4 + 1] = f.y, ts[4 * t4 + 2] = f.z, ts[4 * t4 + 3] = f.w;
+  }
   if (a.kind == FB_EPI_SWIGLU) {
     // tile rows 0..63 are gate rows m*64.., rows 64..127 the matching up rows
     const int half_n = a.n >> 1, j = m * 64 + (rl & 63);
     const float ws = j < half_n ? dec_row_scale(a, rl < 64 ? j : half_n + j) : 0.0f;
 #pragma unroll
-    for (int t = 0; t < kDecTok; ++t) xch[rl * 17 + t] = v[t] * a.tok_scale[t] * ws;
+    for (int t = 0; t < kDecTok; ++t) xch[rl * 17 + t] = v[t] * ts[t] * ws;
     named_bar_sync(2, 128);
     const int r = et & 63, t0 = (et >> 6) * 8, jo = m * 64 + r;
     if (jo < half_n) {
@@ -734,8 +743,8 @@ __device__ __forceinline__ void dec_emit(const DecArgs& a, int m, int rl, int et
 #pragma unroll
     for (int t = 0; t < kDecTok; ++t)
       if (t < a.T) {
-        const float val = v[t] * a.tok_scale[t] * ws;
-        const float4 g = *reinterpret_cast<const float4*>(a.inj + size_t(t) * 4);
+        const float val = v[t] * ts[t] * ws;
+        const float4 g = __ldg(reinterpret_cast<const float4*>(a.inj + size_t(t) * 4));
         xs[(size_t(t) * 4 + 0) * n] = fmaf(g.x, val, x4[t][0]);
         xs[(size_t(t) * 4 + 1) * n] = fmaf(g.y, val, x4[t][1]);
         xs[(size_t(t) * 4 + 2) * n] = fmaf(g.z, val, x4[t][2]);
@@ -743,18 +752,19 @@ __device__ __forceinline__ void dec_emit(const DecArgs& a, int m, int rl, int et
       }
     return;
   }
+  if (a.kind == FB_EPI_SHARED_SCALE) {
+#pragma unroll
+    for (int t = 0; t < kDecTok; ++t)
+      if (t < a.T) ts[t] /= 1.0f + expf(-__ldg(a.gate_logit + size_t(t) * a.gate_stride));  // sigmoid(gate) folded in
+  }
 #pragma unroll
   for (int t = 0; t < kDecTok; ++t) {
     if (t >= a.T) break;
-    const float val = v[t] * a.tok_scale[t] * ws;
-    if (a.kind == FB_EPI_STORE_BF16) {
+    const float val = v[t] * ts[t] * ws;
+    if (a.kind == FB_EPI_STORE_BF16)
       static_cast<__nv_bfloat16*>(a.out)[size_t(t) * a.n + row] = __float2bfloat16_rn(val);
-    } else if (a.kind == FB_EPI_STORE_F32) {
-      static_cast<float*>(a.out)[size_t(t) * a.n + row] = val;
-    } else {  // FB_EPI_SHARED_SCALE
-      const float gl = a.gate_logit[size_t(t) * a.gate_stride];
-      static_cast<float*>(a.out)[size_t(t) * a.n + row] = val / (1.0f + expf(-gl));
-    }
+    else
+      static_cast<float*>(a.out)[size_t(t) * a.n + row] = val;  // StoreF32, SharedScale
   }
 }
 
