@@ -583,6 +583,10 @@ __device__ __forceinline__ bool dec_wait(DecBars* b, uint64_t* bar, uint32_t par
   atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
   return false;
 }
+// Adds to the pending byte count of a barrier without arriving on it.
+__device__ __forceinline__ void mbar_expect_tx_only(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
 // All `threads` threads of named barrier `id` learn whether every one of them passed `ok`.
 __device__ __forceinline__ bool named_bar_all(int id, int threads, bool ok) {
   uint32_t r;
@@ -612,6 +616,8 @@ __device__ __forceinline__ uint32_t float_to_e5m2(float v) {
   return uint32_t(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E5M2));  // round to nearest even
 }
 
+constexpr int kSplitPer = 5;  // 16-byte pieces of a row a thread keeps in registers (rows up to 10240 values)
+
 // One block per token slot. pieces[(p * 16 + t) * K + j], p = 0..2; slots >= T are zero rows. Block 0
 // also clears the tickets and the status word of the projection that follows.
 __global__ void __launch_bounds__(256) fp8_split_tokens_kernel(const __nv_bfloat16* __restrict__ x, int T, int K,
@@ -634,14 +640,28 @@ __global__ void __launch_bounds__(256) fp8_split_tokens_kernel(const __nv_bfloat
     return;
   }
   const uint4* row = reinterpret_cast<const uint4*>(x + size_t(t) * K);
+  // the row stays in registers between the two phases (up to 256 * 8 * kSplitPer values; longer rows
+  // re-read the remainder)
+  uint4 keep[kSplitPer];
   float m = 0.0f;
-  for (int i = tid; i < K / 8; i += 256) {
+#pragma unroll
+  for (int j = 0; j < kSplitPer; ++j) {
+    const int i = tid + j * 256;
+    keep[j] = i < K / 8 ? row[i] : make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t w[4] = {keep[j].x, keep[j].y, keep[j].z, keep[j].w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      m = fmaxf(m, fabsf(__uint_as_float(w[q] << 16)));
+      m = fmaxf(m, fabsf(__uint_as_float(w[q] & 0xFFFF0000u)));
+    }
+  }
+  for (int i = tid + kSplitPer * 256; i < K / 8; i += 256) {
     const uint4 v = row[i];
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      m = fmaxf(m, fabsf(__uint_as_float(w[j] << 16)));
-      m = fmaxf(m, fabsf(__uint_as_float(w[j] & 0xFFFF0000u)));
+    for (int q = 0; q < 4; ++q) {
+      m = fmaxf(m, fabsf(__uint_as_float(w[q] << 16)));
+      m = fmaxf(m, fabsf(__uint_as_float(w[q] & 0xFFFF0000u)));
     }
   }
   __shared__ float red[8];
@@ -656,8 +676,7 @@ __global__ void __launch_bounds__(256) fp8_split_tokens_kernel(const __nv_bfloat
   uint32_t e = (__float_as_uint(m) >> 23) & 0xFFu;
   e = e < 15u ? 15u : (e > 253u ? 253u : e);
   const float scale = __uint_as_float((e - 14u) << 23), inv = __uint_as_float((268u - e) << 23);
-  for (int i = tid; i < K / 8; i += 256) {
-    const uint4 v = row[i];
+  auto split8 = [&](const uint4 v, int i) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
     uint32_t out[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
 #pragma unroll
@@ -673,7 +692,13 @@ __global__ void __launch_bounds__(256) fp8_split_tokens_kernel(const __nv_bfloat
     }
 #pragma unroll
     for (int p = 0; p < 3; ++p) reinterpret_cast<uint2*>(piece[p])[i] = make_uint2(out[p][0], out[p][1]);
+  };
+#pragma unroll
+  for (int j = 0; j < kSplitPer; ++j) {
+    const int i = tid + j * 256;
+    if (i < K / 8) split8(keep[j], i);
   }
+  for (int i = tid + kSplitPer * 256; i < K / 8; i += 256) split8(row[i], i);
   if (tid == 0) tok_scale[t] = scale;
 }
 
@@ -694,21 +719,25 @@ __device__ __forceinline__ float dec_row_scale(const DecArgs& a, int row) {
 
 // Finishes row tile m: v[t] is the K-complete sum of tile row `rl` for token slot t, before scales.
 // Called by all 128 epilogue threads (et = 0..127; rl is the thread's tensor-memory lane).
-__device__ __forceinline__ void dec_emit(const DecArgs& a, int m, int rl, int et, const float (&v)[kDecTok],
-                                         float* xch) {
-  // The token scales (and gate logits below) are fetched before the first store: a load that follows
-  // a store through an unrelated pointer cannot be moved above it by the compiler, and sixteen
-  // dependent memory round trips would cost more than the whole tile.
-  float ts[kDecTok];
-#pragma unroll
-  for (int t4 = 0; t4 < kDecTok / 4; ++t4) {
-    const float4 f = __ldg(reinterpret_cast<const float4*>(a.tok_scale) + t4);
-    ts[4 * t4] = f.x, ts[4 * t4 + 1] = f.y, ts[4 * t4 + 2] = f.z, ts[4 * t4 + 3] = f.w;
+// Row scale of tile row rl of tile m (0 outside the matrix). SwiGlu tiles hold 64 gate rows, then the 64
+// matching up rows.
+__device__ __forceinline__ float dec_tile_row_scale(const DecArgs& a, int m, int rl) {
+  if (a.kind == FB_EPI_SWIGLU) {
+    const int half_n = a.n >> 1, j = m * 64 + (rl & 63);
+    return j < half_n ? dec_row_scale(a, rl < 64 ? j : half_n + j) : 0.0f;
   }
+  const int row = m * 128 + rl;
+  return row < a.n ? dec_row_scale(a, row) : 0.0f;
+}
+
+// ts[t] = token scale (times sigmoid(gate logit) for SharedScale), ws = the row scale of this thread's
+// tile row (dec_tile_row_scale): both are fetched by the caller before it waits for the tile, so no
+// memory round trip stands between the accumulator and the stores.
+__device__ __forceinline__ void dec_emit(const DecArgs& a, int m, int rl, int et, const float (&v)[kDecTok],
+                                         const float (&ts)[kDecTok], float ws, float* xch) {
   if (a.kind == FB_EPI_SWIGLU) {
     // tile rows 0..63 are gate rows m*64.., rows 64..127 the matching up rows
-    const int half_n = a.n >> 1, j = m * 64 + (rl & 63);
-    const float ws = j < half_n ? dec_row_scale(a, rl < 64 ? j : half_n + j) : 0.0f;
+    const int half_n = a.n >> 1;
 #pragma unroll
     for (int t = 0; t < kDecTok; ++t) xch[rl * 17 + t] = v[t] * ts[t] * ws;
     named_bar_sync(2, 128);
@@ -727,7 +756,6 @@ __device__ __forceinline__ void dec_emit(const DecArgs& a, int m, int rl, int et
   }
   const int row = m * 128 + rl;
   if (row >= a.n) return;
-  const float ws = dec_row_scale(a, row);
   if (a.kind == FB_EPI_GR_WRITE) {
     // X[t][s][row] += inj[t][s] * val. All loads first: interleaved with the stores they would be
     // issued one memory round trip at a time.
@@ -751,11 +779,6 @@ __device__ __forceinline__ void dec_emit(const DecArgs& a, int m, int rl, int et
         xs[(size_t(t) * 4 + 3) * n] = fmaf(g.w, val, x4[t][3]);
       }
     return;
-  }
-  if (a.kind == FB_EPI_SHARED_SCALE) {
-#pragma unroll
-    for (int t = 0; t < kDecTok; ++t)
-      if (t < a.T) ts[t] /= 1.0f + expf(-__ldg(a.gate_logit + size_t(t) * a.gate_stride));  // sigmoid(gate) folded in
   }
 #pragma unroll
   for (int t = 0; t < kDecTok; ++t) {
@@ -806,6 +829,19 @@ fp8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   if (warp == 0) {
     // ---------------- TMA producer: 128 weight rows (two 64-row boxes) + the 48 piece rows per K block
     if (lane == 0) {
+      // The weight codes do not depend on the kernel launched just before (the activation split), so
+      // the first ring's worth of them is requested before waiting for it: under programmatic
+      // dependent launch this kernel is resident while the split still runs.
+      const int pre = end - begin < kDecStages ? int(end - begin) : kDecStages;
+      for (int i = 0; i < pre; ++i) {
+        const long long pos = begin + i;
+        const int m = int(pos / kbt), kb = int(pos - (long long)m * kbt);
+        const int r0 = swiglu ? m * 64 : m * 128, r1 = swiglu ? (a.n >> 1) + m * 64 : m * 128 + 64;
+        uint8_t* st = ring + i * kDecStage;
+        mbar_expect_tx_only(&bars->full[i], kDecStageA);
+        tma_load_2d(st, &map_w, kb * BK, r0, &bars->full[i]);
+        tma_load_2d(st + 64 * BK, &map_w, kb * BK, r1, &bars->full[i]);
+      }
       pdl_wait_prior();  // the pieces are written by the kernel launched just before
       uint32_t it = 0;
       bool ok = true;
@@ -815,8 +851,13 @@ fp8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const int r0 = swiglu ? m * 64 : m * 128, r1 = swiglu ? (a.n >> 1) + m * 64 : m * 128 + 64;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % kDecStages;
-          if (!dec_wait(bars, &bars->empty[s], ((it / kDecStages) & 1) ^ 1, a.status)) { ok = false; break; }
           uint8_t* st = ring + s * kDecStage;
+          if (it < uint32_t(pre)) {  // codes already requested: add the pieces and the arrival
+            mbar_expect_tx(&bars->full[s], kDecStageB);
+            tma_load_2d(st + kDecStageA, &map_p, kb * BK, 0, &bars->full[s]);
+            continue;
+          }
+          if (!dec_wait(bars, &bars->empty[s], ((it / kDecStages) & 1) ^ 1, a.status)) { ok = false; break; }
           mbar_expect_tx(&bars->full[s], kDecStage);
           tma_load_2d(st, &map_w, kb * BK, r0, &bars->full[s]);
           tma_load_2d(st + 64 * BK, &map_w, kb * BK, r1, &bars->full[s]);
@@ -856,11 +897,26 @@ fp8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     // ---------------- epilogue warps 2..5: tensor-memory lane quarter = warp % 4
     const int q = warp & 3, rl = q * 32 + lane, et = (warp - 2) * 32 + lane;
     pdl_wait_prior();  // token scales and cleared tickets come from the kernel launched just before
+    float ts[kDecTok];
+#pragma unroll
+    for (int t4 = 0; t4 < kDecTok / 4; ++t4) {
+      const float4 f = __ldg(reinterpret_cast<const float4*>(a.tok_scale) + t4);
+      ts[4 * t4] = f.x, ts[4 * t4 + 1] = f.y, ts[4 * t4 + 2] = f.z, ts[4 * t4 + 3] = f.w;
+    }
+    if (a.kind == FB_EPI_SHARED_SCALE) {  // sigmoid(gate logit) folded into the token scale
+      float gl[kDecTok];
+#pragma unroll
+      for (int t = 0; t < kDecTok; ++t)  // all loads first: the division below branches, and loads do not move across it
+        gl[t] = __ldg(a.gate_logit + size_t(t < a.T ? t : 0) * a.gate_stride);
+#pragma unroll
+      for (int t = 0; t < kDecTok; ++t) ts[t] /= 1.0f + expf(-gl[t]);
+    }
     uint32_t seg = 0;
     for (long long pos = begin; pos < end; ++seg) {
       const int m = int(pos / kbt), kb0 = int(pos - (long long)m * kbt);
       const int kb1 = int(end - pos) < kbt - kb0 ? kb0 + int(end - pos) : kbt;
       const int ab = seg & 1;
+      const float ws = dec_tile_row_scale(a, m, rl);
       const bool got = dec_wait(bars, &bars->tmem_full[ab], (seg >> 1) & 1, a.status);
       if (!named_bar_all(1, 128, got)) break;  // the four warps leave together
       tc_fence_after();
@@ -878,7 +934,7 @@ fp8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty[ab]);
       if (kb0 == 0 && kb1 == kbt) {
-        dec_emit(a, m, rl, et, v, xch);
+        dec_emit(a, m, rl, et, v, ts, ws, xch);
       } else {
         // a partial range: leave the sums in this CTA's slot (first segment: slot 0, a later one: 1)
         float* mine = a.partial + size_t(2 * blockIdx.x + (pos == begin ? 0 : 1)) * kDecPartialFloats;
@@ -894,13 +950,27 @@ fp8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           __threadfence();
 #pragma unroll
           for (int t = 0; t < kDecTok; ++t) v[t] = 0.0f;
-          for (int cc = c_first; cc <= c_last; ++cc) {  // fixed order: results do not depend on arrival order
-            const bool first_seg = dec_begin(cc, G, total) / kbt == m;
-            const float* theirs = a.partial + size_t(2 * cc + (first_seg ? 0 : 1)) * kDecPartialFloats;
+          // fixed order (results do not depend on arrival order); two contributors' loads in flight
+          for (int c0 = c_first; c0 <= c_last; c0 += 2) {
+            float part[2][kDecTok];
 #pragma unroll
-            for (int t = 0; t < kDecTok; ++t) v[t] += __ldcg(theirs + t * 128 + rl);
+            for (int i = 0; i < 2; ++i) {
+              const int cc = c0 + i;
+              if (cc <= c_last) {
+                const bool first_seg = dec_begin(cc, G, total) / kbt == m;
+                const float* theirs = a.partial + size_t(2 * cc + (first_seg ? 0 : 1)) * kDecPartialFloats;
+#pragma unroll
+                for (int t = 0; t < kDecTok; ++t) part[i][t] = __ldcg(theirs + t * 128 + rl);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              if (c0 + i <= c_last) {
+#pragma unroll
+                for (int t = 0; t < kDecTok; ++t) v[t] += part[i][t];
+              }
           }
-          dec_emit(a, m, rl, et, v, xch);
+          dec_emit(a, m, rl, et, v, ts, ws, xch);
         }
       }
       pos += kb1 - kb0;
@@ -1111,9 +1181,13 @@ int32_t fb_linear_fp8_decode(const void* x_bf16, int32_t tokens, const uint8_t* 
   a.status = status;
   const int m_tiles = kind == FB_EPI_SWIGLU ? ((n >> 1) + 63) / 64 : (n + 127) / 128;
   const long long total = (long long)m_tiles * (k / BK);
-  // at least two K blocks per CTA: below that the partial-sum traffic outweighs the extra parallelism
+  // Row tiles that nearly fill the GPU get one CTA each (whole tiles: no partial sums, whose ticketed
+  // reduction costs more than the idle multiprocessors). Otherwise the K blocks are divided evenly,
+  // with at least two per CTA: below that the partial-sum traffic outweighs the extra parallelism.
+  const int sms = sm_count();
   const long long want = total / 2 > 0 ? total / 2 : 1;
-  const int grid = want < sm_count() ? int(want) : sm_count();
+  int grid = want < sms ? int(want) : sms;
+  if (m_tiles <= sms && 4 * m_tiles >= 3 * sms) grid = m_tiles;
   cudaError_t e = launch_pdl(fp8_decode_kernel, dim3(grid), dim3(kThreads), size_t(kDecSmem), s, map_w, map_p, a);
   if (e != cudaSuccess) return check_launch("linear_fp8_decode");
   return check_launch("linear_fp8_decode");
