@@ -60,3 +60,29 @@ def test_layout_and_argument_errors(fb_built):
     assert st == 1 and b"exchange" in lib.fb_last_error_string()
     st = lib.fb_moe_select_publish(0x1000, 513, 0x1000, 0, None, 0, None, None, 17, ctypes.byref(ws), None, None)
     assert st == 1
+
+
+def test_decode_width_projection_argument_checks(fb_built):
+    """fb_linear_fp8_decode refuses bad shapes, epilogues and workspaces before anything is launched
+    (where the reference throws std::invalid_argument, src/kernels/linear/linear_fp8.cpp:83-95)."""
+    lib = fblib.load()
+    need = lib.fb_linear_fp8_decode_workspace_bytes(2560, 640)
+    # pieces [48][k] + two 256-byte words + tickets + 512 partial tiles of 128 x 16 fp32
+    assert need == 48 * 640 + 256 + 256 + 256 + 512 * 128 * 16 * 4
+    assert lib.fb_linear_fp8_decode_workspace_bytes(0, 640) == 0
+    p = 0x10000
+    epi = fblib.LinearEpilogue(fblib.EPI_STORE_F32, 0, p, None, None)
+    e = ctypes.byref(epi)
+    assert lib.fb_linear_fp8_decode(p, 0, p, p, 0, 256, 256, e, p, need, None) == 1
+    assert lib.fb_linear_fp8_decode(p, 17, p, p, 0, 256, 256, e, p, need, None) == 1
+    assert b"1..16" in lib.fb_last_error_string()
+    assert lib.fb_linear_fp8_decode(p, 4, p, p, 0, 256, 192, e, p, need, None) == 1     # k % 128
+    assert lib.fb_linear_fp8_decode(p, 4, p, p, 0, 250, 256, e, p, need, None) == 1     # n % 8
+    assert lib.fb_linear_fp8_decode(p, 4, p, p, 0, 256, 256, e, p + 8, need, None) == 1  # workspace alignment
+    assert lib.fb_linear_fp8_decode(p, 4, p, p, 0, 256, 256, e, p, 1000, None) == 1
+    assert b"workspace" in lib.fb_last_error_string()
+    sw = fblib.LinearEpilogue(fblib.EPI_SWIGLU, 0, p, None, None)
+    assert lib.fb_linear_fp8_decode(p, 4, p, p, 0, 264, 256, ctypes.byref(sw), p, need, None) == 1  # SwiGlu n % 16
+    sh = fblib.LinearEpilogue(fblib.EPI_SHARED_SCALE, 513, p, None, None)
+    assert lib.fb_linear_fp8_decode(p, 4, p, p, 0, 256, 256, ctypes.byref(sh), p, need, None) == 1  # no gate logit
+    assert lib.fb_linear_fp8_decode(p, 4, p, p, 0, 256, 256, None, p, need, None) == 1

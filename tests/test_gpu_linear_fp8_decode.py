@@ -47,7 +47,7 @@ def exact_acc(torch, x, weight):
     return out
 
 
-def judge(torch, got, ref, bf16_out):
+def compare(torch, got, ref, bf16_out):
     got, ref = got.double().reshape(-1), ref.reshape(-1)
     rms = float(ref.pow(2).mean().sqrt())
     allowance = ref.abs() * (2.0 ** -8 * 1.001) if bf16_out else 0.0
@@ -112,7 +112,7 @@ def test_linear_fp8_decode_matches_the_exact_product(T, n, k, kind, bf16_scales)
     linear.linear_fp8_decode(x, weight, make(out), work)
     torch.cuda.synchronize()
     got = out.double() - x0.double() if kind == "gr_write" else out
-    ratio, match = judge(torch, got, ref, bf16_out)
+    ratio, match = compare(torch, got, ref, bf16_out)
     print("fp8 decode T=%d %dx%d %s: worst excess / rms %.2e, bf16 rounding match %.4f" % (T, n, k, kind, ratio, match))
     # deterministic: a second call (fresh output) is bitwise identical
     out2 = x0.clone() if kind == "gr_write" else torch.empty_like(out)
