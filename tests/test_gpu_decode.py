@@ -384,6 +384,43 @@ def test_forward_moe_decode_with_shared_expert(tokens, aux):
           (tokens, float(np.linalg.norm(ysh) / np.linalg.norm(routed)), max(errs)))
 
 
+@pytest.mark.parametrize("fg,fd,inter", [(IQ3_S, IQ3_S, 512), (IQ3_S, IQ4_NL, 640)])
+def test_layers_read_from_a_pack_and_from_gguf(fg, fd, inter, tmp_path):
+    """Expert bytes written as a pack (manifest.json + experts.bin, 4096-aligned stride) and as GGUF expert
+    tensors, read back by fngine_b200.pack and put in HBM, give the decode layer's result bit for bit as
+    the same bytes generated in place, and match the CPU expert path."""
+    torch = _torch()
+    from fngine_b200 import moe, pack
+    n_exp, tokens, seed = 16, 3, 606
+    blobs = np.stack([synth.expert_blob(fg, fd, inter, seed, e) for e in range(n_exp)])
+    info = pack.layer_info(fg, fd, H, inter, 0)
+    assert blobs.shape[1] == info.blob_bytes and info.blob_stride > info.blob_bytes
+    pack.write_expert_pack(str(tmp_path / "pack"), H, inter, [(fg, fd, blobs)])
+    gate, up, down = blobs[:, :info.gate_bytes], blobs[:, info.gate_bytes:2 * info.gate_bytes], blobs[:, 2 * info.gate_bytes:]
+    pack.write_gguf(str(tmp_path / "experts.gguf"),
+                    [("blk.0.ffn_gate_exps.weight", [H, inter, n_exp], fg, np.ascontiguousarray(gate)),
+                     ("blk.0.ffn_up_exps.weight", [H, inter, n_exp], fg, np.ascontiguousarray(up)),
+                     ("blk.0.ffn_down_exps.weight", [inter, H, n_exp], fd, np.ascontiguousarray(down))])
+    lg = forced_logits(tokens, [[(5 * t + i) % n_exp for i in range(10)] for t in range(tokens)])
+    x = synth.activations(17, tokens)
+    xd, ld = torch.from_numpy(x).cuda(), torch.from_numpy(lg).cuda()
+    results = []
+    for layer in (moe.synth_layer(fg, fd, inter, n_exp, seed),
+                  pack.ExpertPack.open(str(tmp_path / "pack")).load_layer(0),
+                  pack.GgufExperts(str(tmp_path / "experts.gguf")).load_layer(0)):
+        ws = moe.DecodeWorkspace(layer)
+        results.append(run_layer(torch, moe, layer, ws, None, xd, tokens, logits=ld).cpu().numpy())
+        assert ws.status() == 0
+    assert np.array_equal(results[1].view(np.uint32), results[0].view(np.uint32))
+    assert np.array_equal(results[2].view(np.uint32), results[0].view(np.uint32))
+    ids, w = O.topk(lg[:, :512])
+    want = oracle_layer(fg, fd, inter, seed, x, ids, w)
+    assert max(rel_l2(results[1][t], want[t]) for t in range(tokens)) <= TOL
+    # a shard of the pack: experts 8..15 as slots 0..7
+    shard = pack.ExpertPack.open(str(tmp_path / "pack")).load_layer(0, first=8, count=8)
+    assert shard.n_slots == 8 and shard.layout.blob_stride == info.blob_stride
+
+
 def test_host_entry_point_matches_device_path():
     torch = _torch()
     from fngine_b200 import moe
