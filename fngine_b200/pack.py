@@ -167,7 +167,7 @@ def _to_device(info, inter, slots, what, device):
     if info.gu_type not in KERNEL_FORMATS or info.down_type not in KERNEL_FORMATS:
         raise PackError("%s: %s gate/up with %s down is in the pack spec but not decoded by the kernels "
                         "(IQ3_S and IQ4_NL are)" % (what, EXPERT_TYPES[info.gu_type][0], EXPERT_TYPES[info.down_type][0]))
-    host = torch.from_numpy(np.ascontiguousarray(slots)).reshape(-1)
+    host = torch.from_numpy(np.array(slots, dtype=np.uint8, order="C")).reshape(-1)  # a writable copy of the mapped bytes
     dev = torch.empty(host.numel(), dtype=torch.uint8, device=device)
     dev.copy_(host.pin_memory() if torch.cuda.is_available() else host, non_blocking=False)
     return moe.ExpertLayer(dev, info.gu_type, info.down_type, inter, info.blob_stride)
