@@ -761,23 +761,27 @@ __device__ __forceinline__ void dec_emit(const DecArgs& a, int m, int rl, int et
     // issued one memory round trip at a time.
     float* xs = static_cast<float*>(a.out) + row;
     const size_t n = size_t(a.n);
-    float x4[kDecTok][4];
 #pragma unroll
-    for (int t = 0; t < kDecTok; ++t)
-      if (t < a.T) {
+    for (int h = 0; h < kDecTok; h += 8) {  // eight tokens at a time: 32 values in registers
+      if (h >= a.T) break;
+      float x4[8][4];
 #pragma unroll
-        for (int st = 0; st < 4; ++st) x4[t][st] = __ldcg(xs + (size_t(t) * 4 + st) * n);
-      }
+      for (int t = 0; t < 8; ++t)
+        if (h + t < a.T) {
 #pragma unroll
-    for (int t = 0; t < kDecTok; ++t)
-      if (t < a.T) {
-        const float val = v[t] * ts[t] * ws;
-        const float4 g = __ldg(reinterpret_cast<const float4*>(a.inj + size_t(t) * 4));
-        xs[(size_t(t) * 4 + 0) * n] = fmaf(g.x, val, x4[t][0]);
-        xs[(size_t(t) * 4 + 1) * n] = fmaf(g.y, val, x4[t][1]);
-        xs[(size_t(t) * 4 + 2) * n] = fmaf(g.z, val, x4[t][2]);
-        xs[(size_t(t) * 4 + 3) * n] = fmaf(g.w, val, x4[t][3]);
-      }
+          for (int st = 0; st < 4; ++st) x4[t][st] = __ldcg(xs + (size_t(h + t) * 4 + st) * n);
+        }
+#pragma unroll
+      for (int t = 0; t < 8; ++t)
+        if (h + t < a.T) {
+          const float val = v[h + t] * ts[h + t] * ws;
+          const float4 g = __ldg(reinterpret_cast<const float4*>(a.inj + size_t(h + t) * 4));
+          xs[(size_t(h + t) * 4 + 0) * n] = fmaf(g.x, val, x4[t][0]);
+          xs[(size_t(h + t) * 4 + 1) * n] = fmaf(g.y, val, x4[t][1]);
+          xs[(size_t(h + t) * 4 + 2) * n] = fmaf(g.z, val, x4[t][2]);
+          xs[(size_t(h + t) * 4 + 3) * n] = fmaf(g.w, val, x4[t][3]);
+        }
+    }
     return;
   }
 #pragma unroll
@@ -788,6 +792,36 @@ __device__ __forceinline__ void dec_emit(const DecArgs& a, int m, int rl, int et
       static_cast<__nv_bfloat16*>(a.out)[size_t(t) * a.n + row] = __float2bfloat16_rn(val);
     else
       static_cast<float*>(a.out)[size_t(t) * a.n + row] = val;  // StoreF32, SharedScale
+  }
+}
+
+// v[t] (t < TT) = sum over the CTAs c_first..c_last that hold a part of row tile m, in CTA order: fixed, so
+// results do not depend on the order of arrival. Two contributors' loads are in flight at a time, six with at
+// most four tokens (usually the whole list in one round trip).
+template <int TT>
+__device__ __forceinline__ void dec_sum_partials(const DecArgs& a, int m, int rl, int c_first, int c_last, int G,
+                                                 long long total, int kbt, float (&v)[kDecTok]) {
+  constexpr int kPer = TT == 16 ? 2 : 6;
+  for (int c0 = c_first; c0 <= c_last; c0 += kPer) {
+    float part[kPer][TT];
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int cc = c0 + i;
+      if (cc <= c_last) {
+        // a contributor's range meets the tile; it is the CTA's first segment iff the range starts inside it
+        // (floor(total * cc / G) >= m * kbt without the division)
+        const bool first_seg = total * cc >= (long long)m * kbt * G;
+        const float* theirs = a.partial + size_t(2 * cc + (first_seg ? 0 : 1)) * kDecPartialFloats;
+#pragma unroll
+        for (int t = 0; t < TT; ++t) part[i][t] = __ldcg(theirs + t * 128 + rl);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kPer; ++i)
+      if (c0 + i <= c_last) {
+#pragma unroll
+        for (int t = 0; t < TT; ++t) v[t] += part[i][t];
+      }
   }
 }
 
@@ -950,26 +984,8 @@ fp8_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           __threadfence();
 #pragma unroll
           for (int t = 0; t < kDecTok; ++t) v[t] = 0.0f;
-          // fixed order (results do not depend on arrival order); two contributors' loads in flight
-          for (int c0 = c_first; c0 <= c_last; c0 += 2) {
-            float part[2][kDecTok];
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              const int cc = c0 + i;
-              if (cc <= c_last) {
-                const bool first_seg = dec_begin(cc, G, total) / kbt == m;
-                const float* theirs = a.partial + size_t(2 * cc + (first_seg ? 0 : 1)) * kDecPartialFloats;
-#pragma unroll
-                for (int t = 0; t < kDecTok; ++t) part[i][t] = __ldcg(theirs + t * 128 + rl);
-              }
-            }
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
-              if (c0 + i <= c_last) {
-#pragma unroll
-                for (int t = 0; t < kDecTok; ++t) v[t] += part[i][t];
-              }
-          }
+          if (a.T <= 4) dec_sum_partials<4>(a, m, rl, c_first, c_last, G, total, kbt, v);
+          else dec_sum_partials<16>(a, m, rl, c_first, c_last, G, total, kbt, v);
           dec_emit(a, m, rl, et, v, ts, ws, xch);
         }
       }
