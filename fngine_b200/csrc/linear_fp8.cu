@@ -19,6 +19,10 @@
 // in front of it cost 17 % of the kernel; with both gone the pair kernel runs at 2.4 PFLOP/s, within
 // 8 % of issuing the MMAs back to back with no barriers at all (2.65 PFLOP/s), while a library FP8
 // GEMM of the same shape on the same GPU reaches 2.7 - 2.9 PFLOP/s.
+//
+// A second operation lives here: the same weights at decode width (T <= 16) with the bf16 activations
+// kept exactly (the reference's "A16" numerics) and its fused epilogues, a stream over the weight codes
+// that reaches 0.9 of the HBM copy rate; see "decode-width projection" below.
 #include "common.cuh"
 
 #include <cuda.h>

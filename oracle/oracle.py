@@ -272,3 +272,24 @@ def quantize_tokens_e4m3(x_bf16):
     for t in range(T):
         scales[t] = port().fbo_quantize_token_e4m3(_ptr(x[t]), K, _ptr(codes[t]))
     return codes, scales
+
+
+def linear_fp8_a16(x_bf16, codes, scales, kind="store", gate_logit=None):
+    """The exact-activation FP8-row projection as the reference's own test oracle states it
+    (tests/kernels/linear/test_linear.cpp:196-243): fp64 dot products of the E4M3 weight values with
+    the bf16 activations, times the row scale, then the epilogue in fp64.
+    x_bf16: uint16 bf16 bits [T][K]; codes uint8 [N][K]; scales float [N] (already the represented
+    values: widen bf16 scales first). kind: "store" -> acc [T][N]; "swiglu" -> silu(acc[:, :N/2]) *
+    acc[:, N/2:]; "shared_scale" -> sigmoid(gate_logit[t]) * acc."""
+    x = (np.ascontiguousarray(x_bf16, dtype=np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+    w = e4m3_table().astype(np.float64)[np.asarray(codes, dtype=np.uint8)]
+    acc = (x.astype(np.float64) @ w.T) * np.asarray(scales, dtype=np.float64)[None, :]
+    if kind == "store":
+        return acc
+    if kind == "swiglu":
+        h = acc.shape[1] // 2
+        g, u = acc[:, :h], acc[:, h:]
+        return g / (1.0 + np.exp(-g)) * u
+    if kind == "shared_scale":
+        return acc / (1.0 + np.exp(-np.asarray(gate_logit, dtype=np.float64)))[:, None]
+    raise ValueError(kind)

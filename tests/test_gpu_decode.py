@@ -368,12 +368,15 @@ def test_forward_moe_decode_with_shared_expert(tokens, aux):
     logits = ws.logits.cpu().numpy()[:tokens * 513].reshape(tokens, 513)
     ids, w = O.topk(logits[:, :512])
     routed = oracle_layer(IQ3_S, IQ3_S, inter, seed, x, ids, w).astype(np.float64)
-    tab = O.e4m3_table().astype(np.float64)
-    acc = (x.astype(np.float64) @ tab[gu_c].T) * synth.bf16_bits_to_f32(synth.to_bf16_bits(gu_s)).astype(np.float64)[None, :]
-    g, u = acc[:, :640], acc[:, 640:]
-    h = synth.bf16_bits_to_f32(synth.to_bf16_bits((g / (1.0 + np.exp(-g)) * u).astype(np.float32))).astype(np.float64)
-    ysh = (h @ tab[dn_c].T) * synth.bf16_bits_to_f32(synth.to_bf16_bits(dn_s)).astype(np.float64)[None, :]
-    ysh = ysh / (1.0 + np.exp(-logits[:, 512].astype(np.float64)))[:, None]
+    widen = lambda sc: synth.bf16_bits_to_f32(synth.to_bf16_bits(sc))  # the row scales as the GPU holds them (bf16)
+    h = O.linear_fp8_a16(xb, gu_c, widen(gu_s), kind="swiglu")
+    hb = synth.to_bf16_bits(h.astype(np.float32))  # h is stored as bf16 between the two projections
+    ysh = O.linear_fp8_a16(hb, dn_c, widen(dn_s), kind="shared_scale", gate_logit=logits[:, 512])
+    # the shared expert on its own (it is small beside the routed sum of these synthetic experts)
+    h_gpu = synth.bf16_bits_to_f32(shared.h[:tokens].view(torch.int16).cpu().numpy().view(np.uint16))
+    assert float(np.mean(h_gpu == synth.bf16_bits_to_f32(hb))) >= 0.99
+    ysh_gpu = shared.y[:tokens].cpu().numpy()
+    assert max(rel_l2(ysh_gpu[t], ysh[t]) for t in range(tokens)) <= TOL
     want = routed + ysh
     got = y.cpu().numpy()
     errs = [rel_l2(got[t], want[t]) for t in range(tokens)]

@@ -194,3 +194,21 @@ def test_port_equals_reference_moe_layer():
     y0 = O.moe_layer(IQ3_S, IQ3_S, 2560, inter, blobs, stride, x, ids, w, threads=2)
     y1 = O.moe_layer(IQ3_S, IQ3_S, 2560, inter, blobs, stride, x, ids, w, threads=3, lib=ref)
     assert np.array_equal(bits(y0), bits(y1))
+
+
+def test_linear_fp8_a16_known_answers():
+    """The fp64 statement of the exact-activation FP8-row projection on values chosen so that every
+    product is an integer: weights E4M3 {1, -2, 0.5, 448}, activations bf16 {2, 4, -8, 0.5}."""
+    t = O.e4m3_table()
+    code = {float(t[c]): c for c in range(256) if np.isfinite(t[c])}
+    codes = np.array([[code[1.0], code[-2.0], code[0.5], code[448.0]],
+                      [code[0.0], code[1.0], code[1.0], code[-1.0]]], dtype=np.uint8)
+    x = np.array([[2.0, 4.0, -8.0, 0.5], [1.0, 1.0, 1.0, 1.0]], dtype=np.float32)
+    xb = (x.view(np.uint32) >> 16).astype(np.uint16)  # exactly representable in bf16
+    acc = O.linear_fp8_a16(xb, codes, np.array([0.5, 2.0]))
+    assert np.array_equal(acc, np.array([[(2 - 8 - 4 + 224) * 0.5, (4 - 8 - 0.5) * 2.0], [447.5 * 0.5, 2.0]]))
+    sw = O.linear_fp8_a16(xb, codes, np.array([0.5, 2.0]), kind="swiglu")
+    g, u = acc[:, :1], acc[:, 1:]
+    assert np.allclose(sw, g / (1 + np.exp(-g)) * u, rtol=1e-15)
+    sh = O.linear_fp8_a16(xb, codes, np.array([0.5, 2.0]), kind="shared_scale", gate_logit=np.array([0.0, 50.0]))
+    assert np.allclose(sh[0], acc[0] * 0.5, rtol=1e-15) and np.allclose(sh[1], acc[1], rtol=1e-15)
