@@ -1208,9 +1208,9 @@ int32_t fb_linear_fp8_decode(const void* x_bf16, int32_t tokens, const uint8_t* 
   const long long want = total / 2 > 0 ? total / 2 : 1;
   int grid = want < sms ? int(want) : sms;
   if (m_tiles <= sms && 4 * m_tiles >= 3 * sms) grid = m_tiles;
-  cudaError_t e = launch_pdl(fp8_decode_kernel, dim3(grid), dim3(kThreads), size_t(kDecSmem), s, map_w, map_p, a);
-  if (e != cudaSuccess) return check_launch("linear_fp8_decode");
-  return check_launch("linear_fp8_decode");
+  const cudaError_t e = launch_pdl(fp8_decode_kernel, dim3(grid), dim3(kThreads), size_t(kDecSmem), s, map_w, map_p, a);
+  const int32_t launched = check_launch("linear_fp8_decode");
+  return launched ? launched : int32_t(e);
 }
 
 }  // extern "C"
