@@ -457,8 +457,7 @@ def run_ours(args, rank, world, local_rank):
         raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        from fngine_b200 import ep
-        return ep.bench_main(args, rank, world, local_rank)
+        return run_ours_multi(args, rank, world, local_rank)
 
     B, Lr = args.batch, args.layers
     layers, routers, xs_host, xs = [], [], [], []
@@ -641,6 +640,267 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks,
     }
     print(json.dumps(line))
+
+
+def ep_prefill_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_tokens=2):
+    """The 48-layer prefill stack of bench.py's single-GPU section, expert-parallel: same seeds, same
+    router bias, experts sharded, tokens data-parallel. Returns the section dict on rank 0 (None on
+    the other ranks). Timed on the device, barrier on both sides, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from fngine_b200 import prefill, synth
+    from fngine_b200.ep_prefill import EpPrefillShard, ep_prefill_layer, topk
+    FMT, INTER = 21, 512
+    shards = [EpPrefillShard(rank, world, 5000 + l, FMT, INTER) for l in range(n_layers)]
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    routers = [(torch.randn(EXPERTS, HIDDEN, generator=g, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(n_layers)]
+    perm = torch.randperm(EXPERTS, generator=g, device="cuda")
+    bias = torch.empty(EXPERTS, device="cuda")
+    bias[perm] = -1.1 * 0.41 * torch.log(torch.arange(1, EXPERTS + 1, device="cuda", dtype=torch.float32))
+    x0 = torch.randn(tokens, HIDDEN, generator=g, device="cuda").to(torch.bfloat16)
+    tl = tokens // world
+    x_local = x0[rank * tl:(rank + 1) * tl].contiguous()
+    ws = prefill.PrefillWorkspace(tokens, INTER)  # a rank may receive a row of every token
+    totals = {"rows_received": 0, "dispatch_bytes": 0, "combine_bytes": 0}
+
+    def step(record=False):
+        x = x_local
+        for l in range(n_layers):
+            logits = (x @ routers[l].t()).float() + bias
+            y, st = ep_prefill_layer(logits, x, shards[l], ws)
+            if record:
+                for k in totals:
+                    totals[k] += st[k]
+            x = (y * torch.rsqrt(y.pow(2).mean(dim=1, keepdim=True) + 1e-12)).to(torch.bfloat16)
+        return x
+
+    # layer 0 alone, for the parity check of the measured workload
+    logits0 = (x_local @ routers[0].t()).float() + bias
+    y_l0, _ = ep_prefill_layer(logits0, x_local, shards[0], ws)
+    e0_, w0_ = topk(logits0)
+    step(record=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        out = step()
+    b.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([a.elapsed_time(b) / steps], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    agg = torch.tensor([float(totals[k]) for k in ("rows_received", "dispatch_bytes", "combine_bytes")], device="cuda")
+    mx = agg.clone()
+    dist.all_reduce(agg)
+    dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    finite = torch.tensor([float(torch.isfinite(out.float()).all().item()), float(ws.status() == 0)], device="cuda")
+    dist.all_reduce(finite, op=dist.ReduceOp.MIN)
+    if rank != 0:
+        return None
+    parity = None
+    try:
+        from oracle import oracle as O
+        ids, w = e0_[:parity_tokens].cpu().numpy(), w0_[:parity_tokens].cpu().numpy()
+        xb = x_local[:parity_tokens].view(torch.int16).cpu().numpy().view(np.uint16)
+        got = y_l0[:parity_tokens].cpu().numpy()
+        errs = []
+        for t_ in range(parity_tokens):
+            want = np.zeros(HIDDEN, dtype=np.float32)
+            for e, wt in sorted(zip(ids[t_].tolist(), w[t_].tolist())):
+                _, ye = O.expert_ffn_bf16(FMT, FMT, HIDDEN, INTER, synth.expert_blob(FMT, FMT, INTER, 5000, int(e)), xb[t_:t_ + 1])
+                want += np.float32(wt) * ye[0]
+            errs.append(float(np.linalg.norm(got[t_] - want) / np.linalg.norm(want)))
+        parity = max(errs)
+    except Exception as exc:  # the oracle is a checker, never a dependency of the measurement
+        parity = "oracle unavailable: %s" % type(exc).__name__
+    flops = float(tokens) * TOPK * 7864320.0 * n_layers
+    peaks_json = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    bf16_peak = float(json.load(open(peaks_json))["bf16_tflops_sustained"]) if os.path.exists(peaks_json) else 1400.0
+    tfl = flops / (ms * 1e-3) / 1e12
+    return {"workload": "%d layers x %d tokens, 512 IQ3_S experts/layer, top-10, Zipf(1.1) router bias; ep%d: %d experts "
+                        "per GPU, %d tokens per GPU" % (n_layers, tokens, world, EXPERTS // world, tl),
+            "tokens_per_s": tokens / (ms * 1e-3), "ms_per_stack": ms, "tflops": tfl, "scaling": "strong",
+            "roofline": {"bound": "tensor", "achieved": tfl / world, "peak": bf16_peak, "unit": "TFLOP/s per GPU",
+                         "frac": tfl / world / bf16_peak,
+                         "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)"},
+            "rows_received_per_stack": {"sum": agg[0].item(), "max_rank": mx[0].item()},
+            "all_to_all_bytes_per_stack": {"dispatch": agg[1].item(), "combine": agg[2].item(),
+                                           "max_rank_dispatch": mx[1].item(), "max_rank_combine": mx[2].item()},
+            "collectives_per_layer": "dense exchange: all-gather of bf16 rows + all-gather of (expert, weight) lists + one "
+                                     "fixed-size fp32 all-to-all, rank-order sum on the owner (NCCL; no host sync)",
+            "parity_layer0_max_rel_l2": parity, "parity_tokens": parity_tokens,
+            "finite_output": bool(finite[0].item()), "device_status_ok": bool(finite[1].item()),
+            "timed_region_includes": "torch router projection + unit-RMS rescale between layers, dispatch gather"}
+
+
+def run_ours_multi(args, rank, world, local_rank):
+    """bench.py for N > 1: strong scaling of the same 16-token decode step over expert-parallel ranks.
+    The timed step exchanges through peer memory inside the kernels (fb_moe_layer_decode_ep_p2p); the
+    same step with NCCL all-to-alls is timed beside it and the two results are compared bit for bit."""
+    import torch
+    import torch.distributed as dist
+    from fngine_b200 import ep, moe, synth
+    from fngine_b200.ep import EpDecodeLayer, PeerExchange, ep_layer_step, layer_decode_ep_p2p, token_range
+
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    B, Lr = args.batch, args.layers
+    lo, hi = token_range(rank, world, B)
+    layers, routers, xs_host, xs = [], [], [], []
+    for l in range(Lr):
+        layers.append(EpDecodeLayer(rank, world, 5000 + l))
+        wr = synth.router_weights(9000 + l)
+        routers.append(torch.from_numpy(wr.view(np.int16)).cuda().view(torch.bfloat16))
+        xh = torch.from_numpy(synth.activations(7000 + l, B)[lo:hi].copy()).pin_memory()
+        xs_host.append(xh)
+        xs.append(xh.cuda())
+    ws = moe.DecodeWorkspace(layers[0].layer)
+    bufs = {"y_partial": torch.empty(B, HIDDEN, dtype=torch.float32, device="cuda"),
+            "y_local": torch.empty(hi - lo, HIDDEN, dtype=torch.float32, device="cuda")}
+    xchg = PeerExchange(rank, world)
+    y_p2p = torch.empty(hi - lo, HIDDEN, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+
+    def step_nccl():
+        for l in range(Lr):
+            ep_layer_step(routers[l], layers[l], xs[l], ws, bufs)
+
+    def step():
+        for l in range(Lr):
+            layer_decode_ep_p2p(routers[l], layers[l], xs[l], ws, xchg, y_p2p)
+
+    # the two exchanges give the same bits (same partial rows, same rank-order sum)
+    same = True
+    for l in range(Lr):
+        y_a = ep_layer_step(routers[l], layers[l], xs[l], ws, bufs).clone()
+        layer_decode_ep_p2p(routers[l], layers[l], xs[l], ws, xchg, y_p2p)
+        torch.cuda.synchronize()
+        same = same and bool(torch.equal(y_a, y_p2p))
+    flag = torch.tensor([1.0 if same else 0.0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    same = bool(flag.item() == 1.0)
+
+    # local distinct experts per layer (for the byte count) and a parity check of layer 0 on rank 0
+    distinct = []
+    for l in range(Lr):
+        ep_layer_step(routers[l], layers[l], xs[l], ws, bufs)
+        torch.cuda.synchronize()
+        distinct.append(ws.work().n_items)
+        if l == 0:
+            layer_decode_ep_p2p(routers[l], layers[l], xs[l], ws, xchg, y_p2p)
+            torch.cuda.synchronize()
+            y0 = y_p2p.clone()
+    local_bytes = torch.tensor([float(sum(d * BLOB + ROUTER_BYTES for d in distinct))], device="cuda")
+    dist.all_reduce(local_bytes)
+    step_bytes = float(local_bytes.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    # the NCCL all-to-all step beside it
+    for _ in range(3):
+        step_nccl()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    n0, n1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0.record()
+    for _ in range(args.steps):
+        step_nccl()
+    n1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    tn = torch.tensor([n0.elapsed_time(n1)], device="cuda")
+    dist.all_reduce(tn, op=dist.ReduceOp.MAX)
+    nccl_ms = float(tn.item())
+
+    # end to end: pinned host rows of the own tokens in, own y rows out, every layer
+    yh = torch.empty(hi - lo, HIDDEN, dtype=torch.float32).pin_memory()
+    xd = torch.empty(hi - lo, HIDDEN, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    dist.barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        for l in range(Lr):
+            xd.copy_(xs_host[l], non_blocking=True)
+            y = layer_decode_ep_p2p(routers[l], layers[l], xd, ws, xchg, y_p2p)
+            yh.copy_(y, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+    f1.record()
+    torch.cuda.synchronize()
+    t2 = torch.tensor([f0.elapsed_time(f1)], device="cuda")
+    dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t2.item())
+
+    clocks = sampler.stop() if rank == 0 else None
+    status = ws.status()
+
+    # parity of the measured workload: layer 0 of this rank's tokens against the CPU oracle
+    parity = None
+    if rank == 0:
+        from oracle import oracle as O
+        x_full = synth.activations(7000, B)
+        wr_bits = synth.router_weights(9000)
+        logits = x_full.astype(np.float32) @ synth.bf16_bits_to_f32(wr_bits).T
+        ids, w = O.topk(np.ascontiguousarray(logits[:, :EXPERTS]))
+        ids, w, xo = ids[lo:hi], w[lo:hi], x_full[lo:hi]
+        used = sorted(set(ids.reshape(-1).tolist()))
+        blobs = np.concatenate([synth.expert_blob(21, 21, 512, 5000, e) for e in used])
+        ids2 = np.vectorize({e: i for i, e in enumerate(used)}.get)(ids).astype(np.int32)
+        want = O.moe_layer(21, 21, HIDDEN, 512, blobs, BLOB, xo, ids2, w, threads=os.cpu_count() or 1, lib=O.ref())
+        got = y0.cpu().numpy()
+        parity = float(max(np.linalg.norm(got[i] - want[i]) / np.linalg.norm(want[i]) for i in range(hi - lo)))
+    dist.barrier()
+    # the 48-layer prefill stack, expert-parallel (the decode layers are released first)
+    pre = None
+    if args.sections == "all" or "prefill" in args.sections.split(","):
+        del layers
+        torch.cuda.empty_cache()
+        pre = ep_prefill_section(rank, world, n_layers=args.prefill_layers)
+    if rank == 0:
+        peak, peak_src = peaks()
+        value = step_bytes * args.steps / (ms * 1e-3) / 1e9
+        ach = value / world  # per GPU, whole layer step (kernels are timed one by one only at N = 1)
+        cfg = workload_config(args, Lr)
+        cfg["parallelism"] = ("ep%d: %d experts per GPU, tokens data-parallel (%d per GPU), dispatch + combine by peer "
+                              "stores over NVLink inside the kernels (no collective call in the step)" % (
+                                  world, EXPERTS // world, B // world))
+        line = {"metric": "iq3s_expert_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+                "config": cfg, "tokens_per_s": B * Lr * args.steps / (ms * 1e-3), "us_per_layer": ms / args.steps / Lr * 1e3,
+                "distinct_local_experts_rank0": distinct,
+                "nccl_all_to_all_step": {"us_per_layer": nccl_ms / args.steps / Lr * 1e3,
+                                         "value": step_bytes * args.steps / (nccl_ms * 1e-3) / 1e9,
+                                         "bitwise_equal_to_peer_exchange": same},
+                "roofline": {"bound": "hbm", "kernel": "whole expert-parallel layer step, per GPU (incl. the exchange)", "achieved": ach, "peak": peak,
+                             "unit": "GB/s", "frac": ach / peak, "peak_source": peak_src, "traffic": None},
+                "e2e": {"value": step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                        "h2d_bytes_per_step": (hi - lo) * HIDDEN * 4 * Lr * world,
+                        "d2h_bytes_per_step": (hi - lo) * HIDDEN * 4 * Lr * world, "ms_per_step": e2e_ms / args.steps},
+                "gpu_launches": args.steps * Lr * 4 * world, "parity_vs_cpu_max_rel_l2": parity,
+                "device_status": status, "clocks": clocks, "prefill_stack": pre,
+                "cpu_baseline": None}
+        print(json.dumps(line))
+    xchg.close()
+    dist.destroy_process_group()
 
 
 def main():

@@ -19,6 +19,28 @@ int sm_count();                          // multiprocessors of the current devic
 
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 
+// One-time set-up that has to be repeated on every device a process drives (function attributes
+// such as the dynamic shared-memory opt-in apply to the current device only). f() runs on the
+// first call per device and again after a failure; its error is returned.
+struct PerDeviceOnce {
+  bool done[64] = {};
+};
+template <class F>
+inline cudaError_t per_device_once(PerDeviceOnce& once, F f) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (once.done[dev]) return cudaSuccess;
+  e = f();
+  if (e == cudaSuccess) once.done[dev] = true;
+  return e;
+}
+template <class K>
+inline cudaError_t opt_in_smem(K kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+}
+
 // ------------------------------------------------------------------------------ device PTX
 // Every wait below is bounded: after kSpinLimit polls it gives up and reports failure, so a lost
 // copy can never hang the GPU. Callers record FB_STATUS_PIPELINE_TIMEOUT and drain.

@@ -1036,10 +1036,13 @@ bool make_map_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t k, in
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
-// CTA pairs of the two-SM kernel that can be resident at once (asked of the occupancy calculator once).
+// CTA pairs of the two-SM kernel that can be resident at once (asked of the occupancy calculator once per device).
 int pair_count() {
-  static int n = [] {
-    cudaFuncSetAttribute(fp8_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem2);
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return sm_count() / 2;
+  if (!cached[dev]) {
+    opt_in_smem(fp8_gemm_pair_kernel<false>, kGemmSmem2);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(sm_count()) & ~1u);
     cfg.blockDim = dim3(kThreads);
@@ -1049,9 +1052,9 @@ int pair_count() {
       cudaGetLastError();
       clusters = sm_count() / 2;
     }
-    return clusters;
-  }();
-  return n;
+    cached[dev] = clusters;
+  }
+  return cached[dev];
 }
 
 }  // namespace
@@ -1093,14 +1096,18 @@ int32_t fb_linear_fp8(const void* x_bf16, int32_t tokens, const uint8_t* w_codes
   uint32_t* status = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a_scales) + align256(size_t(tokens) * 4));
   int32_t st = fb_fp8_quantize_tokens(x_bf16, tokens, k, a_codes, a_scales, stream);
   if (st) return st;
-  static bool once = [] {
-    cudaFuncSetAttribute(fp8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
-    cudaFuncSetAttribute(fp8_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
-    cudaFuncSetAttribute(fp8_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem2);
-    cudaFuncSetAttribute(fp8_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem2);
-    return true;
-  }();
-  (void)once;
+  static PerDeviceOnce once;
+  const cudaError_t attr = per_device_once(once, [] {
+    cudaError_t a = opt_in_smem(fp8_gemm_kernel<false>, kGemmSmem);
+    if (a == cudaSuccess) a = opt_in_smem(fp8_gemm_kernel<true>, kGemmSmem);
+    if (a == cudaSuccess) a = opt_in_smem(fp8_gemm_pair_kernel<false>, kGemmSmem2);
+    if (a == cudaSuccess) a = opt_in_smem(fp8_gemm_pair_kernel<true>, kGemmSmem2);
+    return a;
+  });
+  if (attr != cudaSuccess) {
+    set_error("linear_fp8: shared-memory opt-in: %s", cudaGetErrorString(attr));
+    return int32_t(attr);
+  }
   cudaError_t e = cudaMemsetAsync(status, 0, 4, as_stream(stream));
   if (e != cudaSuccess) return check_launch("linear_fp8: status clear");
   // Two-SM tiles (256 x 256 per CTA pair) once there are enough rows to fill them; the single-CTA
@@ -1169,11 +1176,12 @@ int32_t fb_linear_fp8_decode(const void* x_bf16, int32_t tokens, const uint8_t* 
   int32_t* tickets = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(status) + 256);
   const int n_tickets = (n + 63) / 64;
   float* partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tickets) + align256(size_t(n_tickets) * 4));
-  static bool once = [] {
-    cudaFuncSetAttribute(fp8_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
-    return true;
-  }();
-  (void)once;
+  static PerDeviceOnce once;
+  const cudaError_t attr = per_device_once(once, [] { return opt_in_smem(fp8_decode_kernel, kDecSmem); });
+  if (attr != cudaSuccess) {
+    set_error("linear_fp8_decode: shared-memory opt-in: %s", cudaGetErrorString(attr));
+    return int32_t(attr);
+  }
   cudaStream_t s = as_stream(stream);
   fp8_split_tokens_kernel<<<kDecTok, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x_bf16), tokens, k, pieces,
                                                    tok_scale, tickets, n_tickets, status);

@@ -31,7 +31,7 @@ constexpr int kTT = 2;  // tokens of one work item handled per pass over a stage
 // [8..168) item order, [192..208) finished slices per route row group
 constexpr int kSchedOrderBase = 8;
 constexpr int kEpMaxRanks = FB_EP_MAX_RANKS;
-constexpr uint32_t kPeerSpinLimit = 1u << 20;  // polls of a peer-written flag before giving up (about a second)
+constexpr uint32_t kPeerSpinLimit = 1u << 20;  // default polls of a peer-written flag before giving up (about a second)
 
 // Flag-in-data exchange lines (the low-latency protocol of collective libraries): 16 bytes =
 // {value 0, step, value 1, step}, written by ONE 16-byte store, so a reader that sees the step
@@ -41,10 +41,10 @@ __device__ __forceinline__ void ll_store(uint4* line, float v0, float v1, uint32
                "r"(__float_as_uint(v1)), "r"(step)
                : "memory");
 }
-// Polls the line (a bounded number of times) until both halves carry `step`.
-__device__ __forceinline__ float2 ll_read(const uint4* line, uint32_t step, uint32_t* status) {
+// Polls the line (at most `limit` times) until both halves carry `step`.
+__device__ __forceinline__ float2 ll_read(const uint4* line, uint32_t step, uint32_t* status, uint32_t limit) {
   uint4 v;
-  for (uint32_t i = 0; i < kPeerSpinLimit; ++i) {
+  for (uint32_t i = 0; i < limit; ++i) {
     asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(line)
@@ -356,6 +356,7 @@ struct EpRouteArgs {
   int tpr;               // tokens per rank
   int parity;
   uint32_t step;
+  uint32_t spin_limit;  // polls per awaited line
 };
 
 // Router projection, activation quantization and selection in one launch (the head of the fused
@@ -387,8 +388,9 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
     // Expert-parallel step: this rank's own rows go to every rank as flag-in-data lines (block b
     // serves rank b % R with slice b / R of the rows); readers below poll the lines they need.
     const int R = ep.peers.n_ranks, d = int(blockIdx.x) % R, slice = int(blockIdx.x) / R, n_slices = int(gridDim.x) / R;
-    const int total = ep.tpr * (H / 4), lo = int(int64_t(total) * slice / n_slices),
-              hi = int(int64_t(total) * (slice + 1) / n_slices);
+    // (the host refuses rank counts that do not divide the grid; the clamp keeps a stray block inside the rows)
+    const int total = ep.tpr * (H / 4), lo = min(total, int(int64_t(total) * slice / n_slices)),
+              hi = min(total, int(int64_t(total) * (slice + 1) / n_slices));
     uint4* dst = static_cast<uint4*>(ep.peers.x_all[d]) +
                  (size_t(ep.parity) * kMaxTok + size_t(ep.peers.rank) * ep.tpr) * (H / 2);
     const float4* src = reinterpret_cast<const float4*>(ep.x_local);
@@ -409,7 +411,8 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
     float4 v;
     if constexpr (ep_mode) {
       const uint4* ln = x_lines + (size_t(t) * H + q * kRouteSlice) / 2 + 2 * c;
-      const float2 a = ll_read(ln, ep.step, ws.status), b2 = ll_read(ln + 1, ep.step, ws.status);
+      const float2 a = ll_read(ln, ep.step, ws.status, ep.spin_limit),
+                   b2 = ll_read(ln + 1, ep.step, ws.status, ep.spin_limit);
       v = make_float4(a.x, a.y, b2.x, b2.y);
     } else if constexpr (XBF16) {
       const uint2 u = reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(xv) + size_t(t) * H +
@@ -499,7 +502,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
           const uint4* ln = x_lines + (size_t(t) * H + 256 * b + 8 * lane) / 2;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const float2 f = ll_read(ln + i, ep.step, ws.status);
+            const float2 f = ll_read(ln + i, ep.step, ws.status, ep.spin_limit);
             v[2 * i] = f.x;
             v[2 * i + 1] = f.y;
           }
@@ -520,7 +523,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
         unsigned short dh;
         float xv1;
         if constexpr (ep_mode) {
-          const float2 f = ll_read(x_lines + (size_t(t) * H + 32 * b + lane) / 2, ep.step, ws.status);
+          const float2 f = ll_read(x_lines + (size_t(t) * H + 32 * b + lane) / 2, ep.step, ws.status, ep.spin_limit);
           xv1 = (lane & 1) ? f.y : f.x;
         } else {
           xv1 = load(32 * b + lane);
@@ -1291,7 +1294,8 @@ __global__ void __launch_bounds__(256) sum_ranks_kernel(const float* __restrict_
 // row over the local pairs (slot order) goes straight into its owner's y_parts; threads of tokens
 // this rank owns then read the partial rows of all ranks and add them in rank order.
 __global__ void __launch_bounds__(256) ep_combine_exchange_kernel(fb_moe_decode_workspace ws, fb_ep_peers peers, int tpr,
-                                                                  int parity, uint32_t step, float* __restrict__ y_local) {
+                                                                  int parity, uint32_t step, uint32_t spin_limit,
+                                                                  float* __restrict__ y_local) {
   pdl_launch_dependents();
   pdl_wait_prior();
   const int t = blockIdx.y;
@@ -1311,7 +1315,8 @@ __global__ void __launch_bounds__(256) ep_combine_exchange_kernel(fb_moe_decode_
   const uint4* mine = static_cast<const uint4*>(peers.y_parts[peers.rank]);
   float a0 = 0.0f, a1 = 0.0f;
   for (int s = 0; s < peers.n_ranks; ++s) {
-    const float2 v = ll_read(mine + ((size_t(parity) * kEpMaxRanks + s) * kMaxTok + i) * (H / 2) + c, step, ws.status);
+    const float2 v =
+        ll_read(mine + ((size_t(parity) * kEpMaxRanks + s) * kMaxTok + i) * (H / 2) + c, step, ws.status, spin_limit);
     a0 += v.x;
     a1 += v.y;
   }
@@ -1319,11 +1324,6 @@ __global__ void __launch_bounds__(256) ep_combine_exchange_kernel(fb_moe_decode_
 }
 
 // ------------------------------------------------------------------------------ host side
-template <class K>
-cudaError_t opt_in_smem(K kernel, size_t bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
-}
-
 template <int FMT>
 constexpr size_t gate_up_smem() {
   using C = GateUp<FMT>;
@@ -1346,6 +1346,9 @@ bool layout_ok(const fb_moe_expert_layout* L) {
   if (L->down_format == FB_FMT_IQ3_S) return L->inter % 256 == 0;
   return L->down_format == FB_FMT_IQ4_NL;
 }
+
+// Polls a reader gives a peer-written exchange line before it records FB_STATUS_PIPELINE_TIMEOUT.
+uint32_t g_peer_wait_polls = kPeerSpinLimit;
 
 bool ws_ok(const fb_moe_decode_workspace* ws) {
   return ws && ws->work && ws->xq && ws->h && ws->hq && ws->partial && ws->item_done && ws->sched && ws->status;
@@ -1431,12 +1434,16 @@ int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, c
   if (layout->inter != ws->inter || layout->gate_up_format != ws->gate_up_format ||
       layout->down_format != ws->down_format)
     return invalid("hot_gate_up: workspace was made for a different layout");
-  static bool once = [] {
-    opt_in_smem(gate_up_kernel<FB_FMT_IQ3_S>, gate_up_smem<FB_FMT_IQ3_S>());
-    opt_in_smem(gate_up_kernel<FB_FMT_IQ4_NL>, gate_up_smem<FB_FMT_IQ4_NL>());
-    return true;
-  }();
-  (void)once;
+  static PerDeviceOnce once;
+  const cudaError_t attr = per_device_once(once, [] {
+    cudaError_t a = opt_in_smem(gate_up_kernel<FB_FMT_IQ3_S>, gate_up_smem<FB_FMT_IQ3_S>());
+    if (a == cudaSuccess) a = opt_in_smem(gate_up_kernel<FB_FMT_IQ4_NL>, gate_up_smem<FB_FMT_IQ4_NL>());
+    return a;
+  });
+  if (attr != cudaSuccess) {
+    set_error("hot_gate_up: shared-memory opt-in: %s", cudaGetErrorString(attr));
+    return int32_t(attr);
+  }
   const dim3 grid(sm_count());
   cudaError_t e;
   if (layout->gate_up_format == FB_FMT_IQ3_S)
@@ -1450,13 +1457,17 @@ int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, c
 }
 
 static int32_t launch_down(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, void* stream) {
-  static bool once = [] {
-    opt_in_smem(down_kernel<FB_FMT_IQ3_S, 512>, down_smem<FB_FMT_IQ3_S, 512>());
-    opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 512>, down_smem<FB_FMT_IQ4_NL, 512>());
-    opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 640>, down_smem<FB_FMT_IQ4_NL, 640>());
-    return true;
-  }();
-  (void)once;
+  static PerDeviceOnce once;
+  const cudaError_t attr = per_device_once(once, [] {
+    cudaError_t a = opt_in_smem(down_kernel<FB_FMT_IQ3_S, 512>, down_smem<FB_FMT_IQ3_S, 512>());
+    if (a == cudaSuccess) a = opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 512>, down_smem<FB_FMT_IQ4_NL, 512>());
+    if (a == cudaSuccess) a = opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 640>, down_smem<FB_FMT_IQ4_NL, 640>());
+    return a;
+  });
+  if (attr != cudaSuccess) {
+    set_error("hot_down: shared-memory opt-in: %s", cudaGetErrorString(attr));
+    return int32_t(attr);
+  }
   const dim3 grid(sm_count());
   cudaError_t e;
   if (layout->down_format == FB_FMT_IQ3_S)
@@ -1503,7 +1514,11 @@ static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_
   EpRouteArgs era{};
   if (ep) era = *ep;
   // Four launches: route (router projection + activation quantization + selection), gate/up, down,
-  // combine. Same arithmetic, in the same order, as the five separate entry points.
+  // combine. Gate/up, down and combine are the separate entry points themselves. The route kernel
+  // sums a logit as eight K slices of 320 added in slice order, where fb_router_logits sums 80
+  // values per lane and then the lanes: the two projections agree to fp32 rounding (a few ulp), not
+  // bit for bit, so a near-tie between the tenth and eleventh expert may resolve differently. Only
+  // rows 0..511 of logits_scratch are written: row 512 (the shared-expert gate) is not produced here.
   if (!router_w_bf16 || !x || (!y_out && with_combine) || !logits_scratch || !layout_ok(layout) || !ws_ok(ws) ||
       tokens < 1 || tokens > kMaxTok)
     return invalid("layer_decode: bad arguments (tokens must be 1..16, logits scratch [tokens][513] required)");
@@ -1551,6 +1566,9 @@ int32_t fb_moe_layer_decode_ep_p2p(const void* router_w_bf16, const fb_moe_exper
       peers->rank < 0 || peers->rank >= peers->n_ranks || tokens < peers->n_ranks || tokens > kMaxTok ||
       tokens % peers->n_ranks || step == 0)
     return invalid("layer_decode_ep_p2p: bad arguments (tokens a multiple of the rank count, at most 16; step >= 1)");
+  // the route kernel hands its blocks out to the ranks in equal shares
+  if ((kRouteGroups * kRouteSplits) % peers->n_ranks)
+    return invalid("layer_decode_ep_p2p: the rank count must be 1, 2, 4 or 8");
   for (int d = 0; d < peers->n_ranks; ++d)
     if (!peers->x_all[d] || !peers->y_parts[d])
       return invalid("layer_decode_ep_p2p: a peer buffer address is missing");
@@ -1564,12 +1582,13 @@ int32_t fb_moe_layer_decode_ep_p2p(const void* router_w_bf16, const fb_moe_exper
   era.tpr = tpr;
   era.parity = parity;
   era.step = step;
+  era.spin_limit = g_peer_wait_polls;
   // (the route kernel reads every x row through the exchange lines; x_local only satisfies the argument check)
   int32_t st = layer_decode_impl(router_w_bf16, layout, slot_of, true, x_local, FB_DT_F32, tokens, ws, logits_scratch,
                                  nullptr, stream, &era);
   if (st) return st;
   const cudaError_t e = launch_pdl(ep_combine_exchange_kernel, dim3(H / 512, tokens), dim3(256), 0, s, *ws, *peers, tpr,
-                                   parity, step, y_local);
+                                   parity, step, g_peer_wait_polls, y_local);
   if (e != cudaSuccess) return check_launch("layer_decode_ep_p2p: combine");
   return check_launch("layer_decode_ep_p2p");
 }
@@ -1632,6 +1651,8 @@ int32_t fb_ep_exchange_close(void* x_all, void* y_parts, int32_t own) {
   return st;
 }
 
+void fb_ep_set_wait_limit(uint32_t polls) { g_peer_wait_polls = polls ? polls : kPeerSpinLimit; }
+
 size_t fb_ep_exchange_bytes(int32_t which) { return which == 0 ? kEpBytes[0] : which == 1 ? kEpBytes[1] : 0; }
 
 int32_t fb_ep_sum_ranks(const float* parts, int32_t n_ranks, int32_t rows, float* y, void* stream) {
@@ -1677,6 +1698,8 @@ int32_t fb_moe_layer_decode_host(const void* router_w_bf16, const fb_moe_expert_
 // call outside any stream capture). All calls on a device share the array and it keeps the last
 // call's contents: the entry point clears the one word that must start at zero, and two calls
 // that overlap on the same GPU (different streams) race on it - serialize them.
+// fb_moe_layer_decode_static_status reads the status word of the last call back to the host (a
+// stream-ordered copy out of the array and a wait on that stream; it allocates nothing either).
 namespace {
 constexpr size_t kStaticWorkspaceBytes = 2304 * 1024;  // >= fb_moe_decode_workspace_bytes(640), checked at set-up
 constexpr size_t kStaticLogitsBytes = size_t(FB_DECODE_MAX_TOKENS) * FB_ROUTER_ROWS * 4;
@@ -1686,6 +1709,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 struct StaticScratch {
   bool ready = false;
   unsigned char* base = nullptr;
+  uint32_t* status = nullptr;  // the workspace's status word inside the array (set by the first layer call)
 };
 StaticScratch g_static[64];
 }  // namespace
@@ -1717,15 +1741,32 @@ int32_t fb_moe_layer_decode_static(const void* router_w_bf16, const fb_moe_exper
   fb_moe_decode_workspace ws;
   int32_t st = fb_moe_decode_workspace_make(sc.base, layout, &ws);
   if (st) return st;
+  sc.status = ws.status;
   float* logits = reinterpret_cast<float*>(sc.base + kStaticWorkspaceBytes);
-  // the sticky status word and the route counter are the only state a call inherits
+  // the sticky status word and the scheduler words (tile counters, route tickets) are the only state a call inherits
   e = cudaMemsetAsync(ws.status, 0, sizeof(uint32_t), as_stream(stream));
-  if (e == cudaSuccess) e = cudaMemsetAsync(ws.sched, 0, kSchedOrderBase * sizeof(int32_t), as_stream(stream));
+  if (e == cudaSuccess) e = cudaMemsetAsync(ws.sched, 0, kSchedInts * sizeof(int32_t), as_stream(stream));
   if (e != cudaSuccess) {
     set_error("layer_decode_static: clearing scratch state: %s", cudaGetErrorString(e));
     return int32_t(e);
   }
   return fb_moe_layer_decode(router_w_bf16, layout, x, x_dtype, tokens, &ws, logits, y_out, stream);
+}
+
+int32_t fb_moe_layer_decode_static_status(uint32_t* status_host, void* stream) {
+  if (!status_host) return invalid("layer_decode_static_status: status_host is NULL");
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64 || !g_static[dev].status)
+    return invalid("layer_decode_static_status: fb_moe_layer_decode_static has not run on this device");
+  e = cudaMemcpyAsync(status_host, g_static[dev].status, sizeof(uint32_t), cudaMemcpyDeviceToHost, as_stream(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(as_stream(stream));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error("layer_decode_static_status: %s", cudaGetErrorString(e));
+    return int32_t(e);
+  }
+  return 0;
 }
 
 }  // extern "C"

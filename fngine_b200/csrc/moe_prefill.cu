@@ -1033,12 +1033,16 @@ int32_t fb_moe_grouped_gate_up(const fb_moe_expert_layout* layout, const uint8_t
   if (!pf_layout_ok(layout, expert_blob) || !x_bf16 || !pf_ws_ok(ws, tokens) || layout->inter != ws->inter ||
       (reinterpret_cast<uintptr_t>(x_bf16) & 15))
     return invalid("grouped_gate_up: bad arguments");
-  static bool once = [] {
-    cudaFuncSetAttribute(grouped_gate_up_kernel<FB_FMT_IQ3_S>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGuSmem);
-    cudaFuncSetAttribute(grouped_gate_up_kernel<FB_FMT_IQ4_NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGuSmem);
-    return true;
-  }();
-  (void)once;
+  static PerDeviceOnce once;
+  const cudaError_t attr = per_device_once(once, [] {
+    cudaError_t a = opt_in_smem(grouped_gate_up_kernel<FB_FMT_IQ3_S>, kGuSmem);
+    if (a == cudaSuccess) a = opt_in_smem(grouped_gate_up_kernel<FB_FMT_IQ4_NL>, kGuSmem);
+    return a;
+  });
+  if (attr != cudaSuccess) {
+    set_error("grouped_gate_up: shared-memory opt-in: %s", cudaGetErrorString(attr));
+    return int32_t(attr);
+  }
   const int grid = sm_count();
   const auto* xb = static_cast<const __nv_bfloat16*>(x_bf16);
   auto* hb = static_cast<__nv_bfloat16*>(ws->h);
@@ -1072,12 +1076,16 @@ int32_t fb_moe_grouped_down(const fb_moe_expert_layout* layout, const uint8_t* c
     set_error("grouped_down: cuTensorMapEncodeTiled failed");
     return int32_t(cudaErrorInvalidValue);
   }
-  static bool once = [] {
-    cudaFuncSetAttribute(grouped_down_kernel<FB_FMT_IQ3_S>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDnSmem);
-    cudaFuncSetAttribute(grouped_down_kernel<FB_FMT_IQ4_NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDnSmem);
-    return true;
-  }();
-  (void)once;
+  static PerDeviceOnce once;
+  const cudaError_t attr = per_device_once(once, [] {
+    cudaError_t a = opt_in_smem(grouped_down_kernel<FB_FMT_IQ3_S>, kDnSmem);
+    if (a == cudaSuccess) a = opt_in_smem(grouped_down_kernel<FB_FMT_IQ4_NL>, kDnSmem);
+    return a;
+  });
+  if (attr != cudaSuccess) {
+    set_error("grouped_down: shared-memory opt-in: %s", cudaGetErrorString(attr));
+    return int32_t(attr);
+  }
   const int grid = sm_count();
   const auto* un = static_cast<const int4*>(ws->units_down);
   if (layout->down_format == FB_FMT_IQ3_S)

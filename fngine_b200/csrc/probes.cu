@@ -133,15 +133,19 @@ __host__ __device__ __forceinline__ uint64_t splitmix_at(uint64_t seed, uint64_t
 }
 
 // Block b takes ceil(block_bytes/8) stream words starting at b * words; bytes 2.. of the block are
-// the stream bytes 2.., bytes 0-1 are d_table[word0 & 0xFFFF].
+// the stream bytes 2.., bytes 0-1 are d_table[word0 & 0xFFFF]. The blocks are written in chunks of
+// `chunk_blocks` consecutive blocks, chunk c starting at dst + c * chunk_stride (one chunk per
+// expert when a whole slot array is filled by one launch).
 template <int BLOCK_BYTES>
 __global__ void __launch_bounds__(256) synth_fill_kernel(uint8_t* __restrict__ dst, int64_t n_blocks,
                                                          int64_t first_block, uint64_t seed,
-                                                         const uint16_t* __restrict__ d_table) {
+                                                         const uint16_t* __restrict__ d_table, int64_t chunk_blocks,
+                                                         int64_t chunk_stride) {
   constexpr int kWords = (BLOCK_BYTES + 7) / 8;
   for (int64_t b = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; b < n_blocks; b += int64_t(gridDim.x) * blockDim.x) {
     const uint64_t g = uint64_t(first_block + b);
-    uint8_t* blk = dst + b * BLOCK_BYTES;
+    const int64_t chunk = b / chunk_blocks;
+    uint8_t* blk = dst + chunk * chunk_stride + (b - chunk * chunk_blocks) * BLOCK_BYTES;
     uint64_t w0 = 0;
 #pragma unroll
     for (int i = 0; i < kWords; ++i) {
@@ -173,11 +177,12 @@ int32_t fb_dequant_rows(int32_t format, const uint8_t* rows, int64_t row_bytes, 
   const int grid = (nrows + 7) / 8 < 1184 ? (nrows + 7) / 8 : 1184;
   if (format == FB_FMT_IQ3_S) {
     const size_t smem = kGridRepBytes + 64;
-    static bool once = [] {
-      cudaFuncSetAttribute(dequant_iq3s_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGridRepBytes + 64);
-      return true;
-    }();
-    (void)once;
+    static PerDeviceOnce once;
+    const cudaError_t attr = per_device_once(once, [] { return opt_in_smem(dequant_iq3s_kernel, kGridRepBytes + 64); });
+    if (attr != cudaSuccess) {
+      set_error("dequant_rows: shared-memory opt-in: %s", cudaGetErrorString(attr));
+      return int32_t(attr);
+    }
     dequant_iq3s_kernel<<<grid, 256, smem, as_stream(stream)>>>(rows, row_bytes, nrows, k, out);
   } else {
     dequant_iq4nl_kernel<<<grid, 256, 0, as_stream(stream)>>>(rows, row_bytes, nrows, k, out);
@@ -203,17 +208,33 @@ int32_t fb_quantize_act(int32_t act_format, const void* x, int32_t x_dtype, int3
   return check_launch("quantize_act");
 }
 
+static int32_t synth_fill(int32_t format, uint8_t* dst, int64_t n_blocks, int64_t first_block, uint64_t seed,
+                          const uint16_t* d_table, int64_t chunk_blocks, int64_t chunk_stride, void* stream) {
+  const int grid = int((n_blocks + 255) / 256 < 4736 ? (n_blocks + 255) / 256 : 4736);
+  if (format == FB_FMT_IQ3_S)
+    synth_fill_kernel<110><<<grid, 256, 0, as_stream(stream)>>>(dst, n_blocks, first_block, seed, d_table, chunk_blocks,
+                                                                chunk_stride);
+  else if (format == FB_FMT_IQ4_NL)
+    synth_fill_kernel<18><<<grid, 256, 0, as_stream(stream)>>>(dst, n_blocks, first_block, seed, d_table, chunk_blocks,
+                                                               chunk_stride);
+  else
+    return invalid("synth_fill: unsupported format");
+  return check_launch("synth_fill");
+}
+
 int32_t fb_synth_fill_blocks(int32_t format, uint8_t* dst, int64_t n_blocks, int64_t first_block, uint64_t seed,
                              const uint16_t* d_table, void* stream) {
   if (!dst || !d_table || n_blocks <= 0) return invalid("synth_fill_blocks: bad arguments");
-  const int grid = int((n_blocks + 255) / 256 < 4736 ? (n_blocks + 255) / 256 : 4736);
-  if (format == FB_FMT_IQ3_S)
-    synth_fill_kernel<110><<<grid, 256, 0, as_stream(stream)>>>(dst, n_blocks, first_block, seed, d_table);
-  else if (format == FB_FMT_IQ4_NL)
-    synth_fill_kernel<18><<<grid, 256, 0, as_stream(stream)>>>(dst, n_blocks, first_block, seed, d_table);
-  else
-    return invalid("synth_fill_blocks: unsupported format");
-  return check_launch("synth_fill_blocks");
+  return synth_fill(format, dst, n_blocks, first_block, seed, d_table, n_blocks, 0, stream);
+}
+
+int32_t fb_synth_fill_experts(int32_t format, uint8_t* dst, int64_t expert_stride, int32_t n_experts,
+                              int32_t first_expert, int64_t blocks_per_expert, uint64_t seed, const uint16_t* d_table,
+                              void* stream) {
+  if (!dst || !d_table || n_experts <= 0 || first_expert < 0 || blocks_per_expert <= 0 || expert_stride <= 0)
+    return invalid("synth_fill_experts: bad arguments");
+  return synth_fill(format, dst, int64_t(n_experts) * blocks_per_expert, int64_t(first_expert) * blocks_per_expert, seed,
+                    d_table, blocks_per_expert, expert_stride, stream);
 }
 
 }  // extern "C"

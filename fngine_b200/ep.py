@@ -21,10 +21,6 @@ NVLink and poll their own memory, so a step makes no collective call; both give 
 The split / ordering logic in this file is backend-agnostic and is exercised on CPU ranks (gloo) by
 tests/test_ep_gloo.py.
 """
-import json
-import os
-import time
-
 import numpy as np
 
 EXPERTS = 512
@@ -94,24 +90,11 @@ class EpDecodeLayer:
 
     def __init__(self, rank, world, seed, fmt=21, inter=512):
         import torch
-        from . import moe, synth
-        from . import lib as L
+        from . import moe
         self.rank, self.world = rank, world
         per = experts_per_rank(world)
-        lib = L.load()
-        stride = lib.fb_moe_blob_bytes(fmt, fmt, inter)
-        buf = torch.empty(per * stride, dtype=torch.uint8, device="cuda")
-        table = torch.from_numpy(synth.d_table(fmt).view(np.int16)).cuda()
-        gu_bytes = 2 * inter * lib.fb_moe_row_bytes(fmt, HIDDEN)
-        nb_gu = gu_bytes // synth.BLOCK_BYTES[fmt]
-        nb_dn = (stride - gu_bytes) // synth.BLOCK_BYTES[fmt]
-        stream = torch.cuda.current_stream().cuda_stream
-        for s in range(per):  # same bytes the single-GPU layer holds for global expert e
-            e = rank * per + s
-            base = buf.data_ptr() + s * stride
-            L.check(lib.fb_synth_fill_blocks(fmt, base, nb_gu, e * nb_gu, seed, table.data_ptr(), stream))
-            L.check(lib.fb_synth_fill_blocks(fmt, base + gu_bytes, nb_dn, e * nb_dn, seed ^ 0xD0, table.data_ptr(), stream))
-        self.layer = moe.ExpertLayer(buf, fmt, fmt, inter)
+        # the same bytes the single-GPU layer holds for global experts rank * per .. rank * per + per - 1
+        self.layer = moe.synth_layer(fmt, fmt, inter, per, seed, first_expert=rank * per)
         self.slot_of = torch.from_numpy(local_slot_map(rank, world)).cuda()
 
 
@@ -193,172 +176,3 @@ def ep_layer_step(router, ep_layer, x_local, ws, bufs):
     parts = combine_exchange(bufs["y_partial"], world)
     sum_ranks(parts.contiguous(), bufs["y_local"])
     return bufs["y_local"]
-
-
-def bench_main(args, rank, world, local_rank):
-    """bench.py for N > 1: strong scaling of the same 16-token decode step over expert-parallel ranks.
-    The timed step exchanges through peer memory inside the kernels (fb_moe_layer_decode_ep_p2p); the
-    same step with NCCL all-to-alls is timed beside it and the two results are compared bit for bit."""
-    import torch
-    import torch.distributed as dist
-    from . import moe, synth
-    from bench import BLOB, ROUTER_BYTES, ClockSampler, peaks, workload_config  # bench.py is the caller
-
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    B, Lr = args.batch, args.layers
-    lo, hi = token_range(rank, world, B)
-    layers, routers, xs_host, xs = [], [], [], []
-    for l in range(Lr):
-        layers.append(EpDecodeLayer(rank, world, 5000 + l))
-        wr = synth.router_weights(9000 + l)
-        routers.append(torch.from_numpy(wr.view(np.int16)).cuda().view(torch.bfloat16))
-        xh = torch.from_numpy(synth.activations(7000 + l, B)[lo:hi].copy()).pin_memory()
-        xs_host.append(xh)
-        xs.append(xh.cuda())
-    ws = moe.DecodeWorkspace(layers[0].layer)
-    bufs = {"y_partial": torch.empty(B, HIDDEN, dtype=torch.float32, device="cuda"),
-            "y_local": torch.empty(hi - lo, HIDDEN, dtype=torch.float32, device="cuda")}
-    xchg = PeerExchange(rank, world)
-    y_p2p = torch.empty(hi - lo, HIDDEN, dtype=torch.float32, device="cuda")
-    torch.cuda.synchronize()
-
-    def step_nccl():
-        for l in range(Lr):
-            ep_layer_step(routers[l], layers[l], xs[l], ws, bufs)
-
-    def step():
-        for l in range(Lr):
-            layer_decode_ep_p2p(routers[l], layers[l], xs[l], ws, xchg, y_p2p)
-
-    # the two exchanges give the same bits (same partial rows, same rank-order sum)
-    same = True
-    for l in range(Lr):
-        y_a = ep_layer_step(routers[l], layers[l], xs[l], ws, bufs).clone()
-        layer_decode_ep_p2p(routers[l], layers[l], xs[l], ws, xchg, y_p2p)
-        torch.cuda.synchronize()
-        same = same and bool(torch.equal(y_a, y_p2p))
-    flag = torch.tensor([1.0 if same else 0.0], device="cuda")
-    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    same = bool(flag.item() == 1.0)
-
-    # local distinct experts per layer (for the byte count) and a parity check of layer 0 on rank 0
-    distinct = []
-    for l in range(Lr):
-        ep_layer_step(routers[l], layers[l], xs[l], ws, bufs)
-        torch.cuda.synchronize()
-        distinct.append(ws.work().n_items)
-        if l == 0:
-            layer_decode_ep_p2p(routers[l], layers[l], xs[l], ws, xchg, y_p2p)
-            torch.cuda.synchronize()
-            y0 = y_p2p.clone()
-    local_bytes = torch.tensor([float(sum(d * BLOB + ROUTER_BYTES for d in distinct))], device="cuda")
-    dist.all_reduce(local_bytes)
-    step_bytes = float(local_bytes.item())
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    # the NCCL all-to-all step beside it
-    for _ in range(3):
-        step_nccl()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    n0, n1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    n0.record()
-    for _ in range(args.steps):
-        step_nccl()
-    n1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    tn = torch.tensor([n0.elapsed_time(n1)], device="cuda")
-    dist.all_reduce(tn, op=dist.ReduceOp.MAX)
-    nccl_ms = float(tn.item())
-
-    # end to end: pinned host rows of the own tokens in, own y rows out, every layer
-    yh = torch.empty(hi - lo, HIDDEN, dtype=torch.float32).pin_memory()
-    xd = torch.empty(hi - lo, HIDDEN, dtype=torch.float32, device="cuda")
-    torch.cuda.synchronize()
-    dist.barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    for _ in range(args.steps):
-        for l in range(Lr):
-            xd.copy_(xs_host[l], non_blocking=True)
-            y = layer_decode_ep_p2p(routers[l], layers[l], xd, ws, xchg, y_p2p)
-            yh.copy_(y, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-    f1.record()
-    torch.cuda.synchronize()
-    t2 = torch.tensor([f0.elapsed_time(f1)], device="cuda")
-    dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t2.item())
-
-    clocks = sampler.stop() if rank == 0 else None
-    status = ws.status()
-
-    # parity of the measured workload: layer 0 of this rank's tokens against the CPU oracle
-    parity = None
-    if rank == 0:
-        from oracle import oracle as O
-        x_full = synth.activations(7000, B)
-        wr_bits = synth.router_weights(9000)
-        logits = x_full.astype(np.float32) @ synth.bf16_bits_to_f32(wr_bits).T
-        ids, w = O.topk(np.ascontiguousarray(logits[:, :EXPERTS]))
-        ids, w, xo = ids[lo:hi], w[lo:hi], x_full[lo:hi]
-        used = sorted(set(ids.reshape(-1).tolist()))
-        blobs = np.concatenate([synth.expert_blob(21, 21, 512, 5000, e) for e in used])
-        ids2 = np.vectorize({e: i for i, e in enumerate(used)}.get)(ids).astype(np.int32)
-        want = O.moe_layer(21, 21, HIDDEN, 512, blobs, BLOB, xo, ids2, w, threads=os.cpu_count() or 1, lib=O.ref())
-        got = y0.cpu().numpy()
-        parity = float(max(np.linalg.norm(got[i] - want[i]) / np.linalg.norm(want[i]) for i in range(hi - lo)))
-    dist.barrier()
-    # the 48-layer prefill stack, expert-parallel (the decode layers are released first)
-    pre = None
-    if args.sections == "all" or "prefill" in args.sections.split(","):
-        from . import ep_prefill
-        del layers
-        torch.cuda.empty_cache()
-        pre = ep_prefill.bench_section(rank, world, n_layers=args.prefill_layers)
-    if rank == 0:
-        peak, peak_src = peaks()
-        value = step_bytes * args.steps / (ms * 1e-3) / 1e9
-        ach = value / world  # per GPU, whole layer step (kernels are timed one by one only at N = 1)
-        cfg = workload_config(args, Lr)
-        cfg["parallelism"] = ("ep%d: %d experts per GPU, tokens data-parallel (%d per GPU), dispatch + combine by peer "
-                              "stores over NVLink inside the kernels (no collective call in the step)" % (
-                                  world, EXPERTS // world, B // world))
-        line = {"metric": "iq3s_expert_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
-                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-                "config": cfg, "tokens_per_s": B * Lr * args.steps / (ms * 1e-3), "us_per_layer": ms / args.steps / Lr * 1e3,
-                "distinct_local_experts_rank0": distinct,
-                "nccl_all_to_all_step": {"us_per_layer": nccl_ms / args.steps / Lr * 1e3,
-                                         "value": step_bytes * args.steps / (nccl_ms * 1e-3) / 1e9,
-                                         "bitwise_equal_to_peer_exchange": same},
-                "roofline": {"bound": "hbm", "kernel": "whole expert-parallel layer step, per GPU (incl. the exchange)", "achieved": ach, "peak": peak,
-                             "unit": "GB/s", "frac": ach / peak, "peak_source": peak_src, "traffic": None},
-                "e2e": {"value": step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-                        "h2d_bytes_per_step": (hi - lo) * HIDDEN * 4 * Lr * world,
-                        "d2h_bytes_per_step": (hi - lo) * HIDDEN * 4 * Lr * world, "ms_per_step": e2e_ms / args.steps},
-                "gpu_launches": args.steps * Lr * 4 * world, "parity_vs_cpu_max_rel_l2": parity,
-                "device_status": status, "clocks": clocks, "prefill_stack": pre,
-                "cpu_baseline": None}
-        print(json.dumps(line))
-    xchg.close()
-    dist.destroy_process_group()

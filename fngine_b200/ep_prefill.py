@@ -240,96 +240,3 @@ def ep_prefill_layer(logits_local, x_local, shard, ws, group=None, mode="dense",
     if mode == "dense":
         return ep_layer_dense(x_local, e, w, shard.rank, shard.world, compute, sum_ranks, group, chunks)
     return ep_layer_generic(x_local, e, w, shard.rank, shard.world, compute, scatter_sum, group)
-
-
-def bench_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_tokens=2):
-    """The 48-layer prefill stack of bench.py's single-GPU section, expert-parallel: same seeds, same
-    router bias, experts sharded, tokens data-parallel. Returns the section dict on rank 0 (None on
-    the other ranks). Timed on the device, barrier on both sides, max over ranks."""
-    import json
-    import os
-    import torch.distributed as dist
-    from . import prefill, synth
-    FMT, INTER = 21, 512
-    shards = [EpPrefillShard(rank, world, 5000 + l, FMT, INTER) for l in range(n_layers)]
-    g = torch.Generator(device="cuda").manual_seed(1234)
-    routers = [(torch.randn(EXPERTS, HIDDEN, generator=g, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(n_layers)]
-    perm = torch.randperm(EXPERTS, generator=g, device="cuda")
-    bias = torch.empty(EXPERTS, device="cuda")
-    bias[perm] = -1.1 * 0.41 * torch.log(torch.arange(1, EXPERTS + 1, device="cuda", dtype=torch.float32))
-    x0 = torch.randn(tokens, HIDDEN, generator=g, device="cuda").to(torch.bfloat16)
-    tl = tokens // world
-    x_local = x0[rank * tl:(rank + 1) * tl].contiguous()
-    ws = prefill.PrefillWorkspace(tokens, INTER)  # a rank may receive a row of every token
-    totals = {"rows_received": 0, "dispatch_bytes": 0, "combine_bytes": 0}
-
-    def step(record=False):
-        x = x_local
-        for l in range(n_layers):
-            logits = (x @ routers[l].t()).float() + bias
-            y, st = ep_prefill_layer(logits, x, shards[l], ws)
-            if record:
-                for k in totals:
-                    totals[k] += st[k]
-            x = (y * torch.rsqrt(y.pow(2).mean(dim=1, keepdim=True) + 1e-12)).to(torch.bfloat16)
-        return x
-
-    # layer 0 alone, for the parity check of the measured workload
-    logits0 = (x_local @ routers[0].t()).float() + bias
-    y_l0, _ = ep_prefill_layer(logits0, x_local, shards[0], ws)
-    e0_, w0_ = topk(logits0)
-    step(record=True)
-    torch.cuda.synchronize()
-    dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(steps):
-        out = step()
-    b.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    t = torch.tensor([a.elapsed_time(b) / steps], device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    agg = torch.tensor([float(totals[k]) for k in ("rows_received", "dispatch_bytes", "combine_bytes")], device="cuda")
-    mx = agg.clone()
-    dist.all_reduce(agg)
-    dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-    finite = torch.tensor([float(torch.isfinite(out.float()).all().item()), float(ws.status() == 0)], device="cuda")
-    dist.all_reduce(finite, op=dist.ReduceOp.MIN)
-    if rank != 0:
-        return None
-    parity = None
-    try:
-        from oracle import oracle as O
-        ids, w = e0_[:parity_tokens].cpu().numpy(), w0_[:parity_tokens].cpu().numpy()
-        xb = x_local[:parity_tokens].view(torch.int16).cpu().numpy().view(np.uint16)
-        got = y_l0[:parity_tokens].cpu().numpy()
-        errs = []
-        for t_ in range(parity_tokens):
-            want = np.zeros(HIDDEN, dtype=np.float32)
-            for e, wt in sorted(zip(ids[t_].tolist(), w[t_].tolist())):
-                _, ye = O.expert_ffn_bf16(FMT, FMT, HIDDEN, INTER, synth.expert_blob(FMT, FMT, INTER, 5000, int(e)), xb[t_:t_ + 1])
-                want += np.float32(wt) * ye[0]
-            errs.append(float(np.linalg.norm(got[t_] - want) / np.linalg.norm(want)))
-        parity = max(errs)
-    except Exception as exc:  # the oracle is a checker, never a dependency of the measurement
-        parity = "oracle unavailable: %s" % type(exc).__name__
-    flops = float(tokens) * TOPK * 7864320.0 * n_layers
-    peaks_json = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
-    bf16_peak = float(json.load(open(peaks_json))["bf16_tflops_sustained"]) if os.path.exists(peaks_json) else 1400.0
-    tfl = flops / (ms * 1e-3) / 1e12
-    return {"workload": "%d layers x %d tokens, 512 IQ3_S experts/layer, top-10, Zipf(1.1) router bias; ep%d: %d experts "
-                        "per GPU, %d tokens per GPU" % (n_layers, tokens, world, EXPERTS // world, tl),
-            "tokens_per_s": tokens / (ms * 1e-3), "ms_per_stack": ms, "tflops": tfl, "scaling": "strong",
-            "roofline": {"bound": "tensor", "achieved": tfl / world, "peak": bf16_peak, "unit": "TFLOP/s per GPU",
-                         "frac": tfl / world / bf16_peak,
-                         "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)"},
-            "rows_received_per_stack": {"sum": agg[0].item(), "max_rank": mx[0].item()},
-            "all_to_all_bytes_per_stack": {"dispatch": agg[1].item(), "combine": agg[2].item(),
-                                           "max_rank_dispatch": mx[1].item(), "max_rank_combine": mx[2].item()},
-            "collectives_per_layer": "dense exchange: all-gather of bf16 rows + all-gather of (expert, weight) lists + one "
-                                     "fixed-size fp32 all-to-all, rank-order sum on the owner (NCCL; no host sync)",
-            "parity_layer0_max_rel_l2": parity, "parity_tokens": parity_tokens,
-            "finite_output": bool(finite[0].item()), "device_status_ok": bool(finite[1].item()),
-            "timed_region_includes": "torch router projection + unit-RMS rescale between layers, dispatch gather"}

@@ -15,6 +15,7 @@ ACT_Q8_K, ACT_Q8_0 = 0, 1
 HIDDEN, EXPERTS, TOPK, ROUTER_ROWS = 2560, 512, 10, 513
 DECODE_MAX_TOKENS, DECODE_MAX_PAIRS = 16, 160
 XQ_STRIDE, HQ_STRIDE = 2880, 720
+STATUS_OK, STATUS_PIPELINE_TIMEOUT, STATUS_BAD_WORK = 0, 1, 2
 
 
 class FbError(RuntimeError):
@@ -115,6 +116,8 @@ _SIGNATURES = {
     "fb_moe_route_ep": (_I32, [_P, _P, _I32, _I32, _I32, C.POINTER(PrefillWorkspace), _P]),
     "fb_ep_scatter_sum": (_I32, [_P, _P, _I32, _I32, _P, _P]),
     "fb_moe_layer_decode_static": (_I32, [_P, C.POINTER(ExpertLayout), _P, _I32, _I32, _P, _P]),
+    "fb_moe_layer_decode_static_status": (_I32, [_P, _P]),
+    "fb_ep_set_wait_limit": (None, [C.c_uint32]),
     "fb_linear_fp8_workspace_bytes": (C.c_size_t, [_I32, _I32, _I32]),
     "fb_linear_fp8": (_I32, [_P, _I32, _P, _P, _I32, _I32, _I32, _P, _P, C.c_size_t, _P]),
     "fb_fp8_quantize_tokens": (_I32, [_P, _I32, _I32, _P, _P, _P]),
@@ -123,6 +126,7 @@ _SIGNATURES = {
     "fb_dequant_rows": (_I32, [_I32, _P, _I64, _I32, _I32, _P, _P]),
     "fb_quantize_act": (_I32, [_I32, _P, _I32, _I32, _I32, _P, _P]),
     "fb_synth_fill_blocks": (_I32, [_I32, _P, _I64, _I64, C.c_uint64, _P, _P]),
+    "fb_synth_fill_experts": (_I32, [_I32, _P, _I64, _I32, _I32, _I64, C.c_uint64, _P, _P]),
 }
 
 _lib = None

@@ -53,9 +53,9 @@ class ExpertLayer:
                            self.layout.blob_stride)
 
 
-def synth_layer(gate_up_format, down_format, inter, n_experts, seed, device="cuda"):
+def synth_layer(gate_up_format, down_format, inter, n_experts, seed, device="cuda", first_expert=0):
     """Seeded expert bytes generated on the device; synth.expert_blob() gives the same bytes on
-    the host for any single expert."""
+    the host for any single expert. Slot s holds expert first_expert + s."""
     lib = L.load()
     stride = lib.fb_moe_blob_bytes(gate_up_format, down_format, inter)
     buf = torch.empty(n_experts * stride, dtype=torch.uint8, device=device)
@@ -63,13 +63,17 @@ def synth_layer(gate_up_format, down_format, inter, n_experts, seed, device="cud
     gu_bytes = 2 * inter * lib.fb_moe_row_bytes(gate_up_format, L.HIDDEN)
     nb_gu = gu_bytes // synth.BLOCK_BYTES[gate_up_format]
     nb_dn = (stride - gu_bytes) // synth.BLOCK_BYTES[down_format]
-    for e in range(n_experts):
-        base = buf.data_ptr() + e * stride
-        L.check(lib.fb_synth_fill_blocks(gate_up_format, base, nb_gu, e * nb_gu, seed, tables[gate_up_format].data_ptr(),
-                                         _stream()), "synth_fill_blocks")
-        L.check(lib.fb_synth_fill_blocks(down_format, base + gu_bytes, nb_dn, e * nb_dn, seed ^ 0xD0,
-                                         tables[down_format].data_ptr(), _stream()), "synth_fill_blocks")
+    fill_experts(buf, stride, gate_up_format, down_format, gu_bytes, nb_gu, nb_dn, n_experts, first_expert, seed, tables)
     return ExpertLayer(buf, gate_up_format, down_format, inter)
+
+
+def fill_experts(buf, stride, gate_up_format, down_format, gu_bytes, nb_gu, nb_dn, n_experts, first_expert, seed, tables):
+    """Two launches for a whole slot array: the gate/up part and the down part of every expert."""
+    lib = L.load()
+    L.check(lib.fb_synth_fill_experts(gate_up_format, buf.data_ptr(), stride, n_experts, first_expert, nb_gu, seed,
+                                      tables[gate_up_format].data_ptr(), _stream()), "synth_fill_experts")
+    L.check(lib.fb_synth_fill_experts(down_format, buf.data_ptr() + gu_bytes, stride, n_experts, first_expert, nb_dn,
+                                      seed ^ 0xD0, tables[down_format].data_ptr(), _stream()), "synth_fill_experts")
 
 
 class DecodeWorkspace:
@@ -201,6 +205,13 @@ def moe_layer_decode_static(w_router, layer, x, y_out):
     """The decode layer with the library's built-in scratch (for callers that cannot allocate)."""
     L.check(L.load().fb_moe_layer_decode_static(_ptr(w_router), C.byref(layer.layout), _ptr(x), _dtype_code(x),
                                                 x.shape[0], _ptr(y_out), _stream()), "moe_layer_decode_static")
+
+
+def moe_layer_decode_static_status():
+    """FB_STATUS_* word the last moe_layer_decode_static call on the current GPU left behind."""
+    out = C.c_uint32(0xFFFFFFFF)
+    L.check(L.load().fb_moe_layer_decode_static_status(C.byref(out), _stream()), "moe_layer_decode_static_status")
+    return int(out.value)
 
 
 def dequant_rows(fmt, rows, nrows, k):

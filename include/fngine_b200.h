@@ -164,7 +164,10 @@ int32_t fb_moe_combine(const fb_moe_decode_workspace* ws, const float* y_shared,
 /* One whole decode MoE layer: router projection -> select -> gate/up -> down -> combine, the call
  * sequence of Forward::moe's decode branch (src/model/forward.cpp:333,358-375) without the shared
  * expert. x: device [tokens][2560]; y_out: device fp32 [tokens][2560]. No reference counterpart
- * as a single function. */
+ * as a single function. logits_scratch is fp32 [tokens][513]; only columns 0..511 are written (the
+ * shared-expert gate, row 512 of a 513-row router, is not projected here). The fused router
+ * projection adds a logit's products in a different order than fb_router_logits: the two agree to
+ * fp32 rounding, not bit for bit. */
 int32_t fb_moe_layer_decode(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x,
                             int32_t x_dtype, int32_t tokens, const fb_moe_decode_workspace* ws, float* logits_scratch,
                             float* y_out, void* stream);
@@ -265,8 +268,9 @@ int32_t fb_moe_layer_decode_ep(const void* router_w_bf16, const fb_moe_expert_la
  * that have not arrived yet; the layer runs over the local experts; the combine writes every
  * token's partial row into its owner's y_parts, and the owner adds the n_ranks partial rows in rank
  * order into y_local [tokens / n_ranks][2560]. `step` must be 1, 2, 3, ... in call order and equal
- * on all ranks; polls are bounded (about a second) and end with FB_STATUS_PIPELINE_TIMEOUT in the
- * workspace status word. x_local is fp32.
+ * on all ranks; polls are bounded (about a second, see fb_ep_set_wait_limit) and end with
+ * FB_STATUS_PIPELINE_TIMEOUT in the workspace status word. The rank count must be 1, 2, 4 or 8.
+ * x_local is fp32.
  * Set-up (not part of a step): fb_ep_exchange_create allocates and zero-fills this rank's two
  * buffers on the current device (fb_ep_exchange_bytes(0 / 1) bytes) and writes their CUDA IPC
  * handles (2 x 64 bytes) to `handles`; the ranks trade the handle bytes through any channel and
@@ -281,6 +285,11 @@ typedef struct fb_ep_peers {
   void* y_parts[FB_EP_MAX_RANKS];
 } fb_ep_peers;
 size_t fb_ep_exchange_bytes(int32_t which);
+/* Polls a reader spends on one awaited exchange line before it gives up, records
+ * FB_STATUS_PIPELINE_TIMEOUT and lets the step drain (0 restores the default of 2^20, about a second).
+ * A host setting read at launch time; the reference's counterpart is the timeout_cycles argument of
+ * its exchange waits (src/kernels/moe/moe.h:154-158, src/core/exchange.h:46-57). */
+void fb_ep_set_wait_limit(uint32_t polls);
 int32_t fb_ep_exchange_create(void** x_all, void** y_parts, uint8_t* handles);
 int32_t fb_ep_exchange_open(const uint8_t* handles, void** x_all, void** y_parts);
 int32_t fb_ep_exchange_close(void* x_all, void* y_parts, int32_t own);
@@ -302,6 +311,12 @@ int32_t fb_ep_sum_ranks(const float* parts, int32_t n_ranks, int32_t rows, float
  * stream (or otherwise ordered). x and y_out are the caller's device buffers as above. */
 int32_t fb_moe_layer_decode_static(const void* router_w_bf16, const fb_moe_expert_layout* layout, const void* x,
                                    int32_t x_dtype, int32_t tokens, float* y_out, void* stream);
+/* The device status word (FB_STATUS_*) the last fb_moe_layer_decode_static call on the current GPU
+ * left in the static array, copied to *status_host: the workspace of that entry point is hidden, so
+ * this is how its caller learns that a bounded wait ran out (FB_STATUS_PIPELINE_TIMEOUT) or that
+ * the work list was unusable (FB_STATUS_BAD_WORK). It enqueues one 4-byte copy on `stream` and waits
+ * for that stream; it allocates nothing. No counterpart in the reference. */
+int32_t fb_moe_layer_decode_static_status(uint32_t* status_host, void* stream);
 
 /* ---------------------------------------------------------------- FP8-row dense projection
  * Fp8RowWeight + linear_fp8 with the StoreBf16 epilogue, src/kernels/linear/linear.h:57-62, :137-139:
@@ -369,6 +384,12 @@ int32_t fb_quantize_act(int32_t act_format, const void* x, int32_t x_dtype, int3
  * from splitmix64(seed, counter) and its fp16 scale from `d_table[65536]` (device). */
 int32_t fb_synth_fill_blocks(int32_t format, uint8_t* dst, int64_t n_blocks, int64_t first_block, uint64_t seed,
                              const uint16_t* d_table, void* stream);
+/* The same stream written for `n_experts` consecutive experts in ONE launch: expert first_expert + s
+ * takes blocks [(first_expert + s) * blocks_per_expert, ...) and lands at dst + s * expert_stride
+ * (dst = the slot array base plus the matrix offset inside a blob). */
+int32_t fb_synth_fill_experts(int32_t format, uint8_t* dst, int64_t expert_stride, int32_t n_experts,
+                              int32_t first_expert, int64_t blocks_per_expert, uint64_t seed, const uint16_t* d_table,
+                              void* stream);
 
 #ifdef __cplusplus
 }

@@ -86,3 +86,34 @@ def test_decode_width_projection_argument_checks(fb_built):
     sh = fblib.LinearEpilogue(fblib.EPI_SHARED_SCALE, 513, p, None, None)
     assert lib.fb_linear_fp8_decode(p, 4, p, p, 0, 256, 256, ctypes.byref(sh), p, need, None) == 1  # no gate logit
     assert lib.fb_linear_fp8_decode(p, 4, p, p, 0, 256, 256, None, p, need, None) == 1
+
+
+def test_peer_exchange_layer_refuses_rank_counts_that_do_not_divide_its_grid(fb_built):
+    """fb_moe_layer_decode_ep_p2p hands the 128 blocks of its route kernel out to the ranks in equal
+    shares, so only 1, 2, 4 and 8 ranks are accepted; 3 ranks with 3 tokens passes every other check
+    and must be refused before anything is launched."""
+    lib = fblib.load()
+    lay = fblib.ExpertLayout()
+    assert lib.fb_moe_expert_layout_make(0x1000, 1689600, 21, 21, 512, ctypes.byref(lay)) == 0
+    ws = fblib.DecodeWorkspace()
+    for f in ("work", "xq", "h", "hq", "partial", "item_done", "sched", "status"):
+        setattr(ws, f, 0x1000)
+    ws.gate_up_format, ws.down_format, ws.inter = 21, 21, 512
+    for ranks, tokens in ((3, 3), (5, 5), (6, 12), (7, 14)):
+        peers = fblib.EpPeers()
+        peers.rank, peers.n_ranks = 0, ranks
+        for d in range(ranks):
+            peers.x_all[d], peers.y_parts[d] = 0x2000, 0x3000
+        st = lib.fb_moe_layer_decode_ep_p2p(0x1000, ctypes.byref(lay), 0x1000, 0x1000, tokens, ctypes.byref(peers), 1,
+                                            ctypes.byref(ws), 0x1000, 0x1000, None)
+        assert st == 1 and b"1, 2, 4 or 8" in lib.fb_last_error_string(), ranks
+
+
+def test_static_status_needs_a_prior_static_call(fb_built):
+    """fb_moe_layer_decode_static_status reads the status word of the static array; before the static
+    entry point has run on the device there is nothing to read and the call says so."""
+    lib = fblib.load()
+    out = ctypes.c_uint32(7)
+    assert lib.fb_moe_layer_decode_static_status(None, None) == 1
+    st = lib.fb_moe_layer_decode_static_status(ctypes.byref(out), None)
+    assert st != 0 and out.value == 7

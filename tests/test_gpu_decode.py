@@ -511,3 +511,50 @@ def test_peer_exchange_layer_with_one_rank_equals_the_plain_layer():
         torch.cuda.synchronize()
         assert ws.status() == 0
         assert torch.equal(y, y_ref)
+
+
+def test_peer_wait_that_nobody_answers_runs_out_and_is_reported():
+    """A bounded device-side wait actually running out (the reference has the same test for its CPU
+    exchange, tests/kernels/moe/test_moe_exchange.cpp:286-307): a two-rank peer-exchange step on ONE GPU
+    whose second rank does not exist. Both "ranks'" buffers are local, zeroed, and nobody publishes
+    rank 1's rows, so every reader of those lines gives up after the (shortened) poll limit: the call
+    returns, the status word says FB_STATUS_PIPELINE_TIMEOUT, nothing faults or hangs, and the library
+    keeps working - a plain layer on a fresh workspace right afterwards is bit-exact."""
+    torch = _torch()
+    from fngine_b200 import ep, lib as fblib, moe
+    tokens, seed = 16, 5000
+    lib = fblib.load()
+    wr = torch.from_numpy(synth.router_weights(303, rows=512).view(np.int16)).cuda().view(torch.bfloat16)
+    full = moe.synth_layer(IQ3_S, IQ3_S, 512, 512, seed)
+    ws = moe.DecodeWorkspace(full)
+    x = torch.from_numpy(synth.activations(80, tokens)).cuda()
+    y_ref = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    moe.moe_layer_decode(wr, full, x, ws, y_ref)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+
+    bufs = [[torch.zeros(lib.fb_ep_exchange_bytes(k), dtype=torch.uint8, device="cuda") for k in (0, 1)] for _ in range(2)]
+    xchg = ep.PeerExchange.__new__(ep.PeerExchange)
+    xchg.rank, xchg.world, xchg.step = 0, 2, 0
+    xchg.peers = fblib.EpPeers()
+    xchg.peers.rank, xchg.peers.n_ranks = 0, 2
+    for d in range(2):
+        xchg.peers.x_all[d], xchg.peers.y_parts[d] = (b.data_ptr() for b in bufs[d])
+    shard = type("S", (), {})()
+    shard.layer = full  # rank 0 of 2 would hold experts 0..255; every slot is resident here, which is harmless
+    shard.slot_of = torch.arange(512, dtype=torch.int32, device="cuda")
+    ws2 = moe.DecodeWorkspace(full)
+    y = torch.empty(tokens // 2, H, dtype=torch.float32, device="cuda")
+    lib.fb_ep_set_wait_limit(2000)  # a fraction of a millisecond per awaited line
+    try:
+        ep.layer_decode_ep_p2p(wr, shard, x[: tokens // 2].contiguous(), ws2, xchg, y)
+        torch.cuda.synchronize()
+    finally:
+        lib.fb_ep_set_wait_limit(0)
+    assert ws2.status() == fblib.STATUS_PIPELINE_TIMEOUT
+    # the context is intact and the kernels still give the same bits
+    ws3 = moe.DecodeWorkspace(full)
+    y2 = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    moe.moe_layer_decode(wr, full, x, ws3, y2)
+    torch.cuda.synchronize()
+    assert ws3.status() == 0 and torch.equal(y2, y_ref)

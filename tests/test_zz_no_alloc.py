@@ -33,6 +33,8 @@ def test_static_scratch_layer_matches_workspace_layer():
         moe.moe_layer_decode_static(wr, layer, x, got)
         torch.cuda.synchronize()
         assert np.array_equal(got.cpu().numpy().view(np.uint32), want.cpu().numpy().view(np.uint32))
+        # the hidden scratch's status word is readable: no bounded wait ran out, the work list was usable
+        assert moe.moe_layer_decode_static_status() == 0
     # requests beyond the static array's size are refused, nothing is launched
     lib = fblib.load()
     st = lib.fb_moe_layer_decode_static(wr.data_ptr(), ctypes.byref(layer.layout), x.data_ptr(), 0, 17,
