@@ -1,28 +1,37 @@
-// FP8-row dense projection for sm_100a: out[t][n] = bf16( (sum_k a8[t][k] * w8[n][k]) * sa[t] * sw[n] )
+// FP8-row dense projection for sm_100a: out = epilogue( (sum_k a[t][k] * w8[n][k]) * sa[t] * sw[n] )
 //
-//   a8, sa : per-token E4M3 quantization of the bf16 activations (scale = max|x| / 448), the
-//            reference's "A8" path (src/kernels/linear/fp8/fp8_a8_quantize.cuh:14-26 and
-//            fp8_a8.cu:22-69 of the reference project);
-//   w8, sw : E4M3 weight codes [n][k] with one scale per row (src/kernels/linear/linear.h:57-62).
+//   w8, sw : E4M3 weight codes [n][k] with one scale per row (src/kernels/linear/linear.h:57-62 of the
+//            reference project);
+//   a, sa  : the bf16 activations, two routes as in the reference (linear.h:27-37):
+//            exact (Auto / A16): each token is scaled by a power of two and written as the SUM OF TWO
+//              E4M3 numbers, hi = rne(x) and lo = x - hi, which represents a bf16 value without loss
+//              (eight significant bits = 4 + 4); the GEMM adds both products into one accumulator,
+//              so the result is that of the reference's bf16-activation path while the weight codes
+//              still go from HBM to the tensor core untouched;
+//            A8: one E4M3 code per activation with scale = max|x| / 448
+//              (src/kernels/linear/fp8/fp8_a8_quantize.cuh:14-26, fp8_a8.cu:22-69): half the tensor
+//              work, 1-4 % rms output noise, only on request.
 //
 // The GEMM is a persistent tcgen05 kernel (kind::f8f6f4, E4M3 x E4M3 -> fp32 in tensor memory). One
 // thread issues TMA tile loads (128-byte swizzle, no multicast) into a shared-memory ring, one
 // thread issues the MMAs into one of two 256-column TMEM accumulators, four warps drain the other
-// accumulator (tcgen05.ld), apply the two scales and store bf16. All hand-offs are mbarriers; every
-// wait is bounded and reports through a status word. Two variants:
+// accumulator (tcgen05.ld), apply the two scales and run the epilogue (StoreBf16, StoreF32, GrWrite,
+// SwiGlu, SharedScale of linear.h:64-103). All hand-offs are mbarriers; every wait is bounded and
+// reports through a status word. Two variants:
 //   * CTA pairs (tokens >= 256): the two-SM MMA (cta_group::2), 256 x 256 tiles per cluster of two
-//     CTAs, each CTA staging its 128 rows of A and its 128 rows of B per K step (32 KB, six stages);
-//   * single CTA: 128 x 256 tiles, 48 KB per K step, four stages.
-// What the measurements said (B200, 4096 x 9216 x 2560): operand traffic is not the limit (a run
-// that skips every load after the first ring fill takes the same time); the per-K-step work of the
-// MMA-issuing thread is. A tcgen05 fence after each full-barrier wait and a shared-memory flag load
+//     CTAs, each CTA staging its 128 token rows (one or two pieces) and its 128 weight rows per K
+//     step (32 / 48 KB, six / four stages);
+//   * single CTA: 128 x 256 tiles, 48 / 64 KB per K step, four / three stages.
+// What the measurements said (B200, 4096 x 9216 x 2560, one piece): operand traffic is not the limit
+// (a run that skips every load after the first ring fill takes the same time); the per-K-step work of
+// the MMA-issuing thread is. A tcgen05 fence after each full-barrier wait and a shared-memory flag load
 // in front of it cost 17 % of the kernel; with both gone the pair kernel runs at 2.4 PFLOP/s, within
 // 8 % of issuing the MMAs back to back with no barriers at all (2.65 PFLOP/s), while a library FP8
 // GEMM of the same shape on the same GPU reaches 2.7 - 2.9 PFLOP/s.
 //
 // A second operation lives here: the same weights at decode width (T <= 16) with the bf16 activations
-// kept exactly (the reference's "A16" numerics) and its fused epilogues, a stream over the weight codes
-// that reaches 0.9 of the HBM copy rate; see "decode-width projection" below.
+// kept exactly and the same epilogues, a stream over the weight codes that reaches 0.9 of the HBM copy
+// rate; see "decode-width projection" below. fb_linear_fp8 routes T <= 16 there.
 #include "common.cuh"
 
 #include <cuda.h>
@@ -34,9 +43,8 @@
 namespace fb {
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 128, kStages = 4;
-constexpr int kStageA = BM * BK, kStageB = BN * BK;           // bytes (1 byte per element)
-constexpr int kRingBytes = kStages * (kStageA + kStageB);      // 196608
+constexpr int BM = 128, BN = 256, BK = 128, kStages = 4;      // kStages: the most stages the single-CTA ring has
+constexpr int kRingBytes = kStages * (BM * BK + BN * BK);      // 196608 (1 byte per element)
 constexpr int kGemmSmem = kRingBytes + 256 + 1024;             // + barriers + alignment slack
 constexpr int kThreads = 192;                                  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
 constexpr uint32_t kTmemCols = 512;                            // two 256-column fp32 accumulators
@@ -119,13 +127,26 @@ __device__ __forceinline__ bool gemm_wait(GemmBars* b, uint64_t* bar, uint32_t p
 }
 
 // ------------------------------------------------------------------------------ activation quantization
-// One block per token: scale = max|x| / 448, codes = satfinite_rne_e4m3(x * (1 / scale)). Each thread
-// keeps up to kQPer 16-byte pieces of the row in registers between the two phases (rows up to
-// 256 * 8 * kQPer elements are read from memory once); longer rows re-read the remainder.
+// A8 (one piece): one block per token, scale = max|x| / 448, codes = satfinite_rne_e4m3(x * (1 / scale)).
+// Exact (two pieces, codes_lo given): the scale is the power of two that puts the row maximum in
+// [128, 256), hi = rne_e4m3(x / scale) and lo = rne_e4m3(x / scale - hi). A bf16 value has eight
+// significant bits; hi keeps four of them and the remainder is a multiple of the value's last bit of at
+// most four significant bits, so lo is exact whenever that last bit is at least 2^-9 of the scaled
+// range (|x| >= 2^-9..2^-10 of the row maximum); smaller elements lose bits below 2^-17 of the row
+// maximum. scale * (hi + lo) therefore IS the bf16 activation: the two-piece GEMM has the numerics of
+// the reference's bf16-activation path (src/kernels/linear/linear.h:27-31) on the FP8 tensor cores.
+// Each thread keeps up to kQPer 16-byte pieces of the row in registers between the two phases (rows up
+// to 256 * 8 * kQPer elements are read from memory once); longer rows re-read the remainder.
 constexpr int kQPer = 2;
+
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t pair) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(pair), __NV_E4M3);
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
 
 __global__ void __launch_bounds__(256) fp8_quantize_tokens_kernel(const __nv_bfloat16* __restrict__ x, int K,
                                                                   uint8_t* __restrict__ codes,
+                                                                  uint8_t* __restrict__ codes_lo,
                                                                   float* __restrict__ scales) {
   const int t = blockIdx.x;
   const __nv_bfloat16* row = x + size_t(t) * K;
@@ -154,20 +175,36 @@ __global__ void __launch_bounds__(256) fp8_quantize_tokens_kernel(const __nv_bfl
   m = s_red[0];
 #pragma unroll
   for (int i = 1; i < 8; ++i) m = fmaxf(m, s_red[i]);
-  const float scale = m > 0.0f ? __fdiv_rn(m, 448.0f) : 0.0f;
-  const float inv = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+  const bool two = codes_lo != nullptr;
+  float scale, inv;
+  if (two) {
+    // 2^(e - 7) with 2^e <= m < 2^(e+1); rows of zeros, infinities or NaN get scale 0 (all-zero codes)
+    const int e = int((__float_as_uint(m) >> 23) & 0xFFu) - 127;
+    const bool ok = m > 0.0f && e < 128 && e - 7 >= -126 && 7 - e >= -126;
+    scale = ok ? __uint_as_float(uint32_t(e - 7 + 127) << 23) : 0.0f;
+    inv = ok ? __uint_as_float(uint32_t(7 - e + 127) << 23) : 0.0f;
+  } else {
+    scale = m > 0.0f ? __fdiv_rn(m, 448.0f) : 0.0f;
+    inv = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+  }
   if (threadIdx.x == 0) scales[t] = scale;
   auto encode = [&](const uint4& v, int i) {
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-    uint32_t o[2] = {0, 0};
+    uint32_t o[2] = {0, 0}, ol[2] = {0, 0};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float2 f = make_float2(__fmul_rn(__uint_as_float(u[j] << 16), inv),
                                    __fmul_rn(__uint_as_float(u[j] & 0xFFFF0000u), inv));
       const uint32_t pair = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
       o[j >> 1] |= pair << (16 * (j & 1));
+      if (two) {
+        const float2 hi = e4m3x2_to_float2(pair);
+        const float2 r = make_float2(__fsub_rn(f.x, hi.x), __fsub_rn(f.y, hi.y));
+        ol[j >> 1] |= uint32_t(__nv_cvt_float2_to_fp8x2(r, __NV_SATFINITE, __NV_E4M3)) << (16 * (j & 1));
+      }
     }
     *reinterpret_cast<uint2*>(codes + size_t(t) * K + i) = make_uint2(o[0], o[1]);
+    if (two) *reinterpret_cast<uint2*>(codes_lo + size_t(t) * K + i) = make_uint2(ol[0], ol[1]);
   };
 #pragma unroll
   for (int p = 0; p < kQPer; ++p) {
@@ -177,23 +214,156 @@ __global__ void __launch_bounds__(256) fp8_quantize_tokens_kernel(const __nv_bfl
   for (int i = (kQPer * 256 + threadIdx.x) * 8; i < K; i += 256 * 8) encode(*reinterpret_cast<const uint4*>(row + i), i);
 }
 
-// ------------------------------------------------------------------------------ GEMM
-template <bool SCALE_BF16>
+// ------------------------------------------------------------------------------ GEMM: tiles and epilogues
+// What both GEMM kernels need besides the tensor maps. An output tile is 128 (256 for a CTA pair)
+// tokens x 256 weight rows, staged as two boxes of 128 weight rows: rows n0 .. n0+127 and n0+128 ..
+// n0+255 of the weight, or, for SwiGlu, 128 gate rows j0 .. j0+127 and the matching up rows
+// N/2 + j0 .., so that accumulator column c (gate) and column 128 + c (up) meet in one thread.
+struct GemmArgs {
+  const float* act_scale;   // [M] token scales
+  const void* w_scale;      // [N] fp32 or bf16 row scales
+  void* out;
+  const float* inj;         // GrWrite: fp32 [M][4]
+  const float* gate_logit;  // SharedScale
+  uint32_t* status;
+  int scale_bf16, kind, gate_stride;
+  int M, N, K;
+  int lo_row0;              // two pieces: first row of the second piece inside the activation map
+};
+
+__device__ __forceinline__ int gemm_n_tiles(const GemmArgs& a) {
+  return a.kind == FB_EPI_SWIGLU ? ((a.N >> 1) + 127) / 128 : (a.N + BN - 1) / BN;
+}
+// First weight row of box `half` (0 / 1) of column tile n_blk.
+__device__ __forceinline__ int gemm_box_row(const GemmArgs& a, int n_blk, int half) {
+  return a.kind == FB_EPI_SWIGLU ? half * (a.N >> 1) + n_blk * 128 : n_blk * BN + half * 128;
+}
+// 32 consecutive row scales starting at row n (n % 32 == 0).
+__device__ __forceinline__ void gemm_scales32(const GemmArgs& a, int n, float (&s)[32]) {
+  if (a.scale_bf16) {
+    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.w_scale) + n);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 v = p[q];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        s[8 * q + 2 * j] = __uint_as_float(u[j] << 16);
+        s[8 * q + 2 * j + 1] = __uint_as_float(u[j] & 0xFFFF0000u);
+      }
+    }
+  } else {
+    const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.w_scale) + n);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 v = p[q];
+      s[4 * q] = v.x;
+      s[4 * q + 1] = v.y;
+      s[4 * q + 2] = v.z;
+      s[4 * q + 3] = v.w;
+    }
+  }
+}
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&v)[32]) {
+  uint32_t packed[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    packed[j] = *reinterpret_cast<const uint32_t*>(&b);
+  }
+  uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) d[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+}
+
+// The epilogue of one token row of one tile, by the thread that owns the row's tensor-memory lane:
+// `taddr` = the accumulator's address at this warp's lane quarter, column 0 of the tile; sa = the
+// token scale (0 for rows past M, which are not stored).
+__device__ __forceinline__ void gemm_epilogue_row(const GemmArgs& a, uint32_t taddr, int row, int n_blk, float sa) {
+  const bool live = row < a.M;
+  if (a.kind == FB_EPI_SWIGLU) {
+    const int half_n = a.N >> 1;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t rg[32], ru[32];
+      tmem_ld32(taddr + uint32_t(c * 32), rg);
+      tmem_ld32(taddr + uint32_t(128 + c * 32), ru);
+      const int j0 = n_blk * 128 + c * 32;
+      if (live && j0 < half_n) {
+        float sg[32], su[32], h[32];
+        gemm_scales32(a, j0, sg);
+        gemm_scales32(a, half_n + j0, su);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float g = __uint_as_float(rg[i]) * sa * sg[i], u = __uint_as_float(ru[i]) * sa * su[i];
+          h[i] = g / (1.0f + expf(-g)) * u;
+        }
+        store_bf16x32(static_cast<__nv_bfloat16*>(a.out) + size_t(row) * half_n + j0, h);
+      }
+    }
+    return;
+  }
+  if (a.kind == FB_EPI_SHARED_SCALE && live) sa /= 1.0f + expf(-a.gate_logit[size_t(row) * a.gate_stride]);
+  float4 inj4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (a.kind == FB_EPI_GR_WRITE && live) inj4 = *reinterpret_cast<const float4*>(a.inj + size_t(row) * 4);
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr + uint32_t(c * 32), r);
+    const int n0 = n_blk * BN + c * 32;
+    if (!live || n0 >= a.N) continue;
+    float s[32], v[32];
+    gemm_scales32(a, n0, s);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * sa * s[i];
+    if (a.kind == FB_EPI_STORE_BF16) {
+      store_bf16x32(static_cast<__nv_bfloat16*>(a.out) + size_t(row) * a.N + n0, v);
+    } else if (a.kind == FB_EPI_GR_WRITE) {
+      const float inj[4] = {inj4.x, inj4.y, inj4.z, inj4.w};
+#pragma unroll
+      for (int s4 = 0; s4 < 4; ++s4) {
+        float4* X = reinterpret_cast<float4*>(static_cast<float*>(a.out) + (size_t(row) * 4 + s4) * a.N + n0);
+        float4 xv[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) xv[q] = X[q];  // all loads of a stream before its first store
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          X[q] = make_float4(fmaf(inj[s4], v[4 * q], xv[q].x), fmaf(inj[s4], v[4 * q + 1], xv[q].y),
+                             fmaf(inj[s4], v[4 * q + 2], xv[q].z), fmaf(inj[s4], v[4 * q + 3], xv[q].w));
+      }
+    } else {  // StoreF32, SharedScale
+      float4* d = reinterpret_cast<float4*>(static_cast<float*>(a.out) + size_t(row) * a.N + n0);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) d[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ GEMM, one CTA per tile
+// PIECES activation tiles (128 tokens x 128 bytes each) and the two weight boxes per K step; the
+// MMA thread adds PIECES products per K step into the same accumulator.
+template <int PIECES>
+struct Gemm1 {
+  static constexpr int kStageA = PIECES * BM * BK, kStageB = BN * BK, kStage = kStageA + kStageB;
+  static constexpr int kStages = kRingBytes / kStage;  // 4 (one piece) / 3 (two pieces)
+};
+
+template <int PIECES>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const float* __restrict__ act_scale, const void* __restrict__ w_scale,
-                __nv_bfloat16* __restrict__ out, int M, int N, int K, uint32_t* status) {
+                const GemmArgs a) {
+  using G = Gemm1<PIECES>;
+  constexpr int S = G::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* ring_a = smem;
-  uint8_t* ring_b = smem + kStages * kStageA;
   GemmBars* bars = reinterpret_cast<GemmBars*>(smem + kRingBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, k_blocks = K / BK;
+  const int m_tiles = (a.M + BM - 1) / BM, n_tiles = gemm_n_tiles(a), k_blocks = a.K / BK;
   const int n_work = m_tiles * n_tiles;
+  uint32_t* status = a.status;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kStages; ++i) {
+    for (int i = 0; i < S; ++i) {
       mbar_init(&bars->full[i], 1);
       mbar_init(&bars->empty[i], 1);
     }
@@ -218,11 +388,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
         bool ok = true;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kStages;
-          if (!gemm_wait(bars, &bars->empty[s], ((it / kStages) & 1) ^ 1, status)) { ok = false; break; }
-          mbar_expect_tx(&bars->full[s], kStageA + kStageB);
-          tma_load_2d(ring_a + s * kStageA, &map_a, kb * BK, m_blk * BM, &bars->full[s]);
-          tma_load_2d(ring_b + s * kStageB, &map_b, kb * BK, n_blk * BN, &bars->full[s]);
+          const int s = it % S;
+          if (!gemm_wait(bars, &bars->empty[s], ((it / S) & 1) ^ 1, status)) { ok = false; break; }
+          uint8_t* st = smem + s * G::kStage;
+          mbar_expect_tx(&bars->full[s], G::kStage);
+#pragma unroll
+          for (int p = 0; p < PIECES; ++p)
+            tma_load_2d(st + p * BM * BK, &map_a, kb * BK, p * a.lo_row0 + m_blk * BM, &bars->full[s]);
+          tma_load_2d(st + G::kStageA, &map_b, kb * BK, gemm_box_row(a, n_blk, 0), &bars->full[s]);
+          tma_load_2d(st + G::kStageA + 128 * BK, &map_b, kb * BK, gemm_box_row(a, n_blk, 1), &bars->full[s]);
         }
         if (!ok) break;
       }
@@ -238,15 +412,19 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const uint32_t d_tmem = tmem_base + uint32_t(ab * BN);
         bool ok = true;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kStages;
+          const int s = it % S;
           // (no tcgen05 fence here: the operands were written through the async proxy and the
           // barrier wait orders them; a fence per K step costs a fifth of the kernel)
-          if (!gemm_wait(bars, &bars->full[s], (it / kStages) & 1, status)) { ok = false; break; }
-          const uint64_t da = umma_desc_k128(smem_u32(ring_a + s * kStageA));
-          const uint64_t db = umma_desc_k128(smem_u32(ring_b + s * kStageB));
+          if (!gemm_wait(bars, &bars->full[s], (it / S) & 1, status)) { ok = false; break; }
+          const uint32_t st = smem_u32(smem + s * G::kStage);
+          const uint64_t db = umma_desc_k128(st + G::kStageA);
 #pragma unroll
-          for (int k4 = 0; k4 < BK / 32; ++k4)  // 32 bytes of K per instruction: +2 in 16-byte units
-            umma_f8(d_tmem, da + uint64_t(2 * k4), db + uint64_t(2 * k4), kIdescF8, (kb | k4) ? 1u : 0u);
+          for (int p = 0; p < PIECES; ++p) {
+            const uint64_t da = umma_desc_k128(st + p * BM * BK);
+#pragma unroll
+            for (int k4 = 0; k4 < BK / 32; ++k4)  // 32 bytes of K per instruction: +2 in 16-byte units
+              umma_f8(d_tmem, da + uint64_t(2 * k4), db + uint64_t(2 * k4), kIdescF8, (kb | k4 | p) ? 1u : 0u);
+          }
           umma_commit(&bars->empty[s]);  // stage reusable once these MMAs have read it
         }
         if (!ok) break;
@@ -263,36 +441,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (!gemm_wait(bars, &bars->tmem_full[ab], (tl >> 1) & 1, status)) break;
       tc_fence_after();
       const int row = m_blk * BM + q * 32 + lane;
-      const float sa = row < M ? act_scale[row] : 0.0f;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(ab * BN + c * 32), r);
-        const int col0 = n_blk * BN + c * 32;
-        if (row < M && col0 < N) {
-          uint32_t packed[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float s0, s1;
-            if constexpr (SCALE_BF16) {
-              const uint32_t u = reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(w_scale) + col0)[j];
-              s0 = __uint_as_float(u << 16);
-              s1 = __uint_as_float(u & 0xFFFF0000u);
-            } else {
-              const float2 f = reinterpret_cast<const float2*>(static_cast<const float*>(w_scale) + col0)[j];
-              s0 = f.x;
-              s1 = f.y;
-            }
-            const float v0 = __uint_as_float(r[2 * j]) * sa * s0;
-            const float v1 = __uint_as_float(r[2 * j + 1]) * sa * s1;
-            const __nv_bfloat162 b = __floats2bfloat162_rn(v0, v1);
-            packed[j] = *reinterpret_cast<const uint32_t*>(&b);
-          }
-          uint4* dst = reinterpret_cast<uint4*>(out + size_t(row) * N + col0);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-        }
-      }
+      const float sa = row < a.M ? a.act_scale[row] : 0.0f;
+      gemm_epilogue_row(a, tmem_base + (uint32_t(q * 32) << 16) + uint32_t(ab * BN), row, n_blk, sa);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty[ab]);
@@ -318,9 +468,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 //   tmem_full[a] in each CTA, same multicast commit; tmem_empty[a] in the leader, eight arrivals
 //             (four epilogue warps per CTA, CTA 1's through the cluster window).
 // No TMA load is multicast: each CTA loads only its own operand halves.
-constexpr int BM2 = 256, kStages2 = 6;
-constexpr int kStageA2 = 128 * BK, kStageB2 = 128 * BK;              // per CTA and stage
-constexpr int kRingBytes2 = kStages2 * (kStageA2 + kStageB2);         // 196608
+constexpr int BM2 = 256, kStages2 = 6;                               // kStages2: the most stages the pair ring has
+constexpr int kRingBytes2 = kStages2 * (128 * BK + 128 * BK);         // 196608 per CTA
 constexpr int kGemmSmem2 = kRingBytes2 + 256 + 1024;
 constexpr uint32_t kIdescF8Pair = (1u << 4) | (uint32_t(BN >> 3) << 17) | (uint32_t(BM2 >> 4) << 24);
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the bit that separates the two CTAs of a pair
@@ -389,23 +538,29 @@ __device__ __forceinline__ bool gemm_wait2(GemmBars2* b, uint64_t* bar, uint32_t
   return false;
 }
 
-template <bool SCALE_BF16>
+template <int PIECES>
+struct Gemm2 {
+  static constexpr int kStageA = PIECES * 128 * BK, kStageB = 128 * BK, kStage = kStageA + kStageB;  // per CTA
+  static constexpr int kStages = kRingBytes2 / kStage;  // 6 (one piece) / 4 (two pieces)
+};
+
+template <int PIECES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                     const float* __restrict__ act_scale, const void* __restrict__ w_scale,
-                     __nv_bfloat16* __restrict__ out, int M, int N, int K, uint32_t* status) {
+                     const GemmArgs a) {
+  using G = Gemm2<PIECES>;
+  constexpr int S = G::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* ring_a = smem;
-  uint8_t* ring_b = smem + kStages2 * kStageA2;
   GemmBars2* bars = reinterpret_cast<GemmBars2*>(smem + kRingBytes2);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = int(cluster_ctarank());
-  const int m_tiles = (M + BM2 - 1) / BM2, n_tiles = (N + BN - 1) / BN, k_blocks = K / BK;
+  const int m_tiles = (a.M + BM2 - 1) / BM2, n_tiles = gemm_n_tiles(a), k_blocks = a.K / BK;
   const int n_work = m_tiles * n_tiles, pair = int(blockIdx.x) >> 1, n_pairs = int(gridDim.x) >> 1;
+  uint32_t* status = a.status;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kStages2; ++i) {
+    for (int i = 0; i < S; ++i) {
       mbar_init(&bars->full[i], 1);
       mbar_init(&bars->empty[i], 1);
     }
@@ -424,18 +579,21 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
   if (warp == 0) {
-    // ---------------- TMA producer (both CTAs): own A rows and own B rows, completion on the leader's barrier
+    // ---------------- TMA producer (both CTAs): own token rows and own weight box, completion on the leader's barrier
     if (lane == 0) {
       uint32_t it = 0;
       for (int tile = pair; tile < n_work; tile += n_pairs) {
         const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
         bool ok = true;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kStages2;
-          if (!gemm_wait2(bars, &bars->empty[s], ((it / kStages2) & 1) ^ 1, status)) { ok = false; break; }
-          if (rank == 0) mbar_expect_tx(&bars->full[s], 2 * (kStageA2 + kStageB2));
-          tma_load_2d_pair(ring_a + s * kStageA2, &map_a, kb * BK, m_blk * BM2 + rank * 128, &bars->full[s]);
-          tma_load_2d_pair(ring_b + s * kStageB2, &map_b, kb * BK, n_blk * BN + rank * 128, &bars->full[s]);
+          const int s = it % S;
+          if (!gemm_wait2(bars, &bars->empty[s], ((it / S) & 1) ^ 1, status)) { ok = false; break; }
+          uint8_t* st = smem + s * G::kStage;
+          if (rank == 0) mbar_expect_tx(&bars->full[s], 2 * G::kStage);
+#pragma unroll
+          for (int p = 0; p < PIECES; ++p)
+            tma_load_2d_pair(st + p * 128 * BK, &map_a, kb * BK, p * a.lo_row0 + m_blk * BM2 + rank * 128, &bars->full[s]);
+          tma_load_2d_pair(st + G::kStageA, &map_b, kb * BK, gemm_box_row(a, n_blk, rank), &bars->full[s]);
         }
         if (!ok) break;
       }
@@ -451,13 +609,17 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const uint32_t d_tmem = tmem_base + uint32_t(ab * BN);
         bool ok = true;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kStages2;
-          if (!gemm_wait2(bars, &bars->full[s], (it / kStages2) & 1, status)) { ok = false; break; }
-          const uint64_t da = umma_desc_k128(smem_u32(ring_a + s * kStageA2));
-          const uint64_t db = umma_desc_k128(smem_u32(ring_b + s * kStageB2));
+          const int s = it % S;
+          if (!gemm_wait2(bars, &bars->full[s], (it / S) & 1, status)) { ok = false; break; }
+          const uint32_t st = smem_u32(smem + s * G::kStage);
+          const uint64_t db = umma_desc_k128(st + G::kStageA);
 #pragma unroll
-          for (int k4 = 0; k4 < BK / 32; ++k4)
-            umma_f8_pair(d_tmem, da + uint64_t(2 * k4), db + uint64_t(2 * k4), kIdescF8Pair, (kb | k4) ? 1u : 0u);
+          for (int p = 0; p < PIECES; ++p) {
+            const uint64_t da = umma_desc_k128(st + p * 128 * BK);
+#pragma unroll
+            for (int k4 = 0; k4 < BK / 32; ++k4)
+              umma_f8_pair(d_tmem, da + uint64_t(2 * k4), db + uint64_t(2 * k4), kIdescF8Pair, (kb | k4 | p) ? 1u : 0u);
+          }
           umma_commit_pair(&bars->empty[s]);
         }
         if (!ok) break;
@@ -465,7 +627,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       }
     }
   } else {
-    // ---------------- epilogue warps 2..5 of each CTA: its 128 rows of the pair's tile
+    // ---------------- epilogue warps 2..5 of each CTA: its 128 token rows of the pair's tile
     const int q = warp & 3;
     uint32_t tl = 0;
     for (int tile = pair; tile < n_work; tile += n_pairs, ++tl) {
@@ -474,36 +636,8 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       if (!gemm_wait2(bars, &bars->tmem_full[ab], (tl >> 1) & 1, status)) break;
       tc_fence_after();
       const int row = m_blk * BM2 + rank * 128 + q * 32 + lane;
-      const float sa = row < M ? act_scale[row] : 0.0f;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(ab * BN + c * 32), r);
-        const int col0 = n_blk * BN + c * 32;
-        if (row < M && col0 < N) {
-          uint32_t packed[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float s0, s1;
-            if constexpr (SCALE_BF16) {
-              const uint32_t u = reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(w_scale) + col0)[j];
-              s0 = __uint_as_float(u << 16);
-              s1 = __uint_as_float(u & 0xFFFF0000u);
-            } else {
-              const float2 f = reinterpret_cast<const float2*>(static_cast<const float*>(w_scale) + col0)[j];
-              s0 = f.x;
-              s1 = f.y;
-            }
-            const float v0 = __uint_as_float(r[2 * j]) * sa * s0;
-            const float v1 = __uint_as_float(r[2 * j + 1]) * sa * s1;
-            const __nv_bfloat162 b = __floats2bfloat162_rn(v0, v1);
-            packed[j] = *reinterpret_cast<const uint32_t*>(&b);
-          }
-          uint4* dst = reinterpret_cast<uint4*>(out + size_t(row) * N + col0);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-        }
-      }
+      const float sa = row < a.M ? a.act_scale[row] : 0.0f;
+      gemm_epilogue_row(a, tmem_base + (uint32_t(q * 32) << 16) + uint32_t(ab * BN), row, n_blk, sa);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(&bars->tmem_empty[ab]);
@@ -1042,13 +1176,13 @@ int pair_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return sm_count() / 2;
   if (!cached[dev]) {
-    opt_in_smem(fp8_gemm_pair_kernel<false>, kGemmSmem2);
+    opt_in_smem(fp8_gemm_pair_kernel<1>, kGemmSmem2);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(sm_count()) & ~1u);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = kGemmSmem2;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, fp8_gemm_pair_kernel<false>, &cfg) != cudaSuccess || clusters < 1) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, fp8_gemm_pair_kernel<1>, &cfg) != cudaSuccess || clusters < 1) {
       cudaGetLastError();
       clusters = sm_count() / 2;
     }
@@ -1065,9 +1199,11 @@ using namespace fb;
 extern "C" {
 
 size_t fb_linear_fp8_workspace_bytes(int32_t n, int32_t k, int32_t max_tokens) {
-  (void)n;
-  if (k <= 0 || max_tokens <= 0) return 0;
-  return align256(size_t(max_tokens) * size_t(k)) + align256(size_t(max_tokens) * 4) + 256;
+  if (n <= 0 || k <= 0 || max_tokens <= 0) return 0;
+  // two activation pieces [2][T][k] | token scales | status; at T <= 16 the decode-width projection's scratch
+  const size_t gemm = align256(size_t(2) * size_t(max_tokens) * size_t(k)) + align256(size_t(max_tokens) * 4) + 256;
+  const size_t dec = fb_linear_fp8_decode_workspace_bytes(n, k);
+  return gemm > dec ? gemm : dec;
 }
 
 int32_t fb_fp8_quantize_tokens(const void* x_bf16, int32_t tokens, int32_t k, uint8_t* codes, float* scales,
@@ -1075,33 +1211,59 @@ int32_t fb_fp8_quantize_tokens(const void* x_bf16, int32_t tokens, int32_t k, ui
   if (!x_bf16 || !codes || !scales || tokens <= 0 || k <= 0 || k % 8)
     return invalid("fp8_quantize_tokens: bad arguments (k must be a multiple of 8)");
   fp8_quantize_tokens_kernel<<<tokens, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x_bf16), k, codes,
-                                                                    scales);
+                                                                    nullptr, scales);
   return check_launch("fp8_quantize_tokens");
 }
 
+int32_t fb_fp8_split_tokens(const void* x_bf16, int32_t tokens, int32_t k, uint8_t* codes_hi, uint8_t* codes_lo,
+                            float* scales, void* stream) {
+  if (!x_bf16 || !codes_hi || !codes_lo || !scales || tokens <= 0 || k <= 0 || k % 8)
+    return invalid("fp8_split_tokens: bad arguments (k must be a multiple of 8)");
+  fp8_quantize_tokens_kernel<<<tokens, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x_bf16), k, codes_hi,
+                                                                    codes_lo, scales);
+  return check_launch("fp8_split_tokens");
+}
+
 int32_t fb_linear_fp8(const void* x_bf16, int32_t tokens, const uint8_t* w_codes, const void* w_scales,
-                      int32_t w_scales_dtype, int32_t n, int32_t k, void* out_bf16, void* workspace,
-                      size_t workspace_bytes, void* stream) {
-  if (!x_bf16 || !w_codes || !w_scales || !out_bf16 || tokens <= 0)
+                      int32_t w_scales_dtype, int32_t n, int32_t k, const fb_linear_epilogue* epilogue, void* workspace,
+                      size_t workspace_bytes, void* stream, int32_t path) {
+  if (!x_bf16 || !w_codes || !w_scales || !epilogue || !epilogue->out || tokens <= 0)
     return invalid("linear_fp8: null argument or no tokens");
+  if (path != FB_FP8_PATH_AUTO && path != FB_FP8_PATH_A16 && path != FB_FP8_PATH_A8)
+    return invalid("linear_fp8: unknown path");
+  // decode width on the exact routes: the streaming projection (same numerics, tuned for T <= 16)
+  if (tokens <= kDecTok && path != FB_FP8_PATH_A8)
+    return fb_linear_fp8_decode(x_bf16, tokens, w_codes, w_scales, w_scales_dtype, n, k, epilogue, workspace,
+                                workspace_bytes, stream);
+  const int kind = epilogue->kind;
+  if (kind < FB_EPI_STORE_BF16 || kind > FB_EPI_SHARED_SCALE) return invalid("linear_fp8: unknown epilogue");
   if (n <= 0 || k <= 0 || n % 64 || k % BK)
     return invalid("linear_fp8: unsupported shape (n must be a multiple of 64, k of 128)");
-  if ((reinterpret_cast<uintptr_t>(w_codes) | reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(out_bf16)) & 15)
-    return invalid("linear_fp8: x, weight codes and out must be 16-byte aligned");
+  if (kind == FB_EPI_SWIGLU && n % 128) return invalid("linear_fp8: SwiGlu needs n %% 128 == 0");
+  if (kind == FB_EPI_GR_WRITE && (!epilogue->inj || (reinterpret_cast<uintptr_t>(epilogue->inj) & 15)))
+    return invalid("linear_fp8: GrWrite needs inj fp32 [tokens][4], 16-byte aligned");
+  if (kind == FB_EPI_SHARED_SCALE && !epilogue->gate_logit) return invalid("linear_fp8: SharedScale needs gate_logit");
+  if ((reinterpret_cast<uintptr_t>(w_codes) | reinterpret_cast<uintptr_t>(x_bf16) |
+       reinterpret_cast<uintptr_t>(epilogue->out) | reinterpret_cast<uintptr_t>(w_scales)) & 15)
+    return invalid("linear_fp8: x, weight codes, row scales and out must be 16-byte aligned");
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
       workspace_bytes < fb_linear_fp8_workspace_bytes(n, k, tokens))
     return invalid("linear_fp8: workspace missing, misaligned (256 B) or smaller than fb_linear_fp8_workspace_bytes");
+  const int pieces = path == FB_FP8_PATH_A8 ? 1 : 2;
   uint8_t* a_codes = static_cast<uint8_t*>(workspace);
-  float* a_scales = reinterpret_cast<float*>(a_codes + align256(size_t(tokens) * size_t(k)));
+  uint8_t* a_lo = pieces == 2 ? a_codes + size_t(tokens) * size_t(k) : nullptr;  // directly behind: one tensor map
+  float* a_scales = reinterpret_cast<float*>(a_codes + align256(size_t(2) * size_t(tokens) * size_t(k)));
   uint32_t* status = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a_scales) + align256(size_t(tokens) * 4));
-  int32_t st = fb_fp8_quantize_tokens(x_bf16, tokens, k, a_codes, a_scales, stream);
+  fp8_quantize_tokens_kernel<<<tokens, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x_bf16), k, a_codes,
+                                                                    a_lo, a_scales);
+  int32_t st = check_launch("linear_fp8: activation pieces");
   if (st) return st;
   static PerDeviceOnce once;
   const cudaError_t attr = per_device_once(once, [] {
-    cudaError_t a = opt_in_smem(fp8_gemm_kernel<false>, kGemmSmem);
-    if (a == cudaSuccess) a = opt_in_smem(fp8_gemm_kernel<true>, kGemmSmem);
-    if (a == cudaSuccess) a = opt_in_smem(fp8_gemm_pair_kernel<false>, kGemmSmem2);
-    if (a == cudaSuccess) a = opt_in_smem(fp8_gemm_pair_kernel<true>, kGemmSmem2);
+    cudaError_t a = opt_in_smem(fp8_gemm_kernel<1>, kGemmSmem);
+    if (a == cudaSuccess) a = opt_in_smem(fp8_gemm_kernel<2>, kGemmSmem);
+    if (a == cudaSuccess) a = opt_in_smem(fp8_gemm_pair_kernel<1>, kGemmSmem2);
+    if (a == cudaSuccess) a = opt_in_smem(fp8_gemm_pair_kernel<2>, kGemmSmem2);
     return a;
   });
   if (attr != cudaSuccess) {
@@ -1115,29 +1277,40 @@ int32_t fb_linear_fp8(const void* x_bf16, int32_t tokens, const uint8_t* w_codes
   static const bool force_single = getenv("FB_FP8_SINGLE_CTA") != nullptr;
   const bool pair = tokens >= BM2 && !force_single;
   CUtensorMap map_a, map_b;
-  if (!make_map_u8(&map_a, a_codes, tokens, k, 128) || !make_map_u8(&map_b, w_codes, n, k, pair ? 128 : BN)) {
+  if (!make_map_u8(&map_a, a_codes, int64_t(pieces) * tokens, k, 128) || !make_map_u8(&map_b, w_codes, n, k, 128)) {
     set_error("linear_fp8: cuTensorMapEncodeTiled failed");
     return int32_t(cudaErrorInvalidValue);
   }
+  GemmArgs ga;
+  ga.act_scale = a_scales;
+  ga.w_scale = w_scales;
+  ga.out = epilogue->out;
+  ga.inj = epilogue->inj;
+  ga.gate_logit = epilogue->gate_logit;
+  ga.status = status;
+  ga.scale_bf16 = w_scales_dtype == FB_DT_BF16;
+  ga.kind = kind;
+  ga.gate_stride = epilogue->gate_stride;
+  ga.M = tokens;
+  ga.N = n;
+  ga.K = k;
+  ga.lo_row0 = tokens;
+  const int n_tiles = kind == FB_EPI_SWIGLU ? ((n >> 1) + 127) / 128 : (n + BN - 1) / BN;
   if (pair) {
-    const int work = ((tokens + BM2 - 1) / BM2) * ((n + BN - 1) / BN);
+    const int work = ((tokens + BM2 - 1) / BM2) * n_tiles;
     const int pairs = work < pair_count() ? work : pair_count();
-    if (w_scales_dtype == FB_DT_BF16)
-      fp8_gemm_pair_kernel<true><<<2 * pairs, kThreads, kGemmSmem2, as_stream(stream)>>>(
-          map_a, map_b, a_scales, w_scales, static_cast<__nv_bfloat16*>(out_bf16), tokens, n, k, status);
+    if (pieces == 2)
+      fp8_gemm_pair_kernel<2><<<2 * pairs, kThreads, kGemmSmem2, as_stream(stream)>>>(map_a, map_b, ga);
     else
-      fp8_gemm_pair_kernel<false><<<2 * pairs, kThreads, kGemmSmem2, as_stream(stream)>>>(
-          map_a, map_b, a_scales, w_scales, static_cast<__nv_bfloat16*>(out_bf16), tokens, n, k, status);
+      fp8_gemm_pair_kernel<1><<<2 * pairs, kThreads, kGemmSmem2, as_stream(stream)>>>(map_a, map_b, ga);
     return check_launch("linear_fp8");
   }
-  const int m_tiles = (tokens + BM - 1) / BM, n_tiles = (n + BN - 1) / BN;
+  const int m_tiles = (tokens + BM - 1) / BM;
   const int grid = m_tiles * n_tiles < sm_count() ? m_tiles * n_tiles : sm_count();
-  if (w_scales_dtype == FB_DT_BF16)
-    fp8_gemm_kernel<true><<<grid, kThreads, kGemmSmem, as_stream(stream)>>>(
-        map_a, map_b, a_scales, w_scales, static_cast<__nv_bfloat16*>(out_bf16), tokens, n, k, status);
+  if (pieces == 2)
+    fp8_gemm_kernel<2><<<grid, kThreads, kGemmSmem, as_stream(stream)>>>(map_a, map_b, ga);
   else
-    fp8_gemm_kernel<false><<<grid, kThreads, kGemmSmem, as_stream(stream)>>>(
-        map_a, map_b, a_scales, w_scales, static_cast<__nv_bfloat16*>(out_bf16), tokens, n, k, status);
+    fp8_gemm_kernel<1><<<grid, kThreads, kGemmSmem, as_stream(stream)>>>(map_a, map_b, ga);
   return check_launch("linear_fp8");
 }
 

@@ -67,6 +67,7 @@ class LinearEpilogue(C.Structure):
 
 
 EPI_STORE_BF16, EPI_STORE_F32, EPI_GR_WRITE, EPI_SWIGLU, EPI_SHARED_SCALE = range(5)
+FP8_PATH_AUTO, FP8_PATH_A16, FP8_PATH_A8 = range(3)
 
 
 class EpPeers(C.Structure):
@@ -119,7 +120,8 @@ _SIGNATURES = {
     "fb_moe_layer_decode_static_status": (_I32, [_P, _P]),
     "fb_ep_set_wait_limit": (None, [C.c_uint32]),
     "fb_linear_fp8_workspace_bytes": (C.c_size_t, [_I32, _I32, _I32]),
-    "fb_linear_fp8": (_I32, [_P, _I32, _P, _P, _I32, _I32, _I32, _P, _P, C.c_size_t, _P]),
+    "fb_linear_fp8": (_I32, [_P, _I32, _P, _P, _I32, _I32, _I32, C.POINTER(LinearEpilogue), _P, C.c_size_t, _P, _I32]),
+    "fb_fp8_split_tokens": (_I32, [_P, _I32, _I32, _P, _P, _P, _P]),
     "fb_fp8_quantize_tokens": (_I32, [_P, _I32, _I32, _P, _P, _P]),
     "fb_linear_fp8_decode_workspace_bytes": (C.c_size_t, [_I32, _I32]),
     "fb_linear_fp8_decode": (_I32, [_P, _I32, _P, _P, _I32, _I32, _I32, C.POINTER(LinearEpilogue), _P, C.c_size_t, _P]),

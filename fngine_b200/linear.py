@@ -23,13 +23,18 @@ def linear_fp8_workspace(weight, max_tokens, device="cuda"):
     return buf[off:off + n]
 
 
-def linear_fp8(x, weight, out, workspace):
-    """out[t][n] = bf16((x[t] . W[n]) * scale[n]); x bf16 [T][k], out bf16 [T][n]."""
-    assert x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and x.is_contiguous() and out.is_contiguous()
+def linear_fp8(x, weight, out, workspace, path=L.FP8_PATH_AUTO):
+    """linear_fp8 (linear.h:137-139 of the reference): x bf16 [T][k]; `out` is an epilogue (store_bf16,
+    store_f32, gr_write, swiglu, shared_scale) or, as a shorthand for store_bf16, a bf16 [T][n] tensor.
+    path: FP8_PATH_AUTO / FP8_PATH_A16 = exact activations (the reference's default), FP8_PATH_A8 =
+    one E4M3 code per activation (faster, 1-4 % rms noise)."""
+    import ctypes
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == weight.k
+    epi = store_bf16(out) if isinstance(out, torch.Tensor) else out
     dt = L.DT_BF16 if weight.scales.dtype == torch.bfloat16 else L.DT_F32
     L.check(L.load().fb_linear_fp8(x.data_ptr(), x.shape[0], weight.codes.data_ptr(), weight.scales.data_ptr(), dt,
-                                   weight.n, weight.k, out.data_ptr(), workspace.data_ptr(), workspace.numel(),
-                                   torch.cuda.current_stream().cuda_stream), "linear_fp8")
+                                   weight.n, weight.k, ctypes.byref(epi), workspace.data_ptr(), workspace.numel(),
+                                   torch.cuda.current_stream().cuda_stream, path), "linear_fp8")
 
 
 def _epilogue(kind, gate_stride, out, inj=None, gate_logit=None):
@@ -99,3 +104,14 @@ def fp8_quantize_tokens(x):
     L.check(L.load().fb_fp8_quantize_tokens(x.data_ptr(), T, k, codes.data_ptr(), scales.data_ptr(),
                                             torch.cuda.current_stream().cuda_stream), "fp8_quantize_tokens")
     return codes, scales
+
+
+def fp8_split_tokens(x):
+    """The two E4M3 pieces and the power-of-two scale of the exact route: x == scale * (hi + lo)."""
+    T, k = x.shape
+    hi = torch.empty(T, k, dtype=torch.uint8, device=x.device)
+    lo = torch.empty(T, k, dtype=torch.uint8, device=x.device)
+    scales = torch.empty(T, dtype=torch.float32, device=x.device)
+    L.check(L.load().fb_fp8_split_tokens(x.data_ptr(), T, k, hi.data_ptr(), lo.data_ptr(), scales.data_ptr(),
+                                         torch.cuda.current_stream().cuda_stream), "fp8_split_tokens")
+    return hi, lo, scales

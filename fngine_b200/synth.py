@@ -95,6 +95,16 @@ def router_weights(seed, rows=512, hidden=2560, std=0.02):
     return to_bf16_bits((normal(seed, rows * hidden) * std).astype(np.float32)).reshape(rows, hidden)
 
 
+def zipf_router_bias(seed, n_experts=512, exponent=1.1, spread=0.41):
+    """Router-logit bias that makes expert popularity follow Zipf(exponent) over a seeded permutation of
+    the experts: bias[perm[r]] = -exponent * spread * ln(r + 1). With unit-variance logit noise spread =
+    0.41 gives a fitted log-log slope of pairs against rank of -exponent. float32 [n_experts]."""
+    order = np.argsort(splitmix_words(seed, 0, n_experts), kind="stable")
+    bias = np.empty(n_experts, dtype=np.float32)
+    bias[order] = (-exponent * spread * np.log(np.arange(1, n_experts + 1, dtype=np.float64))).astype(np.float32)
+    return bias
+
+
 def fp8_row_weight(seed, n, k):
     """FP8-row weight of the dense-GEMM benchmark definition: values ~ N(0,1) clipped to +-448 and
     rounded to E4M3FN (nearest even), one fp32 scale per row ~ U(0.001, 0.01).

@@ -319,41 +319,33 @@ int32_t fb_moe_layer_decode_static(const void* router_w_bf16, const fb_moe_exper
 int32_t fb_moe_layer_decode_static_status(uint32_t* status_host, void* stream);
 
 /* ---------------------------------------------------------------- FP8-row dense projection
- * Fp8RowWeight + linear_fp8 with the StoreBf16 epilogue, src/kernels/linear/linear.h:57-62, :137-139:
- * out[t][n] = bf16((x[t] . W[n]) * scale[n]), W = E4M3FN codes [n][k] (16-byte aligned) with one
- * scale per row. This implementation is the reference's "A8" path (linear.h:32-37): each token is
- * quantized to E4M3 with a per-token fp32 scale max|x|/448 into the workspace, then an
- * E4M3 x E4M3 tensor-core GEMM (tcgen05, fp32 accumulation in tensor memory) runs and the epilogue
- * multiplies by act_scale[t] * row_scale[n]. Row scales may be fp32 (FB_DT_F32) or bf16 (FB_DT_BF16,
- * the reference's pack format). Shapes: any n % 64 == 0, k % 128 == 0 (the reference's closed
- * registry, linear_fp8.cpp:19-24, is not enforced). Bad arguments return cudaErrorInvalidValue where
- * the reference throws std::invalid_argument (linear_fp8.cpp:83-95). */
-/* linear_fp8_workspace_bytes, src/kernels/linear/linear.h:132. */
-size_t fb_linear_fp8_workspace_bytes(int32_t n, int32_t k, int32_t max_tokens);
-int32_t fb_linear_fp8(const void* x_bf16, int32_t tokens, const uint8_t* w_codes, const void* w_scales,
-                      int32_t w_scales_dtype, int32_t n, int32_t k, void* out_bf16, void* workspace,
-                      size_t workspace_bytes, void* stream);
-/* The activation quantizer alone (fp8_a8_quantize_kernel, src/kernels/linear/fp8/fp8_a8.cu:22-69):
- * codes [tokens][k], scales [tokens]; bit-identical to the host statement in
- * tests/kernels/linear/linear_ref.h:99-107 of the reference. */
-int32_t fb_fp8_quantize_tokens(const void* x_bf16, int32_t tokens, int32_t k, uint8_t* codes, float* scales,
-                               void* stream);
-
-/* linear_fp8 at decode width, the reference's "A16" path for T <= 16 (src/kernels/linear/linear.h:27-31,
- * :137-139; fp8/fp8_gemv.cuh, fp8/fp8_a16_ksplit_mma.cuh): bf16 activations are kept exactly, E4M3
- * weights are used exactly, fp32 accumulation, one multiplication by the row scale, then the
- * epilogue (LinearEpilogue / LinearEpilogueParams, linear.h:64-103):
+ * Fp8RowWeight + linear_fp8, src/kernels/linear/linear.h:57-62, :116-139:
+ *   out = epilogue((x[t] . W[n]) * scale[n]), W = E4M3FN codes [n][k] (16-byte aligned) with one scale
+ * per row, fp32 (FB_DT_F32) or bf16 (FB_DT_BF16, the reference's pack format). x is bf16 [tokens][k].
+ * Epilogues (LinearEpilogue / LinearEpilogueParams, linear.h:64-103):
  *   FB_EPI_STORE_BF16    out bf16 [T][n]
  *   FB_EPI_STORE_F32     out fp32 [T][n]
  *   FB_EPI_GR_WRITE      out = X fp32 [T][4][n], X[t][s][r] += inj[t][s] * acc[t][r]   (inj fp32 [T][4])
  *   FB_EPI_SWIGLU        out = h bf16 [T][n/2], h[t][j] = silu(acc[t][j]) * acc[t][n/2 + j]
  *   FB_EPI_SHARED_SCALE  out = y fp32 [T][n], y[t][r] = sigmoid(gate_logit[t * gate_stride]) * acc[t][r]
- * (SiluQuarter and GrMix belong to the residual-stream mixer and are not provided.) tokens 1..16,
- * k % 128 == 0, n % 8 == 0; any such shape is accepted (the closed registry of linear_fp8.cpp:19-24
- * is not enforced). Every output element is written once, by one thread, after the complete K
- * reduction, in an order that depends only on the shape: repeated calls are bitwise identical
- * (linear.h:39-41). Bad arguments return cudaErrorInvalidValue where the reference throws. */
+ * (SiluQuarter and GrMix belong to the residual-stream mixer and are not provided.)
+ * Paths (Fp8LinearPath, linear.h:116-120):
+ *   FB_FP8_PATH_AUTO / FB_FP8_PATH_A16  exact activations, the reference's default at every T
+ *     (src/kernels/linear/fp8/fp8_shapes.h:39-43). T <= 16 runs fb_linear_fp8_decode. Above, each token
+ *     is scaled by a power of two and written into the workspace as the sum of two E4M3 numbers
+ *     (hi = rne(x), lo = x - hi: a bf16 value has eight significant bits, four fit each piece), and the
+ *     tcgen05 E4M3 x E4M3 GEMM adds both products into one fp32 accumulator in tensor memory: the
+ *     numerics of the reference's bf16-activation GEMM (elements below 2^-9 of their row's maximum
+ *     lose bits under 2^-17 of that maximum) without widening the weights.
+ *   FB_FP8_PATH_A8  one E4M3 code per activation with a per-token fp32 scale max|x|/448
+ *     (linear.h:32-37): half the tensor-core work, 1-4 % rms output noise; only on request.
+ * Shapes: T > 16 needs n % 64 == 0 (n % 128 for SwiGlu), k % 128 == 0; T <= 16 as fb_linear_fp8_decode.
+ * The reference's closed registry (linear_fp8.cpp:19-24) is not enforced. Every output element is written
+ * once, by one thread, after the complete K reduction, in an order fixed by the shape: repeated calls
+ * are bitwise identical (linear.h:39-44). Bad arguments return cudaErrorInvalidValue where the
+ * reference throws std::invalid_argument (linear_fp8.cpp:83-95). */
 enum { FB_EPI_STORE_BF16 = 0, FB_EPI_STORE_F32 = 1, FB_EPI_GR_WRITE = 2, FB_EPI_SWIGLU = 3, FB_EPI_SHARED_SCALE = 4 };
+enum { FB_FP8_PATH_AUTO = 0, FB_FP8_PATH_A16 = 1, FB_FP8_PATH_A8 = 2 };
 typedef struct fb_linear_epilogue {
   int32_t kind;            /* FB_EPI_* */
   int32_t gate_stride;     /* SharedScale */
@@ -361,6 +353,28 @@ typedef struct fb_linear_epilogue {
   const float* inj;        /* GrWrite */
   const float* gate_logit; /* SharedScale */
 } fb_linear_epilogue;
+/* linear_fp8_workspace_bytes, src/kernels/linear/linear.h:132: enough for any T in [1, max_tokens] on
+ * any path (two activation pieces [2][T][k] + token scales, or the decode-width scratch). */
+size_t fb_linear_fp8_workspace_bytes(int32_t n, int32_t k, int32_t max_tokens);
+/* linear_fp8, src/kernels/linear/linear.h:137-139. `workspace` is 256-byte aligned. */
+int32_t fb_linear_fp8(const void* x_bf16, int32_t tokens, const uint8_t* w_codes, const void* w_scales,
+                      int32_t w_scales_dtype, int32_t n, int32_t k, const fb_linear_epilogue* epilogue,
+                      void* workspace, size_t workspace_bytes, void* stream, int32_t path);
+/* The A8 activation quantizer alone (fp8_a8_quantize_kernel, src/kernels/linear/fp8/fp8_a8.cu:22-69):
+ * codes [tokens][k], scales [tokens]; bit-identical to the host statement in
+ * tests/kernels/linear/linear_ref.h:99-107 of the reference. */
+int32_t fb_fp8_quantize_tokens(const void* x_bf16, int32_t tokens, int32_t k, uint8_t* codes, float* scales,
+                               void* stream);
+/* The two-piece split of the exact route alone (no reference counterpart; a parity probe):
+ * scales[t] = 2^(floor(log2 max|x[t]|) - 7), codes_hi = rne_e4m3(x / scale),
+ * codes_lo = rne_e4m3(x / scale - hi). */
+int32_t fb_fp8_split_tokens(const void* x_bf16, int32_t tokens, int32_t k, uint8_t* codes_hi, uint8_t* codes_lo,
+                            float* scales, void* stream);
+
+/* linear_fp8 at decode width, the reference's "A16" path for T <= 16 (src/kernels/linear/linear.h:27-31,
+ * :137-139; fp8/fp8_gemv.cuh, fp8/fp8_a16_ksplit_mma.cuh): bf16 activations are kept exactly (three
+ * E5M2 pieces per value), E4M3 weights are used exactly, fp32 accumulation, one multiplication by the
+ * row scale, then the epilogue. tokens 1..16, k % 128 == 0, n % 8 == 0 (n % 16 for SwiGlu). */
 size_t fb_linear_fp8_decode_workspace_bytes(int32_t n, int32_t k);
 int32_t fb_linear_fp8_decode(const void* x_bf16, int32_t tokens, const uint8_t* w_codes, const void* w_scales,
                              int32_t w_scales_dtype, int32_t n, int32_t k, const fb_linear_epilogue* epilogue,

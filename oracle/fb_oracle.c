@@ -555,3 +555,29 @@ float fbo_quantize_token_e4m3(const uint16_t* x, int64_t k, uint8_t* codes) {
   for (int64_t j = 0; j < k; ++j) codes[j] = fbo_e4m3_satfinite(fbo_bf16_to_fp32(x[j]) * inv);
   return scale;
 }
+
+// The exact-activation route of this repository's FP8-row GEMM above 16 tokens (no counterpart in the
+// reference, whose bf16-activation GEMM widens the weights instead): a token is scaled by the power of
+// two that puts its largest magnitude in [128, 256) and every value is written as hi + lo with
+// hi = rne_e4m3(v), lo = rne_e4m3(v - hi). x: raw bf16 bits. Returns the scale (0 for a row of zeros or
+// non-finite values: all codes 0).
+float fbo_split_token_e4m3x2(const uint16_t* x, int64_t k, uint8_t* hi, uint8_t* lo) {
+  float mx = 0.0f;
+  for (int64_t j = 0; j < k; ++j) mx = fmaxf(mx, fabsf(fbo_bf16_to_fp32(x[j])));
+  int e = 0;
+  float scale = 0.0f, inv = 0.0f;
+  if (mx > 0.0f && isfinite(mx)) {
+    (void)frexpf(mx, &e);  // mx = f * 2^e, f in [0.5, 1): 2^(e-1) <= mx < 2^e
+    e -= 1;
+    if (e - 7 >= -126 && 7 - e >= -126) {
+      scale = ldexpf(1.0f, e - 7);
+      inv = ldexpf(1.0f, 7 - e);
+    }
+  }
+  for (int64_t j = 0; j < k; ++j) {
+    const float v = fbo_bf16_to_fp32(x[j]) * inv;
+    hi[j] = fbo_e4m3_satfinite(v);
+    lo[j] = fbo_e4m3_satfinite(v - fbo_e4m3_to_float(hi[j]));
+  }
+  return scale;
+}

@@ -57,6 +57,8 @@ def port():
         lib.fbo_e4m3_satfinite.argtypes = [C.c_float]
         lib.fbo_quantize_token_e4m3.restype = C.c_float
         lib.fbo_quantize_token_e4m3.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
+        lib.fbo_split_token_e4m3x2.restype = C.c_float
+        lib.fbo_split_token_e4m3x2.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
         lib.fbo_row_bytes.restype = C.c_int64
         lib.fbo_dequant_rows.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]
         lib.fbo_dequant_rows_bf16.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]
@@ -272,6 +274,19 @@ def quantize_tokens_e4m3(x_bf16):
     for t in range(T):
         scales[t] = port().fbo_quantize_token_e4m3(_ptr(x[t]), K, _ptr(codes[t]))
     return codes, scales
+
+
+def split_tokens_e4m3x2(x_bf16):
+    """uint16 bf16 bits [T][K] -> (hi uint8 [T][K], lo uint8 [T][K], scales float32 [T]): the two-piece
+    statement of the exact route (scale a power of two, hi = rne_e4m3, lo = rne_e4m3 of the remainder)."""
+    x = np.ascontiguousarray(x_bf16, dtype=np.uint16)
+    T, K = x.shape
+    hi = np.empty((T, K), dtype=np.uint8)
+    lo = np.empty((T, K), dtype=np.uint8)
+    scales = np.empty(T, dtype=np.float32)
+    for t in range(T):
+        scales[t] = port().fbo_split_token_e4m3x2(_ptr(x[t]), K, _ptr(hi[t]), _ptr(lo[t]))
+    return hi, lo, scales
 
 
 def linear_fp8_a16(x_bf16, codes, scales, kind="store", gate_logit=None):

@@ -182,3 +182,71 @@ def test_expert_parallel_shards_match_single_gpu(world):
     assert ws.status() == 0
     err = max(rel_l2(got[t], want[t]) for t in range(T))
     assert err <= 1e-5, err
+
+
+def test_prefill_layer_at_8192_tokens_with_zipf_routing():
+    """The prefill-stack benchmark's own size and routing: 8192 bf16 tokens, router N(0, 0.02) plus the
+    Zipf(1.1) popularity bias, so the busiest expert takes several thousand pairs (many 256-token units)
+    and the tail experts a handful. 64 sampled tokens (half of them routed to the busiest expert) are
+    checked against the CPU oracle in the prefill numerics: ids exact, weights 1e-6, down + combine fed
+    with the GPU's own h within 1e-3, end to end reported and held to the bars of the smaller cases."""
+    torch = _torch()
+    from fngine_b200 import moe, prefill
+    T, inter, seed = 8192, 512, 5000
+    layer = moe.synth_layer(IQ3_S, IQ3_S, inter, 512, seed)
+    ws = prefill.PrefillWorkspace(T, inter)
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    router = (torch.randn(512, H, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    bias = torch.from_numpy(synth.zipf_router_bias(1234)).cuda()
+    xd = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
+    logits = ((xd @ router.t()).float() + bias).contiguous()
+    y = run_prefill(torch, layer, ws, logits, xd, T)
+    assert ws.status() == 0 and bool(torch.isfinite(y).all())
+    counts = ws.ints(ws.ws.expert_count, 512)
+    busiest = int(np.argmax(counts))
+    assert counts.sum() == T * 10 and counts[busiest] > 2048  # spans many 256-token units
+    ids_all = ws.ints(ws.ws.topk_expert, T * 10).reshape(T, 10)
+    w_all = ws.floats(ws.ws.topk_weight, T * 10).reshape(T, 10)
+    tpair = ws.ints(ws.ws.token_pair, T * 10).reshape(T, 10)
+    on_busiest = np.nonzero((ids_all == busiest).any(axis=1))[0]
+    rng = np.random.default_rng(7)
+    sample = np.unique(np.concatenate([rng.choice(on_busiest, 32, replace=False), rng.choice(T, 32, replace=False),
+                                       np.array([0, T - 1])]))
+    lg = logits[torch.from_numpy(sample).cuda()].cpu().numpy()
+    ids, w = O.topk(np.ascontiguousarray(lg[:, :512]))
+    assert np.array_equal(ids_all[sample], ids) and np.max(np.abs(w_all[sample] - w)) <= 1e-6
+    xb = xd[torch.from_numpy(sample).cuda()].view(torch.int16).cpu().numpy().view(np.uint16)
+    hbits = ws.h(T * 10)
+    yg = y[torch.from_numpy(sample).cuda()].cpu().numpy()
+    gate_bytes = inter * O.row_bytes(IQ3_S, H)
+    by_expert = {}
+    for i in range(len(sample)):
+        for k in range(10):
+            by_expert.setdefault(int(ids[i, k]), []).append((i, k))
+    y_full = {}
+    y_down = {}
+    for e, lst in sorted(by_expert.items()):
+        blob = synth.expert_blob(IQ3_S, IQ3_S, inter, seed, e)
+        rows = np.array([i for i, _ in lst])
+        _, ye = O.expert_ffn_bf16(IQ3_S, IQ3_S, H, inter, blob, xb[rows], lib=O.ref())
+        hg = np.stack([hbits[tpair[sample[i], k]] for i, k in lst])
+        yd = O.down_bf16(IQ3_S, H, inter, blob[2 * gate_bytes:], hg)
+        for j, (i, k) in enumerate(lst):
+            y_full[(i, e)] = ye[j]
+            y_down[(i, e)] = yd[j]
+    errs, errs_dn = [], []
+    for i in range(len(sample)):
+        want = np.zeros(H, dtype=np.float32)
+        want_dn = np.zeros(H, dtype=np.float32)
+        for e in sorted(ids[i].tolist()):  # ascending expert id, the reference's order
+            wt = np.float32(w[i, list(ids[i]).index(e)])
+            want = want + wt * y_full[(i, e)]
+            want_dn = want_dn + wt * y_down[(i, e)]
+        errs.append(rel_l2(yg[i], want))
+        errs_dn.append(rel_l2(yg[i], want_dn))
+    print("prefill 8192 tokens, Zipf(1.1): busiest expert %d with %d pairs, median expert %d; %d sampled tokens: "
+          "down + combine max rel L2 %.2e (bar 1e-3), end to end median %.2e max %.2e" % (
+              busiest, counts[busiest], int(np.median(counts)), len(sample), max(errs_dn), float(np.median(errs)),
+              max(errs)))
+    assert max(errs_dn) <= 1e-3, max(errs_dn)
+    assert float(np.median(errs)) <= 1e-3 and max(errs) <= 1e-2, (float(np.median(errs)), max(errs))
