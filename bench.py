@@ -164,10 +164,11 @@ def workload_config(args, layers_per_step):
             "activation_format": "Q8_K (reference CPU tier numerics)"}
 
 
-# DRAM bytes moved / algorithmic bytes of one gate_up_kernel launch, from an ncu capture of layer 0 of the
-# benchmark workload (profiles/gate_up_down_iq3s_decode_b16.md): traffic grows with the expert count like the
-# algorithmic bytes do, so the ratio carries over to the other layers.
-GATE_UP_DRAM_TRAFFIC_RATIO = 160.57 / 156.85
+# DRAM bytes moved / algorithmic bytes of one launch of the expert kernel (gate/up + down of every routed
+# expert), from an ncu capture of layer 0 of the benchmark workload (139 experts: 235.05 MB read + 4.24 MB
+# written for 234.85 MB of expert bytes): traffic grows with the expert count like the algorithmic bytes do, so
+# the ratio carries over to the other layers.
+EXPERTS_DRAM_TRAFFIC_RATIO = 239.30 / 234.85
 
 
 def iq4nl_section(torch, steps, n_layers=4):
@@ -530,26 +531,40 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
 
-    # per-kernel device times over the same steps (gate/up is the dominant kernel)
+    # device time of the dominant kernel over the same steps: the expert kernel (gate/up and down tiles of every
+    # routed expert in one persistent launch), bracketed by events on the launching stream; then the same two
+    # projections as the separate gate/up and down launches of the reference's call sequence
     evs = []
     for _ in range(args.steps):
         for l in range(Lr):
             moe.router_logits(routers[l], xs[l], ws.logits)
             moe.moe_select_publish(ws.logits, xs[l], None, 0, None, None, B, ws)
-            a, b, c, d = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+            a, b = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+            a.record()
+            moe.moe_hot_experts(layers[l], B, ws)
+            b.record()
+            moe.moe_combine(ws, None, None, 0, None, None, None, y, B)
+            evs.append((l, a, b))
+    torch.cuda.synchronize()
+    ex_ms = [a.elapsed_time(b) for (_, a, b) in evs]
+    ex_bytes = [distinct[l] * BLOB for (l, _a, _b) in evs]
+    evs2 = []
+    for _ in range(min(args.steps, 4)):
+        for l in range(Lr):
+            moe.router_logits(routers[l], xs[l], ws.logits)
+            moe.moe_select_publish(ws.logits, xs[l], None, 0, None, None, B, ws)
+            a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
             a.record()
             moe.moe_hot_gate_up(layers[l], B, ws)
             b.record()
             moe.moe_hot_down(layers[l], B, ws)
             c.record()
-            moe.moe_combine(ws, None, None, 0, None, None, None, y, B)
-            d.record()
-            evs.append((l, a, b, c, d))
+            evs2.append((l, a, b, c))
     torch.cuda.synchronize()
-    gu_ms = [a.elapsed_time(b) for (_, a, b, _, _) in evs]
-    dn_ms = [b.elapsed_time(c) for (_, _, b, c, _) in evs]
-    gu_bytes = [distinct[l] * (BLOB * 2 // 3) for (l, *_r) in evs]
-    dn_bytes = [distinct[l] * (BLOB // 3) for (l, *_r) in evs]
+    gu_ms = [a.elapsed_time(b) for (_, a, b, _) in evs2]
+    dn_ms = [b.elapsed_time(c) for (_, _, b, c) in evs2]
+    gu_bytes = [distinct[l] * (BLOB * 2 // 3) for (l, *_r) in evs2]
+    dn_bytes = [distinct[l] * (BLOB // 3) for (l, *_r) in evs2]
 
     # end to end through the host entry point: pinned host x in, host y out, every layer
     yh = torch.empty(B, HIDDEN, dtype=torch.float32).pin_memory()
@@ -630,7 +645,7 @@ def run_ours(args, rank, world, local_rank):
     fp8dec = fp8_decode_section(torch) if want("fp8dec") else None
     pre = prefill_section(torch, n_layers=args.prefill_layers) if want("prefill") else None
     peak, peak_src = peaks()
-    gu_ach = sum(gu_bytes) / (sum(gu_ms) * 1e-3) / 1e9
+    ex_ach = sum(ex_bytes) / (sum(ex_ms) * 1e-3) / 1e9
     value = step_bytes * args.steps / (ms * 1e-3) / 1e9
     line = {
         "metric": "iq3s_expert_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
@@ -640,16 +655,20 @@ def run_ours(args, rank, world, local_rank):
         "us_per_layer": ms / args.steps / Lr * 1e3,
         "distinct_experts_per_layer": distinct,
         "frac_of_hbm_peak": value / peak,
-        "roofline": {"bound": "hbm", "kernel": "gate_up_kernel<IQ3_S>", "achieved": gu_ach, "peak": peak,
-                     "unit": "GB/s", "frac": gu_ach / peak, "peak_source": peak_src,
-                     "traffic": GATE_UP_DRAM_TRAFFIC_RATIO * sum(gu_bytes) / len(gu_bytes),
-                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one gate_up_kernel launch on "
-                                       "layer 0 of this workload (160.57 MB for 156.85 MB algorithmic), scaled by the "
-                                       "expert count of each layer",
-                     "us_per_launch": sum(gu_ms) / len(gu_ms) * 1e3,
-                     "algorithmic_bytes_per_launch": sum(gu_bytes) / len(gu_bytes),
-                     "down_kernel": {"achieved": sum(dn_bytes) / (sum(dn_ms) * 1e-3) / 1e9,
-                                     "us_per_launch": sum(dn_ms) / len(dn_ms) * 1e3}},
+        "roofline": {"bound": "hbm", "kernel": "experts_iq3s_kernel (gate/up + down tiles of every routed expert, one launch)",
+                     "achieved": ex_ach, "peak": peak, "unit": "GB/s", "frac": ex_ach / peak, "peak_source": peak_src,
+                     "traffic": EXPERTS_DRAM_TRAFFIC_RATIO * sum(ex_bytes) / len(ex_bytes),
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on layer 0 of this "
+                                       "workload (239.30 MB for 234.85 MB algorithmic), scaled by the expert count of "
+                                       "each layer",
+                     "us_per_launch": sum(ex_ms) / len(ex_ms) * 1e3,
+                     "algorithmic_bytes_per_launch": sum(ex_bytes) / len(ex_bytes),
+                     "algorithmic_bytes": "distinct routed experts x 1,689,600 B (gate + up + down of an IQ3_S expert)",
+                     "as_separate_launches": {
+                         "gate_up": {"achieved": sum(gu_bytes) / (sum(gu_ms) * 1e-3) / 1e9,
+                                     "us_per_launch": sum(gu_ms) / len(gu_ms) * 1e3},
+                         "down": {"achieved": sum(dn_bytes) / (sum(dn_ms) * 1e-3) / 1e9,
+                                  "us_per_launch": sum(dn_ms) / len(dn_ms) * 1e3}}},
         "cpu_baseline": {"value": cpu_bytes / cpu_dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
                          "sample": "layer 0 of the same workload (batch %d, %d distinct experts), %d repetitions, "
                                    "%.2f ms each" % (B, distinct[0], reps, cpu_dt * 1e3)},
@@ -657,7 +676,7 @@ def run_ours(args, rank, world, local_rank):
                 "h2d_bytes_per_step": B * HIDDEN * 4 * Lr, "d2h_bytes_per_step": B * HIDDEN * 4 * Lr,
                 "ms_per_step": e2e_ms / args.steps,
                 "api": "fb_moe_layer_decode_host per layer: pinned host x in, host y out, stream wait inside"},
-        "gpu_launches": args.steps * Lr * 4,
+        "gpu_launches": args.steps * Lr * 3,
         "other_batches": other,
         "iq4nl_decode": iq4,
         "fp8_row_gemm": fp8,

@@ -69,6 +69,26 @@ __host__ __device__ constexpr int act_of(int fmt) { return fmt == FB_FMT_IQ3_S ?
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + expf(-g)) * u; }
 
+// Planar Q8_K rows: codes [k] | block scales float [k/256] (64 bytes reserved) | code sums of every 32
+// codes, int16 [k/32] (Q8_K's bsums added in pairs; the IQ3_S kernels use them, see moe_decode_iq3s.cuh).
+__host__ __device__ constexpr int q8k_asum_off(int k) { return k + 64; }
+
+// Stores block b of a planar Q8_K row from the calling warp's quantizer output (lane l holds codes
+// 8l..8l+7 of the block in q, pair_sum the sum of its 16-code group).
+__device__ __forceinline__ void store_q8k_block_planar(uint8_t* out, int k, int b, const int (&q)[8], int pair_sum,
+                                                       float d) {
+  const int lane = threadIdx.x & 31;
+  uint2 pk;
+  pk.x = uint32_t(uint8_t(q[0])) | (uint32_t(uint8_t(q[1])) << 8) | (uint32_t(uint8_t(q[2])) << 16) |
+         (uint32_t(uint8_t(q[3])) << 24);
+  pk.y = uint32_t(uint8_t(q[4])) | (uint32_t(uint8_t(q[5])) << 8) | (uint32_t(uint8_t(q[6])) << 16) |
+         (uint32_t(uint8_t(q[7])) << 24);
+  *reinterpret_cast<uint2*>(out + 256 * b + 8 * lane) = pk;
+  const int sum32 = pair_sum + __shfl_xor_sync(0xffffffffu, pair_sum, 2);  // lanes 4j..4j+3 hold sub-block j
+  if ((lane & 3) == 0) reinterpret_cast<int16_t*>(out + q8k_asum_off(k))[8 * b + (lane >> 2)] = int16_t(sum32);
+  if (lane == 0) reinterpret_cast<float*>(out + k)[b] = d;
+}
+
 // ------------------------------------------------------------------------------ activation rows
 // One row of k values -> planar codes + scales, by the calling block (any number of warps).
 // Q8_K: codes [k], scales float[k/256]. Q8_0: codes [k] (interleaved per block), scales float[k/32].
@@ -76,20 +96,13 @@ template <class LoadF>
 __device__ __forceinline__ void quantize_row_planar(int act, int k, LoadF load, uint8_t* out) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   if (act == FB_ACT_Q8_K) {
-    float* scales = reinterpret_cast<float*>(out + k);
     for (int b = warp; b < k / 256; b += warps) {
       float v[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] = load(256 * b + 8 * lane + i);
       int q[8], ps;
       const float d = q8k_block_warp(v, q, ps);
-      uint2 pk;
-      pk.x = uint32_t(uint8_t(q[0])) | (uint32_t(uint8_t(q[1])) << 8) | (uint32_t(uint8_t(q[2])) << 16) |
-             (uint32_t(uint8_t(q[3])) << 24);
-      pk.y = uint32_t(uint8_t(q[4])) | (uint32_t(uint8_t(q[5])) << 8) | (uint32_t(uint8_t(q[6])) << 16) |
-             (uint32_t(uint8_t(q[7])) << 24);
-      *reinterpret_cast<uint2*>(out + 256 * b + 8 * lane) = pk;
-      if (lane == 0) scales[b] = d;
+      store_q8k_block_planar(out, k, b, q, ps, d);
     }
   } else {
     float* scales = reinterpret_cast<float*>(out + k);
@@ -512,13 +525,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
         }
         int qv[8], ps;
         const float d = q8k_block_warp(v, qv, ps);
-        uint2 pk;
-        pk.x = uint32_t(uint8_t(qv[0])) | (uint32_t(uint8_t(qv[1])) << 8) | (uint32_t(uint8_t(qv[2])) << 16) |
-               (uint32_t(uint8_t(qv[3])) << 24);
-        pk.y = uint32_t(uint8_t(qv[4])) | (uint32_t(uint8_t(qv[5])) << 8) | (uint32_t(uint8_t(qv[6])) << 16) |
-               (uint32_t(uint8_t(qv[7])) << 24);
-        *reinterpret_cast<uint2*>(out + 256 * b + 8 * lane) = pk;
-        if (lane == 0) scales[b] = d;
+        store_q8k_block_planar(out, H, b, qv, ps, d);
       } else {
         unsigned short dh;
         float xv1;
@@ -600,9 +607,33 @@ struct StageMeta {
   int item;        // work item
   int item_pair0;  // first pair of the item
   int item_tok;    // tokens of the item
-  int pad;
+  int seq;         // entry number of this CTA (the multi-stage rings check it)
   float wgt[kTT];  // routing weights of the pass's pairs (down)
 };
+
+// The part of the device work list a producer needs, copied to shared memory once per CTA: the
+// producer is a single thread, and a chain of dependent global loads per tile (visiting order ->
+// item -> its pairs -> their tokens and weights, about two microseconds) would pace the whole kernel.
+struct WorkCache {
+  int order[kMaxPairs];
+  int pair_begin[kMaxPairs + 1];
+  int slot[kMaxPairs];
+  int pair_token[kMaxPairs];
+  float pair_weight[kMaxPairs];
+};
+// Called by every thread of the block after the wait on the preceding kernel; caller synchronizes.
+__device__ __forceinline__ void work_cache_fill(const fb_moe_decode_workspace& ws, WorkCache& c, int n_items) {
+  const fb_moe_decode_work* work = ws.work;
+  for (int i = threadIdx.x; i < kMaxPairs; i += blockDim.x) {
+    const bool live = i < n_items;
+    c.order[i] = live ? ws.sched[kSchedOrderBase + i] : 0;
+    c.slot[i] = live ? work->item_slot[i] : 0;
+    c.pair_begin[i] = i <= n_items ? work->item_pair_begin[i] : 0;
+    c.pair_token[i] = work->pair_token[i];
+    c.pair_weight[i] = work->pair_weight[i];
+  }
+  if (threadIdx.x == 0) c.pair_begin[kMaxPairs] = n_items == kMaxPairs ? work->item_pair_begin[kMaxPairs] : 0;
+}
 
 struct Ring {
   uint64_t* full;   // [2] count 1 + tx bytes
@@ -633,9 +664,9 @@ __device__ __forceinline__ void ring_init(const Ring& r, int empty_count) {
 // Producer loop of one CTA (one thread): draws tiles from `counter`, stages every pass of each
 // tile through issue(meta, slot), and finally posts the end marker in both slots.
 template <class IssueF>
-__device__ __forceinline__ void producer_loop(const Ring& r, const fb_moe_decode_workspace& ws, int* counter,
-                                              int n_tiles, int tiles_per_item, int rows_per_tile, IssueF issue) {
-  const fb_moe_decode_work* work = ws.work;
+__device__ __forceinline__ void producer_loop(const Ring& r, const fb_moe_decode_workspace& ws, const WorkCache& wc,
+                                              int* counter, int n_tiles, int tiles_per_item, int rows_per_tile,
+                                              IssueF issue) {
   int i = 0;
   auto slot_free = [&](int s) -> bool {
     if (ring_aborted(r)) return false;
@@ -651,11 +682,11 @@ __device__ __forceinline__ void producer_loop(const Ring& r, const fb_moe_decode
     if (tile >= n_tiles) break;
     next = atomicAdd(counter, 1);
     const int pos = tile / tiles_per_item;
-    const int item = ws.sched[kSchedOrder + pos];
+    const int item = wc.order[pos];
     const int sub = tile - pos * tiles_per_item;
-    const int pb = work->item_pair_begin[item];
-    const int ntok = work->item_pair_begin[item + 1] - pb;
-    const int slot_id = work->item_slot[item];
+    const int pb = wc.pair_begin[item];
+    const int ntok = wc.pair_begin[item + 1] - pb;
+    const int slot_id = wc.slot[item];
     for (int tok0 = 0; tok0 < ntok; tok0 += kTT, ++i) {
       const int s = i & 1;
       if (!slot_free(s)) return;
@@ -667,7 +698,7 @@ __device__ __forceinline__ void producer_loop(const Ring& r, const fb_moe_decode
       m->item = item;
       m->item_pair0 = pb;
       m->item_tok = ntok;
-      for (int t = 0; t < kTT; ++t) m->wgt[t] = tok0 + t < ntok ? work->pair_weight[pb + tok0 + t] : 0.0f;
+      for (int t = 0; t < kTT; ++t) m->wgt[t] = tok0 + t < ntok ? wc.pair_weight[pb + tok0 + t] : 0.0f;
       issue(s, slot_id, sub, pb + tok0, min(kTT, ntok - tok0));
     }
   }
@@ -683,61 +714,19 @@ __device__ __forceinline__ void producer_loop(const Ring& r, const fb_moe_decode
 template <int FMT>
 struct GateUp;
 
-// IQ3_S: a tile is 32 intermediate rows (32 gate + 32 up rows of 1100 bytes), cut into ten tasks:
-// task k is block pair k%5 (220 bytes, word aligned, odd word stride between rows -> no bank
-// conflicts) of the 32 gate (k<5) or up (k>=5) rows, one row per lane. Sixteen consumer warps (four
-// per scheduler) draw tasks from a shared-memory ticket; the five partial sums of a row meet in
-// shared memory, where the warp that finishes the tile's last task adds them in a fixed order.
-template <>
-struct GateUp<FB_FMT_IQ3_S> {
-  static constexpr int kJ = 32, kRowBytes = 1100, kWarps = 16, kTasks = 10;
-  static constexpr int kAct = FB_ACT_Q8_K, kActBytes = H + 64;
-  static constexpr bool kGrid = true;
-  static constexpr int kPartialFloats = 2 * kTasks * kTT * 32;
-  static constexpr int kUpPad = 0;
-};
 // IQ4_NL: 32 intermediate rows of 1440 bytes per matrix, cut into sixteen tasks drawn from the same
-// ticket as the IQ3_S tasks: task k is rows 2k, 2k+1 of gate and of up, eight lanes per row, lane q
+// shared-memory ticket: task k is rows 2k, 2k+1 of gate and of up, eight lanes per row, lane q
 // taking the 18-byte blocks q, q + 8, ... (SwiGLU needs no cross-task reduction).
 template <>
 struct GateUp<FB_FMT_IQ4_NL> {
   static constexpr int kJ = 32, kRowBytes = 1440, kWarps = 16, kTasks = 16;
   static constexpr int kAct = FB_ACT_Q8_0, kActBytes = H + H / 8;
-  static constexpr bool kGrid = false;
   static constexpr int kPartialFloats = 0;
   // The up rows sit 64 bytes after the gate rows: a row is 360 words (8 mod 32), so with both
   // parts on the same bank phase the gate and the up lanes of a warp would collide pairwise; 16
   // words apart the 32 lanes' words fall in 32 different banks.
   static constexpr int kUpPad = 64;
 };
-
-template <int TT>
-__device__ __forceinline__ void iq3s_unit_dot(const uint32_t* unit, const uint32_t* grid_lane, const uint32_t* signtab,
-                                              const uint8_t* const (&actrow)[TT], int pair, int act_k,
-                                              float (&acc)[TT]) {
-  const int8_t* a0[TT];
-  const int8_t* a1[TT];
-#pragma unroll
-  for (int t = 0; t < TT; ++t) {
-    a0[t] = reinterpret_cast<const int8_t*>(actrow[t]) + 512 * pair;
-    a1[t] = a0[t] + 256;
-  }
-  int bs[TT];
-  iq3s_block_idot<true, TT>(unit, grid_lane, signtab, a0, bs);
-  const float d0 = ld_fp16<0>(unit);
-#pragma unroll
-  for (int t = 0; t < TT; ++t) {
-    const float da = reinterpret_cast<const float*>(actrow[t] + act_k)[2 * pair];
-    acc[t] = fmaf(float(bs[t]), d0 * da, acc[t]);
-  }
-  iq3s_block_idot<false, TT>(unit + 27, grid_lane, signtab, a1, bs);
-  const float d1 = ld_fp16<110>(unit);
-#pragma unroll
-  for (int t = 0; t < TT; ++t) {
-    const float da = reinterpret_cast<const float*>(actrow[t] + act_k)[2 * pair + 1];
-    acc[t] = fmaf(float(bs[t]), d1 * da, acc[t]);
-  }
-}
 
 // One 36-byte IQ4_NL unit (two blocks) against TT interleaved Q8_0 rows; ublk = index of the
 // unit's first block within the row.
@@ -811,14 +800,12 @@ __device__ __forceinline__ void iq4nl_block_dot(const uint8_t* row, int b, bool 
 
 // h of one finished work item -> planar activation rows for the down projection (one warp).
 __device__ __forceinline__ void quantize_item_h(const fb_moe_decode_workspace& ws, int pair_begin, int n_tok,
-                                                int down_act) {
+                                                int down_act, int I) {
   const int lane = threadIdx.x & 31;
-  const int I = ws.inter;
   for (int p = pair_begin; p < pair_begin + n_tok; ++p) {
     const float* h = ws.h + size_t(p) * I;
     uint8_t* out = ws.hq + size_t(p) * FB_HQ_STRIDE;
     if (down_act == FB_ACT_Q8_K) {
-      float* scales = reinterpret_cast<float*>(out + I);
       for (int b = 0; b < I / 256; ++b) {
         float v[8];
         const float4 a = __ldcg(reinterpret_cast<const float4*>(h + 256 * b + 8 * lane));
@@ -827,13 +814,7 @@ __device__ __forceinline__ void quantize_item_h(const fb_moe_decode_workspace& w
         v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
         int q[8], ps;
         const float d = q8k_block_warp(v, q, ps);
-        uint2 pk;
-        pk.x = uint32_t(uint8_t(q[0])) | (uint32_t(uint8_t(q[1])) << 8) | (uint32_t(uint8_t(q[2])) << 16) |
-               (uint32_t(uint8_t(q[3])) << 24);
-        pk.y = uint32_t(uint8_t(q[4])) | (uint32_t(uint8_t(q[5])) << 8) | (uint32_t(uint8_t(q[6])) << 16) |
-               (uint32_t(uint8_t(q[7])) << 24);
-        *reinterpret_cast<uint2*>(out + 256 * b + 8 * lane) = pk;
-        if (lane == 0) scales[b] = d;
+        store_q8k_block_planar(out, I, b, q, ps, d);
       }
     } else {
       float* scales = reinterpret_cast<float*>(out + I);
@@ -848,9 +829,11 @@ __device__ __forceinline__ void quantize_item_h(const fb_moe_decode_workspace& w
 }
 
 // Counts one finished contribution to an item's h; the last one re-quantizes that item's h for the
-// down kernel. `expected` = contributions per item.
+// down projection and then sets kItemReady in the item's counter (a fused gate/up + down launch polls
+// it before staging the item's rows). `expected` = contributions per item.
+constexpr int kItemReady = 0x40000000;
 __device__ __forceinline__ void item_contribution_done(const fb_moe_decode_workspace& ws, int item, int pair_begin,
-                                                       int n_tok, int expected, int down_act, int lane) {
+                                                       int n_tok, int expected, int down_act, int inter, int lane) {
   __threadfence();
   __syncwarp();
   int ticket = 0;
@@ -858,7 +841,10 @@ __device__ __forceinline__ void item_contribution_done(const fb_moe_decode_works
   ticket = __shfl_sync(0xffffffffu, ticket, 0);
   if (ticket == expected - 1) {
     __threadfence();
-    quantize_item_h(ws, pair_begin, n_tok, down_act);
+    quantize_item_h(ws, pair_begin, n_tok, down_act, inter);
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) atomicOr(&ws.item_done[item], kItemReady);
   }
 }
 
@@ -890,10 +876,6 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   constexpr int kStage = kStageW + kTT * C::kActBytes;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* p = smem;
-  uint32_t* gridrep = reinterpret_cast<uint32_t*>(p);
-  if (C::kGrid) p += kGridRepBytes;
-  uint32_t* signtab = reinterpret_cast<uint32_t*>(p);
-  p += 64;
   uint8_t* stage0 = p;
   p += 2 * kStage;
   float* partials = reinterpret_cast<float*>(p);
@@ -901,10 +883,10 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   uint64_t* bars = reinterpret_cast<uint64_t*>(p);
   __shared__ StageMeta s_meta[2];
   __shared__ int s_misc[4];  // [0] abort, [1] task ticket, [2..3] finished tasks per slot
+  __shared__ WorkCache s_work;
   Ring ring{bars, bars + 2, s_meta, s_misc};
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (C::kGrid) iq3s_tables_fill(gridrep, signtab);
   if (tid == 0) {
     ring_init(ring, 1);  // one arrival frees a slot: the warp that finishes the entry's last task
     s_misc[1] = 0;
@@ -921,11 +903,13 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   const int tpi = I / C::kJ;
   const int n_tiles = n_items * tpi;
   const int down_act = act_of(L.down_format);
+  work_cache_fill(ws, s_work, n_items);
+  __syncthreads();
 
   if (warp == kW) {
     // ---------------- producer: one lane draws tiles and issues their bulk copies into the ring.
     if (lane == 0) {
-      producer_loop(ring, ws, ws.sched + kSchedGateUp, n_tiles, tpi, C::kJ,
+      producer_loop(ring, ws, s_work, ws.sched + kSchedGateUp, n_tiles, tpi, C::kJ,
                     [&](int s, int slot_id, int sub, int pair0, int ntp) {
                       const uint8_t* blob = L.slots + int64_t(slot_id) * L.blob_stride;
                       uint8_t* st = stage0 + s * kStage;
@@ -935,7 +919,7 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
                       bulk_g2s(st + kUp, blob + L.up_offset + off, kPart, &ring.full[s]);
                       for (int t = 0; t < ntp; ++t)
                         bulk_g2s(st + kStageW + t * C::kActBytes,
-                                 ws.xq + size_t(work->pair_token[pair0 + t]) * FB_XQ_STRIDE, C::kActBytes,
+                                 ws.xq + size_t(s_work.pair_token[pair0 + t]) * FB_XQ_STRIDE, C::kActBytes,
                                  &ring.full[s]);
                     });
     }
@@ -943,58 +927,7 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   }
 
   // ---------------- consumers
-  if constexpr (FMT == FB_FMT_IQ3_S) {
-    const uint32_t* grid_lane = gridrep + lane;
-    while (true) {
-      int s, task;
-      if (!draw_task<C::kTasks>(ring, &s_misc[1], ws.status, lane, s, task)) break;
-      const int ntp = ring.meta[s].ntp;
-      uint8_t* st = stage0 + s * kStage;
-      const uint8_t* actbase = st + kStageW;
-      const int mat = task / 5, pair = task - 5 * mat;
-      const uint32_t* unit = reinterpret_cast<const uint32_t*>(st + mat * kUp + lane * C::kRowBytes + pair * 220);
-      float* part = partials + s * (C::kTasks * kTT * 32);
-      if (ntp == 1) {
-        const uint8_t* ar[1] = {actbase};
-        float acc[1] = {0.0f};
-        iq3s_unit_dot<1>(unit, grid_lane, signtab, ar, pair, H, acc);
-        part[(task * kTT + 0) * 32 + lane] = acc[0];
-      } else {
-        const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
-        float acc[2] = {0.0f, 0.0f};
-        iq3s_unit_dot<2>(unit, grid_lane, signtab, ar, pair, H, acc);
-        part[(task * kTT + 0) * 32 + lane] = acc[0];
-        part[(task * kTT + 1) * 32 + lane] = acc[1];
-      }
-      // The warp that finishes the entry's last task adds the ten partial rows (fixed order),
-      // applies SwiGLU and hands the slot back to the producer.
-      __threadfence_block();
-      __syncwarp();
-      int done = 0;
-      if (lane == 0) done = atomicAdd(&s_misc[2 + s], 1);
-      done = __shfl_sync(0xffffffffu, done, 0);
-      if (done == C::kTasks - 1) {
-        __threadfence_block();
-        const int pair0 = ring.meta[s].pair0, j0 = ring.meta[s].row0;
-        const int item = ring.meta[s].item, ipb = ring.meta[s].item_pair0, itok = ring.meta[s].item_tok;
-        for (int t = 0; t < ntp; ++t) {
-          float g = 0.0f, u = 0.0f;
-#pragma unroll
-          for (int q = 0; q < 5; ++q) {
-            g += part[(q * kTT + t) * 32 + lane];
-            u += part[((5 + q) * kTT + t) * 32 + lane];
-          }
-          ws.h[size_t(pair0 + t) * I + j0 + lane] = silu_mul(g, u);
-        }
-        __syncwarp();
-        if (lane == 0) {
-          s_misc[2 + s] = 0;
-          mbar_arrive(&ring.empty[s]);
-        }
-        item_contribution_done(ws, item, ipb, itok, tpi * ((itok + kTT - 1) / kTT), down_act, lane);
-      }
-    }
-  } else {
+  {
     const Iq4nlLevels lv = iq4nl_levels();
     while (true) {
       int s, task;
@@ -1037,7 +970,7 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
         s_misc[2 + s] = 0;
         mbar_arrive(&ring.empty[s]);
       }
-      item_contribution_done(ws, item, ipb, itok, tpi * C::kTasks * ((itok + kTT - 1) / kTT), down_act, lane);
+      item_contribution_done(ws, item, ipb, itok, tpi * C::kTasks * ((itok + kTT - 1) / kTT), down_act, I, lane);
     }
   }
 }
@@ -1045,20 +978,11 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
 // ------------------------------------------------------------------------------ down kernel
 template <int FMT, int INTER>
 struct Down;
-// IQ3_S, inter 512: a row is one 220-byte block pair; tile = 320 rows = ten tasks of 32 rows, one
-// row per lane, drawn by sixteen consumer warps.
-template <>
-struct Down<FB_FMT_IQ3_S, 512> {
-  static constexpr int kRows = 320, kRowBytes = 220, kWarps = 16, kTasks = 10, kAct = FB_ACT_Q8_K,
-                       kActBytes = 512 + 64;
-  static constexpr bool kGrid = true;
-};
 // IQ4_NL, inter 512: a row is eight 36-byte units, eight lanes per row, four rows per warp step.
 template <>
 struct Down<FB_FMT_IQ4_NL, 512> {
   static constexpr int kRows = 320, kRowBytes = 288, kWarps = 16, kTasks = 16, kAct = FB_ACT_Q8_0,
                        kActBytes = 512 + 64;
-  static constexpr bool kGrid = false;
   static constexpr int kLanesPerRow = 8, kUnitsPerLane = 1, kUnitA = 1, kUnitB = 0;
 };
 // IQ4_NL, inter 640: a row is ten units, two lanes per row with five consecutive units each.
@@ -1066,7 +990,6 @@ template <>
 struct Down<FB_FMT_IQ4_NL, 640> {
   static constexpr int kRows = 256, kRowBytes = 360, kWarps = 16, kTasks = 16, kAct = FB_ACT_Q8_0,
                        kActBytes = 640 + 80;
-  static constexpr bool kGrid = false;
   static constexpr int kLanesPerRow = 2, kUnitsPerLane = 5, kUnitA = 5, kUnitB = 1;
 };
 
@@ -1078,19 +1001,15 @@ down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   constexpr int kStage = kStageW + kTT * C::kActBytes;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* p = smem;
-  uint32_t* gridrep = reinterpret_cast<uint32_t*>(p);
-  if (C::kGrid) p += kGridRepBytes;
-  uint32_t* signtab = reinterpret_cast<uint32_t*>(p);
-  p += 64;
   uint8_t* stage0 = p;
   p += 2 * kStage;
   uint64_t* bars = reinterpret_cast<uint64_t*>(p);
   __shared__ StageMeta s_meta[2];
   __shared__ int s_misc[4];
+  __shared__ WorkCache s_work;
   Ring ring{bars, bars + 2, s_meta, s_misc};
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (C::kGrid) iq3s_tables_fill(gridrep, signtab);
   if (tid == 0) {
     ring_init(ring, 1);  // one arrival frees a slot: the warp that finishes the entry's last task
     s_misc[1] = 0;
@@ -1105,10 +1024,12 @@ down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   const int n_items = min(max(work->n_items, 0), kMaxPairs);
   constexpr int tpi = H / C::kRows;
   const int n_tiles = n_items * tpi;
+  work_cache_fill(ws, s_work, n_items);
+  __syncthreads();
 
   if (warp == kW) {
     if (lane == 0) {
-      producer_loop(ring, ws, ws.sched + kSchedDown, n_tiles, tpi, C::kRows,
+      producer_loop(ring, ws, s_work, ws.sched + kSchedDown, n_tiles, tpi, C::kRows,
                     [&](int s, int slot_id, int sub, int pair0, int ntp) {
                       const uint8_t* blob = L.slots + int64_t(slot_id) * L.blob_stride;
                       uint8_t* st = stage0 + s * kStage;
@@ -1122,39 +1043,7 @@ down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
     return;
   }
 
-  if constexpr (FMT == FB_FMT_IQ3_S) {
-    const uint32_t* grid_lane = gridrep + lane;
-    while (true) {
-      int s, task;
-      if (!draw_task<C::kTasks>(ring, &s_misc[1], ws.status, lane, s, task)) break;
-      const int ntp = ring.meta[s].ntp, pair0 = ring.meta[s].pair0, r0 = ring.meta[s].row0;
-      const float w0 = ring.meta[s].wgt[0], w1 = ring.meta[s].wgt[1];
-      uint8_t* st = stage0 + s * kStage;
-      const uint8_t* actbase = st + kStageW;
-      const int row = 32 * task + lane;
-      const uint32_t* unit = reinterpret_cast<const uint32_t*>(st + row * C::kRowBytes);
-      if (ntp == 1) {
-        const uint8_t* ar[1] = {actbase};
-        float acc[1] = {0.0f};
-        iq3s_unit_dot<1>(unit, grid_lane, signtab, ar, 0, INTER, acc);
-        ws.partial[size_t(pair0) * H + r0 + row] = w0 * acc[0];
-      } else {
-        const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
-        float acc[2] = {0.0f, 0.0f};
-        iq3s_unit_dot<2>(unit, grid_lane, signtab, ar, 0, INTER, acc);
-        ws.partial[size_t(pair0) * H + r0 + row] = w0 * acc[0];
-        ws.partial[size_t(pair0 + 1) * H + r0 + row] = w1 * acc[1];
-      }
-      __syncwarp();
-      if (lane == 0) {
-        const int done = atomicAdd(&s_misc[2 + s], 1);
-        if (done == C::kTasks - 1) {  // the tile's last task hands the slot back to the producer
-          s_misc[2 + s] = 0;
-          mbar_arrive(&ring.empty[s]);
-        }
-      }
-    }
-  } else {
+  {
     const Iq4nlLevels lv = iq4nl_levels();
     while (true) {  // sixteen tasks per tile, drawn from the ticket: task k takes row steps k, k + 16, ...
       int s, task;
@@ -1219,6 +1108,8 @@ down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
     }
   }
 }
+
+#include "moe_decode_iq3s.cuh"
 
 // ------------------------------------------------------------------------------ combine
 // y[t][n] = partials of token t in slot order (+ y_shared); optional rank-1 ablation of the routed
@@ -1327,13 +1218,13 @@ __global__ void __launch_bounds__(256) ep_combine_exchange_kernel(fb_moe_decode_
 template <int FMT>
 constexpr size_t gate_up_smem() {
   using C = GateUp<FMT>;
-  return (C::kGrid ? kGridRepBytes : 0) + 64 + 2 * size_t(2 * C::kJ * C::kRowBytes + C::kUpPad + kTT * C::kActBytes) +
+  return 2 * size_t(2 * C::kJ * C::kRowBytes + C::kUpPad + kTT * C::kActBytes) +
          C::kPartialFloats * 4 + 16 + 64;
 }
 template <int FMT, int INTER>
 constexpr size_t down_smem() {
   using C = Down<FMT, INTER>;
-  return (C::kGrid ? kGridRepBytes : 0) + 64 + 2 * size_t(C::kRows * C::kRowBytes + kTT * C::kActBytes) + 64;
+  return 2 * size_t(C::kRows * C::kRowBytes + kTT * C::kActBytes) + 64;
 }
 
 bool layout_ok(const fb_moe_expert_layout* L) {
@@ -1428,39 +1319,59 @@ int32_t fb_moe_select_publish(const float* router_logits, int32_t logits_stride,
   return 0;
 }
 
+// The IQ3_S expert kernel: gate/up tiles, down tiles, or both in one launch (down needs inter 512).
+static int32_t launch_experts_iq3s(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, int phases,
+                                   void* stream, const char* what) {
+  static PerDeviceOnce once;
+  const cudaError_t attr = per_device_once(once, [] { return opt_in_smem(experts_iq3s_kernel, Experts3::kSmem); });
+  if (attr != cudaSuccess) {
+    set_error("%s: shared-memory opt-in: %s", what, cudaGetErrorString(attr));
+    return int32_t(attr);
+  }
+  const cudaError_t e = launch_pdl(experts_iq3s_kernel, dim3(sm_count()), dim3((Experts3::kWarps + 1) * 32), Experts3::kSmem,
+                                   as_stream(stream), *layout, *ws, phases);
+  if (e != cudaSuccess) return check_launch(what);
+  return 0;
+}
+
 int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
                            void* stream) {
   if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_gate_up: bad arguments");
   if (layout->inter != ws->inter || layout->gate_up_format != ws->gate_up_format ||
       layout->down_format != ws->down_format)
     return invalid("hot_gate_up: workspace was made for a different layout");
+  const dim3 grid(sm_count());
+  if (layout->gate_up_format == FB_FMT_IQ3_S) return launch_experts_iq3s(layout, ws, kPhaseGateUp, stream, "hot_gate_up");
   static PerDeviceOnce once;
-  const cudaError_t attr = per_device_once(once, [] {
-    cudaError_t a = opt_in_smem(gate_up_kernel<FB_FMT_IQ3_S>, gate_up_smem<FB_FMT_IQ3_S>());
-    if (a == cudaSuccess) a = opt_in_smem(gate_up_kernel<FB_FMT_IQ4_NL>, gate_up_smem<FB_FMT_IQ4_NL>());
-    return a;
-  });
+  const cudaError_t attr =
+      per_device_once(once, [] { return opt_in_smem(gate_up_kernel<FB_FMT_IQ4_NL>, gate_up_smem<FB_FMT_IQ4_NL>()); });
   if (attr != cudaSuccess) {
     set_error("hot_gate_up: shared-memory opt-in: %s", cudaGetErrorString(attr));
     return int32_t(attr);
   }
-  const dim3 grid(sm_count());
-  cudaError_t e;
-  if (layout->gate_up_format == FB_FMT_IQ3_S)
-    e = launch_pdl(gate_up_kernel<FB_FMT_IQ3_S>, grid, dim3((GateUp<FB_FMT_IQ3_S>::kWarps + 1) * 32),
-                   gate_up_smem<FB_FMT_IQ3_S>(), as_stream(stream), *layout, *ws);
-  else
-    e = launch_pdl(gate_up_kernel<FB_FMT_IQ4_NL>, grid, dim3((GateUp<FB_FMT_IQ4_NL>::kWarps + 1) * 32),
-                   gate_up_smem<FB_FMT_IQ4_NL>(), as_stream(stream), *layout, *ws);
+  const cudaError_t e = launch_pdl(gate_up_kernel<FB_FMT_IQ4_NL>, grid, dim3((GateUp<FB_FMT_IQ4_NL>::kWarps + 1) * 32),
+                                   gate_up_smem<FB_FMT_IQ4_NL>(), as_stream(stream), *layout, *ws);
   if (e != cudaSuccess) return check_launch("hot_gate_up");
   return 0;
 }
 
+int32_t fb_moe_hot_experts(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
+                           void* stream) {
+  if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_experts: bad arguments");
+  if (layout->inter != ws->inter || layout->gate_up_format != ws->gate_up_format ||
+      layout->down_format != ws->down_format)
+    return invalid("hot_experts: workspace was made for a different layout");
+  if (layout->gate_up_format == FB_FMT_IQ3_S && layout->down_format == FB_FMT_IQ3_S)
+    return launch_experts_iq3s(layout, ws, kPhaseGateUp | kPhaseDown, stream, "hot_experts");
+  const int32_t st = fb_moe_hot_gate_up(layout, tokens, ws, stream);
+  return st ? st : fb_moe_hot_down(layout, tokens, ws, stream);
+}
+
 static int32_t launch_down(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, void* stream) {
+  if (layout->down_format == FB_FMT_IQ3_S) return launch_experts_iq3s(layout, ws, kPhaseDown, stream, "hot_down");
   static PerDeviceOnce once;
   const cudaError_t attr = per_device_once(once, [] {
-    cudaError_t a = opt_in_smem(down_kernel<FB_FMT_IQ3_S, 512>, down_smem<FB_FMT_IQ3_S, 512>());
-    if (a == cudaSuccess) a = opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 512>, down_smem<FB_FMT_IQ4_NL, 512>());
+    cudaError_t a = opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 512>, down_smem<FB_FMT_IQ4_NL, 512>());
     if (a == cudaSuccess) a = opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 640>, down_smem<FB_FMT_IQ4_NL, 640>());
     return a;
   });
@@ -1470,10 +1381,7 @@ static int32_t launch_down(const fb_moe_expert_layout* layout, const fb_moe_deco
   }
   const dim3 grid(sm_count());
   cudaError_t e;
-  if (layout->down_format == FB_FMT_IQ3_S)
-    e = launch_pdl(down_kernel<FB_FMT_IQ3_S, 512>, grid, dim3((Down<FB_FMT_IQ3_S, 512>::kWarps + 1) * 32),
-                   down_smem<FB_FMT_IQ3_S, 512>(), as_stream(stream), *layout, *ws);
-  else if (layout->inter == 512)
+  if (layout->inter == 512)
     e = launch_pdl(down_kernel<FB_FMT_IQ4_NL, 512>, grid, dim3((Down<FB_FMT_IQ4_NL, 512>::kWarps + 1) * 32),
                    down_smem<FB_FMT_IQ4_NL, 512>(), as_stream(stream), *layout, *ws);
   else
@@ -1513,8 +1421,9 @@ static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_
   const bool with_combine = ep == nullptr;
   EpRouteArgs era{};
   if (ep) era = *ep;
-  // Four launches: route (router projection + activation quantization + selection), gate/up, down,
-  // combine. Gate/up, down and combine are the separate entry points themselves. The route kernel
+  // Three launches for IQ3_S experts (four otherwise): route (router projection + activation quantization
+  // + selection), the expert kernel (gate/up and down tiles in one persistent launch; the other formats
+  // take a gate/up and a down launch), combine. The expert arithmetic is that of the separate entry points. The route kernel
   // sums a logit as eight K slices of 320 added in slice order, where fb_router_logits sums 80
   // values per lane and then the lanes: the two projections agree to fp32 rounding (a few ulp), not
   // bit for bit, so a near-tie between the tenth and eleventh expert may resolve differently. Only
@@ -1535,9 +1444,7 @@ static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_
                   : x_dtype == FB_DT_BF16 ? launch(route_kernel<true, false>)
                                           : launch(route_kernel<false, false>);
   if (e != cudaSuccess) return check_launch("layer_decode: route");
-  int32_t st = fb_moe_hot_gate_up(layout, tokens, ws, stream);
-  if (st) return st;
-  st = launch_down(layout, ws, stream);
+  const int32_t st = fb_moe_hot_experts(layout, tokens, ws, stream);  // both projections of every routed expert
   if (st || !with_combine) return st;
   return fb_moe_combine(ws, nullptr, nullptr, 0, nullptr, nullptr, nullptr, y_out, tokens, 0, nullptr, 0.0f, stream);
 }

@@ -1,13 +1,19 @@
 // IQ3_S streaming kernels of the decode path (gate/up and down), included by moe_decode.cu inside
 // namespace fb's anonymous namespace.
 //
+// One persistent kernel streams the gate, up and down matrices of every routed expert of a layer:
+// first all gate/up tiles (heaviest experts first), then all down tiles, through one three-stage ring
+// of 40 KB slots, so the codebook set-up, the work-list copy and the pipeline fill are paid once per
+// layer and HBM keeps streaming across the gate/up -> down boundary. A down tile needs its expert's h
+// re-quantized, which the warp that finishes the expert's last gate/up tile does and then flags; the
+// producer asks for a down tile's weights first and polls that flag (a bounded number of times) only
+// before it asks for the activation rows. The same kernel runs one phase alone behind the separate
+// gate/up and down entry points.
+//
 // Shape of the work. A lane owns a weight row; a warp task is one 110-byte block (256 weights) of 32
-// rows (gate/up: 16 gate rows + the 16 matching up rows; down: 32 rows, both blocks of the row), so a
-// staged tile splits into many small tasks that sixteen consumer warps draw from a shared-memory
-// ticket. Tiles are small (35 KB gate/up, 28 KB down) and the ring is three / five stages deep: at any
-// time two / four tiles are in flight from HBM while one is being consumed, and enough tasks are
-// resident that no scheduler runs out of warps (a two-stage ring of 70 KB tiles left the consumer
-// warps waiting on the full barriers for 40 % of their time).
+// rows (gate/up: 16 gate rows + the 16 matching up rows, ten blocks; down: five groups of 32 rows, two
+// blocks), so every tile is ten tasks, five on even blocks and five on odd ones, that the consumer
+// warps draw from two shared-memory tickets.
 //
 // Arithmetic per 4 weights (one codebook look-up). The codebook in shared memory holds G = (g - 1) / 2
 // for every magnitude g in {1, 3, ..., 15}; with m = 0xFF in the bytes of negative weights, the bytes of
@@ -21,9 +27,8 @@
 // ------------------------------------------------------------------------------ planar activation rows
 // Q8_K rows in the workspace and in the staged tiles: codes [k] | block scales float [k/256], padded to
 // 64 bytes | sub-block code sums int16 [k/32].
-__host__ __device__ constexpr int q8k_planar_scales_off(int k) { return k; }
-__host__ __device__ constexpr int q8k_planar_asum_off(int k) { return k + 64; }
-__host__ __device__ constexpr int q8k_planar_bytes(int k) { return k + 64 + ((k / 32 * 2 + 15) & ~15); }
+__host__ __device__ constexpr int q8k_planar_asum_off(int k) { return q8k_asum_off(k); }
+__host__ __device__ constexpr int q8k_planar_bytes(int k) { return q8k_asum_off(k) + ((k / 32 * 2 + 15) & ~15); }
 static_assert(q8k_planar_bytes(2560) <= FB_XQ_STRIDE && q8k_planar_bytes(512) <= FB_HQ_STRIDE, "row strides");
 static_assert(q8k_planar_bytes(2560) % 16 == 0 && q8k_planar_bytes(512) % 16 == 0, "bulk copies");
 
@@ -70,6 +75,9 @@ __device__ __forceinline__ void iq3s_sub_dot(uint32_t qs_lo, uint32_t qs_hi, uin
     const uint32_t idx = prmt(l < 4 ? qs_lo : qs_hi, l < 4 ? h_lo : h_hi, sel);
     const uint32_t g = grid_lane[idx * 32];
     // byte0 = the pre-scaled nibble of look-up l, bytes 1-3 = the table's address bytes
+    // (computing the masks instead - isolate the nibble, one wide multiply that sends bit j to the top of
+    // byte j, one sign-replicating byte-permute - frees a third of the shared-memory wavefronts but the
+    // multiplies queue up in the dispatch stage: measured 96 us against 80 us per layer launch)
     const uint32_t maddr = prmt((l & 1) ? s_odd : s_even, sign_base, 0x7650u | uint32_t(l >> 1));
     uint32_t m;
     asm("ld.shared.u32 %0, [%1];" : "=r"(m) : "r"(maddr));
@@ -96,40 +104,58 @@ __device__ __forceinline__ void iq3s_sub_dot(uint32_t qs_lo, uint32_t qs_hi, uin
 // w = the word that holds the block's fp16 scale (MIS: in its low half, the 27 stream words then sit
 // 2 bytes off word alignment; else in its high half and the stream is aligned); act[t] = the 256
 // codes of the matching Q8_K block, asum[t] = its 8 sub-block code sums (16-byte aligned).
+// |P| <= 32 * 8 * 127 fits 16 bits, so two sub-blocks' P (and their two code sums A) are multiplied by
+// their odd multipliers with one two-way dot product each.
 template <bool MIS, int TT>
 __device__ __forceinline__ void iq3s_block_idot2(const uint32_t* w, const uint32_t* grid_lane, uint32_t sign_base,
                                                  const int8_t* const (&act)[TT], const int16_t* const (&asum)[TT],
                                                  int (&bsum)[TT]) {
   const uint32_t sc = iq3s_stream<MIS>(w, 26);
+  // multipliers 2 s + 1 as bytes: even sub-blocks (low nibbles) and odd sub-blocks (high nibbles)
+  const uint32_t m_even = ((sc << 1) & 0x1E1E1E1Eu) | 0x01010101u;
+  const uint32_t m_odd = ((sc >> 3) & 0x1E1E1E1Eu) | 0x01010101u;
   int4 as[TT];
+  int accP[TT], accA[TT];
 #pragma unroll
   for (int t = 0; t < TT; ++t) {
-    bsum[t] = 0;
+    accP[t] = 0;
     as[t] = *reinterpret_cast<const int4*>(asum[t]);
+  }
+  {  // code-sum part: sum_sb (2 s + 1) * A_sb, four two-way dot products
+    const uint32_t mi01 = __byte_perm(m_even, m_odd, 0x5140), mi23 = __byte_perm(m_even, m_odd, 0x7362);
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+      int a = __dp2a_lo(as[t].x, int(mi01), 0);
+      a = __dp2a_hi(as[t].y, int(mi01), a);
+      a = __dp2a_lo(as[t].z, int(mi23), a);
+      accA[t] = __dp2a_hi(as[t].w, int(mi23), a);
+    }
   }
 #pragma unroll 1
   for (int half = 0; half < 2; ++half) {
     const uint32_t qh = iq3s_stream<MIS>(w, 16 + half);
-    const uint32_t sch = sc >> (16 * half);
+    // bytes {m(4h), m(4h+1), m(4h+2), m(4h+3)} of this half's four sub-blocks
+    const uint32_t mi = __byte_perm(m_even, m_odd, half == 0 ? 0x5140u : 0x7362u);
+    int P[4][TT];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int ib = 4 * half + i;
       const int8_t* a[TT];
 #pragma unroll
       for (int t = 0; t < TT; ++t) a[t] = act[t] + 32 * ib;
-      int P[TT];
       iq3s_sub_dot<TT>(iq3s_stream<MIS>(w, 2 * ib), iq3s_stream<MIS>(w, 2 * ib + 1), qh, 8 * i,
-                       iq3s_stream<MIS>(w, 18 + ib), grid_lane, sign_base, a, P);
-      const int mult = 2 * int((sch >> (4 * i)) & 0xFu) + 1;
+                       iq3s_stream<MIS>(w, 18 + ib), grid_lane, sign_base, a, P[i]);
+    }
 #pragma unroll
-      for (int t = 0; t < TT; ++t) {
-        // the two sums of this half's sub-blocks sit in words (x, y) / (z, w) of the int4, 16 bits each
-        const int pair = half == 0 ? (i < 2 ? as[t].x : as[t].y) : (i < 2 ? as[t].z : as[t].w);
-        const int A = (i & 1) ? (pair >> 16) : int(short(pair & 0xFFFF));
-        bsum[t] += mult * (2 * P[t] + A);
-      }
+    for (int t = 0; t < TT; ++t) {
+      const int p01 = int(__byte_perm(uint32_t(P[0][t]), uint32_t(P[1][t]), 0x5410));
+      const int p23 = int(__byte_perm(uint32_t(P[2][t]), uint32_t(P[3][t]), 0x5410));
+      accP[t] = __dp2a_lo(p01, int(mi), accP[t]);
+      accP[t] = __dp2a_hi(p23, int(mi), accP[t]);
     }
   }
+#pragma unroll
+  for (int t = 0; t < TT; ++t) bsum[t] = 2 * accP[t] + accA[t];
 }
 
 // scale of the block, fp16 -> fp32
@@ -139,13 +165,21 @@ __device__ __forceinline__ float iq3s_block_d(const uint32_t* w) {
   return __half2float(__ushort_as_half(static_cast<unsigned short>(v)));
 }
 
+// The 64-byte mask table sits on a 256-byte boundary (its address bytes 1-3 ride in a byte-permute)
+// inside an area of kSignArea bytes.
+constexpr int kSignArea = 320;
+__device__ __forceinline__ uint32_t* sign_table_at(uint8_t* area) {
+  return reinterpret_cast<uint32_t*>(area + ((256u - (smem_u32(area) & 255u)) & 255u));
+}
+
 // ------------------------------------------------------------------------------ multi-stage ring
 template <int S>
 struct RingN {
   uint64_t* full;   // [S] count 1 + tx bytes
   uint64_t* empty;  // [S]
   volatile StageMeta* meta;  // [S]
-  volatile int* abort;
+  // number of entries the producer staged in all; INT_MAX while it is still staging; 0 after a time-out
+  volatile int* end_seq;
 };
 
 // try_wait with a suspend-time hint: the thread may sleep inside the instruction until the phase
@@ -175,62 +209,19 @@ __device__ __forceinline__ void ringn_init(const RingN<S>& r) {
     mbar_init(&r.full[s], 1);
     mbar_init(&r.empty[s], 1);  // one arrival frees a slot: the warp that finishes the entry's last task
     r.meta[s].tile = -1;
+    r.meta[s].seq = -1;
   }
-  *r.abort = 0;
+  *r.end_seq = 0x7fffffff;
   mbar_fence_init();
 }
 
-// Producer loop of one CTA (one thread): draws tiles from `counter`, stages every pass of each tile
-// through issue(slot, ...), and finally posts the end marker in every slot.
-template <int S, class IssueF>
-__device__ __forceinline__ void producer_loop_n(const RingN<S>& r, const fb_moe_decode_workspace& ws, int* counter,
-                                                int n_tiles, int tiles_per_item, int rows_per_tile, IssueF issue) {
-  const fb_moe_decode_work* work = ws.work;
-  int i = 0;
-  auto slot_free = [&](int s) -> bool {
-    if (*r.abort) return false;
-    if (i >= S && !mbar_wait_hint(&r.empty[s], ((i / S) - 1) & 1)) {
-      *r.abort = 1;
-      atomicMax(ws.status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
-      return false;
-    }
-    return true;
-  };
-  int next = atomicAdd(counter, 1);  // drawn one step ahead of its use
-  while (true) {
-    const int tile = next;
-    if (tile >= n_tiles) break;
-    next = atomicAdd(counter, 1);
-    const int pos = tile / tiles_per_item;
-    const int item = ws.sched[kSchedOrder + pos];
-    const int sub = tile - pos * tiles_per_item;
-    const int pb = work->item_pair_begin[item];
-    const int ntok = work->item_pair_begin[item + 1] - pb;
-    const int slot_id = work->item_slot[item];
-    for (int tok0 = 0; tok0 < ntok; tok0 += kTT, ++i) {
-      const int s = i % S;
-      if (!slot_free(s)) return;
-      volatile StageMeta* m = &r.meta[s];
-      m->tile = tile;
-      m->pair0 = pb + tok0;
-      m->ntp = min(kTT, ntok - tok0);
-      m->row0 = sub * rows_per_tile;
-      m->item = item;
-      m->item_pair0 = pb;
-      m->item_tok = ntok;
-      for (int t = 0; t < kTT; ++t) m->wgt[t] = tok0 + t < ntok ? work->pair_weight[pb + tok0 + t] : 0.0f;
-      issue(s, slot_id, sub, pb + tok0, min(kTT, ntok - tok0));
-    }
-  }
-  for (int e = 0; e < S; ++e, ++i) {  // end marker in every slot: every waiting warp sees it
-    const int s = i % S;
-    if (!slot_free(s)) return;
-    r.meta[s].tile = -1;
-    mbar_arrive(&r.full[s]);
-  }
-}
-
-// Consumer side: draws the next (entry, task) ticket; returns false at the end.
+// Consumer side: draws the next (entry, task) ticket and waits for that entry's data; returns false
+// at the end. A warp may hold a ticket for an entry that is S or more entries ahead of the one its slot
+// is being filled with, and the barrier's one-bit phase cannot tell those apart. So the warp first waits
+// (polling one shared-memory word, asleep in between) until the producer has written this entry's number
+// into the slot, which it does before it arms the barrier; only then is the barrier's current phase the
+// entry's own, and the warp can sleep inside try_wait. On a time-out the producer sets end_seq to 0, which
+// releases every waiting warp.
 template <int S, int TASKS>
 __device__ __forceinline__ bool draw_task_n(const RingN<S>& r, int* ticket_ctr, uint32_t* status, int lane, int& s,
                                             int& task) {
@@ -240,49 +231,97 @@ __device__ __forceinline__ bool draw_task_n(const RingN<S>& r, int* ticket_ctr, 
   const int seq = ticket / TASKS;
   task = ticket - seq * TASKS;
   s = seq % S;
-  if (*r.abort) return false;
-  if (!mbar_wait_hint(&r.full[s], (seq / S) & 1)) {
-    *r.abort = 1;
-    atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
-    return false;
+  uint32_t tries = 0;
+  while (r.meta[s].seq != seq) {
+    if (*r.end_seq <= seq) return false;
+    if (++tries > (1u << 20)) {  // bounded: about a second
+      *r.end_seq = 0;
+      atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+      return false;
+    }
+    // the entry's data arrives a microsecond or more after its number is written: a long nap costs nothing
+    __nanosleep(800);
   }
-  return r.meta[s].tile >= 0;
+  const uint32_t parity = (seq / S) & 1;
+  for (uint32_t i = 0; i < (1u << 21); ++i) {  // bounded: each try takes at most about a microsecond
+    if (mbar_try_wait_hint(&r.full[s], parity)) return true;
+    if (*r.end_seq <= seq) return false;
+  }
+  *r.end_seq = 0;
+  atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+  return false;
 }
 
-// ------------------------------------------------------------------------------ gate/up, IQ3_S
-// Tile = 16 intermediate rows: 16 gate rows and the 16 matching up rows (17,600 bytes each) plus the
-// activation rows of the pass. Task b (0..9) = block b of all 32 rows: lanes 0-15 the gate rows, lanes
-// 16-31 the up rows. The warp that finishes a tile's last task adds each row's ten block terms in block
-// order, pairs gate with up through a shuffle, applies SwiGLU and frees the slot.
-struct GateUp3 {
-  static constexpr int kJ = 16, kRowBytes = 1100, kWarps = 16, kTasks = 10, kStages = 3;
-  static constexpr int kPart = kJ * kRowBytes;                 // 17,600
-  static constexpr int kActBytes = q8k_planar_bytes(H);        // 2,784
-  static constexpr int kStage = 2 * kPart + kTT * kActBytes;   // 40,768
+// ------------------------------------------------------------------------------ the expert kernel
+// Gate/up tile = 16 intermediate rows: 16 gate rows and the 16 matching up rows (17,600 bytes each);
+// task b (0..9) = block b of all 32 rows, lanes 0-15 the gate rows, lanes 16-31 the up rows; the warp
+// that finishes the tile's last task adds each row's ten block terms in block order, pairs gate with
+// up through a shuffle and applies SwiGLU.
+// Down tile = 160 output rows (35,200 bytes; a row is two blocks); task 2k + b = block b of rows
+// 32k .. 32k+31; the finishing warp adds each row's two block terms and applies the routing weight.
+// Both kinds carry the activation rows of the pass behind the weights.
+struct Experts3 {
+  static constexpr int kWarps = 24, kTasks = 10, kStages = 3, kInter = 512;
+  static constexpr int kGuRows = 16, kGuRowBytes = 1100, kGuPart = kGuRows * kGuRowBytes;  // 17,600
+  static constexpr int kDnRows = 160, kDnRowBytes = 220, kDnTile = kDnRows * kDnRowBytes;  // 35,200
+  static constexpr int kGuAct = q8k_planar_bytes(H), kDnAct = q8k_planar_bytes(kInter);    // 2,784 / 608
+  static constexpr int kSlot = 2 * kGuPart + kTT * kGuAct;                                 // 40,768
+  static constexpr int kDnTilesPerItem = H / kDnRows;                                      // 16
   static constexpr int kPartialFloats = kStages * kTasks * kTT * 32;
-  static constexpr size_t kSmem = size_t(kGridRepBytes) + 256 + size_t(kStages) * kStage + kPartialFloats * 4 + 128;
+  static constexpr size_t kSmem = size_t(kGridRepBytes) + kSignArea + size_t(kStages) * kSlot + kPartialFloats * 4 + 128;
 };
-static_assert(GateUp3::kStage % 16 == 0 && GateUp3::kPart % 16 == 0, "bulk copy alignment");
+static_assert(Experts3::kDnTile + kTT * Experts3::kDnAct <= Experts3::kSlot, "a down tile fits a slot");
+static_assert(Experts3::kSlot % 16 == 0 && Experts3::kGuPart % 16 == 0 && Experts3::kDnTile % 16 == 0, "bulk copies");
+static_assert(H % Experts3::kDnRows == 0 && Experts3::kDnRows % 32 == 0, "down tiles");
+enum { kPhaseGateUp = 1, kPhaseDown = 2 };
 
-__global__ void __launch_bounds__((GateUp3::kWarps + 1) * 32, 1)
-gate_up_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
-  using C = GateUp3;
+// One block (256 weights) of the lane's row against the pass's tokens: term[t] = bsum * d * d_act.
+template <bool MIS>
+__device__ __forceinline__ void expert_block_terms(const uint32_t* w, const uint32_t* grid_lane, uint32_t sign_base,
+                                                   const uint8_t* act0, int act_bytes, int k, int blk, int ntp,
+                                                   float (&term)[kTT]) {
+  const float d = iq3s_block_d<MIS>(w);
+  if (ntp == 1) {
+    const int8_t* a[1] = {reinterpret_cast<const int8_t*>(act0) + 256 * blk};
+    const int16_t* as[1] = {reinterpret_cast<const int16_t*>(act0 + q8k_planar_asum_off(k)) + 8 * blk};
+    int bs[1];
+    iq3s_block_idot2<MIS, 1>(w, grid_lane, sign_base, a, as, bs);
+    term[0] = float(bs[0]) * (d * reinterpret_cast<const float*>(act0 + k)[blk]);
+    term[1] = 0.0f;
+  } else {
+    const uint8_t* act1 = act0 + act_bytes;
+    const int8_t* a[2] = {reinterpret_cast<const int8_t*>(act0) + 256 * blk,
+                          reinterpret_cast<const int8_t*>(act1) + 256 * blk};
+    const int16_t* as[2] = {reinterpret_cast<const int16_t*>(act0 + q8k_planar_asum_off(k)) + 8 * blk,
+                            reinterpret_cast<const int16_t*>(act1 + q8k_planar_asum_off(k)) + 8 * blk};
+    int bs[2];
+    iq3s_block_idot2<MIS, 2>(w, grid_lane, sign_base, a, as, bs);
+    term[0] = float(bs[0]) * (d * reinterpret_cast<const float*>(act0 + k)[blk]);
+    term[1] = float(bs[1]) * (d * reinterpret_cast<const float*>(act1 + k)[blk]);
+  }
+}
+
+__global__ void __launch_bounds__((Experts3::kWarps + 1) * 32, 1)
+experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phases) {
+  using C = Experts3;
   constexpr int S = C::kStages;
-  extern __shared__ __align__(256) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   uint32_t* gridrep = reinterpret_cast<uint32_t*>(smem);
-  uint32_t* signtab = reinterpret_cast<uint32_t*>(smem + kGridRepBytes);  // 256-byte aligned
-  uint8_t* stage0 = smem + kGridRepBytes + 256;
-  float* partials = reinterpret_cast<float*>(stage0 + S * C::kStage);
+  uint32_t* signtab = sign_table_at(smem + kGridRepBytes);
+  uint8_t* stage0 = smem + kGridRepBytes + kSignArea;
+  float* partials = reinterpret_cast<float*>(stage0 + S * C::kSlot);
   uint64_t* bars = reinterpret_cast<uint64_t*>(partials + C::kPartialFloats);
   __shared__ StageMeta s_meta[S];
-  __shared__ int s_misc[2 + S];  // [0] abort, [1] task ticket, [2..] finished tasks per slot
-  RingN<S> ring{bars, bars + S, s_meta, s_misc};
+  __shared__ int s_misc[3 + S];  // [1..2] task tickets (even / odd blocks), [3..] finished tasks per slot
+  __shared__ int s_end;
+  __shared__ WorkCache s_work;
+  RingN<S> ring{bars, bars + S, s_meta, &s_end};
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   iq3s_half_tables_fill(gridrep, signtab);
   if (tid == 0) {
     ringn_init(ring);
-    for (int i = 1; i < 2 + S; ++i) s_misc[i] = 0;
+    for (int i = 1; i < 3 + S; ++i) s_misc[i] = 0;
   }
   __syncthreads();
   pdl_launch_dependents();
@@ -290,27 +329,104 @@ gate_up_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
 
   const fb_moe_decode_work* work = ws.work;
   const int n_items = min(max(work->n_items, 0), kMaxPairs);
-  const int I = L.inter;
-  const int tpi = I / C::kJ;
-  const int n_tiles = n_items * tpi;
-  const int down_act = act_of(L.down_format);
+  const int I = L.inter;  // gate/up takes 512 or 640; the down phase is for 512 (checked on the host)
+  const int gu_tpi = I / C::kGuRows;
+  const int n_gu = (phases & kPhaseGateUp) ? n_items * gu_tpi : 0;
+  const int n_dn = (phases & kPhaseDown) ? n_items * C::kDnTilesPerItem : 0;
+  work_cache_fill(ws, s_work, n_items);
+  __syncthreads();
 
   if (warp == C::kWarps) {
-    // ---------------- producer: one lane draws tiles and issues their bulk copies into the ring.
-    if (lane == 0) {
-      producer_loop_n<S>(ring, ws, ws.sched + kSchedGateUp, n_tiles, tpi, C::kJ,
-                         [&](int s, int slot_id, int sub, int pair0, int ntp) {
-                           const uint8_t* blob = L.slots + int64_t(slot_id) * L.blob_stride;
-                           uint8_t* st = stage0 + s * C::kStage;
-                           mbar_expect_tx(&ring.full[s], uint32_t(2 * C::kPart + ntp * C::kActBytes));
-                           const size_t off = size_t(sub) * C::kPart;
-                           bulk_g2s(st, blob + L.gate_offset + off, C::kPart, &ring.full[s]);
-                           bulk_g2s(st + C::kPart, blob + L.up_offset + off, C::kPart, &ring.full[s]);
-                           for (int t = 0; t < ntp; ++t)
-                             bulk_g2s(st + 2 * C::kPart + t * C::kActBytes,
-                                      ws.xq + size_t(work->pair_token[pair0 + t]) * FB_XQ_STRIDE, C::kActBytes,
-                                      &ring.full[s]);
-                         });
+    // ---------------- producer: one lane draws tiles (two steps ahead of their use) and issues their
+    // bulk copies into the ring; every pass of kTT tokens of a tile is one ring entry.
+    if (lane != 0) return;
+    int* counter = ws.sched + ((phases & kPhaseGateUp) ? kSchedGateUp : kSchedDown);
+    const int n_tiles = n_gu + n_dn;
+    int i = 0;
+    bool failed = false;
+    struct EndMark {  // whichever way the loop is left, waiting consumers learn how many entries exist
+      const RingN<S>& r;
+      const int& i;
+      const bool& failed;
+      __device__ ~EndMark() { *r.end_seq = failed ? 0 : i; }
+    } end_mark{ring, i, failed};
+    auto give_up = [&]() {
+      failed = true;
+      atomicMax(ws.status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
+    };
+    auto slot_free = [&](int s) -> bool {
+      if (*ring.end_seq == 0) return false;  // a consumer gave up
+      if (i >= S && !mbar_wait_hint(&ring.empty[s], ((i / S) - 1) & 1)) {
+        give_up();
+        return false;
+      }
+      return true;
+    };
+    int next = atomicAdd(counter, 1), next2 = atomicAdd(counter, 1);
+    while (true) {
+      const int tile = next;
+      if (tile >= n_tiles) break;
+      next = next2;
+      next2 = atomicAdd(counter, 1);
+      const bool down = tile >= n_gu;
+      const int tl = down ? tile - n_gu : tile;
+      const int pos = down ? tl / C::kDnTilesPerItem : tl / gu_tpi;
+      const int sub = down ? tl - pos * C::kDnTilesPerItem : tl - pos * gu_tpi;
+      const int item = s_work.order[pos];
+      const int pb = s_work.pair_begin[item];
+      const int ntok = s_work.pair_begin[item + 1] - pb;
+      const uint8_t* blob = L.slots + int64_t(s_work.slot[item]) * L.blob_stride;
+      bool ready = !down || !(phases & kPhaseGateUp);  // a down-only launch runs behind a finished gate/up launch
+      for (int tok0 = 0; tok0 < ntok; tok0 += kTT, ++i) {
+        const int s = i % S;
+        if (!slot_free(s)) return;
+        const int ntp = min(kTT, ntok - tok0);
+        volatile StageMeta* m = &ring.meta[s];
+        m->seq = i;
+        m->tile = down ? 1 : 0;  // entry kind
+        m->pair0 = pb + tok0;
+        m->ntp = ntp;
+        m->row0 = sub * (down ? C::kDnRows : C::kGuRows);
+        m->item = item;
+        m->item_pair0 = pb;
+        m->item_tok = ntok;
+        for (int t = 0; t < kTT; ++t) m->wgt[t] = tok0 + t < ntok ? s_work.pair_weight[pb + tok0 + t] : 0.0f;
+        uint8_t* st = stage0 + s * C::kSlot;
+        if (!down) {
+          mbar_expect_tx(&ring.full[s], uint32_t(2 * C::kGuPart + ntp * C::kGuAct));
+          const size_t off = size_t(sub) * C::kGuPart;
+          bulk_g2s(st, blob + L.gate_offset + off, C::kGuPart, &ring.full[s]);
+          bulk_g2s(st + C::kGuPart, blob + L.up_offset + off, C::kGuPart, &ring.full[s]);
+          for (int t = 0; t < ntp; ++t)
+            bulk_g2s(st + 2 * C::kGuPart + t * C::kGuAct,
+                     ws.xq + size_t(s_work.pair_token[pb + tok0 + t]) * FB_XQ_STRIDE, C::kGuAct, &ring.full[s]);
+        } else {
+          mbar_expect_tx(&ring.full[s], uint32_t(C::kDnTile + ntp * C::kDnAct));
+          bulk_g2s(st, blob + L.down_offset + size_t(sub) * C::kDnTile, C::kDnTile, &ring.full[s]);
+          if (!ready) {  // the item's h must have been re-quantized (bounded poll of its flag)
+            const int* flag = ws.item_done + item;
+            uint32_t tries = 0;
+            while (true) {
+              int v;
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+              if (v & kItemReady) break;
+              if (++tries > (1u << 22) || *ring.end_seq == 0) {
+                give_up();
+                break;
+              }
+              __nanosleep(200);
+            }
+            ready = true;
+          }
+          for (int t = 0; t < ntp; ++t)
+            bulk_g2s(st + C::kDnTile + t * C::kDnAct, ws.hq + size_t(pb + tok0 + t) * FB_HQ_STRIDE, C::kDnAct,
+                     &ring.full[s]);
+          if (failed) {  // nobody will use the entry: see its copies land (bounded), then leave
+            mbar_wait_hint(&ring.full[s], (i / S) & 1);
+            return;
+          }
+        }
+      }
     }
     return;
   }
@@ -318,182 +434,73 @@ gate_up_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   // ---------------- consumers
   const uint32_t* grid_lane = gridrep + lane;
   const uint32_t sign_base = smem_u32(signtab);
-  const int row_off = (lane >> 4) * C::kPart + (lane & 15) * C::kRowBytes;
+  const int gu_row_off = (lane >> 4) * C::kGuPart + (lane & 15) * C::kGuRowBytes;
+  // Even blocks start on a word boundary (their 27-word stream is 2 bytes off), odd blocks the other
+  // way round: two code paths. A warp keeps to one parity, and since warp w issues on scheduler w % 4,
+  // each scheduler's instruction cache sees one path only.
+  const int parity = warp & 1;
+  const int down_act = act_of(L.down_format);
   while (true) {
-    int s, task;
-    if (!draw_task_n<S, C::kTasks>(ring, &s_misc[1], ws.status, lane, s, task)) break;
+    int s, k;
+    if (!draw_task_n<S, C::kTasks / 2>(ring, &s_misc[1 + parity], ws.status, lane, s, k)) break;
+    const int task = 2 * k + parity;
     const int ntp = ring.meta[s].ntp;
-    uint8_t* st = stage0 + s * C::kStage;
-    const uint8_t* act0 = st + 2 * C::kPart;
-    const uint8_t* blk = st + row_off + task * 110;
+    const bool down = ring.meta[s].tile != 0;
+    uint8_t* st = stage0 + s * C::kSlot;
+    // the lane's block, the activation rows, and which of their blocks it meets
+    const uint8_t* blk = down ? st + (32 * k + lane) * C::kDnRowBytes + parity * 110 : st + gu_row_off + task * 110;
+    const uint8_t* act0 = st + (down ? C::kDnTile : 2 * C::kGuPart);
+    const int act_bytes = down ? C::kDnAct : C::kGuAct, act_k = down ? C::kInter : H, ablk = down ? parity : task;
+    float term[kTT];
+    if (parity == 0)
+      expert_block_terms<true>(reinterpret_cast<const uint32_t*>(blk), grid_lane, sign_base, act0, act_bytes, act_k, ablk,
+                               ntp, term);
+    else
+      expert_block_terms<false>(reinterpret_cast<const uint32_t*>(blk - 2), grid_lane, sign_base, act0, act_bytes, act_k,
+                                ablk, ntp, term);
     float* part = partials + (s * C::kTasks + task) * (kTT * 32);
-    const bool mis = (task & 1) == 0;  // even blocks start on a word boundary: their stream is 2 bytes off
-    const uint32_t* w = reinterpret_cast<const uint32_t*>(blk - (mis ? 0 : 2));
-    if (ntp == 1) {
-      const int8_t* a[1] = {reinterpret_cast<const int8_t*>(act0) + 256 * task};
-      const int16_t* as[1] = {reinterpret_cast<const int16_t*>(act0 + q8k_planar_asum_off(H)) + 8 * task};
-      int bs[1];
-      float d;
-      if (mis) {
-        iq3s_block_idot2<true, 1>(w, grid_lane, sign_base, a, as, bs);
-        d = iq3s_block_d<true>(w);
-      } else {
-        iq3s_block_idot2<false, 1>(w, grid_lane, sign_base, a, as, bs);
-        d = iq3s_block_d<false>(w);
-      }
-      part[lane] = float(bs[0]) * (d * reinterpret_cast<const float*>(act0 + H)[task]);
-    } else {
-      const uint8_t* act1 = act0 + C::kActBytes;
-      const int8_t* a[2] = {reinterpret_cast<const int8_t*>(act0) + 256 * task,
-                            reinterpret_cast<const int8_t*>(act1) + 256 * task};
-      const int16_t* as[2] = {reinterpret_cast<const int16_t*>(act0 + q8k_planar_asum_off(H)) + 8 * task,
-                              reinterpret_cast<const int16_t*>(act1 + q8k_planar_asum_off(H)) + 8 * task};
-      int bs[2];
-      float d;
-      if (mis) {
-        iq3s_block_idot2<true, 2>(w, grid_lane, sign_base, a, as, bs);
-        d = iq3s_block_d<true>(w);
-      } else {
-        iq3s_block_idot2<false, 2>(w, grid_lane, sign_base, a, as, bs);
-        d = iq3s_block_d<false>(w);
-      }
-      part[lane] = float(bs[0]) * (d * reinterpret_cast<const float*>(act0 + H)[task]);
-      part[32 + lane] = float(bs[1]) * (d * reinterpret_cast<const float*>(act1 + H)[task]);
-    }
-    // The warp that finishes the entry's last task adds the ten block terms of every row (fixed
-    // order), applies SwiGLU and hands the slot back to the producer.
+    part[lane] = term[0];
+    part[32 + lane] = term[1];
+    // The warp that finishes the entry's last task adds the block terms of every row in a fixed
+    // order, finishes the rows and hands the slot back to the producer.
     __threadfence_block();
     __syncwarp();
     int done = 0;
-    if (lane == 0) done = atomicAdd(&s_misc[2 + s], 1);
+    if (lane == 0) done = atomicAdd(&s_misc[3 + s], 1);
     done = __shfl_sync(0xffffffffu, done, 0);
-    if (done == C::kTasks - 1) {
-      __threadfence_block();
-      const int pair0 = ring.meta[s].pair0, j0 = ring.meta[s].row0;
+    if (done != C::kTasks - 1) continue;
+    __threadfence_block();
+    const int pair0 = ring.meta[s].pair0, r0 = ring.meta[s].row0;
+    const float* pt = partials + s * C::kTasks * (kTT * 32);
+    if (!down) {
       const int item = ring.meta[s].item, ipb = ring.meta[s].item_pair0, itok = ring.meta[s].item_tok;
-      const float* pt = partials + s * C::kTasks * (kTT * 32);
       for (int t = 0; t < ntp; ++t) {
         float v = 0.0f;
 #pragma unroll
         for (int b = 0; b < C::kTasks; ++b) v += pt[(b * kTT + t) * 32 + lane];
         const float u = __shfl_down_sync(0xffffffffu, v, 16);
-        if (lane < 16) ws.h[size_t(pair0 + t) * I + j0 + lane] = silu_mul(v, u);
+        if (lane < 16) ws.h[size_t(pair0 + t) * I + r0 + lane] = silu_mul(v, u);
       }
       __syncwarp();
       if (lane == 0) {
-        s_misc[2 + s] = 0;
+        s_misc[3 + s] = 0;
         mbar_arrive(&ring.empty[s]);
       }
-      item_contribution_done(ws, item, ipb, itok, tpi * ((itok + kTT - 1) / kTT), down_act, lane);
-    }
-  }
-}
-
-// ------------------------------------------------------------------------------ down, IQ3_S, inter 512
-// A row is two blocks (220 bytes); tile = 128 rows = four tasks of 32 rows, one row per lane, no
-// cross-warp reduction.
-struct Down3 {
-  static constexpr int kRows = 128, kRowBytes = 220, kWarps = 16, kTasks = 4, kStages = 5, kInter = 512;
-  static constexpr int kTile = kRows * kRowBytes;              // 28,160
-  static constexpr int kActBytes = q8k_planar_bytes(kInter);   // 608
-  static constexpr int kStage = kTile + kTT * kActBytes;       // 29,376
-  static constexpr size_t kSmem = size_t(kGridRepBytes) + 256 + size_t(kStages) * kStage + 128;
-};
-static_assert(Down3::kStage % 16 == 0 && Down3::kTile % 16 == 0, "bulk copy alignment");
-
-__global__ void __launch_bounds__((Down3::kWarps + 1) * 32, 1)
-down_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
-  using C = Down3;
-  constexpr int S = C::kStages;
-  extern __shared__ __align__(256) uint8_t smem[];
-  uint32_t* gridrep = reinterpret_cast<uint32_t*>(smem);
-  uint32_t* signtab = reinterpret_cast<uint32_t*>(smem + kGridRepBytes);
-  uint8_t* stage0 = smem + kGridRepBytes + 256;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stage0 + S * C::kStage);
-  __shared__ StageMeta s_meta[S];
-  __shared__ int s_misc[2 + S];
-  RingN<S> ring{bars, bars + S, s_meta, s_misc};
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  iq3s_half_tables_fill(gridrep, signtab);
-  if (tid == 0) {
-    ringn_init(ring);
-    for (int i = 1; i < 2 + S; ++i) s_misc[i] = 0;
-  }
-  __syncthreads();
-  pdl_launch_dependents();
-  pdl_wait_prior();
-
-  const fb_moe_decode_work* work = ws.work;
-  const int n_items = min(max(work->n_items, 0), kMaxPairs);
-  constexpr int tpi = H / C::kRows;
-  const int n_tiles = n_items * tpi;
-
-  if (warp == C::kWarps) {
-    if (lane == 0) {
-      producer_loop_n<S>(ring, ws, ws.sched + kSchedDown, n_tiles, tpi, C::kRows,
-                         [&](int s, int slot_id, int sub, int pair0, int ntp) {
-                           const uint8_t* blob = L.slots + int64_t(slot_id) * L.blob_stride;
-                           uint8_t* st = stage0 + s * C::kStage;
-                           mbar_expect_tx(&ring.full[s], uint32_t(C::kTile + ntp * C::kActBytes));
-                           bulk_g2s(st, blob + L.down_offset + size_t(sub) * C::kTile, C::kTile, &ring.full[s]);
-                           for (int t = 0; t < ntp; ++t)
-                             bulk_g2s(st + C::kTile + t * C::kActBytes, ws.hq + size_t(pair0 + t) * FB_HQ_STRIDE,
-                                      C::kActBytes, &ring.full[s]);
-                         });
-    }
-    return;
-  }
-
-  const uint32_t* grid_lane = gridrep + lane;
-  const uint32_t sign_base = smem_u32(signtab);
-  while (true) {
-    int s, task;
-    if (!draw_task_n<S, C::kTasks>(ring, &s_misc[1], ws.status, lane, s, task)) break;
-    const int ntp = ring.meta[s].ntp, pair0 = ring.meta[s].pair0, r0 = ring.meta[s].row0;
-    const float w0 = ring.meta[s].wgt[0], w1 = ring.meta[s].wgt[1];
-    uint8_t* st = stage0 + s * C::kStage;
-    const uint8_t* act0 = st + C::kTile;
-    const int row = 32 * task + lane;
-    const uint32_t* unit = reinterpret_cast<const uint32_t*>(st + row * C::kRowBytes);
-    const uint32_t* wB = unit + 27;  // the word whose high half holds the second block's scale
-    if (ntp == 1) {
-      const int8_t* a[1] = {reinterpret_cast<const int8_t*>(act0)};
-      const int16_t* as[1] = {reinterpret_cast<const int16_t*>(act0 + q8k_planar_asum_off(C::kInter))};
-      const float* da = reinterpret_cast<const float*>(act0 + C::kInter);
-      int bs[1];
-      iq3s_block_idot2<true, 1>(unit, grid_lane, sign_base, a, as, bs);
-      float acc = float(bs[0]) * (iq3s_block_d<true>(unit) * da[0]);
-      const int8_t* a2[1] = {a[0] + 256};
-      const int16_t* as2[1] = {as[0] + 8};
-      iq3s_block_idot2<false, 1>(wB, grid_lane, sign_base, a2, as2, bs);
-      acc = fmaf(float(bs[0]), iq3s_block_d<false>(wB) * da[1], acc);
-      ws.partial[size_t(pair0) * H + r0 + row] = w0 * acc;
+      item_contribution_done(ws, item, ipb, itok, gu_tpi * ((itok + kTT - 1) / kTT), down_act, I, lane);
     } else {
-      const uint8_t* act1 = act0 + C::kActBytes;
-      const int8_t* a[2] = {reinterpret_cast<const int8_t*>(act0), reinterpret_cast<const int8_t*>(act1)};
-      const int16_t* as[2] = {reinterpret_cast<const int16_t*>(act0 + q8k_planar_asum_off(C::kInter)),
-                              reinterpret_cast<const int16_t*>(act1 + q8k_planar_asum_off(C::kInter))};
-      const float* da0 = reinterpret_cast<const float*>(act0 + C::kInter);
-      const float* da1 = reinterpret_cast<const float*>(act1 + C::kInter);
-      int bs[2];
-      iq3s_block_idot2<true, 2>(unit, grid_lane, sign_base, a, as, bs);
-      const float dA = iq3s_block_d<true>(unit);
-      float acc0 = float(bs[0]) * (dA * da0[0]), acc1 = float(bs[1]) * (dA * da1[0]);
-      const int8_t* a2[2] = {a[0] + 256, a[1] + 256};
-      const int16_t* as2[2] = {as[0] + 8, as[1] + 8};
-      iq3s_block_idot2<false, 2>(wB, grid_lane, sign_base, a2, as2, bs);
-      const float dB = iq3s_block_d<false>(wB);
-      acc0 = fmaf(float(bs[0]), dB * da0[1], acc0);
-      acc1 = fmaf(float(bs[1]), dB * da1[1], acc1);
-      ws.partial[size_t(pair0) * H + r0 + row] = w0 * acc0;
-      ws.partial[size_t(pair0 + 1) * H + r0 + row] = w1 * acc1;
-    }
-    __syncwarp();
-    if (lane == 0) {
-      const int done = atomicAdd(&s_misc[2 + s], 1);
-      if (done == C::kTasks - 1) {  // the tile's last task hands the slot back to the producer
-        s_misc[2 + s] = 0;
+      const float w0 = ring.meta[s].wgt[0], w1 = ring.meta[s].wgt[1];
+#pragma unroll
+      for (int g = 0; g < C::kDnRows / 32; ++g) {
+        const float v0 = pt[((2 * g) * kTT + 0) * 32 + lane] + pt[((2 * g + 1) * kTT + 0) * 32 + lane];
+        ws.partial[size_t(pair0) * H + r0 + 32 * g + lane] = w0 * v0;
+        if (ntp == 2) {
+          const float v1 = pt[((2 * g) * kTT + 1) * 32 + lane] + pt[((2 * g + 1) * kTT + 1) * 32 + lane];
+          ws.partial[size_t(pair0 + 1) * H + r0 + 32 * g + lane] = w1 * v1;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        s_misc[3 + s] = 0;
         mbar_arrive(&ring.empty[s]);
       }
     }

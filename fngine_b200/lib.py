@@ -7,7 +7,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libfngine_b200.so")
+# FNGINE_B200_LIB names another build of the same library (A/B runs of kernel variants).
+LIB_PATH = os.environ.get("FNGINE_B200_LIB") or os.path.join(HERE, "libfngine_b200.so")
 
 FMT_IQ4_NL, FMT_IQ3_S = 20, 21
 DT_F32, DT_BF16 = 0, 1
@@ -92,6 +93,7 @@ _SIGNATURES = {
     "fb_moe_select_publish": (_I32, [_P, _I32, _P, _I32, _P, _I32, _P, _P, _I32, C.POINTER(DecodeWorkspace), _P, _P]),
     "fb_moe_hot_gate_up": (_I32, [C.POINTER(ExpertLayout), _I32, C.POINTER(DecodeWorkspace), _P]),
     "fb_moe_hot_down": (_I32, [C.POINTER(ExpertLayout), _I32, C.POINTER(DecodeWorkspace), _P]),
+    "fb_moe_hot_experts": (_I32, [C.POINTER(ExpertLayout), _I32, C.POINTER(DecodeWorkspace), _P]),
     "fb_moe_combine": (_I32, [C.POINTER(DecodeWorkspace), _P, _P, _I32, _P, _P, _P, _P, _I32, C.c_longlong, _P,
                               C.c_float, _P]),
     "fb_moe_layer_decode": (_I32, [_P, C.POINTER(ExpertLayout), _P, _I32, _I32, C.POINTER(DecodeWorkspace), _P, _P, _P]),

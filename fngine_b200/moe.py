@@ -139,6 +139,11 @@ def moe_hot_down(layer, tokens, ws):
     L.check(L.load().fb_moe_hot_down(C.byref(layer.layout), tokens, C.byref(ws.ws), _stream()), "moe_hot_down")
 
 
+def moe_hot_experts(layer, tokens, ws):
+    """moe_hot_gate_up + moe_hot_down, one launch where the formats allow it."""
+    L.check(L.load().fb_moe_hot_experts(C.byref(layer.layout), tokens, C.byref(ws.ws), _stream()), "moe_hot_experts")
+
+
 def moe_combine(ws, y_shared, exchange, layer, seq, inj, X, y_out, tokens, timeout_cycles=0, ablate_direction=None,
                 ablate_scale=0.0):
     L.check(L.load().fb_moe_combine(C.byref(ws.ws), _ptr(y_shared), exchange, layer, _ptr(seq), _ptr(inj), _ptr(X),

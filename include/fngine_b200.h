@@ -153,6 +153,12 @@ int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, c
 /* moe_hot_down, src/kernels/moe/moe.h:141-142: partial[pair][n] = w_pair * (down_n . q8(h[pair])). */
 int32_t fb_moe_hot_down(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
                         void* stream);
+/* moe_hot_gate_up followed by moe_hot_down as ONE launch where the formats allow it (IQ3_S gate/up and
+ * down: a persistent kernel streams all gate/up tiles and then all down tiles through one pipeline, an
+ * expert's down tiles waiting for its re-quantized h); otherwise the two launches. Same results as the
+ * two calls, bit for bit. No counterpart in the reference as a single function. */
+int32_t fb_moe_hot_experts(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
+                           void* stream);
 /* moe_combine, src/kernels/moe/moe.h:154-158: y[t] = sum of token t's partials in slot order
  * + y_shared[t] (optional); X[t][s][d] += inj[t][s] * y[t][d] when X is given; y_out optional.
  * `exchange` must be NULL (no CPU tier), so timeout_cycles is unused; the rank-1 ablation of the

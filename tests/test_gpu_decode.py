@@ -35,6 +35,14 @@ def fast_lib():
     return O.ref()
 
 
+def q8k_sums32(blocks, k):
+    """Sums of every 32 codes of ggml Q8_K blocks: block_q8_K's bsums (16-code groups) added in pairs,
+    int16 [k / 32]; the planar workspace rows keep them behind the scales (64 bytes after the codes)."""
+    b = blocks.reshape(k // 256, 292)
+    bs = b[:, 260:292].copy().view(np.int16).astype(np.int32).reshape(-1, 8, 2).sum(axis=2)
+    return bs.reshape(-1).astype(np.int16)
+
+
 def planar_from_blocks(act, blocks, k):
     """ggml activation blocks -> (codes int8 [k] in the workspace order, scales float32)."""
     if act == O.ACT_Q8_K:
@@ -156,9 +164,11 @@ def test_router_and_select(tokens, bf16):
     # int8 activations: bit-identical to the host quantizer
     xq = ws.xq(tokens)
     for t in range(tokens):
-        codes, scales = planar_from_blocks(O.ACT_Q8_K, O.quantize_act(O.ACT_Q8_K, x[t]), H)
+        blocks = O.quantize_act(O.ACT_Q8_K, x[t])
+        codes, scales = planar_from_blocks(O.ACT_Q8_K, blocks, H)
         assert np.array_equal(xq[t, :H].view(np.int8), codes)
         assert np.array_equal(xq[t, H:H + 40].copy().view(np.float32), scales)
+        assert np.array_equal(xq[t, H + 64:H + 64 + 160].copy().view(np.int16), q8k_sums32(blocks, H))
     assert ws.status() == 0
 
 
@@ -303,9 +313,12 @@ def test_crowded_experts_and_h_requantization(fg, fd):
     hs, hq = ws.h(work.n_pairs), ws.hq(work.n_pairs)
     nscale = inter // (256 if act == O.ACT_Q8_K else 32)
     for p in range(work.n_pairs):
-        codes, scales = planar_from_blocks(act, O.quantize_act(act, hs[p]), inter)
+        blocks = O.quantize_act(act, hs[p])
+        codes, scales = planar_from_blocks(act, blocks, inter)
         assert np.array_equal(hq[p, :inter].view(np.int8), codes)
         assert np.array_equal(hq[p, inter:inter + 4 * nscale].copy().view(np.float32), scales)
+        if act == O.ACT_Q8_K:
+            assert np.array_equal(hq[p, inter + 64:inter + 64 + inter // 16].copy().view(np.int16), q8k_sums32(blocks, inter))
     assert ws.status() == 0
 
 
