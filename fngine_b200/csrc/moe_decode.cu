@@ -66,6 +66,10 @@ __host__ __device__ constexpr int act_row_bytes_planar(int act, int k) {
   return act == FB_ACT_Q8_K ? k + 64 : k + k / 8;
 }
 __host__ __device__ constexpr int act_of(int fmt) { return fmt == FB_FMT_IQ3_S ? FB_ACT_Q8_K : FB_ACT_Q8_0; }
+// ws.xq holds [2][16][FB_XQ_STRIDE]: the Q8_K rows of the step's tokens, then their Q8_0 rows. A workspace
+// made for a layout gets the one its gate/up format needs; one made without a layout gets both from
+// the stand-alone selection (which does not see the layout).
+__host__ __device__ constexpr size_t xq_offset(int act) { return act == FB_ACT_Q8_0 ? size_t(kMaxTok) * FB_XQ_STRIDE : 0; }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + expf(-g)) * u; }
 
@@ -352,7 +356,9 @@ __global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ l
       if constexpr (XBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(xv)[size_t(t) * H + i]);
       else return static_cast<const float*>(xv)[size_t(t) * H + i];
     };
-    quantize_row_planar(act_of(ws.gate_up_format), H, load, ws.xq + size_t(t) * FB_XQ_STRIDE);
+    for (int act = FB_ACT_Q8_K; act <= FB_ACT_Q8_0; ++act)
+      if (ws.gate_up_format == 0 || act_of(ws.gate_up_format) == act)
+        quantize_row_planar(act, H, load, ws.xq + xq_offset(act) + size_t(t) * FB_XQ_STRIDE);
     return;
   }
   select_block(
@@ -370,6 +376,7 @@ struct EpRouteArgs {
   int parity;
   uint32_t step;
   uint32_t spin_limit;  // polls per awaited line
+  int act;              // activation format the layer's gate/up weights pair with (set for every launch)
 };
 
 // Router projection, activation quantization and selection in one launch (the head of the fused
@@ -498,7 +505,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
   }
   // activation quantization, one warp per ggml block, strided over every warp of the grid
   {
-    const int act = act_of(ws.gate_up_format);
+    const int act = ep.act;
     const int per_tok = act == FB_ACT_Q8_K ? H / 256 : H / 32;
     const int n_warps = gridDim.x * 16;
     for (int task = blockIdx.x * 16 + warp; task < T * per_tok; task += n_warps) {
@@ -507,7 +514,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
         if constexpr (XBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(xv)[size_t(t) * H + i]);
         else return static_cast<const float*>(xv)[size_t(t) * H + i];
       };
-      uint8_t* out = ws.xq + size_t(t) * FB_XQ_STRIDE;
+      uint8_t* out = ws.xq + xq_offset(act) + size_t(t) * FB_XQ_STRIDE;
       float* scales = reinterpret_cast<float*>(out + H);
       if (act == FB_ACT_Q8_K) {
         float v[8];
@@ -919,7 +926,8 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
                       bulk_g2s(st + kUp, blob + L.up_offset + off, kPart, &ring.full[s]);
                       for (int t = 0; t < ntp; ++t)
                         bulk_g2s(st + kStageW + t * C::kActBytes,
-                                 ws.xq + size_t(s_work.pair_token[pair0 + t]) * FB_XQ_STRIDE, C::kActBytes,
+                                 ws.xq + xq_offset(C::kAct) + size_t(s_work.pair_token[pair0 + t]) * FB_XQ_STRIDE,
+                                 C::kActBytes,
                                  &ring.full[s]);
                     });
     }
@@ -1241,6 +1249,14 @@ bool layout_ok(const fb_moe_expert_layout* L) {
 // Polls a reader gives a peer-written exchange line before it records FB_STATUS_PIPELINE_TIMEOUT.
 uint32_t g_peer_wait_polls = kPeerSpinLimit;
 
+// A workspace made for a layout must be used with that layout; one made without (formats 0) fits all.
+bool ws_fits(const fb_moe_decode_workspace* ws, const fb_moe_expert_layout* L, bool gate_up, bool down) {
+  if (ws->inter && ws->inter != L->inter) return false;
+  if (gate_up && ws->gate_up_format && ws->gate_up_format != L->gate_up_format) return false;
+  if (down && ws->down_format && ws->down_format != L->down_format) return false;
+  return true;
+}
+
 bool ws_ok(const fb_moe_decode_workspace* ws) {
   return ws && ws->work && ws->xq && ws->h && ws->hq && ws->partial && ws->item_done && ws->sched && ws->status;
 }
@@ -1255,20 +1271,20 @@ extern "C" {
 size_t fb_moe_decode_workspace_bytes(int32_t inter) {
   (void)inter;
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
-  return up(sizeof(fb_moe_decode_work)) + up(size_t(kMaxTok) * FB_XQ_STRIDE) + up(size_t(kMaxPairs) * 640 * 4) +
+  return up(sizeof(fb_moe_decode_work)) + up(size_t(2 * kMaxTok) * FB_XQ_STRIDE) + up(size_t(kMaxPairs) * 640 * 4) +
          up(size_t(kMaxPairs) * FB_HQ_STRIDE) + up(size_t(kMaxPairs) * H * 4) + up(kMaxPairs * 4) +
          up(kSchedInts * 4) + 256;
 }
 
 int32_t fb_moe_decode_workspace_make(void* base, const fb_moe_expert_layout* layout, fb_moe_decode_workspace* out) {
   if (!base || !out || (reinterpret_cast<uintptr_t>(base) & 255)) return invalid("decode workspace: base must be 256-byte aligned");
-  if (!layout_ok(layout)) return invalid("decode workspace: unsupported expert layout");
+  if (layout && !layout_ok(layout)) return invalid("decode workspace: unsupported expert layout");
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
   uint8_t* p = static_cast<uint8_t*>(base);
   out->work = reinterpret_cast<fb_moe_decode_work*>(p);
   p += up(sizeof(fb_moe_decode_work));
   out->xq = p;
-  p += up(size_t(kMaxTok) * FB_XQ_STRIDE);
+  p += up(size_t(2 * kMaxTok) * FB_XQ_STRIDE);
   out->h = reinterpret_cast<float*>(p);
   p += up(size_t(kMaxPairs) * 640 * 4);
   out->hq = p;
@@ -1280,9 +1296,9 @@ int32_t fb_moe_decode_workspace_make(void* base, const fb_moe_expert_layout* lay
   out->sched = reinterpret_cast<int32_t*>(p);
   p += up(kSchedInts * 4);
   out->status = reinterpret_cast<uint32_t*>(p);
-  out->gate_up_format = layout->gate_up_format;
-  out->down_format = layout->down_format;
-  out->inter = layout->inter;
+  out->gate_up_format = layout ? layout->gate_up_format : 0;  // 0: any (the selection quantizes x both ways)
+  out->down_format = layout ? layout->down_format : 0;
+  out->inter = layout ? layout->inter : 0;
   out->reserved = 0;
   return 0;
 }
@@ -1337,8 +1353,7 @@ static int32_t launch_experts_iq3s(const fb_moe_expert_layout* layout, const fb_
 int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
                            void* stream) {
   if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_gate_up: bad arguments");
-  if (layout->inter != ws->inter || layout->gate_up_format != ws->gate_up_format ||
-      layout->down_format != ws->down_format)
+  if (!ws_fits(ws, layout, true, true))
     return invalid("hot_gate_up: workspace was made for a different layout");
   const dim3 grid(sm_count());
   if (layout->gate_up_format == FB_FMT_IQ3_S) return launch_experts_iq3s(layout, ws, kPhaseGateUp, stream, "hot_gate_up");
@@ -1358,8 +1373,7 @@ int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, c
 int32_t fb_moe_hot_experts(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
                            void* stream) {
   if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_experts: bad arguments");
-  if (layout->inter != ws->inter || layout->gate_up_format != ws->gate_up_format ||
-      layout->down_format != ws->down_format)
+  if (!ws_fits(ws, layout, true, true))
     return invalid("hot_experts: workspace was made for a different layout");
   if (layout->gate_up_format == FB_FMT_IQ3_S && layout->down_format == FB_FMT_IQ3_S)
     return launch_experts_iq3s(layout, ws, kPhaseGateUp | kPhaseDown, stream, "hot_experts");
@@ -1394,7 +1408,7 @@ static int32_t launch_down(const fb_moe_expert_layout* layout, const fb_moe_deco
 int32_t fb_moe_hot_down(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
                         void* stream) {
   if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_down: bad arguments");
-  if (layout->inter != ws->inter || layout->down_format != ws->down_format)
+  if (!ws_fits(ws, layout, false, true))
     return invalid("hot_down: workspace was made for a different layout");
   return launch_down(layout, ws, stream);
 }
@@ -1421,6 +1435,7 @@ static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_
   const bool with_combine = ep == nullptr;
   EpRouteArgs era{};
   if (ep) era = *ep;
+  era.act = layout_ok(layout) ? act_of(layout->gate_up_format) : FB_ACT_Q8_K;
   // Three launches for IQ3_S experts (four otherwise): route (router projection + activation quantization
   // + selection), the expert kernel (gate/up and down tiles in one persistent launch; the other formats
   // take a gate/up and a down launch), combine. The expert arithmetic is that of the separate entry points. The route kernel
@@ -1431,8 +1446,7 @@ static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_
   if (!router_w_bf16 || !x || (!y_out && with_combine) || !logits_scratch || !layout_ok(layout) || !ws_ok(ws) ||
       tokens < 1 || tokens > kMaxTok)
     return invalid("layer_decode: bad arguments (tokens must be 1..16, logits scratch [tokens][513] required)");
-  if (layout->inter != ws->inter || layout->gate_up_format != ws->gate_up_format ||
-      layout->down_format != ws->down_format)
+  if (!ws_fits(ws, layout, true, true))
     return invalid("layer_decode: workspace was made for a different layout");
   // the [8][16][512] slice sums borrow the head of ws->partial, which nothing reads before the down kernel
   const dim3 grid(kRouteGroups * kRouteSplits), block(512);

@@ -79,14 +79,16 @@ def fill_experts(buf, stride, gate_up_format, down_format, gu_bytes, nb_gu, nb_d
 class DecodeWorkspace:
     """MoeDecodeWorkspace (moe.h:108-117 of the reference): caller-owned, allocated once."""
 
-    def __init__(self, layer, device="cuda"):
+    def __init__(self, layer=None, device="cuda"):
+        """layer=None makes a workspace that fits every layout (the reference's make_moe_decode_workspace takes
+        no layout either); the stand-alone selection then quantizes x for both activation formats."""
         self.lib = L.load()
-        n = self.lib.fb_moe_decode_workspace_bytes(layer.layout.inter)
+        n = self.lib.fb_moe_decode_workspace_bytes(layer.layout.inter if layer is not None else 640)
         self.buf = torch.zeros(n + 256, dtype=torch.uint8, device=device)
         base = (self.buf.data_ptr() + 255) & ~255
         self.ws = L.DecodeWorkspace()
-        L.check(self.lib.fb_moe_decode_workspace_make(base, C.byref(layer.layout), C.byref(self.ws)),
-                "decode_workspace_make")
+        L.check(self.lib.fb_moe_decode_workspace_make(base, C.byref(layer.layout) if layer is not None else None,
+                                                      C.byref(self.ws)), "decode_workspace_make")
         self.logits = torch.empty(L.DECODE_MAX_TOKENS * L.ROUTER_ROWS, dtype=torch.float32, device=device)
 
     def _view(self, ptr, nbytes):
@@ -101,14 +103,16 @@ class DecodeWorkspace:
     def status(self):
         return int(self._view(self.ws.status, 4).view(torch.int32).item())
 
-    def xq(self, tokens):
-        return self._view(self.ws.xq, L.DECODE_MAX_TOKENS * L.XQ_STRIDE).view(L.DECODE_MAX_TOKENS, L.XQ_STRIDE)[:tokens].cpu().numpy()
+    def xq(self, tokens, act=L.ACT_Q8_K):
+        """Planar activation rows of the step's tokens: the Q8_K rows, or (act = ACT_Q8_0) the Q8_0 rows."""
+        both = self._view(self.ws.xq, 2 * L.DECODE_MAX_TOKENS * L.XQ_STRIDE).view(2, L.DECODE_MAX_TOKENS, L.XQ_STRIDE)
+        return both[1 if act == L.ACT_Q8_0 else 0, :tokens].cpu().numpy()
 
     def hq(self, pairs):
         return self._view(self.ws.hq, L.DECODE_MAX_PAIRS * L.HQ_STRIDE).view(L.DECODE_MAX_PAIRS, L.HQ_STRIDE)[:pairs].cpu().numpy()
 
     def h(self, pairs):
-        inter = self.ws.inter
+        inter = self.ws.inter or 640
         return self._view(self.ws.h, L.DECODE_MAX_PAIRS * inter * 4).view(torch.float32).view(L.DECODE_MAX_PAIRS, inter)[:pairs].cpu().numpy()
 
     def partial(self, pairs):

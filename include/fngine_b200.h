@@ -3,8 +3,8 @@
  * Every entry point replaces one function of the reference engine's kernel interface for the
  * routed-expert MoE path and the FP8-row dense projection; the comment above each declaration
  * names the reference declaration it stands in for (paths relative to the reference project).
- * The reference exposes these as C++ free functions (namespace fngine::kernels); the header
- * include/fngine_b200/kernels.hpp re-creates those C++ names on top of this ABI.
+ * The reference exposes these as C++ free functions (namespace fngine::kernels); the translation unit
+ * fngine_b200/binding/fngine_kernels_b200.cpp defines those C++ names on top of this ABI.
  *
  * Conventions (same as the reference, src/kernels/moe/moe.h:19-24, src/kernels/linear/linear.h:46-47):
  *  - all tensor arguments are raw device pointers owned by the caller; kernels never allocate and
@@ -113,7 +113,7 @@ typedef struct fb_moe_decode_work {
  * when a bounded wait runs out. */
 typedef struct fb_moe_decode_workspace {
   fb_moe_decode_work* work;
-  uint8_t* xq;        /* [16][FB_XQ_STRIDE] */
+  uint8_t* xq;        /* [2][16][FB_XQ_STRIDE]: Q8_K rows, then Q8_0 rows */
   float* h;           /* [160 pairs][inter] fp32 silu(g)*u */
   uint8_t* hq;        /* [160 pairs][FB_HQ_STRIDE] */
   float* partial;     /* [160 pairs][2560], routing weight applied */
@@ -128,7 +128,11 @@ typedef struct fb_moe_decode_workspace {
 enum { FB_XQ_STRIDE = 2880, FB_HQ_STRIDE = 720 };
 
 /* moe_decode_workspace_bytes / make_moe_decode_workspace, src/kernels/moe/moe.h:116-117.
- * `base` is 256-byte aligned device memory of at least the returned size, zero-filled once. */
+ * `base` is 256-byte aligned device memory of at least the returned size, zero-filled once. The carve
+ * depends on `base` only (`work` is the first region). `layout` may be NULL, as the reference's
+ * make_moe_decode_workspace(base) has none: the workspace then fits every supported layout, and
+ * fb_moe_select_publish, which does not see the layout either, quantizes x for both activation
+ * formats (Q8_K and Q8_0) instead of the one the layout's gate/up format needs. */
 size_t fb_moe_decode_workspace_bytes(int32_t inter);
 int32_t fb_moe_decode_workspace_make(void* base, const fb_moe_expert_layout* layout,
                                      fb_moe_decode_workspace* out);

@@ -127,6 +127,11 @@ def ref():
         lib.ref_moe_layer.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_void_p,
                                       C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
         lib.ref_expert_ffn_bf16.argtypes = lib.ref_expert_ffn.argtypes
+        if hasattr(lib, "ref_pool_decode_step"):  # built where the CUDA headers (bf16 type) were present
+            lib.ref_pool_decode_step.restype = C.c_int
+            lib.ref_pool_decode_step.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.c_int, C.c_longlong,
+                                                 C.c_longlong, C.c_longlong, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+                                                 C.c_int, C.c_void_p, C.c_char_p, C.c_int]
         _ref = lib
     return _ref
 
@@ -252,6 +257,34 @@ def moe_layer(fmt_gu, fmt_down, hidden, inter, blobs, blob_stride, x, ids, w, th
     fn = port().fbo_moe_layer if (lib is None or lib is port()) else lib.ref_moe_layer
     fn(fmt_gu, fmt_down, hidden, inter, _ptr(blobs), blob_stride, _ptr(x), T, k, _ptr(ids), _ptr(w), _ptr(y),
        threads)
+    return y
+
+
+def pool_available():
+    """True where the reference's own cpu::ExpertPool was built into oracle/_ref and can run here."""
+    return ref() is not None and hasattr(ref(), "ref_pool_decode_step")
+
+
+def pool_decode_step(fmt_gu, fmt_down, blobs, blob_stride, x_bf16, ids, w, workers=4):
+    """One decode step of one layer through the reference's production CPU tier, cpu::ExpertPool
+    (src/cpu/expert_pool.h:76-102), driven through its host exchange as the reference's harness does
+    (tests/cpu/pool_bench.h:42-140). The pool's shape is fixed: hidden 2560, intermediate 640, a Q8_0-family
+    down format. blobs: experts `blob_stride` bytes apart (gate | up | down back to back); x_bf16: uint16
+    [T][2560], T <= 16; ids int32 [T][10] index into blobs; w float32 [T][10]. Returns y float32 [T][2560]."""
+    lib = ref()
+    blobs = np.ascontiguousarray(blobs, dtype=np.uint8)
+    x = np.ascontiguousarray(x_bf16, dtype=np.uint16).reshape(-1, 2560)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    T = x.shape[0]
+    assert ids.shape == (T, 10) and w.shape == (T, 10)
+    gate_bytes = 640 * row_bytes(fmt_gu, 2560)
+    y = np.empty((T, 2560), dtype=np.float32)
+    err = C.create_string_buffer(512)
+    rc = lib.ref_pool_decode_step(fmt_gu, fmt_down, _ptr(blobs), blob_stride, blobs.size // blob_stride, 0, gate_bytes,
+                                  2 * gate_bytes, _ptr(x), T, _ptr(ids), _ptr(w), workers, _ptr(y), err, 512)
+    if rc:
+        raise RuntimeError("cpu::ExpertPool step failed: " + err.value.decode("utf-8", "replace"))
     return y
 
 

@@ -571,3 +571,70 @@ def test_peer_wait_that_nobody_answers_runs_out_and_is_reported():
     moe.moe_layer_decode(wr, full, x, ws3, y2)
     torch.cuda.synchronize()
     assert ws3.status() == 0 and torch.equal(y2, y_ref)
+
+
+@pytest.mark.parametrize("fg,fd,inter", [(IQ3_S, IQ3_S, 512), (IQ4_NL, IQ4_NL, 512), (IQ3_S, IQ4_NL, 640)])
+def test_workspace_without_a_layout_gives_the_same_bits(fg, fd, inter):
+    """The reference makes its decode workspace from a base address alone (make_moe_decode_workspace,
+    src/kernels/moe/moe.h:117) and its selection does not see the expert layout. A workspace made that way
+    (NULL layout) must drive select -> gate/up -> down -> combine to the same bits as one made for the
+    layout; the selection then writes the tokens' Q8_K and Q8_0 rows both."""
+    torch = _torch()
+    from fngine_b200 import moe
+    tokens = 7
+    layer = moe.synth_layer(fg, fd, inter, 512, 909)
+    wr = torch.from_numpy(synth.router_weights(41, rows=513).view(np.int16)).cuda().view(torch.bfloat16)
+    x = torch.from_numpy(synth.to_bf16_bits(synth.activations(42, tokens)).view(np.int16)).cuda().view(torch.bfloat16)
+    outs = []
+    for ws in (moe.DecodeWorkspace(layer), moe.DecodeWorkspace(None)):
+        y = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+        moe.router_logits(wr, x, ws.logits)
+        moe.moe_select_publish(ws.logits, x, None, 0, None, None, tokens, ws)
+        moe.moe_hot_gate_up(layer, tokens, ws)
+        moe.moe_hot_down(layer, tokens, ws)
+        moe.moe_combine(ws, None, None, 0, None, None, None, y, tokens)
+        torch.cuda.synchronize()
+        assert ws.status() == 0
+        outs.append(y)
+    assert torch.equal(outs[0], outs[1])
+    both = moe.DecodeWorkspace(None)
+    moe.router_logits(wr, x, both.logits)
+    moe.moe_select_publish(both.logits, x, None, 0, None, None, tokens, both)
+    torch.cuda.synchronize()
+    xf = synth.bf16_bits_to_f32(synth.to_bf16_bits(synth.activations(42, tokens)))
+    for act in (O.ACT_Q8_K, O.ACT_Q8_0):
+        rows = both.xq(tokens, act)
+        for t in range(tokens):
+            codes, scales = planar_from_blocks(act, O.quantize_act(act, xf[t]), H)
+            assert np.array_equal(rows[t, :H].view(np.int8), codes)
+            assert np.array_equal(rows[t, H:H + 4 * len(scales)].copy().view(np.float32), scales)
+
+
+@pytest.mark.skipif(not O.pool_available(), reason="the reference's cpu::ExpertPool is not built on this host")
+def test_decode_layer_against_the_reference_expert_pool():
+    """The GPU decode layer at the reference's native shape (IQ3_S gate/up, IQ4_NL down, intermediate 640,
+    bf16 tokens) against the reference's production CPU tier, cpu::ExpertPool, run through its own host
+    exchange on the same tokens, experts and routing weights."""
+    torch = _torch()
+    from fngine_b200 import moe
+    tokens, inter, seed = 9, 640, 2027
+    layer = moe.synth_layer(IQ3_S, IQ4_NL, inter, 512, seed)
+    ws = moe.DecodeWorkspace(layer)
+    wr = torch.from_numpy(synth.router_weights(515, rows=512).view(np.int16)).cuda().view(torch.bfloat16)
+    xb = synth.to_bf16_bits(synth.activations(516, tokens))
+    x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    y = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    moe.moe_layer_decode(wr, layer, x, ws, y)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    logits = ws.logits.cpu().numpy()[:tokens * 513].reshape(tokens, 513)[:, :512]
+    ids, w = O.topk(logits)
+    used = sorted(set(ids.reshape(-1).tolist()))
+    stride = synth.blob_bytes(IQ3_S, IQ4_NL, inter)
+    blobs = np.concatenate([synth.expert_blob(IQ3_S, IQ4_NL, inter, seed, e) for e in used])
+    local = np.vectorize({e: i for i, e in enumerate(used)}.get)(ids).astype(np.int32)
+    want = O.pool_decode_step(IQ3_S, IQ4_NL, blobs, stride, xb, local, w)
+    got = y.cpu().numpy()
+    err = max(rel_l2(got[t], want[t]) for t in range(tokens))
+    print("decode layer vs cpu::ExpertPool (inter 640, IQ3_S + IQ4_NL): max rel L2 %.2e" % err)
+    assert err <= TOL, err

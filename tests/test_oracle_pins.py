@@ -196,6 +196,41 @@ def test_port_equals_reference_moe_layer():
     assert np.array_equal(bits(y0), bits(y1))
 
 
+@pytest.mark.skipif(not O.pool_available(), reason="the reference's cpu::ExpertPool is not built here")
+@pytest.mark.parametrize("fg,fd", [(IQ3_S, IQ4_NL), (IQ4_NL, IQ4_NL)])
+def test_port_equals_the_reference_expert_pool(fg, fd):
+    """The reference's production CPU tier itself, cpu::ExpertPool at its native shape (intermediate 640, Q8_0
+    down), run through its host exchange: the restatement's MoE layer gives the same bits for the same bf16
+    tokens, experts and weights. Batch sizes 1 and 9 (tokens share experts, so the pool groups pairs)."""
+    inter, E = 640, 14
+    stride = synth.blob_bytes(fg, fd, inter)
+    blobs = np.concatenate([synth.expert_blob(fg, fd, inter, 31, e) for e in range(E)])
+    rng = np.random.default_rng(5)
+    for T in (1, 9):
+        xb = synth.to_bf16_bits(synth.activations(60 + T, T))
+        ids = np.stack([rng.permutation(E)[:10] for _ in range(T)]).astype(np.int32)
+        w = rng.random((T, 10)).astype(np.float32)
+        want = O.pool_decode_step(fg, fd, blobs, stride, xb, ids, w, workers=3)
+        got = O.moe_layer(fg, fd, 2560, inter, blobs, stride, synth.bf16_bits_to_f32(xb), ids, w, threads=2)
+        assert np.array_equal(bits(got), bits(want))
+
+
+def test_split_tokens_e4m3x2_is_lossless():
+    """The two-piece activation split of the exact FP8-row route (the statement the GPU kernel is checked
+    against): scale * (hi + lo) returns every bf16 value of at least 2^-9 of its row's scaled range exactly."""
+    x = synth.activations(3, 6) * np.array([1e-3, 0.1, 1.0, 7.0, 300.0, 1e4], dtype=np.float32)[:, None]
+    xb = synth.to_bf16_bits(x)
+    hi, lo, sc = O.split_tokens_e4m3x2(xb)
+    tab = O.e4m3_table().astype(np.float64)
+    v = synth.bf16_bits_to_f32(xb).astype(np.float64)
+    s = sc.astype(np.float64)[:, None]
+    back = s * (tab[hi] + tab[lo])
+    big = np.abs(v) >= 0.25 * s
+    assert np.array_equal(back[big], v[big]) and np.all(np.abs(back - v) <= s * 2.0 ** -10)
+    mx = np.abs(v).max(axis=1)
+    assert np.all((mx / sc >= 128) & (mx / sc < 256))
+
+
 def test_linear_fp8_a16_known_answers():
     """The fp64 statement of the exact-activation FP8-row projection on values chosen so that every
     product is an integer: weights E4M3 {1, -2, 0.5, 448}, activations bf16 {2, 4, -8, 0.5}."""
