@@ -75,3 +75,38 @@ def moe_layer_prefill(router_logits, layer, x, ws, y_out):
     moe_grouped_gate_up(layer, None, x, tokens, ws)
     moe_grouped_down(layer, None, tokens, ws)
     moe_prefill_combine(ws, None, None, 0, None, None, None, y_out, tokens)
+
+
+class SharedExpertPrefill:
+    """The shared expert at prefill width: Fp8RowWeight gate_up (2 * inter_s, 2560) with the SwiGlu epilogue and
+    down (2560, inter_s) with the SharedScale epilogue (src/kernels/linear/linear.h:11-12), exact activations.
+    Owns the projection workspaces and the two intermediate buffers for up to `max_tokens` tokens."""
+
+    def __init__(self, gate_up, down, max_tokens):
+        from . import linear
+        assert gate_up.n == 2 * down.k and down.n == gate_up.k
+        self.gate_up, self.down = gate_up, down
+        self.work_gu = linear.linear_fp8_workspace(gate_up, max_tokens)
+        self.work_dn = linear.linear_fp8_workspace(down, max_tokens)
+        self.h = torch.empty(max_tokens, down.k, dtype=torch.bfloat16, device=gate_up.codes.device)
+        self.y = torch.empty(max_tokens, down.n, dtype=torch.float32, device=gate_up.codes.device)
+
+
+def forward_moe_prefill(w_router, shared, layer, x, ws, inj, X, logits, y_out=None):
+    """The prefill branch of Forward::moe (src/model/forward.cpp:333-353 of the reference): 513-row router
+    projection (row 512 = the shared-expert gate), moe_route, the shared expert (linear_fp8 with the SwiGlu
+    epilogue, then with SharedScale reading the shared-gate logit), grouped gate/up, grouped down, and the
+    combine that adds y_shared and writes the residual streams X += inj * y. x: bf16 [T][2560];
+    logits: fp32 scratch [T][513]."""
+    from . import linear, moe
+    T = x.shape[0]
+    assert x.dtype == torch.bfloat16 and w_router.shape[0] == L.ROUTER_ROWS and T <= shared.h.shape[0]
+    moe.router_logits(w_router, x, logits)
+    moe_route(logits, x, None, 0, None, None, T, ws, logits_stride=L.ROUTER_ROWS)
+    h, y_sh = shared.h[:T], shared.y[:T]
+    linear.linear_fp8(x, shared.gate_up, linear.swiglu(h), shared.work_gu)
+    gate = logits.view(-1)[L.ROUTER_ROWS - 1:]
+    linear.linear_fp8(h, shared.down, linear.shared_scale(y_sh, gate, L.ROUTER_ROWS), shared.work_dn)
+    moe_grouped_gate_up(layer, None, x, T, ws)
+    moe_grouped_down(layer, None, T, ws)
+    moe_prefill_combine(ws, y_sh, None, 0, None, inj, X, y_out, T)

@@ -581,3 +581,37 @@ float fbo_split_token_e4m3x2(const uint16_t* x, int64_t k, uint8_t* hi, uint8_t*
   }
   return scale;
 }
+
+// FP8-row pack rule: how a bf16 weight matrix becomes E4M3FN codes + one bf16 scale per row
+// (tools/fp8row.py:21-44 quantize_rows; host port tests/kernels/linear/linear_ref.h:72-97):
+//   scale = bf16_rne(float(double(max|row|) / 448)), a scale that rounds to zero becomes the smallest
+//   positive bf16 (word 0x0001), an all-zero row gets scale 0 and codes 0;
+//   code = e4m3_rne(clamp(float(double(x) * double(float(1 / double(scale)))), -448, 448)).
+// weight: raw bf16 bits [n][k]; scales: raw bf16 bits [n].
+void fbo_quantize_fp8_rows(const uint16_t* weight, int64_t n, int64_t k, uint8_t* codes, uint16_t* scales) {
+  for (int64_t r = 0; r < n; ++r) {
+    const uint16_t* row = weight + r * k;
+    uint8_t* out = codes + r * k;
+    float mx = 0.0f;
+    for (int64_t j = 0; j < k; ++j) mx = fmaxf(mx, fabsf(fbo_bf16_to_fp32(row[j])));
+    if (mx == 0.0f) {
+      memset(out, 0, (size_t)k);
+      scales[r] = 0;
+      continue;
+    }
+    const float raw = (float)((double)mx / 448.0);
+    uint32_t bits;
+    memcpy(&bits, &raw, 4);
+    uint16_t word = (uint16_t)((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16);
+    if (word == 0) word = 1;
+    scales[r] = word;
+    const float scale = fbo_bf16_to_fp32(word);
+    const float recip = (float)(1.0 / (double)scale);
+    for (int64_t j = 0; j < k; ++j) {
+      float v = (float)((double)fbo_bf16_to_fp32(row[j]) * (double)recip);
+      v = fminf(448.0f, fmaxf(-448.0f, v));
+      out[j] = fbo_e4m3_satfinite(v);
+    }
+  }
+}
+

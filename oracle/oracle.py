@@ -57,6 +57,8 @@ def port():
         lib.fbo_e4m3_satfinite.argtypes = [C.c_float]
         lib.fbo_quantize_token_e4m3.restype = C.c_float
         lib.fbo_quantize_token_e4m3.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
+        lib.fbo_quantize_fp8_rows.restype = None
+        lib.fbo_quantize_fp8_rows.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
         lib.fbo_split_token_e4m3x2.restype = C.c_float
         lib.fbo_split_token_e4m3x2.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
         lib.fbo_row_bytes.restype = C.c_int64
@@ -306,6 +308,17 @@ def quantize_tokens_e4m3(x_bf16):
     scales = np.empty(T, dtype=np.float32)
     for t in range(T):
         scales[t] = port().fbo_quantize_token_e4m3(_ptr(x[t]), K, _ptr(codes[t]))
+    return codes, scales
+
+
+def quantize_fp8_rows(w_bf16):
+    """The FP8-row pack rule (tools/fp8row.py:21-44 of the reference): uint16 bf16 bits [n][k] ->
+    (codes uint8 [n][k], scales uint16 bf16 bits [n])."""
+    w = np.ascontiguousarray(w_bf16, dtype=np.uint16)
+    n, k = w.shape
+    codes = np.empty((n, k), dtype=np.uint8)
+    scales = np.empty(n, dtype=np.uint16)
+    port().fbo_quantize_fp8_rows(_ptr(w), n, k, _ptr(codes), _ptr(scales))
     return codes, scales
 
 

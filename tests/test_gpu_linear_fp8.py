@@ -188,6 +188,31 @@ def test_linear_fp8_epilogues_above_decode_width(T, kind):
     compare(torch, out, ref, bf)
 
 
+def test_linear_fp8_on_a_weight_packed_by_the_reference_rule():
+    """A bf16 weight matrix packed by the reference's FP8-row rule (tools/fp8row.py quantize_rows, restated in
+    the oracle and pinned to the tool's own outputs: bf16 row scales, clamped round-to-nearest-even codes),
+    then both routes against the fp64 product over the packed values; and the packing itself loses what
+    E4M3 loses (about 3 % per element, 2.5e-2 relative L2 of the output), not more."""
+    torch = _torch()
+    from fngine_b200 import linear
+    T, N, K = 96, 512, 1024
+    wb = synth.to_bf16_bits((synth.normal(7001, N * K) * 0.02).astype(np.float32).reshape(N, K))
+    wb[3] = 0  # an all-zero row: scale 0, codes 0
+    codes, scales = O.quantize_fp8_rows(wb)
+    weight = linear.Fp8RowWeight(torch.from_numpy(codes).cuda(),
+                                 torch.from_numpy(scales.view(np.int16)).cuda().view(torch.bfloat16))
+    x = bf16_tensor(torch, synth.activations(7002, T, hidden=K))
+    out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    work = linear.linear_fp8_workspace(weight, T)
+    linear.linear_fp8(x, weight, out, work)
+    torch.cuda.synchronize()
+    ref = exact_acc(torch, x.double(), weight)
+    compare(torch, out, ref, True)
+    assert float(out[:, 3].abs().max()) == 0.0
+    dense = x.double() @ torch.from_numpy(synth.bf16_bits_to_f32(wb).astype(np.float64)).cuda().T
+    assert float((ref - dense).norm() / dense.norm()) <= 4e-2
+
+
 def test_linear_fp8_benchmark_shape():
     """bf16 [4096 x 2560] x E4M3 [9216 x 2560] with fp32 row scales -> bf16 [4096 x 9216], both routes.
     The stated bar (2e-2 relative L2 against an fp32 reference on dequantized weights and the given bf16

@@ -250,3 +250,53 @@ def test_prefill_layer_at_8192_tokens_with_zipf_routing():
               max(errs)))
     assert max(errs_dn) <= 1e-3, max(errs_dn)
     assert float(np.median(errs)) <= 1e-3 and max(errs) <= 1e-2, (float(np.median(errs)), max(errs))
+
+
+@pytest.mark.parametrize("T", [24, 200])
+def test_forward_moe_prefill_with_shared_expert(T):
+    """The whole prefill branch of Forward::moe (src/model/forward.cpp:333-353 of the reference): 513-row
+    router, moe_route, the FP8-row shared expert at prefill width (SwiGlu, then SharedScale with the shared-gate
+    logit, exact activations), the grouped GEMMs, and the combine that adds y_shared and writes the residual
+    streams. Against the CPU oracle in the prefill numerics plus an fp64 shared expert over the represented
+    weights."""
+    torch = _torch()
+    from fngine_b200 import linear, moe, prefill
+    seed, inter = 4243, 512
+    layer = moe.synth_layer(IQ3_S, IQ3_S, inter, 512, seed)
+    ws = prefill.PrefillWorkspace(max(T, 64), inter)
+    wr = torch.from_numpy(synth.router_weights(910, rows=513).view(np.int16)).cuda().view(torch.bfloat16)
+    gu_c, gu_s = synth.fp8_row_weight(33, 1280, H)
+    dn_c, dn_s = synth.fp8_row_weight(34, H, 640)
+    gu_s = gu_s * np.float32(10.0)  # gate and up values of order one, so that the shared part matters
+    shared = prefill.SharedExpertPrefill(
+        linear.Fp8RowWeight(torch.from_numpy(gu_c).cuda(), torch.from_numpy(gu_s).cuda().to(torch.bfloat16)),
+        linear.Fp8RowWeight(torch.from_numpy(dn_c).cuda(), torch.from_numpy(dn_s).cuda().to(torch.bfloat16)), T)
+    xb = synth.to_bf16_bits(synth.activations(78 + T, T))
+    xd = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    inj = torch.from_numpy(synth.normal(63, T * 4).astype(np.float32).reshape(T, 4)).cuda()
+    X0 = torch.from_numpy(synth.normal(64, T * 4 * H).astype(np.float32).reshape(T, 4, H)).cuda()
+    X = X0.clone()
+    y = torch.empty(T, H, dtype=torch.float32, device="cuda")
+    logits_d = torch.empty(T, 513, dtype=torch.float32, device="cuda")
+    prefill.forward_moe_prefill(wr, shared, layer, xd, ws, inj, X, logits_d, y)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    logits = logits_d.cpu().numpy()
+    ids, w = O.topk(np.ascontiguousarray(logits[:, :512]))
+    routed, _ = oracle_prefill(IQ3_S, IQ3_S, inter, seed, xb, ids, w)
+    widen = lambda sc: synth.bf16_bits_to_f32(synth.to_bf16_bits(sc))  # the row scales as the GPU holds them (bf16)
+    h = O.linear_fp8_a16(xb, gu_c, widen(gu_s), kind="swiglu")
+    hb = synth.to_bf16_bits(h.astype(np.float32))  # h is stored as bf16 between the two projections
+    ysh = O.linear_fp8_a16(hb, dn_c, widen(dn_s), kind="shared_scale", gate_logit=logits[:, 512])
+    h_gpu = synth.bf16_bits_to_f32(shared.h[:T].view(torch.int16).cpu().numpy().view(np.uint16))
+    assert float(np.mean(h_gpu == synth.bf16_bits_to_f32(hb))) >= 0.99
+    ysh_gpu = shared.y[:T].cpu().numpy()
+    assert max(rel_l2(ysh_gpu[t], ysh[t]) for t in range(T)) <= 1e-3
+    want = routed.astype(np.float64) + ysh
+    got = y.cpu().numpy()
+    errs = [rel_l2(got[t], want[t]) for t in range(T)]
+    assert float(np.median(errs)) <= 1e-3 and max(errs) <= 1e-2, (float(np.median(errs)), max(errs))
+    wantX = X0.cpu().numpy().astype(np.float64) + inj.cpu().numpy().astype(np.float64)[:, :, None] * got.astype(np.float64)[:, None, :]
+    assert rel_l2(X.cpu().numpy(), wantX) <= 1e-6
+    print("forward moe prefill T=%d: shared/routed norm %.2f, end to end median %.2e max %.2e" %
+          (T, float(np.linalg.norm(ysh) / np.linalg.norm(routed)), float(np.median(errs)), max(errs)))

@@ -215,6 +215,24 @@ def test_port_equals_the_reference_expert_pool(fg, fd):
         assert np.array_equal(bits(got), bits(want))
 
 
+def test_fp8_row_pack_rule_matches_the_reference_tool():
+    """The restatement of the FP8-row pack rule (scale = bf16_rne(max / 448), zero rows, clamped round-to-
+    nearest-even codes) against outputs of the reference's own tools/fp8row.py quantize_rows, committed as
+    tests/golden/fp8row_vectors.npz by tests/golden/make_fp8row_golden.py: codes and scales bit for bit."""
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "fp8row_vectors.npz"))
+    codes, scales = O.quantize_fp8_rows(g["weight"])
+    assert np.array_equal(scales, g["scales"])
+    assert np.array_equal(codes, g["codes"])
+    assert scales[2] == 0 and not codes[2].any()  # the all-zero row
+    # dequantized rows (code value x scale) stay within half an E4M3 step of the source
+    tab = O.e4m3_table().astype(np.float64)
+    w = synth.bf16_bits_to_f32(g["weight"]).astype(np.float64)
+    sc = synth.bf16_bits_to_f32(scales).astype(np.float64)[:, None]
+    live = sc[:, 0] > 0
+    err = np.abs(tab[codes] * sc - w)[live]
+    assert np.all(err <= 2.0 ** -4 * np.maximum(np.abs(w[live]), sc[live] * 2.0 ** -6) + 1e-300)
+
+
 def test_split_tokens_e4m3x2_is_lossless():
     """The two-piece activation split of the exact FP8-row route (the statement the GPU kernel is checked
     against): scale * (hi + lo) returns every bf16 value of at least 2^-9 of its row's scaled range exactly."""
