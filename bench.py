@@ -370,6 +370,95 @@ def fp8_decode_section(torch, iters=10):
     return res
 
 
+def legacy_section(torch, n_layers=4, steps=20):
+    """The reference's own GPU decode kernels (src/kernels/moe/moe_decode.cu, compiled unchanged for sm_100a
+    into oracle/_ref_gpu by oracle/build_ref_gpu.py: test infrastructure, never on the product path) beside this
+    library's, on this GPU, at the reference's native shape: 512 experts per layer with IQ3_S gate/up [640 x 2560]
+    and IQ4_NL down [2560 x 640] (2,329,600 B each), bf16 tokens, T = 1, 4, 9. Both sides run the reference's
+    four-call decode sequence (select -> hot gate/up -> hot down -> combine with the residual write) from the same
+    router logits, as CUDA-graph replays over rotating layers (4.8 GB, larger than L2). The two differ in
+    activation numerics (the reference GPU tier quantizes per 32 values with an fp32 scale, this library follows
+    the CPU tier's Q8_K / Q8_0), so their results agree to the ~1e-2 those two families have between themselves."""
+    import ctypes
+    from fngine_b200 import moe, synth
+    so = os.path.join(ROOT, "oracle", "_ref_gpu", "libfngine_ref_gpu.so")
+    if not os.path.exists(so):
+        return {"unavailable": "oracle/_ref_gpu is not built (needs the reference checkout at build time)"}
+    ref = ctypes.CDLL(so)
+    ref.refgpu_decode_workspace_bytes.restype = ctypes.c_size_t
+    ref.refgpu_layer_decode.restype = ctypes.c_int
+    ref.refgpu_layer_decode.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int,
+                                        ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    fg, fd, inter = 21, 20, 640
+    blob = synth.blob_bytes(fg, fd, inter)
+    layers = [moe.synth_layer(fg, fd, inter, EXPERTS, 8000 + l) for l in range(n_layers)]
+    routers = [torch.from_numpy(synth.router_weights(9200 + l, rows=513).view(np.int16)).cuda().view(torch.bfloat16)
+               for l in range(n_layers)]
+    ws = moe.DecodeWorkspace(layers[0])
+    rbuf = torch.zeros(ref.refgpu_decode_workspace_bytes() + 256, dtype=torch.uint8, device="cuda")
+    rbase = (rbuf.data_ptr() + 255) & ~255
+    res = {"shape": "512 experts/layer, IQ3_S gate/up [640x2560] + IQ4_NL down [2560x640], %d rotating layers" % n_layers,
+           "sequence": "select -> hot gate/up -> hot down -> combine (the reference's four decode calls), CUDA graph"}
+    for T in (1, 4, 9):
+        xs = [torch.from_numpy(synth.to_bf16_bits(synth.activations(7200 + l, T)).view(np.int16)).cuda().view(torch.bfloat16)
+              for l in range(n_layers)]
+        logits = [torch.empty(T, 513, dtype=torch.float32, device="cuda") for _ in range(n_layers)]
+        for l in range(n_layers):
+            moe.router_logits(routers[l], xs[l], logits[l])
+        zeros = torch.zeros(T, HIDDEN, dtype=torch.float32, device="cuda")
+        inj = torch.zeros(T, 4, dtype=torch.float32, device="cuda")
+        X = torch.zeros(T, 4, HIDDEN, dtype=torch.float32, device="cuda")
+        y_ours = torch.empty(T, HIDDEN, dtype=torch.float32, device="cuda")
+        y_ref = torch.empty(T, HIDDEN, dtype=torch.float32, device="cuda")
+
+        def ours(l):
+            moe.moe_select_publish(logits[l], xs[l], None, 0, None, None, T, ws)
+            moe.moe_hot_gate_up(layers[l], T, ws)
+            moe.moe_hot_down(layers[l], T, ws)
+            moe.moe_combine(ws, zeros, None, 0, None, inj, X, y_ours, T)
+
+        def theirs(l):
+            st = ref.refgpu_layer_decode(logits[l].data_ptr(), xs[l].data_ptr(), layers[l].slots.data_ptr(), blob, fg, fd, T,
+                                         rbase, zeros.data_ptr(), inj.data_ptr(), X.data_ptr(), y_ref.data_ptr(),
+                                         torch.cuda.current_stream().cuda_stream)
+            if st:
+                raise RuntimeError("reference decode kernels returned cudaError %d" % st)
+
+        ours(0)
+        theirs(0)
+        torch.cuda.synchronize()
+        diff = float((y_ours - y_ref).norm() / y_ref.norm())
+        distinct = ws.work().n_items
+        entry = {"rel_l2_between_the_two": diff, "distinct_experts_layer0": distinct}
+        for name, fn in (("this_library", ours), ("reference_kernels", theirs)):
+            for l in range(n_layers):
+                fn(l)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            st = torch.cuda.Stream()
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                with torch.cuda.graph(g, stream=st):
+                    for l in range(n_layers):
+                        fn(l)
+            torch.cuda.synchronize()
+            for _ in range(3):
+                g.replay()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            entry[name + "_us_per_layer"] = a.elapsed_time(b) / steps / n_layers * 1e3
+        res["T%d" % T] = entry
+    res["device_status"] = ws.status()
+    del layers
+    torch.cuda.empty_cache()
+    return res
+
+
 def prefill_cpu_baseline(seed, x_bits, ids, budget_s=8.0):
     """The reference's CPU prefill path (decode_rows_bf16 + gemm_bf16 per expert, h rounded to bf16) on a
     bounded sample: the first tokens of layer 0 with their real routing, experts spread over the host cores.
@@ -584,7 +673,7 @@ def run_ours(args, rank, world, local_rank):
     status = ws.status()
 
     # other batch sizes of the same layer definition, CUDA-graph replayed (launch-bound otherwise)
-    sections = set("batches,cpu,iq4nl,fp8,fp8dec,prefill".split(",")) if args.sections == "all" else \
+    sections = set("batches,cpu,iq4nl,fp8,fp8dec,prefill,legacy".split(",")) if args.sections == "all" else \
         set(x for x in args.sections.split(",") if x and x != "none")
 
     def want(name):
@@ -644,6 +733,10 @@ def run_ours(args, rank, world, local_rank):
     fp8 = fp8_gemm_section(torch) if want("fp8") else None
     fp8dec = fp8_decode_section(torch) if want("fp8dec") else None
     pre = prefill_section(torch, n_layers=args.prefill_layers) if want("prefill") else None
+    try:  # test infrastructure beside the measurement: never allowed to break it
+        legacy = legacy_section(torch, steps=args.steps) if want("legacy") else None
+    except Exception as exc:
+        legacy = {"unavailable": "%s: %s" % (type(exc).__name__, exc)}
     peak, peak_src = peaks()
     ex_ach = sum(ex_bytes) / (sum(ex_ms) * 1e-3) / 1e9
     value = step_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -682,6 +775,7 @@ def run_ours(args, rank, world, local_rank):
         "fp8_row_gemm": fp8,
         "fp8_row_decode": fp8dec,
         "prefill_stack": pre,
+        "reference_gpu_kernels_same_box": legacy,
         "parity_vs_cpu_max_rel_l2": parity,
         "device_status": status,
         "clocks": clocks,
@@ -961,7 +1055,7 @@ def main():
                     help="layers of the prefill stack section (a profiler run wants 1)")
     ap.add_argument("--sections", default="all",
                     help="extra sections beside the headline decode measurement: all | none | comma list of "
-                         "batches,cpu,iq4nl,fp8,fp8dec,prefill (a profiler run wants none)")
+                         "batches,cpu,iq4nl,fp8,fp8dec,prefill,legacy (a profiler run wants none)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

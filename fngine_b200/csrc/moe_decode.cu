@@ -628,10 +628,11 @@ struct WorkCache {
   int pair_token[kMaxPairs];
   float pair_weight[kMaxPairs];
 };
-// Called by every thread of the block after the wait on the preceding kernel; caller synchronizes.
+// Called by the 32 lanes of the producer warp (the only reader) after the wait on the preceding kernel;
+// the caller follows with __syncwarp().
 __device__ __forceinline__ void work_cache_fill(const fb_moe_decode_workspace& ws, WorkCache& c, int n_items) {
   const fb_moe_decode_work* work = ws.work;
-  for (int i = threadIdx.x; i < kMaxPairs; i += blockDim.x) {
+  for (int i = threadIdx.x & 31; i < kMaxPairs; i += 32) {
     const bool live = i < n_items;
     c.order[i] = live ? ws.sched[kSchedOrderBase + i] : 0;
     c.slot[i] = live ? work->item_slot[i] : 0;
@@ -639,7 +640,7 @@ __device__ __forceinline__ void work_cache_fill(const fb_moe_decode_workspace& w
     c.pair_token[i] = work->pair_token[i];
     c.pair_weight[i] = work->pair_weight[i];
   }
-  if (threadIdx.x == 0) c.pair_begin[kMaxPairs] = n_items == kMaxPairs ? work->item_pair_begin[kMaxPairs] : 0;
+  if ((threadIdx.x & 31) == 0) c.pair_begin[kMaxPairs] = n_items == kMaxPairs ? work->item_pair_begin[kMaxPairs] : 0;
 }
 
 struct Ring {
@@ -910,11 +911,11 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   const int tpi = I / C::kJ;
   const int n_tiles = n_items * tpi;
   const int down_act = act_of(L.down_format);
-  work_cache_fill(ws, s_work, n_items);
-  __syncthreads();
 
   if (warp == kW) {
     // ---------------- producer: one lane draws tiles and issues their bulk copies into the ring.
+    work_cache_fill(ws, s_work, n_items);
+    __syncwarp();
     if (lane == 0) {
       producer_loop(ring, ws, s_work, ws.sched + kSchedGateUp, n_tiles, tpi, C::kJ,
                     [&](int s, int slot_id, int sub, int pair0, int ntp) {
@@ -1032,10 +1033,10 @@ down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   const int n_items = min(max(work->n_items, 0), kMaxPairs);
   constexpr int tpi = H / C::kRows;
   const int n_tiles = n_items * tpi;
-  work_cache_fill(ws, s_work, n_items);
-  __syncthreads();
 
   if (warp == kW) {
+    work_cache_fill(ws, s_work, n_items);
+    __syncwarp();
     if (lane == 0) {
       producer_loop(ring, ws, s_work, ws.sched + kSchedDown, n_tiles, tpi, C::kRows,
                     [&](int s, int slot_id, int sub, int pair0, int ntp) {

@@ -333,12 +333,12 @@ experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phas
   const int gu_tpi = I / C::kGuRows;
   const int n_gu = (phases & kPhaseGateUp) ? n_items * gu_tpi : 0;
   const int n_dn = (phases & kPhaseDown) ? n_items * C::kDnTilesPerItem : 0;
-  work_cache_fill(ws, s_work, n_items);
-  __syncthreads();
 
   if (warp == C::kWarps) {
     // ---------------- producer: one lane draws tiles (two steps ahead of their use) and issues their
     // bulk copies into the ring; every pass of kTT tokens of a tile is one ring entry.
+    work_cache_fill(ws, s_work, n_items);
+    __syncwarp();
     if (lane != 0) return;
     int* counter = ws.sched + ((phases & kPhaseGateUp) ? kSchedGateUp : kSchedDown);
     const int n_tiles = n_gu + n_dn;
