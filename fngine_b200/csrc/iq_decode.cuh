@@ -34,12 +34,10 @@ __device__ __forceinline__ uint32_t iq3s_grid_entry(int i) {
 
 // Called by every thread of the block; caller synchronizes afterwards.
 __device__ __forceinline__ void iq3s_tables_fill(uint32_t* gridrep, uint32_t* signtab) {
-  for (int i = threadIdx.x; i < 512; i += blockDim.x) {
-    const uint32_t w = iq3s_grid_entry(i);
-    uint4 v = make_uint4(w, w, w, w);
-    uint4* dst = reinterpret_cast<uint4*>(gridrep + i * 32);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dst[j] = v;
+  // consecutive threads write consecutive 16-byte pieces (eight per entry): no bank conflicts
+  for (int i = threadIdx.x; i < 512 * 8; i += blockDim.x) {
+    const uint32_t w = iq3s_grid_entry(i >> 3);
+    reinterpret_cast<uint4*>(gridrep)[i] = make_uint4(w, w, w, w);
   }
   if (threadIdx.x < 16) {
     uint32_t m = 0;
@@ -412,5 +410,75 @@ __device__ __forceinline__ void warp_topk10(LoadF load_logit, int* ids, float* w
   topk_softmax(vals, weights);
 }
 
+// The same selection as a short dependent chain (a decode step runs it in every CTA). The tenth largest
+// of the 32 lanes' own maxima is a lower bound of the tenth largest logit (ten different logits reach it),
+// so only logits at or above it can win; they are compacted into `scratch` (32 entries of this warp, shared
+// memory), one per lane, every lane ranks its candidate against the others through shuffles (larger key,
+// then lower id: a strict order), and ranks 0..9 are the winners. More than 32 survivors (many equal
+// logits) take the general path. Same winners, same order, same weights as warp_topk10; out_ids / out_w
+// (ten entries each, shared memory) are complete after the caller's next barrier.
+template <class LoadF>
+__device__ __forceinline__ void warp_topk10_pruned(LoadF load_logit, uint2* scratch, int* out_ids, float* out_w) {
+  const int lane = threadIdx.x & 31;
+  uint32_t key[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) key[i] = logit_key(load_logit(lane + 32 * i));
+  uint32_t lm = key[0];
+#pragma unroll
+  for (int i = 1; i < 16; ++i) lm = max(lm, key[i]);
+  int above = 0;  // lanes whose maximum is larger than this lane's
+#pragma unroll
+  for (int j = 0; j < 32; ++j) above += __shfl_sync(0xffffffffu, lm, j) > lm ? 1 : 0;
+  const uint32_t thr = __reduce_min_sync(0xffffffffu, above < FB_TOPK ? lm : 0xffffffffu);
+  int total = 0;
+  const uint32_t below = (1u << lane) - 1u;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const bool in = key[i] >= thr;
+    const uint32_t m = __ballot_sync(0xffffffffu, in);
+    const int pos = total + __popc(m & below);
+    if (in && pos < 32) scratch[pos] = make_uint2(key[i], uint32_t(lane + 32 * i));
+    total += __popc(m);
+  }
+  if (total > 32) {
+    int ids[FB_TOPK];
+    float w[FB_TOPK];
+    warp_topk10(load_logit, ids, w);
+#pragma unroll
+    for (int k = 0; k < FB_TOPK; ++k)
+      if (lane == k) {
+        out_ids[k] = ids[k];
+        out_w[k] = w[k];
+      }
+    return;
+  }
+  __syncwarp();
+  uint32_t ck = 0u, cid = 0xffffffffu;  // padding lanes lose to every candidate
+  if (lane < total) {
+    const uint2 c = scratch[lane];
+    ck = c.x;
+    cid = c.y;
+  }
+  int rank = 0;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const uint32_t ok = __shfl_sync(0xffffffffu, ck, j), oi = __shfl_sync(0xffffffffu, cid, j);
+    rank += (ok > ck || (ok == ck && oi < cid)) ? 1 : 0;
+  }
+  __syncwarp();  // every lane holds its candidate: the scratch entries can carry the winners' logits now
+  float* vals = reinterpret_cast<float*>(scratch);
+  if (rank < FB_TOPK) {
+    out_ids[rank] = int(cid);
+    vals[rank] = key_logit(ck);
+  }
+  __syncwarp();
+  // softmax over the winners exactly as topk_softmax: exp(v - top), summed in rank order. Lane k computes
+  // the k-th term; the ten terms then reach every lane through shuffles and are added in the same order.
+  const float e = expf(vals[lane < FB_TOPK ? lane : 0] - vals[0]);
+  float sum = 0.0f;
+#pragma unroll
+  for (int k = 0; k < FB_TOPK; ++k) sum += __shfl_sync(0xffffffffu, e, k);
+  if (lane < FB_TOPK) out_w[lane] = e * __fdiv_rn(1.0f, sum);
+}
 
 }  // namespace fb

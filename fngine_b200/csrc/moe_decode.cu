@@ -27,8 +27,7 @@ constexpr int kExperts = FB_EXPERTS;
 constexpr int kMaxTok = FB_DECODE_MAX_TOKENS;
 constexpr int kMaxPairs = FB_DECODE_MAX_PAIRS;
 constexpr int kTT = 2;  // tokens of one work item handled per pass over a staged tile
-// ws.sched: [0] gate/up tile counter, [1] down tile counter, [2] finished route row groups,
-// [8..168) item order, [192..208) finished slices per route row group
+// ws.sched: [0] gate/up tile counter, [1] down tile counter, [8..168) item order
 constexpr int kSchedOrderBase = 8;
 constexpr int kEpMaxRanks = FB_EP_MAX_RANKS;
 constexpr uint32_t kPeerSpinLimit = 1u << 20;  // default polls of a peer-written flag before giving up (about a second)
@@ -58,8 +57,6 @@ __device__ __forceinline__ float2 ll_read(const uint4* line, uint32_t step, uint
   atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
   return make_float2(0.0f, 0.0f);
 }
-constexpr int kSchedRoute = 2;
-constexpr int kSchedGroup = 192;  // 32 row-group tickets of route_kernel
 constexpr int kSchedInts = 256;
 
 __host__ __device__ constexpr int act_row_bytes_planar(int act, int k) {
@@ -184,155 +181,192 @@ __global__ void __launch_bounds__(128) router_kernel(const __nv_bfloat16* __rest
   }
 }
 
+// The part of the work list a producer needs, in shared memory: the producer is a single thread, and a
+// chain of dependent global loads per tile (visiting order -> item -> its pairs -> their tokens and
+// weights, about two microseconds) would pace the whole kernel. Either copied from the device work list
+// (work_cache_fill) or built in place by the CTA's own selection (select_block).
+struct WorkCache {
+  int order[kMaxPairs];
+  int pair_begin[kMaxPairs + 1];
+  int slot[kMaxPairs];
+  int pair_token[kMaxPairs];
+  float pair_weight[kMaxPairs];
+  int n_items;
+};
+// Called by the 32 lanes of the producer warp (the only reader) after the wait on the preceding kernel;
+// the caller follows with __syncwarp().
+__device__ __forceinline__ void work_cache_fill(const fb_moe_decode_workspace& ws, WorkCache& c, int n_items) {
+  const fb_moe_decode_work* work = ws.work;
+  for (int i = threadIdx.x & 31; i < kMaxPairs; i += 32) {
+    const bool live = i < n_items;
+    c.order[i] = live ? ws.sched[kSchedOrderBase + i] : 0;
+    c.slot[i] = live ? work->item_slot[i] : 0;
+    c.pair_begin[i] = i <= n_items ? work->item_pair_begin[i] : 0;
+    c.pair_token[i] = work->pair_token[i];
+    c.pair_weight[i] = work->pair_weight[i];
+  }
+  if ((threadIdx.x & 31) == 0) {
+    c.pair_begin[kMaxPairs] = n_items == kMaxPairs ? work->item_pair_begin[kMaxPairs] : 0;
+    c.n_items = n_items;
+  }
+}
+
 // ------------------------------------------------------------------------------ select
-// topk(t, ids, weights): the calling warp's top-10 of token t (ids and softmax weights, rank order).
-template <class TopkF>
+// topk(t, scratch, ids, weights): the calling warp writes token t's top-10 (ids and softmax weights, rank
+// order) to ids / weights in shared memory; scratch = 32 entries of shared memory for that warp.
+// Called by every thread of a block of 512 or more threads. The work list goes to `wc` in shared memory
+// (complete when the call returns) and, with `publish`, to the device work list as well; `reset` clears
+// the tile and item counters of the streaming kernels (only where no such kernel can be running). The
+// list is a function of the logits alone: every block that runs this on the same logits builds the same
+// list. Every CTA of a decode step waits for this, so it is kept a short chain of five barriers:
+// token masks per physical slot (shared-memory atomics), a scan over the 512 slots (thread = slot), the
+// pairs placed from the scan, and the items ranked by comparing each with all the others (SPLIT threads
+// per item, 16-byte loads).
+//   items  = distinct selected experts held on this rank, in physical-slot order
+//   pairs  = (item, token), tokens ascending inside an item
+//   order  = items by token count, most first, ties by item index (the streaming kernels' visiting order)
+template <int SPLIT, class TopkF>
 __device__ __forceinline__ void select_block(TopkF topk, const int32_t* slot_of, int T,
-                                             const fb_moe_decode_workspace& ws, uint32_t* counts,
-                                             bool remote_ok = false) {
+                                             const fb_moe_decode_workspace& ws, uint32_t* counts, bool remote_ok,
+                                             bool publish, bool reset, WorkCache& wc) {
+  static_assert(SPLIT == 2 || SPLIT == 4, "threads per item: adjacent lanes of one warp");
+  static_assert(kMaxPairs % (4 * SPLIT) == 0, "each thread ranks against whole 16-byte groups of items");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   __shared__ int s_id[kMaxTok][kTopK];
   __shared__ float s_w[kMaxTok][kTopK];
   __shared__ int s_pair[kMaxTok][kTopK];
-  __shared__ uint32_t s_mask[kExperts];
-  __shared__ int s_begin[kExperts];
-  __shared__ int s_hot_slot[kMaxPairs];
-  __shared__ int s_hot_cnt[kMaxPairs];
-  __shared__ int s_item_cnt[kMaxPairs];
-  __shared__ int s_scan[2][16];
-  __shared__ int s_hist[5][kMaxTok + 1];
+  __shared__ uint32_t s_tok[kExperts];  // physical slot -> mask of the tokens that chose it
+  __shared__ int s_begin[kExperts];     // physical slot -> first pair of its item
+  __shared__ int s_scan[2][kExperts / 32];
+  __shared__ __align__(16) int s_item_cnt[kMaxPairs];
+  __shared__ uint2 s_cand[kMaxTok][32];
   fb_moe_decode_work* work = ws.work;
-  s_mask[tid] = 0;
-  if (tid < 5 * (kMaxTok + 1)) (&s_hist[0][0])[tid] = 0;
-  if (tid < kMaxPairs) ws.item_done[tid] = 0;
-  if (tid < kSchedOrderBase) ws.sched[tid] = 0;
-  const int e_slot = slot_of ? slot_of[tid] : tid;
-  if (warp < T) {
-    int ids[kTopK];
-    float w[kTopK];
-    topk(warp, ids, w);
-#pragma unroll
-    for (int k = 0; k < kTopK; ++k)
-      if (lane == k) {
-        s_id[warp][k] = ids[k];
-        s_w[warp][k] = w[k];
-      }
+  if (tid < kExperts) s_tok[tid] = 0;
+  if (reset) {
+    if (tid < kMaxPairs) ws.item_done[tid] = 0;
+    if (tid < kSchedOrderBase) ws.sched[tid] = 0;
   }
+  if (warp < T) topk(warp, s_cand[warp], s_id[warp], s_w[warp]);
   __syncthreads();
-  const int pt = tid / kTopK, pk = tid % kTopK;
-  const bool valid = tid < T * kTopK;
+  const int np = T * kTopK;
+  const bool valid = tid < np;
+  const int pt = tid / kTopK, pk = tid - pt * kTopK;
   int my_e = 0, my_slot = -1;
   if (valid) {
     my_e = s_id[pt][pk];
     my_slot = slot_of ? slot_of[my_e] : my_e;
-    if (my_slot >= 0) atomicOr(&s_mask[my_e], 1u << pt);
+    if (my_slot >= kExperts) my_slot = -1;
+    if (my_slot >= 0) atomicOr(&s_tok[my_slot], 1u << pt);
     if (counts) atomicAdd(&counts[my_e], 1u);
   }
-  const int n_cold = __syncthreads_count(valid && my_slot < 0);
-  // Exclusive scans of (pairs, hot flag) over the 512 experts.
-  const uint32_t mask = s_mask[tid];
-  const int c = __popc(mask);
+  __syncthreads();
+  // inclusive scans of (tokens, chosen flag) over the 512 slots: inside the warps first
+  const int c = tid < kExperts ? __popc(s_tok[tid]) : 0;
   int incl_c = c, incl_n = c > 0 ? 1 : 0;
+  if (tid < kExperts) {  // (whole warps)
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int a = __shfl_up_sync(0xffffffffu, incl_c, o), b = __shfl_up_sync(0xffffffffu, incl_n, o);
-    if (lane >= o) {
-      incl_c += a;
-      incl_n += b;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int x = __shfl_up_sync(0xffffffffu, incl_c, o), y = __shfl_up_sync(0xffffffffu, incl_n, o);
+      if (lane >= o) {
+        incl_c += x;
+        incl_n += y;
+      }
     }
-  }
-  if (lane == 31) {
-    s_scan[0][warp] = incl_c;
-    s_scan[1][warp] = incl_n;
+    if (lane == 31) {
+      s_scan[0][warp] = incl_c;
+      s_scan[1][warp] = incl_n;
+    }
   }
   __syncthreads();
   int base_c = 0, base_n = 0, n_pairs = 0, n_items = 0;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
+  for (int i = 0; i < kExperts / 32; ++i) {
     const int sc = s_scan[0][i], sn = s_scan[1][i];
-    if (i < warp) {
-      base_c += sc;
-      base_n += sn;
-    }
+    base_c += i < warp ? sc : 0;
+    base_n += i < warp ? sn : 0;
     n_pairs += sc;
     n_items += sn;
   }
-  int item = base_n + incl_n - (c > 0 ? 1 : 0);  // expert order == slot order when slot_of is null
-  int pair_begin = base_c + incl_c - c;
-  if (slot_of) {  // rank the hot experts by physical slot instead
-    if (c > 0) {
-      s_hot_slot[item] = e_slot;
-      s_hot_cnt[item] = c;
-    }
-    __syncthreads();
-    if (c > 0) {
-      int it = 0, pb = 0;
-#pragma unroll 8
-      for (int i = 0; i < n_items; ++i) {
-        const bool before = s_hot_slot[i] < e_slot;
-        it += before ? 1 : 0;
-        pb += before ? s_hot_cnt[i] : 0;
-      }
-      item = it;
-      pair_begin = pb;
-    }
-  }
-  if (c > 0) {
+  if (c > 0) {  // thread = a chosen slot = an item
+    const int item = base_n + incl_n - 1, pair_begin = base_c + incl_c - c;
     s_begin[tid] = pair_begin;
     s_item_cnt[item] = c;
-    work->item_slot[item] = e_slot;
-    work->item_pair_begin[item] = pair_begin;
-  }
-  if (tid == 0) {
-    work->item_pair_begin[n_items] = n_pairs;
-    work->n_items = n_items;
-    work->n_pairs = n_pairs;
-    work->n_cold = n_cold;
-    work->tokens = T;
-    if (n_cold && !remote_ok) atomicMax(ws.status, uint32_t(FB_STATUS_BAD_WORK));
-  }
-  __syncthreads();
-  // Visiting order of the streaming kernels: most tokens first, ties by item index. Counting
-  // sort: rank = items with more tokens + items with as many tokens and a lower index.
-  {
-    const bool live = tid < n_items;
-    const int mine = live ? s_item_cnt[tid] : 0;
-    const unsigned peers = __match_any_sync(0xffffffffu, mine);
-    const int before_in_warp = __popc(peers & ((1u << lane) - 1u));
-    if (live && before_in_warp == 0) s_hist[warp][mine] = __popc(peers);  // one lane per (warp, count)
-    __syncthreads();
-    if (live) {
-      int rank = before_in_warp;
-      for (int wv = 0; wv < (n_items + 31) / 32; ++wv)
-        for (int cnt = mine; cnt <= kMaxTok; ++cnt)
-          if (cnt > mine || wv < warp) rank += s_hist[wv][cnt];
-      ws.sched[kSchedOrderBase + rank] = tid;
+    wc.slot[item] = tid;
+    wc.pair_begin[item] = pair_begin;
+    if (publish) {
+      work->item_slot[item] = tid;
+      work->item_pair_begin[item] = pair_begin;
     }
   }
+  if (tid == 0) {
+    wc.pair_begin[n_items] = n_pairs;
+    wc.n_items = n_items;
+    if (publish) {
+      work->item_pair_begin[n_items] = n_pairs;
+      work->n_items = n_items;
+      work->n_pairs = n_pairs;
+      work->n_cold = np - n_pairs;
+      work->tokens = T;
+      if (np - n_pairs && !remote_ok) atomicMax(ws.status, uint32_t(FB_STATUS_BAD_WORK));
+    }
+  }
+  __syncthreads();
   if (valid) {
     int idx = -1;
     if (my_slot >= 0) {
-      idx = s_begin[my_e] + __popc(s_mask[my_e] & ((1u << pt) - 1u));  // tokens ascending inside an item
-      work->pair_token[idx] = pt;
-      work->pair_weight[idx] = s_w[pt][pk];
+      idx = s_begin[my_slot] + __popc(s_tok[my_slot] & ((1u << pt) - 1u));  // tokens ascending inside an item
+      wc.pair_token[idx] = pt;
+      wc.pair_weight[idx] = s_w[pt][pk];
+      if (publish) {
+        work->pair_token[idx] = pt;
+        work->pair_weight[idx] = s_w[pt][pk];
+      }
     }
     s_pair[pt][pk] = idx;
-    work->topk_expert[pt][pk] = my_e;
-    work->topk_weight[pt][pk] = s_w[pt][pk];
+    if (publish) {
+      work->topk_expert[pt][pk] = my_e;
+      work->topk_weight[pt][pk] = s_w[pt][pk];
+    }
+  }
+  {  // rank of item p = items with more tokens + items with as many tokens and a lower index
+    constexpr int kShare = kMaxPairs / SPLIT;  // items a thread compares its item with
+    const int p = tid / SPLIT, sub = tid - p * SPLIT;
+    const bool live = p < n_items;
+    const int mine = live ? s_item_cnt[p] : 0;
+    int rank = 0;
+    if (live) {
+#pragma unroll
+      for (int g = 0; g < kShare / 4; ++g) {
+        const int j0 = sub * kShare + 4 * g;
+        if (j0 < n_items) {
+          const int4 v = *reinterpret_cast<const int4*>(&s_item_cnt[j0]);
+          const int cj[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            rank += (j0 + i < n_items && (cj[i] > mine || (cj[i] == mine && j0 + i < p))) ? 1 : 0;
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 1; o < SPLIT; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);  // (whole warps)
+    if (live && sub == 0) {
+      wc.order[rank] = p;
+      if (publish) ws.sched[kSchedOrderBase + rank] = p;
+    }
   }
   __syncthreads();
-  if (tid < T) {
-    int idx[kTopK];
+  if (publish && tid < T) {
+    int idx10[kTopK];
 #pragma unroll
-    for (int k = 0; k < kTopK; ++k) idx[k] = s_pair[tid][k];
+    for (int k = 0; k < kTopK; ++k) idx10[k] = s_pair[tid][k];
     int nh = 0;
 #pragma unroll
     for (int k = 0; k < kTopK; ++k) {
-      if (idx[k] >= 0) {
+      if (idx10[k] >= 0) {
         int rank = 0;
 #pragma unroll
-        for (int k2 = 0; k2 < kTopK; ++k2) rank += (idx[k2] >= 0 && idx[k2] < idx[k]) ? 1 : 0;
-        work->token_pairs[tid][rank] = idx[k];  // slot order == pair order
+        for (int k2 = 0; k2 < kTopK; ++k2) rank += (idx10[k2] >= 0 && idx10[k2] < idx10[k]) ? 1 : 0;
+        work->token_pairs[tid][rank] = idx10[k];  // slot order == pair order
         ++nh;
       }
     }
@@ -340,6 +374,17 @@ __device__ __forceinline__ void select_block(TopkF topk, const int32_t* slot_of,
     work->token_cold_count[tid] = kTopK - nh;
   }
 }
+
+// What a streaming kernel needs to run the selection itself (the fused layer call): every CTA builds the
+// work list in its own shared memory from the logits the route kernel stored, and block 0 also writes the
+// device work list for the combine kernel and the host.
+struct SelectArgs {
+  const float* logits;  // [tokens][stride]
+  int stride;
+  const int32_t* slot_of;
+  int tokens;
+  int remote_ok;
+};
 
 // Stand-alone selection (the reference's moe_select_publish): block 0 routes, blocks 1..T quantize
 // one token's activations each.
@@ -361,11 +406,12 @@ __global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ l
         quantize_row_planar(act, H, load, ws.xq + xq_offset(act) + size_t(t) * FB_XQ_STRIDE);
     return;
   }
-  select_block(
-      [&](int t, int* ids, float* wts) {
-        warp_topk10([&](int e) { return logits[size_t(t) * logits_stride + e]; }, ids, wts);
+  __shared__ WorkCache s_work;  // the streaming kernels of this path read the device work list instead
+  select_block<2>(
+      [&](int t, uint2* scratch, int* ids, float* wts) {
+        warp_topk10_pruned([&](int e) { return logits[size_t(t) * logits_stride + e]; }, scratch, ids, wts);
       },
-      slot_of, T, ws, counts);
+      slot_of, T, ws, counts, false, true, true, s_work);
 }
 
 // What route_kernel needs for an expert-parallel step with peer-memory exchange (n_ranks == 0: none).
@@ -379,26 +425,25 @@ struct EpRouteArgs {
   int act;              // activation format the layer's gate/up weights pair with (set for every launch)
 };
 
-// Router projection, activation quantization and selection in one launch (the head of the fused
-// layer call). Block (g, q) projects router rows 32g..32g+31 over the K slice [320q, 320q+320): the
-// x slice of all tokens sits in shared memory, one warp per row pair (every x value read from
-// shared memory feeds two rows), all tokens in flight at once; partial sums go to `part`
-// [8][16][512]. 128 blocks: one per SM, no second wave. Every block also quantizes a share of the
-// activation blocks. Hand-offs use device tickets, nobody waits: the block that finishes last in its
-// row group adds the group's eight slices in order 0..7 (fixed: repeated calls are bitwise
-// identical), stores the logits and, per token, the ten best of its 32 experts; the row group that
-// finishes last merges the sixteen candidate lists of each token (the global top-10 is among them)
-// and runs the selection.
+// Router projection and activation quantization in one launch (the head of the fused layer call; the
+// selection runs inside the streaming kernel that follows, see SelectArgs). 128 blocks in sixteen
+// clusters of eight: cluster g owns router rows 32g..32g+31, its CTA q the K slice [320q, 320q+320). The
+// x slice of all tokens sits in the CTA's shared memory (sixteen CTAs read each slice: no line of x is
+// wanted by all SMs at once), one warp per row pair (every x value read from shared memory feeds two
+// rows), all tokens in flight at once. The eight slice sums of a logit meet through distributed shared
+// memory: after a cluster barrier CTA q adds the slices of rows 4q..4q+3 in order 0..7 (fixed: repeated
+// calls are bitwise identical) and stores the logits. No block waits on device memory for another. Every
+// warp of the grid also quantizes a share of the activation blocks, and block 0 clears the counters of
+// the streaming kernels (none can be running: this kernel waited for its predecessor).
 constexpr int kRouteSplits = 8, kRouteSlice = H / kRouteSplits;  // 320
 constexpr int kRouteGroups = kExperts / 32;                      // 16
+constexpr int kRouteBlocks = kRouteGroups * kRouteSplits;
 static_assert(kRouteSlice == 320, "lane layout below: two 128-element chunks and a 64-element tail");
 
 template <bool XBF16, bool EP>
 __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restrict__ w, const void* __restrict__ xv,
                                                     int T, float* __restrict__ logits, int stride,
-                                                    float* __restrict__ part, fb_moe_decode_workspace ws,
-                                                    const int32_t* __restrict__ slot_of, bool remote_ok,
-                                                    EpRouteArgs ep) {
+                                                    fb_moe_decode_workspace ws, EpRouteArgs ep) {
   pdl_launch_dependents();
   pdl_wait_prior();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -421,11 +466,13 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
     }
     x_lines = static_cast<const uint4*>(ep.peers.x_all[ep.peers.rank]) + size_t(ep.parity) * kMaxTok * (H / 2);
   }
-  // x slice [token][320]; later the logits [token][expert]
-  __shared__ __align__(16) float s_buf[kMaxTok * kExperts];
-  __shared__ int s_last;
-  float(*s_x)[kRouteSlice] = reinterpret_cast<float(*)[kRouteSlice]>(s_buf);
-  const int g = blockIdx.x / kRouteSplits, q = blockIdx.x - g * kRouteSplits;
+  if (blockIdx.x == 0) {
+    if (tid < kMaxPairs) ws.item_done[tid] = 0;
+    if (tid < kSchedOrderBase) ws.sched[tid] = 0;
+  }
+  __shared__ __align__(16) float s_x[kMaxTok][kRouteSlice];  // x slice [token][320]
+  __shared__ float s_part[32][kMaxTok];                       // this slice's sums [row of the group][token]
+  const int g = blockIdx.x / kRouteSplits, q = int(cluster_cta_rank());  // (clusters are eight consecutive blocks)
   for (int i = tid; i < T * (kRouteSlice / 4); i += 512) {
     const int t = i / (kRouteSlice / 4), c = i - t * (kRouteSlice / 4);
     float4 v;
@@ -500,15 +547,25 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
         acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
       }
     }
-    const int t = lane & 15;
-    if (t < T) part[(size_t(q) * kMaxTok + t) * kExperts + row0 + (lane >> 4)] = acc[0];
+    s_part[2 * warp + (lane >> 4)][lane & 15] = acc[0];
   }
-  // activation quantization, one warp per ggml block, strided over every warp of the grid
+  cluster_sync();
+  if (tid < 4 * kMaxTok) {
+    const int r = 4 * q + (tid >> 4), t = tid & 15;
+    if (t < T) {
+      float v = 0.0f;
+#pragma unroll
+      for (int qq = 0; qq < kRouteSplits; ++qq) v += ld_cluster_f32(&s_part[r][t], uint32_t(qq));
+      logits[size_t(t) * stride + g * 32 + r] = v;
+    }
+  }
+  // activation quantization, one warp per ggml block, strided over every warp of the grid (spread over
+  // the blocks first: a single token's ten blocks go to ten different SMs)
   {
     const int act = ep.act;
     const int per_tok = act == FB_ACT_Q8_K ? H / 256 : H / 32;
     const int n_warps = gridDim.x * 16;
-    for (int task = blockIdx.x * 16 + warp; task < T * per_tok; task += n_warps) {
+    for (int task = warp * gridDim.x + blockIdx.x; task < T * per_tok; task += n_warps) {
       const int t = task / per_tok, b = task - t * per_tok;
       auto load = [&](int i) -> float {
         if constexpr (XBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(xv)[size_t(t) * H + i]);
@@ -518,7 +575,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
       float* scales = reinterpret_cast<float*>(out + H);
       if (act == FB_ACT_Q8_K) {
         float v[8];
-        if constexpr (ep_mode) {
+        if constexpr (EP) {
           const uint4* ln = x_lines + (size_t(t) * H + 256 * b + 8 * lane) / 2;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -536,7 +593,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
       } else {
         unsigned short dh;
         float xv1;
-        if constexpr (ep_mode) {
+        if constexpr (EP) {
           const float2 f = ll_read(x_lines + (size_t(t) * H + 32 * b + lane) / 2, ep.step, ws.status, ep.spin_limit);
           xv1 = (lane & 1) ? f.y : f.x;
         } else {
@@ -548,52 +605,7 @@ __global__ void __launch_bounds__(512) route_kernel(const __nv_bfloat16* __restr
       }
     }
   }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int ticket = atomicAdd(ws.sched + kSchedGroup + g, 1);
-    s_last = ticket == kRouteSplits - 1;
-    if (s_last) ws.sched[kSchedGroup + g] = 0;
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  // Candidate lists of the two-level top-10 sit behind the slice sums: [token][row group][10] x {key, id}.
-  uint2* cands = reinterpret_cast<uint2*>(part + size_t(kRouteSplits) * kMaxTok * kExperts);
-  {  // warp = token, lane = row of the group
-    const int t = warp, e = g * 32 + lane;
-    if (t < T) {
-      float v = 0.0f;
-#pragma unroll
-      for (int qq = 0; qq < kRouteSplits; ++qq) v += __ldcg(part + (size_t(qq) * kMaxTok + t) * kExperts + e);
-      logits[size_t(t) * stride + e] = v;
-      uint32_t ck;
-      int ci;
-      warp_top10_of32(v, e, ck, ci);  // the group's ten best of this token, best first
-      if (lane < kTopK) cands[(size_t(t) * kRouteGroups + g) * kTopK + lane] = make_uint2(ck, uint32_t(ci));
-    }
-  }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int ticket = atomicAdd(ws.sched + kSchedRoute, 1);
-    s_last = ticket == kRouteGroups - 1;
-    if (s_last) ws.sched[kSchedRoute] = 0;
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  select_block(
-      [&](int t, int* ids, float* wts) {  // merge the sixteen row groups' candidate lists of token t
-        warp_topk10_merge(
-            [&](int c, uint32_t& k, int& id) {
-              const uint2 v = __ldcg(cands + size_t(t) * kRouteGroups * kTopK + c);
-              k = v.x;
-              id = int(v.y);
-            },
-            kRouteGroups * kTopK, ids, wts);
-      },
-      slot_of, T, ws, nullptr, remote_ok);
+  cluster_sync();  // no CTA of the cluster leaves while another may still read its slice sums
 }
 
 // ------------------------------------------------------------------------------ streaming skeleton
@@ -617,31 +629,6 @@ struct StageMeta {
   int seq;         // entry number of this CTA (the multi-stage rings check it)
   float wgt[kTT];  // routing weights of the pass's pairs (down)
 };
-
-// The part of the device work list a producer needs, copied to shared memory once per CTA: the
-// producer is a single thread, and a chain of dependent global loads per tile (visiting order ->
-// item -> its pairs -> their tokens and weights, about two microseconds) would pace the whole kernel.
-struct WorkCache {
-  int order[kMaxPairs];
-  int pair_begin[kMaxPairs + 1];
-  int slot[kMaxPairs];
-  int pair_token[kMaxPairs];
-  float pair_weight[kMaxPairs];
-};
-// Called by the 32 lanes of the producer warp (the only reader) after the wait on the preceding kernel;
-// the caller follows with __syncwarp().
-__device__ __forceinline__ void work_cache_fill(const fb_moe_decode_workspace& ws, WorkCache& c, int n_items) {
-  const fb_moe_decode_work* work = ws.work;
-  for (int i = threadIdx.x & 31; i < kMaxPairs; i += 32) {
-    const bool live = i < n_items;
-    c.order[i] = live ? ws.sched[kSchedOrderBase + i] : 0;
-    c.slot[i] = live ? work->item_slot[i] : 0;
-    c.pair_begin[i] = i <= n_items ? work->item_pair_begin[i] : 0;
-    c.pair_token[i] = work->pair_token[i];
-    c.pair_weight[i] = work->pair_weight[i];
-  }
-  if ((threadIdx.x & 31) == 0) c.pair_begin[kMaxPairs] = n_items == kMaxPairs ? work->item_pair_begin[kMaxPairs] : 0;
-}
 
 struct Ring {
   uint64_t* full;   // [2] count 1 + tx bytes
@@ -684,11 +671,11 @@ __device__ __forceinline__ void producer_loop(const Ring& r, const fb_moe_decode
     }
     return true;
   };
-  int next = atomicAdd(counter, 1);  // drawn one step ahead of its use
+  int next = int(blockIdx.x);  // a block's first tile needs no ticket; later ones are drawn one step ahead of their use
   while (true) {
     const int tile = next;
     if (tile >= n_tiles) break;
-    next = atomicAdd(counter, 1);
+    next = int(gridDim.x) + atomicAdd(counter, 1);
     const int pos = tile / tiles_per_item;
     const int item = wc.order[pos];
     const int sub = tile - pos * tiles_per_item;
@@ -878,7 +865,7 @@ __device__ __forceinline__ bool draw_task(const Ring& r, int* ticket_ctr, uint32
 // ------------------------------------------------------------------------------ gate/up kernel
 template <int FMT>
 __global__ void __launch_bounds__((GateUp<FMT>::kWarps + 1) * 32, 1)
-gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
+gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, bool select, SelectArgs sel) {
   using C = GateUp<FMT>;
   constexpr int kW = C::kWarps, kPart = C::kJ * C::kRowBytes, kUp = kPart + C::kUpPad, kStageW = kUp + kPart;
   constexpr int kStage = kStageW + kTT * C::kActBytes;
@@ -905,8 +892,17 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
   pdl_launch_dependents();
   pdl_wait_prior();
 
-  const fb_moe_decode_work* work = ws.work;
-  const int n_items = min(max(work->n_items, 0), kMaxPairs);
+  int n_items;
+  if (select) {  // the fused layer call: every CTA builds the work list itself (see SelectArgs)
+    select_block<2>(
+        [&](int t, uint2* scratch, int* ids, float* wts) {
+          warp_topk10_pruned([&](int e) { return __ldcg(sel.logits + size_t(t) * sel.stride + e); }, scratch, ids, wts);
+        },
+        sel.slot_of, sel.tokens, ws, nullptr, sel.remote_ok != 0, blockIdx.x == 0, false, s_work);
+    n_items = s_work.n_items;
+  } else {
+    n_items = min(max(ws.work->n_items, 0), kMaxPairs);
+  }
   const int I = L.inter;
   const int tpi = I / C::kJ;
   const int n_tiles = n_items * tpi;
@@ -914,8 +910,10 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
 
   if (warp == kW) {
     // ---------------- producer: one lane draws tiles and issues their bulk copies into the ring.
-    work_cache_fill(ws, s_work, n_items);
-    __syncwarp();
+    if (!select) {
+      work_cache_fill(ws, s_work, n_items);
+      __syncwarp();
+    }
     if (lane == 0) {
       producer_loop(ring, ws, s_work, ws.sched + kSchedGateUp, n_tiles, tpi, C::kJ,
                     [&](int s, int slot_id, int sub, int pair0, int ntp) {
@@ -1338,7 +1336,7 @@ int32_t fb_moe_select_publish(const float* router_logits, int32_t logits_stride,
 
 // The IQ3_S expert kernel: gate/up tiles, down tiles, or both in one launch (down needs inter 512).
 static int32_t launch_experts_iq3s(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, int phases,
-                                   void* stream, const char* what) {
+                                   void* stream, const char* what, const SelectArgs* sel = nullptr) {
   static PerDeviceOnce once;
   const cudaError_t attr = per_device_once(once, [] { return opt_in_smem(experts_iq3s_kernel, Experts3::kSmem); });
   if (attr != cudaSuccess) {
@@ -1346,18 +1344,18 @@ static int32_t launch_experts_iq3s(const fb_moe_expert_layout* layout, const fb_
     return int32_t(attr);
   }
   const cudaError_t e = launch_pdl(experts_iq3s_kernel, dim3(sm_count()), dim3((Experts3::kWarps + 1) * 32), Experts3::kSmem,
-                                   as_stream(stream), *layout, *ws, phases);
+                                   as_stream(stream), *layout, *ws, sel ? (phases | kPhaseSelect) : phases,
+                                   sel ? *sel : SelectArgs{});
   if (e != cudaSuccess) return check_launch(what);
   return 0;
 }
 
-int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
-                           void* stream) {
-  if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_gate_up: bad arguments");
-  if (!ws_fits(ws, layout, true, true))
-    return invalid("hot_gate_up: workspace was made for a different layout");
+// `sel`: the kernel runs the selection itself (the fused layer call), else it reads the device work list.
+static int32_t launch_gate_up(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, void* stream,
+                              const SelectArgs* sel) {
   const dim3 grid(sm_count());
-  if (layout->gate_up_format == FB_FMT_IQ3_S) return launch_experts_iq3s(layout, ws, kPhaseGateUp, stream, "hot_gate_up");
+  if (layout->gate_up_format == FB_FMT_IQ3_S)
+    return launch_experts_iq3s(layout, ws, kPhaseGateUp, stream, "hot_gate_up", sel);
   static PerDeviceOnce once;
   const cudaError_t attr =
       per_device_once(once, [] { return opt_in_smem(gate_up_kernel<FB_FMT_IQ4_NL>, gate_up_smem<FB_FMT_IQ4_NL>()); });
@@ -1366,20 +1364,38 @@ int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, c
     return int32_t(attr);
   }
   const cudaError_t e = launch_pdl(gate_up_kernel<FB_FMT_IQ4_NL>, grid, dim3((GateUp<FB_FMT_IQ4_NL>::kWarps + 1) * 32),
-                                   gate_up_smem<FB_FMT_IQ4_NL>(), as_stream(stream), *layout, *ws);
+                                   gate_up_smem<FB_FMT_IQ4_NL>(), as_stream(stream), *layout, *ws, sel != nullptr,
+                                   sel ? *sel : SelectArgs{});
   if (e != cudaSuccess) return check_launch("hot_gate_up");
   return 0;
 }
+
+int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
+                           void* stream) {
+  if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_gate_up: bad arguments");
+  if (!ws_fits(ws, layout, true, true))
+    return invalid("hot_gate_up: workspace was made for a different layout");
+  return launch_gate_up(layout, ws, stream, nullptr);
+}
+
+static int32_t launch_down(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, void* stream);
+
+// Both projections of every routed expert: one launch for IQ3_S experts, a gate/up and a down launch otherwise.
+static int32_t launch_experts(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, void* stream,
+                              const SelectArgs* sel) {
+  if (layout->gate_up_format == FB_FMT_IQ3_S && layout->down_format == FB_FMT_IQ3_S)
+    return launch_experts_iq3s(layout, ws, kPhaseGateUp | kPhaseDown, stream, "hot_experts", sel);
+  const int32_t st = launch_gate_up(layout, ws, stream, sel);
+  return st ? st : launch_down(layout, ws, stream);
+}
+
 
 int32_t fb_moe_hot_experts(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
                            void* stream) {
   if (!layout_ok(layout) || !ws_ok(ws) || tokens < 1 || tokens > kMaxTok) return invalid("hot_experts: bad arguments");
   if (!ws_fits(ws, layout, true, true))
     return invalid("hot_experts: workspace was made for a different layout");
-  if (layout->gate_up_format == FB_FMT_IQ3_S && layout->down_format == FB_FMT_IQ3_S)
-    return launch_experts_iq3s(layout, ws, kPhaseGateUp | kPhaseDown, stream, "hot_experts");
-  const int32_t st = fb_moe_hot_gate_up(layout, tokens, ws, stream);
-  return st ? st : fb_moe_hot_down(layout, tokens, ws, stream);
+  return launch_experts(layout, ws, stream, nullptr);
 }
 
 static int32_t launch_down(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, void* stream) {
@@ -1437,29 +1453,31 @@ static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_
   EpRouteArgs era{};
   if (ep) era = *ep;
   era.act = layout_ok(layout) ? act_of(layout->gate_up_format) : FB_ACT_Q8_K;
-  // Three launches for IQ3_S experts (four otherwise): route (router projection + activation quantization
-  // + selection), the expert kernel (gate/up and down tiles in one persistent launch; the other formats
-  // take a gate/up and a down launch), combine. The expert arithmetic is that of the separate entry points. The route kernel
-  // sums a logit as eight K slices of 320 added in slice order, where fb_router_logits sums 80
-  // values per lane and then the lanes: the two projections agree to fp32 rounding (a few ulp), not
-  // bit for bit, so a near-tie between the tenth and eleventh expert may resolve differently. Only
-  // rows 0..511 of logits_scratch are written: row 512 (the shared-expert gate) is not produced here.
+  // Three launches for IQ3_S experts (four otherwise): route (router projection + activation quantization),
+  // the expert kernel (every CTA runs the selection on the stored logits, then gate/up and down tiles in
+  // one persistent launch; the other formats take a gate/up and a down launch), combine. The expert
+  // arithmetic is that of the separate entry points. The route kernel sums a logit as eight K slices of
+  // 320 added in slice order, where fb_router_logits sums 80 values per lane and then the lanes: the two
+  // projections agree to fp32 rounding (a few ulp), not bit for bit, so a near-tie between the tenth and
+  // eleventh expert may resolve differently. Only rows 0..511 of logits_scratch are written: row 512
+  // (the shared-expert gate) is not produced here.
   if (!router_w_bf16 || !x || (!y_out && with_combine) || !logits_scratch || !layout_ok(layout) || !ws_ok(ws) ||
       tokens < 1 || tokens > kMaxTok)
     return invalid("layer_decode: bad arguments (tokens must be 1..16, logits scratch [tokens][513] required)");
   if (!ws_fits(ws, layout, true, true))
     return invalid("layer_decode: workspace was made for a different layout");
-  // the [8][16][512] slice sums borrow the head of ws->partial, which nothing reads before the down kernel
-  const dim3 grid(kRouteGroups * kRouteSplits), block(512);
+  const dim3 grid(kRouteBlocks), block(512);
   auto launch = [&](auto kernel) {
-    return launch_pdl(kernel, grid, block, 0, as_stream(stream), static_cast<const __nv_bfloat16*>(router_w_bf16), x,
-                      tokens, logits_scratch, int(FB_ROUTER_ROWS), ws->partial, *ws, slot_of, remote_ok, era);
+    return launch_pdl_cluster(kernel, grid, block, 0, as_stream(stream), unsigned(kRouteSplits),
+                              static_cast<const __nv_bfloat16*>(router_w_bf16), x, tokens, logits_scratch,
+                              int(FB_ROUTER_ROWS), *ws, era);
   };
   cudaError_t e = ep                       ? launch(route_kernel<false, true>)
                   : x_dtype == FB_DT_BF16 ? launch(route_kernel<true, false>)
                                           : launch(route_kernel<false, false>);
   if (e != cudaSuccess) return check_launch("layer_decode: route");
-  const int32_t st = fb_moe_hot_experts(layout, tokens, ws, stream);  // both projections of every routed expert
+  const SelectArgs sel{logits_scratch, int(FB_ROUTER_ROWS), slot_of, tokens, remote_ok ? 1 : 0};
+  const int32_t st = launch_experts(layout, ws, stream, &sel);  // selection + both projections of every routed expert
   if (st || !with_combine) return st;
   return fb_moe_combine(ws, nullptr, nullptr, 0, nullptr, nullptr, nullptr, y_out, tokens, 0, nullptr, 0.0f, stream);
 }
@@ -1489,7 +1507,7 @@ int32_t fb_moe_layer_decode_ep_p2p(const void* router_w_bf16, const fb_moe_exper
       tokens % peers->n_ranks || step == 0)
     return invalid("layer_decode_ep_p2p: bad arguments (tokens a multiple of the rank count, at most 16; step >= 1)");
   // the route kernel hands its blocks out to the ranks in equal shares
-  if ((kRouteGroups * kRouteSplits) % peers->n_ranks)
+  if (kRouteBlocks % peers->n_ranks)
     return invalid("layer_decode_ep_p2p: the rank count must be 1, 2, 4 or 8");
   for (int d = 0; d < peers->n_ranks; ++d)
     if (!peers->x_all[d] || !peers->y_parts[d])

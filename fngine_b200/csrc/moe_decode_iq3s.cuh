@@ -35,12 +35,10 @@ static_assert(q8k_planar_bytes(2560) % 16 == 0 && q8k_planar_bytes(512) % 16 == 
 // ------------------------------------------------------------------------------ codebook for the 2x+1 form
 // Entry i of lane l at word i*32 + l (as iq3s_tables_fill), bytes (g - 1) / 2.
 __device__ __forceinline__ void iq3s_half_tables_fill(uint32_t* gridrep, uint32_t* signtab) {
-  for (int i = threadIdx.x; i < 512; i += blockDim.x) {
-    const uint32_t w = (iq3s_grid_entry(i) >> 1) & 0x07070707u;
-    uint4 v = make_uint4(w, w, w, w);
-    uint4* dst = reinterpret_cast<uint4*>(gridrep + i * 32);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dst[j] = v;
+  // consecutive threads write consecutive 16-byte pieces (eight per entry): no bank conflicts
+  for (int i = threadIdx.x; i < 512 * 8; i += blockDim.x) {
+    const uint32_t w = (iq3s_grid_entry(i >> 3) >> 1) & 0x07070707u;
+    reinterpret_cast<uint4*>(gridrep)[i] = make_uint4(w, w, w, w);
   }
   if (threadIdx.x < 16) {
     uint32_t m = 0;
@@ -273,7 +271,9 @@ struct Experts3 {
 static_assert(Experts3::kDnTile + kTT * Experts3::kDnAct <= Experts3::kSlot, "a down tile fits a slot");
 static_assert(Experts3::kSlot % 16 == 0 && Experts3::kGuPart % 16 == 0 && Experts3::kDnTile % 16 == 0, "bulk copies");
 static_assert(H % Experts3::kDnRows == 0 && Experts3::kDnRows % 32 == 0, "down tiles");
-enum { kPhaseGateUp = 1, kPhaseDown = 2 };
+// kPhaseSelect: the CTA builds the work list itself from the router logits (SelectArgs) instead of
+// reading the device work list a selection kernel left.
+enum { kPhaseGateUp = 1, kPhaseDown = 2, kPhaseSelect = 4 };
 
 // One block (256 weights) of the lane's row against the pass's tokens: term[t] = bsum * d * d_act.
 template <bool MIS>
@@ -302,7 +302,7 @@ __device__ __forceinline__ void expert_block_terms(const uint32_t* w, const uint
 }
 
 __global__ void __launch_bounds__((Experts3::kWarps + 1) * 32, 1)
-experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phases) {
+experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phases, SelectArgs sel) {
   using C = Experts3;
   constexpr int S = C::kStages;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -327,8 +327,17 @@ experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phas
   pdl_launch_dependents();
   pdl_wait_prior();
 
-  const fb_moe_decode_work* work = ws.work;
-  const int n_items = min(max(work->n_items, 0), kMaxPairs);
+  int n_items;
+  if (phases & kPhaseSelect) {
+    select_block<4>(
+        [&](int t, uint2* scratch, int* ids, float* wts) {
+          warp_topk10_pruned([&](int e) { return __ldcg(sel.logits + size_t(t) * sel.stride + e); }, scratch, ids, wts);
+        },
+        sel.slot_of, sel.tokens, ws, nullptr, sel.remote_ok != 0, blockIdx.x == 0, false, s_work);
+    n_items = s_work.n_items;
+  } else {
+    n_items = min(max(ws.work->n_items, 0), kMaxPairs);
+  }
   const int I = L.inter;  // gate/up takes 512 or 640; the down phase is for 512 (checked on the host)
   const int gu_tpi = I / C::kGuRows;
   const int n_gu = (phases & kPhaseGateUp) ? n_items * gu_tpi : 0;
@@ -337,8 +346,10 @@ experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phas
   if (warp == C::kWarps) {
     // ---------------- producer: one lane draws tiles (two steps ahead of their use) and issues their
     // bulk copies into the ring; every pass of kTT tokens of a tile is one ring entry.
-    work_cache_fill(ws, s_work, n_items);
-    __syncwarp();
+    if (!(phases & kPhaseSelect)) {
+      work_cache_fill(ws, s_work, n_items);
+      __syncwarp();
+    }
     if (lane != 0) return;
     int* counter = ws.sched + ((phases & kPhaseGateUp) ? kSchedGateUp : kSchedDown);
     const int n_tiles = n_gu + n_dn;
@@ -362,12 +373,14 @@ experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phas
       }
       return true;
     };
-    int next = atomicAdd(counter, 1), next2 = atomicAdd(counter, 1);
+    // a block's first two tiles need no ticket; the counter hands out the tiles behind those
+    const int first_ticket = 2 * int(gridDim.x);
+    int next = int(blockIdx.x), next2 = int(blockIdx.x + gridDim.x);
     while (true) {
       const int tile = next;
       if (tile >= n_tiles) break;
       next = next2;
-      next2 = atomicAdd(counter, 1);
+      next2 = first_ticket + atomicAdd(counter, 1);
       const bool down = tile >= n_gu;
       const int tl = down ? tile - n_gu : tile;
       const int pos = down ? tl / C::kDnTilesPerItem : tl / gu_tpi;
