@@ -171,6 +171,50 @@ def workload_config(args, layers_per_step):
 EXPERTS_DRAM_TRAFFIC_RATIO = 239.30 / 234.85
 
 
+def single_expert_section(torch, layers, routers, steps):
+    """One token through ONE routed expert per layer (the single-expert case the benchmark definition opens
+    with), on the GPU: the decode layer call with a slot map that holds only the token's best expert (the
+    other nine count as experts of another rank), CUDA-graph replays over the rotating layers, so the
+    1,689,600 weight bytes of every call come from HBM. Three launches per call (route, experts, combine)."""
+    import types
+    from fngine_b200 import ep, moe, synth
+    ws = moe.DecodeWorkspace(layers[0])
+    n = len(layers)
+    xs = [torch.from_numpy(synth.activations(7300 + l, 1)).cuda() for l in range(n)]
+    y = torch.empty(1, HIDDEN, dtype=torch.float32, device="cuda")
+    shards = []
+    for l in range(n):
+        moe.moe_layer_decode(routers[l], layers[l], xs[l], ws, y)
+        torch.cuda.synchronize()
+        best = int(ws.work().topk_expert[0][0])
+        slot_of = np.full(EXPERTS, -1, dtype=np.int32)
+        slot_of[best] = best
+        shards.append(types.SimpleNamespace(layer=layers[l], slot_of=torch.from_numpy(slot_of).cuda()))
+    g = torch.cuda.CUDAGraph()
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        for l in range(n):
+            ep.layer_decode_ep(routers[l], shards[l], xs[l], ws, y)
+        with torch.cuda.graph(g, stream=st):
+            for l in range(n):
+                ep.layer_decode_ep(routers[l], shards[l], xs[l], ws, y)
+    torch.cuda.synchronize()
+    items = ws.work().n_items
+    for _ in range(3):
+        g.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / steps / n * 1e3
+    return {"us_per_call": us, "experts_per_call": items, "weight_bytes_per_call": BLOB,
+            "gbs": (BLOB + ROUTER_BYTES) / us / 1e3, "timing": "CUDA graph of %d rotating layers" % n,
+            "call": "fb_moe_layer_decode_ep with one resident expert of the token's ten", "device_status": ws.status()}
+
+
 def iq4nl_section(torch, steps, n_layers=4):
     """The IQ4_NL resident-expert variant (18-byte blocks, Q8_0 activations): the same decode layer at batch
     1 and 8, four rotating layers (4.5 GB, larger than L2), CUDA-graph replays, device time."""
@@ -707,6 +751,7 @@ def run_ours(args, rank, world, local_rank):
         by = sum(d * BLOB + ROUTER_BYTES for d in d2)
         other[str(b2)] = {"gbs": by / t / 1e6, "us_per_layer": t / Lr * 1e3, "distinct_experts_mean": sum(d2) / Lr,
                           "timing": "CUDA graph of %d layers" % Lr}
+    single = single_expert_section(torch, layers, routers, args.steps) if want("batches") else None
 
     # CPU baseline beside it: the same layer-0 step on the host cores, bounded to ~10 s
     threads = os.cpu_count() or 1
@@ -771,6 +816,7 @@ def run_ours(args, rank, world, local_rank):
                 "api": "fb_moe_layer_decode_host per layer: pinned host x in, host y out, stream wait inside"},
         "gpu_launches": args.steps * Lr * 3,
         "other_batches": other,
+        "single_expert": single,
         "iq4nl_decode": iq4,
         "fp8_row_gemm": fp8,
         "fp8_row_decode": fp8dec,
@@ -1049,7 +1095,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=16)
-    ap.add_argument("--layers", type=int, default=48,
+    ap.add_argument("--layers", type=int, default=64,
                     help="MoE layers per step, each with its own 865 MB expert set (48 = the model's depth)")
     ap.add_argument("--prefill-layers", type=int, default=48,
                     help="layers of the prefill stack section (a profiler run wants 1)")

@@ -716,7 +716,7 @@ template <>
 struct GateUp<FB_FMT_IQ4_NL> {
   static constexpr int kJ = 32, kRowBytes = 1440, kWarps = 16, kTasks = 16;
   static constexpr int kAct = FB_ACT_Q8_0, kActBytes = H + H / 8;
-  static constexpr int kPartialFloats = 0;
+  static constexpr int kPartialFloats = 2 * kTT * kJ;  // h of the entry in each of the two slots
   // The up rows sit 64 bytes after the gate rows: a row is 360 words (8 mod 32), so with both
   // parts on the same bank phase the gate and the up lanes of a warp would collide pairwise; 16
   // words apart the 32 lanes' words fall in 32 different banks.
@@ -959,6 +959,8 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, bool select, 
 #pragma unroll 2
         for (int it = 0; it < 10; ++it) iq4nl_block_dot<2>(row, q + 8 * it, odd, swap, lv, ar, H, acc);
       }
+      // the task's two rows of h wait in shared memory for the warp that finishes the entry
+      float* hrow = partials + s * (kTT * C::kJ);
 #pragma unroll
       for (int t = 0; t < kTT; ++t) {
         float v = acc[t];
@@ -966,18 +968,25 @@ gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, bool select, 
         v += __shfl_xor_sync(0xffffffffu, v, 2);
         v += __shfl_xor_sync(0xffffffffu, v, 4);
         const float up = __shfl_down_sync(0xffffffffu, v, 16);
-        if (t < ntp && q == 0 && mat == 0) ws.h[size_t(pair0 + t) * I + j0 + 2 * task + r] = silu_mul(v, up);
+        if (t < ntp && q == 0 && mat == 0) hrow[t * C::kJ + 2 * task + r] = silu_mul(v, up);
       }
-      // the warp that finishes the entry's last task hands the slot back to the producer
+      // The warp that finishes the entry's last task stores the entry's 32 rows of h (one 128-byte line per
+      // token), hands the slot back to the producer and counts the entry as one contribution to its item:
+      // one device-wide fence and one device atomic per entry instead of one per task.
+      __threadfence_block();
       __syncwarp();
       int done = 0;
       if (lane == 0) done = atomicAdd(&s_misc[2 + s], 1);
       done = __shfl_sync(0xffffffffu, done, 0);
-      if (done == C::kTasks - 1 && lane == 0) {
+      if (done != C::kTasks - 1) continue;
+      __threadfence_block();
+      for (int t = 0; t < ntp; ++t) ws.h[size_t(pair0 + t) * I + j0 + lane] = hrow[t * C::kJ + lane];
+      __syncwarp();
+      if (lane == 0) {
         s_misc[2 + s] = 0;
         mbar_arrive(&ring.empty[s]);
       }
-      item_contribution_done(ws, item, ipb, itok, tpi * C::kTasks * ((itok + kTT - 1) / kTT), down_act, I, lane);
+      item_contribution_done(ws, item, ipb, itok, tpi * ((itok + kTT - 1) / kTT), down_act, I, lane);
     }
   }
 }
