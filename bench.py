@@ -829,16 +829,19 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line))
 
 
-def ep_prefill_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_tokens=2):
+def ep_prefill_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_tokens=2, spare_slots=4):
     """The 48-layer prefill stack of bench.py's single-GPU section, expert-parallel: same seeds, same
-    router bias, experts sharded, tokens data-parallel. Returns the section dict on rank 0 (None on
-    the other ranks). Timed on the device, barrier on both sides, max over ranks."""
+    router bias, tokens data-parallel. Two placements of the experts are timed one after the other:
+    contiguous shards (expert e on rank e // (512 / N)), which also serve as the profiling pass that records
+    every layer's routing histogram, and the placement planned from that profile (fngine_b200/placement.py:
+    experts spread by load, the hottest copied into `spare_slots` extra slots per rank). The headline
+    tokens_per_s is the planned placement's. Returns the section dict on rank 0 (None on the other ranks).
+    Timed on the device, barrier on both sides, max over ranks."""
     import torch
     import torch.distributed as dist
-    from fngine_b200 import prefill, synth
+    from fngine_b200 import placement, prefill, synth
     from fngine_b200.ep_prefill import EpPrefillShard, ep_prefill_layer, topk
     FMT, INTER = 21, 512
-    shards = [EpPrefillShard(rank, world, 5000 + l, FMT, INTER) for l in range(n_layers)]
     g = torch.Generator(device="cuda").manual_seed(1234)
     routers = [(torch.randn(EXPERTS, HIDDEN, generator=g, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(n_layers)]
     bias = torch.from_numpy(synth.zipf_router_bias(1234)).cuda()
@@ -847,35 +850,75 @@ def ep_prefill_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_to
     x_local = x0[rank * tl:(rank + 1) * tl].contiguous()
     ws = prefill.PrefillWorkspace(tokens, INTER)  # a rank may receive a row of every token
     totals = {"rows_received": 0, "dispatch_bytes": 0, "combine_bytes": 0}
+    hist = torch.zeros(n_layers, EXPERTS, dtype=torch.int64, device="cuda")
+    shards = []
+    combine = "all_to_all"
 
     def step(record=False):
         x = x_local
         for l in range(n_layers):
             logits = (x @ routers[l].t()).float() + bias
-            y, st = ep_prefill_layer(logits, x, shards[l], ws)
+            if record:
+                hist[l] += torch.bincount(topk(logits)[0].reshape(-1).long(), minlength=EXPERTS)
+            y, st = ep_prefill_layer(logits, x, shards[l], ws, combine=combine)
             if record:
                 for k in totals:
                     totals[k] += st[k]
             x = (y * torch.rsqrt(y.pow(2).mean(dim=1, keepdim=True) + 1e-12)).to(torch.bfloat16)
         return x
 
+    def timed():
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            out_ = step()
+        b.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([a.elapsed_time(b) / steps], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), out_
+
+    # 1. contiguous shards: the profiling pass (routing histograms of every layer) and the first timing
+    shards = [EpPrefillShard(rank, world, 5000 + l, FMT, INTER) for l in range(n_layers)]
+    step(record=True)
+    dist.all_reduce(hist)
+    ms_contiguous, _ = timed()
+    load = hist.cpu().numpy().astype(np.float64)
+    contiguous = placement.Placement.contiguous(world)
+    plans = [placement.plan_placement(load[l], world, EXPERTS // world + spare_slots) for l in range(n_layers)]
+    balance = {"contiguous_shards": float(np.mean([contiguous.imbalance(load[l]) for l in range(n_layers)])),
+               "planned": float(np.mean([plans[l].imbalance(load[l]) for l in range(n_layers)])),
+               "planned_worst_layer": float(max(plans[l].imbalance(load[l]) for l in range(n_layers))),
+               "experts_copied_per_layer": float(np.mean([sum(len(c) > 1 for c in p.copies) for p in plans])),
+               "spare_slots_per_rank": spare_slots,
+               "what": "pairs on the busiest rank / mean over the ranks, averaged over the layers, from the routing "
+                       "histogram of the profiling pass (the timed passes route the same way)"}
+    # 2. the planned placement: what the section reports
+    del shards
+    torch.cuda.empty_cache()
+    shards = [EpPrefillShard(rank, world, 5000 + l, FMT, INTER, placement=plans[l]) for l in range(n_layers)]
+
     # layer 0 alone, for the parity check of the measured workload
     logits0 = (x_local @ routers[0].t()).float() + bias
     y_l0, _ = ep_prefill_layer(logits0, x_local, shards[0], ws)
     e0_, w0_ = topk(logits0)
-    step(record=True)
-    torch.cuda.synchronize()
-    dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(steps):
-        out = step()
-    b.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    t = torch.tensor([a.elapsed_time(b) / steps], device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    step()
+    ms_a2a, out = timed()
+    # 3. the same placement with the combine as one reduce-scatter instead of all-to-all + owner sum
+    combine = "reduce_scatter"
+    step()
+    ms_rs, out_rs = timed()
+    # (the two are compared on one layer: the stack is a random deep network without residuals, in which a
+    # last-bit difference flips a near-tie of some token's top-10 a few layers on and the outputs part)
+    y_l0_rs, _ = ep_prefill_layer(logits0, x_local, shards[0], ws, combine="reduce_scatter")
+    rs_vs_a2a = float(((y_l0_rs - y_l0).norm() / y_l0.norm()).item())
+    if ms_rs <= ms_a2a:
+        ms, out = ms_rs, out_rs
+    else:
+        ms = ms_a2a
     agg = torch.tensor([float(totals[k]) for k in ("rows_received", "dispatch_bytes", "combine_bytes")], device="cuda")
     mx = agg.clone()
     dist.all_reduce(agg)
@@ -907,6 +950,13 @@ def ep_prefill_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_to
     return {"workload": "%d layers x %d tokens, 512 IQ3_S experts/layer, top-10, Zipf(1.1) router bias; ep%d: %d experts "
                         "per GPU, %d tokens per GPU" % (n_layers, tokens, world, EXPERTS // world, tl),
             "tokens_per_s": tokens / (ms * 1e-3), "ms_per_stack": ms, "tflops": tfl, "scaling": "strong",
+            "placement": "planned from the routing profile of a first pass: experts spread over the ranks by load, "
+                         "the hottest copied (their pairs split by row number)",
+            "pair_load_max_over_mean": balance,
+            "contiguous_shards": {"ms_per_stack": ms_contiguous, "tokens_per_s": tokens / (ms_contiguous * 1e-3)},
+            "combine": {"all_to_all_plus_owner_sum_ms": ms_a2a, "reduce_scatter_ms": ms_rs,
+                        "reported": "reduce_scatter" if ms_rs <= ms_a2a else "all_to_all",
+                        "layer0_rel_l2_between_the_two": rs_vs_a2a},
             "roofline": {"bound": "tensor", "achieved": tfl / world, "peak": bf16_peak, "unit": "TFLOP/s per GPU",
                          "frac": tfl / world / bf16_peak,
                          "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)"},

@@ -397,14 +397,21 @@ __global__ void __launch_bounds__(256) pf_topk_kernel(const float* __restrict__ 
 }
 
 // Expert-parallel routing: the (expert, weight) lists arrive with the dispatched rows; entries of
-// experts other ranks own ([lo, hi) is this rank's range) become -1 and take no part.
+// experts other ranks own ([lo, hi) is this rank's range) become -1 and take no part. With a share
+// table (placement with copies) the rule is per expert instead: share[e] < 0 = not held here, else
+// (n << 8) | i = this rank holds copy i of n and takes the rows r with r % n == i.
 __global__ void __launch_bounds__(256) pf_import_kernel(const int32_t* __restrict__ in_e, const float* __restrict__ in_w,
-                                                        int lo, int hi, int n, int32_t* __restrict__ topk_e,
-                                                        float* __restrict__ topk_w, int32_t* __restrict__ count) {
+                                                        int lo, int hi, const int32_t* __restrict__ share, int n,
+                                                        int32_t* __restrict__ topk_e, float* __restrict__ topk_w,
+                                                        int32_t* __restrict__ count) {
   const int i = blockIdx.x * 256 + threadIdx.x;
   if (i >= n) return;
   const int e = in_e[i];
-  const bool local = e >= lo && e < hi;
+  bool local = e >= lo && e < hi;
+  if (share) {
+    const int sh = e >= 0 && e < kExperts ? share[e] : -1;
+    local = sh >= 0 && (i / kTopK) % max(sh >> 8, 1) == (sh & 255);
+  }
   topk_e[i] = local ? e : -1;
   topk_w[i] = in_w[i];
   if (local) atomicAdd(&count[e], 1);
@@ -1001,17 +1008,31 @@ int32_t fb_moe_topk(const float* router_logits, int32_t logits_stride, int32_t t
   return check_launch("topk");
 }
 
+static int32_t route_ep_impl(const int32_t* topk_expert, const float* topk_weight, int32_t expert_lo, int32_t expert_hi,
+                             const int32_t* share, int32_t rows, const fb_moe_prefill_workspace* ws, void* stream);
+
 int32_t fb_moe_route_ep(const int32_t* topk_expert, const float* topk_weight, int32_t expert_lo, int32_t expert_hi,
                         int32_t rows, const fb_moe_prefill_workspace* ws, void* stream) {
   if (!topk_expert || !topk_weight || expert_lo < 0 || expert_hi > kExperts || expert_lo >= expert_hi ||
       !pf_ws_ok(ws, rows))
     return invalid("route_ep: bad arguments");
+  return route_ep_impl(topk_expert, topk_weight, expert_lo, expert_hi, nullptr, rows, ws, stream);
+}
+
+int32_t fb_moe_route_placed(const int32_t* topk_expert, const float* topk_weight, const int32_t* share, int32_t rows,
+                            const fb_moe_prefill_workspace* ws, void* stream) {
+  if (!topk_expert || !topk_weight || !share || !pf_ws_ok(ws, rows)) return invalid("route_placed: bad arguments");
+  return route_ep_impl(topk_expert, topk_weight, 0, 0, share, rows, ws, stream);
+}
+
+static int32_t route_ep_impl(const int32_t* topk_expert, const float* topk_weight, int32_t expert_lo, int32_t expert_hi,
+                             const int32_t* share, int32_t rows, const fb_moe_prefill_workspace* ws, void* stream) {
   cudaStream_t s = as_stream(stream);
   cudaError_t e = cudaMemsetAsync(ws->expert_count, 0, kExperts * 4, s);
   if (e != cudaSuccess) return check_launch("route_ep: memset");
   const int n = rows * kTopK;
-  pf_import_kernel<<<(n + 255) / 256, 256, 0, s>>>(topk_expert, topk_weight, expert_lo, expert_hi, n, ws->topk_expert,
-                                                   ws->topk_weight, ws->expert_count);
+  pf_import_kernel<<<(n + 255) / 256, 256, 0, s>>>(topk_expert, topk_weight, expert_lo, expert_hi, share, n,
+                                                   ws->topk_expert, ws->topk_weight, ws->expert_count);
   pf_scan_kernel<<<1, 512, 0, s>>>(ws->expert_count, ws->expert_offset, ws->expert_cursor,
                                    static_cast<int4*>(ws->units_gate_up), static_cast<int4*>(ws->units_down), ws->meta,
                                    ws->inter, ws->max_units_gate_up, ws->max_units_down);

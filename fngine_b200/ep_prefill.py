@@ -118,9 +118,15 @@ def ep_layer_generic(x_local, topk_expert, topk_weight, rank, world, local_rows_
     return y, stats
 
 
-def ep_layer_dense(x_local, topk_expert, topk_weight, rank, world, local_rows_fn, sum_ranks_fn, group=None, chunks=1):
+def ep_layer_dense(x_local, topk_expert, topk_weight, rank, world, local_rows_fn, sum_ranks_fn, group=None, chunks=1,
+                   combine="all_to_all"):
     """Dense exchange: all-gather rows and lists, partial rows for all tokens, fixed-size all-to-all,
     rank-order sum. local_rows_fn as in ep_layer_generic; sum_ranks_fn([R][rows][H]) -> [rows][H].
+    combine = "reduce_scatter": the all-to-all and the owner's sum are one reduce-scatter of the library
+    (a rank's partial rows are already grouped by owner): a rank then receives one summed row per token
+    instead of R partial rows, and the switch may add them on the way; the order of the additions is the
+    library's (fixed for a topology, not rank order), so results agree with the all-to-all form to fp32
+    rounding, not bit for bit.
     With chunks > 1 the rank's tokens are cut into that many pieces and pipelined: the all-to-all of
     piece c runs (on the collective library's stream) while piece c+1 is gathered and computed. That
     only pays when the grouped GEMMs are bound by the tokens: they are bound by the dequantization of
@@ -160,30 +166,44 @@ def ep_layer_dense(x_local, topk_expert, topk_weight, rank, world, local_rows_fn
         x_all = x_all_b.view(x_local.dtype).reshape(n * world, x_local.shape[1])
         e_rows, w_rows = unpack_lists(l_all)
         y_part = local_rows_fn(x_all, e_rows, w_rows, rank * per, (rank + 1) * per)  # [n * R][H] fp32
-        recv = torch.empty_like(y_part)
-        work = dist.all_to_all_single(recv, y_part.contiguous(), group=group, async_op=True)
+        if combine == "reduce_scatter":
+            recv = torch.empty(n, y_part.shape[1], dtype=y_part.dtype, device=y_part.device)
+            work = dist.reduce_scatter_tensor(recv, y_part.contiguous(), group=group, async_op=True)
+        else:
+            recv = torch.empty_like(y_part)
+            work = dist.all_to_all_single(recv, y_part.contiguous(), group=group, async_op=True)
         returns.append((recv, work, n, y_part))
     outs = []
     for recv, work, n, _keep in returns:
         work.wait()
-        outs.append(sum_ranks_fn(recv.view(world, n, recv.shape[1])))
+        outs.append(recv if combine == "reduce_scatter" else sum_ranks_fn(recv.view(world, n, recv.shape[1])))
     return (outs[0] if chunks == 1 else torch.cat(outs)), stats
 
 
 # --------------------------------------------------------------------------------------------- GPU side
 class EpPrefillShard:
     """One layer's experts on this rank, with the [512] table of blob addresses by global expert id
-    (0 for experts of other ranks) the grouped kernels index."""
+    (0 for experts of other ranks) the grouped kernels index. With a placement (placement.Placement) the
+    rank holds the experts the plan gives it, copies of hot experts included, and `share` is its table
+    for fb_moe_route_placed; without one the shards are contiguous."""
 
-    def __init__(self, rank, world, seed, fmt=21, inter=512):
-        from . import ep
+    def __init__(self, rank, world, seed, fmt=21, inter=512, placement=None):
+        from . import ep, moe
         self.rank, self.world = rank, world
-        shard = ep.EpDecodeLayer(rank, world, seed, fmt, inter)  # the same bytes the single-GPU layer holds
-        self.layer = shard.layer
-        per = experts_per_rank(world)
-        stride = self.layer.layout.blob_stride
         table = np.zeros(EXPERTS, dtype=np.int64)
-        table[rank * per:(rank + 1) * per] = self.layer.slots.data_ptr() + stride * np.arange(per, dtype=np.int64)
+        if placement is None:
+            shard = ep.EpDecodeLayer(rank, world, seed, fmt, inter)  # the same bytes the single-GPU layer holds
+            self.layer = shard.layer
+            per = experts_per_rank(world)
+            stride = self.layer.layout.blob_stride
+            table[rank * per:(rank + 1) * per] = self.layer.slots.data_ptr() + stride * np.arange(per, dtype=np.int64)
+            self.share = None
+        else:
+            held = placement.rank_experts[rank]
+            self.layer = moe.synth_layer_of(fmt, fmt, inter, held, seed)
+            stride = self.layer.layout.blob_stride
+            table[np.asarray(held, dtype=np.int64)] = self.layer.slots.data_ptr() + stride * np.arange(len(held), dtype=np.int64)
+            self.share = torch.from_numpy(placement.share_table(rank)).cuda()
         self.blob_table = torch.from_numpy(table).cuda()
 
 
@@ -208,7 +228,12 @@ def local_rows(shard, ws, x_rows, e_rows, w_rows, lo, hi):
     y = torch.empty(rows, HIDDEN, dtype=torch.float32, device=x_rows.device)
     if rows == 0:
         return y
-    L.check(L.load().fb_moe_route_ep(_ptr(e_rows), _ptr(w_rows), lo, hi, rows, C.byref(ws.ws), _stream()), "moe_route_ep")
+    if getattr(shard, "share", None) is not None:  # placed shards: the share table decides, not [lo, hi)
+        L.check(L.load().fb_moe_route_placed(_ptr(e_rows), _ptr(w_rows), _ptr(shard.share), rows, C.byref(ws.ws),
+                                             _stream()), "moe_route_placed")
+    else:
+        L.check(L.load().fb_moe_route_ep(_ptr(e_rows), _ptr(w_rows), lo, hi, rows, C.byref(ws.ws), _stream()),
+                "moe_route_ep")
     prefill.moe_grouped_gate_up(shard.layer, shard.blob_table, x_rows, rows, ws)
     prefill.moe_grouped_down(shard.layer, shard.blob_table, rows, ws)
     prefill.moe_prefill_combine(ws, None, None, 0, None, None, None, y, rows)
@@ -233,10 +258,14 @@ def sum_ranks(parts):
     return y
 
 
-def ep_prefill_layer(logits_local, x_local, shard, ws, group=None, mode="dense", chunks=1):
-    """One expert-parallel prefill layer on GPUs; returns (y of this rank's tokens, stats)."""
+def ep_prefill_layer(logits_local, x_local, shard, ws, group=None, mode="dense", chunks=1, combine="all_to_all"):
+    """One expert-parallel prefill layer on GPUs; returns (y of this rank's tokens, stats). Shards built
+    from a placement need the dense exchange (their copies split pairs by row number, which must mean the
+    same row on every rank)."""
+    if getattr(shard, "share", None) is not None and mode != "dense":
+        raise ValueError("placed shards run with the dense exchange only")
     e, w = topk(logits_local)
     compute = lambda xr, er, wr, lo, hi: local_rows(shard, ws, xr, er, wr, lo, hi)  # noqa: E731
     if mode == "dense":
-        return ep_layer_dense(x_local, e, w, shard.rank, shard.world, compute, sum_ranks, group, chunks)
+        return ep_layer_dense(x_local, e, w, shard.rank, shard.world, compute, sum_ranks, group, chunks, combine)
     return ep_layer_generic(x_local, e, w, shard.rank, shard.world, compute, scatter_sum, group)

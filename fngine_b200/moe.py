@@ -67,6 +67,28 @@ def synth_layer(gate_up_format, down_format, inter, n_experts, seed, device="cud
     return ExpertLayer(buf, gate_up_format, down_format, inter)
 
 
+def synth_layer_of(gate_up_format, down_format, inter, experts, seed, device="cuda"):
+    """The same seeded bytes for an arbitrary list of experts: slot s holds expert experts[s] (a placement's
+    share of a layer). Consecutive ids are filled together."""
+    lib = L.load()
+    stride = lib.fb_moe_blob_bytes(gate_up_format, down_format, inter)
+    experts = [int(e) for e in experts]
+    buf = torch.empty(max(len(experts), 1) * stride, dtype=torch.uint8, device=device)
+    tables = {f: torch.from_numpy(synth.d_table(f).view(np.int16)).to(device) for f in {gate_up_format, down_format}}
+    gu_bytes = 2 * inter * lib.fb_moe_row_bytes(gate_up_format, L.HIDDEN)
+    nb_gu = gu_bytes // synth.BLOCK_BYTES[gate_up_format]
+    nb_dn = (stride - gu_bytes) // synth.BLOCK_BYTES[down_format]
+    s = 0
+    while s < len(experts):
+        n = 1
+        while s + n < len(experts) and experts[s + n] == experts[s] + n:
+            n += 1
+        fill_experts(buf[s * stride:], stride, gate_up_format, down_format, gu_bytes, nb_gu, nb_dn, n, experts[s], seed,
+                     tables)
+        s += n
+    return ExpertLayer(buf, gate_up_format, down_format, inter)
+
+
 def fill_experts(buf, stride, gate_up_format, down_format, gu_bytes, nb_gu, nb_dn, n_experts, first_expert, seed, tables):
     """Two launches for a whole slot array: the gate/up part and the down part of every expert."""
     lib = L.load()

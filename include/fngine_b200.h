@@ -261,6 +261,15 @@ int32_t fb_moe_route_ep(const int32_t* topk_expert, const float* topk_weight, in
                         int32_t rows, const fb_moe_prefill_workspace* ws, void* stream);
 int32_t fb_ep_scatter_sum(const float* recv, const int32_t* row_of, int32_t n_ranks, int32_t tokens, float* y,
                           void* stream);
+/* fb_moe_route_ep for a placement that is not contiguous and may hold several copies of a hot expert
+ * (the cross-GPU counterpart of the reference's routing-EMA expert placement, src/model/routing_counts.h:
+ * there the hottest experts move to the GPU, here they are spread, and the very hottest copied, so that the
+ * ranks get equal shares of the pairs). share [512]: -1 = this rank does not hold the expert; otherwise
+ * (n << 8) | i, 0 <= i < n <= 255: this rank holds copy i of n and takes the pairs of rows r with
+ * r % n == i. Rows are numbered as they are passed in, so the n copies split an expert's pairs without
+ * overlap only when every rank is given the same rows in the same order (the dense exchange). */
+int32_t fb_moe_route_placed(const int32_t* topk_expert, const float* topk_weight, const int32_t* share, int32_t rows,
+                            const fb_moe_prefill_workspace* ws, void* stream);
 /* One decode layer over this rank's experts: x holds ALL tokens of the step (after dispatch),
  * y_partial[t] = sum over token t's LOCAL experts, in slot order; pairs of other ranks are skipped
  * and counted in the work list's n_cold. */

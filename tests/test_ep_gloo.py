@@ -141,11 +141,17 @@ def _prefill_rank_main(rank, world, port, out_dir, mode):
     x, ids, w = _prefill_routing()
     lo, hi = ep.token_range(rank, world, TP)
 
+    plan = _skewed_plan(world) if mode == "placed" else None
+
     def local_rows(x_rows, e_rows, w_rows, elo, ehi):  # what route_ep + grouped kernels + combine compute
         out = np.zeros((x_rows.shape[0], H), dtype=np.float32)
         for r in range(x_rows.shape[0]):
-            pairs = sorted((int(e), float(wt)) for e, wt in zip(e_rows[r].tolist(), w_rows[r].tolist()) if elo <= e < ehi)
-            assert pairs or mode.startswith("dense"), "a row was sent to a rank that holds none of its experts"
+            if plan is not None:  # fb_moe_route_placed: the share table decides, rows numbered as they arrive
+                keep = lambda e: plan.keeps(rank, e, r)  # noqa: E731
+            else:
+                keep = lambda e: elo <= e < ehi  # noqa: E731
+            pairs = sorted((int(e), float(wt)) for e, wt in zip(e_rows[r].tolist(), w_rows[r].tolist()) if keep(int(e)))
+            assert pairs or mode != "sparse", "a row was sent to a rank that holds none of its experts"
             for e, wt in pairs:  # ascending expert id
                 out[r] += np.float32(wt) * _expert_row(e, x_rows[r].numpy().view(np.uint16))
         return torch.from_numpy(out)
@@ -160,7 +166,7 @@ def _prefill_rank_main(rank, world, port, out_dir, mode):
 
     args = (torch.from_numpy(x[lo:hi].view(np.int16).copy()), torch.from_numpy(ids[lo:hi].copy()),
             torch.from_numpy(w[lo:hi].copy()), rank, world, local_rows)
-    if mode.startswith("dense"):
+    if mode != "sparse":
         y, stats = ep_prefill.ep_layer_dense(*args, ep.combine_sum, chunks=3 if mode == "dense3" else 1)
         assert stats["rows_received"] == TP
     else:
@@ -170,7 +176,20 @@ def _prefill_rank_main(rank, world, port, out_dir, mode):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode,port", [("sparse", 29613), ("dense", 29614), ("dense3", 29615)])
+def _skewed_plan(world):
+    """A placement with copies: the load is the routing histogram of the test's tokens with three experts
+    made hot, planned with four spare slots per rank."""
+    from fngine_b200 import placement
+    _, ids, _ = _prefill_routing()
+    load = np.bincount(ids.reshape(-1), minlength=512).astype(np.float64)
+    hot = np.argsort(-load)[:3]
+    load[hot] *= 40
+    plan = placement.plan_placement(load, world, 512 // world + 4)
+    assert any(len(c) > 1 for c in plan.copies)
+    return plan
+
+
+@pytest.mark.parametrize("mode,port", [("sparse", 29613), ("dense", 29614), ("dense3", 29615), ("placed", 29616)])
 def test_two_rank_prefill_exchange_equals_single_rank(tmp_path, mode, port):
     mp.spawn(_prefill_rank_main, args=(2, port, str(tmp_path), mode), nprocs=2, join=True)
     x, ids, w = _prefill_routing()

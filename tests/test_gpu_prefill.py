@@ -184,6 +184,39 @@ def test_expert_parallel_shards_match_single_gpu(world):
     assert err <= 1e-5, err
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_placed_shards_with_copies_match_single_gpu(world):
+    """Shards built from a placement plan (experts spread by load, the hottest copied, fb_moe_route_placed
+    splitting a copied expert's pairs by row number) run rank by rank on one GPU over ALL rows, as the dense
+    exchange has them: the rank-order sum of the partial rows equals the single-GPU layer."""
+    torch = _torch()
+    from fngine_b200 import ep_prefill, moe, placement, prefill
+    T, inter, seed = 192, 512, 78
+    layer = moe.synth_layer(IQ3_S, IQ3_S, inter, 512, seed)
+    ws = prefill.PrefillWorkspace(T, inter)
+    xd = torch.from_numpy(synth.to_bf16_bits(synth.activations(911, T)).view(np.int16)).cuda().view(torch.bfloat16)
+    lg = (synth.normal(912, T * 513) * 1.5).astype(np.float32).reshape(T, 513)
+    lg[:, :512] += synth.zipf_router_bias(913)[None, :]
+    logits = torch.from_numpy(lg).cuda()
+    want = run_prefill(torch, layer, ws, logits, xd, T).cpu().numpy()
+    e, w = ep_prefill.topk(logits)
+    load = np.bincount(e.cpu().numpy().reshape(-1), minlength=512)
+    plan = placement.plan_placement(load, world, 512 // world + 4, tolerance=-1.0)  # (never level enough: uses every spare slot)
+    copied = sum(len(c) > 1 for c in plan.copies)
+    assert copied >= 1 and plan.slots_needed() <= 512 // world + 4
+    got = torch.zeros(T, H, dtype=torch.float32, device="cuda")
+    for d in range(world):  # rank order
+        shard = ep_prefill.EpPrefillShard(d, world, seed, IQ3_S, inter, placement=plan)
+        got += ep_prefill.local_rows(shard, ws, xd, e, w, 0, 0)
+        torch.cuda.synchronize()
+    assert ws.status() == 0
+    got = got.cpu().numpy()
+    err = max(rel_l2(got[t], want[t]) for t in range(T))
+    print("placed shards, world %d: %d experts copied, busiest rank / mean %.3f (contiguous %.3f), max rel L2 %.2e"
+          % (world, copied, plan.imbalance(load), placement.Placement.contiguous(world).imbalance(load), err))
+    assert err <= 1e-5, err
+
+
 def test_prefill_layer_at_8192_tokens_with_zipf_routing():
     """The prefill-stack benchmark's own size and routing: 8192 bf16 tokens, router N(0, 0.02) plus the
     Zipf(1.1) popularity bias, so the busiest expert takes several thousand pairs (many 256-token units)
