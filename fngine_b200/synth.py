@@ -12,9 +12,11 @@ The byte streams are defined with integer arithmetic only, so the device generat
 import numpy as np
 
 GOLDEN = np.uint64(0x9E3779B97F4A7C15)
-BLOCK_BYTES = {21: 110, 20: 18}
-BLOCK_ELEMS = {21: 256, 20: 32}
-D_SCALE = {21: 0.02, 20: 0.05}
+# ggml type ids: 21 IQ3_S, 20 IQ4_NL; the other expert formats of the reference: 18 IQ3_XXS, 22 IQ2_S, 23 IQ4_XS,
+# 42 Q2_0 (a 64-element block). Every block starts with its fp16 scale.
+BLOCK_BYTES = {21: 110, 20: 18, 18: 98, 22: 82, 23: 136, 42: 18}
+BLOCK_ELEMS = {21: 256, 20: 32, 18: 256, 22: 256, 23: 256, 42: 64}
+D_SCALE = {21: 0.02, 20: 0.05, 18: 0.004, 22: 0.004, 23: 0.002, 42: 0.05}
 
 
 def splitmix_words(seed, start, count):
@@ -40,7 +42,7 @@ def normal(seed, count):
 
 
 def d_table(fmt, seed=0xD7AB1E):
-    """65536 fp16 scales |N(0,1)| * (0.02 for IQ3_S, 0.05 for IQ4_NL), as uint16 bit patterns."""
+    """65536 fp16 scales |N(0,1)| * D_SCALE[fmt] (0.02 for IQ3_S, 0.05 for IQ4_NL), as uint16 bit patterns."""
     v = np.abs(normal(seed + fmt, 65536)) * D_SCALE[fmt]
     return v.astype(np.float16).view(np.uint16)
 

@@ -18,8 +18,12 @@
 
 #include "fb_oracle_codebooks.h"
 
+#define FBO_IQ3_XXS 18
 #define FBO_IQ4_NL 20
 #define FBO_IQ3_S 21
+#define FBO_IQ2_S 22
+#define FBO_IQ4_XS 23
+#define FBO_Q2_0 42
 #define FBO_ACT_Q8_K 0
 #define FBO_ACT_Q8_0 1
 
@@ -29,31 +33,53 @@
 #pragma pack(push, 1)
 typedef struct { uint16_t d; uint8_t qs[64]; uint8_t qh[8]; uint8_t signs[32]; uint8_t scales[4]; } fbo_iq3s;
 typedef struct { uint16_t d; uint8_t qs[16]; } fbo_iq4nl;
+typedef struct { uint16_t d; uint8_t qs[64]; uint8_t qh[8]; uint8_t scales[8]; } fbo_iq2s;   /* ggml-iq.h:59-64; qs[32..63] = signs */
+typedef struct { uint16_t d; uint8_t qs[96]; } fbo_iq3xxs;                                    /* :67-70; qs[64..95] = scales and signs */
+typedef struct { uint16_t d; uint16_t scales_h; uint8_t scales_l[4]; uint8_t qs[128]; } fbo_iq4xs; /* :73-78 */
+typedef struct { uint16_t d; uint8_t qs[16]; } fbo_q20;                                        /* :26-29, 64 elements */
 typedef struct { float d; int8_t qs[256]; int16_t bsums[16]; } fbo_q8k;
 typedef struct { uint16_t d; int8_t qs[32]; } fbo_q80;
 #pragma pack(pop)
 _Static_assert(sizeof(fbo_iq3s) == 110, "iq3_s block");
 _Static_assert(sizeof(fbo_iq4nl) == 18, "iq4_nl block");
+_Static_assert(sizeof(fbo_iq2s) == 82 && sizeof(fbo_iq3xxs) == 98 && sizeof(fbo_iq4xs) == 136 && sizeof(fbo_q20) == 18,
+               "iq2_s / iq3_xxs / iq4_xs / q2_0 blocks");
 _Static_assert(sizeof(fbo_q8k) == 292, "q8_K block");
 _Static_assert(sizeof(fbo_q80) == 34, "q8_0 block");
 
 static uint8_t g_grid[512][4];
+static uint8_t g_grid3xxs[256][4];
+static uint8_t g_grid2s[1024][8];
 static int g_grid_ready = 0;
 static void grid_init(void) {
   if (g_grid_ready) return;
   for (int i = 0; i < 512; ++i)
     for (int j = 0; j < 4; ++j) g_grid[i][j] = (uint8_t)(2 * ((kIq3sGridPacked[i] >> (3 * j)) & 7) + 1);
+  for (int i = 0; i < 256; ++i)
+    for (int j = 0; j < 4; ++j) {
+      const int c = (kIq3xxsGridPacked[i] >> (3 * j)) & 7;
+      g_grid3xxs[i][j] = (uint8_t)(c < 7 ? 4 + 8 * c : 62);
+    }
+  static const uint8_t lv2[4] = {8, 25, 43, 0};
+  for (int i = 0; i < 1024; ++i)
+    for (int j = 0; j < 8; ++j) g_grid2s[i][j] = lv2[(kIq2sGridPacked[i] >> (2 * j)) & 3];
   g_grid_ready = 1;
 }
+// ksigns_iq2xs (ggml-iq-tables.h): the 7-bit index with its parity as bit 7.
+static uint8_t ksigns(int i) { return (uint8_t)(i | ((__builtin_popcount((unsigned)i) & 1) << 7)); }
 
 // Row bytes: src/kernels/moe/moe_format.cpp:5-15.
 int64_t fbo_row_bytes(int fmt, int k) {
   if (fmt == FBO_IQ3_S) return (int64_t)(k / 256) * 110;
   if (fmt == FBO_IQ4_NL) return (int64_t)(k / 32) * 18;
+  if (fmt == FBO_IQ3_XXS) return (int64_t)(k / 256) * 98;
+  if (fmt == FBO_IQ2_S) return (int64_t)(k / 256) * 82;
+  if (fmt == FBO_IQ4_XS) return (int64_t)(k / 256) * 136;
+  if (fmt == FBO_Q2_0) return (int64_t)(k / 64) * 18;
   return 0;
 }
 // Activation format a weight format pairs with: src/cpu/iq_cpu.cpp:467-478.
-int fbo_act_of(int fmt) { return fmt == FBO_IQ3_S ? FBO_ACT_Q8_K : FBO_ACT_Q8_0; }
+int fbo_act_of(int fmt) { return fmt == FBO_IQ4_NL || fmt == FBO_Q2_0 ? FBO_ACT_Q8_0 : FBO_ACT_Q8_K; }
 
 // ---------------------------------------------------------------------------------- fp16 / bf16
 // IEEE binary16 <-> binary32, round to nearest even (what GGML_FP32_TO_FP16 / _FP16_TO_FP32
@@ -158,11 +184,137 @@ void fbo_dequant_iq4_nl(const void* blocks, float* y, int64_t k) {
   }
 }
 
+// third_party/ggml-iq/ggml-iq.c:171-199: sub-block ib uses qs[4ib..4ib+3] with two more index bits each from
+// qh[ib], signs qs[32+4ib..], and two 4-bit scales (first / second 16 weights): d*(0.5+s)*0.25.
+void fbo_dequant_iq2_s(const void* blocks, float* y, int64_t k) {
+  grid_init();
+  const fbo_iq2s* x = (const fbo_iq2s*)blocks;
+  for (int64_t b = 0; b < k / 256; ++b) {
+    const float d = fbo_fp16_to_fp32(x[b].d);
+    for (int ib = 0; ib < 8; ++ib) {
+      float db[2];
+      db[0] = d * (0.5f + (float)(x[b].scales[ib] & 0xF)) * 0.25f;
+      db[1] = d * (0.5f + (float)(x[b].scales[ib] >> 4)) * 0.25f;
+      for (int l = 0; l < 4; ++l) {
+        const int idx = x[b].qs[4 * ib + l] | ((x[b].qh[ib] << (8 - 2 * l)) & 0x300);
+        const uint8_t sg = x[b].qs[32 + 4 * ib + l];
+        for (int j = 0; j < 8; ++j) *y++ = db[l / 2] * (float)g_grid2s[idx][j] * (((sg >> j) & 1) ? -1.f : 1.f);
+      }
+    }
+  }
+}
+
+// :201-229: sub-block ib uses qs[8ib..8ib+7] (entries of four weights) and the word qs[64+4ib..]: four
+// 7-bit sign indices and a 4-bit scale in the top bits: d*(0.5+s)*0.5.
+void fbo_dequant_iq3_xxs(const void* blocks, float* y, int64_t k) {
+  grid_init();
+  const fbo_iq3xxs* x = (const fbo_iq3xxs*)blocks;
+  for (int64_t b = 0; b < k / 256; ++b) {
+    const float d = fbo_fp16_to_fp32(x[b].d);
+    for (int ib = 0; ib < 8; ++ib) {
+      uint32_t aux;
+      memcpy(&aux, x[b].qs + 64 + 4 * ib, 4);
+      const float db = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+      for (int l = 0; l < 4; ++l) {
+        const uint8_t sg = ksigns((aux >> (7 * l)) & 127);
+        const uint8_t* g1 = g_grid3xxs[x[b].qs[8 * ib + 2 * l]];
+        const uint8_t* g2 = g_grid3xxs[x[b].qs[8 * ib + 2 * l + 1]];
+        for (int j = 0; j < 4; ++j) y[j] = db * (float)g1[j] * (((sg >> j) & 1) ? -1.f : 1.f);
+        for (int j = 0; j < 4; ++j) y[j + 4] = db * (float)g2[j] * (((sg >> (j + 4)) & 1) ? -1.f : 1.f);
+        y += 8;
+      }
+    }
+  }
+}
+
+// :290-311: sub-block ib: 6-bit scale ls (4 bits from scales_l, 2 from scales_h), d*(ls-32); nibbles index
+// the IQ4_NL levels, low nibbles first.
+void fbo_dequant_iq4_xs(const void* blocks, float* y, int64_t k) {
+  const fbo_iq4xs* x = (const fbo_iq4xs*)blocks;
+  for (int64_t b = 0; b < k / 256; ++b) {
+    const float d = fbo_fp16_to_fp32(x[b].d);
+    for (int ib = 0; ib < 8; ++ib) {
+      const int ls = ((x[b].scales_l[ib / 2] >> (4 * (ib % 2))) & 0xF) | (((x[b].scales_h >> (2 * ib)) & 3) << 4);
+      const float dl = d * (float)(ls - 32);
+      const uint8_t* qs = x[b].qs + 16 * ib;
+      for (int j = 0; j < 16; ++j) {
+        y[j] = dl * (float)kIq4nlLevels[qs[j] & 0xF];
+        y[j + 16] = dl * (float)kIq4nlLevels[qs[j] >> 4];
+      }
+      y += 32;
+    }
+  }
+}
+
+// :135-152: 64 two-bit codes, LSB first, value (q - 1) * d.
+void fbo_dequant_q2_0(const void* blocks, float* y, int64_t k) {
+  const fbo_q20* x = (const fbo_q20*)blocks;
+  for (int64_t b = 0; b < k / 64; ++b) {
+    const float d = fbo_fp16_to_fp32(x[b].d);
+    for (int j = 0; j < 64; ++j) *y++ = (float)((int)((x[b].qs[j / 4] >> ((j % 4) * 2)) & 3) - 1) * d;
+  }
+}
+
 void fbo_dequant_rows(int fmt, const void* rows, int64_t row_bytes, int nrows, int k, float* y) {
   for (int r = 0; r < nrows; ++r) {
     const uint8_t* p = (const uint8_t*)rows + (int64_t)r * row_bytes;
-    if (fmt == FBO_IQ3_S) fbo_dequant_iq3_s(p, y + (int64_t)r * k, k);
-    else fbo_dequant_iq4_nl(p, y + (int64_t)r * k, k);
+    float* o = y + (int64_t)r * k;
+    if (fmt == FBO_IQ3_S) fbo_dequant_iq3_s(p, o, k);
+    else if (fmt == FBO_IQ4_NL) fbo_dequant_iq4_nl(p, o, k);
+    else if (fmt == FBO_IQ2_S) fbo_dequant_iq2_s(p, o, k);
+    else if (fmt == FBO_IQ3_XXS) fbo_dequant_iq3_xxs(p, o, k);
+    else if (fmt == FBO_IQ4_XS) fbo_dequant_iq4_xs(p, o, k);
+    else fbo_dequant_q2_0(p, o, k);
+  }
+}
+
+// Exact integer weights of one 256-block of the other Q8_K formats, the integer multiplier of each of the
+// 16 lanes (elements 16j..16j+15) and the block's float factor, as the CPU tier's decoders leave them
+// (src/cpu/iq_cpu.cpp:166-217 iq2_s and iq3_xxs, :238-255 iq4_xs): F_j = float(mult_j) * dprime.
+static void int_weights_q8k(int fmt, const void* block, int8_t* w /*256*/, int* mult /*16*/, float* dprime) {
+  grid_init();
+  if (fmt == FBO_IQ2_S) {
+    const fbo_iq2s* x = (const fbo_iq2s*)block;
+    *dprime = fbo_fp16_to_fp32(x->d) * 0.125f;
+    for (int ib = 0; ib < 8; ++ib) {
+      mult[2 * ib] = 2 * (x->scales[ib] & 0xF) + 1;
+      mult[2 * ib + 1] = 2 * (x->scales[ib] >> 4) + 1;
+      for (int l = 0; l < 4; ++l) {
+        const int idx = x->qs[4 * ib + l] | ((x->qh[ib] << (8 - 2 * l)) & 0x300);
+        const uint8_t sg = x->qs[32 + 4 * ib + l];
+        for (int j = 0; j < 8; ++j) {
+          const int m = g_grid2s[idx][j];
+          w[32 * ib + 8 * l + j] = (int8_t)(((sg >> j) & 1) ? -m : m);
+        }
+      }
+    }
+  } else if (fmt == FBO_IQ3_XXS) {
+    const fbo_iq3xxs* x = (const fbo_iq3xxs*)block;
+    *dprime = fbo_fp16_to_fp32(x->d) * 0.25f;
+    for (int ib = 0; ib < 8; ++ib) {
+      uint32_t aux;
+      memcpy(&aux, x->qs + 64 + 4 * ib, 4);
+      mult[2 * ib] = mult[2 * ib + 1] = 2 * (int)(aux >> 28) + 1;
+      for (int l = 0; l < 4; ++l) {
+        const uint8_t sg = ksigns((aux >> (7 * l)) & 127);
+        for (int h = 0; h < 2; ++h)
+          for (int j = 0; j < 4; ++j) {
+            const int m = g_grid3xxs[x->qs[8 * ib + 2 * l + h]][j];
+            w[32 * ib + 8 * l + 4 * h + j] = (int8_t)(((sg >> (4 * h + j)) & 1) ? -m : m);
+          }
+      }
+    }
+  } else {  // IQ4_XS
+    const fbo_iq4xs* x = (const fbo_iq4xs*)block;
+    *dprime = fbo_fp16_to_fp32(x->d);
+    for (int ib = 0; ib < 8; ++ib) {
+      const int ls = ((x->scales_l[ib / 2] >> (4 * (ib % 2))) & 0xF) | (((x->scales_h >> (2 * ib)) & 3) << 4);
+      mult[2 * ib] = mult[2 * ib + 1] = ls - 32;
+      for (int j = 0; j < 16; ++j) {
+        w[32 * ib + j] = kIq4nlLevels[x->qs[16 * ib + j] & 0xF];
+        w[32 * ib + 16 + j] = kIq4nlLevels[x->qs[16 * ib + j] >> 4];
+      }
+    }
   }
 }
 
@@ -301,8 +453,55 @@ float fbo_dot_iq4_nl_q8_0(int n, const void* wrow, const void* arow) {
   return hsum16(acc);
 }
 
+// The other Q8_K formats in the same micro-kernel arithmetic (src/cpu/iq_cpu.cpp:332-374): per lane
+// acc_j = fma(float(isum_j), F_j * dA, acc_j), F_j = float(mult_j) * dprime.
+static float dot_q8k_generic(int fmt, int n, const void* wrow, const void* arow) {
+  const uint8_t* w = (const uint8_t*)wrow;
+  const int64_t bb = fbo_row_bytes(fmt, 256);
+  const fbo_q8k* a = (const fbo_q8k*)arow;
+  float acc[16] = {0};
+  int8_t iw[256];
+  int mult[16];
+  float dp;
+  for (int b = 0; b < n / 256; ++b) {
+    int_weights_q8k(fmt, w + b * bb, iw, mult, &dp);
+    for (int j = 0; j < 16; ++j) {
+      int32_t isum = 0;
+      for (int i = 0; i < 16; ++i) isum += (int32_t)iw[16 * j + i] * a[b].qs[16 * j + i];
+      const float f = (float)mult[j] * dp;
+      acc[j] = fmaf((float)isum, f * a[b].d, acc[j]);
+    }
+  }
+  return hsum16(acc);
+}
+
+// Q2_0 against Q8_0 (src/cpu/iq_cpu.cpp:279-287, :311-319): a group is one 64-element weight block and two
+// activation blocks; lanes 0-7 cover the first 32 elements (four each), lanes 8-15 the second; F = the block's
+// d in every lane, dA = the lane's activation block scale.
+static float dot_q2_0_q8_0(int n, const void* wrow, const void* arow) {
+  const fbo_q20* w = (const fbo_q20*)wrow;
+  const fbo_q80* a = (const fbo_q80*)arow;
+  float acc[16] = {0};
+  for (int g = 0; g < n / 64; ++g) {
+    const float d = fbo_fp16_to_fp32(w[g].d);
+    for (int j = 0; j < 16; ++j) {
+      const fbo_q80* ab = &a[2 * g + j / 8];
+      int32_t isum = 0;
+      for (int i = 0; i < 4; ++i) {
+        const int e = 4 * j + i;
+        isum += ((int32_t)((w[g].qs[e / 4] >> ((e % 4) * 2)) & 3) - 1) * ab->qs[4 * (j % 8) + i];
+      }
+      acc[j] = fmaf((float)isum, d * fbo_fp16_to_fp32(ab->d), acc[j]);
+    }
+  }
+  return hsum16(acc);
+}
+
 float fbo_dot(int fmt, int n, const void* wrow, const void* arow) {
-  return fmt == FBO_IQ3_S ? fbo_dot_iq3_s_q8_K(n, wrow, arow) : fbo_dot_iq4_nl_q8_0(n, wrow, arow);
+  if (fmt == FBO_IQ3_S) return fbo_dot_iq3_s_q8_K(n, wrow, arow);
+  if (fmt == FBO_IQ4_NL) return fbo_dot_iq4_nl_q8_0(n, wrow, arow);
+  if (fmt == FBO_Q2_0) return dot_q2_0_q8_0(n, wrow, arow);
+  return dot_q8k_generic(fmt, n, wrow, arow);
 }
 
 // ---------------------------------------------------------------------------------- SwiGLU

@@ -17,9 +17,10 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 IQ4_NL, IQ3_S = 20, 21
+IQ3_XXS, IQ2_S, IQ4_XS, Q2_0 = 18, 22, 23, 42  # the other expert formats of the reference (ggml type ids)
 ACT_Q8_K, ACT_Q8_0 = 0, 1
-BLOCK = {IQ3_S: (256, 110), IQ4_NL: (32, 18)}
-ACT_OF = {IQ3_S: ACT_Q8_K, IQ4_NL: ACT_Q8_0}
+BLOCK = {IQ3_S: (256, 110), IQ4_NL: (32, 18), IQ3_XXS: (256, 98), IQ2_S: (256, 82), IQ4_XS: (256, 136), Q2_0: (64, 18)}
+ACT_OF = {IQ3_S: ACT_Q8_K, IQ4_NL: ACT_Q8_0, IQ3_XXS: ACT_Q8_K, IQ2_S: ACT_Q8_K, IQ4_XS: ACT_Q8_K, Q2_0: ACT_Q8_0}
 ACT_BLOCK = {ACT_Q8_K: (256, 292), ACT_Q8_0: (32, 34)}
 
 _port = None
@@ -158,8 +159,8 @@ def dequant_rows(fmt, rows, nrows, k, lib=None):
     if lib is None or lib is port():
         port().fbo_dequant_rows(fmt, _ptr(rows), row_bytes(fmt, k), nrows, k, _ptr(y))
     else:
-        fn = lib.ref_dequant_iq3_s if fmt == IQ3_S else lib.ref_dequant_iq4_nl
-        fn(_ptr(rows), _ptr(y), nrows * k)  # rows are contiguous blocks
+        if not lib.ref_dequant(fmt, _ptr(rows), _ptr(y), nrows * k):  # rows are contiguous blocks
+            raise ValueError("the reference build does not know format %d" % fmt)
     return y
 
 

@@ -38,6 +38,18 @@ void ref_dequant_iq3_s(const void* blocks, float* y, int64_t k) {
 void ref_dequant_iq4_nl(const void* blocks, float* y, int64_t k) {
   dequantize_row_iq4_nl(static_cast<const block_iq4_nl*>(blocks), y, k);
 }
+// any of the six expert formats by its ggml type id; returns 0 for an id it does not know
+int ref_dequant(int fmt, const void* blocks, float* y, int64_t k) {
+  switch (fmt) {
+    case 18: dequantize_row_iq3_xxs(static_cast<const block_iq3_xxs*>(blocks), y, k); return 1;
+    case 20: dequantize_row_iq4_nl(static_cast<const block_iq4_nl*>(blocks), y, k); return 1;
+    case 21: dequantize_row_iq3_s(static_cast<const block_iq3_s*>(blocks), y, k); return 1;
+    case 22: dequantize_row_iq2_s(static_cast<const block_iq2_s*>(blocks), y, k); return 1;
+    case 23: dequantize_row_iq4_xs(static_cast<const block_iq4_xs*>(blocks), y, k); return 1;
+    case 42: dequantize_row_q2_0(static_cast<const block_q2_0*>(blocks), y, k); return 1;
+    default: return 0;
+  }
+}
 
 // ggml reference activation quantizers and the reference's AVX-512 versions.
 void ref_quantize_q8_K(const float* x, void* y, int64_t k) {

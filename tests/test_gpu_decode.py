@@ -492,6 +492,45 @@ def test_expert_parallel_shards_on_one_gpu(world):
     assert max(rel_l2(got[t], want[t]) for t in range(tokens)) <= TOL
 
 
+def test_decode_shards_from_a_placement_plan():
+    """Decode over shards that follow a placement plan instead of contiguous ranges (experts spread over four
+    ranks by a routing average, fngine_b200/placement.py): each rank's slot map comes from the plan, the ranks
+    are played one after another on a single GPU, and the rank-order sum equals the single-GPU layer."""
+    torch = _torch()
+    from types import SimpleNamespace
+
+    from fngine_b200 import ep, moe, placement
+    tokens, seed, world = 16, 5003, 4
+    wr = torch.from_numpy(synth.router_weights(304, rows=512).view(np.int16)).cuda().view(torch.bfloat16)
+    xd = torch.from_numpy(synth.activations(78, tokens)).cuda()
+    full = moe.synth_layer(IQ3_S, IQ3_S, 512, 512, seed)
+    ws = moe.DecodeWorkspace(full)
+    y_full = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    moe.moe_layer_decode(wr, full, xd, ws, y_full)
+    torch.cuda.synchronize()
+    # a routing average with a few hot experts, as decode traffic has; no copies at decode (a copy would be
+    # streamed by two ranks in the same step)
+    avg = placement.RoutingEma(1).update(np.bincount(np.asarray(ws.work().topk_expert).reshape(-1)[:tokens * 10],
+                                                      minlength=512).astype(np.uint32)[None, :])[0] + 0.01
+    plan = placement.plan_placement(avg, world, 128)
+    assert all(len(c) == 1 for c in plan.copies) and plan.imbalance(avg) <= placement.Placement.contiguous(world).imbalance(avg)
+    parts = torch.empty(world, tokens, H, dtype=torch.float32, device="cuda")
+    n_local = 0
+    for r in range(world):
+        shard = SimpleNamespace(layer=moe.synth_layer_of(IQ3_S, IQ3_S, 512, plan.rank_experts[r], seed),
+                                slot_of=torch.from_numpy(plan.slot_map(r)).cuda())
+        ep.layer_decode_ep(wr, shard, xd, ws, parts[r])
+        torch.cuda.synchronize()
+        n_local += ws.work().n_pairs
+        assert ws.status() == 0
+    assert n_local == tokens * 10
+    y = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    ep.sum_ranks(parts, y)
+    torch.cuda.synchronize()
+    got, ref = y.cpu().numpy(), y_full.cpu().numpy()
+    assert max(rel_l2(got[t], ref[t]) for t in range(tokens)) <= 1e-6
+
+
 def test_peer_exchange_layer_with_one_rank_equals_the_plain_layer():
     """fb_moe_layer_decode_ep_p2p with a world of one rank: the rank is its own peer, so the publish /
     wait / partial-row / rank-order-sum machinery runs on one GPU (nobody else is waited for) and must

@@ -7,6 +7,7 @@ Bit-exact for weights, int8 activations, SwiGLU and expert outputs of the decode
 prefill (bf16) family is compared within 1e-5 relative (fp32 summation order differs).
 """
 import os
+import sys
 
 import numpy as np
 import pytest
@@ -29,6 +30,21 @@ def test_dequant_matches_golden(fmt, seed, name):
     rows = synth.fill_blocks(fmt, nb, 0, seed)
     assert np.array_equal(bits(O.dequant_rows(fmt, rows, 2, 2560)), bits(GOLD["dequant_" + name]))
     assert np.array_equal(O.dequant_rows_bf16(fmt, rows, 2, 2560), GOLD["dequant_bf16_" + name])
+
+
+def test_other_formats_match_golden():
+    """IQ3_XXS, IQ2_S, IQ4_XS and Q2_0 (the reference's other expert formats): dequantized rows against the
+    vendored ggml dequantizers, single-expert outputs against the AVX-512 expert tier, bit for bit."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+    import make_golden_formats as G
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_vectors_formats.npz"))
+    for fmt, seed, name in G.DEQUANT:
+        rows = synth.fill_blocks(fmt, 2 * 2560 // synth.BLOCK_ELEMS[fmt], 0, seed)
+        assert np.array_equal(bits(O.dequant_rows(fmt, rows, 2, 2560)), bits(gold["dequant_" + name])), name
+    xs = synth.activations(32, 2)
+    for fg, fd, inter, name in G.FFN:
+        h, y = O.expert_ffn(fg, fd, 2560, inter, synth.expert_blob(fg, fd, inter, 43, 6), xs)
+        assert np.array_equal(bits(h), bits(gold[name + "_h"])) and np.array_equal(bits(y), bits(gold[name + "_y"])), name
 
 
 def test_quantizers_match_golden():
@@ -155,6 +171,23 @@ def test_port_equals_reference_dequant_and_dot(fmt):
             a = O.port().fbo_dot(fmt, k, rows[r * rb:].ctypes.data, aq[t].ctypes.data)
             b = fn(k, rows[r * rb:].ctypes.data, aq[t].ctypes.data)
             assert abs(a - b) <= 2e-5 * max(1.0, abs(b))
+
+
+@ref_only
+@pytest.mark.parametrize("fg,fd,inter", [(O.IQ3_XXS, O.IQ4_NL, 512), (O.IQ2_S, O.IQ4_NL, 640), (O.IQ4_XS, O.Q2_0, 512),
+                                         (O.IQ2_S, O.Q2_0, 640), (O.IQ3_XXS, O.IQ3_XXS, 512), (O.IQ4_XS, O.IQ4_XS, 512),
+                                         (O.IQ2_S, O.IQ2_S, 512)])
+def test_port_equals_reference_on_the_other_formats(fg, fd, inter):
+    ref = O.ref()
+    for fmt in {fg, fd}:
+        k = 2560
+        rows = synth.fill_blocks(fmt, 16 * k // synth.BLOCK_ELEMS[fmt], 5, 78)
+        assert np.array_equal(bits(O.dequant_rows(fmt, rows, 16, k)), bits(O.dequant_rows(fmt, rows, 16, k, lib=ref)))
+    xs = synth.activations(89, 4)
+    blob = synth.expert_blob(fg, fd, inter, 98, 11)
+    h0, y0 = O.expert_ffn(fg, fd, 2560, inter, blob, xs)
+    h1, y1 = O.expert_ffn(fg, fd, 2560, inter, blob, xs, lib=ref)
+    assert np.array_equal(bits(h0), bits(h1)) and np.array_equal(bits(y0), bits(y1))
 
 
 @ref_only
