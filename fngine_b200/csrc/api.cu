@@ -55,12 +55,17 @@ int64_t fb_moe_row_bytes(int32_t format, int32_t k) {
   if (k <= 0) return 0;
   if (format == FB_FMT_IQ3_S) return k % 256 ? 0 : int64_t(k) / 256 * 110;
   if (format == FB_FMT_IQ4_NL) return k % 32 ? 0 : int64_t(k) / 32 * 18;
+  if (format == FB_FMT_IQ3_XXS) return k % 256 ? 0 : int64_t(k) / 256 * 98;
+  if (format == FB_FMT_IQ2_S) return k % 256 ? 0 : int64_t(k) / 256 * 82;
+  if (format == FB_FMT_IQ4_XS) return k % 256 ? 0 : int64_t(k) / 256 * 136;
+  if (format == FB_FMT_Q2_0) return k % 64 ? 0 : int64_t(k) / 64 * 18;
   return 0;
 }
 
 int32_t fb_moe_act_format(int32_t format) {
-  if (format == FB_FMT_IQ3_S) return FB_ACT_Q8_K;
-  if (format == FB_FMT_IQ4_NL) return FB_ACT_Q8_0;
+  if (format == FB_FMT_IQ3_S || format == FB_FMT_IQ3_XXS || format == FB_FMT_IQ2_S || format == FB_FMT_IQ4_XS)
+    return FB_ACT_Q8_K;
+  if (format == FB_FMT_IQ4_NL || format == FB_FMT_Q2_0) return FB_ACT_Q8_0;
   return -1;
 }
 
@@ -82,7 +87,7 @@ int32_t fb_moe_expert_layout_make(const uint8_t* slots, int64_t blob_stride, int
   if (!out) return fb::invalid("expert_layout_make: out is NULL");
   const int64_t gate_bytes = int64_t(inter) * fb_moe_row_bytes(gate_up_format, FB_HIDDEN);
   if (gate_bytes <= 0 || !fb_moe_row_bytes(down_format, inter))
-    return fb::invalid("expert_layout_make: unsupported format/inter (formats IQ3_S=21, IQ4_NL=20)");
+    return fb::invalid("expert_layout_make: unsupported format/inter (ggml type ids 18, 20, 21, 22, 23, 42)");
   if (blob_stride < fb_moe_blob_bytes(gate_up_format, down_format, inter) || (blob_stride & 15))
     return fb::invalid("expert_layout_make: blob_stride too small or not a multiple of 16");
   out->slots = slots;

@@ -62,7 +62,13 @@ constexpr int kSchedInts = 256;
 __host__ __device__ constexpr int act_row_bytes_planar(int act, int k) {
   return act == FB_ACT_Q8_K ? k + 64 : k + k / 8;
 }
-__host__ __device__ constexpr int act_of(int fmt) { return fmt == FB_FMT_IQ3_S ? FB_ACT_Q8_K : FB_ACT_Q8_0; }
+__host__ __device__ constexpr int act_of(int fmt) {
+  return fmt == FB_FMT_IQ4_NL || fmt == FB_FMT_Q2_0 ? FB_ACT_Q8_0 : FB_ACT_Q8_K;
+}
+// gate/up formats without a streaming kernel (plain kernels in moe_decode_generic.cuh)
+__host__ __device__ constexpr bool plain_gate_up(int fmt) {
+  return fmt == FB_FMT_IQ3_XXS || fmt == FB_FMT_IQ2_S || fmt == FB_FMT_IQ4_XS;
+}
 // ws.xq holds [2][16][FB_XQ_STRIDE]: the Q8_K rows of the step's tokens, then their Q8_0 rows. A workspace
 // made for a layout gets the one its gate/up format needs; one made without a layout gets both from
 // the stand-alone selection (which does not see the layout).
@@ -412,6 +418,19 @@ __global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ l
         warp_topk10_pruned([&](int e) { return logits[size_t(t) * logits_stride + e]; }, scratch, ids, wts);
       },
       slot_of, T, ws, counts, false, true, true, s_work);
+}
+
+// The selection alone, from logits a route kernel stored (one block): for layers whose gate/up format has
+// only plain kernels, which read the device work list.
+__global__ void __launch_bounds__(512) select_only_kernel(SelectArgs sel, fb_moe_decode_workspace ws) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  __shared__ WorkCache s_work;
+  select_block<2>(
+      [&](int t, uint2* scratch, int* ids, float* wts) {
+        warp_topk10_pruned([&](int e) { return __ldcg(sel.logits + size_t(t) * sel.stride + e); }, scratch, ids, wts);
+      },
+      sel.slot_of, sel.tokens, ws, nullptr, sel.remote_ok != 0, true, false, s_work);
 }
 
 // What route_kernel needs for an expert-parallel step with peer-memory exchange (n_ranks == 0: none).
@@ -1126,6 +1145,8 @@ down_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws) {
 }
 
 #include "moe_decode_iq3s.cuh"
+#define FB_MOE_DECODE_TU
+#include "moe_decode_generic.cuh"
 
 // ------------------------------------------------------------------------------ combine
 // y[t][n] = partials of token t in slot order (+ y_shared); optional rank-1 ablation of the routed
@@ -1249,9 +1270,10 @@ bool layout_ok(const fb_moe_expert_layout* L) {
        uintptr_t(L->up_offset) | uintptr_t(L->down_offset)) & 15)
     return false;
   if (L->inter != 512 && L->inter != 640) return false;
-  if (L->gate_up_format != FB_FMT_IQ3_S && L->gate_up_format != FB_FMT_IQ4_NL) return false;
+  if (L->gate_up_format != FB_FMT_IQ3_S && L->gate_up_format != FB_FMT_IQ4_NL && !plain_gate_up(L->gate_up_format))
+    return false;
   if (L->down_format == FB_FMT_IQ3_S) return L->inter % 256 == 0;
-  return L->down_format == FB_FMT_IQ4_NL;
+  return L->down_format == FB_FMT_IQ4_NL || L->down_format == FB_FMT_Q2_0;
 }
 
 // Polls a reader gives a peer-written exchange line before it records FB_STATUS_PIPELINE_TIMEOUT.
@@ -1365,6 +1387,20 @@ static int32_t launch_gate_up(const fb_moe_expert_layout* layout, const fb_moe_d
   const dim3 grid(sm_count());
   if (layout->gate_up_format == FB_FMT_IQ3_S)
     return launch_experts_iq3s(layout, ws, kPhaseGateUp, stream, "hot_gate_up", sel);
+  if (plain_gate_up(layout->gate_up_format)) {  // plain kernels: they read the device work list (sel is not for them)
+    const dim3 pgrid(sm_count() * 8);
+    cudaError_t pe;
+    if (layout->gate_up_format == FB_FMT_IQ3_XXS)
+      pe = launch_pdl(gate_up_generic_kernel<FB_FMT_IQ3_XXS>, pgrid, dim3(256), 0, as_stream(stream), *layout, *ws);
+    else if (layout->gate_up_format == FB_FMT_IQ2_S)
+      pe = launch_pdl(gate_up_generic_kernel<FB_FMT_IQ2_S>, pgrid, dim3(256), 0, as_stream(stream), *layout, *ws);
+    else
+      pe = launch_pdl(gate_up_generic_kernel<FB_FMT_IQ4_XS>, pgrid, dim3(256), 0, as_stream(stream), *layout, *ws);
+    if (pe == cudaSuccess)  // the down projection wants h re-quantized: one warp per pair
+      pe = launch_pdl(requant_h_kernel, dim3(kMaxPairs / 8), dim3(256), 0, as_stream(stream), *layout, *ws);
+    if (pe != cudaSuccess) return check_launch("hot_gate_up");
+    return 0;
+  }
   static PerDeviceOnce once;
   const cudaError_t attr =
       per_device_once(once, [] { return opt_in_smem(gate_up_kernel<FB_FMT_IQ4_NL>, gate_up_smem<FB_FMT_IQ4_NL>()); });
@@ -1409,6 +1445,11 @@ int32_t fb_moe_hot_experts(const fb_moe_expert_layout* layout, int32_t tokens, c
 
 static int32_t launch_down(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, void* stream) {
   if (layout->down_format == FB_FMT_IQ3_S) return launch_experts_iq3s(layout, ws, kPhaseDown, stream, "hot_down");
+  if (layout->down_format == FB_FMT_Q2_0) {
+    if (launch_pdl(down_q2_0_kernel, dim3(sm_count() * 8), dim3(256), 0, as_stream(stream), *layout, *ws) != cudaSuccess)
+      return check_launch("hot_down");
+    return 0;
+  }
   static PerDeviceOnce once;
   const cudaError_t attr = per_device_once(once, [] {
     cudaError_t a = opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 512>, down_smem<FB_FMT_IQ4_NL, 512>());
@@ -1486,7 +1527,14 @@ static int32_t layer_decode_impl(const void* router_w_bf16, const fb_moe_expert_
                                           : launch(route_kernel<false, false>);
   if (e != cudaSuccess) return check_launch("layer_decode: route");
   const SelectArgs sel{logits_scratch, int(FB_ROUTER_ROWS), slot_of, tokens, remote_ok ? 1 : 0};
-  const int32_t st = launch_experts(layout, ws, stream, &sel);  // selection + both projections of every routed expert
+  int32_t st;
+  if (plain_gate_up(layout->gate_up_format)) {  // no streaming kernel to select inside: one more launch
+    if (launch_pdl(select_only_kernel, dim3(1), dim3(512), 0, as_stream(stream), sel, *ws) != cudaSuccess)
+      return check_launch("layer_decode: select");
+    st = launch_experts(layout, ws, stream, nullptr);
+  } else {
+    st = launch_experts(layout, ws, stream, &sel);  // selection + both projections of every routed expert
+  }
   if (st || !with_combine) return st;
   return fb_moe_combine(ws, nullptr, nullptr, 0, nullptr, nullptr, nullptr, y_out, tokens, 0, nullptr, 0.0f, stream);
 }

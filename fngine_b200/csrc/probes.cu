@@ -8,6 +8,8 @@
 namespace fb {
 namespace {
 
+#include "moe_decode_generic.cuh"
+
 // One warp per row; lane l walks the row's sub-blocks l, l+32, ... through the shared-memory
 // codebook path. Output value = (d * (1 + 2s)) * float(signed magnitude), the reference's
 // rounding (third_party/ggml-iq/ggml-iq.c:242-250).
@@ -184,8 +186,15 @@ int32_t fb_dequant_rows(int32_t format, const uint8_t* rows, int64_t row_bytes, 
       return int32_t(attr);
     }
     dequant_iq3s_kernel<<<grid, 256, smem, as_stream(stream)>>>(rows, row_bytes, nrows, k, out);
-  } else {
+  } else if (format == FB_FMT_IQ4_NL) {
     dequant_iq4nl_kernel<<<grid, 256, 0, as_stream(stream)>>>(rows, row_bytes, nrows, k, out);
+  } else {
+    const int64_t units = int64_t(nrows) * (k / 32);
+    const int g2 = int((units + 255) / 256 < 2368 ? (units + 255) / 256 : 2368);
+    if (format == FB_FMT_IQ3_XXS) dequant_generic_kernel<FB_FMT_IQ3_XXS><<<g2, 256, 0, as_stream(stream)>>>(rows, row_bytes, nrows, k, out);
+    else if (format == FB_FMT_IQ2_S) dequant_generic_kernel<FB_FMT_IQ2_S><<<g2, 256, 0, as_stream(stream)>>>(rows, row_bytes, nrows, k, out);
+    else if (format == FB_FMT_IQ4_XS) dequant_generic_kernel<FB_FMT_IQ4_XS><<<g2, 256, 0, as_stream(stream)>>>(rows, row_bytes, nrows, k, out);
+    else dequant_generic_kernel<FB_FMT_Q2_0><<<g2, 256, 0, as_stream(stream)>>>(rows, row_bytes, nrows, k, out);
   }
   return check_launch("dequant_rows");
 }
@@ -214,9 +223,18 @@ static int32_t synth_fill(int32_t format, uint8_t* dst, int64_t n_blocks, int64_
   if (format == FB_FMT_IQ3_S)
     synth_fill_kernel<110><<<grid, 256, 0, as_stream(stream)>>>(dst, n_blocks, first_block, seed, d_table, chunk_blocks,
                                                                 chunk_stride);
-  else if (format == FB_FMT_IQ4_NL)
+  else if (format == FB_FMT_IQ4_NL || format == FB_FMT_Q2_0)
     synth_fill_kernel<18><<<grid, 256, 0, as_stream(stream)>>>(dst, n_blocks, first_block, seed, d_table, chunk_blocks,
                                                                chunk_stride);
+  else if (format == FB_FMT_IQ3_XXS)
+    synth_fill_kernel<98><<<grid, 256, 0, as_stream(stream)>>>(dst, n_blocks, first_block, seed, d_table, chunk_blocks,
+                                                               chunk_stride);
+  else if (format == FB_FMT_IQ2_S)
+    synth_fill_kernel<82><<<grid, 256, 0, as_stream(stream)>>>(dst, n_blocks, first_block, seed, d_table, chunk_blocks,
+                                                               chunk_stride);
+  else if (format == FB_FMT_IQ4_XS)
+    synth_fill_kernel<136><<<grid, 256, 0, as_stream(stream)>>>(dst, n_blocks, first_block, seed, d_table, chunk_blocks,
+                                                                chunk_stride);
   else
     return invalid("synth_fill: unsupported format");
   return check_launch("synth_fill");

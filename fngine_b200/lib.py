@@ -11,6 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("FNGINE_B200_LIB") or os.path.join(HERE, "libfngine_b200.so")
 
 FMT_IQ4_NL, FMT_IQ3_S = 20, 21
+FMT_IQ3_XXS, FMT_IQ2_S, FMT_IQ4_XS, FMT_Q2_0 = 18, 22, 23, 42  # decode width only (plain kernels)
 DT_F32, DT_BF16 = 0, 1
 ACT_Q8_K, ACT_Q8_0 = 0, 1
 HIDDEN, EXPERTS, TOPK, ROUTER_ROWS = 2560, 512, 10, 513

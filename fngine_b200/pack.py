@@ -4,9 +4,10 @@ tensors `blk.N.ffn_{gate,up,down}_exps.weight` of a GGUF v3 file (tools/gguf.py:
 layer, 512 blobs `gate | up | down` of raw ggml blocks; `load_layer` puts them in HBM as the slot array
 the kernels read (stride kept from the pack, 4096-aligned).
 
-The kernels decode IQ3_S and IQ4_NL. A layer in another format of the pack spec (IQ3_XXS, IQ2_S, IQ4_XS
-gate/up; Q2_0 down) is described and validated like the rest, and refused by `load_layer` with a PackError
-that names it. Everything here is host code; device memory comes from torch."""
+The decode kernels take gate/up in IQ3_S, IQ4_NL, IQ3_XXS, IQ2_S or IQ4_XS and down in IQ3_S, IQ4_NL or Q2_0
+(IQ3_S and IQ4_NL through the streaming kernels, the others through plain ones). A layer in another
+combination of the pack spec's formats is described and validated like the rest, and refused by `load_layer`
+with a PackError that names it. Everything here is host code; device memory comes from torch."""
 import json
 import os
 import struct
@@ -18,7 +19,8 @@ import numpy as np
 EXPERT_TYPES = {18: ("IQ3_XXS", 98, 256), 20: ("IQ4_NL", 18, 32), 21: ("IQ3_S", 110, 256), 22: ("IQ2_S", 82, 256),
                 23: ("IQ4_XS", 136, 256), 42: ("Q2_0", 18, 64)}
 TYPE_ID_OF = {v[0]: k for k, v in EXPERT_TYPES.items()}
-KERNEL_FORMATS = (20, 21)  # what the GPU kernels decode
+GATE_UP_FORMATS = (18, 20, 21, 22, 23)  # what the GPU decode kernels take as gate/up ...
+DOWN_FORMATS = (20, 21, 42)             # ... and as down
 BLOB_ALIGN = 4096
 
 
@@ -152,7 +154,7 @@ class ExpertPack:
 
     def supported(self, layer):
         info = self.layers[layer]
-        return info.gu_type in KERNEL_FORMATS and info.down_type in KERNEL_FORMATS
+        return info.gu_type in GATE_UP_FORMATS and info.down_type in DOWN_FORMATS
 
     def load_layer(self, layer, first=0, count=None, device="cuda"):
         """The layer's experts (or the shard first .. first + count - 1 of them) as an ExpertLayer in HBM."""
@@ -164,9 +166,10 @@ def _to_device(info, inter, slots, what, device):
     import torch
 
     from . import moe
-    if info.gu_type not in KERNEL_FORMATS or info.down_type not in KERNEL_FORMATS:
+    if info.gu_type not in GATE_UP_FORMATS or info.down_type not in DOWN_FORMATS:
         raise PackError("%s: %s gate/up with %s down is in the pack spec but not decoded by the kernels "
-                        "(IQ3_S and IQ4_NL are)" % (what, EXPERT_TYPES[info.gu_type][0], EXPERT_TYPES[info.down_type][0]))
+                        "(gate/up: IQ3_S, IQ4_NL, IQ3_XXS, IQ2_S, IQ4_XS; down: IQ3_S, IQ4_NL, Q2_0)"
+                        % (what, EXPERT_TYPES[info.gu_type][0], EXPERT_TYPES[info.down_type][0]))
     host = torch.from_numpy(np.array(slots, dtype=np.uint8, order="C")).reshape(-1)  # a writable copy of the mapped bytes
     dev = torch.empty(host.numel(), dtype=torch.uint8, device=device)
     dev.copy_(host.pin_memory() if torch.cuda.is_available() else host, non_blocking=False)

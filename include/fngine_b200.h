@@ -34,8 +34,10 @@
 extern "C" {
 #endif
 
-/* ggml type ids of the expert formats (src/kernels/moe/moe.h:48-55). */
-enum { FB_FMT_IQ4_NL = 20, FB_FMT_IQ3_S = 21 };
+/* ggml type ids of the expert formats (src/kernels/moe/moe.h:48-55). IQ3_S and IQ4_NL have the streaming
+ * decode kernels and the prefill kernels; IQ3_XXS, IQ2_S and IQ4_XS (gate/up) and Q2_0 (down) run at decode
+ * width through plain, untuned kernels (no prefill path). */
+enum { FB_FMT_IQ3_XXS = 18, FB_FMT_IQ4_NL = 20, FB_FMT_IQ3_S = 21, FB_FMT_IQ2_S = 22, FB_FMT_IQ4_XS = 23, FB_FMT_Q2_0 = 42 };
 /* element types of activation inputs */
 enum { FB_DT_F32 = 0, FB_DT_BF16 = 1 };
 /* activation block formats (src/cpu/iq_cpu.h:44) */

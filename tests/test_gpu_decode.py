@@ -58,19 +58,24 @@ def planar_from_blocks(act, blocks, k):
 
 
 # ---------------------------------------------------------------------------------- probes
-@pytest.mark.parametrize("fmt", [IQ3_S, IQ4_NL])
+IQ3_XXS, IQ2_S, IQ4_XS, Q2_0 = O.IQ3_XXS, O.IQ2_S, O.IQ4_XS, O.Q2_0
+
+
+@pytest.mark.parametrize("fmt", [IQ3_S, IQ4_NL, IQ3_XXS, IQ2_S, IQ4_XS, Q2_0])
 def test_synth_device_equals_host(fmt):
     torch = _torch()
     from fngine_b200 import moe
-    layer = moe.synth_layer(fmt, fmt, 512, 3, 77)
+    fmt, fd = (IQ4_NL, Q2_0) if fmt == Q2_0 else (fmt, fmt if fmt in (IQ3_S, IQ4_NL) else IQ4_NL)
+    layer = moe.synth_layer(fmt, fd, 512, 3, 77)
     torch.cuda.synchronize()
     dev = layer.slots.cpu().numpy()
     for e in range(3):
-        host = synth.expert_blob(fmt, fmt, 512, 77, e)
+        host = synth.expert_blob(fmt, fd, 512, 77, e)
         assert np.array_equal(dev[e * len(host):(e + 1) * len(host)], host)
 
 
-@pytest.mark.parametrize("fmt,k", [(IQ3_S, 2560), (IQ3_S, 512), (IQ4_NL, 2560), (IQ4_NL, 640)])
+@pytest.mark.parametrize("fmt,k", [(IQ3_S, 2560), (IQ3_S, 512), (IQ4_NL, 2560), (IQ4_NL, 640), (IQ3_XXS, 2560),
+                                   (IQ2_S, 2560), (IQ4_XS, 2560), (Q2_0, 512), (Q2_0, 640)])
 def test_dequant_bit_exact(fmt, k):
     torch = _torch()
     from fngine_b200 import moe
@@ -287,6 +292,37 @@ def test_moe_layer_decode(fg, fd, inter, tokens):
     assert np.array_equal(y5.cpu().numpy().view(np.uint32), y1.view(np.uint32))
     print("layer fmt %d/%d inter %d T=%d: distinct experts %d, max rel L2 %.2e" %
           (fg, fd, inter, tokens, work.n_items, max(errs)))
+
+
+@pytest.mark.parametrize("fg,fd,inter,tokens", [(IQ3_XXS, IQ4_NL, 512, 3), (IQ2_S, IQ4_NL, 640, 9), (IQ4_XS, Q2_0, 512, 16),
+                                                (IQ2_S, Q2_0, 640, 1), (IQ3_S, Q2_0, 512, 5), (IQ4_NL, Q2_0, 640, 7)])
+def test_moe_layer_decode_in_the_other_formats(fg, fd, inter, tokens):
+    """The reference's other expert formats (IQ3_XXS / IQ2_S / IQ4_XS gate/up, Q2_0 down) through the same layer
+    call, against the CPU expert path on identical bytes (the oracle is pinned to the reference build for them)."""
+    torch = _torch()
+    from fngine_b200 import moe
+    seed = 2000 + inter + fg
+    layer = moe.synth_layer(fg, fd, inter, 512, seed)
+    ws = moe.DecodeWorkspace(layer)
+    wr = torch.from_numpy(synth.router_weights(305, rows=512).view(np.int16)).cuda().view(torch.bfloat16)
+    x = synth.activations(504 + tokens, tokens)
+    xd = torch.from_numpy(x).cuda()
+    y = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    moe.moe_layer_decode(wr, layer, xd, ws, y)
+    torch.cuda.synchronize()
+    y1 = y.cpu().numpy()
+    logits = ws.logits.cpu().numpy()[:tokens * 513].reshape(tokens, 513)[:, :512]
+    ids, w = O.topk(logits)
+    work = ws.work()
+    assert np.array_equal(np.array([list(work.topk_expert[t]) for t in range(tokens)]), ids)
+    want = oracle_layer(fg, fd, inter, seed, x, ids, w)
+    errs = [rel_l2(y1[t], want[t]) for t in range(tokens)]
+    assert max(errs) <= TOL, errs
+    assert ws.status() == 0
+    # the fused layer call equals the reference's five-call sequence on the same logits
+    y5 = run_layer(torch, moe, layer, ws, None, xd, tokens, logits=ws.logits.clone())
+    assert np.array_equal(y5.cpu().numpy().view(np.uint32), y1.view(np.uint32))
+    print("layer fmt %d/%d inter %d T=%d: distinct experts %d, max rel L2 %.2e" % (fg, fd, inter, tokens, work.n_items, max(errs)))
 
 
 @pytest.mark.parametrize("fg,fd", [(IQ3_S, IQ3_S), (IQ4_NL, IQ4_NL)])

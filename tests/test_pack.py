@@ -128,14 +128,17 @@ def test_pack_round_trip_and_validation(tmp_path):
 
 
 def test_formats_the_kernels_do_not_decode_are_named(tmp_path):
-    """An IQ2_S / Q2_0 layer is a valid pack layer; loading it for the GPU is refused by name."""
+    """An IQ2_S / Q2_0 layer is a valid pack layer the decode kernels take; Q2_0 as a gate/up format (or
+    IQ2_S as a down format) is a valid description too, but loading it for the GPU is refused by name."""
     hidden, inter = 256, 256
     info = pack.layer_info(IQ2_S, 42, hidden, inter, 0)
     blobs = np.zeros((2, info.blob_bytes), dtype=np.uint8)
+    info2 = pack.layer_info(IQ4_NL, IQ2_S, hidden, inter, 0)
+    blobs2 = np.zeros((2, info2.blob_bytes), dtype=np.uint8)
     d = str(tmp_path / "pack")
-    pack.write_expert_pack(d, hidden, inter, [(IQ2_S, 42, blobs)])
+    pack.write_expert_pack(d, hidden, inter, [(IQ2_S, 42, blobs), (IQ4_NL, IQ2_S, blobs2)])
     p = pack.ExpertPack.open(d)
     assert p.layers[0].gate_bytes == 256 * 82 and p.layers[0].down_bytes == 256 * 4 * 18
-    assert not p.supported(0)
-    with pytest.raises(pack.PackError, match="IQ2_S gate/up with Q2_0 down"):
-        p.load_layer(0, device="cpu")
+    assert p.supported(0) and not p.supported(1)
+    with pytest.raises(pack.PackError, match="IQ4_NL gate/up with IQ2_S down"):
+        p.load_layer(1, device="cpu")
