@@ -215,18 +215,18 @@ def single_expert_section(torch, layers, routers, steps):
             "call": "fb_moe_layer_decode_ep with one resident expert of the token's ten", "device_status": ws.status()}
 
 
-def iq4nl_section(torch, steps, n_layers=4):
+def iq4nl_section(torch, steps, n_layers=4, fg=20, fd=20, inter=INTER, batches=(1, 8)):
     """The IQ4_NL resident-expert variant (18-byte blocks, Q8_0 activations): the same decode layer at batch
-    1 and 8, four rotating layers (4.5 GB, larger than L2), CUDA-graph replays, device time."""
+    1 and 8, four rotating layers (4.5 GB, larger than L2), CUDA-graph replays, device time. With other
+    formats: the same measurement for a layer of the reference's other expert formats (plain kernels)."""
     from fngine_b200 import moe, synth
-    fmt = 20
-    blob = 3 * 737280
-    layers = [moe.synth_layer(fmt, fmt, INTER, EXPERTS, 6000 + l) for l in range(n_layers)]
+    blob = synth.blob_bytes(fg, fd, inter)
+    layers = [moe.synth_layer(fg, fd, inter, EXPERTS, 6000 + l) for l in range(n_layers)]
     routers = [torch.from_numpy(synth.router_weights(9100 + l).view(np.int16)).cuda().view(torch.bfloat16)
                for l in range(n_layers)]
     ws = moe.DecodeWorkspace(layers[0])
     res = {}
-    for b in (1, 8):
+    for b in batches:
         xs = [torch.from_numpy(synth.activations(7100 + l, b)).cuda() for l in range(n_layers)]
         y = torch.empty(b, HIDDEN, dtype=torch.float32, device="cuda")
         d = []
@@ -253,7 +253,11 @@ def iq4nl_section(torch, steps, n_layers=4):
         t = e0.elapsed_time(e1) / steps
         by = sum(k * blob + ROUTER_BYTES for k in d)
         res[str(b)] = {"gbs": by / t / 1e6, "us_per_layer": t / n_layers * 1e3, "distinct_experts_mean": sum(d) / n_layers}
-    res["workload"] = "512 IQ4_NL experts per layer (2,211,840 B each), Q8_0 activations, %d rotating layers" % n_layers
+    if (fg, fd, inter) == (20, 20, INTER):
+        res["workload"] = "512 IQ4_NL experts per layer (2,211,840 B each), Q8_0 activations, %d rotating layers" % n_layers
+    else:
+        res["workload"] = "512 experts per layer, gate/up ggml type %d, down type %d, intermediate %d (%d B each), %d " \
+                          "rotating layers; plain (untuned) kernels for the formats beside IQ3_S and IQ4_NL" % (fg, fd, inter, blob, n_layers)
     res["device_status"] = ws.status()
     del layers
     torch.cuda.empty_cache()
@@ -777,6 +781,10 @@ def run_ours(args, rank, world, local_rank):
     iq4 = iq4nl_section(torch, args.steps) if want("iq4nl") else None
     fp8 = fp8_gemm_section(torch) if want("fp8") else None
     fp8dec = fp8_decode_section(torch) if want("fp8dec") else None
+    other_formats = None
+    if want("iq4nl"):  # the reference pool's own default pair (IQ2_S gate/up, IQ4_NL down, 640) and a Q2_0 down
+        other_formats = {"iq2s_iq4nl_640": iq4nl_section(torch, args.steps, fg=22, fd=20, inter=640, batches=(1, 8)),
+                         "iq4xs_q2_0_512": iq4nl_section(torch, args.steps, fg=23, fd=42, inter=512, batches=(8,))}
     pre = prefill_section(torch, n_layers=args.prefill_layers) if want("prefill") else None
     try:  # test infrastructure beside the measurement: never allowed to break it
         legacy = legacy_section(torch, steps=args.steps) if want("legacy") else None
@@ -818,6 +826,7 @@ def run_ours(args, rank, world, local_rank):
         "other_batches": other,
         "single_expert": single,
         "iq4nl_decode": iq4,
+        "other_formats_decode": other_formats,
         "fp8_row_gemm": fp8,
         "fp8_row_decode": fp8dec,
         "prefill_stack": pre,
