@@ -801,7 +801,7 @@ def run_ours(args, rank, world, local_rank):
         "us_per_layer": ms / args.steps / Lr * 1e3,
         "distinct_experts_per_layer": distinct,
         "frac_of_hbm_peak": value / peak,
-        "roofline": {"bound": "hbm", "kernel": "experts_iq3s_kernel (gate/up + down tiles of every routed expert, one launch)",
+        "roofline": {"bound": "hbm", "kernel": "experts_kernel<IQ3_S> (selection, then gate/up + down tiles of every routed expert, one launch)",
                      "achieved": ex_ach, "peak": peak, "unit": "GB/s", "frac": ex_ach / peak, "peak_source": peak_src,
                      "traffic": EXPERTS_DRAM_TRAFFIC_RATIO * sum(ex_bytes) / len(ex_bytes),
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on layer 0 of this "

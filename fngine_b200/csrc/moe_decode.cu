@@ -1,15 +1,17 @@
 // Decode-width (T <= 16) routed-expert kernels on native GGUF expert bytes.
 //
-//   route    router projection, once-per-token activation quantization, top-10, sorted work list
-//            (select = the same selection from given logits)
+//   route    router projection, once-per-token activation quantization
+//   select   top-10 and the sorted work list (stand-alone from given logits, or inside the expert kernel)
 //   gate_up  h[pair][j] = silu(gate_j . x) * (up_j . x)
 //   down     partial[pair][n] = w_pair * (down_n . q8(h[pair]))
 //   combine  y[t] = sum of token t's partials in slot order (+ shared, + residual write)
 //
-// gate_up and down are persistent, one CTA per SM. A producer warp streams whole row groups of the
-// expert blob into a two-stage shared-memory ring with 1-D bulk async copies (TMA, no multicast)
-// signalled through mbarriers; consumer warps decode the blocks from shared memory with the
-// codebooks held there and accumulate exact int8 dot products (dp4a). Numerics are those of the
+// gate_up and down of IQ3_S and IQ4_NL experts are one persistent kernel, one CTA per SM
+// (moe_decode_iq3s.cuh): a producer thread streams tiles of the expert blob into a three-stage
+// shared-memory ring with 1-D bulk async copies (TMA, no multicast) signalled through mbarriers;
+// consumer warps decode the blocks from shared memory and accumulate exact int8 dot products (dp4a).
+// (IQ4_NL down at intermediate 640 keeps an earlier two-stage kernel; the other formats have plain
+// kernels, moe_decode_generic.cuh.) Numerics are those of the
 // reference's CPU expert tier (src/cpu/iq_cpu.h:12-40 of the reference project): Q8_K activations
 // for IQ3_S weights, Q8_0 for IQ4_NL, integer sums per block, one fp32 scale step per block.
 #include "iq_decode.cuh"
@@ -725,23 +727,6 @@ __device__ __forceinline__ void producer_loop(const Ring& r, const fb_moe_decode
 }
 
 // ------------------------------------------------------------------------------ per-format tile math
-template <int FMT>
-struct GateUp;
-
-// IQ4_NL: 32 intermediate rows of 1440 bytes per matrix, cut into sixteen tasks drawn from the same
-// shared-memory ticket: task k is rows 2k, 2k+1 of gate and of up, eight lanes per row, lane q
-// taking the 18-byte blocks q, q + 8, ... (SwiGLU needs no cross-task reduction).
-template <>
-struct GateUp<FB_FMT_IQ4_NL> {
-  static constexpr int kJ = 32, kRowBytes = 1440, kWarps = 16, kTasks = 16;
-  static constexpr int kAct = FB_ACT_Q8_0, kActBytes = H + H / 8;
-  static constexpr int kPartialFloats = 2 * kTT * kJ;  // h of the entry in each of the two slots
-  // The up rows sit 64 bytes after the gate rows: a row is 360 words (8 mod 32), so with both
-  // parts on the same bank phase the gate and the up lanes of a warp would collide pairwise; 16
-  // words apart the 32 lanes' words fall in 32 different banks.
-  static constexpr int kUpPad = 64;
-};
-
 // One 36-byte IQ4_NL unit (two blocks) against TT interleaved Q8_0 rows; ublk = index of the
 // unit's first block within the row.
 template <int TT>
@@ -879,135 +864,6 @@ __device__ __forceinline__ bool draw_task(const Ring& r, int* ticket_ctr, uint32
     return false;
   }
   return r.meta[s].tile >= 0;
-}
-
-// ------------------------------------------------------------------------------ gate/up kernel
-template <int FMT>
-__global__ void __launch_bounds__((GateUp<FMT>::kWarps + 1) * 32, 1)
-gate_up_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, bool select, SelectArgs sel) {
-  using C = GateUp<FMT>;
-  constexpr int kW = C::kWarps, kPart = C::kJ * C::kRowBytes, kUp = kPart + C::kUpPad, kStageW = kUp + kPart;
-  constexpr int kStage = kStageW + kTT * C::kActBytes;
-  extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* p = smem;
-  uint8_t* stage0 = p;
-  p += 2 * kStage;
-  float* partials = reinterpret_cast<float*>(p);
-  p += C::kPartialFloats * 4 + 16;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p);
-  __shared__ StageMeta s_meta[2];
-  __shared__ int s_misc[4];  // [0] abort, [1] task ticket, [2..3] finished tasks per slot
-  __shared__ WorkCache s_work;
-  Ring ring{bars, bars + 2, s_meta, s_misc};
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) {
-    ring_init(ring, 1);  // one arrival frees a slot: the warp that finishes the entry's last task
-    s_misc[1] = 0;
-    s_misc[2] = 0;
-    s_misc[3] = 0;
-  }
-  __syncthreads();
-  pdl_launch_dependents();
-  pdl_wait_prior();
-
-  int n_items;
-  if (select) {  // the fused layer call: every CTA builds the work list itself (see SelectArgs)
-    select_block<2>(
-        [&](int t, uint2* scratch, int* ids, float* wts) {
-          warp_topk10_pruned([&](int e) { return __ldcg(sel.logits + size_t(t) * sel.stride + e); }, scratch, ids, wts);
-        },
-        sel.slot_of, sel.tokens, ws, nullptr, sel.remote_ok != 0, blockIdx.x == 0, false, s_work);
-    n_items = s_work.n_items;
-  } else {
-    n_items = min(max(ws.work->n_items, 0), kMaxPairs);
-  }
-  const int I = L.inter;
-  const int tpi = I / C::kJ;
-  const int n_tiles = n_items * tpi;
-  const int down_act = act_of(L.down_format);
-
-  if (warp == kW) {
-    // ---------------- producer: one lane draws tiles and issues their bulk copies into the ring.
-    if (!select) {
-      work_cache_fill(ws, s_work, n_items);
-      __syncwarp();
-    }
-    if (lane == 0) {
-      producer_loop(ring, ws, s_work, ws.sched + kSchedGateUp, n_tiles, tpi, C::kJ,
-                    [&](int s, int slot_id, int sub, int pair0, int ntp) {
-                      const uint8_t* blob = L.slots + int64_t(slot_id) * L.blob_stride;
-                      uint8_t* st = stage0 + s * kStage;
-                      mbar_expect_tx(&ring.full[s], uint32_t(2 * kPart + ntp * C::kActBytes));
-                      const size_t off = size_t(sub) * kPart;
-                      bulk_g2s(st, blob + L.gate_offset + off, kPart, &ring.full[s]);
-                      bulk_g2s(st + kUp, blob + L.up_offset + off, kPart, &ring.full[s]);
-                      for (int t = 0; t < ntp; ++t)
-                        bulk_g2s(st + kStageW + t * C::kActBytes,
-                                 ws.xq + xq_offset(C::kAct) + size_t(s_work.pair_token[pair0 + t]) * FB_XQ_STRIDE,
-                                 C::kActBytes,
-                                 &ring.full[s]);
-                    });
-    }
-    return;
-  }
-
-  // ---------------- consumers
-  {
-    const Iq4nlLevels lv = iq4nl_levels();
-    while (true) {
-      int s, task;
-      if (!draw_task<C::kTasks>(ring, &s_misc[1], ws.status, lane, s, task)) break;
-      const int ntp = ring.meta[s].ntp, pair0 = ring.meta[s].pair0, j0 = ring.meta[s].row0;
-      const int item = ring.meta[s].item, ipb = ring.meta[s].item_pair0, itok = ring.meta[s].item_tok;
-      uint8_t* st = stage0 + s * kStage;
-      const uint8_t* actbase = st + kStageW;
-      // lanes 0-7 gate row 2k, 8-15 gate 2k+1, 16-23 up 2k, 24-31 up 2k+1
-      const int q = lane & 7, r = (lane >> 3) & 1, mat = lane >> 4;
-      const uint8_t* row = st + mat * kUp + (2 * task + r) * C::kRowBytes;
-      float acc[kTT] = {0.0f, 0.0f};
-      const bool odd = (q & 1) != 0, swap = (q & 4) != 0;
-      if (ntp == 1) {
-        const uint8_t* ar[1] = {actbase};
-        float a1[1] = {0.0f};
-#pragma unroll 2
-        for (int it = 0; it < 10; ++it) iq4nl_block_dot<1>(row, q + 8 * it, odd, swap, lv, ar, H, a1);
-        acc[0] = a1[0];
-      } else {
-        const uint8_t* ar[2] = {actbase, actbase + C::kActBytes};
-#pragma unroll 2
-        for (int it = 0; it < 10; ++it) iq4nl_block_dot<2>(row, q + 8 * it, odd, swap, lv, ar, H, acc);
-      }
-      // the task's two rows of h wait in shared memory for the warp that finishes the entry
-      float* hrow = partials + s * (kTT * C::kJ);
-#pragma unroll
-      for (int t = 0; t < kTT; ++t) {
-        float v = acc[t];
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        v += __shfl_xor_sync(0xffffffffu, v, 4);
-        const float up = __shfl_down_sync(0xffffffffu, v, 16);
-        if (t < ntp && q == 0 && mat == 0) hrow[t * C::kJ + 2 * task + r] = silu_mul(v, up);
-      }
-      // The warp that finishes the entry's last task stores the entry's 32 rows of h (one 128-byte line per
-      // token), hands the slot back to the producer and counts the entry as one contribution to its item:
-      // one device-wide fence and one device atomic per entry instead of one per task.
-      __threadfence_block();
-      __syncwarp();
-      int done = 0;
-      if (lane == 0) done = atomicAdd(&s_misc[2 + s], 1);
-      done = __shfl_sync(0xffffffffu, done, 0);
-      if (done != C::kTasks - 1) continue;
-      __threadfence_block();
-      for (int t = 0; t < ntp; ++t) ws.h[size_t(pair0 + t) * I + j0 + lane] = hrow[t * C::kJ + lane];
-      __syncwarp();
-      if (lane == 0) {
-        s_misc[2 + s] = 0;
-        mbar_arrive(&ring.empty[s]);
-      }
-      item_contribution_done(ws, item, ipb, itok, tpi * ((itok + kTT - 1) / kTT), down_act, I, lane);
-    }
-  }
 }
 
 // ------------------------------------------------------------------------------ down kernel
@@ -1252,12 +1108,6 @@ __global__ void __launch_bounds__(256) ep_combine_exchange_kernel(fb_moe_decode_
 }
 
 // ------------------------------------------------------------------------------ host side
-template <int FMT>
-constexpr size_t gate_up_smem() {
-  using C = GateUp<FMT>;
-  return 2 * size_t(2 * C::kJ * C::kRowBytes + C::kUpPad + kTT * C::kActBytes) +
-         C::kPartialFloats * 4 + 16 + 64;
-}
 template <int FMT, int INTER>
 constexpr size_t down_smem() {
   using C = Down<FMT, INTER>;
@@ -1289,6 +1139,24 @@ bool ws_fits(const fb_moe_decode_workspace* ws, const fb_moe_expert_layout* L, b
 
 bool ws_ok(const fb_moe_decode_workspace* ws) {
   return ws && ws->work && ws->xq && ws->h && ws->hq && ws->partial && ws->item_done && ws->sched && ws->status;
+}
+
+// The streaming expert kernel of a format (IQ3_S or IQ4_NL) over the given phases.
+template <int FMT>
+int32_t launch_experts_fmt(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, int phases,
+                           void* stream, const char* what, const SelectArgs* sel) {
+  using C = ExpertsCfg<FMT>;
+  static PerDeviceOnce once;
+  const cudaError_t attr = per_device_once(once, [] { return opt_in_smem(experts_kernel<FMT>, C::kSmem); });
+  if (attr != cudaSuccess) {
+    set_error("%s: shared-memory opt-in: %s", what, cudaGetErrorString(attr));
+    return int32_t(attr);
+  }
+  const cudaError_t e = launch_pdl(experts_kernel<FMT>, dim3(sm_count()), dim3((C::kWarps + 1) * 32), C::kSmem,
+                                   as_stream(stream), *layout, *ws, sel ? (phases | kPhaseSelect) : phases,
+                                   sel ? *sel : SelectArgs{});
+  if (e != cudaSuccess) return check_launch(what);
+  return 0;
 }
 
 }  // namespace
@@ -1368,23 +1236,12 @@ int32_t fb_moe_select_publish(const float* router_logits, int32_t logits_stride,
 // The IQ3_S expert kernel: gate/up tiles, down tiles, or both in one launch (down needs inter 512).
 static int32_t launch_experts_iq3s(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, int phases,
                                    void* stream, const char* what, const SelectArgs* sel = nullptr) {
-  static PerDeviceOnce once;
-  const cudaError_t attr = per_device_once(once, [] { return opt_in_smem(experts_iq3s_kernel, Experts3::kSmem); });
-  if (attr != cudaSuccess) {
-    set_error("%s: shared-memory opt-in: %s", what, cudaGetErrorString(attr));
-    return int32_t(attr);
-  }
-  const cudaError_t e = launch_pdl(experts_iq3s_kernel, dim3(sm_count()), dim3((Experts3::kWarps + 1) * 32), Experts3::kSmem,
-                                   as_stream(stream), *layout, *ws, sel ? (phases | kPhaseSelect) : phases,
-                                   sel ? *sel : SelectArgs{});
-  if (e != cudaSuccess) return check_launch(what);
-  return 0;
+  return launch_experts_fmt<FB_FMT_IQ3_S>(layout, ws, phases, stream, what, sel);
 }
 
 // `sel`: the kernel runs the selection itself (the fused layer call), else it reads the device work list.
 static int32_t launch_gate_up(const fb_moe_expert_layout* layout, const fb_moe_decode_workspace* ws, void* stream,
                               const SelectArgs* sel) {
-  const dim3 grid(sm_count());
   if (layout->gate_up_format == FB_FMT_IQ3_S)
     return launch_experts_iq3s(layout, ws, kPhaseGateUp, stream, "hot_gate_up", sel);
   if (plain_gate_up(layout->gate_up_format)) {  // plain kernels: they read the device work list (sel is not for them)
@@ -1401,18 +1258,9 @@ static int32_t launch_gate_up(const fb_moe_expert_layout* layout, const fb_moe_d
     if (pe != cudaSuccess) return check_launch("hot_gate_up");
     return 0;
   }
-  static PerDeviceOnce once;
-  const cudaError_t attr =
-      per_device_once(once, [] { return opt_in_smem(gate_up_kernel<FB_FMT_IQ4_NL>, gate_up_smem<FB_FMT_IQ4_NL>()); });
-  if (attr != cudaSuccess) {
-    set_error("hot_gate_up: shared-memory opt-in: %s", cudaGetErrorString(attr));
-    return int32_t(attr);
-  }
-  const cudaError_t e = launch_pdl(gate_up_kernel<FB_FMT_IQ4_NL>, grid, dim3((GateUp<FB_FMT_IQ4_NL>::kWarps + 1) * 32),
-                                   gate_up_smem<FB_FMT_IQ4_NL>(), as_stream(stream), *layout, *ws, sel != nullptr,
-                                   sel ? *sel : SelectArgs{});
-  if (e != cudaSuccess) return check_launch("hot_gate_up");
-  return 0;
+  if (layout->gate_up_format == FB_FMT_IQ4_NL)
+    return launch_experts_fmt<FB_FMT_IQ4_NL>(layout, ws, kPhaseGateUp, stream, "hot_gate_up", sel);
+  return invalid("hot_gate_up: unsupported gate/up format");
 }
 
 int32_t fb_moe_hot_gate_up(const fb_moe_expert_layout* layout, int32_t tokens, const fb_moe_decode_workspace* ws,
@@ -1430,6 +1278,8 @@ static int32_t launch_experts(const fb_moe_expert_layout* layout, const fb_moe_d
                               const SelectArgs* sel) {
   if (layout->gate_up_format == FB_FMT_IQ3_S && layout->down_format == FB_FMT_IQ3_S)
     return launch_experts_iq3s(layout, ws, kPhaseGateUp | kPhaseDown, stream, "hot_experts", sel);
+  if (layout->gate_up_format == FB_FMT_IQ4_NL && layout->down_format == FB_FMT_IQ4_NL && layout->inter == 512)
+    return launch_experts_fmt<FB_FMT_IQ4_NL>(layout, ws, kPhaseGateUp | kPhaseDown, stream, "hot_experts", sel);
   const int32_t st = launch_gate_up(layout, ws, stream, sel);
   return st ? st : launch_down(layout, ws, stream);
 }
@@ -1450,6 +1300,7 @@ static int32_t launch_down(const fb_moe_expert_layout* layout, const fb_moe_deco
       return check_launch("hot_down");
     return 0;
   }
+  if (layout->inter == 512) return launch_experts_fmt<FB_FMT_IQ4_NL>(layout, ws, kPhaseDown, stream, "hot_down", nullptr);
   static PerDeviceOnce once;
   const cudaError_t attr = per_device_once(once, [] {
     cudaError_t a = opt_in_smem(down_kernel<FB_FMT_IQ4_NL, 512>, down_smem<FB_FMT_IQ4_NL, 512>());

@@ -1,5 +1,7 @@
-// IQ3_S streaming kernels of the decode path (gate/up and down), included by moe_decode.cu inside
-// namespace fb's anonymous namespace.
+// The streaming expert kernel of the decode path (gate/up and down of IQ3_S and of IQ4_NL experts), included
+// by moe_decode.cu inside namespace fb's anonymous namespace. Written for IQ3_S, described for IQ3_S; IQ4_NL
+// rides the same skeleton with its own tile sizes and block arithmetic (ExpertsCfg<FB_FMT_IQ4_NL>,
+// iq4nl_task_terms).
 //
 // One persistent kernel streams the gate, up and down matrices of every routed expert of a layer:
 // first all gate/up tiles (heaviest experts first), then all down tiles, through one three-stage ring
@@ -258,19 +260,48 @@ __device__ __forceinline__ bool draw_task_n(const RingN<S>& r, int* ticket_ctr, 
 // Down tile = 160 output rows (35,200 bytes; a row is two blocks); task 2k + b = block b of rows
 // 32k .. 32k+31; the finishing warp adds each row's two block terms and applies the routing weight.
 // Both kinds carry the activation rows of the pass behind the weights.
-struct Experts3 {
+template <int FMT>
+struct ExpertsCfg;
+template <>
+struct ExpertsCfg<FB_FMT_IQ3_S> {
   static constexpr int kWarps = 24, kTasks = 10, kStages = 3, kInter = 512;
+  static constexpr int kTaskBytes = 110;  // one block of 256 weights
   static constexpr int kGuRows = 16, kGuRowBytes = 1100, kGuPart = kGuRows * kGuRowBytes;  // 17,600
   static constexpr int kDnRows = 160, kDnRowBytes = 220, kDnTile = kDnRows * kDnRowBytes;  // 35,200
+  static constexpr int kAct = FB_ACT_Q8_K;
   static constexpr int kGuAct = q8k_planar_bytes(H), kDnAct = q8k_planar_bytes(kInter);    // 2,784 / 608
   static constexpr int kSlot = 2 * kGuPart + kTT * kGuAct;                                 // 40,768
   static constexpr int kDnTilesPerItem = H / kDnRows;                                      // 16
   static constexpr int kPartialFloats = kStages * kTasks * kTT * 32;
-  static constexpr size_t kSmem = size_t(kGridRepBytes) + kSignArea + size_t(kStages) * kSlot + kPartialFloats * 4 + 128;
+  static constexpr int kTableBytes = kGridRepBytes + kSignArea;  // codebook replica and sign masks
+  static constexpr size_t kSmem = size_t(kTableBytes) + size_t(kStages) * kSlot + kPartialFloats * 4 + 128;
 };
-static_assert(Experts3::kDnTile + kTT * Experts3::kDnAct <= Experts3::kSlot, "a down tile fits a slot");
-static_assert(Experts3::kSlot % 16 == 0 && Experts3::kGuPart % 16 == 0 && Experts3::kDnTile % 16 == 0, "bulk copies");
-static_assert(H % Experts3::kDnRows == 0 && Experts3::kDnRows % 32 == 0, "down tiles");
+// IQ4_NL: the same tile and task shapes with a "block" of eight consecutive 18-byte blocks (256 weights, 144
+// bytes, 16-byte aligned in every row): gate/up tile = 16 + 16 rows of 1440 bytes, down tile = 160 rows of 288.
+// No table: the sixteen levels live in registers.
+template <>
+struct ExpertsCfg<FB_FMT_IQ4_NL> {
+  static constexpr int kWarps = 24, kTasks = 10, kStages = 3, kInter = 512;
+  static constexpr int kTaskBytes = 144;
+  static constexpr int kGuRows = 16, kGuRowBytes = 1440, kGuPart = kGuRows * kGuRowBytes;  // 23,040
+  static constexpr int kDnRows = 160, kDnRowBytes = 288, kDnTile = kDnRows * kDnRowBytes;  // 46,080
+  static constexpr int kAct = FB_ACT_Q8_0;
+  static constexpr int kGuAct = H + H / 8, kDnAct = kInter + kInter / 8;                    // 2,880 / 576
+  static constexpr int kSlot = 2 * kGuPart + kTT * kGuAct;                                 // 51,840
+  static constexpr int kDnTilesPerItem = H / kDnRows;
+  static constexpr int kPartialFloats = kStages * kTasks * kTT * 32;
+  static constexpr int kTableBytes = 0;
+  static constexpr size_t kSmem = size_t(kStages) * kSlot + kPartialFloats * 4 + 128;
+};
+using Experts3 = ExpertsCfg<FB_FMT_IQ3_S>;
+template <int FMT>
+constexpr bool experts_cfg_ok() {
+  using C = ExpertsCfg<FMT>;
+  return C::kDnTile + kTT * C::kDnAct <= C::kSlot && C::kSlot % 16 == 0 && C::kGuPart % 16 == 0 && C::kDnTile % 16 == 0 &&
+         C::kGuAct % 16 == 0 && C::kDnAct % 16 == 0 && H % C::kDnRows == 0 && C::kDnRows % 32 == 0 &&
+         C::kGuRowBytes == C::kTasks * C::kTaskBytes && C::kDnRowBytes == 2 * C::kTaskBytes && C::kTaskBytes % 2 == 0;
+}
+static_assert(experts_cfg_ok<FB_FMT_IQ3_S>() && experts_cfg_ok<FB_FMT_IQ4_NL>(), "tile shapes, bulk-copy sizes");
 // kPhaseSelect: the CTA builds the work list itself from the router logits (SelectArgs) instead of
 // reading the device work list a selection kernel left.
 enum { kPhaseGateUp = 1, kPhaseDown = 2, kPhaseSelect = 4 };
@@ -301,14 +332,60 @@ __device__ __forceinline__ void expert_block_terms(const uint32_t* w, const uint
   }
 }
 
-__global__ void __launch_bounds__((Experts3::kWarps + 1) * 32, 1)
-experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phases, SelectArgs sel) {
-  using C = Experts3;
+// IQ4_NL: one task = eight consecutive blocks (144 bytes at `wp`, 16-byte aligned) of the lane's row against
+// the pass's tokens; blk0 = index of the first of them in the row. Even blocks start on a word (scale in the
+// low half, codes two bytes off: funnel shifts), odd blocks on a half word (scale in the high half, codes
+// aligned). term[t] = sum over the eight blocks, in block order, of isum * (d * d_act).
+__device__ __forceinline__ void iq4nl_task_terms(const uint8_t* wp, const Iq4nlLevels& lv, const uint8_t* act0,
+                                                 int act_bytes, int k, int blk0, int ntp, float (&term)[kTT]) {
+  uint32_t w[36];
+#pragma unroll
+  for (int c = 0; c < 9; ++c) {
+    const uint4 v = reinterpret_cast<const uint4*>(wp)[c];
+    w[4 * c] = v.x;
+    w[4 * c + 1] = v.y;
+    w[4 * c + 2] = v.z;
+    w[4 * c + 3] = v.w;
+  }
+  term[0] = term[1] = 0.0f;
+  const uint8_t* act1 = act0 + (ntp == 2 ? act_bytes : 0);
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    uint32_t q[4];
+    float d;
+    if (b % 2 == 0) {
+      const int base = 9 * b / 2;
+      d = __half2float(__ushort_as_half(static_cast<unsigned short>(w[base] & 0xFFFFu)));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) q[i] = __funnelshift_r(w[base + i], w[base + i + 1], 16);
+    } else {
+      const int base = (18 * b - 2) / 4;
+      d = __half2float(__ushort_as_half(static_cast<unsigned short>(w[base] >> 16)));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) q[i] = w[base + 1 + i];
+    }
+    int wq[8];
+    iq4nl_decode32(lv, q, wq);
+    const int blk = blk0 + b;
+    const int s0 = dot32(wq, reinterpret_cast<const int8_t*>(act0) + 32 * blk);
+    term[0] = fmaf(float(s0), d * reinterpret_cast<const float*>(act0 + k)[blk], term[0]);
+    if (ntp == 2) {
+      const int s1 = dot32(wq, reinterpret_cast<const int8_t*>(act1) + 32 * blk);
+      term[1] = fmaf(float(s1), d * reinterpret_cast<const float*>(act1 + k)[blk], term[1]);
+    }
+  }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__((ExpertsCfg<FMT>::kWarps + 1) * 32, 1)
+experts_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phases, SelectArgs sel) {
+  using C = ExpertsCfg<FMT>;
   constexpr int S = C::kStages;
+  constexpr bool kIq3s = FMT == FB_FMT_IQ3_S;
   extern __shared__ __align__(128) uint8_t smem[];
   uint32_t* gridrep = reinterpret_cast<uint32_t*>(smem);
-  uint32_t* signtab = sign_table_at(smem + kGridRepBytes);
-  uint8_t* stage0 = smem + kGridRepBytes + kSignArea;
+  uint32_t* signtab = kIq3s ? sign_table_at(smem + kGridRepBytes) : nullptr;
+  uint8_t* stage0 = smem + C::kTableBytes;
   float* partials = reinterpret_cast<float*>(stage0 + S * C::kSlot);
   uint64_t* bars = reinterpret_cast<uint64_t*>(partials + C::kPartialFloats);
   __shared__ StageMeta s_meta[S];
@@ -318,7 +395,7 @@ experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phas
   RingN<S> ring{bars, bars + S, s_meta, &s_end};
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  iq3s_half_tables_fill(gridrep, signtab);
+  if constexpr (kIq3s) iq3s_half_tables_fill(gridrep, signtab);
   if (tid == 0) {
     ringn_init(ring);
     for (int i = 1; i < 3 + S; ++i) s_misc[i] = 0;
@@ -339,6 +416,7 @@ experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phas
     n_items = min(max(ws.work->n_items, 0), kMaxPairs);
   }
   const int I = L.inter;  // gate/up takes 512 or 640; the down phase is for 512 (checked on the host)
+  const uint8_t* xq_rows = ws.xq + xq_offset(C::kAct);
   const int gu_tpi = I / C::kGuRows;
   const int n_gu = (phases & kPhaseGateUp) ? n_items * gu_tpi : 0;
   const int n_dn = (phases & kPhaseDown) ? n_items * C::kDnTilesPerItem : 0;
@@ -412,7 +490,7 @@ experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phas
           bulk_g2s(st + C::kGuPart, blob + L.up_offset + off, C::kGuPart, &ring.full[s]);
           for (int t = 0; t < ntp; ++t)
             bulk_g2s(st + 2 * C::kGuPart + t * C::kGuAct,
-                     ws.xq + size_t(s_work.pair_token[pb + tok0 + t]) * FB_XQ_STRIDE, C::kGuAct, &ring.full[s]);
+                     xq_rows + size_t(s_work.pair_token[pb + tok0 + t]) * FB_XQ_STRIDE, C::kGuAct, &ring.full[s]);
         } else {
           mbar_expect_tx(&ring.full[s], uint32_t(C::kDnTile + ntp * C::kDnAct));
           bulk_g2s(st, blob + L.down_offset + size_t(sub) * C::kDnTile, C::kDnTile, &ring.full[s]);
@@ -446,7 +524,8 @@ experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phas
 
   // ---------------- consumers
   const uint32_t* grid_lane = gridrep + lane;
-  const uint32_t sign_base = smem_u32(signtab);
+  const uint32_t sign_base = kIq3s ? smem_u32(signtab) : 0u;
+  const Iq4nlLevels lv = iq4nl_levels();
   const int gu_row_off = (lane >> 4) * C::kGuPart + (lane & 15) * C::kGuRowBytes;
   // Even blocks start on a word boundary (their 27-word stream is 2 bytes off), odd blocks the other
   // way round: two code paths. A warp keeps to one parity, and since warp w issues on scheduler w % 4,
@@ -461,11 +540,14 @@ experts_iq3s_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phas
     const bool down = ring.meta[s].tile != 0;
     uint8_t* st = stage0 + s * C::kSlot;
     // the lane's block, the activation rows, and which of their blocks it meets
-    const uint8_t* blk = down ? st + (32 * k + lane) * C::kDnRowBytes + parity * 110 : st + gu_row_off + task * 110;
+    const uint8_t* blk = down ? st + (32 * k + lane) * C::kDnRowBytes + parity * C::kTaskBytes
+                              : st + gu_row_off + task * C::kTaskBytes;
     const uint8_t* act0 = st + (down ? C::kDnTile : 2 * C::kGuPart);
     const int act_bytes = down ? C::kDnAct : C::kGuAct, act_k = down ? C::kInter : H, ablk = down ? parity : task;
     float term[kTT];
-    if (parity == 0)
+    if constexpr (!kIq3s)
+      iq4nl_task_terms(blk, lv, act0, act_bytes, act_k, 8 * ablk, ntp, term);
+    else if (parity == 0)
       expert_block_terms<true>(reinterpret_cast<const uint32_t*>(blk), grid_lane, sign_base, act0, act_bytes, act_k, ablk,
                                ntp, term);
     else
