@@ -563,16 +563,29 @@ def prefill_section(torch, n_layers=48, tokens=8192, steps=2):
             x = (y * torch.rsqrt(y.pow(2).mean(dim=1, keepdim=True) + 1e-12)).to(torch.bfloat16)
         return x
 
-    step()
-    torch.cuda.synchronize()
+    def timed_stack():
+        step()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            o = step()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps, o
+
+    # both hand-offs between the down projection and the combine are timed; the faster one is reported
+    prefill.set_accumulation(True)
+    ms_fixed, out_fixed = timed_stack()
+    prefill.set_accumulation(False)
+    ms_pairs, out = timed_stack()
     counts = ws.ints(ws.ws.expert_count, EXPERTS)
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(steps):
-        out = step()
-    b.record()
-    torch.cuda.synchronize()
-    ms = a.elapsed_time(b) / steps
+    accumulation = {"fixed_point_atomics_ms": ms_fixed, "per_pair_rows_ms": ms_pairs,
+                    "reported": "fixed_point_atomics" if ms_fixed < ms_pairs else "per_pair_rows"}
+    ms = min(ms_fixed, ms_pairs)
+    if ms_fixed < ms_pairs:
+        out = out_fixed
+        prefill.set_accumulation(True)
     # the two grouped GEMMs of one layer, timed alone
     logits = (x0 @ routers[0].t()).float() + bias
     prefill.moe_route(logits, x0, None, 0, None, None, tokens, ws)
@@ -595,6 +608,7 @@ def prefill_section(torch, n_layers=48, tokens=8192, steps=2):
            "gate_up_ms_layer0": ev[0].elapsed_time(ev[1]), "down_ms_layer0": ev[1].elapsed_time(ev[2]),
            "gate_up_tflops_layer0": flops_layer * 2 / 3 / (ev[0].elapsed_time(ev[1]) * 1e-3) / 1e12,
            "down_tflops_layer0": flops_layer / 3 / (ev[1].elapsed_time(ev[2]) * 1e-3) / 1e12,
+           "down_to_combine": accumulation,
            "busiest_expert_pairs_last_layer": int(counts.max()), "median_expert_pairs_last_layer": int(np.median(counts)),
            "device_status": ws.status(), "finite_output": bool(torch.isfinite(out.float()).all().item()),
            "timed_region_includes": "torch router projection + unit-RMS rescale between layers"}
@@ -609,6 +623,7 @@ def prefill_section(torch, n_layers=48, tokens=8192, steps=2):
                                              n_cpu, pairs, tokens * n_layers / (ms * 1e-3))}
     except Exception as exc:  # the oracle is a checker, never a dependency of the measurement
         res["cpu_baseline"] = {"unavailable": type(exc).__name__}
+    prefill.set_accumulation(False)
     del layers
     torch.cuda.empty_cache()
     return res

@@ -712,6 +712,9 @@ struct DnBars {
 constexpr int kDnStage = kTileA + kTileB;  // 48 KB
 constexpr int kDnRaw = 128 * kRawStrideMax + 16;
 constexpr int kDnSmem = kStagesDN * kDnStage + kDnRaw + sizeof(DnBars) + 1024;
+#ifndef PREFILL_FIXED_DEFAULT
+#define PREFILL_FIXED_DEFAULT 0
+#endif
 constexpr int kDnThreads = 14 * 32;  // warp 0 MMA, warp 1 TMA, 2-9 dequant, 10-13 epilogue
 
 // yp[pair][n] = w_pair * (down_n . h[pair])
@@ -720,7 +723,7 @@ __global__ void __launch_bounds__(kDnThreads, 1)
 grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ expert_blob,
                     const __grid_constant__ CUtensorMap map_h, const int4* __restrict__ units,
                     const int32_t* __restrict__ meta, const float* __restrict__ pair_weight, float* __restrict__ yp,
-                    uint32_t* status) {
+                    const int32_t* __restrict__ pair_token, unsigned long long* __restrict__ y_fixed, uint32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = smem;
@@ -819,9 +822,19 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
         uint32_t r[32];
         tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * 256 + c0), r);
         tmem_ld_wait();
+        if (y_fixed) {  // the reference's accumulation (src/kernels/moe/moe.h:186-192): y_fixed[token] += fixed(w * v)
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c0 + i < un.w) yp[size_t(un.z + c0 + i) * H + n] = pair_weight[un.z + c0 + i] * __uint_as_float(r[i]);
+          for (int i = 0; i < 32; ++i)
+            if (c0 + i < un.w) {
+              const float v = pair_weight[un.z + c0 + i] * __uint_as_float(r[i]);
+              atomicAdd(y_fixed + size_t(pair_token[un.z + c0 + i]) * H + n,
+                        static_cast<unsigned long long>(__float2ll_rn(v * 4294967296.0f)));
+            }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c0 + i < un.w) yp[size_t(un.z + c0 + i) * H + n] = pair_weight[un.z + c0 + i] * __uint_as_float(r[i]);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -843,8 +856,19 @@ __global__ void __launch_bounds__(256) pf_combine_kernel(const int32_t* __restri
                                                          const int32_t* __restrict__ token_pair,
                                                          const float* __restrict__ yp, const float* __restrict__ y_shared,
                                                          const float* __restrict__ inj, float* __restrict__ X,
-                                                         float* __restrict__ y_out) {
+                                                         float* __restrict__ y_out, const long long* __restrict__ y_fixed) {
   const int t = blockIdx.y;
+  if (y_fixed) {  // fixed-point sums: one rounding, the scale is exact (moe_y_fixed_to_float of the reference)
+    const int n = blockIdx.x * 256 + threadIdx.x;
+    float y = static_cast<float>(y_fixed[size_t(t) * H + n]) * (1.0f / 4294967296.0f);
+    if (y_shared) y += y_shared[size_t(t) * H + n];
+    if (y_out) y_out[size_t(t) * H + n] = y;
+    if (X) {
+#pragma unroll
+      for (int s = 0; s < 4; ++s) X[(size_t(t) * 4 + s) * H + n] += inj[t * 4 + s] * y;
+    }
+    return;
+  }
   __shared__ int s_order[kTopK];
   if (threadIdx.x < kTopK) {
     // ascending expert id; entries without a local pair (expert-parallel shards) sort last
@@ -976,6 +1000,18 @@ int32_t fb_moe_prefill_workspace_make(void* base, int32_t capacity, int32_t inte
   return 0;
 }
 
+// 1: the down projection adds into fixed-point per-token sums (the reference's scheme: exact, order-free,
+// no per-pair buffer to write and re-read); 0: it stores fp32 per-pair rows that the combine adds in ascending
+// expert order. Both are deterministic. The sums live in the head of the yp buffer.
+static int g_prefill_fixed = PREFILL_FIXED_DEFAULT;
+int32_t fb_moe_prefill_set_accumulation(int32_t fixed_point) {
+  g_prefill_fixed = fixed_point ? 1 : 0;
+  return 0;
+}
+static cudaError_t clear_fixed(const fb_moe_prefill_workspace* ws, int32_t tokens, cudaStream_t s) {
+  return g_prefill_fixed ? cudaMemsetAsync(ws->yp, 0, size_t(tokens) * H * 8, s) : cudaSuccess;
+}
+
 int32_t fb_moe_route(const float* router_logits, int32_t logits_stride, const void* x, const uint8_t* const* expert_blob,
                      int32_t layer, const uint32_t* seq, void* control, int32_t tokens,
                      const fb_moe_prefill_workspace* ws, void* stream) {
@@ -987,6 +1023,7 @@ int32_t fb_moe_route(const float* router_logits, int32_t logits_stride, const vo
   if (!router_logits || logits_stride < kExperts || !pf_ws_ok(ws, tokens)) return invalid("route: bad arguments");
   cudaStream_t s = as_stream(stream);
   cudaError_t e = cudaMemsetAsync(ws->expert_count, 0, kExperts * 4, s);
+  if (e == cudaSuccess) e = clear_fixed(ws, tokens, s);
   if (e != cudaSuccess) return check_launch("route: memset");
   pf_topk_kernel<<<(tokens + 7) / 8, 256, 0, s>>>(router_logits, logits_stride, tokens, ws->topk_expert, ws->topk_weight,
                                                   ws->expert_count);
@@ -1029,6 +1066,7 @@ static int32_t route_ep_impl(const int32_t* topk_expert, const float* topk_weigh
                              const int32_t* share, int32_t rows, const fb_moe_prefill_workspace* ws, void* stream) {
   cudaStream_t s = as_stream(stream);
   cudaError_t e = cudaMemsetAsync(ws->expert_count, 0, kExperts * 4, s);
+  if (e == cudaSuccess) e = clear_fixed(ws, rows, s);
   if (e != cudaSuccess) return check_launch("route_ep: memset");
   const int n = rows * kTopK;
   pf_import_kernel<<<(n + 255) / 256, 256, 0, s>>>(topk_expert, topk_weight, expert_lo, expert_hi, share, n,
@@ -1109,12 +1147,13 @@ int32_t fb_moe_grouped_down(const fb_moe_expert_layout* layout, const uint8_t* c
   }
   const int grid = sm_count();
   const auto* un = static_cast<const int4*>(ws->units_down);
+  unsigned long long* yf = g_prefill_fixed ? reinterpret_cast<unsigned long long*>(ws->yp) : nullptr;
   if (layout->down_format == FB_FMT_IQ3_S)
     grouped_down_kernel<FB_FMT_IQ3_S><<<grid, kDnThreads, kDnSmem, as_stream(stream)>>>(
-        *layout, expert_blob, map_h, un, ws->meta, ws->pair_weight, ws->yp, ws->status);
+        *layout, expert_blob, map_h, un, ws->meta, ws->pair_weight, ws->yp, ws->pair_token, yf, ws->status);
   else
     grouped_down_kernel<FB_FMT_IQ4_NL><<<grid, kDnThreads, kDnSmem, as_stream(stream)>>>(
-        *layout, expert_blob, map_h, un, ws->meta, ws->pair_weight, ws->yp, ws->status);
+        *layout, expert_blob, map_h, un, ws->meta, ws->pair_weight, ws->yp, ws->pair_token, yf, ws->status);
   return check_launch("grouped_down");
 }
 
@@ -1129,8 +1168,9 @@ int32_t fb_moe_prefill_combine(const fb_moe_prefill_workspace* ws, const float* 
   if (control) return invalid("prefill_combine: no CPU expert tier exists behind these kernels; control must be NULL");
   if (ablate_direction) return invalid("prefill_combine: the rank-1 ablation is not built for the prefill path");
   if (!pf_ws_ok(ws, tokens) || (X && !inj) || (!X && !y_out)) return invalid("prefill_combine: bad arguments");
-  pf_combine_kernel<<<dim3(H / 256, tokens), 256, 0, as_stream(stream)>>>(ws->topk_expert, ws->token_pair, ws->yp,
-                                                                        y_shared, inj, X, y_out);
+  pf_combine_kernel<<<dim3(H / 256, tokens), 256, 0, as_stream(stream)>>>(
+      ws->topk_expert, ws->token_pair, ws->yp, y_shared, inj, X, y_out,
+      g_prefill_fixed ? reinterpret_cast<const long long*>(ws->yp) : nullptr);
   return check_launch("prefill_combine");
 }
 

@@ -43,6 +43,13 @@ class PrefillWorkspace:
         return self._view(self.ws.h, 2 * pairs * self.inter).view(torch.int16).cpu().numpy().view("uint16").reshape(pairs, self.inter)
 
 
+def set_accumulation(fixed_point):
+    """How the down projection hands results to the combine: True = 64-bit fixed-point per-token sums with
+    integer atomics (the reference's scheme, moe.h:186-192), False = fp32 rows per pair added in ascending
+    expert order. Process-wide; call it between layers, not inside one."""
+    L.check(L.load().fb_moe_prefill_set_accumulation(1 if fixed_point else 0), "prefill_set_accumulation")
+
+
 def moe_route(router_logits, x, expert_blob, layer, seq, control, tokens, ws, logits_stride=None):
     stride = logits_stride or router_logits.shape[-1]
     L.check(L.load().fb_moe_route(_ptr(router_logits), stride, _ptr(x), _ptr(expert_blob), layer, _ptr(seq), control,

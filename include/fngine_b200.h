@@ -263,6 +263,11 @@ int32_t fb_moe_route_ep(const int32_t* topk_expert, const float* topk_weight, in
                         int32_t rows, const fb_moe_prefill_workspace* ws, void* stream);
 int32_t fb_ep_scatter_sum(const float* recv, const int32_t* row_of, int32_t n_ranks, int32_t tokens, float* y,
                           void* stream);
+/* How fb_moe_grouped_down hands its results to fb_moe_prefill_combine. fixed_point != 0: the reference's scheme
+ * (src/kernels/moe/moe.h:186-192): every addend w * (down . h) is rounded once to 2^-32 fixed point and added to
+ * a 64-bit per-token sum with integer atomics: exact, independent of the order, no per-pair buffer. 0: fp32 rows
+ * per pair, added by the combine in ascending expert order. Process-wide; set it before a layer's route call. */
+int32_t fb_moe_prefill_set_accumulation(int32_t fixed_point);
 /* fb_moe_route_ep for a placement that is not contiguous and may hold several copies of a hot expert
  * (the cross-GPU counterpart of the reference's routing-EMA expert placement, src/model/routing_counts.h:
  * there the hottest experts move to the GPU, here they are spread, and the very hottest copied, so that the

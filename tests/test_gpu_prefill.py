@@ -122,6 +122,32 @@ def test_prefill_layer_small_batches(T):
     print("prefill IQ3_S T=%d: max rel L2 down %.2e, end to end %.2e" % ((T,) + err))
 
 
+@pytest.mark.parametrize("T", [3, 300])
+def test_prefill_layer_with_fixed_point_accumulation(T):
+    """The reference's hand-off between the down projection and the combine (moe.h:186-192): every addend rounded
+    once to 2^-32 fixed point and added with 64-bit integer atomics. Same bars; bitwise repeatable (the sum is exact
+    whatever the order); within 1e-6 of the per-pair path."""
+    torch = _torch()
+    from fngine_b200 import moe, prefill
+    logits = (synth.normal(61 + T, T * 512) * 1.5).astype(np.float32).reshape(T, 512)
+    prefill.set_accumulation(True)
+    try:
+        err = check_layer(IQ3_S, IQ3_S, 512, T, logits)
+        layer = moe.synth_layer(IQ3_S, IQ3_S, 512, 512, 90)
+        ws = prefill.PrefillWorkspace(T, 512)
+        xd = torch.from_numpy(synth.to_bf16_bits(synth.activations(62, T)).view(np.int16)).cuda().view(torch.bfloat16)
+        lg = torch.from_numpy(np.concatenate([logits, np.zeros((T, 1), np.float32)], axis=1)).cuda()
+        y1 = run_prefill(torch, layer, ws, lg, xd, T).cpu().numpy()
+        y2 = run_prefill(torch, layer, ws, lg, xd, T).cpu().numpy()
+        assert np.array_equal(y1.view(np.uint32), y2.view(np.uint32))
+        prefill.set_accumulation(False)
+        y3 = run_prefill(torch, layer, ws, lg, xd, T).cpu().numpy()
+        assert max(rel_l2(y1[t], y3[t]) for t in range(T)) <= 1e-6
+    finally:
+        prefill.set_accumulation(False)
+    print("prefill fixed-point accumulation T=%d: max rel L2 down %.2e, end to end %.2e" % ((T,) + err))
+
+
 @pytest.mark.parametrize("fg,fd,inter", [(IQ4_NL, IQ4_NL, 512), (IQ3_S, IQ4_NL, 640)])
 def test_prefill_layer_other_formats(fg, fd, inter):
     T = 40
