@@ -459,12 +459,13 @@ __device__ __forceinline__ void warp_topk10_pruned(LoadF load_logit, uint2* scra
     ck = c.x;
     cid = c.y;
   }
-  int rank = 0;
-#pragma unroll
-  for (int j = 0; j < 32; ++j) {
+  int rank = 0;  // (only the real candidates take a turn: a lone warp pays a few cycles per instruction)
+#pragma unroll 4
+  for (int j = 0; j < total; ++j) {
     const uint32_t ok = __shfl_sync(0xffffffffu, ck, j), oi = __shfl_sync(0xffffffffu, cid, j);
     rank += (ok > ck || (ok == ck && oi < cid)) ? 1 : 0;
   }
+  if (lane >= total) rank = 32;
   __syncwarp();  // every lane holds its candidate: the scratch entries can carry the winners' logits now
   float* vals = reinterpret_cast<float*>(scratch);
   if (rank < FB_TOPK) {

@@ -257,6 +257,104 @@ __device__ __forceinline__ void select_block(TopkF topk, const int32_t* slot_of,
   if (warp < T) topk(warp, s_cand[warp], s_id[warp], s_w[warp]);
   __syncthreads();
   const int np = T * kTopK;
+  if (np <= 32) {
+    // Up to three tokens: the pairs fit one warp, which builds the whole list through shuffles (lane = pair),
+    // two barriers in all instead of five. Same list as the general path below.
+    if (warp == 0) {
+      const bool pv = lane < np;
+      const int t = lane / kTopK, k = lane - t * kTopK;
+      const int e = pv ? s_id[t][k] : 0;
+      int slot = !pv ? -1 : slot_of ? slot_of[e] : e;
+      if (slot >= kExperts) slot = -1;
+      const float wt = pv ? s_w[t][k] : 0.0f;
+      const int key = slot >= 0 ? slot * kMaxTok + t : 0x7fffffff;  // pairs not held here sort last
+      // (a lone warp runs at a few cycles per instruction: the loops below take np turns, not 32, and a single
+      // token, whose ten pairs are ten different experts, needs only the first)
+      int idx = 0, trank = 0, cnt = 0;
+#pragma unroll 2
+      for (int j = 0; j < np; ++j) {
+        const int kj = __shfl_sync(0xffffffffu, key, j);
+        const bool same = kj != 0x7fffffff && (kj / kMaxTok) == slot;
+        idx += kj < key ? 1 : 0;
+        cnt += same ? 1 : 0;
+        trank += same && kj < key ? 1 : 0;
+      }
+      const bool hot = slot >= 0, first = hot && trank == 0;
+      const uint32_t hot_m = __ballot_sync(0xffffffffu, hot), first_m = __ballot_sync(0xffffffffu, first);
+      const int n_pairs = __popc(hot_m), n_items = __popc(first_m);
+      int item = idx, rank = idx;  // one token: every held pair is an item of one token, in key order
+      if (T > 1) {
+        item = 0;  // distinct slots below this pair's slot = first pairs with a smaller key
+#pragma unroll 2
+        for (int j = 0; j < np; ++j) {
+          const int kj = __shfl_sync(0xffffffffu, key, j);
+          item += ((first_m >> j) & 1u) && (kj / kMaxTok) < slot ? 1 : 0;
+        }
+        rank = 0;  // visiting order among the items: more tokens first, then lower item index
+#pragma unroll 2
+        for (int j = 0; j < np; ++j) {
+          const int cj = __shfl_sync(0xffffffffu, cnt, j), ij = __shfl_sync(0xffffffffu, item, j);
+          rank += ((first_m >> j) & 1u) && (cj > cnt || (cj == cnt && ij < item)) ? 1 : 0;
+        }
+      }
+      if (hot) {
+        wc.pair_token[idx] = t;
+        wc.pair_weight[idx] = wt;
+        if (publish) {
+          work->pair_token[idx] = t;
+          work->pair_weight[idx] = wt;
+        }
+      }
+      if (first) {
+        wc.slot[item] = slot;
+        wc.pair_begin[item] = idx;
+        wc.order[rank] = item;
+        if (publish) {
+          work->item_slot[item] = slot;
+          work->item_pair_begin[item] = idx;
+          ws.sched[kSchedOrderBase + rank] = item;
+        }
+      }
+      if (lane == 0) {
+        wc.pair_begin[n_items] = n_pairs;
+        wc.n_items = n_items;
+      }
+      if (pv && counts) atomicAdd(&counts[e], 1u);
+      if (publish) {
+        if (pv) {
+          work->topk_expert[t][k] = e;
+          work->topk_weight[t][k] = wt;
+        }
+        // a token's held pairs in pair order (= slot order)
+        int prank = idx, nh = n_pairs;
+        if (T > 1) {
+          prank = nh = 0;
+#pragma unroll 2
+          for (int j = 0; j < np; ++j) {
+            const int kj = __shfl_sync(0xffffffffu, key, j), ixj = __shfl_sync(0xffffffffu, idx, j);
+            const bool mine = j / kTopK == t && kj != 0x7fffffff;
+            nh += mine ? 1 : 0;
+            prank += mine && ixj < idx ? 1 : 0;
+          }
+        }
+        if (hot) work->token_pairs[t][prank] = idx;
+        if (pv && k == 0) {
+          work->token_pair_count[t] = nh;
+          work->token_cold_count[t] = kTopK - nh;
+        }
+        if (lane == 0) {
+          work->item_pair_begin[n_items] = n_pairs;
+          work->n_items = n_items;
+          work->n_pairs = n_pairs;
+          work->n_cold = np - n_pairs;
+          work->tokens = T;
+          if (np - n_pairs && !remote_ok) atomicMax(ws.status, uint32_t(FB_STATUS_BAD_WORK));
+        }
+      }
+    }
+    __syncthreads();
+    return;
+  }
   const bool valid = tid < np;
   const int pt = tid / kTopK, pk = tid - pt * kTopK;
   int my_e = 0, my_slot = -1;
@@ -805,15 +903,23 @@ __device__ __forceinline__ void quantize_item_h(const fb_moe_decode_workspace& w
     const float* h = ws.h + size_t(p) * I;
     uint8_t* out = ws.hq + size_t(p) * FB_HQ_STRIDE;
     if (down_act == FB_ACT_Q8_K) {
-      for (int b = 0; b < I / 256; ++b) {
-        float v[8];
-        const float4 a = __ldcg(reinterpret_cast<const float4*>(h + 256 * b + 8 * lane));
-        const float4 c = __ldcg(reinterpret_cast<const float4*>(h + 256 * b + 8 * lane) + 1);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-        v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
-        int q[8], ps;
-        const float d = q8k_block_warp(v, q, ps);
-        store_q8k_block_planar(out, I, b, q, ps, d);
+      for (int b0 = 0; b0 < I / 256; b0 += 2) {  // two blocks' loads in flight: the finishing warp waits on this chain
+        const int nb = min(2, I / 256 - b0);
+        float4 a[2], c[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          if (i < nb) {
+            a[i] = __ldcg(reinterpret_cast<const float4*>(h + 256 * (b0 + i) + 8 * lane));
+            c[i] = __ldcg(reinterpret_cast<const float4*>(h + 256 * (b0 + i) + 8 * lane) + 1);
+          }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          if (i < nb) {
+            float v[8] = {a[i].x, a[i].y, a[i].z, a[i].w, c[i].x, c[i].y, c[i].z, c[i].w};
+            int q[8], ps;
+            const float d = q8k_block_warp(v, q, ps);
+            store_q8k_block_planar(out, I, b0 + i, q, ps, d);
+          }
       }
     } else {
       float* scales = reinterpret_cast<float*>(out + I);

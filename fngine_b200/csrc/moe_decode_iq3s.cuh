@@ -239,8 +239,9 @@ __device__ __forceinline__ bool draw_task_n(const RingN<S>& r, int* ticket_ctr, 
       atomicMax(status, uint32_t(FB_STATUS_PIPELINE_TIMEOUT));
       return false;
     }
-    // the entry's data arrives a microsecond or more after its number is written: a long nap costs nothing
-    __nanosleep(800);
+    // (the producer is behind only at the start of a phase; the nap is short because at one to three tokens this
+    // wait sits on the layer's critical path)
+    __nanosleep(200);
   }
   const uint32_t parity = (seq / S) & 1;
   for (uint32_t i = 0; i < (1u << 21); ++i) {  // bounded: each try takes at most about a microsecond
@@ -461,7 +462,7 @@ experts_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phases, S
       next2 = first_ticket + atomicAdd(counter, 1);
       const bool down = tile >= n_gu;
       const int tl = down ? tile - n_gu : tile;
-      const int pos = down ? tl / C::kDnTilesPerItem : tl / gu_tpi;
+      const int pos = down ? tl / C::kDnTilesPerItem : I == 512 ? tl >> 5 : tl / (640 / C::kGuRows);  // (no run-time division)
       const int sub = down ? tl - pos * C::kDnTilesPerItem : tl - pos * gu_tpi;
       const int item = s_work.order[pos];
       const int pb = s_work.pair_begin[item];
