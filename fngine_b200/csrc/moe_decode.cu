@@ -226,19 +226,19 @@ __device__ __forceinline__ void work_cache_fill(const fb_moe_decode_workspace& w
 // (complete when the call returns) and, with `publish`, to the device work list as well; `reset` clears
 // the tile and item counters of the streaming kernels (only where no such kernel can be running). The
 // list is a function of the logits alone: every block that runs this on the same logits builds the same
-// list. Every CTA of a decode step waits for this, so it is kept a short chain of five barriers:
-// token masks per physical slot (shared-memory atomics), a scan over the 512 slots (thread = slot), the
-// pairs placed from the scan, and the items ranked by comparing each with all the others (SPLIT threads
-// per item, 16-byte loads).
+// list. Every CTA of a decode step waits for this, so it is kept a short chain of six barriers: token
+// masks per physical slot (shared-memory atomics), a scan over the 512 slots (thread = slot), the pairs
+// placed from the scan, and the items ranked by a counting sort on their token counts (warp votes). Few
+// warps do this work and a warp on its own retires an instruction every few cycles: what counts here is the
+// number of instructions on the longest chain, not the arithmetic. (Up to three tokens: one warp, shuffles.)
 //   items  = distinct selected experts held on this rank, in physical-slot order
 //   pairs  = (item, token), tokens ascending inside an item
 //   order  = items by token count, most first, ties by item index (the streaming kernels' visiting order)
-template <int SPLIT, class TopkF>
+template <class TopkF>
 __device__ __forceinline__ void select_block(TopkF topk, const int32_t* slot_of, int T,
                                              const fb_moe_decode_workspace& ws, uint32_t* counts, bool remote_ok,
                                              bool publish, bool reset, WorkCache& wc) {
-  static_assert(SPLIT == 2 || SPLIT == 4, "threads per item: adjacent lanes of one warp");
-  static_assert(kMaxPairs % (4 * SPLIT) == 0, "each thread ranks against whole 16-byte groups of items");
+  static_assert(kMaxPairs % 32 == 0 && kMaxTok % 4 == 0, "the ranking below votes by whole warps and reads 16-byte groups");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   __shared__ int s_id[kMaxTok][kTopK];
   __shared__ float s_w[kMaxTok][kTopK];
@@ -247,6 +247,7 @@ __device__ __forceinline__ void select_block(TopkF topk, const int32_t* slot_of,
   __shared__ int s_begin[kExperts];     // physical slot -> first pair of its item
   __shared__ int s_scan[2][kExperts / 32];
   __shared__ __align__(16) int s_item_cnt[kMaxPairs];
+  __shared__ __align__(16) int s_hist[kMaxPairs / 32][kMaxTok];  // [warp of items][token count - 1] -> items
   __shared__ uint2 s_cand[kMaxTok][32];
   fb_moe_decode_work* work = ws.work;
   if (tid < kExperts) s_tok[tid] = 0;
@@ -434,30 +435,40 @@ __device__ __forceinline__ void select_block(TopkF topk, const int32_t* slot_of,
       work->topk_weight[pt][pk] = s_w[pt][pk];
     }
   }
-  {  // rank of item p = items with more tokens + items with as many tokens and a lower index
-    constexpr int kShare = kMaxPairs / SPLIT;  // items a thread compares its item with
-    const int p = tid / SPLIT, sub = tid - p * SPLIT;
-    const bool live = p < n_items;
-    const int mine = live ? s_item_cnt[p] : 0;
-    int rank = 0;
-    if (live) {
+  // Visiting order: rank of an item = items with more tokens + items with as many tokens and a lower index.
+  // A counting sort on the token count (1..16): every warp of items votes its histogram, then an item adds the
+  // counts above its own, the earlier warps' share of its own count, and its place among its warp's equals.
+  {
+    const bool live = tid < n_items;
+    const int mine = live ? s_item_cnt[tid] : 0;
+    uint32_t equals = 0;
+    if (tid < kMaxPairs) {  // (whole warps: kMaxPairs is a multiple of 32)
 #pragma unroll
-      for (int g = 0; g < kShare / 4; ++g) {
-        const int j0 = sub * kShare + 4 * g;
-        if (j0 < n_items) {
-          const int4 v = *reinterpret_cast<const int4*>(&s_item_cnt[j0]);
-          const int cj[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            rank += (j0 + i < n_items && (cj[i] > mine || (cj[i] == mine && j0 + i < p))) ? 1 : 0;
-        }
+      for (int cnt = 1; cnt <= kMaxTok; ++cnt) {
+        const uint32_t b = __ballot_sync(0xffffffffu, mine == cnt);
+        equals = mine == cnt ? b : equals;
+        if (lane == cnt - 1) s_hist[warp][cnt - 1] = __popc(b);
       }
     }
+    __syncthreads();
+    if (live) {
+      int rank = __popc(equals & ((1u << lane) - 1u));
 #pragma unroll
-    for (int o = 1; o < SPLIT; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);  // (whole warps)
-    if (live && sub == 0) {
-      wc.order[rank] = p;
-      if (publish) ws.sched[kSchedOrderBase + rank] = p;
+      for (int wv = 0; wv < kMaxPairs / 32; ++wv) {
+        const int4* hp = reinterpret_cast<const int4*>(s_hist[wv]);
+#pragma unroll
+        for (int g = 0; g < kMaxTok / 4; ++g) {
+          const int4 hv = hp[g];
+          const int hc[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int cnt = 4 * g + i + 1;
+            rank += (cnt > mine || (cnt == mine && wv < warp)) ? hc[i] : 0;
+          }
+        }
+      }
+      wc.order[rank] = tid;
+      if (publish) ws.sched[kSchedOrderBase + rank] = tid;
     }
   }
   __syncthreads();
@@ -513,7 +524,7 @@ __global__ void __launch_bounds__(512) select_kernel(const float* __restrict__ l
     return;
   }
   __shared__ WorkCache s_work;  // the streaming kernels of this path read the device work list instead
-  select_block<2>(
+  select_block(
       [&](int t, uint2* scratch, int* ids, float* wts) {
         warp_topk10_pruned([&](int e) { return logits[size_t(t) * logits_stride + e]; }, scratch, ids, wts);
       },
@@ -526,7 +537,7 @@ __global__ void __launch_bounds__(512) select_only_kernel(SelectArgs sel, fb_moe
   pdl_launch_dependents();
   pdl_wait_prior();
   __shared__ WorkCache s_work;
-  select_block<2>(
+  select_block(
       [&](int t, uint2* scratch, int* ids, float* wts) {
         warp_topk10_pruned([&](int e) { return __ldcg(sel.logits + size_t(t) * sel.stride + e); }, scratch, ids, wts);
       },

@@ -407,7 +407,7 @@ experts_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phases, S
 
   int n_items;
   if (phases & kPhaseSelect) {
-    select_block<4>(
+    select_block(
         [&](int t, uint2* scratch, int* ids, float* wts) {
           warp_topk10_pruned([&](int e) { return __ldcg(sel.logits + size_t(t) * sel.stride + e); }, scratch, ids, wts);
         },
