@@ -77,8 +77,13 @@ fb_linear_epilogue to_fb(const LinearEpilogueParams& e) {
 // ---------------------------------------------------------------------------------- formats
 int64_t moe_row_bytes(MoeFormat f, int32_t k) { return fb_moe_row_bytes(static_cast<int32_t>(f), k); }
 
-bool moe_gate_up_format_supported(MoeFormat f) { return f == MoeFormat::IQ3_S || f == MoeFormat::IQ4_NL; }
-bool moe_down_format_supported(MoeFormat f) { return f == MoeFormat::IQ4_NL; }
+// (decode width: all of the reference's formats; the prefill kernels exist for IQ3_S and IQ4_NL only and return
+// cudaErrorInvalidValue for a layer in another format)
+bool moe_gate_up_format_supported(MoeFormat f) {
+  return f == MoeFormat::IQ2_S || f == MoeFormat::IQ3_XXS || f == MoeFormat::IQ3_S || f == MoeFormat::IQ4_XS ||
+         f == MoeFormat::IQ4_NL;
+}
+bool moe_down_format_supported(MoeFormat f) { return f == MoeFormat::IQ4_NL || f == MoeFormat::Q2_0; }
 
 MoeExpertLayout make_moe_expert_layout(const uint8_t* slots, int64_t blob_stride, MoeFormat gate_up_format,
                                        MoeFormat down_format) {

@@ -177,6 +177,38 @@ def test_router_and_select(tokens, bf16):
     assert ws.status() == 0
 
 
+@pytest.mark.parametrize("tokens", [1, 3, 4, 16])
+def test_fused_route_agrees_with_the_separate_router(tokens):
+    """The fused layer call projects the router in eight K slices met through distributed shared memory, the
+    separate fb_router_logits sums 80 values per lane and then the lanes: the two agree to fp32 rounding (stated
+    tolerance: 2e-6 of the logits' rms), and on these seeded inputs they select the same experts with weights
+    equal to 1e-6. Row 512 (the shared-expert gate) is produced by the separate call only."""
+    torch = _torch()
+    from fngine_b200 import moe
+    wr = torch.from_numpy(synth.router_weights(111, rows=513).view(np.int16)).cuda().view(torch.bfloat16)
+    xd = torch.from_numpy(synth.activations(212 + tokens, tokens)).cuda()
+    layer = moe.synth_layer(IQ3_S, IQ3_S, 512, 512, 3)
+    ws = moe.DecodeWorkspace(layer)
+    moe.router_logits(wr, xd, ws.logits)
+    moe.moe_select_publish(ws.logits, xd, None, 0, None, None, tokens, ws)
+    torch.cuda.synchronize()
+    sep = ws.logits.cpu().numpy()[:tokens * 513].reshape(tokens, 513).copy()
+    w1 = ws.work()
+    ids1 = np.array([list(w1.topk_expert[t]) for t in range(tokens)])
+    wt1 = np.array([list(w1.topk_weight[t]) for t in range(tokens)])
+    y = torch.empty(tokens, H, dtype=torch.float32, device="cuda")
+    moe.moe_layer_decode(wr, layer, xd, ws, y)
+    torch.cuda.synchronize()
+    fused = ws.logits.cpu().numpy()[:tokens * 513].reshape(tokens, 513)
+    w2 = ws.work()
+    ids2 = np.array([list(w2.topk_expert[t]) for t in range(tokens)])
+    wt2 = np.array([list(w2.topk_weight[t]) for t in range(tokens)])
+    rms = float(np.sqrt(np.mean(sep[:, :512] ** 2)))
+    assert np.max(np.abs(fused[:, :512] - sep[:, :512])) <= 2e-6 * rms
+    assert np.array_equal(ids1, ids2) and np.max(np.abs(wt1 - wt2)) <= 1e-6
+    assert ws.status() == 0
+
+
 def test_select_ties_nan_and_slot_map():
     torch = _torch()
     from fngine_b200 import moe
