@@ -509,6 +509,8 @@ experts_kernel(fb_moe_expert_layout L, fb_moe_decode_workspace ws, int phases, S
               __nanosleep(200);
             }
             ready = true;
+            // the rows were written by another SM's ordinary stores and are read by bulk copies
+            asm volatile("fence.proxy.async.global;" ::: "memory");
           }
           for (int t = 0; t < ntp; ++t)
             bulk_g2s(st + C::kDnTile + t * C::kDnAct, ws.hq + size_t(pb + tok0 + t) * FB_HQ_STRIDE, C::kDnAct,
