@@ -1635,10 +1635,19 @@ int32_t fb_moe_layer_decode_host(const void* router_w_bf16, const fb_moe_expert_
   const size_t xb = size_t(tokens) * H * (x_dtype == FB_DT_BF16 ? 2 : 4);
   cudaError_t e = cudaMemcpyAsync(x_dev, x_host, xb, cudaMemcpyHostToDevice, as_stream(stream));
   if (e != cudaSuccess) return check_launch("layer_decode_host: copy in");
-  int32_t st = fb_moe_layer_decode(router_w_bf16, layout, x_dev, x_dtype, tokens, ws, logits_scratch, y_dev, stream);
+  // A pinned result buffer is written by the combine kernel itself (page-locked host memory has a device address
+  // under unified addressing): one copy operation and its launch less per call. Pageable memory takes the copy.
+  cudaPointerAttributes pa{};
+  const bool direct = cudaPointerGetAttributes(&pa, y_host) == cudaSuccess && pa.type == cudaMemoryTypeHost &&
+                      pa.devicePointer != nullptr;
+  if (!direct) (void)cudaGetLastError();  // (an unregistered pointer reports an error on older drivers: not ours to keep)
+  float* y_target = direct ? static_cast<float*>(pa.devicePointer) : y_dev;
+  int32_t st = fb_moe_layer_decode(router_w_bf16, layout, x_dev, x_dtype, tokens, ws, logits_scratch, y_target, stream);
   if (st) return st;
-  e = cudaMemcpyAsync(y_host, y_dev, size_t(tokens) * H * 4, cudaMemcpyDeviceToHost, as_stream(stream));
-  if (e != cudaSuccess) return check_launch("layer_decode_host: copy out");
+  if (!direct) {
+    e = cudaMemcpyAsync(y_host, y_dev, size_t(tokens) * H * 4, cudaMemcpyDeviceToHost, as_stream(stream));
+    if (e != cudaSuccess) return check_launch("layer_decode_host: copy out");
+  }
   e = cudaStreamSynchronize(as_stream(stream));
   if (e != cudaSuccess) {
     set_error("layer_decode_host: %s", cudaGetErrorString(e));

@@ -521,6 +521,10 @@ def test_host_entry_point_matches_device_path():
     moe.moe_layer_decode(wr, layer, xh.cuda(), ws, y2)
     torch.cuda.synchronize()
     assert np.array_equal(yh.numpy().view(np.uint32), y2.cpu().numpy().view(np.uint32))
+    # a pageable result buffer takes the copy instead of the direct write: same bits
+    yp = torch.empty(tokens, H, dtype=torch.float32)
+    moe.moe_layer_decode_host(wr, layer, xh, ws, xd, yd, yp)
+    assert np.array_equal(yp.numpy().view(np.uint32), y2.cpu().numpy().view(np.uint32))
 
 
 @pytest.mark.parametrize("world", [2, 8])
