@@ -864,7 +864,8 @@ def ep_prefill_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_to
     import torch
     import torch.distributed as dist
     from fngine_b200 import placement, prefill, synth
-    from fngine_b200.ep_prefill import EpPrefillShard, ep_prefill_layer, topk
+    from fngine_b200.ep_prefill import (EpPrefillScratch, EpPrefillShard, comm_pointer, ep_prefill_layer,
+                                        ep_prefill_layer_c, topk)
     FMT, INTER = 21, 512
     g = torch.Generator(device="cuda").manual_seed(1234)
     routers = [(torch.randn(EXPERTS, HIDDEN, generator=g, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(n_layers)]
@@ -877,6 +878,7 @@ def ep_prefill_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_to
     hist = torch.zeros(n_layers, EXPERTS, dtype=torch.int64, device="cuda")
     shards = []
     combine = "all_to_all"
+    c_call = None  # (communicator, scratch, y buffer): the layer through fb_ep_prefill_layer instead of the mirror
 
     def step(record=False):
         x = x_local
@@ -884,7 +886,10 @@ def ep_prefill_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_to
             logits = (x @ routers[l].t()).float() + bias
             if record:
                 hist[l] += torch.bincount(topk(logits)[0].reshape(-1).long(), minlength=EXPERTS)
-            y, st = ep_prefill_layer(logits, x, shards[l], ws, combine=combine)
+            if c_call is not None:
+                y, st = ep_prefill_layer_c(logits, x, shards[l], ws, c_call[1], c_call[2], c_call[0]), None
+            else:
+                y, st = ep_prefill_layer(logits, x, shards[l], ws, combine=combine)
             if record:
                 for k in totals:
                     totals[k] += st[k]
@@ -909,6 +914,7 @@ def ep_prefill_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_to
     shards = [EpPrefillShard(rank, world, 5000 + l, FMT, INTER) for l in range(n_layers)]
     step(record=True)
     dist.all_reduce(hist)
+    step()
     ms_contiguous, _ = timed()
     load = hist.cpu().numpy().astype(np.float64)
     contiguous = placement.Placement.contiguous(world)
@@ -943,6 +949,22 @@ def ep_prefill_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_to
         ms, out = ms_rs, out_rs
     else:
         ms = ms_a2a
+    # 4. the same layers through the one C entry point (fb_ep_prefill_layer) on torch's communicator
+    comm = comm_pointer()
+    y_c = torch.empty(tl, HIDDEN, dtype=torch.float32, device="cuda")
+    ms_c, c_equal = {}, None
+    for comb in ("all_to_all", "reduce_scatter"):
+        c_call = (comm, EpPrefillScratch(tl, world, comb), y_c)
+        if comb == "all_to_all":
+            c_equal = bool(torch.equal(ep_prefill_layer_c(logits0, x_local, shards[0], ws, c_call[1], y_c, comm), y_l0))
+        step()
+        ms_c[comb], out_c = timed()
+        if ms_c[comb] < ms:
+            ms, out = ms_c[comb], out_c
+    c_call = None
+    eq = torch.tensor([float(c_equal)], device="cuda")
+    dist.all_reduce(eq, op=dist.ReduceOp.MIN)
+    c_equal = bool(eq.item())
     agg = torch.tensor([float(totals[k]) for k in ("rows_received", "dispatch_bytes", "combine_bytes")], device="cuda")
     mx = agg.clone()
     dist.all_reduce(agg)
@@ -981,6 +1003,10 @@ def ep_prefill_section(rank, world, n_layers=48, tokens=8192, steps=2, parity_to
             "combine": {"all_to_all_plus_owner_sum_ms": ms_a2a, "reduce_scatter_ms": ms_rs,
                         "reported": "reduce_scatter" if ms_rs <= ms_a2a else "all_to_all",
                         "layer0_rel_l2_between_the_two": rs_vs_a2a},
+            "c_entry_point": {"what": "the same stack with every layer enqueued by one fb_ep_prefill_layer call on the "
+                                      "process group's ncclComm_t (all collectives on the compute stream)",
+                              "all_to_all_plus_owner_sum_ms": ms_c["all_to_all"], "reduce_scatter_ms": ms_c["reduce_scatter"],
+                              "layer0_bit_equal_to_the_python_mirror": c_equal},
             "roofline": {"bound": "tensor", "achieved": tfl / world, "peak": bf16_peak, "unit": "TFLOP/s per GPU",
                          "frac": tfl / world / bf16_peak,
                          "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)"},

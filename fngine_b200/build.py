@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfngine_b200.so")
-SOURCES = ["api.cu", "probes.cu", "moe_decode.cu", "linear_fp8.cu", "moe_prefill.cu"]
+SOURCES = ["api.cu", "probes.cu", "moe_decode.cu", "linear_fp8.cu", "moe_prefill.cu", "ep_prefill.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
@@ -45,7 +45,7 @@ def build(force=False, verbose=False):
         f.write("\n".join(log))
     if verbose:
         print("\n".join(log))
-    subprocess.check_call([nvcc, "-shared", "-o", LIB] + objs + ["-cudart", "static"])
+    subprocess.check_call([nvcc, "-shared", "-o", LIB] + objs + ["-cudart", "static", "-ldl"])
     return LIB
 
 

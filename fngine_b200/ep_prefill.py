@@ -269,3 +269,50 @@ def ep_prefill_layer(logits_local, x_local, shard, ws, group=None, mode="dense",
     if mode == "dense":
         return ep_layer_dense(x_local, e, w, shard.rank, shard.world, compute, sum_ranks, group, chunks, combine)
     return ep_layer_generic(x_local, e, w, shard.rank, shard.world, compute, scatter_sum, group)
+
+
+# --------------------------------------------------------------------------------------------- one C call
+COMBINE_CODES = {"all_to_all": 0, "reduce_scatter": 1}
+
+
+def comm_pointer(group=None, device=None):
+    """The ncclComm_t of a torch.distributed NCCL process group as an integer, for fb_ep_prefill_layer. The group
+    creates its communicator at its first collective, so one small all-reduce runs first; the caller must not have
+    collectives of the same group in flight on other streams while the C entry point uses the communicator."""
+    import torch.distributed as dist
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    dist.all_reduce(torch.zeros(1, device=device), group=group)
+    torch.cuda.synchronize()
+    backend = (group or dist.group.WORLD)._get_backend(device)
+    return int(backend._comm_ptr())
+
+
+class EpPrefillScratch:
+    """Caller-owned device memory of fb_ep_prefill_layer for `tokens_local` tokens per rank."""
+
+    def __init__(self, tokens_local, world, combine="reduce_scatter", device="cuda"):
+        from . import lib as L
+        self.combine = COMBINE_CODES[combine]
+        n = L.load().fb_ep_prefill_scratch_bytes(tokens_local, world, self.combine)
+        if n == 0:
+            raise L.FbError("unsupported expert-parallel prefill shape")
+        self.buf = torch.empty(n + 256, dtype=torch.uint8, device=device)
+        self.base = (self.buf.data_ptr() + 255) & ~255
+        self.tokens_local, self.world = tokens_local, world
+
+
+def ep_prefill_layer_c(logits_local, x_local, shard, ws, scratch, y_local, comm=0):
+    """Mirror of fb_ep_prefill_layer: the whole dense-exchange layer (top-10, all-gather, this rank's experts,
+    combine) enqueued by one C call on the current stream; `comm` = comm_pointer() (0 with one rank)."""
+    import ctypes as C
+    from . import lib as L
+    from .moe import _ptr, _stream
+    assert x_local.dtype == torch.bfloat16 and y_local.dtype == torch.float32
+    assert x_local.shape[0] == scratch.tokens_local and shard.world == scratch.world
+    per = experts_per_rank(shard.world)
+    L.check(L.load().fb_ep_prefill_layer(C.byref(shard.layer.layout), _ptr(shard.blob_table), _ptr(shard.share),
+                                         shard.rank * per, (shard.rank + 1) * per, _ptr(logits_local),
+                                         logits_local.shape[-1], _ptr(x_local), x_local.shape[0], shard.world,
+                                         scratch.combine, C.byref(ws.ws), scratch.base, _ptr(y_local), comm, _stream()),
+            "ep_prefill_layer")
+    return y_local

@@ -119,6 +119,9 @@ _SIGNATURES = {
     "fb_moe_topk": (_I32, [_P, _I32, _I32, _P, _P, _P]),
     "fb_moe_route_ep": (_I32, [_P, _P, _I32, _I32, _I32, C.POINTER(PrefillWorkspace), _P]),
     "fb_moe_prefill_set_accumulation": (_I32, [_I32]),
+    "fb_ep_prefill_scratch_bytes": (C.c_size_t, [_I32, _I32, _I32]),
+    "fb_ep_prefill_layer": (_I32, [C.POINTER(ExpertLayout), _P, _P, _I32, _I32, _P, _I32, _P, _I32, _I32, _I32,
+                                   C.POINTER(PrefillWorkspace), _P, _P, _P, _P]),
     "fb_moe_route_placed": (_I32, [_P, _P, _P, _I32, C.POINTER(PrefillWorkspace), _P]),
     "fb_ep_scatter_sum": (_I32, [_P, _P, _I32, _I32, _P, _P]),
     "fb_moe_layer_decode_static": (_I32, [_P, C.POINTER(ExpertLayout), _P, _I32, _I32, _P, _P]),

@@ -325,6 +325,29 @@ int32_t fb_moe_layer_decode_ep_p2p(const void* router_w_bf16, const fb_moe_exper
                                    float* logits_scratch, float* y_local, void* stream);
 /* Combine on the owning rank: y[r] = parts[0][r] + parts[1][r] + ... (rank order), rows x 2560 fp32. */
 int32_t fb_ep_sum_ranks(const float* parts, int32_t n_ranks, int32_t rows, float* y, void* stream);
+/* One expert-parallel prefill layer with the dense exchange, the whole step behind one call (no reference
+ * counterpart: the reference is single-GPU). Every rank owns `tokens_local` consecutive tokens (the same count
+ * on every rank) and a shard of the experts. The call enqueues on `stream`: fb_moe_topk of the rank's tokens;
+ * an all-gather of the bf16 rows and of the (expert, weight) lists; fb_moe_route_placed (share != NULL: the
+ * rank's [512] share table) or fb_moe_route_ep over [expert_lo, expert_hi) on all tokens_local * n_ranks rows;
+ * the grouped gate/up and down GEMMs and the per-row sums over this rank's experts; then the combine:
+ * FB_EP_COMBINE_ALL_TO_ALL returns each owner the n_ranks partial rows of its tokens and adds them in rank
+ * order (fb_ep_sum_ranks; results are those of the single-GPU layer up to the parentheses of the fp32 sum),
+ * FB_EP_COMBINE_REDUCE_SCATTER lets the collective library add them on the way (one summed row per token
+ * arrives; the order of the additions is the library's). y_local: fp32 [tokens_local][2560].
+ * `comm` is an ncclComm_t of exactly n_ranks ranks whose rank r owns tokens [r * tokens_local, (r + 1) *
+ * tokens_local); the collective library is looked up in the process at the first call, not linked; with
+ * n_ranks == 1 nothing of it is touched and comm may be NULL. `expert_blob` is the device table of blob
+ * addresses by GLOBAL expert id (fb_moe_grouped_gate_up). `ws` must hold tokens_local * n_ranks rows;
+ * `scratch` is caller-owned device memory of fb_ep_prefill_scratch_bytes() bytes, 256-byte aligned. Nothing is
+ * allocated and nothing is read back on the host: the call may sit inside a longer stream of work. */
+enum { FB_EP_COMBINE_ALL_TO_ALL = 0, FB_EP_COMBINE_REDUCE_SCATTER = 1 };
+size_t fb_ep_prefill_scratch_bytes(int32_t tokens_local, int32_t n_ranks, int32_t combine);
+int32_t fb_ep_prefill_layer(const fb_moe_expert_layout* layout, const uint8_t* const* expert_blob, const int32_t* share,
+                            int32_t expert_lo, int32_t expert_hi, const float* router_logits, int32_t logits_stride,
+                            const void* x_bf16, int32_t tokens_local, int32_t n_ranks, int32_t combine,
+                            const fb_moe_prefill_workspace* ws, void* scratch, float* y_local, void* comm,
+                            void* stream);
 
 /* The decode layer for callers that may not allocate: no workspace, no logits scratch. This entry
  * point has no counterpart in the reference (whose kernels always take a caller workspace). It is

@@ -117,3 +117,34 @@ def test_static_status_needs_a_prior_static_call(fb_built):
     assert lib.fb_moe_layer_decode_static_status(None, None) == 1
     st = lib.fb_moe_layer_decode_static_status(ctypes.byref(out), None)
     assert st != 0 and out.value == 7
+
+
+def test_ep_prefill_layer_scratch_and_argument_checks(fb_built):
+    """fb_ep_prefill_layer refuses bad shapes before anything runs; the scratch grows with ranks and with the
+    all-to-all combine's receive buffer."""
+    import ctypes as C
+    from fngine_b200 import lib as L
+    lib = L.load()
+    f = lib.fb_ep_prefill_scratch_bytes
+    assert f(0, 2, 0) == 0 and f(64, 0, 0) == 0 and f(64, 9, 0) == 0
+    rows = 64 * 2
+    payload = rows * 2560 * 2 + rows * 2560 * 4 + 2 * rows * 40 + 2 * 64 * 40
+    assert payload <= f(64, 2, 1) <= payload + 8 * 256
+    assert f(64, 2, 0) - f(64, 2, 1) == rows * 2560 * 4
+    assert f(64, 1, 0) == f(64, 1, 1)  # one rank: nothing to receive
+    layout, ws = L.ExpertLayout(), L.PrefillWorkspace()
+    assert lib.fb_ep_prefill_layer(None, None, None, 0, 256, None, 512, None, 64, 2, 0, None, None, None, None, None) != 0
+    one = C.c_void_p(256)
+    ws.capacity = 64
+    args = lambda **kw: [C.byref(layout), one, kw.get("share"), kw.get("lo", 0), kw.get("hi", 256), one, 512, one,
+                         kw.get("tokens", 64), kw.get("ranks", 2), kw.get("combine", 0), C.byref(ws), kw.get("scratch", one),
+                         one, kw.get("comm"), None]
+    assert lib.fb_ep_prefill_layer(*args(ranks=9)) != 0
+    assert lib.fb_ep_prefill_layer(*args(combine=2)) != 0
+    assert lib.fb_ep_prefill_layer(*args(scratch=C.c_void_p(264))) != 0
+    assert lib.fb_ep_prefill_layer(*args()) != 0  # 128 rows in a workspace of 64
+    assert b"capacity" in lib.fb_last_error_string()
+    ws.capacity = 128
+    assert lib.fb_ep_prefill_layer(*args(lo=300, hi=200)) != 0
+    assert lib.fb_ep_prefill_layer(*args()) != 0  # two ranks, no communicator
+    assert b"communicator" in lib.fb_last_error_string()
