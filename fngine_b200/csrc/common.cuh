@@ -77,6 +77,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking probe of a phase: the instruction only reads the barrier, so its result can be consumed many
+// instructions later while independent work proceeds.
+__device__ __forceinline__ uint32_t mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
 // Returns false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < kSpinLimit; ++i)

@@ -89,9 +89,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// One arrival on `bar` (already counted in its expected arrivals) once every cp.async this thread has issued so far
+// is complete.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 
 // K-major bf16 tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
@@ -306,9 +309,13 @@ __device__ __forceinline__ void raw_prefetch(const uint8_t* warp_rows, int row_b
 // `tile_off` = byte offset of the A tile inside a ring stage, `row` = this thread's tile row and
 // `half` its half of the K step. `s`/`ph` = ring stage and phase, carried across units. After a
 // failed wait the remaining waits fall through at once (the abort flag is set), so the loop just
-// drains.
+// drains. `pre` holds the warp's raw words of this unit's first column on entry (raw_prefetch) and
+// those of `next_rows`' first column on return (next_rows = the warp's rows in its next unit, or
+// nullptr): the load is issued behind the last column's staging, so that a unit does not start with
+// a round trip to memory.
 template <int FMT, int STAGES>
-__device__ __forceinline__ void dequant_unit(const uint8_t* warp_rows, int row_bytes, int k_steps, uint8_t* raw,
+__device__ __forceinline__ void dequant_unit(const uint8_t* warp_rows, const uint8_t* next_rows, uint32_t (&pre)[16],
+                                             int row_bytes, int k_steps, uint8_t* raw,
                                              int slot0, uint8_t* ring, int stage_bytes, int tile_off, int row,
                                              int half, uint64_t* full, uint64_t* empty, int& s, uint32_t& ph,
                                              const Abort& ab, const uint16_t* seltab) {
@@ -323,8 +330,15 @@ __device__ __forceinline__ void dequant_unit(const uint8_t* warp_rows, int row_b
   const uint32_t slot = smem_u32(raw) + kRawBase + (slot0 + (lane >> 1)) * R::kStride;
   const uint32_t slot_h = slot + (FMT == FB_FMT_IQ3_S ? 8 : 18) * half, slot_hh = slot + 4 * half;
   const int shift0 = int(reinterpret_cast<uintptr_t>(warp_rows) & 3);
-  uint32_t pre[16];
-  raw_prefetch<FMT>(warp_rows, row_bytes, 0, lane, pre);
+  int pending = -1;  // stage whose tile rows are stored but not yet fenced and announced
+  auto publish_pending = [&]() {
+    if (pending >= 0) {
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full[pending]);
+      pending = -1;
+    }
+  };
   for (int col = 0; col < n_cols; ++col) {
     const int shift = (shift0 + col * R::kPiece) & 3;
     if (FMT == FB_FMT_IQ3_S && shift == 0) {
@@ -336,20 +350,28 @@ __device__ __forceinline__ void dequant_unit(const uint8_t* warp_rows, int row_b
     }
     __syncwarp();  // a warp stages and consumes only its own 16 rows
     if (col + 1 < n_cols) raw_prefetch<FMT>(warp_rows, row_bytes, col + 1, lane, pre);
+    else if (next_rows) raw_prefetch<FMT>(next_rows, row_bytes, 0, lane, pre);
     Iq3sColumn cc{};
     if constexpr (FMT == FB_FMT_IQ3_S) cc = iq3s_column(slot, half);
+    // One K step. Reading a barrier costs a few hundred cycles even when its phase is long complete, and so do
+    // the tile stores followed by the proxy fence; neither may sit on the decode's path, the longest chain of the
+    // kernel. So the stage's `empty` barrier is probed without blocking BEFORE the step is decoded (the answer is
+    // looked at after the decode; only a stage that was really still in use falls into the bounded wait), and a
+    // step's fence + arrival are issued after the NEXT step's decode, when its stores have long landed.
+    // (Decoding two steps per round of probe, fence and arrivals was measured and is slower: with three or four
+    // stages the later publication of the first step costs more than the saved synchronization.)
     auto step = [&](auto qc) {
       constexpr int Q = decltype(qc)::value;
-      uint32_t out[16];  // decoded before the stage is known to be free: the wait is off the decode's path
+      const uint32_t free_now = mbar_test_wait(&empty[s], ph ^ 1);
+      uint32_t out[16];
       if constexpr (FMT == FB_FMT_IQ3_S) dequant_sub_iq3s<Q>(slot_h, slot_hh, cc, seltab, out);
       else dequant_sub_iq4nl<36 * Q>(slot_h, out);
-      ab.wait(&empty[s], ph ^ 1);
+      publish_pending();
+      if (!free_now) ab.wait(&empty[s], ph ^ 1);
       const uint32_t tile_row = tile_row0 + s * stage_bytes;
 #pragma unroll
       for (int c = 0; c < 4; ++c) sts_v4(tile_row + coff[c], out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&full[s]);
+      pending = s;
       if (++s == STAGES) { s = 0; ph ^= 1; }
     };
     step(std::integral_constant<int, 0>{});
@@ -360,6 +382,7 @@ __device__ __forceinline__ void dequant_unit(const uint8_t* warp_rows, int row_b
     }
     __syncwarp();  // the warp is done with this column's pieces
   }
+  publish_pending();  // a unit's last step does not wait for the next unit's first decode
 }
 
 // Fills the 512-entry selector table of dequant_sub_iq3s from the packed codebook (3 bits per
@@ -523,7 +546,15 @@ struct GuBars {
 constexpr int kGuStage = 2 * kTileA + kTileB;                       // 64 KB
 constexpr int kGuRaw = 256 * kRawStrideMax + 16;  // staged raw pieces of the 256 weight rows
 constexpr int kGuSmem = kStagesGU * kGuStage + kGuRaw + sizeof(GuBars) + 1024;
-constexpr int kGuThreads = 23 * 32;  // warp 0 MMA, 1-2 gather, 3-18 dequant, 19-22 epilogue
+#ifndef GU_EPI
+#define GU_EPI 8
+#endif
+// warp 0 MMA, four gather warps, 16 dequant warps, the epilogue warps (a multiple of four: one or two per
+// tensor-memory lane quarter)
+constexpr int kGuGatherWarps = 4, kGuEpilogueWarps = GU_EPI;
+constexpr int kGuFirstDequant = 1 + kGuGatherWarps, kGuFirstEpilogue = kGuFirstDequant + 16;
+constexpr int kGuThreads = (kGuFirstEpilogue + kGuEpilogueWarps) * 32;
+constexpr int kGuRowsPerGather = kTileN / (4 * kGuGatherWarps);  // token rows a gather thread copies per K step
 
 template <int FMT>
 __global__ void __launch_bounds__(kGuThreads, 1)
@@ -546,12 +577,12 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
   iq3s_selector_table_fill(seltab, tid, kGuThreads);
   if (tid == 0) {
     for (int i = 0; i < kStagesGU; ++i) {
-      mbar_init(&bars->full[i], 18);  // 2 gather warps + 16 dequant warps
+      mbar_init(&bars->full[i], 32 * kGuGatherWarps + 16);  // gather threads (arrival tied to their copies) + dequant warps
       mbar_init(&bars->empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->tmem_full[i], 1);
-      mbar_init(&bars->tmem_empty[i], 4);
+      mbar_init(&bars->tmem_empty[i], kGuEpilogueWarps);
     }
     bars->abort = 0;
     mbar_fence_init();
@@ -584,7 +615,8 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
         for (int kb = 0; kb < kSteps; ++kb, ++it) {
           const int s = it % kStagesGU;
           if (!ab.wait(&bars->full[s], (it / kStagesGU) & 1)) { ok = false; break; }
-          uint8_t* st = ring + s * kGuStage;  // (the barrier orders the operand writes; no tcgen05 fence per K step)
+          fence_proxy_async();  // the token rows were written by cp.async (generic proxy), the MMA reads them through the async proxy
+          uint8_t* st = ring + s * kGuStage;
           const uint64_t dg = umma_desc_k128(smem_u32(st)), du = umma_desc_k128(smem_u32(st + kTileA));
           const uint64_t db = umma_desc_k128(smem_u32(st + 2 * kTileA));
 #pragma unroll
@@ -600,20 +632,24 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
         if (!wide) nb ^= 1u;
       }
     }
-  } else if (warp <= 2) {
-    // ---------------- token-row gather: 256 rows x 128 bytes per K step, 16-byte cp.async each.
-    // Thread tg copies chunk (tg & 7) of rows 8i + (tg >> 3), i < 32; it keeps those 32 token ids
-    // in registers for the whole unit.
-    const int tg = tid - 32;  // 0..63
+  } else if (warp < kGuFirstDequant) {
+    // ---------------- token-row gather: 256 rows x 128 bytes per K step, 16-byte cp.async each. Thread tg
+    // copies chunk (tg & 7) of rows (tg >> 3) + 16 i; it keeps those token ids in registers for the whole
+    // unit. A thread's arrival on the stage's barrier is tied to the completion of its copies, so it goes on to
+    // the next stage at once, as many stages ahead as the ring is free. (Measured alternatives: a TMA gather of
+    // four rows per instruction is correct and slower, 1.46 ms against 0.91 ms per layer - 64 small copies per
+    // K step; rows pre-gathered into pair order by an extra kernel and loaded as one TMA box per K step come to
+    // the same time as this and cost 420 MB of workspace.)
+    const int tg = tid - 32;
     const int c = tg & 7, nbase = tg >> 3;
+    constexpr int kRowStep = 4 * kGuGatherWarps;
     uint32_t it = 0;
-    int pending = -1;  // stage whose copies are committed but not yet published
     for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
       const int4 un = units[u];
-      int tok[32];
+      int tok[kGuRowsPerGather];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int n = 8 * i + nbase;
+      for (int i = 0; i < kGuRowsPerGather; ++i) {
+        const int n = kRowStep * i + nbase;
         tok[i] = n < un.w ? pair_token[un.z + n] : -1;
       }
       bool ok = true;
@@ -622,42 +658,40 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
         if (!ab.wait(&bars->empty[s], ((it / kStagesGU) & 1) ^ 1)) { ok = false; break; }
         uint8_t* tb = ring + s * kGuStage + 2 * kTileA;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int n = 8 * i + nbase;
+        for (int i = 0; i < kGuRowsPerGather; ++i) {
+          const int n = kRowStep * i + nbase;
           if (tok[i] >= 0) cp_async16(tb + swz(n, c), x + size_t(tok[i]) * H + kb * kBK + c * 8);
         }
-        cp_async_commit();
-        if (pending >= 0) {  // the previous stage's copies have landed once only one group is in flight
-          cp_async_wait<1>();
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars->full[pending]);
-        }
-        pending = s;
+        cp_async_arrive_noinc(&bars->full[s]);
       }
       if (!ok) break;
     }
-    if (pending >= 0) {
-      cp_async_wait<0>();
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->full[pending]);
-    }
-  } else if (warp <= 18) {
+    cp_async_wait_all();
+  } else if (warp < kGuFirstEpilogue) {
     // ---------------- dequant: warp = (matrix, 16 rows), lane = (row, half of the K step)
-    const int wd = warp - 3, mat = wd >> 3, row0 = (wd & 7) * 16;
+    const int wd = warp - kGuFirstDequant, mat = wd >> 3, row0 = (wd & 7) * 16;
     int s = 0;
     uint32_t ph = 0;
-    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+    auto rows_of = [&](int u) -> const uint8_t* {  // the warp's 16 rows in unit u (nullptr behind the last unit)
+      if (u >= n_units) return nullptr;
       const int4 un = units[u];
       const uint8_t* blob = expert_blob ? expert_blob[un.x] : L.slots + int64_t(un.x) * L.blob_stride;
-      const uint8_t* warp_rows = blob + (mat ? L.up_offset : L.gate_offset) + size_t(un.y + row0) * row_bytes;
-      dequant_unit<FMT, kStagesGU>(warp_rows, row_bytes, kSteps, raw, wd * 16, ring, kGuStage, mat * kTileA,
-                                   row0 + (lane >> 1), lane & 1, bars->full, bars->empty, s, ph, ab, seltab);
+      return blob + (mat ? L.up_offset : L.gate_offset) + size_t(un.y + row0) * row_bytes;
+    };
+    uint32_t pre[16];
+    const uint8_t* warp_rows = rows_of(blockIdx.x);
+    if (warp_rows) raw_prefetch<FMT>(warp_rows, row_bytes, 0, lane, pre);
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+      const uint8_t* next_rows = rows_of(u + gridDim.x);  // (read well before its use behind the unit's last column)
+      dequant_unit<FMT, kStagesGU>(warp_rows, next_rows, pre, row_bytes, kSteps, raw, wd * 16, ring, kGuStage,
+                                          mat * kTileA, row0 + (lane >> 1), lane & 1, bars->full, bars->empty, s, ph, ab,
+                                          seltab);
+      warp_rows = next_rows;
     }
   } else {
-    // ---------------- epilogue: lane quarter = warp % 4; thread = intermediate row j
-    const int q = warp & 3;
+    // ---------------- epilogue: lane quarter = warp % 4 (two warps per quarter, which take alternate chunks of 16
+    // tokens); thread = intermediate row j
+    const int q = warp & 3, chunk0 = 16 * ((warp - kGuFirstEpilogue) >> 2);
     uint32_t use0 = 0, use1 = 0, nb = 0;
     for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
       const int4 un = units[u];
@@ -670,7 +704,7 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
       const uint32_t gcol = tmem_base + (uint32_t(q * 32) << 16) + (wide ? 0u : nb * 256u);
       const uint32_t ucol = gcol + (wide ? 256u : 128u);
       const int j = un.y + q * 32 + lane;
-      for (int c0 = 0; c0 < un.w; c0 += 16) {
+      for (int c0 = chunk0; c0 < un.w; c0 += 4 * kGuEpilogueWarps) {
         uint32_t g[16], up[16];
         tmem_ld16(gcol + uint32_t(c0), g);
         tmem_ld16(ucol + uint32_t(c0), up);
@@ -715,7 +749,11 @@ constexpr int kDnSmem = kStagesDN * kDnStage + kDnRaw + sizeof(DnBars) + 1024;
 #ifndef PREFILL_FIXED_DEFAULT
 #define PREFILL_FIXED_DEFAULT 0
 #endif
-constexpr int kDnThreads = 14 * 32;  // warp 0 MMA, warp 1 TMA, 2-9 dequant, 10-13 epilogue
+#ifndef DN_EPI
+#define DN_EPI 8
+#endif
+constexpr int kDnEpilogueWarps = DN_EPI;               // a multiple of four: every lane quarter gets as many
+constexpr int kDnThreads = (10 + kDnEpilogueWarps) * 32;  // warp 0 MMA, warp 1 TMA, 2-9 dequant, the rest epilogue
 
 // yp[pair][n] = w_pair * (down_n . h[pair])
 template <int FMT>
@@ -745,7 +783,7 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->tmem_full[i], 1);
-      mbar_init(&bars->tmem_empty[i], 4);
+      mbar_init(&bars->tmem_empty[i], kDnEpilogueWarps);
     }
     bars->abort = 0;
     mbar_fence_init();
@@ -785,8 +823,10 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
     // ---------------- h rows of the unit's pairs: expert-sorted, so one TMA box per K step
     if (lane == 0) {
       uint32_t it = 0;
+      int4 un_next = blockIdx.x < n_units ? units[blockIdx.x] : make_int4(0, 0, 0, 0);
       for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
-        const int4 un = units[u];
+        const int4 un = un_next;
+        if (u + gridDim.x < n_units) un_next = units[u + gridDim.x];  // one unit ahead: off the copy path
         bool ok = true;
         for (int kb = 0; kb < k_steps; ++kb, ++it) {
           const int s = it % kStagesDN;
@@ -802,15 +842,23 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
     const int wd = warp - 2, row0 = wd * 16;
     int s = 0;
     uint32_t ph = 0;
-    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+    auto rows_of = [&](int u) -> const uint8_t* {  // the warp's 16 rows in unit u (nullptr behind the last unit)
+      if (u >= n_units) return nullptr;
       const int4 un = units[u];
       const uint8_t* blob = expert_blob ? expert_blob[un.x] : L.slots + int64_t(un.x) * L.blob_stride;
-      const uint8_t* warp_rows = blob + L.down_offset + size_t(un.y + row0) * row_bytes;
-      dequant_unit<FMT, kStagesDN>(warp_rows, row_bytes, k_steps, raw, row0, ring, kDnStage, 0, row0 + (lane >> 1),
-                                   lane & 1, bars->full, bars->empty, s, ph, ab, seltab);
+      return blob + L.down_offset + size_t(un.y + row0) * row_bytes;
+    };
+    uint32_t pre[16];
+    const uint8_t* warp_rows = rows_of(blockIdx.x);
+    if (warp_rows) raw_prefetch<FMT>(warp_rows, row_bytes, 0, lane, pre);
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+      const uint8_t* next_rows = rows_of(u + gridDim.x);  // (read well before its use behind the unit's last column)
+      dequant_unit<FMT, kStagesDN>(warp_rows, next_rows, pre, row_bytes, k_steps, raw, row0, ring, kDnStage, 0,
+                                                 row0 + (lane >> 1), lane & 1, bars->full, bars->empty, s, ph, ab, seltab);
+      warp_rows = next_rows;
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3, chunk0 = 32 * ((warp - 10) >> 2);  // the warps of a lane quarter take chunks of 32 tokens in turn
     uint32_t ul = 0;
     for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++ul) {
       const int4 un = units[u];
@@ -818,7 +866,7 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
       if (!ab.wait(&bars->tmem_full[acc], (ul >> 1) & 1)) break;
       tc_fence_after();
       const int n = un.y + q * 32 + lane;
-      for (int c0 = 0; c0 < un.w; c0 += 32) {
+      for (int c0 = chunk0; c0 < un.w; c0 += 8 * kDnEpilogueWarps) {
         uint32_t r[32];
         tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * 256 + c0), r);
         tmem_ld_wait();
@@ -1103,6 +1151,7 @@ int32_t fb_moe_grouped_gate_up(const fb_moe_expert_layout* layout, const uint8_t
     return int32_t(attr);
   }
   const int grid = sm_count();
+  if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return invalid("grouped_gate_up: x must be 16-byte aligned");
   const auto* xb = static_cast<const __nv_bfloat16*>(x_bf16);
   auto* hb = static_cast<__nv_bfloat16*>(ws->h);
   const auto* un = static_cast<const int4*>(ws->units_gate_up);
