@@ -46,12 +46,19 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
+// D[tmem] (+)= A * B, bf16 operands in shared memory. The operand descriptors are given by their low words (the
+// high word is the same for every tile of these kernels, see umma_desc_lo_k128): the issuing lane steps through a
+// stage's tiles and K slices with 32-bit adds.
+constexpr uint32_t kDescHiK128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ void umma_bf16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                             uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiK128)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -96,11 +103,14 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// K-major bf16 tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
-  return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
-         (uint64_t(1) << 46) | (uint64_t(2) << 61);
+// Shared-memory operand descriptor of a K-major bf16 tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024
+// bytes apart: low word = address / 16 | leading offset 1 << 16, high word (kDescHiK128) = stride 1024 / 16 |
+// descriptor version 1 << 14 | swizzle mode 2 << 29.
+__device__ __forceinline__ uint32_t umma_desc_lo_k128(uint32_t smem_addr) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
 }
+static_assert((uint64_t(kDescHiK128) << 32) == ((uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61)),
+              "descriptor high word");
 // D fp32, A and B bf16, both K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t idesc_bf16(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
@@ -600,6 +610,7 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
     // second), so its epilogue overlaps the next unit's K loop; a wider unit takes both (gate in
     // columns [0,256), up in [256,512)). The epilogue warps walk the same sequence.
     if (lane == 0) {
+      const uint32_t ring_lo = umma_desc_lo_k128(smem_u32(ring));
       uint32_t it = 0, use0 = 0, use1 = 0, nb = 0;
       for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
         const int4 un = units[u];
@@ -616,13 +627,17 @@ grouped_gate_up_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict_
           const int s = it % kStagesGU;
           if (!ab.wait(&bars->full[s], (it / kStagesGU) & 1)) { ok = false; break; }
           fence_proxy_async();  // the token rows were written by cp.async (generic proxy), the MMA reads them through the async proxy
-          uint8_t* st = ring + s * kGuStage;
-          const uint64_t dg = umma_desc_k128(smem_u32(st)), du = umma_desc_k128(smem_u32(st + kTileA));
-          const uint64_t db = umma_desc_k128(smem_u32(st + 2 * kTileA));
+          // low descriptor words of the stage's gate tile; the up tile and the token tile sit kTileA and 2 kTileA
+          // bytes on (descriptor addresses count 16 bytes)
+          const uint32_t lg = ring_lo + uint32_t(s) * (kGuStage >> 4);
+          constexpr uint32_t kUp = kTileA >> 4, kTok = (2 * kTileA) >> 4;
+          const uint32_t first = kb ? 1u : 0u;
+          umma_bf16_lo(gcol, lg, lg + kTok, idesc, first);
+          umma_bf16_lo(ucol, lg + kUp, lg + kTok, idesc, first);
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {  // 16 bf16 = 32 bytes of K per instruction
-            umma_bf16(gcol, dg + uint64_t(2 * k4), db + uint64_t(2 * k4), idesc, (kb | k4) ? 1u : 0u);
-            umma_bf16(ucol, du + uint64_t(2 * k4), db + uint64_t(2 * k4), idesc, (kb | k4) ? 1u : 0u);
+          for (int k4 = 1; k4 < 4; ++k4) {  // 16 bf16 = 32 bytes of K per instruction
+            umma_bf16_lo(gcol, lg + 2 * k4, lg + kTok + 2 * k4, idesc, 1u);
+            umma_bf16_lo(ucol, lg + kUp + 2 * k4, lg + kTok + 2 * k4, idesc, 1u);
           }
           umma_commit(&bars->empty[s]);
         }
@@ -796,6 +811,7 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
 
   if (warp == 0) {
     if (lane == 0) {
+      const uint32_t ring_lo = umma_desc_lo_k128(smem_u32(ring));
       uint32_t it = 0, ul = 0;
       for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++ul) {
         const int4 un = units[u];
@@ -807,12 +823,12 @@ grouped_down_kernel(fb_moe_expert_layout L, const uint8_t* const* __restrict__ e
         for (int kb = 0; kb < k_steps; ++kb, ++it) {
           const int s = it % kStagesDN;
           if (!ab.wait(&bars->full[s], (it / kStagesDN) & 1)) { ok = false; break; }
-          uint8_t* st = ring + s * kDnStage;
-          const uint64_t da = umma_desc_k128(smem_u32(st)), db = umma_desc_k128(smem_u32(st + kTileA));
+          const uint32_t la = ring_lo + uint32_t(s) * (kDnStage >> 4);  // low descriptor word of the stage's weight tile
+          constexpr uint32_t kTok = kTileA >> 4;
+          const uint32_t dcol = tmem_base + uint32_t(acc * 256);
+          umma_bf16_lo(dcol, la, la + kTok, idesc, kb ? 1u : 0u);
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4)
-            umma_bf16(tmem_base + uint32_t(acc * 256), da + uint64_t(2 * k4), db + uint64_t(2 * k4), idesc,
-                      (kb | k4) ? 1u : 0u);
+          for (int k4 = 1; k4 < 4; ++k4) umma_bf16_lo(dcol, la + 2 * k4, la + kTok + 2 * k4, idesc, 1u);
           umma_commit(&bars->empty[s]);
         }
         if (!ok) break;
